@@ -1,0 +1,166 @@
+/*
+ * qk_kernels.h - C ABI of libqk_kernels.so, the sm_100a implementation of the
+ * quantibbler-kernels hot path.
+ *
+ * Every entry point is what a Rust `extern "C"` block (or ctypes / cffi) binds in
+ * place of one item of the reference crate's API; the comment above each one names
+ * the reference item it replaces as file:line inside the reference project.
+ *
+ * Conventions
+ *  - Every function returns a qk_status; QK_OK is 0.  On failure the message is
+ *    readable through qk_last_error() on the calling thread until that thread's
+ *    next failing call.  No exception crosses the ABI.
+ *  - QK_ERR_VALUE carries the reference's KernelError text verbatim
+ *    (crates/quantibbler-kernels/src/core.rs:31-44); a Python binding raises
+ *    ValueError with it (crates/quantibbler-kernels/src/lib.rs:34-36).
+ *  - Inputs are borrowed for the duration of the call and never retained, except by
+ *    qk_layer_create / qk_model_* which copy them to the device.  Outputs are
+ *    caller-allocated.
+ *  - "host" pointers are ordinary process memory; "dev" pointers are CUDA device
+ *    memory on the context's device.  bfloat16 travels as uint16_t bit patterns
+ *    (crates/quantibbler-kernels/src/lib.rs:245-261).
+ *  - Products run on the GPU.  There is no CPU fallback: without a usable device the
+ *    product entry points fail with QK_ERR_INIT and the text of QK_GPU_INIT_HINT.
+ *  - A qk_ctx may be used from several host threads; calls on one context are
+ *    serialised on its stream.
+ */
+#ifndef QK_KERNELS_H
+#define QK_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t qk_status;
+enum {
+    QK_OK = 0,
+    QK_ERR_VALUE = 1,   /* validation failure: the reference's KernelError */
+    QK_ERR_INIT = 2,    /* no usable CUDA device / context creation failed */
+    QK_ERR_CUDA = 3,    /* a CUDA runtime call failed after start-up */
+    QK_ERR_TIMEOUT = 4, /* a bounded device-side wait gave up */
+    QK_ERR_ALLOC = 5
+};
+
+/* dtype tags: crates/quantibbler-kernels/src/dtype.rs:99-129 (Dtype, NAMES). */
+enum { QK_F64 = 0, QK_F32 = 1, QK_BF16 = 2 };
+
+typedef struct qk_ctx qk_ctx;
+typedef struct qk_layer qk_layer;
+
+/* Thread-local text of the last failure on this thread ("" if none). */
+const char *qk_last_error(void);
+
+/* crates/quantibbler-kernels/src/lib.rs:86-89 (backend_version). */
+const char *qk_backend_version(void);
+
+/* crates/quantibbler-kernels/src/gpu.rs:36-40 (GPU_INIT_HINT): the actionable text
+ * embedded in every initialisation failure, here naming the CUDA requirements. */
+const char *qk_gpu_init_hint(void);
+
+/* ---- integer bitplane core (host) ------------------------------------------ */
+
+/* core.rs:129-162 (pack_bits).  factor is row-major n_rows x n_cols of +-1; out
+ * holds n_rows * ceil(n_cols/8) bytes. */
+qk_status qk_pack_bits(const int8_t *factor, size_t factor_len, size_t n_rows, size_t n_cols,
+                       uint8_t *out, size_t out_len);
+/* lib.rs:93-116 (the PyO3 pack_bits): float64 values, anything but exactly +-1.0 is
+ * rejected before packing. */
+qk_status qk_pack_bits_f64(const double *factor, size_t factor_len, size_t n_rows,
+                           size_t n_cols, uint8_t *out, size_t out_len);
+/* core.rs:166-189 (unpack_bits). */
+qk_status qk_unpack_bits(const uint8_t *packed, size_t packed_len, size_t n_rows, size_t n_bits,
+                         int8_t *out, size_t out_len);
+/* core.rs:193-197 (sign_estimate). */
+qk_status qk_sign_estimate(const double *x, size_t n, int8_t *out);
+/* core.rs:223-240 (validate_packed). */
+qk_status qk_validate_packed(size_t packed_len, size_t n_rows, size_t n_bits, size_t *n_words);
+/* dtype.rs:106-119 (Dtype::from_name) and :121-128 (Dtype::name). */
+qk_status qk_dtype_from_name(const char *name, int32_t *dtype);
+const char *qk_dtype_name(int32_t dtype);
+/* crates/quantibbler-server/src/engine/mod.rs:258-273 (container_to_rows) and
+ * :277-289 (container_to_rows_transposed): container bit stream -> per-row planes. */
+qk_status qk_container_to_rows(const uint8_t *packed, size_t packed_len, size_t n_rows, size_t r,
+                               uint8_t *out, size_t out_len);
+qk_status qk_container_to_rows_transposed(const uint8_t *packed, size_t packed_len, size_t din,
+                                          size_t r, uint8_t *out, size_t out_len);
+
+/* ---- device context --------------------------------------------------------- */
+
+/* gpu.rs:187-189 (gpu_available): 1 if a context can be created on device 0. */
+int32_t qk_gpu_available(void);
+/* gpu.rs:85-101 (GpuContext::init_at, ::init).  *out receives an owned context. */
+qk_status qk_gpu_init_at(size_t device_index, qk_ctx **out);
+qk_status qk_gpu_init(qk_ctx **out);
+void qk_gpu_free(qk_ctx *ctx);
+/* Blocks until every call issued on the context has finished on the device. */
+qk_status qk_gpu_synchronize(qk_ctx *ctx);
+/* The CUDA stream (cudaStream_t) the context launches on, for event timing. */
+void *qk_gpu_stream(qk_ctx *ctx);
+/* Make the context launch on a caller-owned stream (cudaStream_t; NULL restores the
+ * context's own stream).  Lets a host framework order these kernels with its own work
+ * without a device-wide synchronisation. */
+qk_status qk_gpu_set_stream(qk_ctx *ctx, void *stream);
+
+/* ---- packed products, host buffers in and out -------------------------------- */
+
+/* gpu.rs:116-183 (GpuContext::packed_matvec): float64, strictly sequential
+ * accumulation per row, bit-identical to the CPU faces.  Validation happens before
+ * any device work; zero-size work returns zeros without a launch. */
+qk_status qk_gpu_packed_matvec(qk_ctx *ctx, const uint8_t *packed, size_t packed_len,
+                               size_t n_rows, size_t n_bits, const double *vec, size_t vec_len,
+                               double *out);
+/* core.rs:247-260 (packed_matvec::<T>) / dispatch.rs:81-93 (packed_matvec_dyn) /
+ * lib.rs:292-321 (packed_matvec_dtype).  vec and out have the tagged dtype; the
+ * accumulation is sequential in the dtype's accumulator (f64, f32, f32) and the
+ * result is bit-identical to the reference's.  ctx may be NULL: a process-wide
+ * context on device 0 is created on first use. */
+qk_status qk_packed_matvec(qk_ctx *ctx, const uint8_t *packed, size_t packed_len, size_t n_rows,
+                           size_t n_bits, int32_t dtype, const void *vec, size_t vec_len,
+                           void *out);
+/* core.rs:288-317 (packed_matmul::<T>) / dispatch.rs:96-109 / lib.rs:326-381.
+ * mat is addressed mat[t*n_cols + j]; the output is n_rows x (mat_len / n_bits). */
+qk_status qk_packed_matmul(qk_ctx *ctx, const uint8_t *packed, size_t packed_len, size_t n_rows,
+                           size_t n_bits, int32_t dtype, const void *mat, size_t mat_len,
+                           size_t n_cols, void *out, size_t out_len);
+
+/* ---- the factorized linear with device-resident factors ----------------------
+ * Replaces crates/quantibbler-server/src/engine/mod.rs:313-381 (PackedLayer,
+ * PackedLayer::from_layer) and :393-480 (apply, apply_bf16, kernel_matvec).  The
+ * reference re-reads its factors from host memory on every call; here they are
+ * uploaded once and re-tiled for the GEMV kernels. */
+
+/* ub_rows: dout x ceil(r/8) bytes; vb_t_rows: r x ceil(din/8) bytes (per-row
+ * bitplanes, as PackedLayer holds them); s1[dout], s2[din] float32; bias[dout]
+ * float32 or NULL (the all-zero bias of a version-1 stream).  serving_dtype is QK_F32
+ * (ServingDtype::Fp32) or QK_BF16 (ServingDtype::Bf16). */
+qk_status qk_layer_create(qk_ctx *ctx, const uint8_t *ub_rows, size_t ub_len,
+                          const uint8_t *vb_t_rows, size_t vb_t_len, size_t dout, size_t din,
+                          size_t r, const float *s1, const float *s2, const float *bias,
+                          int32_t serving_dtype, qk_layer **out);
+void qk_layer_free(qk_layer *layer);
+/* y[n_tokens x dout] = layer(x[n_tokens x din]), float32 row-major device buffers.
+ * Asynchronous on the context's stream. */
+qk_status qk_layer_apply(qk_ctx *ctx, const qk_layer *layer, const float *x_dev, size_t n_tokens,
+                         float *y_dev);
+/* The same with host buffers: x is copied in, y is copied out, and the call returns
+ * when y is complete.  This is the drop-in for PackedLayer::apply. */
+qk_status qk_layer_apply_host(qk_ctx *ctx, const qk_layer *layer, const float *x, size_t x_len,
+                              float *y, size_t y_len);
+/* n_layers independent layers of identical shape, layer i reading x_dev + i*din and
+ * writing y_dev + i*dout, in one pair of launches (how q/k/v or gate/up share a
+ * launch, and how the bandwidth benchmark streams more bytes than the L2 holds). */
+qk_status qk_layers_apply_group(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers,
+                                const float *x_dev, float *y_dev);
+/* Which GEMV kernel qk_layer_apply uses: 0 = sign-select SIMT, 1 = bit-sliced INT8
+ * tensor-core.  Returns the previous value; values out of range leave it unchanged. */
+int32_t qk_set_gemv_kernel(qk_ctx *ctx, int32_t which);
+/* Number of kernels launched on this context since creation (for benchmarks). */
+uint64_t qk_gpu_launch_count(qk_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QK_KERNELS_H */

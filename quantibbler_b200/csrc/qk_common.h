@@ -1,0 +1,81 @@
+// Internal declarations shared by the translation units of libqk_kernels.so.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/qk_kernels.h"
+
+namespace qk {
+
+// Thread-local error text behind qk_last_error().
+void set_error(const char *fmt, ...) __attribute__((format(printf, 1, 2)));
+qk_status fail(qk_status code, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
+
+// Index ceiling of the device kernels' 32-bit address arithmetic
+// (crates/quantibbler-kernels/src/gpu.rs:42-45, GPU_INDEX_CEILING).
+constexpr uint64_t kIndexCeiling = 0xFFFFFFFFull;
+
+inline size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
+
+// Shared validation of a packed operand (core.rs:223-240); sets the error text.
+qk_status validate_packed(size_t packed_len, size_t n_rows, size_t n_bits, size_t *n_words);
+
+#define QK_CUDA(call)                                                                   \
+    do {                                                                                \
+        cudaError_t e__ = (call);                                                       \
+        if (e__ != cudaSuccess)                                                         \
+            return qk::fail(QK_ERR_CUDA, "CUDA call %s failed: %s", #call,              \
+                            cudaGetErrorString(e__));                                   \
+    } while (0)
+
+}  // namespace qk
+
+// A device buffer that grows on demand and is reused between calls.
+struct qk_scratch {
+    void *ptr = nullptr;
+    size_t cap = 0;
+    qk_status reserve(size_t bytes);
+    void release();
+};
+
+struct qk_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;      // the stream calls launch on
+    cudaStream_t own_stream = nullptr;  // created with the context
+    std::mutex mu;  // serialises calls from several host threads
+    int sm_count = 0;
+    int gemv_kernel = 0;
+    std::atomic<uint64_t> launches{0};
+    // staging for the host-buffer entry points
+    qk_scratch d_packed, d_in, d_out;
+    // intermediates of the factorized linear (z and t) and of grouped applies
+    qk_scratch d_z, d_t, d_ptrs;
+    void *h_pinned = nullptr;
+    size_t h_pinned_cap = 0;
+    qk_status pinned(size_t bytes, void **out);
+};
+
+struct qk_layer {
+    int device = 0;
+    size_t dout = 0, din = 0, r = 0;
+    int serving = QK_F32;
+    // per-row bitplanes, rows padded to a multiple of 16 bytes (zero pad bits)
+    uint8_t *ub = nullptr;    // dout rows x ub_stride bytes
+    uint8_t *vbt = nullptr;   // r rows x vbt_stride bytes
+    size_t ub_stride = 0, vbt_stride = 0;
+    float *s1 = nullptr, *s2 = nullptr, *bias = nullptr;  // bias may be null
+};
+
+namespace qk {
+// Returns the context to use for a call: `ctx` itself, or the process-wide default on
+// device 0 (created on first use) when `ctx` is null.
+qk_status resolve_ctx(qk_ctx *ctx, qk_ctx **out);
+}  // namespace qk

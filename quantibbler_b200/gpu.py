@@ -1,0 +1,202 @@
+"""Host-side mirror of the reference's device face and factorized-linear layer.
+
+``GpuContext`` mirrors crates/quantibbler-kernels/src/gpu.rs:76-184 (``init``,
+``init_at``, ``packed_matvec``) and gpu_attention.rs:451-756 (``attention``,
+``attention_sage``); ``AttentionShape`` mirrors gpu_attention.rs:402-411;
+``PackedLayer`` mirrors crates/quantibbler-server/src/engine/mod.rs:313-480.  Names,
+argument meaning and error behaviour follow the reference; the arithmetic runs in
+libqk_kernels.so.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib
+from ._lib import QK_BF16, QK_F32, DeviceError, KernelError, check
+
+GPU_INDEX_CEILING = 0xFFFFFFFF  # gpu.rs:42-45
+
+
+def gpu_init_hint() -> str:
+    """gpu.rs:36-40 (GPU_INIT_HINT), naming the CUDA requirements."""
+    return _lib.lib().qk_gpu_init_hint().decode()
+
+
+def gpu_available() -> bool:
+    """gpu.rs:187-189."""
+    return bool(_lib.lib().qk_gpu_available())
+
+
+@dataclass(frozen=True)
+class AttentionShape:
+    """gpu_attention.rs:402-411."""
+    batch: int
+    n_heads: int
+    n_kv_heads: int
+    seq_q: int
+    seq_kv: int
+    head_dim: int
+    val_dim: int
+
+
+def _f(a, dtype):
+    return np.ascontiguousarray(np.asarray(a, dtype=dtype))
+
+
+class GpuContext:
+    """A live CUDA context on one device (gpu.rs:76-113).
+
+    Construction fails closed: every failure raises ``DeviceError`` with
+    ``gpu_init_hint()`` embedded.  Safe to share between host threads.
+    """
+
+    def __init__(self, handle):
+        self._h = handle
+
+    @classmethod
+    def init_at(cls, device_index: int) -> "GpuContext":
+        h = ctypes.c_void_p()
+        check(_lib.lib().qk_gpu_init_at(int(device_index), ctypes.byref(h)))
+        return cls(h)
+
+    @classmethod
+    def init(cls) -> "GpuContext":
+        return cls.init_at(0)
+
+    def close(self) -> None:
+        if self._h:
+            _lib.lib().qk_gpu_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    def synchronize(self) -> None:
+        check(_lib.lib().qk_gpu_synchronize(self._h))
+
+    @property
+    def stream(self) -> int:
+        return int(_lib.lib().qk_gpu_stream(self._h) or 0)
+
+    def set_stream(self, cuda_stream: int | None) -> None:
+        check(_lib.lib().qk_gpu_set_stream(self._h, ctypes.c_void_p(cuda_stream or 0)))
+
+    def set_gemv_kernel(self, which: int) -> int:
+        return int(_lib.lib().qk_set_gemv_kernel(self._h, int(which)))
+
+    @property
+    def launch_count(self) -> int:
+        return int(_lib.lib().qk_gpu_launch_count(self._h))
+
+    def packed_matvec(self, packed, n_rows: int, n_bits: int, vec) -> np.ndarray:
+        """float64 ``unpack(packed) @ vec`` on the device (gpu.rs:116-183)."""
+        p = _f(packed, np.uint8).ravel()
+        v = _f(vec, np.float64).ravel()
+        out = np.zeros(int(n_rows), dtype=np.float64)
+        check(_lib.lib().qk_gpu_packed_matvec(self._h, p.ctypes.data, p.size, int(n_rows),
+                                              int(n_bits), v.ctypes.data, v.size,
+                                              out.ctypes.data))
+        return out
+
+
+class PackedLayer:
+    """Device-resident factorized linear (engine/mod.rs:313-381).
+
+    ``ub_rows`` is ``dout x ceil(r/8)`` and ``vb_t_rows`` is ``r x ceil(din/8)`` uint8, the
+    per-row bitplanes the reference's ``PackedLayer`` holds; ``serving`` is ``"float32"``
+    or ``"bfloat16"`` (``ServingDtype``).
+    """
+
+    def __init__(self, ctx: GpuContext, ub_rows, vb_t_rows, dout: int, din: int, r: int, s1, s2,
+                 bias=None, serving: str = "float32", name: str = ""):
+        if serving not in ("float32", "bfloat16"):
+            raise KernelError(f"serving dtype must be float32 or bfloat16, got {serving!r}")
+        self.ctx, self.name = ctx, name
+        self.dout, self.din, self.r, self.serving = int(dout), int(din), int(r), serving
+        ub = _f(ub_rows, np.uint8).ravel()
+        vbt = _f(vb_t_rows, np.uint8).ravel()
+        s1 = _f(s1, np.float32).ravel()
+        s2 = _f(s2, np.float32).ravel()
+        if s1.size != self.dout or s2.size != self.din:
+            raise KernelError(f"layer {name}: scale lengths {s1.size}/{s2.size} do not match "
+                              f"dout={dout}, din={din}")
+        b = None
+        if bias is not None and np.size(bias):
+            b = _f(bias, np.float32).ravel()
+            if b.size != self.dout:  # engine/mod.rs:357-363
+                raise KernelError(
+                    f"layer {name}: bias has {b.size} entries; expected dout={dout}")
+        h = ctypes.c_void_p()
+        check(_lib.lib().qk_layer_create(
+            ctx.handle, ub.ctypes.data, ub.size, vbt.ctypes.data, vbt.size, self.dout, self.din,
+            self.r, s1.ctypes.data, s2.ctypes.data, b.ctypes.data if b is not None else None,
+            QK_F32 if serving == "float32" else QK_BF16, ctypes.byref(h)))
+        self._h = h
+
+    @classmethod
+    def from_container(cls, ctx, ub_packed, vb_packed, dout, din, r, s1, s2, bias=None,
+                       serving="float32", name=""):
+        """engine/mod.rs:342-381 (from_layer): container bit streams -> per-row planes."""
+        ub = _f(ub_packed, np.uint8).ravel()
+        vb = _f(vb_packed, np.uint8).ravel()
+        ub_rows = np.zeros(dout * ((r + 7) // 8), np.uint8)
+        vb_t_rows = np.zeros(r * ((din + 7) // 8), np.uint8)
+        check(_lib.lib().qk_container_to_rows(ub.ctypes.data, ub.size, dout, r,
+                                              ub_rows.ctypes.data, ub_rows.size))
+        check(_lib.lib().qk_container_to_rows_transposed(vb.ctypes.data, vb.size, din, r,
+                                                         vb_t_rows.ctypes.data, vb_t_rows.size))
+        return cls(ctx, ub_rows, vb_t_rows, dout, din, r, s1, s2, bias, serving, name)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            _lib.lib().qk_layer_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    def apply(self, x) -> np.ndarray:
+        """``y = s1*(Ub(Vb^T(s2*x))) + bias`` for one token, host arrays in and out
+        (engine/mod.rs:393-437 and :449-460)."""
+        xv = _f(x, np.float32).ravel()
+        if xv.size != self.din:
+            raise KernelError(
+                f"layer {self.name} expects input dim {self.din}, got {xv.size}")
+        y = np.zeros(self.dout, dtype=np.float32)
+        check(_lib.lib().qk_layer_apply_host(self.ctx.handle, self._h, xv.ctypes.data, xv.size,
+                                             y.ctypes.data, y.size))
+        return y
+
+    def apply_device(self, x_ptr: int, n_tokens: int, y_ptr: int) -> None:
+        """Asynchronous apply on device buffers (float32, row-major tokens)."""
+        check(_lib.lib().qk_layer_apply(self.ctx.handle, self._h, ctypes.c_void_p(x_ptr),
+                                        int(n_tokens), ctypes.c_void_p(y_ptr)))
+
+
+def apply_group(ctx: GpuContext, layers, x_ptr: int, y_ptr: int) -> None:
+    """Same-shape layers in one pair of launches; layer i reads x + i*din floats."""
+    arr = (ctypes.c_void_p * len(layers))(*[l.handle for l in layers])
+    check(_lib.lib().qk_layers_apply_group(ctx.handle, arr, len(layers), ctypes.c_void_p(x_ptr),
+                                           ctypes.c_void_p(y_ptr)))
+
+
+__all__ = ["GpuContext", "AttentionShape", "PackedLayer", "apply_group", "gpu_available",
+           "gpu_init_hint", "GPU_INDEX_CEILING", "KernelError", "DeviceError"]

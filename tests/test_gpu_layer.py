@@ -1,0 +1,152 @@
+"""GPU parity of the device-resident factorized linear through the C ABI."""
+
+import ctypes
+
+import numpy as np
+import pytest
+
+import oracle
+from conftest import golden, make_layer
+from quantibbler_b200.gpu import PackedLayer, apply_group
+
+pytestmark = pytest.mark.gpu
+
+# crates/quantibbler-kernels/tests/parity.rs:795,806: backward bounds on sum|v_k|
+F32_BACKWARD = 1e-6
+BF16_BACKWARD = 1e-2
+
+
+def backward_scale(L):
+    """Upper bound of sum_k |term| for each output of the two-stage product."""
+    z = np.abs(L["s2"].astype(np.float64) * L["x"].astype(np.float64))
+    t_abs = np.full(L["r"], z.sum())             # |t_j| <= sum|z|
+    return np.abs(L["s1"].astype(np.float64)) * t_abs.sum()  # |y_i| <= s1_i * sum_j |t_j|
+
+
+def exact_layer(L):
+    z = (L["s2"] * L["x"]).astype(np.float32).astype(np.float64)
+    t = oracle.unpack_signs(L["vb_t_rows"], L["din"]) @ z
+    u = oracle.unpack_signs(L["ub_rows"], L["r"]) @ t
+    y = u * L["s1"].astype(np.float64)
+    if L["bias"] is not None:
+        y = y + L["bias"]
+    return y, t
+
+
+def check_layer(ctx, L, serving):
+    layer = PackedLayer(ctx, L["ub_rows"], L["vb_t_rows"], L["dout"], L["din"], L["r"], L["s1"],
+                        L["s2"], L["bias"], serving=serving)
+    y = layer.apply(L["x"])
+    want = oracle.layer_apply(L["ub_rows"], L["vb_t_rows"], L["dout"], L["din"], L["r"], L["s1"],
+                              L["s2"], L["bias"], L["x"], serving=serving)
+    exact, t = exact_layer(L)
+    # stage-wise backward bound: each output's error is measured against the magnitude
+    # scale of the terms that were summed to make it
+    term_scale = np.abs(L["s1"].astype(np.float64)) * np.abs(t).sum()
+    tol = F32_BACKWARD if serving == "float32" else BF16_BACKWARD
+    # two chained products: stage-1 error propagates through stage 2
+    err = np.abs(y.astype(np.float64) - want.astype(np.float64))
+    assert (err / np.maximum(term_scale, 1e-300)).max() <= 2 * tol, serving
+    # the BASELINE bound: max error relative to the largest reference output
+    rel = err.max() / np.abs(want).max()
+    assert rel <= (2e-3 if serving == "float32" else 2e-2), (serving, rel)
+    # run-to-run bit identity
+    assert np.array_equal(layer.apply(L["x"]), y)
+    layer.close()
+    return y, want
+
+
+@pytest.mark.parametrize("serving", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["small", "odd", "mid"])
+def test_golden_layers(gpu_ctx, key, serving):
+    g = golden("layer")
+    m = g.meta[key]
+    L = dict(ub_rows=g[key + "_ub_rows"], vb_t_rows=g[key + "_vb_t_rows"], s1=g[key + "_s1"],
+             s2=g[key + "_s2"], x=g[key + "_x"], bias=g[key + "_bias"] if m["bias"] else None,
+             dout=m["dout"], din=m["din"], r=m["r"])
+    y, want = check_layer(gpu_ctx, L, serving)
+    gold = g[key + ("_y_f32" if serving == "float32" else "_y_bf16")]
+    assert np.array_equal(want, gold)
+
+
+@pytest.mark.parametrize("serving", ["float32", "bfloat16"])
+def test_config0_layer_against_reference_vector(gpu_ctx, serving):
+    g = golden("layer")
+    m = g.meta["config0"]
+    L = make_layer(m["dout"], m["din"], m["r"], m["seed"])
+    layer = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], L["dout"], L["din"], L["r"],
+                        L["s1"], L["s2"], None, serving=serving)
+    y = layer.apply(L["x"])
+    gold = g["config0_y_f32" if serving == "float32" else "config0_y_bf16"]
+    rel = np.abs(y.astype(np.float64) - gold).max() / np.abs(gold).max()
+    assert rel <= (2e-5 if serving == "float32" else 2e-2), rel
+    if serving == "float32":
+        t = g["config0_t_f64"]
+        scale = np.abs(L["s1"].astype(np.float64)) * np.abs(t).sum()
+        assert (np.abs(y - gold) / scale).max() <= 2 * F32_BACKWARD
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1), (8, 8, 8), (33, 129, 17), (300, 4097, 130),
+                                   (64, 14336, 96), (4096, 300, 1102)])
+def test_odd_shapes(gpu_ctx, shape):
+    dout, din, r = shape
+    L = make_layer(dout, din, r, seed=dout + din + r, with_bias=(dout % 2 == 0))
+    check_layer(gpu_ctx, L, "float32")
+    check_layer(gpu_ctx, L, "bfloat16")
+
+
+def test_dirty_pad_bits_are_ignored(gpu_ctx):
+    # crates/quantibbler-kernels/tests/fixtures/packed_matvec.json (packed_dirty): bits
+    # beyond n_bits in the last byte of a row must not change any result
+    L = make_layer(24, 21, 13, seed=77)
+    clean = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], 24, 21, 13, L["s1"], L["s2"])
+    ub_dirty = L["ub_rows"].copy()
+    ub_dirty[:, -1] |= 0xE0
+    vbt_dirty = L["vb_t_rows"].copy()
+    vbt_dirty[:, -1] |= 0xE0
+    dirty = PackedLayer(gpu_ctx, ub_dirty, vbt_dirty, 24, 21, 13, L["s1"], L["s2"])
+    assert np.array_equal(clean.apply(L["x"]), dirty.apply(L["x"]))
+
+
+def test_group_apply_matches_single(gpu_ctx):
+    import torch
+    n = 5
+    layers, xs, want = [], [], []
+    for i in range(n):
+        L = make_layer(128, 256, 64, seed=100 + i, with_bias=True)
+        layer = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], 128, 256, 64, L["s1"], L["s2"],
+                            L["bias"])
+        layers.append(layer)
+        xs.append(L["x"])
+        want.append(layer.apply(L["x"]))
+    x = torch.from_numpy(np.stack(xs)).cuda()
+    y = torch.zeros(n, 128, device="cuda")
+    torch.cuda.synchronize()
+    apply_group(gpu_ctx, layers, x.data_ptr(), y.data_ptr())
+    gpu_ctx.synchronize()
+    assert np.array_equal(y.cpu().numpy(), np.stack(want))
+
+
+def test_multi_token_apply(gpu_ctx):
+    import torch
+    L = make_layer(96, 160, 72, seed=11, with_bias=True)
+    layer = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], 96, 160, 72, L["s1"], L["s2"],
+                        L["bias"])
+    rng = np.random.default_rng(4)
+    xs = rng.standard_normal((7, 160)).astype(np.float32)
+    want = np.stack([layer.apply(x) for x in xs])
+    x = torch.from_numpy(xs).cuda()
+    y = torch.zeros(7, 96, device="cuda")
+    torch.cuda.synchronize()
+    layer.apply_device(x.data_ptr(), 7, y.data_ptr())
+    gpu_ctx.synchronize()
+    assert np.array_equal(y.cpu().numpy(), want)
+
+
+def test_layer_validation(gpu_ctx):
+    L = make_layer(16, 24, 8, seed=1)
+    with pytest.raises(ValueError, match="bitplane length mismatch after repack"):
+        PackedLayer(gpu_ctx, L["ub_rows"][:-1], L["vb_t_rows"], 16, 24, 8, L["s1"], L["s2"])
+    layer = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], 16, 24, 8, L["s1"], L["s2"])
+    with pytest.raises(ValueError, match="expects input dim 24, got 23"):
+        layer.apply(np.zeros(23, np.float32))

@@ -1,0 +1,144 @@
+"""Host side of the C-ABI library: it loads, exports what the header declares, and its
+integer core and error texts match the reference.  No GPU needed, no compute calls."""
+
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, golden
+from quantibbler_b200 import _build, _lib, kernels
+from quantibbler_b200._lib import DeviceError, KernelError
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "qk_kernels.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(qk_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_builds_and_exports_every_declared_symbol():
+    path = _build.build()
+    handle = ctypes.CDLL(path)
+    declared = header_symbols()
+    assert len(declared) >= 25
+    for name in declared:
+        assert hasattr(handle, name), f"{name} declared in qk_kernels.h but not exported"
+    assert sorted(_lib.exported_symbols()) == declared
+
+
+def test_pack_unpack_golden_bytes():
+    g = golden("bitplanes")
+    for key in g.cases("pack"):
+        factor, packed = g[key + "_factor"], g[key + "_packed"]
+        n_bits = g.meta[key]["n_bits"]
+        if factor.ndim < 2 or factor.shape[-1] != n_bits:
+            continue
+        got = kernels.pack_bits(factor)
+        assert got.dtype == np.uint8 and np.array_equal(got, packed), key
+        assert np.array_equal(kernels.pack_bits(factor.astype(np.float64)), packed)
+        back = kernels.unpack_bits(packed, n_bits, "int8")
+        assert back.dtype == np.int8 and np.array_equal(back, factor)
+        assert kernels.unpack_bits(packed, n_bits, "float64").dtype == np.float64
+
+
+def test_pack_any_dimensionality_and_degenerate_shapes():
+    rng = np.random.default_rng(1)
+    f = rng.choice(np.array([-1, 1], dtype=np.int8), size=(2, 3, 11))
+    p = kernels.pack_bits(f)
+    assert p.shape == (6, 2)
+    assert np.array_equal(kernels.unpack_bits(p, 11), f.reshape(6, 11))
+    assert kernels.pack_bits(np.zeros((2, 0), np.int8)).shape == (2, 0)
+    assert kernels.pack_bits(np.zeros((0, 7), np.int8)).shape == (0, 1)
+    assert kernels.unpack_bits(np.zeros((3, 0), np.uint8), 0).shape == (3, 0)
+
+
+def test_error_texts_match_reference():
+    # crates/quantibbler-kernels/tests/parity.rs:1062-1081 pins these as values
+    with pytest.raises(ValueError, match=r"pack_bits expects values in \{-1, \+1\}; got 0 at row 1, "
+                                         r"column 2"):
+        kernels.pack_bits(np.array([[1, -1, 1], [1, 1, 0]], dtype=np.int8))
+    with pytest.raises(ValueError, match=r"got 1\.0001$"):
+        kernels.pack_bits(np.array([[1.0, 1.0001]]))
+    with pytest.raises(ValueError, match=r"got 2\.0$"):
+        kernels.pack_bits(np.array([[2.0, 1.0]]))
+    with pytest.raises(ValueError, match=r"n_bits=17 exceeds the packed width 2 \(16 bits\)"):
+        kernels.unpack_bits(np.zeros((1, 2), np.uint8), 17)
+    with pytest.raises(ValueError, match=r"unpack_bits dtype must be 'int8' or 'float64'"):
+        kernels.unpack_bits(np.zeros((1, 2), np.uint8), 9, "int32")
+    lib = _lib.lib()
+    n_words = ctypes.c_size_t()
+    assert lib.qk_validate_packed(6, 3, 13, ctypes.byref(n_words)) == 0 and n_words.value == 2
+    assert lib.qk_validate_packed(5, 3, 13, ctypes.byref(n_words)) == _lib.QK_ERR_VALUE
+    assert _lib.last_error() == "packed length 5 does not match 3 rows x 2 bitplanes"
+    assert lib.qk_validate_packed(4, 2, 0, ctypes.byref(n_words)) == _lib.QK_ERR_VALUE
+    assert _lib.last_error() == "n_bits=0 with non-empty packed rows"
+    tag = ctypes.c_int32()
+    assert lib.qk_dtype_from_name(b"float16", ctypes.byref(tag)) == _lib.QK_ERR_VALUE
+    assert _lib.last_error() == ('unknown kernel dtype "float16"; expected one of "float64", '
+                                 '"float32", "bfloat16"')
+    for i, name in enumerate(["float64", "float32", "bfloat16"]):
+        assert lib.qk_dtype_from_name(name.encode(), ctypes.byref(tag)) == 0 and tag.value == i
+        assert lib.qk_dtype_name(i) == name.encode()
+
+
+def test_product_validation_happens_before_any_device_work():
+    # these are refused on the host, so they raise ValueError even without a GPU
+    p = np.zeros((6, 2), np.uint8)
+    with pytest.raises(ValueError, match=r"vec must have length 13, got 12"):
+        kernels.packed_matvec(p, 13, np.zeros(12))
+    with pytest.raises(ValueError, match=r"packed length 12 does not match 6 rows x 3 bitplanes"):
+        kernels.packed_matvec(p, 17, np.zeros(17))
+    with pytest.raises(ValueError, match=r"mat length 25 is not a multiple of n_bits 13"):
+        kernels.packed_matmul(p, 13, np.zeros((5, 5)))
+    with pytest.raises(ValueError, match=r'unknown kernel dtype "half"'):
+        kernels.packed_matvec_dtype(p, 13, np.zeros(13), "half")
+    # zero-size work returns zeros without touching a device (gpu.rs:139-143)
+    assert kernels.packed_matvec(np.zeros((0, 2), np.uint8), 13, np.zeros(13)).shape == (0,)
+    assert np.array_equal(kernels.packed_matvec(np.zeros((3, 0), np.uint8), 0, np.zeros(0)),
+                          np.zeros(3))
+
+
+def test_sign_estimate_host():
+    g = golden("bitplanes")
+    x = g["sign0_x"]
+    assert np.array_equal(kernels.sign_estimate(x), g["sign0_x_signs"].ravel())
+
+
+def test_container_repack_host():
+    import oracle
+    rng = np.random.default_rng(8)
+    lib = _lib.lib()
+    for n_rows, r in [(5, 7), (4, 16), (9, 35)]:
+        bits = rng.random((n_rows, r)) < 0.5
+        stream = np.packbits(bits.ravel(), bitorder="little")
+        out = np.zeros(n_rows * ((r + 7) // 8), np.uint8)
+        assert lib.qk_container_to_rows(stream.ctypes.data, stream.size, n_rows, r,
+                                        out.ctypes.data, out.size) == 0
+        assert np.array_equal(out.reshape(n_rows, -1), oracle.container_to_rows(stream, n_rows, r))
+        out_t = np.zeros(r * ((n_rows + 7) // 8), np.uint8)
+        assert lib.qk_container_to_rows_transposed(stream.ctypes.data, stream.size, n_rows, r,
+                                                   out_t.ctypes.data, out_t.size) == 0
+        assert np.array_equal(out_t.reshape(r, -1),
+                              oracle.container_to_rows_transposed(stream, n_rows, r))
+
+
+def test_init_failure_is_typed_and_carries_the_hint():
+    # crates/quantibbler-kernels/tests/gpu_attention_parity.rs:183-204: an impossible device
+    # index must give a typed error that embeds the staging hint, with or without hardware
+    from quantibbler_b200.gpu import GpuContext, gpu_init_hint
+    with pytest.raises(DeviceError) as info:
+        GpuContext.init_at(2**40)
+    assert gpu_init_hint() in str(info.value)
+    assert "CUDA" in gpu_init_hint() and "no CPU fallback" in gpu_init_hint()
+
+
+def test_drop_in_module_exposes_the_reference_names():
+    import quantibbler_kernels as qk
+    for name in ["backend_version", "pack_bits", "unpack_bits", "sign_estimate", "packed_matvec",
+                 "packed_matmul", "packed_matvec_dtype", "packed_matmul_dtype"]:
+        assert callable(getattr(qk, name)), name
+    assert isinstance(qk.backend_version(), str)
+    assert issubclass(KernelError, ValueError)
