@@ -1,0 +1,299 @@
+#!/usr/bin/env python
+"""Benchmark of the factorized-linear decode GEMV on B200.
+
+One step = one pass of the hot path over one batch of synthetic input: every layer of a
+stack of L distinct, device-resident factorized linears (the shape of BASELINE.json's
+config 0: d_in = d_out = 4096, rank 1024, one token each) is applied once, in one
+grouped launch pair.  The stack is larger than the L2 (L x 1.06 MB > 126 MB), so the
+packed bits stream from HBM on every step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints one JSON line (rank 0).  `value` is algorithmic GB/s with inputs resident in
+HBM; `e2e` is the same metric through PackedLayer.apply with host buffers (the
+reference-facing call), host<->device copies inside the timed region.
+`--impl reference` times the CPU restatement of the reference's fast CPU face
+(crates/quantibbler-kernels/src/fast.rs) on the host cores: the reference's own
+kernels are Rust and no Rust toolchain exists on this image.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+DOUT = DIN = 4096
+RANK = 1024
+# bits of both factors + s1,s2 + x + y, float32 vectors
+BYTES_PER_APPLY = (DOUT * RANK + DIN * RANK) // 8 + 4 * (DOUT + DIN) + 4 * DIN + 4 * DOUT
+METRIC = "factorized_gemv_hbm_gbs"
+UNIT = "GB/s"
+
+
+def make_stack(n_layers: int, seed: int):
+    """Seeded synthetic layers as BASELINE.json config 0 prescribes."""
+    rng = np.random.default_rng(seed)
+    for _ in range(n_layers):
+        ub_rows = rng.integers(0, 256, size=(DOUT, RANK // 8), dtype=np.uint8)
+        vb_t_rows = rng.integers(0, 256, size=(RANK, DIN // 8), dtype=np.uint8)
+        s1 = (np.abs(rng.standard_normal(DOUT)) * 0.02 + 1e-3).astype(np.float32)
+        s2 = (np.abs(rng.standard_normal(DIN)) * 0.02 + 1e-3).astype(np.float32)
+        yield ub_rows, vb_t_rows, s1, s2
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows: list[list[str]] = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        sm = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names)
+                   if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def cpu_baseline(seconds: float, n_layers: int = 16) -> dict:
+    """The oracle's restatement of the reference's fast CPU face, all host threads."""
+    import oracle
+    cores = os.cpu_count() or 1
+    layers = list(make_stack(n_layers, seed=4242))
+    rng = np.random.default_rng(1)
+    xs = rng.standard_normal((n_layers, DIN)).astype(np.float32)
+    oracle.layer_apply(*layers[0][:2], DOUT, DIN, RANK, layers[0][2], layers[0][3], None, xs[0],
+                       use_fast=True, n_threads=cores)
+    applies = 0
+    t0 = time.perf_counter()
+    while True:
+        for (ub, vbt, s1, s2), x in zip(layers, xs):
+            oracle.layer_apply(ub, vbt, DOUT, DIN, RANK, s1, s2, None, x, use_fast=True,
+                               n_threads=cores)
+        applies += n_layers
+        dt = time.perf_counter() - t0
+        if dt >= seconds:
+            break
+    return {"value": applies * BYTES_PER_APPLY / dt / 1e9, "unit": UNIT, "cores": cores,
+            "kind": "port",
+            "sample": f"{applies} layer-applies over {n_layers} distinct config-0 layers in "
+                      f"{dt:.1f} s; C restatement of fast.rs (byte->sign table, 4 f64 lanes, "
+                      f"64-row tasks on {cores} threads)",
+            "ms_per_apply": dt / applies * 1e3}
+
+
+def run_reference(args, rank: int) -> None:
+    if rank != 0:
+        return
+    per_step = 64
+    cores = os.cpu_count() or 1
+    import oracle
+    layers = list(make_stack(16, seed=4242))
+    rng = np.random.default_rng(1)
+    xs = rng.standard_normal((16, DIN)).astype(np.float32)
+
+    def step():
+        for i in range(per_step):
+            ub, vbt, s1, s2 = layers[i % 16]
+            oracle.layer_apply(ub, vbt, DOUT, DIN, RANK, s1, s2, None, xs[i % 16], use_fast=True,
+                               n_threads=cores)
+
+    for _ in range(max(args.warmup, 1)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    value = args.steps * per_step * BYTES_PER_APPLY / dt / 1e9
+    sample = (f"each step = {per_step} layer-applies cycling over 16 distinct config-0 layers; C "
+              f"restatement of the reference's fast CPU face on {cores} threads")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64",
+        "data": "synthetic",
+        "config": {"workload": "config0 factorized linear 4096x4096 r1024, 1 token, CPU sample",
+                   "layers_per_step": per_step},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=296, help="distinct layers per step (2 x 148)")
+    ap.add_argument("--kernel", type=int, default=-1, help="GEMV kernel override (debug)")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--e2e-applies", type=int, default=296)
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from quantibbler_b200.gpu import GpuContext, LayerGroup, PackedLayer
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    ctx = GpuContext.init_at(local_rank)
+    if args.kernel >= 0:
+        ctx.set_gemv_kernel(args.kernel)
+    stream = torch.cuda.Stream()
+    ctx.set_stream(stream.cuda_stream)
+
+    L = args.layers
+    layers = [PackedLayer(ctx, ub, vbt, DOUT, DIN, RANK, s1, s2, None, serving="float32")
+              for ub, vbt, s1, s2 in make_stack(L, seed=1000 + rank)]
+    rng = np.random.default_rng(77 + rank)
+    x_host = torch.from_numpy(rng.standard_normal((L, DIN)).astype(np.float32)).pin_memory()
+    y_host = torch.empty((L, DOUT), dtype=torch.float32).pin_memory()
+    x_dev = x_host.cuda()
+    y_dev = torch.zeros((L, DOUT), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+
+    group = LayerGroup(ctx, layers, x_dev.data_ptr(), y_dev.data_ptr())
+
+    def step():
+        group.apply()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        barrier()
+        launches0 = ctx.launch_count
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks:
+            start.record(stream)
+            for _ in range(args.steps):
+                step()
+            stop.record(stream)
+            barrier()
+            # keep the sampler alive for at least a few samples on short runs
+            if args.steps * 0.1 < 1:
+                for _ in range(20):
+                    step()
+                torch.cuda.synchronize()
+        elapsed_ms = start.elapsed_time(stop)
+        launches = ctx.launch_count - launches0
+
+        # end-to-end: PackedLayer.apply with host buffers, one call per layer
+        n_e2e = min(args.e2e_applies, L)
+        xh = x_host.numpy()
+        for i in range(min(8, n_e2e)):
+            layers[i].apply(xh[i])
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(n_e2e):
+            y_host[i].numpy()[:] = layers[i].apply(xh[i])
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+
+    if world > 1:
+        t = torch.tensor([elapsed_ms, e2e_s], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, e2e_s = float(t[0]), float(t[1])
+
+    if rank == 0:
+        ms_per_step = elapsed_ms / args.steps
+        value = world * L * BYTES_PER_APPLY / (ms_per_step * 1e-3) / 1e9
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(peaks_path):
+            peak, peak_src = json.load(open(peaks_path))["hbm_gbs"], "measured"
+        else:
+            peak, peak_src = 6650.0, "fallback"
+        per_gpu = value / world
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"config0 factorized linear 4096x4096 r1024, 1 token, stack of "
+                                   f"{L} distinct resident layers per GPU per step",
+                       "layers_per_gpu": L, "bytes_per_apply": BYTES_PER_APPLY,
+                       "l2_policy": f"inputs larger than L2: {L * BYTES_PER_APPLY / 1e6:.0f} MB "
+                                    f"streamed per step",
+                       "parallelism": f"independent layer stacks x{world}, no collective"},
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": UNIT,
+                         "frac": per_gpu / peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "gemv stage kernel, 2 launches per step, average"},
+            "e2e": {"value": world * n_e2e * BYTES_PER_APPLY / e2e_s / 1e9, "unit": UNIT,
+                    "h2d_bytes_per_step": n_e2e * DIN * 4, "d2h_bytes_per_step": n_e2e * DOUT * 4,
+                    "call": "PackedLayer.apply(x_host) -> y_host per layer"},
+            "gpu_launches": launches,
+            "clocks": clocks.summary(),
+        }
+        if world == 1 and args.cpu_seconds > 0:
+            line["cpu_baseline"] = cpu_baseline(args.cpu_seconds)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

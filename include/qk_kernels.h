@@ -49,6 +49,7 @@ enum { QK_F64 = 0, QK_F32 = 1, QK_BF16 = 2 };
 
 typedef struct qk_ctx qk_ctx;
 typedef struct qk_layer qk_layer;
+typedef struct qk_group qk_group;
 
 /* Thread-local text of the last failure on this thread ("" if none). */
 const char *qk_last_error(void);
@@ -154,6 +155,12 @@ qk_status qk_layer_apply_host(qk_ctx *ctx, const qk_layer *layer, const float *x
  * launch, and how the bandwidth benchmark streams more bytes than the L2 holds). */
 qk_status qk_layers_apply_group(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers,
                                 const float *x_dev, float *y_dev);
+/* The same set of layers bound once to its buffers: qk_group_apply is then exactly two
+ * kernel launches with no host-side staging, so steps can be queued back to back. */
+qk_status qk_group_create(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers,
+                          const float *x_dev, float *y_dev, qk_group **out);
+qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group);
+void qk_group_free(qk_group *group);
 /* Which GEMV kernel qk_layer_apply uses: 0 = sign-select SIMT, 1 = bit-sliced INT8
  * tensor-core.  Returns the previous value; values out of range leave it unchanged. */
 int32_t qk_set_gemv_kernel(qk_ctx *ctx, int32_t which);

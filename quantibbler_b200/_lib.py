@@ -64,6 +64,10 @@ _SIGNATURES = {
     "qk_layer_apply": (c_int32, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "qk_layer_apply_host": (c_int32, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_size_t]),
     "qk_layers_apply_group": (c_int32, [c_void_p, POINTER(c_void_p), c_size_t, c_void_p, c_void_p]),
+    "qk_group_create": (c_int32, [c_void_p, POINTER(c_void_p), c_size_t, c_void_p, c_void_p,
+                                  POINTER(c_void_p)]),
+    "qk_group_apply": (c_int32, [c_void_p, c_void_p]),
+    "qk_group_free": (None, [c_void_p]),
     "qk_set_gemv_kernel": (c_int32, [c_void_p, c_int32]),
     "qk_gpu_launch_count": (c_uint64, [c_void_p]),
 }

@@ -74,6 +74,16 @@ struct qk_layer {
     float *s1 = nullptr, *s2 = nullptr, *bias = nullptr;  // bias may be null
 };
 
+// A fixed set of same-shape layers bound to input/output buffers: the launch parameters
+// live on the device, so applying the group is two kernel launches and nothing else.
+struct qk_group {
+    int device = 0;
+    size_t n_inst = 0;
+    qk_layer shape;          // dimensions/strides of the member layers
+    float *t_dev = nullptr;  // rank-sized intermediates, one per member
+    void *params = nullptr;  // device array of 2*n_inst stage parameter records
+};
+
 namespace qk {
 // Returns the context to use for a call: `ctx` itself, or the process-wide default on
 // device 0 (created on first use) when `ctx` is null.

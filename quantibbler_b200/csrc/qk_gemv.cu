@@ -159,13 +159,11 @@ qk_status launch_stage(qk_ctx *c, const StageParams &single, const StageParams *
     return QK_OK;
 }
 
-// Both stages for n_layers same-shape layers x n_tokens tokens.  Token t of layer i
-// reads x + (t*n_layers_x_stride ...) as laid out by the caller through `x_of`/`y_of`.
-qk_status apply_group(qk_ctx *c, const qk_layer *const *layers, size_t n_layers, const float *x_dev,
-                      float *y_dev, size_t n_tokens, size_t x_layer_stride, size_t y_layer_stride) {
+qk_status check_group(qk_ctx *c, const qk_layer *const *layers, size_t n_layers) {
     const qk_layer *l0 = layers[0];
     for (size_t i = 0; i < n_layers; ++i) {
         const qk_layer *l = layers[i];
+        if (!l) return qk::fail(QK_ERR_VALUE, "layer %zu is null", i);
         if (l->device != c->device)
             return qk::fail(QK_ERR_VALUE, "layer %zu lives on device %d, context on device %d", i,
                             l->device, c->device);
@@ -178,8 +176,43 @@ qk_status apply_group(qk_ctx *c, const qk_layer *const *layers, size_t n_layers,
     if (smem_bytes(l0->din) > 200 * 1024 || smem_bytes(l0->r) > 200 * 1024)
         return qk::fail(QK_ERR_VALUE, "input width %zu exceeds the GEMV kernel's staging limit",
                         l0->din > l0->r ? l0->din : l0->r);
+    return QK_OK;
+}
+
+// Fills 2*n_inst StageParams (stage 1 entries, then stage 2 entries) for n_layers
+// same-shape layers x n_tokens tokens.  Instance k = t*n_layers + i reads
+// x + i*x_layer_stride + t*din and writes y + i*y_layer_stride + t*dout.
+void fill_params(StageParams *h, const qk_layer *const *layers, size_t n_layers, size_t n_tokens,
+                 const float *x_dev, float *y_dev, float *t_dev, size_t x_layer_stride,
+                 size_t y_layer_stride) {
     const size_t n_inst = n_layers * n_tokens;
-    qk_status st;
+    for (size_t t = 0; t < n_tokens; ++t)
+        for (size_t i = 0; i < n_layers; ++i) {
+            const qk_layer *l = layers[i];
+            size_t k = t * n_layers + i;
+            const float *x = x_dev + i * x_layer_stride + t * l->din;
+            float *y = y_dev + i * y_layer_stride + t * l->dout;
+            h[k] = StageParams{l->vbt, x, l->s2, t_dev + k * l->r, nullptr, nullptr};
+            h[n_inst + k] = StageParams{l->ub, t_dev + k * l->r, nullptr, y, l->s1, l->bias};
+        }
+}
+
+qk_status launch_both(qk_ctx *c, const qk_layer *l0, const StageParams *d, size_t n_inst) {
+    const bool bf16 = l0->serving == QK_BF16;
+    StageParams none{};
+    qk_status st = launch_stage(c, none, d, n_inst, l0->r, l0->din, l0->vbt_stride, bf16);
+    if (st != QK_OK) return st;
+    return launch_stage(c, none, d + n_inst, n_inst, l0->dout, l0->r, l0->ub_stride, bf16);
+}
+
+// Both stages for n_layers same-shape layers x n_tokens tokens, parameters built and
+// uploaded on the fly.
+qk_status apply_group(qk_ctx *c, const qk_layer *const *layers, size_t n_layers, const float *x_dev,
+                      float *y_dev, size_t n_tokens, size_t x_layer_stride, size_t y_layer_stride) {
+    qk_status st = check_group(c, layers, n_layers);
+    if (st != QK_OK) return st;
+    const qk_layer *l0 = layers[0];
+    const size_t n_inst = n_layers * n_tokens;
     if ((st = c->d_t.reserve(n_inst * l0->r * sizeof(float))) != QK_OK) return st;
     const bool bf16 = l0->serving == QK_BF16;
     if (n_inst == 1) {
@@ -196,24 +229,12 @@ qk_status apply_group(qk_ctx *c, const qk_layer *const *layers, size_t n_layers,
     if ((st = c->pinned(2 * n_inst * sizeof(StageParams), &hp)) != QK_OK) return st;
     // the pinned block is reused by the next call: wait for the previous copy out of it
     QK_CUDA(cudaStreamSynchronize(c->stream));
-    StageParams *h = (StageParams *)hp;
-    float *t_dev = (float *)c->d_t.ptr;
-    for (size_t t = 0; t < n_tokens; ++t)
-        for (size_t i = 0; i < n_layers; ++i) {
-            const qk_layer *l = layers[i];
-            size_t k = t * n_layers + i;
-            const float *x = x_dev + i * x_layer_stride + t * l->din;
-            float *y = y_dev + i * y_layer_stride + t * l->dout;
-            h[k] = StageParams{l->vbt, x, l->s2, t_dev + k * l->r, nullptr, nullptr};
-            h[n_inst + k] = StageParams{l->ub, t_dev + k * l->r, nullptr, y, l->s1, l->bias};
-        }
+    fill_params((StageParams *)hp, layers, n_layers, n_tokens, x_dev, y_dev, (float *)c->d_t.ptr,
+                x_layer_stride, y_layer_stride);
     StageParams *d = (StageParams *)c->d_ptrs.ptr;
-    QK_CUDA(cudaMemcpyAsync(d, h, 2 * n_inst * sizeof(StageParams), cudaMemcpyHostToDevice,
+    QK_CUDA(cudaMemcpyAsync(d, hp, 2 * n_inst * sizeof(StageParams), cudaMemcpyHostToDevice,
                             c->stream));
-    StageParams none{};
-    if ((st = launch_stage(c, none, d, n_inst, l0->r, l0->din, l0->vbt_stride, bf16)) != QK_OK)
-        return st;
-    return launch_stage(c, none, d + n_inst, n_inst, l0->dout, l0->r, l0->ub_stride, bf16);
+    return launch_both(c, l0, d, n_inst);
 }
 
 qk_status upload_padded(qk_ctx *c, const uint8_t *host, size_t len, size_t n_rows, size_t n_bits,
@@ -358,6 +379,59 @@ qk_status qk_layers_apply_group(qk_ctx *ctx, const qk_layer *const *layers, size
     std::lock_guard<std::mutex> lock(c->mu);
     QK_CUDA(cudaSetDevice(c->device));
     return apply_group(c, layers, n_layers, x_dev, y_dev, 1, layers[0]->din, layers[0]->dout);
+}
+
+qk_status qk_group_create(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers,
+                          const float *x_dev, float *y_dev, qk_group **out) {
+    if (!out) return qk::fail(QK_ERR_VALUE, "qk_group_create: out is null");
+    *out = nullptr;
+    if (n_layers == 0 || !layers) return qk::fail(QK_ERR_VALUE, "qk_group_create: no layers");
+    qk_ctx *c;
+    qk_status st = qk::resolve_ctx(ctx, &c);
+    if (st != QK_OK) return st;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    if ((st = check_group(c, layers, n_layers)) != QK_OK) return st;
+    const qk_layer *l0 = layers[0];
+    qk_group *g = new qk_group();
+    g->device = c->device;
+    g->n_inst = n_layers;
+    g->shape = *l0;  // dimensions and strides only; the pointers are not used
+    cudaError_t e = cudaMalloc(&g->t_dev, n_layers * l0->r * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&g->params, 2 * n_layers * sizeof(StageParams));
+    if (e != cudaSuccess) {
+        qk_group_free(g);
+        return qk::fail(QK_ERR_ALLOC, "device allocation for a layer group failed: %s",
+                        cudaGetErrorString(e));
+    }
+    std::vector<StageParams> h(2 * n_layers);
+    fill_params(h.data(), layers, n_layers, 1, x_dev, y_dev, g->t_dev, l0->din, l0->dout);
+    QK_CUDA(cudaMemcpyAsync(g->params, h.data(), h.size() * sizeof(StageParams),
+                            cudaMemcpyHostToDevice, c->stream));
+    QK_CUDA(cudaStreamSynchronize(c->stream));
+    *out = g;
+    return QK_OK;
+}
+
+qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group) {
+    if (!group) return qk::fail(QK_ERR_VALUE, "qk_group_apply: group is null");
+    qk_ctx *c;
+    qk_status st = qk::resolve_ctx(ctx, &c);
+    if (st != QK_OK) return st;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    if (group->device != c->device)
+        return qk::fail(QK_ERR_VALUE, "group lives on device %d, context on device %d",
+                        group->device, c->device);
+    return launch_both(c, &group->shape, (const StageParams *)group->params, group->n_inst);
+}
+
+void qk_group_free(qk_group *g) {
+    if (!g) return;
+    cudaSetDevice(g->device);
+    if (g->t_dev) cudaFree(g->t_dev);
+    if (g->params) cudaFree(g->params);
+    delete g;
 }
 
 }  // extern "C"

@@ -198,5 +198,32 @@ def apply_group(ctx: GpuContext, layers, x_ptr: int, y_ptr: int) -> None:
                                            ctypes.c_void_p(y_ptr)))
 
 
-__all__ = ["GpuContext", "AttentionShape", "PackedLayer", "apply_group", "gpu_available",
+class LayerGroup:
+    """Same-shape layers bound once to device buffers (layer i reads x + i*din floats and
+    writes y + i*dout floats); ``apply`` is two kernel launches."""
+
+    def __init__(self, ctx: GpuContext, layers, x_ptr: int, y_ptr: int):
+        self.ctx, self.layers = ctx, list(layers)
+        arr = (ctypes.c_void_p * len(self.layers))(*[l.handle for l in self.layers])
+        h = ctypes.c_void_p()
+        check(_lib.lib().qk_group_create(ctx.handle, arr, len(self.layers), ctypes.c_void_p(x_ptr),
+                                         ctypes.c_void_p(y_ptr), ctypes.byref(h)))
+        self._h = h
+
+    def apply(self) -> None:
+        check(_lib.lib().qk_group_apply(self.ctx.handle, self._h))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            _lib.lib().qk_group_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+__all__ = ["LayerGroup", "GpuContext", "AttentionShape", "PackedLayer", "apply_group", "gpu_available",
            "gpu_init_hint", "GPU_INDEX_CEILING", "KernelError", "DeviceError"]
