@@ -52,7 +52,7 @@ struct qk_ctx {
     cudaStream_t own_stream = nullptr;  // created with the context
     std::mutex mu;  // serialises calls from several host threads
     int sm_count = 0;
-    int gemv_kernel = 0;
+    int gemv_kernel = 1;  // 0 sign-select, 1 bit-sliced INT8 tensor core
     std::atomic<uint64_t> launches{0};
     // staging for the host-buffer entry points
     qk_scratch d_packed, d_in, d_out;
@@ -70,6 +70,8 @@ struct qk_layer {
     // per-row bitplanes, rows padded to a multiple of 16 bytes (zero pad bits)
     uint8_t *ub = nullptr;    // dout rows x ub_stride bytes
     uint8_t *vbt = nullptr;   // r rows x vbt_stride bytes
+    // the same factors as 16-row x 512-bit tiles for the tensor-core GEMV
+    uint8_t *ub_tiles = nullptr, *vbt_tiles = nullptr;
     size_t ub_stride = 0, vbt_stride = 0;
     float *s1 = nullptr, *s2 = nullptr, *bias = nullptr;  // bias may be null
 };
@@ -80,7 +82,7 @@ struct qk_group {
     int device = 0;
     size_t n_inst = 0;
     qk_layer shape;          // dimensions/strides of the member layers
-    float *t_dev = nullptr;  // rank-sized intermediates, one per member
+    void *scratch = nullptr; // per member: intermediate t, digit tables, stage metadata
     void *params = nullptr;  // device array of 2*n_inst stage parameter records
 };
 

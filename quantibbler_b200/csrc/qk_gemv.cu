@@ -5,36 +5,62 @@
 // :342-381 (PackedLayer::from_layer) and :393-480 (apply / apply_bf16), whose inner
 // loop is crates/quantibbler-kernels/src/core.rs:202-221 (accumulate_row).
 //
-// Data layout in HBM.  Each factor keeps the reference's per-row bitplane order
-// (element k of a row at bit k&7 of byte k>>3) but every row is padded with zero bits
-// to a multiple of 16 bytes, so that a lane can fetch 128 weights with one aligned
-// 128-bit load and a warp fetches 512 contiguous bytes of one row.  Pad bits are
-// cleared when the layer is created; the matching vector entries are zero, so they
-// add nothing.
+// Why the main kernel uses the INT8 tensor pipe.  At HBM speed a B200 SM receives about
+// 185 weight bits per clock, but it can issue only 128 lane-instructions per clock, so
+// any kernel that spends an instruction per weight (sign select + add) is issue-bound
+// far below the memory roofline.  The bit-sliced kernel spends 0.3 instructions per
+// weight and is exact:
+//   * sum_k s_k v_k = 2 * sum_{bit_k = 1} v_k - sum_k v_k, so only the 0/1 weights matter;
+//   * v is converted once per call to fixed point, v_k ~ q_k * 2^-sh with |q_k| < 2^47,
+//     and q_k * 2^(7-i) (i = k mod 8) is split into eight balanced base-256 digits;
+//   * a 32-bit word of weight bits ANDed with 0x01010101 << i is four unsigned bytes
+//     holding bit * 2^i: a ready-made A fragment of mma.sync.m16n8k32.u8.s8 with no
+//     unpacking.  The eight digit columns are the N dimension, so one MMA retires
+//     16 rows x 32 weights against all digits, accumulating exactly in int32;
+//   * the eight int32 column sums recombine as sum_n c_n 256^n = 128 * sum bit_k q_k.
+// Integer accumulation is associative, so results do not depend on the order of
+// summation and are bit-reproducible.  The only roundings are the fixed-point
+// conversion (relative 2^-47 of max|v|) and one rounding of the final sum: closer to
+// the exact sum than the reference's own float64 left-to-right loop.
 //
-// Rounding points.  fp32 serving computes z = s2*x in float32 as the reference does;
-// the reference then sums in float64, this kernel sums float32 lane partials combined
-// by a fixed butterfly (bit-reproducible run to run), inside the reference's declared
-// backward bound for reassociating faces (|delta| <= 1e-6 * sum|v_k|,
-// crates/quantibbler-kernels/tests/parity.rs:795).  bf16 serving rounds z, t and u to
+// Data layout in HBM (built once by qk_layer_create):
+//   * tiles: the factor's rows are cut into 16-row x 512-bit tiles of 1 KB, stored
+//     row-tile-major then k-step-major.  Inside a tile, the 16-byte piece of row
+//     (g + 8*h) at byte offset 16*t is stored at piece index h*32 + 4*g + t, so lane
+//     (g,t) of a warp fetches its two pieces with two fully coalesced 512-byte
+//     128-bit loads.  Rows are padded to a multiple of 16 and bits to a multiple of
+//     512 with zeros.
+//   * rows: the reference's per-row bitplanes padded to 16-byte rows; only the
+//     sign-select kernel reads it.
+//
+// Rounding points follow the reference: fp32 serving forms z = s2*x in float32 and
+// keeps t and u in float64 between the stages; bf16 serving rounds z, t and u to
 // bfloat16 exactly where apply_bf16 does.
+#include <cmath>
 #include <cstring>
 
 #include "qk_common.h"
 
 namespace {
 
-constexpr int kWarpsPerBlock = 8;
-constexpr int kRowsPerWarp = 4;
-constexpr int kChunkBits = 4096;  // 32 lanes x 128 bits
+// ------------------------------------------------------------------ shared helpers
+struct StageMeta {
+    long long total;  // sum_k q_k
+    int shift;        // v_k ~ q_k * 2^-shift
+    int nonfinite;    // the input held a NaN or an infinity
+};
 
+// One (layer, token) instance of one stage.
 struct StageParams {
-    const uint8_t *w;       // rows x stride bytes
-    const float *in;        // n_bits values
-    const float *in_scale;  // n_bits values or null (s2)
-    float *out;             // n_rows values
-    const float *out_scale; // n_rows values or null (s1)
-    const float *out_bias;  // n_rows values or null
+    const uint8_t *w_rows;   // padded per-row bitplanes (sign-select kernel)
+    const uint8_t *w_tiles;  // 16 x 512 tiles (tensor-core kernel)
+    const void *in;          // float[n_bits] (stage 1) or the previous stage's output
+    const float *in_scale;   // s2 or null
+    void *out;               // intermediate (float or double) or float y
+    const float *out_scale;  // s1 or null
+    const float *out_bias;   // bias or null
+    uint2 *digits;           // tensor-core kernel: digit table of the input vector
+    StageMeta *meta;
 };
 
 __device__ __forceinline__ float round_bf16(float v) {
@@ -44,6 +70,11 @@ __device__ __forceinline__ float round_bf16(float v) {
     return __uint_as_float(u);
 }
 
+// ------------------------------------------------------------------ sign-select kernel
+constexpr int kWarpsPerBlock = 8;
+constexpr int kRowsPerWarp = 4;
+constexpr int kChunkBits = 4096;  // 32 lanes x 128 bits
+
 // (bit b of w) ? v : -v: the weight bit is moved onto the sign position and flips
 // the sign of v when it is 0.  Compiles to one shift and one three-input logic op.
 __device__ __forceinline__ float signed_term(uint32_t w, int b, float v) {
@@ -51,20 +82,22 @@ __device__ __forceinline__ float signed_term(uint32_t w, int b, float v) {
     return __uint_as_float(__float_as_uint(v) ^ (~t & 0x80000000u));
 }
 
-// One stage of the factorized linear: out[i] = epilogue(sum_k sign(i,k) * prologue(in[k])).
-// grid.x tiles the rows, grid.y indexes the layer of a group.
+// out[i] = epilogue(sum_k sign(i,k) * prologue(in[k])), float32 lane partials combined by
+// a fixed butterfly.  grid.x tiles the rows, grid.y indexes the instance.
 template <bool kRoundBf16>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-gemv_signselect_kernel(const StageParams single, const StageParams *__restrict__ many,
-                       uint32_t n_rows, uint32_t n_bits, uint32_t stride) {
+gemv_signselect_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint32_t n_bits,
+                       uint32_t stride) {
     extern __shared__ float vs[];  // permuted copy of the input vector, zero padded
-    const StageParams p = many ? many[blockIdx.y] : single;
+    const StageParams p = many[blockIdx.y];
+    const float *in = static_cast<const float *>(p.in);
+    float *out = static_cast<float *>(p.out);
     const uint32_t n_chunks = (n_bits + kChunkBits - 1) / kChunkBits;
-    // stage the vector: element k of chunk c held by lane l = (k/128)%32 at slot e = k%128
+    // element k of chunk c is used by lane l = (k/128)%32 as its e = k%128-th weight
     for (uint32_t k = threadIdx.x; k < n_chunks * kChunkBits; k += blockDim.x) {
         float v = 0.f;
         if (k < n_bits) {
-            v = p.in[k];
+            v = in[k];
             if (p.in_scale) v = p.in_scale[k] * v;
             if (kRoundBf16) v = round_bf16(v);
         }
@@ -82,14 +115,15 @@ gemv_signselect_kernel(const StageParams single, const StageParams *__restrict__
 
     for (uint32_t c = 0; c < n_chunks; ++c) {
         const uint32_t byte_off = (c * 32 + lane) * 16;
+        if (byte_off >= stride) continue;  // vector entries there are zero as well
         uint4 w[kRowsPerWarp];
 #pragma unroll
         for (int r = 0; r < kRowsPerWarp; ++r) {
             w[r] = make_uint4(0, 0, 0, 0);
-            if (row0 + r < n_rows && byte_off < stride)
-                w[r] = *reinterpret_cast<const uint4 *>(p.w + (size_t)(row0 + r) * stride + byte_off);
+            if (row0 + r < n_rows)
+                w[r] = *reinterpret_cast<const uint4 *>(p.w_rows + (size_t)(row0 + r) * stride +
+                                                        byte_off);
         }
-        if (byte_off >= stride) continue;  // vector entries there are zero as well
         const float4 *vrow = reinterpret_cast<const float4 *>(vs) + (size_t)c * 32 * 32 + lane;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -118,11 +152,233 @@ gemv_signselect_kernel(const StageParams single, const StageParams *__restrict__
             if (kRoundBf16) a = round_bf16(a);
             if (p.out_scale) a = a * p.out_scale[row0 + r];
             if (p.out_bias) a = a + p.out_bias[row0 + r];
-            p.out[row0 + r] = a;
+            out[row0 + r] = a;
         }
     }
 }
 
+// ------------------------------------------------------------------ tensor-core kernel
+constexpr int kTileRows = 16;
+constexpr int kStepBits = 512;      // bits of one row inside one tile
+constexpr int kTileBytes = 1024;
+constexpr int kTilesPerWarp = 4;    // row tiles that share one B fragment
+constexpr int kQBits = 46;          // |q_k| < 2^(kQBits+1)
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_stream(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// Converts one instance's input vector to its digit table.  One block per instance.
+//   kInDouble: the input is the float64 intermediate of the previous stage.
+// Table layout (uint2 units): record ((ks*4 + q)*4 + ip)*4 + t holds, for digit column n,
+// the B fragment pair of lane (g = n, t) for the MMA that consumes word q of k-step ks
+// under masks 2*ip (b0) and 2*ip+1 (b1); byte j of b0/b1 belongs to
+// k = 512*ks + 128*t + 32*q + 8*j + i.
+template <bool kInDouble, bool kRoundBf16>
+__global__ void __launch_bounds__(256)
+digit_table_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32_t n_steps) {
+    const StageParams p = many[blockIdx.x];
+    __shared__ double red_max[8];
+    __shared__ long long red_sum[8];
+    __shared__ __align__(16) uint8_t chunk[kStepBits * 8];
+    __shared__ int sh_shift, sh_bad;
+    const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+
+    auto load = [&](uint32_t k) -> double {
+        if (k >= n_bits) return 0.0;
+        if (kInDouble) return static_cast<const double *>(p.in)[k];  // rounded by its producer
+        float v = static_cast<const float *>(p.in)[k];
+        if (p.in_scale) v = p.in_scale[k] * v;  // float32 product, as the reference forms z
+        if (kRoundBf16) v = round_bf16(v);
+        return (double)v;
+    };
+
+    double mx = 0.0;
+    int bad = 0;
+    for (uint32_t k = tid; k < n_bits; k += 256) {
+        double a = fabs(load(k));
+        if (!(a <= 1.7e308)) bad = 1;  // NaN or infinity
+        mx = fmax(mx, a);
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        bad |= __shfl_xor_sync(0xffffffffu, bad, off);
+    }
+    if (lane == 0) {
+        red_max[warp] = mx;
+        red_sum[warp] = bad;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        double m = 0.0;
+        int b = 0;
+        for (int w = 0; w < 8; ++w) {
+            m = fmax(m, red_max[w]);
+            b |= (int)red_sum[w];
+        }
+        int e = 0;
+        if (m > 0.0 && !b) frexp(m, &e);  // m = f * 2^e, f in [0.5, 1)
+        sh_shift = kQBits + 1 - e;        // |v| * 2^shift < 2^(kQBits+1)
+        sh_bad = b;
+    }
+    __syncthreads();
+    const int shift = sh_shift;
+    const bool nonfinite = sh_bad != 0;
+
+    long long total = 0;
+    for (uint32_t ks = 0; ks < n_steps; ++ks) {
+        for (uint32_t e = tid; e < (uint32_t)kStepBits; e += 256) {
+            uint32_t k = ks * kStepBits + e;
+            long long q = nonfinite ? 0 : __double2ll_rn(ldexp(load(k), shift));
+            total += q;
+            uint32_t t = e / 128, qw = (e % 128) / 32, bit = e % 32;
+            uint32_t j = bit / 8, i = bit % 8, ip = i / 2, which = i % 2;
+            long long v = q << (7 - i);
+            uint32_t rec = ((qw * 4 + ip) * 4 + t) * 8;  // uint2 index inside the k-step
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                int d = (int)(v & 0xff);
+                if (d >= 128) d -= 256;
+                v = (v - d) >> 8;
+                chunk[(rec + n) * 8 + which * 4 + j] = (uint8_t)d;
+            }
+        }
+        __syncthreads();
+        reinterpret_cast<uint4 *>(p.digits)[(size_t)ks * 256 + tid] =
+            reinterpret_cast<const uint4 *>(chunk)[tid];
+        __syncthreads();
+    }
+    for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+    if (lane == 0) red_sum[warp] = total;
+    __syncthreads();
+    if (tid == 0) {
+        long long s = 0;
+        for (int w = 0; w < 8; ++w) s += red_sum[w];
+        p.meta->total = s;
+        p.meta->shift = shift;
+        p.meta->nonfinite = nonfinite;
+    }
+}
+
+// out[row] = epilogue((2 * sum_{bit=1} q_k - sum q_k) * 2^-shift).
+//   kFinal = false: writes the float64 intermediate t;  true: y = float(u)*s1 + bias.
+// grid.x tiles the rows (8 warps x 4 tiles x 16 rows per block), grid.y is the instance.
+template <bool kRoundBf16, bool kFinal>
+__global__ void __launch_bounds__(256, 2)
+gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint32_t n_tiles,
+                     uint32_t n_steps) {
+    const StageParams p = many[blockIdx.y];
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t g = lane / 4, t = lane % 4;
+    const uint32_t tile0 = (blockIdx.x * 8 + warp) * kTilesPerWarp;
+    if (tile0 >= n_tiles) return;
+    const uint32_t my_tiles = min((uint32_t)kTilesPerWarp, n_tiles - tile0);
+
+    int acc[kTilesPerWarp][4];
+#pragma unroll
+    for (int m = 0; m < kTilesPerWarp; ++m)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[m][e] = 0;
+
+    const uint4 *wbase =
+        reinterpret_cast<const uint4 *>(p.w_tiles + (size_t)tile0 * n_steps * kTileBytes) + lane;
+    const size_t tile_stride = (size_t)n_steps * (kTileBytes / 16);  // in uint4
+    const uint2 *dig = p.digits + t * 8 + g;
+
+    uint4 cur[kTilesPerWarp][2], nxt[kTilesPerWarp][2];
+#pragma unroll
+    for (int m = 0; m < kTilesPerWarp; ++m) {
+        cur[m][0] = cur[m][1] = make_uint4(0, 0, 0, 0);
+        if ((uint32_t)m < my_tiles) {
+            cur[m][0] = ld_stream(wbase + m * tile_stride);
+            cur[m][1] = ld_stream(wbase + m * tile_stride + 32);
+        }
+    }
+    for (uint32_t ks = 0; ks < n_steps; ++ks) {
+#pragma unroll
+        for (int m = 0; m < kTilesPerWarp; ++m) {
+            nxt[m][0] = nxt[m][1] = make_uint4(0, 0, 0, 0);
+            if (ks + 1 < n_steps && (uint32_t)m < my_tiles) {
+                nxt[m][0] = ld_stream(wbase + m * tile_stride + (size_t)(ks + 1) * 64);
+                nxt[m][1] = ld_stream(wbase + m * tile_stride + (size_t)(ks + 1) * 64 + 32);
+            }
+        }
+        const uint2 *dk = dig + (size_t)ks * 512;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+            for (int ip = 0; ip < 4; ++ip) {
+                const uint2 b = __ldg(dk + (q * 4 + ip) * 32);
+                const uint32_t m0 = 0x01010101u << (2 * ip), m1 = m0 << 1;
+#pragma unroll
+                for (int m = 0; m < kTilesPerWarp; ++m) {
+                    const uint32_t wg = q == 0 ? cur[m][0].x : q == 1 ? cur[m][0].y
+                                      : q == 2 ? cur[m][0].z : cur[m][0].w;
+                    const uint32_t wh = q == 0 ? cur[m][1].x : q == 1 ? cur[m][1].y
+                                      : q == 2 ? cur[m][1].z : cur[m][1].w;
+                    mma_u8s8(acc[m], wg & m0, wh & m0, wg & m1, wh & m1, b.x, b.y);
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < kTilesPerWarp; ++m) {
+            cur[m][0] = nxt[m][0];
+            cur[m][1] = nxt[m][1];
+        }
+    }
+
+    // Exact recombination.  Lane (g,t) holds digit columns 2t and 2t+1 of rows g
+    // (acc[.][0..1]) and g+8 (acc[.][2..3]).  With X = sum_n c_n 256^n = 128 * S and
+    // T = sum q_k, the row's value is (X - 64 T) / 64 * 2^-shift.  X is kept as
+    // hi * 2^32 + lo (digits 4..7 and 0..3) and 64 T as th * 2^32 + tl, so the
+    // subtraction is exact in int64 and only the last conversion rounds.
+    const StageMeta meta = *p.meta;
+    const long long th = meta.total >> 26;
+    const long long tl = (meta.total & ((1ll << 26) - 1)) << 6;
+    const int sh0 = 16 * (t & 1);
+#pragma unroll
+    for (int m = 0; m < kTilesPerWarp; ++m) {
+        long long pg = ((long long)acc[m][0] << sh0) + ((long long)acc[m][1] << (sh0 + 8));
+        long long ph = ((long long)acc[m][2] << sh0) + ((long long)acc[m][3] << (sh0 + 8));
+        pg += __shfl_xor_sync(0xffffffffu, pg, 1);  // lanes t=0,1: low half; t=2,3: high half
+        ph += __shfl_xor_sync(0xffffffffu, ph, 1);
+        const long long og = __shfl_xor_sync(0xffffffffu, pg, 2);
+        const long long oh = __shfl_xor_sync(0xffffffffu, ph, 2);
+        if (t < 2 && (uint32_t)m < my_tiles) {
+            const uint32_t row = (tile0 + m) * kTileRows + g + 8 * t;
+            if (row < n_rows) {
+                const long long lo = t == 0 ? pg : ph, hi = t == 0 ? og : oh;
+                double val = ldexp((double)(hi - th) * 4294967296.0 + (double)(lo - tl),
+                                   -meta.shift - 6);
+                if (meta.nonfinite) val = nan("");
+                if (kRoundBf16) val = (double)round_bf16((float)val);
+                if (kFinal) {
+                    float y = (float)val;
+                    if (p.out_scale) y = y * p.out_scale[row];
+                    if (p.out_bias) y = y + p.out_bias[row];
+                    static_cast<float *>(p.out)[row] = y;
+                } else {
+                    static_cast<double *>(p.out)[row] = val;
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ layer construction
 // Copy host-layout rows (row_words bytes each) into 16-byte padded rows, clearing the
 // pad bits of the last byte.
 __global__ void pad_rows_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst,
@@ -140,23 +396,86 @@ __global__ void pad_rows_kernel(const uint8_t *__restrict__ src, uint8_t *__rest
     dst[gid] = v;
 }
 
-size_t smem_bytes(size_t n_bits) {
+// Padded rows -> 16 x 512 tiles (one thread per 16-byte piece of the tile array).
+__global__ void tile_rows_kernel(const uint8_t *__restrict__ rows, uint8_t *__restrict__ tiles,
+                                 uint32_t n_rows, uint32_t stride, uint32_t n_tiles,
+                                 uint32_t n_steps) {
+    uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= (uint64_t)n_tiles * n_steps * 64) return;
+    uint64_t blk = gid / 64;
+    uint32_t within = (uint32_t)(gid % 64);
+    uint32_t rt = (uint32_t)(blk / n_steps), ks = (uint32_t)(blk % n_steps);
+    uint32_t half = within / 32, lane = within % 32, g = lane / 4, t = lane % 4;
+    uint32_t row = rt * kTileRows + g + 8 * half;
+    uint32_t off = ks * 64 + t * 16;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < n_rows && off < stride)
+        v = *reinterpret_cast<const uint4 *>(rows + (size_t)row * stride + off);
+    reinterpret_cast<uint4 *>(tiles)[gid] = v;
+}
+
+size_t signselect_smem(size_t n_bits) {
     return qk::ceil_div(n_bits, kChunkBits) * kChunkBits * sizeof(float);
 }
 
-// `many` (device array, one entry per grid.y index) or, when null, `single` by value.
-qk_status launch_stage(qk_ctx *c, const StageParams &single, const StageParams *many,
-                       size_t n_layers, size_t n_rows, size_t n_bits, size_t stride, bool bf16) {
-    size_t smem = smem_bytes(n_bits);
-    dim3 grid((unsigned)qk::ceil_div(n_rows, kWarpsPerBlock * kRowsPerWarp), (unsigned)n_layers);
+// ------------------------------------------------------------------ launches
+struct StageShape {
+    size_t n_rows, n_bits, row_stride, n_tiles, n_steps;
+};
+
+StageShape stage1_shape(const qk_layer *l) {
+    return {l->r, l->din, l->vbt_stride, qk::ceil_div(l->r, kTileRows),
+            qk::ceil_div(l->din, kStepBits)};
+}
+StageShape stage2_shape(const qk_layer *l) {
+    return {l->dout, l->r, l->ub_stride, qk::ceil_div(l->dout, kTileRows),
+            qk::ceil_div(l->r, kStepBits)};
+}
+
+qk_status launch_signselect(qk_ctx *c, const StageParams *many, size_t n_inst, const StageShape &s,
+                            bool bf16) {
+    size_t smem = signselect_smem(s.n_bits);
+    dim3 grid((unsigned)qk::ceil_div(s.n_rows, kWarpsPerBlock * kRowsPerWarp), (unsigned)n_inst);
     auto kern = bf16 ? gemv_signselect_kernel<true> : gemv_signselect_kernel<false>;
     if (smem > 48 * 1024)
         QK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, kWarpsPerBlock * 32, smem, c->stream>>>(single, many, (uint32_t)n_rows,
-                                                         (uint32_t)n_bits, (uint32_t)stride);
+    kern<<<grid, kWarpsPerBlock * 32, smem, c->stream>>>(many, (uint32_t)s.n_rows,
+                                                         (uint32_t)s.n_bits, (uint32_t)s.row_stride);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     return QK_OK;
+}
+
+template <bool kFinal>
+qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, const StageShape &s,
+                          bool bf16) {
+    // the digit table of every instance, then the product
+    auto table = kFinal ? (bf16 ? digit_table_kernel<true, true> : digit_table_kernel<true, false>)
+                        : (bf16 ? digit_table_kernel<false, true> : digit_table_kernel<false, false>);
+    table<<<(unsigned)n_inst, 256, 0, c->stream>>>(many, (uint32_t)s.n_bits, (uint32_t)s.n_steps);
+    QK_CUDA(cudaGetLastError());
+    c->launches++;
+    dim3 grid((unsigned)qk::ceil_div(s.n_tiles, 8 * kTilesPerWarp), (unsigned)n_inst);
+    auto gemv = bf16 ? gemv_bitslice_kernel<true, kFinal> : gemv_bitslice_kernel<false, kFinal>;
+    gemv<<<grid, 256, 0, c->stream>>>(many, (uint32_t)s.n_rows, (uint32_t)s.n_tiles,
+                                      (uint32_t)s.n_steps);
+    QK_CUDA(cudaGetLastError());
+    c->launches++;
+    return QK_OK;
+}
+
+// Scratch one instance needs besides its inputs and outputs.
+struct InstanceScratch {
+    size_t t_bytes, dig1_bytes, dig2_bytes, meta_bytes, total;
+};
+InstanceScratch scratch_of(const qk_layer *l) {
+    InstanceScratch s;
+    s.t_bytes = qk::ceil_div(l->r * sizeof(double), 256) * 256;
+    s.dig1_bytes = qk::ceil_div(l->din, kStepBits) * kStepBits * 8;
+    s.dig2_bytes = qk::ceil_div(l->r, kStepBits) * kStepBits * 8;
+    s.meta_bytes = 256;
+    s.total = s.t_bytes + s.dig1_bytes + s.dig2_bytes + s.meta_bytes;
+    return s;
 }
 
 qk_status check_group(qk_ctx *c, const qk_layer *const *layers, size_t n_layers) {
@@ -173,36 +492,50 @@ qk_status check_group(qk_ctx *c, const qk_layer *const *layers, size_t n_layers)
                             "differs from layer 0)",
                             i);
     }
-    if (smem_bytes(l0->din) > 200 * 1024 || smem_bytes(l0->r) > 200 * 1024)
-        return qk::fail(QK_ERR_VALUE, "input width %zu exceeds the GEMV kernel's staging limit",
-                        l0->din > l0->r ? l0->din : l0->r);
     return QK_OK;
 }
 
 // Fills 2*n_inst StageParams (stage 1 entries, then stage 2 entries) for n_layers
 // same-shape layers x n_tokens tokens.  Instance k = t*n_layers + i reads
-// x + i*x_layer_stride + t*din and writes y + i*y_layer_stride + t*dout.
+// x + i*x_layer_stride + t*din and writes y + i*y_layer_stride + t*dout; its scratch is
+// the k-th slice of `scratch`.
 void fill_params(StageParams *h, const qk_layer *const *layers, size_t n_layers, size_t n_tokens,
-                 const float *x_dev, float *y_dev, float *t_dev, size_t x_layer_stride,
+                 const float *x_dev, float *y_dev, uint8_t *scratch, size_t x_layer_stride,
                  size_t y_layer_stride) {
     const size_t n_inst = n_layers * n_tokens;
+    const InstanceScratch sc = scratch_of(layers[0]);
     for (size_t t = 0; t < n_tokens; ++t)
         for (size_t i = 0; i < n_layers; ++i) {
             const qk_layer *l = layers[i];
             size_t k = t * n_layers + i;
+            uint8_t *base = scratch + k * sc.total;
+            void *t_buf = base;
+            uint2 *dig1 = (uint2 *)(base + sc.t_bytes);
+            uint2 *dig2 = (uint2 *)(base + sc.t_bytes + sc.dig1_bytes);
+            StageMeta *meta = (StageMeta *)(base + sc.t_bytes + sc.dig1_bytes + sc.dig2_bytes);
             const float *x = x_dev + i * x_layer_stride + t * l->din;
             float *y = y_dev + i * y_layer_stride + t * l->dout;
-            h[k] = StageParams{l->vbt, x, l->s2, t_dev + k * l->r, nullptr, nullptr};
-            h[n_inst + k] = StageParams{l->ub, t_dev + k * l->r, nullptr, y, l->s1, l->bias};
+            h[k] = StageParams{l->vbt, l->vbt_tiles, x, l->s2, t_buf, nullptr, nullptr, dig1, meta};
+            h[n_inst + k] =
+                StageParams{l->ub, l->ub_tiles, t_buf, nullptr, y, l->s1, l->bias, dig2, meta + 1};
         }
 }
 
-qk_status launch_both(qk_ctx *c, const qk_layer *l0, const StageParams *d, size_t n_inst) {
+qk_status launch_both(qk_ctx *c, const qk_layer *l0, const StageParams *d, size_t n_inst,
+                      int kernel) {
     const bool bf16 = l0->serving == QK_BF16;
-    StageParams none{};
-    qk_status st = launch_stage(c, none, d, n_inst, l0->r, l0->din, l0->vbt_stride, bf16);
-    if (st != QK_OK) return st;
-    return launch_stage(c, none, d + n_inst, n_inst, l0->dout, l0->r, l0->ub_stride, bf16);
+    const StageShape s1 = stage1_shape(l0), s2 = stage2_shape(l0);
+    qk_status st;
+    if (kernel == 0) {
+        if (signselect_smem(l0->din) > 200 * 1024 || signselect_smem(l0->r) > 200 * 1024)
+            return qk::fail(QK_ERR_VALUE,
+                            "input width %zu exceeds the sign-select kernel's staging limit",
+                            l0->din > l0->r ? l0->din : l0->r);
+        if ((st = launch_signselect(c, d, n_inst, s1, bf16)) != QK_OK) return st;
+        return launch_signselect(c, d + n_inst, n_inst, s2, bf16);
+    }
+    if ((st = launch_bitslice<false>(c, d, n_inst, s1, bf16)) != QK_OK) return st;
+    return launch_bitslice<true>(c, d + n_inst, n_inst, s2, bf16);
 }
 
 // Both stages for n_layers same-shape layers x n_tokens tokens, parameters built and
@@ -213,51 +546,53 @@ qk_status apply_group(qk_ctx *c, const qk_layer *const *layers, size_t n_layers,
     if (st != QK_OK) return st;
     const qk_layer *l0 = layers[0];
     const size_t n_inst = n_layers * n_tokens;
-    if ((st = c->d_t.reserve(n_inst * l0->r * sizeof(float))) != QK_OK) return st;
-    const bool bf16 = l0->serving == QK_BF16;
-    if (n_inst == 1) {
-        // one layer, one token: parameters travel as kernel arguments, no staging copy
-        float *t1 = (float *)c->d_t.ptr;
-        StageParams a{l0->vbt, x_dev, l0->s2, t1, nullptr, nullptr};
-        StageParams b{l0->ub, t1, nullptr, y_dev, l0->s1, l0->bias};
-        if ((st = launch_stage(c, a, nullptr, 1, l0->r, l0->din, l0->vbt_stride, bf16)) != QK_OK)
-            return st;
-        return launch_stage(c, b, nullptr, 1, l0->dout, l0->r, l0->ub_stride, bf16);
-    }
+    if (n_inst > 65535)
+        return qk::fail(QK_ERR_VALUE, "%zu layer-token instances exceed one launch (65535)", n_inst);
+    const InstanceScratch sc = scratch_of(l0);
+    if ((st = c->d_t.reserve(n_inst * sc.total)) != QK_OK) return st;
     if ((st = c->d_ptrs.reserve(2 * n_inst * sizeof(StageParams))) != QK_OK) return st;
     void *hp;
     if ((st = c->pinned(2 * n_inst * sizeof(StageParams), &hp)) != QK_OK) return st;
     // the pinned block is reused by the next call: wait for the previous copy out of it
     QK_CUDA(cudaStreamSynchronize(c->stream));
-    fill_params((StageParams *)hp, layers, n_layers, n_tokens, x_dev, y_dev, (float *)c->d_t.ptr,
+    fill_params((StageParams *)hp, layers, n_layers, n_tokens, x_dev, y_dev, (uint8_t *)c->d_t.ptr,
                 x_layer_stride, y_layer_stride);
     StageParams *d = (StageParams *)c->d_ptrs.ptr;
     QK_CUDA(cudaMemcpyAsync(d, hp, 2 * n_inst * sizeof(StageParams), cudaMemcpyHostToDevice,
                             c->stream));
-    return launch_both(c, l0, d, n_inst);
+    return launch_both(c, l0, d, n_inst, c->gemv_kernel);
 }
 
-qk_status upload_padded(qk_ctx *c, const uint8_t *host, size_t len, size_t n_rows, size_t n_bits,
-                        uint8_t **out, size_t *stride_out) {
+qk_status upload_factor(qk_ctx *c, const uint8_t *host, size_t len, size_t n_rows, size_t n_bits,
+                        uint8_t **rows_out, size_t *stride_out, uint8_t **tiles_out) {
     size_t row_words = qk::ceil_div(n_bits, 8);
     size_t stride = qk::ceil_div(row_words, 16) * 16;
+    size_t n_tiles = qk::ceil_div(n_rows, kTileRows), n_steps = qk::ceil_div(n_bits, kStepBits);
     qk_status st;
     if ((st = c->d_packed.reserve(len)) != QK_OK) return st;
-    uint8_t *dst = nullptr;
-    cudaError_t e = cudaMalloc(&dst, n_rows * stride);
-    if (e != cudaSuccess)
-        return qk::fail(QK_ERR_ALLOC, "device allocation of %zu bytes failed: %s", n_rows * stride,
-                        cudaGetErrorString(e));
+    uint8_t *rows = nullptr, *tiles = nullptr;
+    cudaError_t e = cudaMalloc(&rows, n_rows * stride);
+    if (e == cudaSuccess) e = cudaMalloc(&tiles, n_tiles * n_steps * kTileBytes);
+    if (e != cudaSuccess) {
+        if (rows) cudaFree(rows);
+        return qk::fail(QK_ERR_ALLOC, "device allocation of %zu bytes failed: %s",
+                        n_rows * stride + n_tiles * n_steps * kTileBytes, cudaGetErrorString(e));
+    }
+    *rows_out = rows;
+    *tiles_out = tiles;
+    *stride_out = stride;
     QK_CUDA(cudaMemcpyAsync(c->d_packed.ptr, host, len, cudaMemcpyHostToDevice, c->stream));
     size_t total = n_rows * stride;
     pad_rows_kernel<<<(unsigned)qk::ceil_div(total, 256), 256, 0, c->stream>>>(
-        (const uint8_t *)c->d_packed.ptr, dst, (uint32_t)n_rows, (uint32_t)n_bits,
+        (const uint8_t *)c->d_packed.ptr, rows, (uint32_t)n_rows, (uint32_t)n_bits,
         (uint32_t)row_words, (uint32_t)stride);
     QK_CUDA(cudaGetLastError());
-    c->launches++;
+    size_t pieces = n_tiles * n_steps * 64;
+    tile_rows_kernel<<<(unsigned)qk::ceil_div(pieces, 256), 256, 0, c->stream>>>(
+        rows, tiles, (uint32_t)n_rows, (uint32_t)stride, (uint32_t)n_tiles, (uint32_t)n_steps);
+    QK_CUDA(cudaGetLastError());
+    c->launches += 2;
     QK_CUDA(cudaStreamSynchronize(c->stream));
-    *out = dst;
-    *stride_out = stride;
     return QK_OK;
 }
 
@@ -267,9 +602,9 @@ qk_status upload_f32(qk_ctx *c, const float *host, size_t n, float **out) {
     if (e != cudaSuccess)
         return qk::fail(QK_ERR_ALLOC, "device allocation of %zu bytes failed: %s",
                         n * sizeof(float), cudaGetErrorString(e));
+    *out = d;
     QK_CUDA(cudaMemcpyAsync(d, host, n * sizeof(float), cudaMemcpyHostToDevice, c->stream));
     QK_CUDA(cudaStreamSynchronize(c->stream));
-    *out = d;
     return QK_OK;
 }
 
@@ -296,6 +631,11 @@ qk_status qk_layer_create(qk_ctx *ctx, const uint8_t *ub_rows, size_t ub_len,
         (uint64_t)r * qk::ceil_div(din, 8) > qk::kIndexCeiling)
         return qk::fail(QK_ERR_VALUE, "layer exceeds the device u32 index ceiling (%llu)",
                         (unsigned long long)qk::kIndexCeiling);
+    if (din > (1u << 16) || r > (1u << 16))
+        return qk::fail(QK_ERR_VALUE,
+                        "reduction width %zu exceeds the int32 digit accumulator's 65536-term "
+                        "bound",
+                        din > r ? din : r);
     qk_ctx *c;
     qk_status st = qk::resolve_ctx(ctx, &c);
     if (st != QK_OK) return st;
@@ -307,8 +647,9 @@ qk_status qk_layer_create(qk_ctx *ctx, const uint8_t *ub_rows, size_t ub_len,
     l->din = din;
     l->r = r;
     l->serving = serving_dtype;
-    st = upload_padded(c, ub_rows, ub_len, dout, r, &l->ub, &l->ub_stride);
-    if (st == QK_OK) st = upload_padded(c, vb_t_rows, vb_t_len, r, din, &l->vbt, &l->vbt_stride);
+    st = upload_factor(c, ub_rows, ub_len, dout, r, &l->ub, &l->ub_stride, &l->ub_tiles);
+    if (st == QK_OK)
+        st = upload_factor(c, vb_t_rows, vb_t_len, r, din, &l->vbt, &l->vbt_stride, &l->vbt_tiles);
     if (st == QK_OK) st = upload_f32(c, s1, dout, &l->s1);
     if (st == QK_OK) st = upload_f32(c, s2, din, &l->s2);
     if (st == QK_OK && bias) st = upload_f32(c, bias, dout, &l->bias);
@@ -325,6 +666,8 @@ void qk_layer_free(qk_layer *l) {
     cudaSetDevice(l->device);
     if (l->ub) cudaFree(l->ub);
     if (l->vbt) cudaFree(l->vbt);
+    if (l->ub_tiles) cudaFree(l->ub_tiles);
+    if (l->vbt_tiles) cudaFree(l->vbt_tiles);
     if (l->s1) cudaFree(l->s1);
     if (l->s2) cudaFree(l->s2);
     if (l->bias) cudaFree(l->bias);
@@ -372,7 +715,8 @@ qk_status qk_layer_apply_host(qk_ctx *ctx, const qk_layer *layer, const float *x
 qk_status qk_layers_apply_group(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers,
                                 const float *x_dev, float *y_dev) {
     if (n_layers == 0) return QK_OK;
-    if (!layers) return qk::fail(QK_ERR_VALUE, "qk_layers_apply_group: layers is null");
+    if (!layers || !layers[0])
+        return qk::fail(QK_ERR_VALUE, "qk_layers_apply_group: layers is null");
     qk_ctx *c;
     qk_status st = qk::resolve_ctx(ctx, &c);
     if (st != QK_OK) return st;
@@ -385,7 +729,10 @@ qk_status qk_group_create(qk_ctx *ctx, const qk_layer *const *layers, size_t n_l
                           const float *x_dev, float *y_dev, qk_group **out) {
     if (!out) return qk::fail(QK_ERR_VALUE, "qk_group_create: out is null");
     *out = nullptr;
-    if (n_layers == 0 || !layers) return qk::fail(QK_ERR_VALUE, "qk_group_create: no layers");
+    if (n_layers == 0 || !layers || !layers[0])
+        return qk::fail(QK_ERR_VALUE, "qk_group_create: no layers");
+    if (n_layers > 65535)
+        return qk::fail(QK_ERR_VALUE, "%zu layers exceed one launch (65535)", n_layers);
     qk_ctx *c;
     qk_status st = qk::resolve_ctx(ctx, &c);
     if (st != QK_OK) return st;
@@ -397,7 +744,8 @@ qk_status qk_group_create(qk_ctx *ctx, const qk_layer *const *layers, size_t n_l
     g->device = c->device;
     g->n_inst = n_layers;
     g->shape = *l0;  // dimensions and strides only; the pointers are not used
-    cudaError_t e = cudaMalloc(&g->t_dev, n_layers * l0->r * sizeof(float));
+    const InstanceScratch sc = scratch_of(l0);
+    cudaError_t e = cudaMalloc(&g->scratch, n_layers * sc.total);
     if (e == cudaSuccess) e = cudaMalloc(&g->params, 2 * n_layers * sizeof(StageParams));
     if (e != cudaSuccess) {
         qk_group_free(g);
@@ -405,7 +753,8 @@ qk_status qk_group_create(qk_ctx *ctx, const qk_layer *const *layers, size_t n_l
                         cudaGetErrorString(e));
     }
     std::vector<StageParams> h(2 * n_layers);
-    fill_params(h.data(), layers, n_layers, 1, x_dev, y_dev, g->t_dev, l0->din, l0->dout);
+    fill_params(h.data(), layers, n_layers, 1, x_dev, y_dev, (uint8_t *)g->scratch, l0->din,
+                l0->dout);
     QK_CUDA(cudaMemcpyAsync(g->params, h.data(), h.size() * sizeof(StageParams),
                             cudaMemcpyHostToDevice, c->stream));
     QK_CUDA(cudaStreamSynchronize(c->stream));
@@ -423,13 +772,14 @@ qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group) {
     if (group->device != c->device)
         return qk::fail(QK_ERR_VALUE, "group lives on device %d, context on device %d",
                         group->device, c->device);
-    return launch_both(c, &group->shape, (const StageParams *)group->params, group->n_inst);
+    return launch_both(c, &group->shape, (const StageParams *)group->params, group->n_inst,
+                       c->gemv_kernel);
 }
 
 void qk_group_free(qk_group *g) {
     if (!g) return;
     cudaSetDevice(g->device);
-    if (g->t_dev) cudaFree(g->t_dev);
+    if (g->scratch) cudaFree(g->scratch);
     if (g->params) cudaFree(g->params);
     delete g;
 }

@@ -33,6 +33,13 @@ def exact_layer(L):
     return y, t
 
 
+@pytest.fixture(params=[1, 0], ids=["bitslice", "signselect"])
+def kernel_ctx(gpu_ctx, request):
+    prev = gpu_ctx.set_gemv_kernel(request.param)
+    yield gpu_ctx
+    gpu_ctx.set_gemv_kernel(prev)
+
+
 def check_layer(ctx, L, serving):
     layer = PackedLayer(ctx, L["ub_rows"], L["vb_t_rows"], L["dout"], L["din"], L["r"], L["s1"],
                         L["s2"], L["bias"], serving=serving)
@@ -52,13 +59,20 @@ def check_layer(ctx, L, serving):
     assert rel <= (2e-3 if serving == "float32" else 2e-2), (serving, rel)
     # run-to-run bit identity
     assert np.array_equal(layer.apply(L["x"]), y)
+    if ctx.set_gemv_kernel(-1) == 1 and serving == "float32":
+        # the bit-sliced kernel sums exactly, so it reproduces the reference's float64
+        # stages to the last float32 bit except where u sits on a rounding boundary
+        ulp = np.spacing(np.abs(want).astype(np.float32)).astype(np.float64)
+        assert (err <= 2 * ulp + 1e-30).all()
+        assert np.mean(y == want) >= 0.9
     layer.close()
     return y, want
 
 
 @pytest.mark.parametrize("serving", ["float32", "bfloat16"])
 @pytest.mark.parametrize("key", ["small", "odd", "mid"])
-def test_golden_layers(gpu_ctx, key, serving):
+def test_golden_layers(kernel_ctx, key, serving):
+    gpu_ctx = kernel_ctx
     g = golden("layer")
     m = g.meta[key]
     L = dict(ub_rows=g[key + "_ub_rows"], vb_t_rows=g[key + "_vb_t_rows"], s1=g[key + "_s1"],
@@ -70,7 +84,8 @@ def test_golden_layers(gpu_ctx, key, serving):
 
 
 @pytest.mark.parametrize("serving", ["float32", "bfloat16"])
-def test_config0_layer_against_reference_vector(gpu_ctx, serving):
+def test_config0_layer_against_reference_vector(kernel_ctx, serving):
+    gpu_ctx = kernel_ctx
     g = golden("layer")
     m = g.meta["config0"]
     L = make_layer(m["dout"], m["din"], m["r"], m["seed"])
@@ -88,14 +103,16 @@ def test_config0_layer_against_reference_vector(gpu_ctx, serving):
 
 @pytest.mark.parametrize("shape", [(1, 1, 1), (8, 8, 8), (33, 129, 17), (300, 4097, 130),
                                    (64, 14336, 96), (4096, 300, 1102)])
-def test_odd_shapes(gpu_ctx, shape):
+def test_odd_shapes(kernel_ctx, shape):
+    gpu_ctx = kernel_ctx
     dout, din, r = shape
     L = make_layer(dout, din, r, seed=dout + din + r, with_bias=(dout % 2 == 0))
     check_layer(gpu_ctx, L, "float32")
     check_layer(gpu_ctx, L, "bfloat16")
 
 
-def test_dirty_pad_bits_are_ignored(gpu_ctx):
+def test_dirty_pad_bits_are_ignored(kernel_ctx):
+    gpu_ctx = kernel_ctx
     # crates/quantibbler-kernels/tests/fixtures/packed_matvec.json (packed_dirty): bits
     # beyond n_bits in the last byte of a row must not change any result
     L = make_layer(24, 21, 13, seed=77)
@@ -141,6 +158,26 @@ def test_multi_token_apply(gpu_ctx):
     layer.apply_device(x.data_ptr(), 7, y.data_ptr())
     gpu_ctx.synchronize()
     assert np.array_equal(y.cpu().numpy(), want)
+
+
+def test_nonfinite_input_gives_nan(gpu_ctx):
+    L = make_layer(32, 40, 16, seed=5)
+    layer = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], 32, 40, 16, L["s1"], L["s2"])
+    x = L["x"].copy()
+    x[3] = np.inf
+    assert np.isnan(layer.apply(x)).all()
+    x[3] = np.nan
+    assert np.isnan(layer.apply(x)).all()
+    assert np.array_equal(layer.apply(np.zeros(40, np.float32)), np.zeros(32, np.float32))
+
+
+def test_extreme_dynamic_range(gpu_ctx):
+    # one huge entry among tiny ones: the fixed-point grid is set by the largest entry
+    L = make_layer(64, 512, 48, seed=9)
+    x = (L["x"] * 1e-6).astype(np.float32)
+    x[7] = 3.0e4
+    L["x"] = x
+    check_layer(gpu_ctx, L, "float32")
 
 
 def test_layer_validation(gpu_ctx):
