@@ -127,6 +127,29 @@ qk_status qk_packed_matmul(qk_ctx *ctx, const uint8_t *packed, size_t packed_len
                            size_t n_bits, int32_t dtype, const void *mat, size_t mat_len,
                            size_t n_cols, void *out, size_t out_len);
 
+/* ---- attention, host buffers in and out --------------------------------------- */
+
+/* gpu_attention.rs:402-411 (AttentionShape). */
+typedef struct qk_attention_shape {
+    size_t batch, n_heads, n_kv_heads, seq_q, seq_kv, head_dim, val_dim;
+} qk_attention_shape;
+
+/* gpu_attention.rs:451-570 (GpuContext::attention): exact softmax(QK^T/sqrt(d))V in
+ * float32.  query [B,H,Sq,d], key [B,KV,Skv,d], value [B,KV,Skv,dv], out [B,H,Sq,dv],
+ * packed row-major; head h reads kv head h/(H/KV); causal masks key j for query i when
+ * j + Sq > i + Skv.  GQA is native: no head expansion on the host. */
+qk_status qk_gpu_attention(qk_ctx *ctx, const qk_attention_shape *shape, const float *query,
+                           size_t q_len, const float *key, size_t k_len, const float *value,
+                           size_t v_len, int32_t causal, float *out, size_t out_len);
+/* gpu_attention.rs:589-756 (GpuContext::attention_sage) with the arithmetic of
+ * sage_int8_tile_kernel (:67-397): per-token INT8 Q/sqrt(d), per-key-block mean-smoothed
+ * per-token INT8 K, static-scale INT8 P, per-channel-per-block INT8 V, int32 dots.
+ * Requires seq_q == seq_kv; block_size is the key-block width. */
+qk_status qk_gpu_attention_sage(qk_ctx *ctx, const qk_attention_shape *shape, const float *query,
+                                size_t q_len, const float *key, size_t k_len, const float *value,
+                                size_t v_len, int32_t causal, size_t block_size, float *out,
+                                size_t out_len);
+
 /* ---- the factorized linear with device-resident factors ----------------------
  * Replaces crates/quantibbler-server/src/engine/mod.rs:313-381 (PackedLayer,
  * PackedLayer::from_layer) and :393-480 (apply, apply_bf16, kernel_matvec).  The

@@ -112,7 +112,15 @@ def attention_sage(q, k, v, *, causal=False, block_size=64, rows=None, ft=np.flo
         j1 = min(j0 + block_size, s)
         cols = np.arange(j0, j1)
         kb = k[:, :, j0:j1]
-        k_mean = kb.mean(axis=-2, keepdims=True, dtype=ft)
+        if ft is np.float64:
+            k_mean = kb.mean(axis=-2, keepdims=True)
+        else:
+            # the device kernel sums the block's tokens one by one in float32 and divides
+            # once (gpu_attention.rs:197-209); reproduce that order so codes can match
+            ssum = np.zeros(kb.shape[:2] + (1, d), dtype=ft)
+            for jj in range(kb.shape[2]):
+                ssum = (ssum + kb[:, :, jj:jj + 1]).astype(ft)
+            k_mean = (ssum / ft(kb.shape[2])).astype(ft)
         k_hat, k_scale = quantize_per_token(kb - k_mean, ft)
         dot = np.matmul(q_hat.astype(np.int32), k_hat[:, kv_index].astype(np.int32).swapaxes(-1, -2))
         scores = dot.astype(ft) * q_scale * k_scale[:, kv_index].swapaxes(-1, -2) \

@@ -57,6 +57,10 @@ _SIGNATURES = {
                                    c_void_p, c_size_t, c_void_p]),
     "qk_packed_matmul": (c_int32, [c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_int32,
                                    c_void_p, c_size_t, c_size_t, c_void_p, c_size_t]),
+    "qk_gpu_attention": (c_int32, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_size_t,
+                                   c_void_p, c_size_t, c_int32, c_void_p, c_size_t]),
+    "qk_gpu_attention_sage": (c_int32, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_size_t,
+                                        c_void_p, c_size_t, c_int32, c_size_t, c_void_p, c_size_t]),
     "qk_layer_create": (c_int32, [c_void_p, c_void_p, c_size_t, c_void_p, c_size_t, c_size_t,
                                   c_size_t, c_size_t, c_void_p, c_void_p, c_void_p, c_int32,
                                   POINTER(c_void_p)]),

@@ -1,0 +1,570 @@
+// Exact tiled attention and Sage INT8 attention: host buffers in, host buffers out.
+//
+// Replaces crates/quantibbler-kernels/src/gpu_attention.rs:451-570 (GpuContext::attention,
+// which wraps the third-party cubek-attention 0.3.0 kernel and expands GQA heads on the
+// host) and :589-756 + :67-397 (GpuContext::attention_sage and sage_int8_tile_kernel).
+// Layouts are the reference's: q [B, H, Sq, d], k [B, KV, Skv, d], v [B, KV, Skv, dv],
+// out [B, H, Sq, dv], packed row-major float32; head h reads kv head h / (H / KV);
+// causal masks key j for query i when j + Sq > i + Skv.
+//
+// Exact face: FlashAttention-style online softmax in float32, GQA handled by indexing
+// (no host-side head expansion).  Four lanes share one query row, each owning a quarter
+// of the head dimension; K and V tiles of 32 keys are staged in shared memory.
+//
+// Sage face: the arithmetic of the reference's device kernel, stage for stage, in
+// float32: Q/sqrt(d) per-token INT8, per-key-block channel mean removed from K then
+// per-token INT8, integer QK^T, scores = dQ*dK*dot + (dQ*Qhat).mean, online softmax in
+// full precision, P quantised at the static 1/127 scale, V per-channel INT8 per key block,
+// integer PV, O = alpha*O + pv*(1/127)*dV, O/l at the end.  Unlike the reference (one thread
+// per query row re-quantising every K/V tile into global scratch), the K, V and Q codes are
+// produced once per call by three small kernels and the main kernel takes its integer
+// dots with dp4a.  A key block's P codes all depend on the block's row maximum, so each
+// block is swept twice: once for the maximum, once for P and the PV product.
+#include <cmath>
+#include <cstring>
+#include <string>
+
+#include "qk_common.h"
+
+namespace {
+
+struct AttnDims {
+    uint32_t B, H, KV, Sq, Skv, d, dv, group;
+};
+
+constexpr int kQT = 64;  // queries per block (4 lanes each)
+constexpr int kTK = 32;  // keys per shared-memory tile
+
+// ------------------------------------------------------------------ exact attention
+template <int DPL>
+__global__ void __launch_bounds__(256)
+attention_exact_kernel(const float *__restrict__ q, const float *__restrict__ k,
+                       const float *__restrict__ v, float *__restrict__ out, AttnDims dm,
+                       int causal) {
+    constexpr int PITCH = DPL + 4;  // +4 floats: the four parts of a key land in distinct banks
+    extern __shared__ float sm[];
+    float *Ks = sm, *Vs = sm + kTK * 4 * PITCH;
+    const int qi = threadIdx.x >> 2, part = threadIdx.x & 3;
+    const int i = blockIdx.x * kQT + qi;
+    const bool valid = i < (int)dm.Sq;
+    const int h = blockIdx.y, b = blockIdx.z, kvh = h / dm.group;
+    const float scale = 1.0f / sqrtf((float)dm.d);
+
+    float qr[DPL], o[DPL];
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) {
+        int c = part * DPL + e;
+        qr[e] = (valid && c < (int)dm.d)
+                    ? q[(((size_t)b * dm.H + h) * dm.Sq + i) * dm.d + c] : 0.f;
+        o[e] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    const int skew = (int)dm.Skv - (int)dm.Sq;
+    const int last_key = !valid ? -1 : causal ? i + skew : (int)dm.Skv - 1;
+    const int i_max = min((int)dm.Sq - 1, (int)blockIdx.x * kQT + kQT - 1);
+    const int j_hi = causal ? min((int)dm.Skv, i_max + skew + 1) : (int)dm.Skv;
+    const float *kb = k + ((size_t)b * dm.KV + kvh) * dm.Skv * dm.d;
+    const float *vb = v + ((size_t)b * dm.KV + kvh) * dm.Skv * dm.dv;
+
+    for (int j0 = 0; j0 < j_hi; j0 += kTK) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < kTK * 4 * DPL; idx += 256) {
+            int key = idx / (4 * DPL), c = idx % (4 * DPL);
+            int p2 = c / DPL, e = c % DPL;
+            bool in = j0 + key < (int)dm.Skv;
+            Ks[(key * 4 + p2) * PITCH + e] =
+                (in && c < (int)dm.d) ? kb[(size_t)(j0 + key) * dm.d + c] : 0.f;
+            Vs[(key * 4 + p2) * PITCH + e] =
+                (in && c < (int)dm.dv) ? vb[(size_t)(j0 + key) * dm.dv + c] : 0.f;
+        }
+        __syncthreads();
+        float s[kTK];
+        float tmax = -INFINITY;
+#pragma unroll
+        for (int kk = 0; kk < kTK; ++kk) {
+            const float *kr = Ks + (kk * 4 + part) * PITCH;
+            float dot = 0.f;
+#pragma unroll
+            for (int e = 0; e < DPL; ++e) dot = fmaf(qr[e], kr[e], dot);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            float sc = dot * scale;
+            if (j0 + kk > last_key) sc = -INFINITY;
+            s[kk] = sc;
+            tmax = fmaxf(tmax, sc);
+        }
+        const float m_new = fmaxf(m, tmax);
+        if (m_new == -INFINITY) continue;  // nothing admissible yet (barriers sit at the loop top)
+        const float alpha = expf(m - m_new);
+        l *= alpha;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) o[e] *= alpha;
+#pragma unroll
+        for (int kk = 0; kk < kTK; ++kk) {
+            const float p = expf(s[kk] - m_new);
+            l += p;
+            const float *vr = Vs + (kk * 4 + part) * PITCH;
+#pragma unroll
+            for (int e = 0; e < DPL; ++e) o[e] = fmaf(p, vr[e], o[e]);
+        }
+        m = m_new;
+    }
+    if (valid) {
+        float *orow = out + (((size_t)b * dm.H + h) * dm.Sq + i) * dm.dv;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+            int c = part * DPL + e;
+            if (c < (int)dm.dv) orow[c] = o[e] / l;  // a row with no admissible key is 0/0 = NaN
+        }
+    }
+}
+
+// ------------------------------------------------------------------ Sage quantisers
+__device__ __forceinline__ int quant_code(float x, float delta) {
+    // rint half-to-even of x/delta, clamped to +-127 (gpu_attention.rs:132-155)
+    float r = rintf(x / delta);
+    r = fminf(fmaxf(r, -127.f), 127.f);
+    return (int)r;
+}
+
+// psi_Q: one warp per query row.  codes [rows][dpad] int8 (zero padded), scale [rows].
+__global__ void sage_quant_q_kernel(const float *__restrict__ q, int8_t *__restrict__ codes,
+                                    float *__restrict__ scale, uint32_t rows, uint32_t d,
+                                    uint32_t dpad, float inv_sqrt_d) {
+    uint32_t row = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32, lane = threadIdx.x % 32;
+    if (row >= rows) return;
+    const float *qr = q + (size_t)row * d;
+    float peak = 0.f;
+    for (uint32_t c = lane; c < d; c += 32) peak = fmaxf(peak, fabsf(qr[c] * inv_sqrt_d));
+    for (int off = 16; off > 0; off >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, off));
+    const float delta = peak > 0.f ? peak / 127.f : 1.f;
+    for (uint32_t c = lane; c < dpad; c += 32)
+        codes[(size_t)row * dpad + c] = c < d ? (int8_t)quant_code(qr[c] * inv_sqrt_d, delta) : 0;
+    if (lane == 0) scale[row] = delta;
+}
+
+// gamma + psi_K: one block per (b, kv head, key block).  mean [blk][d] float32 (sequential
+// float32 sum over the block's tokens, then one division, as the reference kernel does),
+// codes [token][dpad], scale [token].
+__global__ void sage_quant_k_kernel(const float *__restrict__ k, int8_t *__restrict__ codes,
+                                    float *__restrict__ scale, float *__restrict__ mean,
+                                    uint32_t S, uint32_t d, uint32_t dpad, uint32_t block,
+                                    uint32_t n_blocks) {
+    extern __shared__ float mu[];  // d floats
+    const uint32_t plane = blockIdx.y, jb = blockIdx.x;
+    const uint32_t j0 = jb * block, j1 = min(S, j0 + block), kj = j1 - j0;
+    const float *kp = k + (size_t)plane * S * d;
+    for (uint32_t c = threadIdx.x; c < d; c += blockDim.x) {
+        float ssum = 0.f;
+        for (uint32_t j = j0; j < j1; ++j) ssum += kp[(size_t)j * d + c];
+        float mval = ssum / (float)kj;
+        mu[c] = mval;
+        mean[((size_t)plane * n_blocks + jb) * d + c] = mval;
+    }
+    __syncthreads();
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, n_warps = blockDim.x / 32;
+    for (uint32_t j = j0 + warp; j < j1; j += n_warps) {
+        const float *kr = kp + (size_t)j * d;
+        float peak = 0.f;
+        for (uint32_t c = lane; c < d; c += 32) peak = fmaxf(peak, fabsf(kr[c] - mu[c]));
+        for (int off = 16; off > 0; off >>= 1)
+            peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, off));
+        const float delta = peak > 0.f ? peak / 127.f : 1.f;
+        int8_t *cr = codes + ((size_t)plane * S + j) * dpad;
+        for (uint32_t c = lane; c < dpad; c += 32)
+            cr[c] = c < d ? (int8_t)quant_code(kr[c] - mu[c], delta) : 0;
+        if (lane == 0) scale[(size_t)plane * S + j] = delta;
+    }
+}
+
+// psi_V: one block per (b, kv head, key block): per-channel scale over the block's tokens,
+// codes stored channel-major with the block's keys contiguous: [blk][dv][bpad] int8.
+__global__ void sage_quant_v_kernel(const float *__restrict__ v, int8_t *__restrict__ codes,
+                                    float *__restrict__ scale, uint32_t S, uint32_t dv,
+                                    uint32_t block, uint32_t bpad, uint32_t n_blocks) {
+    const uint32_t plane = blockIdx.y, jb = blockIdx.x;
+    const uint32_t j0 = jb * block, j1 = min(S, j0 + block);
+    const float *vp = v + (size_t)plane * S * dv;
+    for (uint32_t c = threadIdx.x; c < dv; c += blockDim.x) {
+        float peak = 0.f;
+        for (uint32_t j = j0; j < j1; ++j) peak = fmaxf(peak, fabsf(vp[(size_t)j * dv + c]));
+        const float delta = peak > 0.f ? peak / 127.f : 1.f;
+        int8_t *cr = codes + (((size_t)plane * n_blocks + jb) * dv + c) * bpad;
+        for (uint32_t j = j0; j < j0 + bpad; ++j)
+            cr[j - j0] = j < j1 ? (int8_t)quant_code(vp[(size_t)j * dv + c], delta) : 0;
+        scale[((size_t)plane * n_blocks + jb) * dv + c] = delta;
+    }
+}
+
+struct SageArgs {
+    const int8_t *qc;
+    const float *qs;
+    const int8_t *kc;
+    const float *ks;
+    const float *kmean;
+    const int8_t *vc;
+    const float *vs;
+    float *out;
+    uint32_t dpad, bpad, block, n_blocks;
+};
+
+// Main Sage kernel.  Lane (query, part) owns DPL = dpad/4 (resp. dvpad/4) channels; WPL
+// is that count in 32-bit words of four int8 codes.
+template <int WPL>
+__global__ void __launch_bounds__(256)
+attention_sage_kernel(SageArgs a, AttnDims dm, int causal) {
+    constexpr int DPL = WPL * 4;
+    extern __shared__ int smi[];
+    int *Kt = smi;                     // [kTK][4][WPL+1] words of K codes
+    float *Kscale = (float *)(Kt + kTK * 4 * (WPL + 1));  // [kTK]
+    int *Vt = (int *)(Kscale + kTK);   // [4*DPL channels][kTK/4 + 1] words of V codes (keys packed)
+    const int qi = threadIdx.x >> 2, part = threadIdx.x & 3;
+    const int i = blockIdx.x * kQT + qi;
+    const bool valid = i < (int)dm.Sq;
+    const int h = blockIdx.y, b = blockIdx.z, kvh = h / dm.group;
+    const size_t qrow = ((size_t)b * dm.H + h) * dm.Sq + (valid ? i : 0);
+    const size_t plane = (size_t)b * dm.KV + kvh;
+
+    int qw[WPL];
+    float qdq[DPL];  // dequantised query, for the mean shift
+    const float qdelta = a.qs[qrow];
+#pragma unroll
+    for (int w = 0; w < WPL; ++w) {
+        int word = valid ? reinterpret_cast<const int *>(a.qc + qrow * a.dpad)[part * WPL + w] : 0;
+        qw[w] = word;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) qdq[w * 4 + e] = (float)(int8_t)(word >> (8 * e)) * qdelta;
+    }
+    float o[DPL];
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) o[e] = 0.f;
+    float m = -INFINITY, l = 0.f;
+
+    const int block = (int)a.block;
+    const int i_max = min((int)dm.Sq - 1, (int)blockIdx.x * kQT + kQT - 1);
+    const int jb_hi = causal ? i_max / block + 1 : (int)a.n_blocks;  // key blocks this tile visits
+    const int my_jb_hi = !valid ? 0 : causal ? i / block + 1 : (int)a.n_blocks;
+
+    for (int jb = 0; jb < jb_hi; ++jb) {
+        const int j0 = jb * block, kj = min(block, (int)dm.Skv - j0);
+        const bool mine = jb < my_jb_hi;
+        // shift = (dQ * Qhat) . mean of this block
+        float shift = 0.f;
+        {
+            const float *mu = a.kmean + (plane * a.n_blocks + jb) * dm.d;
+#pragma unroll
+            for (int e = 0; e < DPL; ++e) {
+                int c = part * DPL + e;
+                if (c < (int)dm.d) shift = fmaf(qdq[e], mu[c], shift);
+            }
+            shift += __shfl_xor_sync(0xffffffffu, shift, 1);
+            shift += __shfl_xor_sync(0xffffffffu, shift, 2);
+        }
+        float m_new = m;
+        int pv[DPL];
+        float esum = 0.f, alpha = 0.f;
+        for (int pass = 0; pass < 2; ++pass) {
+            if (pass == 1) {
+                alpha = (m_new == -INFINITY) ? 0.f : expf(m - m_new);
+#pragma unroll
+                for (int e = 0; e < DPL; ++e) pv[e] = 0;
+            }
+            for (int t0 = 0; t0 < kj; t0 += kTK) {
+                const int tk = min(kTK, kj - t0);
+                __syncthreads();
+                for (int idx = threadIdx.x; idx < kTK * 4 * WPL; idx += 256) {
+                    int key = idx / (4 * WPL), w = idx % (4 * WPL);
+                    int word = 0;
+                    if (key < tk)
+                        word = reinterpret_cast<const int *>(
+                            a.kc + (plane * dm.Skv + j0 + t0 + key) * a.dpad)[w];
+                    Kt[(key * 4 + w / WPL) * (WPL + 1) + w % WPL] = word;
+                }
+                if (threadIdx.x < kTK)
+                    Kscale[threadIdx.x] =
+                        (int)threadIdx.x < tk ? a.ks[plane * dm.Skv + j0 + t0 + threadIdx.x] : 1.f;
+                if (pass == 1) {
+                    for (int idx = threadIdx.x; idx < 4 * DPL * (kTK / 4); idx += 256) {
+                        int c = idx / (kTK / 4), w = idx % (kTK / 4);
+                        int word = 0;
+                        if (c < (int)dm.dv && t0 + w * 4 < (int)a.bpad)
+                            word = reinterpret_cast<const int *>(
+                                a.vc + ((plane * a.n_blocks + jb) * dm.dv + c) * a.bpad + t0)[w];
+                        Vt[c * (kTK / 4 + 1) + w] = word;
+                    }
+                }
+                __syncthreads();
+                float s[kTK];
+#pragma unroll
+                for (int kk = 0; kk < kTK; ++kk) {
+                    const int *kr = Kt + (kk * 4 + part) * (WPL + 1);
+                    int dot = 0;
+#pragma unroll
+                    for (int w = 0; w < WPL; ++w) dot = __dp4a(qw[w], kr[w], dot);
+                    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+                    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+                    float sc = (float)dot * qdelta * Kscale[kk] + shift;
+                    const int j = j0 + t0 + kk;
+                    if (kk >= tk || !mine || (causal && j > i)) sc = -INFINITY;
+                    s[kk] = sc;
+                }
+                if (pass == 0) {
+#pragma unroll
+                    for (int kk = 0; kk < kTK; ++kk) m_new = fmaxf(m_new, s[kk]);
+                } else {
+                    // P codes of this 32-key slice, four keys per word, then the integer PV
+                    int pw[kTK / 4];
+#pragma unroll
+                    for (int w = 0; w < kTK / 4; ++w) {
+                        int word = 0;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float p = (m_new == -INFINITY) ? 0.f : expf(s[w * 4 + e] - m_new);
+                            esum += p;
+                            float r = fminf(fmaxf(rintf(p * 127.f), 0.f), 127.f);
+                            word |= ((int)r) << (8 * e);
+                        }
+                        pw[w] = word;
+                    }
+#pragma unroll
+                    for (int e = 0; e < DPL; ++e) {
+                        const int *vr = Vt + (part * DPL + e) * (kTK / 4 + 1);
+                        int acc = pv[e];
+#pragma unroll
+                        for (int w = 0; w < kTK / 4; ++w) acc = __dp4a(pw[w], vr[w], acc);
+                        pv[e] = acc;
+                    }
+                }
+            }
+        }
+        if (mine && m_new != -INFINITY) {
+            const float *vsc = a.vs + (plane * a.n_blocks + jb) * dm.dv;
+            l = alpha * l + esum;
+#pragma unroll
+            for (int e = 0; e < DPL; ++e) {
+                int c = part * DPL + e;
+                float vd = c < (int)dm.dv ? vsc[c] : 1.f;
+                o[e] = alpha * o[e] + (float)pv[e] * (1.0f / 127.0f) * vd;
+            }
+            m = m_new;
+        }
+    }
+    if (valid) {
+        float *orow = a.out + qrow * dm.dv;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+            int c = part * DPL + e;
+            if (c < (int)dm.dv) orow[c] = o[e] / l;
+        }
+    }
+}
+
+// ------------------------------------------------------------------ host side
+std::string shape_debug(const qk_attention_shape *s) {
+    // Rust's `{:?}` of AttentionShape (gpu_attention.rs:402-411)
+    char buf[256];
+    snprintf(buf, sizeof buf,
+             "AttentionShape { batch: %zu, n_heads: %zu, n_kv_heads: %zu, seq_q: %zu, seq_kv: %zu, "
+             "head_dim: %zu, val_dim: %zu }",
+             s->batch, s->n_heads, s->n_kv_heads, s->seq_q, s->seq_kv, s->head_dim, s->val_dim);
+    return buf;
+}
+
+// gpu_attention.rs:468-508 / :604-655: the checks shared by both faces, in the
+// reference's order and with its texts.
+qk_status validate_attention(const qk_attention_shape *s, size_t q_len, size_t k_len, size_t v_len,
+                             bool sage, size_t block_size, size_t out_len) {
+    if (!s) return qk::fail(QK_ERR_VALUE, "attention shape is null");
+    if (s->batch == 0 || s->n_heads == 0 || s->n_kv_heads == 0)
+        return qk::fail(QK_ERR_VALUE, "attention requires non-empty batch and head dimensions");
+    if (s->n_heads % s->n_kv_heads != 0)
+        return qk::fail(QK_ERR_VALUE, "n_kv_heads must divide n_heads: n_heads=%zu, n_kv_heads=%zu",
+                        s->n_heads, s->n_kv_heads);
+    if (s->seq_q == 0 || s->seq_kv == 0 || s->head_dim == 0 || s->val_dim == 0)
+        return qk::fail(QK_ERR_VALUE, "attention requires non-empty sequence and head dimensions");
+    if (sage) {
+        if (s->seq_q != s->seq_kv)
+            return qk::fail(QK_ERR_VALUE,
+                            "sage attention is self-attention over one cache: seq_q=%zu, seq_kv=%zu",
+                            s->seq_q, s->seq_kv);
+        if (block_size == 0)
+            return qk::fail(QK_ERR_VALUE,
+                            "sage attention requires a positive block_size ([SA] \xC2\xA7"
+                            "4's tile width)");
+    }
+    size_t eq = s->batch * s->n_heads * s->seq_q * s->head_dim;
+    size_t ek = s->batch * s->n_kv_heads * s->seq_kv * s->head_dim;
+    size_t ev = s->batch * s->n_kv_heads * s->seq_kv * s->val_dim;
+    if (q_len != eq)
+        return qk::fail(QK_ERR_VALUE, "query must hold %zu values for %s, got %zu", eq,
+                        shape_debug(s).c_str(), q_len);
+    if (k_len != ek)
+        return qk::fail(QK_ERR_VALUE, "key must hold %zu values for %s, got %zu", ek,
+                        shape_debug(s).c_str(), k_len);
+    if (v_len != ev)
+        return qk::fail(QK_ERR_VALUE, "value must hold %zu values for %s, got %zu", ev,
+                        shape_debug(s).c_str(), v_len);
+    uint64_t largest = eq > ek ? eq : ek;
+    if (ev > largest) largest = ev;
+    if (largest > qk::kIndexCeiling)
+        return qk::fail(QK_ERR_VALUE,
+                        sage ? "sage attention inputs exceed the device u32 index ceiling (%llu); "
+                               "use the reference face"
+                             : "attention inputs exceed the device u32 index ceiling (%llu); use "
+                               "the CPU reference face",
+                        (unsigned long long)qk::kIndexCeiling);
+    size_t eo = s->batch * s->n_heads * s->seq_q * s->val_dim;
+    if (out_len != eo)
+        return qk::fail(QK_ERR_VALUE, "output must hold %zu values for %s, got %zu", eo,
+                        shape_debug(s).c_str(), out_len);
+    if (s->head_dim > 256 || s->val_dim > 256)
+        return qk::fail(QK_ERR_VALUE, "head_dim/val_dim above 256 are not supported: %s",
+                        shape_debug(s).c_str());
+    return QK_OK;
+}
+
+AttnDims dims_of(const qk_attention_shape *s) {
+    return {(uint32_t)s->batch,   (uint32_t)s->n_heads,  (uint32_t)s->n_kv_heads,
+            (uint32_t)s->seq_q,   (uint32_t)s->seq_kv,   (uint32_t)s->head_dim,
+            (uint32_t)s->val_dim, (uint32_t)(s->n_heads / s->n_kv_heads)};
+}
+
+template <int DPL>
+qk_status launch_exact(qk_ctx *c, const float *q, const float *k, const float *v, float *out,
+                       const AttnDims &dm, int causal) {
+    size_t smem = 2 * kTK * 4 * (DPL + 4) * sizeof(float);
+    if (smem > 48 * 1024)
+        QK_CUDA(cudaFuncSetAttribute(attention_exact_kernel<DPL>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)qk::ceil_div(dm.Sq, kQT), dm.H, dm.B);
+    attention_exact_kernel<DPL><<<grid, 256, smem, c->stream>>>(q, k, v, out, dm, causal);
+    QK_CUDA(cudaGetLastError());
+    c->launches++;
+    return QK_OK;
+}
+
+template <int WPL>
+qk_status launch_sage(qk_ctx *c, const SageArgs &a, const AttnDims &dm, int causal) {
+    size_t smem = (kTK * 4 * (WPL + 1) + kTK + 16 * WPL * (kTK / 4 + 1)) * sizeof(int);
+    if (smem > 48 * 1024)
+        QK_CUDA(cudaFuncSetAttribute(attention_sage_kernel<WPL>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)qk::ceil_div(dm.Sq, kQT), dm.H, dm.B);
+    attention_sage_kernel<WPL><<<grid, 256, smem, c->stream>>>(a, dm, causal);
+    QK_CUDA(cudaGetLastError());
+    c->launches++;
+    return QK_OK;
+}
+
+}  // namespace
+
+namespace qk {
+
+// Device-buffer form of the exact face (also used by the decoder path).
+qk_status attention_exact_dev(qk_ctx *c, const float *q, const float *k, const float *v,
+                              float *out, const qk_attention_shape *s, int causal) {
+    AttnDims dm = dims_of(s);
+    size_t widest = s->head_dim > s->val_dim ? s->head_dim : s->val_dim;
+    if (widest <= 16) return launch_exact<4>(c, q, k, v, out, dm, causal);
+    if (widest <= 64) return launch_exact<16>(c, q, k, v, out, dm, causal);
+    if (widest <= 128) return launch_exact<32>(c, q, k, v, out, dm, causal);
+    return launch_exact<64>(c, q, k, v, out, dm, causal);
+}
+
+}  // namespace qk
+
+extern "C" {
+
+qk_status qk_gpu_attention(qk_ctx *ctx, const qk_attention_shape *shape, const float *query,
+                           size_t q_len, const float *key, size_t k_len, const float *value,
+                           size_t v_len, int32_t causal, float *out, size_t out_len) {
+    qk_status st = validate_attention(shape, q_len, k_len, v_len, false, 0, out_len);
+    if (st != QK_OK) return st;
+    qk_ctx *c;
+    if ((st = qk::resolve_ctx(ctx, &c)) != QK_OK) return st;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    const size_t qb = q_len * 4, kb = k_len * 4, vb = v_len * 4, ob = out_len * 4;
+    auto up = [](size_t n) { return (n + 255) / 256 * 256; };
+    if ((st = c->d_in.reserve(up(qb) + up(kb) + up(vb))) != QK_OK) return st;
+    if ((st = c->d_out.reserve(ob)) != QK_OK) return st;
+    uint8_t *base = (uint8_t *)c->d_in.ptr;
+    float *dq = (float *)base, *dk = (float *)(base + up(qb)), *dv = (float *)(base + up(qb) + up(kb));
+    QK_CUDA(cudaMemcpyAsync(dq, query, qb, cudaMemcpyHostToDevice, c->stream));
+    QK_CUDA(cudaMemcpyAsync(dk, key, kb, cudaMemcpyHostToDevice, c->stream));
+    QK_CUDA(cudaMemcpyAsync(dv, value, vb, cudaMemcpyHostToDevice, c->stream));
+    if ((st = qk::attention_exact_dev(c, dq, dk, dv, (float *)c->d_out.ptr, shape, causal != 0)) !=
+        QK_OK)
+        return st;
+    QK_CUDA(cudaMemcpyAsync(out, c->d_out.ptr, ob, cudaMemcpyDeviceToHost, c->stream));
+    QK_CUDA(cudaStreamSynchronize(c->stream));
+    return QK_OK;
+}
+
+qk_status qk_gpu_attention_sage(qk_ctx *ctx, const qk_attention_shape *shape, const float *query,
+                                size_t q_len, const float *key, size_t k_len, const float *value,
+                                size_t v_len, int32_t causal, size_t block_size, float *out,
+                                size_t out_len) {
+    qk_status st = validate_attention(shape, q_len, k_len, v_len, true, block_size, out_len);
+    if (st != QK_OK) return st;
+    qk_ctx *c;
+    if ((st = qk::resolve_ctx(ctx, &c)) != QK_OK) return st;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    const AttnDims dm = dims_of(shape);
+    const size_t S = dm.Skv;
+    if (block_size > S) block_size = S;  // one block covers the whole sequence either way
+    const size_t n_blocks = qk::ceil_div(S, block_size);
+    const size_t widest = dm.d > dm.dv ? dm.d : dm.dv;
+    const size_t wpl = widest <= 16 ? 1 : widest <= 64 ? 4 : widest <= 128 ? 8 : 16;
+    const size_t dpad = wpl * 16;                       // four lanes x WPL words x four codes
+    const size_t bpad = qk::ceil_div(block_size, kTK) * kTK;  // keys of a block, padded to the tile
+    const size_t planes = (size_t)dm.B * dm.KV, qrows = (size_t)dm.B * dm.H * dm.Sq;
+    auto up = [](size_t n) { return (n + 255) / 256 * 256; };
+    const size_t qb = q_len * 4, kb = k_len * 4, vb = v_len * 4, ob = out_len * 4;
+    // scratch: inputs, then codes and scales
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o2 = off; off += up(bytes); return o2; };
+    const size_t o_q = take(qb), o_k = take(kb), o_v = take(vb);
+    const size_t o_qc = take(qrows * dpad), o_qs = take(qrows * 4);
+    const size_t o_kc = take(planes * S * dpad), o_ks = take(planes * S * 4);
+    const size_t o_km = take(planes * n_blocks * dm.d * 4);
+    const size_t o_vc = take(planes * n_blocks * dm.dv * bpad), o_vs = take(planes * n_blocks * dm.dv * 4);
+    if ((st = c->d_in.reserve(off)) != QK_OK) return st;
+    if ((st = c->d_out.reserve(ob)) != QK_OK) return st;
+    uint8_t *base = (uint8_t *)c->d_in.ptr;
+    float *dq = (float *)(base + o_q), *dk = (float *)(base + o_k), *dv = (float *)(base + o_v);
+    QK_CUDA(cudaMemcpyAsync(dq, query, qb, cudaMemcpyHostToDevice, c->stream));
+    QK_CUDA(cudaMemcpyAsync(dk, key, kb, cudaMemcpyHostToDevice, c->stream));
+    QK_CUDA(cudaMemcpyAsync(dv, value, vb, cudaMemcpyHostToDevice, c->stream));
+    const float inv_sqrt_d = 1.0f / sqrtf((float)dm.d);  // gpu_attention.rs:720
+    sage_quant_q_kernel<<<(unsigned)qk::ceil_div(qrows, 8), 256, 0, c->stream>>>(
+        dq, (int8_t *)(base + o_qc), (float *)(base + o_qs), (uint32_t)qrows, dm.d, (uint32_t)dpad,
+        inv_sqrt_d);
+    QK_CUDA(cudaGetLastError());
+    dim3 kgrid((unsigned)n_blocks, (unsigned)planes);
+    sage_quant_k_kernel<<<kgrid, 128, dm.d * sizeof(float), c->stream>>>(
+        dk, (int8_t *)(base + o_kc), (float *)(base + o_ks), (float *)(base + o_km), (uint32_t)S,
+        dm.d, (uint32_t)dpad, (uint32_t)block_size, (uint32_t)n_blocks);
+    QK_CUDA(cudaGetLastError());
+    sage_quant_v_kernel<<<kgrid, 128, 0, c->stream>>>(
+        dv, (int8_t *)(base + o_vc), (float *)(base + o_vs), (uint32_t)S, dm.dv,
+        (uint32_t)block_size, (uint32_t)bpad, (uint32_t)n_blocks);
+    QK_CUDA(cudaGetLastError());
+    c->launches += 3;
+    SageArgs a{(const int8_t *)(base + o_qc), (const float *)(base + o_qs),
+               (const int8_t *)(base + o_kc), (const float *)(base + o_ks),
+               (const float *)(base + o_km),  (const int8_t *)(base + o_vc),
+               (const float *)(base + o_vs),  (float *)c->d_out.ptr,
+               (uint32_t)dpad, (uint32_t)bpad, (uint32_t)block_size, (uint32_t)n_blocks};
+    if (wpl == 1) st = launch_sage<1>(c, a, dm, causal != 0);
+    else if (wpl == 4) st = launch_sage<4>(c, a, dm, causal != 0);
+    else if (wpl == 8) st = launch_sage<8>(c, a, dm, causal != 0);
+    else st = launch_sage<16>(c, a, dm, causal != 0);
+    if (st != QK_OK) return st;
+    QK_CUDA(cudaMemcpyAsync(out, c->d_out.ptr, ob, cudaMemcpyDeviceToHost, c->stream));
+    QK_CUDA(cudaStreamSynchronize(c->stream));
+    return QK_OK;
+}
+
+}  // extern "C"

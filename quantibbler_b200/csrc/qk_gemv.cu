@@ -24,12 +24,14 @@
 // the exact sum than the reference's own float64 left-to-right loop.
 //
 // Data layout in HBM (built once by qk_layer_create):
-//   * tiles: the factor's rows are cut into 16-row x 512-bit tiles of 1 KB, stored
-//     row-tile-major then k-step-major.  Inside a tile, the 16-byte piece of row
-//     (g + 8*h) at byte offset 16*t is stored at piece index h*32 + 4*g + t, so lane
-//     (g,t) of a warp fetches its two pieces with two fully coalesced 512-byte
-//     128-bit loads.  Rows are padded to a multiple of 16 and bits to a multiple of
-//     512 with zeros.
+//   * tiles: the factor's rows are cut into groups of 64 rows and k-steps of 512 bits.
+//     One (group, k-step) pair is a 4 KB chunk holding four 16-row x 512-bit tiles;
+//     chunks are stored group-major then k-step-major, which is exactly the order a
+//     warp consumes them in, so every warp streams one contiguous byte range.  Inside
+//     a tile, the 16-byte piece of row (g + 8*h) at byte offset 16*t sits at piece
+//     index h*32 + 4*g + t, so lane (g,t) of a warp moves its own eight pieces of a
+//     chunk with eight fully coalesced 512-byte warp transfers.  Rows are padded to a
+//     multiple of 64 and bits to a multiple of 512 with zeros.
 //   * rows: the reference's per-row bitplanes padded to 16-byte rows; only the
 //     sign-select kernel reads it.
 //
@@ -161,7 +163,10 @@ gemv_signselect_kernel(const StageParams *__restrict__ many, uint32_t n_rows, ui
 constexpr int kTileRows = 16;
 constexpr int kStepBits = 512;      // bits of one row inside one tile
 constexpr int kTileBytes = 1024;
-constexpr int kTilesPerWarp = 4;    // row tiles that share one B fragment
+constexpr int kTilesPerWarp = 4;    // row tiles of a group; they share every B fragment
+constexpr int kGroupRows = kTileRows * kTilesPerWarp;
+constexpr int kChunkBytes = kTileBytes * kTilesPerWarp;
+constexpr int kStages = 3;          // chunks in flight per warp (cp.async ring)
 constexpr int kQBits = 46;          // |q_k| < 2^(kQBits+1)
 
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -173,12 +178,16 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 ld_stream(const uint4 *p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+    uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // Converts one instance's input vector to its digit table.  One block per instance.
@@ -275,46 +284,58 @@ digit_table_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32
 
 // out[row] = epilogue((2 * sum_{bit=1} q_k - sum q_k) * 2^-shift).
 //   kFinal = false: writes the float64 intermediate t;  true: y = float(u)*s1 + bias.
-// grid.x tiles the rows (8 warps x 4 tiles x 16 rows per block), grid.y is the instance.
+// grid.y is the instance; the instance's row groups are dealt to the grid.x * 8 warps
+// in contiguous runs of `groups_per_warp`, so each warp reads one contiguous range of
+// chunks.  Every lane copies exactly the eight 16-byte pieces it will consume itself
+// through a private three-deep cp.async ring: no barrier of any kind is needed.
 template <bool kRoundBf16, bool kFinal>
 __global__ void __launch_bounds__(256, 2)
-gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint32_t n_tiles,
-                     uint32_t n_steps) {
+gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint32_t n_groups,
+                     uint32_t n_steps, uint32_t groups_per_warp) {
+    extern __shared__ __align__(16) uint8_t ring_all[];
     const StageParams p = many[blockIdx.y];
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t g = lane / 4, t = lane % 4;
-    const uint32_t tile0 = (blockIdx.x * 8 + warp) * kTilesPerWarp;
-    if (tile0 >= n_tiles) return;
-    const uint32_t my_tiles = min((uint32_t)kTilesPerWarp, n_tiles - tile0);
+    const uint32_t group_begin = (blockIdx.x * 8 + warp) * groups_per_warp;
+    if (group_begin >= n_groups) return;
+    const uint32_t group_end = min(n_groups, group_begin + groups_per_warp);
+    const uint32_t c_begin = group_begin * n_steps, c_end = group_end * n_steps;
+
+    uint4 *ring = reinterpret_cast<uint4 *>(ring_all + (size_t)warp * kStages * kChunkBytes) + lane;
+    const uint4 *src = reinterpret_cast<const uint4 *>(p.w_tiles) + lane;
+    auto issue = [&](uint32_t c) {
+        if (c < c_end) {
+            uint4 *dst = ring + (size_t)(c % kStages) * (kChunkBytes / 16);
+            const uint4 *from = src + (size_t)c * (kChunkBytes / 16);
+#pragma unroll
+            for (int piece = 0; piece < 8; ++piece) cp_async16(dst + piece * 32, from + piece * 32);
+        }
+        cp_async_commit();  // an empty group keeps the group count in step with c
+    };
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) issue(c_begin + s);
 
     int acc[kTilesPerWarp][4];
 #pragma unroll
     for (int m = 0; m < kTilesPerWarp; ++m)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[m][e] = 0;
-
-    const uint4 *wbase =
-        reinterpret_cast<const uint4 *>(p.w_tiles + (size_t)tile0 * n_steps * kTileBytes) + lane;
-    const size_t tile_stride = (size_t)n_steps * (kTileBytes / 16);  // in uint4
     const uint2 *dig = p.digits + t * 8 + g;
+    const StageMeta meta = *p.meta;
+    const long long th = meta.total >> 26;
+    const long long tl = (meta.total & ((1ll << 26) - 1)) << 6;
+    const int sh0 = 16 * (t & 1);
 
-    uint4 cur[kTilesPerWarp][2], nxt[kTilesPerWarp][2];
-#pragma unroll
-    for (int m = 0; m < kTilesPerWarp; ++m) {
-        cur[m][0] = cur[m][1] = make_uint4(0, 0, 0, 0);
-        if ((uint32_t)m < my_tiles) {
-            cur[m][0] = ld_stream(wbase + m * tile_stride);
-            cur[m][1] = ld_stream(wbase + m * tile_stride + 32);
-        }
-    }
-    for (uint32_t ks = 0; ks < n_steps; ++ks) {
+    uint32_t ks = 0, group = group_begin;
+    for (uint32_t c = c_begin; c < c_end; ++c) {
+        issue(c + kStages - 1);          // refills the slot consumed one iteration ago
+        cp_async_wait<kStages - 1>();    // this lane's pieces of chunk c have landed
+        const uint4 *stage = ring + (size_t)(c % kStages) * (kChunkBytes / 16);
+        uint4 cur[kTilesPerWarp][2];
 #pragma unroll
         for (int m = 0; m < kTilesPerWarp; ++m) {
-            nxt[m][0] = nxt[m][1] = make_uint4(0, 0, 0, 0);
-            if (ks + 1 < n_steps && (uint32_t)m < my_tiles) {
-                nxt[m][0] = ld_stream(wbase + m * tile_stride + (size_t)(ks + 1) * 64);
-                nxt[m][1] = ld_stream(wbase + m * tile_stride + (size_t)(ks + 1) * 64 + 32);
-            }
+            cur[m][0] = stage[m * 64];
+            cur[m][1] = stage[m * 64 + 32];
         }
         const uint2 *dk = dig + (size_t)ks * 512;
 #pragma unroll
@@ -333,33 +354,25 @@ gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint
                 }
             }
         }
+        if (++ks < n_steps) continue;
+        ks = 0;
+        // ---- the group's 64 rows are complete
+        // Exact recombination.  Lane (g,t) holds digit columns 2t and 2t+1 of rows g
+        // (acc[.][0..1]) and g+8 (acc[.][2..3]).  With X = sum_n c_n 256^n = 128 * S and
+        // T = sum q_k, the row's value is (X - 64 T) / 64 * 2^-shift.  X is kept as
+        // hi * 2^32 + lo (digits 4..7 and 0..3) and 64 T as th * 2^32 + tl, so the
+        // subtraction is exact in int64 and only the last conversion rounds.
 #pragma unroll
         for (int m = 0; m < kTilesPerWarp; ++m) {
-            cur[m][0] = nxt[m][0];
-            cur[m][1] = nxt[m][1];
-        }
-    }
-
-    // Exact recombination.  Lane (g,t) holds digit columns 2t and 2t+1 of rows g
-    // (acc[.][0..1]) and g+8 (acc[.][2..3]).  With X = sum_n c_n 256^n = 128 * S and
-    // T = sum q_k, the row's value is (X - 64 T) / 64 * 2^-shift.  X is kept as
-    // hi * 2^32 + lo (digits 4..7 and 0..3) and 64 T as th * 2^32 + tl, so the
-    // subtraction is exact in int64 and only the last conversion rounds.
-    const StageMeta meta = *p.meta;
-    const long long th = meta.total >> 26;
-    const long long tl = (meta.total & ((1ll << 26) - 1)) << 6;
-    const int sh0 = 16 * (t & 1);
-#pragma unroll
-    for (int m = 0; m < kTilesPerWarp; ++m) {
-        long long pg = ((long long)acc[m][0] << sh0) + ((long long)acc[m][1] << (sh0 + 8));
-        long long ph = ((long long)acc[m][2] << sh0) + ((long long)acc[m][3] << (sh0 + 8));
-        pg += __shfl_xor_sync(0xffffffffu, pg, 1);  // lanes t=0,1: low half; t=2,3: high half
-        ph += __shfl_xor_sync(0xffffffffu, ph, 1);
-        const long long og = __shfl_xor_sync(0xffffffffu, pg, 2);
-        const long long oh = __shfl_xor_sync(0xffffffffu, ph, 2);
-        if (t < 2 && (uint32_t)m < my_tiles) {
-            const uint32_t row = (tile0 + m) * kTileRows + g + 8 * t;
-            if (row < n_rows) {
+            long long pg = ((long long)acc[m][0] << sh0) + ((long long)acc[m][1] << (sh0 + 8));
+            long long ph = ((long long)acc[m][2] << sh0) + ((long long)acc[m][3] << (sh0 + 8));
+            pg += __shfl_xor_sync(0xffffffffu, pg, 1);  // t=0,1: low half; t=2,3: high half
+            ph += __shfl_xor_sync(0xffffffffu, ph, 1);
+            const long long og = __shfl_xor_sync(0xffffffffu, pg, 2);
+            const long long oh = __shfl_xor_sync(0xffffffffu, ph, 2);
+            acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0;
+            const uint32_t row = group * kGroupRows + m * kTileRows + g + 8 * t;
+            if (t < 2 && row < n_rows) {
                 const long long lo = t == 0 ? pg : ph, hi = t == 0 ? og : oh;
                 double val = ldexp((double)(hi - th) * 4294967296.0 + (double)(lo - tl),
                                    -meta.shift - 6);
@@ -375,7 +388,9 @@ gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint
                 }
             }
         }
+        ++group;
     }
+    cp_async_wait<0>();
 }
 
 // ------------------------------------------------------------------ layer construction
@@ -396,17 +411,18 @@ __global__ void pad_rows_kernel(const uint8_t *__restrict__ src, uint8_t *__rest
     dst[gid] = v;
 }
 
-// Padded rows -> 16 x 512 tiles (one thread per 16-byte piece of the tile array).
+// Padded rows -> 4 KB chunks of four 16 x 512 tiles (one thread per 16-byte piece).
 __global__ void tile_rows_kernel(const uint8_t *__restrict__ rows, uint8_t *__restrict__ tiles,
-                                 uint32_t n_rows, uint32_t stride, uint32_t n_tiles,
+                                 uint32_t n_rows, uint32_t stride, uint32_t n_groups,
                                  uint32_t n_steps) {
     uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (gid >= (uint64_t)n_tiles * n_steps * 64) return;
-    uint64_t blk = gid / 64;
-    uint32_t within = (uint32_t)(gid % 64);
-    uint32_t rt = (uint32_t)(blk / n_steps), ks = (uint32_t)(blk % n_steps);
-    uint32_t half = within / 32, lane = within % 32, g = lane / 4, t = lane % 4;
-    uint32_t row = rt * kTileRows + g + 8 * half;
+    if (gid >= (uint64_t)n_groups * n_steps * 256) return;
+    uint64_t chunk = gid / 256;
+    uint32_t within = (uint32_t)(gid % 256);
+    uint32_t grp = (uint32_t)(chunk / n_steps), ks = (uint32_t)(chunk % n_steps);
+    uint32_t m = within / 64, half = (within % 64) / 32, lane = within % 32;
+    uint32_t g = lane / 4, t = lane % 4;
+    uint32_t row = grp * kGroupRows + m * kTileRows + g + 8 * half;
     uint32_t off = ks * 64 + t * 16;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (row < n_rows && off < stride)
@@ -420,15 +436,15 @@ size_t signselect_smem(size_t n_bits) {
 
 // ------------------------------------------------------------------ launches
 struct StageShape {
-    size_t n_rows, n_bits, row_stride, n_tiles, n_steps;
+    size_t n_rows, n_bits, row_stride, n_groups, n_steps;
 };
 
 StageShape stage1_shape(const qk_layer *l) {
-    return {l->r, l->din, l->vbt_stride, qk::ceil_div(l->r, kTileRows),
+    return {l->r, l->din, l->vbt_stride, qk::ceil_div(l->r, kGroupRows),
             qk::ceil_div(l->din, kStepBits)};
 }
 StageShape stage2_shape(const qk_layer *l) {
-    return {l->dout, l->r, l->ub_stride, qk::ceil_div(l->dout, kTileRows),
+    return {l->dout, l->r, l->ub_stride, qk::ceil_div(l->dout, kGroupRows),
             qk::ceil_div(l->r, kStepBits)};
 }
 
@@ -455,10 +471,20 @@ qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, con
     table<<<(unsigned)n_inst, 256, 0, c->stream>>>(many, (uint32_t)s.n_bits, (uint32_t)s.n_steps);
     QK_CUDA(cudaGetLastError());
     c->launches++;
-    dim3 grid((unsigned)qk::ceil_div(s.n_tiles, 8 * kTilesPerWarp), (unsigned)n_inst);
+    // Deal the row groups to warps: about eight chunks per warp keeps the copy ring in
+    // steady state, but never fewer warps than it takes to give every SM two blocks.
+    size_t chunks = s.n_groups * s.n_steps;
+    size_t warps = qk::ceil_div(chunks, 8);
+    size_t fill = qk::ceil_div((size_t)c->sm_count * 2 * 8, n_inst);
+    if (warps < fill) warps = fill;
+    if (warps > s.n_groups) warps = s.n_groups;
+    size_t gpw = qk::ceil_div(s.n_groups, warps);
+    dim3 grid((unsigned)qk::ceil_div(qk::ceil_div(s.n_groups, gpw), 8), (unsigned)n_inst);
+    const size_t smem = 8 * kStages * kChunkBytes;
     auto gemv = bf16 ? gemv_bitslice_kernel<true, kFinal> : gemv_bitslice_kernel<false, kFinal>;
-    gemv<<<grid, 256, 0, c->stream>>>(many, (uint32_t)s.n_rows, (uint32_t)s.n_tiles,
-                                      (uint32_t)s.n_steps);
+    QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    gemv<<<grid, 256, smem, c->stream>>>(many, (uint32_t)s.n_rows, (uint32_t)s.n_groups,
+                                         (uint32_t)s.n_steps, (uint32_t)gpw);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     return QK_OK;
@@ -567,16 +593,16 @@ qk_status upload_factor(qk_ctx *c, const uint8_t *host, size_t len, size_t n_row
                         uint8_t **rows_out, size_t *stride_out, uint8_t **tiles_out) {
     size_t row_words = qk::ceil_div(n_bits, 8);
     size_t stride = qk::ceil_div(row_words, 16) * 16;
-    size_t n_tiles = qk::ceil_div(n_rows, kTileRows), n_steps = qk::ceil_div(n_bits, kStepBits);
+    size_t n_groups = qk::ceil_div(n_rows, kGroupRows), n_steps = qk::ceil_div(n_bits, kStepBits);
     qk_status st;
     if ((st = c->d_packed.reserve(len)) != QK_OK) return st;
     uint8_t *rows = nullptr, *tiles = nullptr;
     cudaError_t e = cudaMalloc(&rows, n_rows * stride);
-    if (e == cudaSuccess) e = cudaMalloc(&tiles, n_tiles * n_steps * kTileBytes);
+    if (e == cudaSuccess) e = cudaMalloc(&tiles, n_groups * n_steps * kChunkBytes);
     if (e != cudaSuccess) {
         if (rows) cudaFree(rows);
         return qk::fail(QK_ERR_ALLOC, "device allocation of %zu bytes failed: %s",
-                        n_rows * stride + n_tiles * n_steps * kTileBytes, cudaGetErrorString(e));
+                        n_rows * stride + n_groups * n_steps * kChunkBytes, cudaGetErrorString(e));
     }
     *rows_out = rows;
     *tiles_out = tiles;
@@ -587,9 +613,9 @@ qk_status upload_factor(qk_ctx *c, const uint8_t *host, size_t len, size_t n_row
         (const uint8_t *)c->d_packed.ptr, rows, (uint32_t)n_rows, (uint32_t)n_bits,
         (uint32_t)row_words, (uint32_t)stride);
     QK_CUDA(cudaGetLastError());
-    size_t pieces = n_tiles * n_steps * 64;
+    size_t pieces = n_groups * n_steps * 256;
     tile_rows_kernel<<<(unsigned)qk::ceil_div(pieces, 256), 256, 0, c->stream>>>(
-        rows, tiles, (uint32_t)n_rows, (uint32_t)stride, (uint32_t)n_tiles, (uint32_t)n_steps);
+        rows, tiles, (uint32_t)n_rows, (uint32_t)stride, (uint32_t)n_groups, (uint32_t)n_steps);
     QK_CUDA(cudaGetLastError());
     c->launches += 2;
     QK_CUDA(cudaStreamSynchronize(c->stream));

@@ -110,6 +110,44 @@ class GpuContext:
         return out
 
 
+class _ShapeStruct(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_size_t) for n in ("batch", "n_heads", "n_kv_heads", "seq_q", "seq_kv",
+                                               "head_dim", "val_dim")]
+
+
+def _attention(self, fn_name, shape, query, key, value, causal, block_size=None):
+    q = _f(query, np.float32).ravel()
+    k = _f(key, np.float32).ravel()
+    v = _f(value, np.float32).ravel()
+    st = _ShapeStruct(shape.batch, shape.n_heads, shape.n_kv_heads, shape.seq_q, shape.seq_kv,
+                      shape.head_dim, shape.val_dim)
+    out = np.zeros(shape.batch * shape.n_heads * shape.seq_q * shape.val_dim, dtype=np.float32)
+    fn = getattr(_lib.lib(), fn_name)
+    args = [self._h, ctypes.byref(st), q.ctypes.data, q.size, k.ctypes.data, k.size, v.ctypes.data,
+            v.size, int(bool(causal))]
+    if block_size is not None:
+        args.append(int(block_size))
+    check(fn(*args, out.ctypes.data, out.size))
+    return out
+
+
+def _gpu_attention(self, shape: AttentionShape, query, key, value, causal: bool) -> np.ndarray:
+    """Exact tiled attention, flat float32 in and out (gpu_attention.rs:451-570)."""
+    return _attention(self, "qk_gpu_attention", shape, query, key, value, causal)
+
+
+def _gpu_attention_sage(self, shape: AttentionShape, query, key, value, causal: bool,
+                        block_size: int) -> np.ndarray:
+    """Sage INT8 attention (gpu_attention.rs:589-756)."""
+    if block_size < 0:
+        raise OverflowError("can't convert negative int to unsigned")
+    return _attention(self, "qk_gpu_attention_sage", shape, query, key, value, causal, block_size)
+
+
+GpuContext.attention = _gpu_attention
+GpuContext.attention_sage = _gpu_attention_sage
+
+
 class PackedLayer:
     """Device-resident factorized linear (engine/mod.rs:313-381).
 

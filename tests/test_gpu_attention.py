@@ -1,0 +1,182 @@
+"""GPU parity of the exact and Sage attention faces through the C ABI."""
+
+import numpy as np
+import pytest
+
+from conftest import golden
+from oracle import attention_np as anp
+from quantibbler_b200.gpu import AttentionShape
+
+pytestmark = pytest.mark.gpu
+
+# crates/quantibbler-kernels/tests/gpu_attention_parity.rs:34-37
+EXACT_RTOL, BAND = 1e-5, 1e-1
+# crates/quantibbler-kernels/tests/gpu_attention_sage.rs:39-46
+SAGE_RTOL, COS_MIN, REL_L1_MAX, ENVELOPE_SLACK = 1e-4, 0.999, 0.02, 1e-3
+
+
+def shape_of(q, k, v):
+    b, h, sq, d = q.shape
+    return AttentionShape(b, h, k.shape[1], sq, k.shape[2], d, v.shape[3])
+
+
+def run_exact(ctx, q, k, v, causal):
+    sh = shape_of(q, k, v)
+    out = ctx.attention(sh, q, k, v, causal)
+    return out.reshape(sh.batch, sh.n_heads, sh.seq_q, sh.val_dim)
+
+
+def run_sage(ctx, q, k, v, causal, block):
+    sh = shape_of(q, k, v)
+    out = ctx.attention_sage(sh, q, k, v, causal, block)
+    return out.reshape(sh.batch, sh.n_heads, sh.seq_q, sh.val_dim)
+
+
+def test_exact_reference_battery(gpu_ctx):
+    g = golden("attention")
+    cases = g.cases("tiled")
+    assert len(cases) == 9
+    for key in cases:
+        q, k, v = g[key + "_q"], g[key + "_k"], g[key + "_v"]
+        got = run_exact(gpu_ctx, q, k, v, g.meta[key]["causal"])
+        inf_rel, worst = anp.parity_two_part(got, g[key + "_out"], v.shape[3], EXACT_RTOL, BAND)
+        assert inf_rel <= EXACT_RTOL and worst <= EXACT_RTOL, (key, inf_rel, worst)
+
+
+def test_exact_seeded_shapes(gpu_ctx):
+    g = golden("attention")
+    for key in g.cases("xatt"):
+        q, k, v = g[key + "_q"], g[key + "_k"], g[key + "_v"]
+        got = run_exact(gpu_ctx, q, k, v, g.meta[key]["causal"])
+        inf_rel, worst = anp.parity_two_part(got, g[key + "_out_tiled"], v.shape[3], EXACT_RTOL,
+                                             BAND)
+        assert inf_rel <= EXACT_RTOL and worst <= EXACT_RTOL, (key, inf_rel, worst)
+        assert np.array_equal(got, run_exact(gpu_ctx, q, k, v, g.meta[key]["causal"]))
+
+
+@pytest.mark.parametrize("sq,skv", [(1, 77), (1, 4096), (5, 37), (40, 9)])
+def test_exact_rectangular_causal(gpu_ctx, sq, skv):
+    # decode-style shapes: bottom-right causal alignment (engine/mod.rs:1041-1067)
+    rng = np.random.default_rng(sq * 1000 + skv)
+    q = rng.standard_normal((2, 8, sq, 64)).astype(np.float32)
+    k = rng.standard_normal((2, 2, skv, 64)).astype(np.float32)
+    v = rng.standard_normal((2, 2, skv, 32)).astype(np.float32)
+    got = run_exact(gpu_ctx, q, k, v, True)
+    with np.errstate(invalid="ignore"):
+        want = anp.attention_exact(q, k, v, causal=True)
+    # rows with no admissible key are NaN in both (the reference's 0/0 contract)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    ok = ~np.isnan(want)
+    assert ok.any()
+    assert np.abs(got[ok] - want[ok]).max() <= EXACT_RTOL * np.abs(want[ok]).max()
+
+
+def test_exact_matches_scalar_decode_routine(gpu_ctx):
+    import oracle
+    rng = np.random.default_rng(3)
+    n_heads, n_kv, d, n_pos = 8, 2, 32, 300
+    q = rng.standard_normal(n_heads * d).astype(np.float32)
+    keys = rng.standard_normal((n_pos, n_kv * d)).astype(np.float32)
+    vals = rng.standard_normal((n_pos, n_kv * d)).astype(np.float32)
+    want = oracle.gqa_attention_scalar(q, keys, vals, n_heads, n_kv, d)
+    k4 = np.ascontiguousarray(keys.reshape(n_pos, n_kv, d).transpose(1, 0, 2))[None]
+    v4 = np.ascontiguousarray(vals.reshape(n_pos, n_kv, d).transpose(1, 0, 2))[None]
+    got = run_exact(gpu_ctx, q.reshape(1, n_heads, 1, d), k4, v4, True)
+    assert np.abs(got.ravel() - want).max() <= 1e-5 * np.abs(want).max()
+
+
+def test_exact_config2_shape_row_sample(gpu_ctx):
+    # BASELINE config 2 shape, full size; the oracle checks a sample of query rows
+    rng = np.random.default_rng(2)
+    b, h, kvh, s, d = 1, 32, 8, 8192, 128
+    q = rng.standard_normal((b, h, s, d), dtype=np.float32)
+    k = rng.standard_normal((b, kvh, s, d), dtype=np.float32) \
+        + (2.0 * rng.standard_normal((1, kvh, 1, d))).astype(np.float32)
+    v = rng.standard_normal((b, kvh, s, d), dtype=np.float32)
+    got = run_exact(gpu_ctx, q, k, v, True)
+    rows = np.array([0, 1, 63, 64, 1000, 4095, 4096, 8191])
+    heads = [0, 5, 31]
+    for hh in heads:
+        kv = hh // 4
+        w = anp.attention_exact(q[:, hh:hh + 1], k[:, kv:kv + 1], v[:, kv:kv + 1], causal=True,
+                                rows=rows)
+        gsub = got[:, hh:hh + 1][:, :, rows]
+        assert np.abs(gsub - w).max() <= EXACT_RTOL * np.abs(w).max(), hh
+    assert np.isfinite(got).all()
+
+
+def test_validation_texts(gpu_ctx):
+    z = np.zeros(64, np.float32)
+    sh = AttentionShape(1, 3, 2, 4, 4, 4, 4)
+    with pytest.raises(ValueError, match="n_kv_heads must divide n_heads: n_heads=3, n_kv_heads=2"):
+        gpu_ctx.attention(sh, z, z, z, False)
+    sh = AttentionShape(1, 2, 1, 8, 8, 4, 4)
+    with pytest.raises(ValueError, match=r"key must hold 32 values for AttentionShape \{ batch: 1, "
+                                         r"n_heads: 2, n_kv_heads: 1, seq_q: 8, seq_kv: 8, "
+                                         r"head_dim: 4, val_dim: 4 \}, got 64"):
+        gpu_ctx.attention(sh, z, z, z[:32], False)
+    with pytest.raises(ValueError, match="attention requires non-empty batch and head dimensions"):
+        gpu_ctx.attention(AttentionShape(0, 2, 1, 8, 8, 4, 4), z, z, z, False)
+    with pytest.raises(ValueError, match="sage attention is self-attention over one cache: "
+                                         "seq_q=1, seq_kv=8"):
+        gpu_ctx.attention_sage(AttentionShape(1, 2, 1, 1, 8, 4, 4), z[:8], z[:32], z[:32], False, 4)
+    with pytest.raises(ValueError, match="sage attention requires a positive block_size"):
+        gpu_ctx.attention_sage(sh, z, z[:32], z[:32], False, 0)
+
+
+def test_sage_reference_battery(gpu_ctx):
+    g = golden("attention")
+    cases = g.cases("sage")
+    assert len(cases) == 10
+    for key in cases:
+        m = g.meta[key]
+        q, k, v = g[key + "_q"], g[key + "_k"], g[key + "_v"]
+        got = run_sage(gpu_ctx, q, k, v, m["causal"], m["block_size"])
+        inf_rel, worst = anp.parity_two_part(got, g[key + "_out"], v.shape[3], SAGE_RTOL, BAND)
+        assert inf_rel <= SAGE_RTOL and worst <= SAGE_RTOL, (key, inf_rel, worst)
+        cos, rel_l1, _ = anp.quality_metrics(got, g[key + "_exact"])
+        assert cos >= COS_MIN and rel_l1 <= REL_L1_MAX, (key, cos, rel_l1)
+        ref = m["reference_metrics"]
+        assert cos >= ref["cosine"] - ENVELOPE_SLACK
+        assert rel_l1 <= ref["relative_l1"] + ENVELOPE_SLACK
+
+
+def test_sage_seeded_shapes_against_float32_restatement(gpu_ctx):
+    g = golden("attention")
+    for key in g.cases("xatt"):
+        m = g.meta[key]
+        q, k, v = g[key + "_q"], g[key + "_k"], g[key + "_v"]
+        got = run_sage(gpu_ctx, q, k, v, m["causal"], m["block_size"])
+        w32 = anp.attention_sage(q, k, v, causal=m["causal"], block_size=m["block_size"],
+                                 ft=np.float32)
+        w64 = g[key + "_out_sage"]
+        # against the float32 restatement (same arithmetic): only P codes whose exp lands
+        # on a rounding tie may differ
+        assert np.median(np.abs(got - w32)) <= 1e-6, key
+        assert np.abs(got - w32).max() <= 2e-3 * np.abs(w32).max(), key
+        # against the float64 reference: a flipped K/V/P code moves an output by ~1/127 of
+        # one term, so compare in the aggregate
+        cos, rel_l1, _ = anp.quality_metrics(got, w64)
+        assert cos >= 0.99999 and rel_l1 <= 1e-3, (key, cos, rel_l1)
+        assert np.array_equal(got, run_sage(gpu_ctx, q, k, v, m["causal"], m["block_size"]))
+
+
+def test_sage_config2_shape_row_sample(gpu_ctx):
+    rng = np.random.default_rng(4)
+    b, h, kvh, s, d = 1, 8, 2, 2048, 128
+    q = rng.standard_normal((b, h, s, d), dtype=np.float32)
+    k = rng.standard_normal((b, kvh, s, d), dtype=np.float32) \
+        + (2.0 * rng.standard_normal((1, kvh, 1, d))).astype(np.float32)
+    v = rng.standard_normal((b, kvh, s, d), dtype=np.float32)
+    got = run_sage(gpu_ctx, q, k, v, True, 64)
+    rows = np.array([0, 63, 64, 777, 2047])
+    for hh in (0, 7):
+        kv = hh // 4
+        w = anp.attention_sage(q[:, hh:hh + 1], k[:, kv:kv + 1], v[:, kv:kv + 1], causal=True,
+                               block_size=64, rows=rows, ft=np.float32)
+        gsub = got[:, hh:hh + 1][:, :, rows]
+        assert np.abs(gsub - w).max() <= 2e-3 * np.abs(w).max(), hh
+        exact = anp.attention_exact(q[:, hh:hh + 1], k[:, kv:kv + 1], v[:, kv:kv + 1],
+                                    causal=True, rows=rows)
+        cos, rel_l1, _ = anp.quality_metrics(gsub, exact)
+        assert cos >= COS_MIN and rel_l1 <= REL_L1_MAX

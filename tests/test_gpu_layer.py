@@ -63,7 +63,9 @@ def check_layer(ctx, L, serving):
         # the bit-sliced kernel sums exactly, so it reproduces the reference's float64
         # stages to the last float32 bit except where u sits on a rounding boundary
         ulp = np.spacing(np.abs(want).astype(np.float32)).astype(np.float64)
-        assert (err <= 2 * ulp + 1e-30).all()
+        # (where rows cancel, the reference's own float64 loop is only good to 1e-12 of the
+        # term scale: fast.rs:10-18)
+        assert (err <= 2 * ulp + 1e-12 * term_scale).all()
         assert np.mean(y == want) >= 0.9
     layer.close()
     return y, want
