@@ -190,6 +190,78 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// One element of a stage's input vector as float64 (zero beyond n_bits).
+//   kInDouble: the input is the float64 intermediate of the previous stage.
+template <bool kInDouble, bool kRoundBf16>
+__device__ __forceinline__ double load_input(const StageParams &p, uint32_t k, uint32_t n_bits) {
+    if (k >= n_bits) return 0.0;
+    if (kInDouble) return static_cast<const double *>(p.in)[k];  // rounded by its producer
+    float v = static_cast<const float *>(p.in)[k];
+    if (p.in_scale) v = p.in_scale[k] * v;  // float32 product, as the reference forms z
+    if (kRoundBf16) v = round_bf16(v);
+    return (double)v;
+}
+
+// Fixed-point grid of a vector whose largest magnitude is m: |v| * 2^shift < 2^(kQBits+1).
+struct FixedPoint {
+    int shift;
+    bool direct;   // 2^shift is a normal double
+    double pow2;
+    __device__ __forceinline__ long long quant(double v) const {
+        return __double2ll_rn(direct ? v * pow2 : ldexp(v, shift));
+    }
+};
+__device__ __forceinline__ FixedPoint fixed_point_of(double m) {
+    int e = 0;
+    if (m > 0.0) {
+        int biased = (__double2hiint(m) >> 20) & 0x7ff;  // m = f * 2^e, f in [0.5, 1)
+        if (biased) e = biased - 1022; else frexp(m, &e);
+    }
+    FixedPoint fp;
+    fp.shift = kQBits + 1 - e;
+    fp.direct = fp.shift > -1000 && fp.shift < 1000;
+    fp.pow2 = fp.direct ? __hiloint2double((1023 + fp.shift) << 20, 0) : 0.0;
+    return fp;
+}
+
+// Record rec = (qw*4 + ip)*4 + t of k-step ks: the eight uint2 B-fragment pairs (one per
+// digit column) built from the eight vector entries k = 512*ks + 128*t + 32*qw + 8*j + i,
+// i in {2*ip, 2*ip+1}, j in 0..3.  q8[which*4 + j] holds their fixed-point values.
+__device__ __forceinline__ void build_record(const long long (&q8)[8], uint32_t ip, uint4 *dst) {
+    // Balanced base-256 digits without a carry loop: adding 128 to every byte position and
+    // flipping each byte's top bit turns the two's-complement bytes into digits in
+    // [-128, 127] with sum_n d_n 256^n equal to the value.
+    const unsigned long long bias = 0x8080808080808080ull;
+    uint32_t w[2][4][2];  // [which][j][low digits 0-3 / high digits 4-7]
+#pragma unroll
+    for (int which = 0; which < 2; ++which)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            unsigned long long u =
+                (((unsigned long long)q8[which * 4 + j] << (7 - (2 * ip + which))) + bias) ^ bias;
+            w[which][j][0] = (uint32_t)u;
+            w[which][j][1] = (uint32_t)(u >> 32);
+        }
+    // 4x4 byte transposes: word n of the result holds digit n of the four entries j = 0..3
+    uint32_t out[2][8];
+#pragma unroll
+    for (int which = 0; which < 2; ++which)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const uint32_t a = w[which][0][half], b2 = w[which][1][half];
+            const uint32_t c = w[which][2][half], d = w[which][3][half];
+            const uint32_t t0 = __byte_perm(a, b2, 0x5140), t1 = __byte_perm(c, d, 0x5140);
+            const uint32_t t2 = __byte_perm(a, b2, 0x7362), t3 = __byte_perm(c, d, 0x7362);
+            out[which][half * 4 + 0] = __byte_perm(t0, t1, 0x5410);
+            out[which][half * 4 + 1] = __byte_perm(t0, t1, 0x7632);
+            out[which][half * 4 + 2] = __byte_perm(t2, t3, 0x5410);
+            out[which][half * 4 + 3] = __byte_perm(t2, t3, 0x7632);
+        }
+#pragma unroll
+    for (int n = 0; n < 8; n += 2)
+        dst[n / 2] = make_uint4(out[0][n], out[1][n], out[0][n + 1], out[1][n + 1]);
+}
+
 // Converts one instance's input vector to its digit table.
 //   kInDouble: the input is the float64 intermediate of the previous stage.
 // Table layout (uint2 units): record ((ks*4 + q)*4 + ip)*4 + t holds, for digit column n,
@@ -210,19 +282,10 @@ digit_table_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32
     __shared__ int sh_bad;
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
 
-    auto load = [&](uint32_t k) -> double {
-        if (k >= n_bits) return 0.0;
-        if (kInDouble) return static_cast<const double *>(p.in)[k];  // rounded by its producer
-        float v = static_cast<const float *>(p.in)[k];
-        if (p.in_scale) v = p.in_scale[k] * v;  // float32 product, as the reference forms z
-        if (kRoundBf16) v = round_bf16(v);
-        return (double)v;
-    };
-
     double mx = 0.0;
     int bad = 0;
     for (uint32_t k = tid; k < n_bits; k += 256) {
-        double a = fabs(load(k));
+        double a = fabs(load_input<kInDouble, kRoundBf16>(p, k, n_bits));
         if (!(a <= 1.7e308)) bad = 1;  // NaN or infinity
         mx = fmax(mx, a);
     }
@@ -239,24 +302,13 @@ digit_table_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32
 #pragma unroll
     for (int w = 1; w < 8; ++w) m = fmax(m, red_max[w]);
     const bool nonfinite = sh_bad != 0;
-    // m = f * 2^e with f in [0.5, 1): |v| * 2^shift < 2^(kQBits+1)
-    int e = 0;
-    if (m > 0.0 && !nonfinite) e = (int)((__double2hiint(m) >> 20) & 0x7ff) - 1022;
-    if (m > 0.0 && !nonfinite && ((__double2hiint(m) >> 20) & 0x7ff) == 0) frexp(m, &e);
-    const int shift = kQBits + 1 - e;
-    // 2^shift as a double; shifts outside the normal range only arise for inputs whose
-    // magnitude is itself at the edge of float64, where ldexp takes over
-    const bool direct = shift > -1000 && shift < 1000;
-    const double pow2 = direct ? __hiloint2double((1023 + shift) << 20, 0) : 0.0;
-    auto quant = [&](uint32_t k) -> long long {
-        if (nonfinite) return 0;
-        double v = load(k);
-        return __double2ll_rn(direct ? v * pow2 : ldexp(v, shift));
-    };
+    const FixedPoint fp = fixed_point_of(nonfinite ? 0.0 : m);
 
     if (blockIdx.x == 0) {
         long long total = 0;
-        for (uint32_t k = tid; k < n_bits; k += 256) total += quant(k);
+        if (!nonfinite)
+            for (uint32_t k = tid; k < n_bits; k += 256)
+                total += fp.quant(load_input<kInDouble, kRoundBf16>(p, k, n_bits));
         for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
         if (lane == 0) red_sum[warp] = total;
         __syncthreads();
@@ -264,7 +316,7 @@ digit_table_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32
             long long sum = 0;
             for (int w = 0; w < 8; ++w) sum += red_sum[w];
             p.meta->total = sum;
-            p.meta->shift = shift;
+            p.meta->shift = fp.shift;
             p.meta->nonfinite = nonfinite;
         }
     }
@@ -273,63 +325,48 @@ digit_table_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32
     if (ks >= n_steps) return;
     const uint32_t rec = tid % 64;  // (qw*4 + ip)*4 + t
     const uint32_t t = rec % 4, ip = (rec / 4) % 4, qw = rec / 16;
-    uint32_t lo[8], hi[8];
+    long long q8[8];
 #pragma unroll
-    for (int n = 0; n < 8; ++n) lo[n] = hi[n] = 0;
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t i = 2 * ip + which;
-            long long v = quant(ks * kStepBits + 128 * t + 32 * qw + 8 * j + i) << (7 - i);
-#pragma unroll
-            for (int n = 0; n < 8; ++n) {
-                int d = (int)(v & 0xff);
-                if (d >= 128) d -= 256;
-                v = (v - d) >> 8;
-                if (which == 0) lo[n] |= (uint32_t)(d & 0xff) << (8 * j);
-                else hi[n] |= (uint32_t)(d & 0xff) << (8 * j);
-            }
-        }
+    for (int e = 0; e < 8; ++e) {
+        uint32_t k = ks * kStepBits + 128 * t + 32 * qw + 8 * (e % 4) + 2 * ip + e / 4;
+        q8[e] = nonfinite ? 0 : fp.quant(load_input<kInDouble, kRoundBf16>(p, k, n_bits));
     }
-    uint4 *dst = reinterpret_cast<uint4 *>(p.digits + ((size_t)ks * 64 + rec) * 8);
-#pragma unroll
-    for (int n = 0; n < 8; n += 2) dst[n / 2] = make_uint4(lo[n], hi[n], lo[n + 1], hi[n + 1]);
+    build_record(q8, ip, reinterpret_cast<uint4 *>(p.digits + ((size_t)ks * 64 + rec) * 8));
 }
 
 // out[row] = epilogue((2 * sum_{bit=1} q_k - sum q_k) * 2^-shift).
 //   kFinal = false: writes the float64 intermediate t;  true: y = float(u)*s1 + bias.
-//   kSmemDigits: the instance's digit table is copied to shared memory first (it is read
-//   sixteen times per chunk by every warp); otherwise it is read through L1.
+//   kSmemDigits: the block builds the instance's digit table in shared memory itself,
+//   straight from the input vector (no separate kernel, no table in global memory);
+//   otherwise the table made by digit_table_kernel is read through L1 (only for inputs
+//   too wide for shared memory).
 // grid.y is the instance; the instance's row groups are dealt to the grid.x * (warps per
 // block) warps in contiguous runs of `groups_per_warp`, so each warp reads one contiguous
 // range of chunks.  Every lane copies exactly the eight 16-byte pieces it will consume
 // itself through a private cp.async ring, so the ring needs no barrier of any kind.
 // Measured on B200: with the table in shared memory, 16 warps per SM and a two-deep ring
 // the loop runs at 92% of what the INT8 tensor pipe plus the mask ALU work allow.
-template <bool kRoundBf16, bool kFinal, bool kSmemDigits>
-__global__ void __launch_bounds__(512, 1)
-gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint32_t n_groups,
-                     uint32_t n_steps, uint32_t groups_per_warp) {
-    extern __shared__ __align__(16) uint8_t smem_all[];
-    const StageParams p = many[blockIdx.y];
+//   kInSmem / kOutSmem: the input vector is read from / the result written to shared memory
+//   as float64 (the fused kernel keeps t on the SM between the two stages).
+// smem_all: [digit table when kSmemDigits][warps x kStages x 4 KB ring].
+template <bool kRoundBf16, bool kFinal, bool kSmemDigits, bool kInSmem, bool kOutSmem>
+__device__ __forceinline__ void
+bitslice_stage(const StageParams &p, uint8_t *smem_all, const double *in_smem, double *out_smem,
+               uint32_t n_rows, uint32_t n_bits, uint32_t n_groups, uint32_t n_steps,
+               uint32_t block_in_instance, uint32_t groups_per_warp) {
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t warps_per_block = blockDim.x / 32;
     const uint32_t g = lane / 4, t = lane % 4;
+    auto input = [&](uint32_t k) -> double {
+        if (kInSmem) return k < n_bits ? in_smem[k] : 0.0;
+        return load_input<kFinal, kRoundBf16>(p, k, n_bits);
+    };
     const uint32_t group_begin =
-        min(n_groups, (blockIdx.x * warps_per_block + warp) * groups_per_warp);
+        min(n_groups, (block_in_instance * warps_per_block + warp) * groups_per_warp);
     const uint32_t group_end = min(n_groups, group_begin + groups_per_warp);
     const uint32_t c_begin = group_begin * n_steps, c_end = group_end * n_steps;
 
     const size_t table_bytes = kSmemDigits ? (size_t)n_steps * 4096 : 0;
-    if (kSmemDigits) {
-        // group 0 of every thread: its share of the table
-        const uint4 *tsrc = reinterpret_cast<const uint4 *>(p.digits);
-        uint4 *tdst = reinterpret_cast<uint4 *>(smem_all);
-        for (uint32_t i = threadIdx.x; i < n_steps * 256; i += blockDim.x)
-            cp_async16(tdst + i, tsrc + i);
-        cp_async_commit();
-    }
     uint4 *ring =
         reinterpret_cast<uint4 *>(smem_all + table_bytes + (size_t)warp * kStages * kChunkBytes) +
         lane;
@@ -345,9 +382,56 @@ gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint
     };
 #pragma unroll
     for (int s = 0; s < kStages - 1; ++s) issue(c_begin + s);
+    // ---- the digit table of this instance (the weight ring is already filling)
+    __shared__ double red_max[16];
+    __shared__ long long red_sum[16];
+    __shared__ int sh_bad;
+    StageMeta meta;
     if (kSmemDigits) {
-        cp_async_wait<kStages - 1>();  // older groups finish first: the table has landed
-        __syncthreads();               // ... for every thread's share
+        const uint32_t n_records = n_steps * 64;
+        double mx = 0.0;
+        int bad = 0;
+        for (uint32_t k = threadIdx.x; k < n_bits; k += blockDim.x) {
+            double a = fabs(input(k));
+            if (!(a <= 1.7e308)) bad = 1;  // NaN or infinity
+            mx = fmax(mx, a);
+        }
+        for (int off = 16; off > 0; off >>= 1) {
+            mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+            bad |= __shfl_xor_sync(0xffffffffu, bad, off);
+        }
+        if (lane == 0) red_max[warp] = mx;
+        if (threadIdx.x == 0) sh_bad = 0;
+        __syncthreads();
+        if (lane == 0 && bad) sh_bad = 1;
+        __syncthreads();
+        double m = red_max[0];
+        for (uint32_t w = 1; w < warps_per_block; ++w) m = fmax(m, red_max[w]);
+        meta.nonfinite = sh_bad;
+        const FixedPoint fp = fixed_point_of(meta.nonfinite ? 0.0 : m);
+        meta.shift = fp.shift;
+        long long total = 0;
+        for (uint32_t r = threadIdx.x; r < n_records; r += blockDim.x) {
+            const uint32_t ks = r / 64, rec = r % 64;
+            const uint32_t tt = rec % 4, ip = (rec / 4) % 4, qw = rec / 16;
+            long long q8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                uint32_t k = ks * kStepBits + 128 * tt + 32 * qw + 8 * (e % 4) + 2 * ip + e / 4;
+                q8[e] = meta.nonfinite ? 0
+                                       : fp.quant(input(k));
+                total += q8[e];
+            }
+            build_record(q8, ip, reinterpret_cast<uint4 *>(smem_all) + (size_t)r * 4);
+        }
+        for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+        if (lane == 0) red_sum[warp] = total;
+        __syncthreads();  // the table and the partial totals are complete
+        total = 0;
+        for (uint32_t w = 0; w < warps_per_block; ++w) total += red_sum[w];
+        meta.total = total;
+    } else {
+        meta = *p.meta;
     }
 
     int acc[kTilesPerWarp][4];
@@ -357,10 +441,13 @@ gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint
         for (int e = 0; e < 4; ++e) acc[m][e] = 0;
     const uint2 *dig =
         (kSmemDigits ? reinterpret_cast<const uint2 *>(smem_all) : p.digits) + t * 8 + g;
-    const StageMeta meta = *p.meta;
     const long long th = meta.total >> 26;
     const long long tl = (meta.total & ((1ll << 26) - 1)) << 6;
     const int sh0 = 16 * (t & 1);
+    // 2^(-shift-6) as a double (one multiply per row instead of a call to ldexp)
+    const int oexp = -meta.shift - 6;
+    const bool odirect = oexp > -1000 && oexp < 1000;
+    const double oscale = odirect ? __hiloint2double((1023 + oexp) << 20, 0) : 0.0;
 
     uint32_t ks = 0, group = group_begin;
     for (uint32_t c = c_begin; c < c_end; ++c) {
@@ -410,11 +497,13 @@ gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint
             const uint32_t row = group * kGroupRows + m * kTileRows + g + 8 * t;
             if (t < 2 && row < n_rows) {
                 const long long lo = t == 0 ? pg : ph, hi = t == 0 ? og : oh;
-                double val = ldexp((double)(hi - th) * 4294967296.0 + (double)(lo - tl),
-                                   -meta.shift - 6);
+                double val = (double)(hi - th) * 4294967296.0 + (double)(lo - tl);
+                val = odirect ? val * oscale : ldexp(val, oexp);
                 if (meta.nonfinite) val = nan("");
                 if (kRoundBf16) val = (double)round_bf16((float)val);
-                if (kFinal) {
+                if (kOutSmem) {
+                    out_smem[row] = val;
+                } else if (kFinal) {
                     float y = (float)val;
                     if (p.out_scale) y = y * p.out_scale[row];
                     if (p.out_bias) y = y + p.out_bias[row];
@@ -427,6 +516,42 @@ gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint
         ++group;
     }
     cp_async_wait<0>();
+}
+
+// One stage of the factorized linear.  grid.y is the instance, grid.x the blocks that
+// share its row groups.
+template <bool kRoundBf16, bool kFinal, bool kSmemDigits>
+__global__ void __launch_bounds__(512, 1)
+gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint32_t n_bits,
+                     uint32_t n_groups, uint32_t n_steps, uint32_t groups_per_warp) {
+    extern __shared__ __align__(16) uint8_t smem_dyn[];
+    const StageParams p = many[blockIdx.y];
+    bitslice_stage<kRoundBf16, kFinal, kSmemDigits, false, false>(
+        p, smem_dyn, nullptr, nullptr, n_rows, n_bits, n_groups, n_steps, blockIdx.x,
+        groups_per_warp);
+}
+
+// Both stages of one layer instance in one block: t = Vb^T z stays in shared memory as
+// float64, the second digit table is built from it there, and the second factor's first
+// chunks are already in flight while that happens.  Used whenever one block per instance
+// is the right grain (many independent instances per launch).
+// smem: [t: r doubles][table (larger of the two stages)][ring].
+template <bool kRoundBf16>
+__global__ void __launch_bounds__(512, 1)
+layer_bitslice_fused_kernel(const StageParams *__restrict__ stage1,
+                            const StageParams *__restrict__ stage2, uint32_t r, uint32_t din,
+                            uint32_t dout, uint32_t t_bytes, uint32_t gpw1, uint32_t gpw2) {
+    extern __shared__ __align__(16) uint8_t smem_dyn[];
+    double *t_smem = reinterpret_cast<double *>(smem_dyn);
+    uint8_t *work = smem_dyn + t_bytes;
+    const StageParams p1 = stage1[blockIdx.x], p2 = stage2[blockIdx.x];
+    bitslice_stage<kRoundBf16, false, true, false, true>(
+        p1, work, nullptr, t_smem, r, din, (r + kGroupRows - 1) / kGroupRows,
+        (din + kStepBits - 1) / kStepBits, 0, gpw1);
+    __syncthreads();  // every row of t is in shared memory; the ring and table are free again
+    bitslice_stage<kRoundBf16, true, true, true, false>(
+        p2, work, t_smem, nullptr, dout, r, (dout + kGroupRows - 1) / kGroupRows,
+        (r + kStepBits - 1) / kStepBits, 0, gpw2);
 }
 
 // ------------------------------------------------------------------ layer construction
@@ -498,48 +623,84 @@ qk_status launch_signselect(qk_ctx *c, const StageParams *many, size_t n_inst, c
     return QK_OK;
 }
 
-template <bool kFinal>
-qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, const StageShape &s,
-                          bool bf16) {
-    // the digit table of every instance, then the product
-    auto table = kFinal ? (bf16 ? digit_table_kernel<true, true> : digit_table_kernel<true, false>)
-                        : (bf16 ? digit_table_kernel<false, true> : digit_table_kernel<false, false>);
-    dim3 tgrid((unsigned)qk::ceil_div(s.n_steps, 4), (unsigned)n_inst);
-    table<<<tgrid, 256, 0, c->stream>>>(many, (uint32_t)s.n_bits, (uint32_t)s.n_steps);
-    QK_CUDA(cudaGetLastError());
-    c->launches++;
+// How one stage is cut into blocks and warps.
+struct StagePlan {
+    bool smem_digits;
+    size_t warps_per_block, gpw, blocks, smem;
+};
 
+constexpr size_t kSmemBudget = 224 * 1024;
+constexpr size_t kRingPerWarp = (size_t)kStages * kChunkBytes;
+
+StagePlan plan_stage(const qk_ctx *c, const StageShape &s, size_t n_inst) {
     // Shared memory: the digit table (4 KB per k-step) plus a ring of kStages chunks per
     // warp.  Prefer 16 warps per block (one block per SM); use fewer warps when the table
     // is large, and read the table through L1 when it does not fit at all.
-    const size_t budget = 224 * 1024, ring_per_warp = (size_t)kStages * kChunkBytes;
+    StagePlan pl;
     const size_t table_bytes = s.n_steps * 4096;
-    bool smem_digits = table_bytes + 4 * ring_per_warp <= budget;
-    size_t warps_per_block = 16;
-    if (smem_digits)
-        while (table_bytes + warps_per_block * ring_per_warp > budget) warps_per_block -= 4;
+    pl.smem_digits = table_bytes + 4 * kRingPerWarp <= kSmemBudget;
+    pl.warps_per_block = 16;
+    if (pl.smem_digits)
+        while (table_bytes + pl.warps_per_block * kRingPerWarp > kSmemBudget)
+            pl.warps_per_block -= 4;
     // Deal the row groups to warps: about eight chunks per warp keeps the ring in steady
     // state; with few instances, spread each one over more and smaller blocks instead.
-    size_t gpw = s.n_steps >= 8 ? 1 : 8 / s.n_steps;
-    if (gpw > s.n_groups) gpw = s.n_groups;
-    size_t blocks = qk::ceil_div(qk::ceil_div(s.n_groups, gpw), warps_per_block);
-    while (n_inst * blocks < (size_t)c->sm_count && (gpw > 1 || warps_per_block > 4)) {
-        if (gpw > 1) gpw = qk::ceil_div(gpw, 2);
-        else warps_per_block /= 2;
-        blocks = qk::ceil_div(qk::ceil_div(s.n_groups, gpw), warps_per_block);
+    pl.gpw = s.n_steps >= 8 ? 1 : 8 / s.n_steps;
+    if (pl.gpw > s.n_groups) pl.gpw = s.n_groups;
+    pl.blocks = qk::ceil_div(qk::ceil_div(s.n_groups, pl.gpw), pl.warps_per_block);
+    while (n_inst * pl.blocks < (size_t)c->sm_count && (pl.gpw > 1 || pl.warps_per_block > 4)) {
+        if (pl.gpw > 1) pl.gpw = qk::ceil_div(pl.gpw, 2);
+        else pl.warps_per_block /= 2;
+        pl.blocks = qk::ceil_div(qk::ceil_div(s.n_groups, pl.gpw), pl.warps_per_block);
     }
-    const size_t smem = (smem_digits ? table_bytes : 0) + warps_per_block * ring_per_warp;
-    dim3 grid((unsigned)blocks, (unsigned)n_inst);
-    auto gemv = smem_digits ? (bf16 ? gemv_bitslice_kernel<true, kFinal, true>
-                                    : gemv_bitslice_kernel<false, kFinal, true>)
-                            : (bf16 ? gemv_bitslice_kernel<true, kFinal, false>
-                                    : gemv_bitslice_kernel<false, kFinal, false>);
-    QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget));
-    gemv<<<grid, (unsigned)warps_per_block * 32, smem, c->stream>>>(
-        many, (uint32_t)s.n_rows, (uint32_t)s.n_groups, (uint32_t)s.n_steps, (uint32_t)gpw);
+    pl.smem = (pl.smem_digits ? table_bytes : 0) + pl.warps_per_block * kRingPerWarp;
+    return pl;
+}
+
+template <bool kFinal>
+qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, const StageShape &s,
+                          bool bf16) {
+    const StagePlan pl = plan_stage(c, s, n_inst);
+    if (!pl.smem_digits) {
+        // too wide for shared memory: the table is made in global memory first
+        auto table = kFinal ? (bf16 ? digit_table_kernel<true, true> : digit_table_kernel<true, false>)
+                            : (bf16 ? digit_table_kernel<false, true>
+                                    : digit_table_kernel<false, false>);
+        dim3 tgrid((unsigned)qk::ceil_div(s.n_steps, 4), (unsigned)n_inst);
+        table<<<tgrid, 256, 0, c->stream>>>(many, (uint32_t)s.n_bits, (uint32_t)s.n_steps);
+        QK_CUDA(cudaGetLastError());
+        c->launches++;
+    }
+    dim3 grid((unsigned)pl.blocks, (unsigned)n_inst);
+    auto gemv = pl.smem_digits ? (bf16 ? gemv_bitslice_kernel<true, kFinal, true>
+                                       : gemv_bitslice_kernel<false, kFinal, true>)
+                               : (bf16 ? gemv_bitslice_kernel<true, kFinal, false>
+                                       : gemv_bitslice_kernel<false, kFinal, false>);
+    QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kSmemBudget));
+    gemv<<<grid, (unsigned)pl.warps_per_block * 32, pl.smem, c->stream>>>(
+        many, (uint32_t)s.n_rows, (uint32_t)s.n_bits, (uint32_t)s.n_groups, (uint32_t)s.n_steps,
+        (uint32_t)pl.gpw);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     return QK_OK;
+}
+
+// The fused form applies when there are enough instances to give every SM a block of its
+// own and both digit tables, t and the ring fit in shared memory together.
+bool fused_plan(const qk_ctx *c, const StageShape &s1, const StageShape &s2, size_t n_inst,
+                size_t *warps, size_t *t_bytes, size_t *smem) {
+    if (n_inst < (size_t)c->sm_count) return false;
+    const size_t table = (s1.n_steps > s2.n_steps ? s1.n_steps : s2.n_steps) * 4096;
+    *t_bytes = qk::ceil_div(s1.n_rows * sizeof(double), 128) * 128;
+    for (size_t w = 16; w >= 8; w -= 4) {
+        if (*t_bytes + table + w * kRingPerWarp <= kSmemBudget) {
+            *warps = w;
+            *smem = *t_bytes + table + w * kRingPerWarp;
+            return true;
+        }
+    }
+    return false;
 }
 
 // Scratch one instance needs besides its inputs and outputs.
@@ -611,6 +772,19 @@ qk_status launch_both(qk_ctx *c, const qk_layer *l0, const StageParams *d, size_
                             l0->din > l0->r ? l0->din : l0->r);
         if ((st = launch_signselect(c, d, n_inst, s1, bf16)) != QK_OK) return st;
         return launch_signselect(c, d + n_inst, n_inst, s2, bf16);
+    }
+    size_t warps, t_bytes, smem;
+    if (fused_plan(c, s1, s2, n_inst, &warps, &t_bytes, &smem)) {
+        auto fused = bf16 ? layer_bitslice_fused_kernel<true> : layer_bitslice_fused_kernel<false>;
+        QK_CUDA(cudaFuncSetAttribute(fused, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)kSmemBudget));
+        fused<<<(unsigned)n_inst, (unsigned)warps * 32, smem, c->stream>>>(
+            d, d + n_inst, (uint32_t)l0->r, (uint32_t)l0->din, (uint32_t)l0->dout,
+            (uint32_t)t_bytes, (uint32_t)qk::ceil_div(s1.n_groups, warps),
+            (uint32_t)qk::ceil_div(s2.n_groups, warps));
+        QK_CUDA(cudaGetLastError());
+        c->launches++;
+        return QK_OK;
     }
     if ((st = launch_bitslice<false>(c, d, n_inst, s1, bf16)) != QK_OK) return st;
     return launch_bitslice<true>(c, d + n_inst, n_inst, s2, bf16);

@@ -147,6 +147,44 @@ def test_group_apply_matches_single(gpu_ctx):
     assert np.array_equal(y.cpu().numpy(), np.stack(want))
 
 
+@pytest.mark.parametrize("serving", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape", [(96, 160, 72), (130, 1100, 515)])
+def test_fused_layer_kernel_matches_two_stage_path(gpu_ctx, shape, serving):
+    # with at least one instance per SM the two stages run fused in one block per layer;
+    # both paths accumulate in integers, so they must agree bit for bit
+    import torch
+    from quantibbler_b200.gpu import LayerGroup
+    dout, din, r = shape
+    n = 160
+    layers, xs, want = [], [], []
+    for i in range(n):
+        L = make_layer(dout, din, r, seed=500 + i % 7, with_bias=(i % 2 == 0))
+        layer = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], dout, din, r, L["s1"],
+                            L["s2"], L["bias"], serving=serving)
+        layers.append(layer)
+        x = (L["x"] * (1 + i)).astype(np.float32)
+        xs.append(x)
+        if i < 7:
+            want.append(layer.apply(x))
+            ref = oracle.layer_apply(L["ub_rows"], L["vb_t_rows"], dout, din, r, L["s1"],
+                                     L["s2"], L["bias"], x, serving=serving)
+            tol = 2e-5 if serving == "float32" else 2e-2
+            assert np.abs(want[-1] - ref).max() <= tol * np.abs(ref).max()
+    x = torch.from_numpy(np.stack(xs)).cuda()
+    y = torch.zeros(n, dout, device="cuda")
+    torch.cuda.synchronize()
+    group = LayerGroup(gpu_ctx, layers, x.data_ptr(), y.data_ptr())
+    group.apply()
+    gpu_ctx.synchronize()
+    got = y.cpu().numpy()
+    for i in range(7):
+        assert np.array_equal(got[i], want[i]), i
+    first = got.copy()
+    group.apply()
+    gpu_ctx.synchronize()
+    assert np.array_equal(y.cpu().numpy(), first)
+
+
 def test_multi_token_apply(gpu_ctx):
     import torch
     L = make_layer(96, 160, 72, seed=11, with_bias=True)
