@@ -171,12 +171,17 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=296, help="distinct layers per step (2 x 148)")
+    ap.add_argument("--layers", type=int, default=592, help="distinct layers per step (4 x 148)")
     ap.add_argument("--kernel", type=int, default=-1, help="GEMV kernel override (debug)")
+    ap.add_argument("--shape", default="", help="dout,din,rank override (debug; not the metric)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--e2e-applies", type=int, default=296)
     args = ap.parse_args()
 
+    if args.shape:
+        global DOUT, DIN, RANK, BYTES_PER_APPLY
+        DOUT, DIN, RANK = (int(v) for v in args.shape.split(","))
+        BYTES_PER_APPLY = (DOUT * RANK + DIN * RANK) // 8 + 4 * (DOUT + DIN) + 4 * DIN + 4 * DOUT
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
