@@ -182,10 +182,60 @@ qk_status qk_layers_apply_group(qk_ctx *ctx, const qk_layer *const *layers, size
  * kernel launches with no host-side staging, so steps can be queued back to back. */
 qk_status qk_group_create(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers,
                           const float *x_dev, float *y_dev, qk_group **out);
+/* The general form: instance k applies layers[k] to x_ptrs[k] (din floats) and writes
+ * y_ptrs[k] (dout floats); all layers share one shape.  This is how a batch of tokens
+ * shares q/k/v (same input pointers) or gate/up launches. */
+qk_status qk_plan_create(qk_ctx *ctx, const qk_layer *const *layers, const float *const *x_ptrs,
+                         float *const *y_ptrs, size_t n_inst, qk_group **out);
 qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group);
 void qk_group_free(qk_group *group);
+/* ---- decoder-side kernels on device buffers -----------------------------------
+ * What one transformer block needs around its linears.  All are launch-only on the
+ * context's stream (no allocation, no synchronisation), so a whole decode step can be
+ * captured in a CUDA graph.  Activations are float32 row-major [tokens, width]. */
+
+/* engine/mod.rs:1154-1160 (rms_norm_into) + :837-851 (norm_apply).  h = x + residual
+ * (residual may be NULL); if x_out is not NULL it receives h; y = h*rsqrt(mean(h^2)+eps)*w.
+ * bfloat16 serving rounds h and y to bfloat16 as the reference does. */
+qk_status qk_rmsnorm(qk_ctx *ctx, const float *x, const float *residual, const float *weight,
+                     size_t n_tokens, size_t d, float eps, int32_t serving_dtype, float *x_out,
+                     float *y);
+/* engine/mod.rs:1169-1184 (rope_rotate) and :1204-1209 (KvCache::push).  Rotates q
+ * [tokens, n_heads*d] in place and writes the rotated k and v [tokens, n_kv*d] into the
+ * head-major cache [n_seq, n_kv, s_max, d] (float32 or bfloat16) at row positions[t] of
+ * sequence seq_index[t].  cos_sin is [max_pos, d/2, 2] float32. */
+qk_status qk_rope_cache(qk_ctx *ctx, float *q, const float *k, const float *v,
+                        const float *cos_sin, const int32_t *positions, const int32_t *seq_index,
+                        void *cache_k, void *cache_v, int32_t kv_dtype, size_t n_tokens,
+                        size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t s_max);
+/* engine/mod.rs:1074-1121 (gqa_attention_scalar): one query per sequence, q [batch,
+ * n_heads, d], against kv_len[b] cached positions; out [batch, n_heads, d].  The keys are
+ * split n_splits ways across blocks; scratch must hold qk_decode_attention_scratch bytes. */
+size_t qk_decode_attention_scratch(size_t batch, size_t n_heads, size_t head_dim, size_t n_splits);
+qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
+                              const void *cache_v, int32_t kv_dtype, const int32_t *kv_len,
+                              size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                              size_t s_max, size_t n_splits, float *scratch, float *out);
+/* engine/mod.rs:931-935: out = g*u/(1+exp(-g)). */
+qk_status qk_swiglu(qk_ctx *ctx, const float *gate, const float *up, size_t n, float *out);
+/* engine/mod.rs:921-924: out = a + b. */
+qk_status qk_add(qk_ctx *ctx, const float *a, const float *b, size_t n, float *out);
+/* engine/mod.rs:768-777 (embed): out[t] = table[ids[t]] (float32 or bfloat16 table). */
+qk_status qk_embed(qk_ctx *ctx, const void *table, int32_t table_dtype, const int32_t *ids,
+                   size_t n_tokens, size_t d, size_t vocab, float *out);
+/* engine/mod.rs:788-800 (logits): logits[t*logits_stride + v] = hidden[t] . weight[v],
+ * float32 accumulation; weight [vocab, d] float32 or bfloat16. */
+qk_status qk_lm_head(qk_ctx *ctx, const float *hidden, const void *weight, int32_t weight_dtype,
+                     size_t n_tokens, size_t vocab, size_t d, size_t logits_stride,
+                     float *logits);
+/* crates/quantibbler-server/src/sampler.rs:5-16 (greedy): the first maximum of each row;
+ * out_idx is offset by index_base (for a vocabulary shard). */
+qk_status qk_argmax_first(qk_ctx *ctx, const float *logits, size_t n_tokens, size_t vocab,
+                          size_t logits_stride, int32_t index_base, float *out_val,
+                          int32_t *out_idx);
+
 /* Which GEMV kernel qk_layer_apply uses: 0 = sign-select SIMT, 1 = bit-sliced INT8
- * tensor-core.  Returns the previous value; values out of range leave it unchanged. */
+ * tensor-core (default), 2 = the same with 16-warp fused blocks.  Returns the previous value; values out of range leave it unchanged. */
 int32_t qk_set_gemv_kernel(qk_ctx *ctx, int32_t which);
 /* Number of kernels launched on this context since creation (for benchmarks). */
 uint64_t qk_gpu_launch_count(qk_ctx *ctx);

@@ -1,0 +1,92 @@
+"""NumPy restatement of the reference's decoder forward.  TEST INFRASTRUCTURE ONLY.
+
+Follows crates/quantibbler-server/src/engine/mod.rs: transformer (:878-945), norm_apply
+(:837-851), rms_norm_into (:1154-1160), rope_rotate (:1169-1184), gqa_attention_scalar
+(:1074-1121, through oracle.gqa_attention_scalar), logits (:788-800) and
+sampler.rs:5-16 (greedy).  The linears go through oracle.layer_apply, which is pinned to
+the reference's vectors; the remaining pieces are pinned only as restatements (the
+reference's model-level golden, tests/fixtures/parity-tiny, needs its container reader).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+import oracle
+
+
+def _bf16(a):
+    return oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(np.asarray(a, np.float32)))
+
+
+def rms_norm(x, w, eps, serving):
+    x = np.asarray(x, np.float32)
+    if serving == "bfloat16":
+        x = _bf16(x)
+    ss = np.float32(0.0)
+    for v in x:  # sequential float32 sum, as the iterator sum in the reference
+        ss = np.float32(ss + v * v)
+    ss = np.float32(ss / np.float32(len(x)))
+    inv = np.float32(1.0) / np.sqrt(np.float32(ss + np.float32(eps)))
+    out = (x * inv * w).astype(np.float32)
+    return _bf16(out) if serving == "bfloat16" else out
+
+
+def rope_rotate(v, head_dim, pos, theta):
+    v = np.array(v, np.float32, copy=True)
+    half = head_dim // 2
+    for head in range(len(v) // head_dim):
+        base = head * head_dim
+        for i in range(half):
+            inv_freq = float(theta) ** (-(2.0 * i) / head_dim)
+            s, c = np.float32(np.sin(pos * inv_freq)), np.float32(np.cos(pos * inv_freq))
+            a, b = v[base + i], v[base + half + i]
+            v[base + i] = a * c - b * s
+            v[base + half + i] = b * c + a * s
+    return v
+
+
+def apply(layer, x, serving):
+    return oracle.layer_apply(layer["ub_rows"], layer["vb_t_rows"], layer["dout"], layer["din"],
+                              layer["r"], layer["s1"], layer["s2"], layer.get("bias"), x,
+                              serving=serving)
+
+
+class Session:
+    """One sequence: weights + an append-only KV cache (KvCache, engine/mod.rs:1189-1209)."""
+
+    def __init__(self, cfg, weights, kv_round=None):
+        self.cfg, self.w = cfg, weights
+        self.keys = [[] for _ in range(cfg.n_layers)]
+        self.vals = [[] for _ in range(cfg.n_layers)]
+        self.kv_round = kv_round  # optional storage rounding of the cache (bfloat16 cache)
+
+    def transformer(self, x):
+        cfg, sv = self.cfg, self.cfg.serving
+        pos = len(self.keys[0])
+        h = np.asarray(x, np.float32)
+        for b, lw in enumerate(self.w["layers"]):
+            normed = rms_norm(h, lw["input_norm"], cfg.rms_eps, sv)
+            q, k, v = (apply(lw[n], normed, sv) for n in ("q", "k", "v"))
+            q = rope_rotate(q, cfg.head_dim, pos, cfg.rope_theta)
+            k = rope_rotate(k, cfg.head_dim, pos, cfg.rope_theta)
+            if self.kv_round:
+                k, v = self.kv_round(k), self.kv_round(v)
+            self.keys[b].append(k)
+            self.vals[b].append(v)
+            attn = oracle.gqa_attention_scalar(q, np.stack(self.keys[b]), np.stack(self.vals[b]),
+                                               cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
+            h = (apply(lw["o"], attn, sv) + h).astype(np.float32)
+            normed = rms_norm(h, lw["post_norm"], cfg.rms_eps, sv)
+            g, u = apply(lw["gate"], normed, sv), apply(lw["up"], normed, sv)
+            hidden = (g * u / (np.float32(1.0) + np.exp(-g))).astype(np.float32)
+            h = (apply(lw["down"], hidden, sv) + h).astype(np.float32)
+        return rms_norm(h, self.w["final_norm"], cfg.rms_eps, sv)
+
+    def logits(self, hidden):
+        return (self.w["lm_head"].astype(np.float32) @ hidden.astype(np.float32)).astype(np.float32)
+
+    def step(self, token):
+        hidden = self.transformer(self.w["embedding"][token])
+        lg = self.logits(hidden)
+        return int(np.argmax(lg)), lg  # np.argmax returns the first maximum, like greedy()

@@ -70,8 +70,27 @@ _SIGNATURES = {
     "qk_layers_apply_group": (c_int32, [c_void_p, POINTER(c_void_p), c_size_t, c_void_p, c_void_p]),
     "qk_group_create": (c_int32, [c_void_p, POINTER(c_void_p), c_size_t, c_void_p, c_void_p,
                                   POINTER(c_void_p)]),
+    "qk_plan_create": (c_int32, [c_void_p, POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p),
+                                 c_size_t, POINTER(c_void_p)]),
     "qk_group_apply": (c_int32, [c_void_p, c_void_p]),
     "qk_group_free": (None, [c_void_p]),
+    "qk_rmsnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_float,
+                             c_int32, c_void_p, c_void_p]),
+    "qk_rope_cache": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_int32, c_size_t, c_size_t,
+                                c_size_t, c_size_t, c_size_t]),
+    "qk_decode_attention_scratch": (c_size_t, [c_size_t, c_size_t, c_size_t, c_size_t]),
+    "qk_decode_attention": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p,
+                                      c_size_t, c_size_t, c_size_t, c_size_t, c_size_t, c_size_t,
+                                      c_void_p, c_void_p]),
+    "qk_swiglu": (c_int32, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "qk_add": (c_int32, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "qk_embed": (c_int32, [c_void_p, c_void_p, c_int32, c_void_p, c_size_t, c_size_t, c_size_t,
+                           c_void_p]),
+    "qk_lm_head": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_size_t, c_size_t, c_size_t,
+                             c_size_t, c_void_p]),
+    "qk_argmax_first": (c_int32, [c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_int32,
+                                  c_void_p, c_void_p]),
     "qk_set_gemv_kernel": (c_int32, [c_void_p, c_int32]),
     "qk_gpu_launch_count": (c_uint64, [c_void_p]),
 }

@@ -1,0 +1,531 @@
+// Decoder-side kernels around the factorized linear: what one transformer block needs
+// besides its seven linears, on device buffers, launch-only (safe inside CUDA graph
+// capture: no allocation, no synchronisation, no host copies).
+//
+// Semantics follow crates/quantibbler-server/src/engine/mod.rs:
+//   RMSNorm        :1154-1160 (rms_norm_into) and :837-851 (norm_apply: bf16 serving rounds
+//                  the operand and the result to bfloat16)
+//   RoPE           :1169-1184 (rope_rotate: HF rotate_half, pairs (i, i + d/2), the angle
+//                  pos * theta^(-2i/d) evaluated in float64 and cast to float32)
+//   KV cache       :1189-1209 (append one row per position), kept head-major
+//                  [B, KV, S_max, d] as the device contract of gpu_attention.rs wants
+//   attention      :1074-1121 (gqa_attention_scalar: one query position against the cache)
+//   SwiGLU         :931-935   g * u / (1 + exp(-g))
+//   residual       :921-924, :937-940
+//   embedding      :768-777, logits :788-800 (float32 accumulation over d_model),
+//   greedy         crates/quantibbler-server/src/sampler.rs:5-16 (first maximum wins)
+#include <cuda_bf16.h>
+
+#include <cmath>
+
+#include "qk_common.h"
+
+namespace {
+
+__device__ __forceinline__ float round_bf16f(float v) {
+    uint32_t u = __float_as_uint(v);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return __uint_as_float((u | 0x00400000u) & 0xffff0000u);
+    u = (u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u;
+    return __uint_as_float(u);
+}
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) {
+    return __uint_as_float((uint32_t)b << 16);
+}
+__device__ __forceinline__ uint16_t float_to_bf16_bits(float v) {
+    return (uint16_t)(__float_as_uint(round_bf16f(v)) >> 16);
+}
+
+template <typename T> __device__ __forceinline__ float load_as_float(const T *p, size_t i);
+template <> __device__ __forceinline__ float load_as_float<float>(const float *p, size_t i) {
+    return p[i];
+}
+template <> __device__ __forceinline__ float load_as_float<uint16_t>(const uint16_t *p, size_t i) {
+    return bf16_bits_to_float(p[i]);
+}
+template <typename T> __device__ __forceinline__ void store_from_float(T *p, size_t i, float v);
+template <> __device__ __forceinline__ void store_from_float<float>(float *p, size_t i, float v) {
+    p[i] = v;
+}
+template <> __device__ __forceinline__ void store_from_float<uint16_t>(uint16_t *p, size_t i,
+                                                                       float v) {
+    p[i] = float_to_bf16_bits(v);
+}
+
+__device__ __forceinline__ float block_sum(float v, float *red) {
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, nw = blockDim.x / 32;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+    for (int w = 0; w < nw; ++w) total += red[w];
+    __syncthreads();
+    return total;
+}
+
+// h = x (+ residual); x_out = h; y = h * rsqrt(mean(h^2) + eps) * w.  One block per token.
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
+               const float *__restrict__ w, float *__restrict__ x_out, float *__restrict__ y,
+               uint32_t d, float eps, int bf16) {
+    __shared__ float red[8];
+    const size_t base = (size_t)blockIdx.x * d;
+    float ss = 0.f;
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+        float h = x[base + i];
+        if (residual) h += residual[base + i];
+        if (x_out) x_out[base + i] = h;
+        if (bf16) h = round_bf16f(h);
+        ss += h * h;
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+        float h = x[base + i];
+        if (residual) h += residual[base + i];
+        if (bf16) h = round_bf16f(h);
+        float o = h * inv * w[i];
+        y[base + i] = bf16 ? round_bf16f(o) : o;
+    }
+}
+
+// Rotates q in place and writes rotated k and v into the cache row of (seq, pos).
+// cos_sin: [max_pos][d/2][2] float32.  One block per token; threads cover (head, i).
+template <typename KV>
+__global__ void __launch_bounds__(256)
+rope_cache_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                  const float *__restrict__ cos_sin, const int32_t *__restrict__ positions,
+                  const int32_t *__restrict__ seq_index, KV *__restrict__ cache_k,
+                  KV *__restrict__ cache_v, uint32_t n_heads, uint32_t n_kv, uint32_t d,
+                  uint32_t s_max) {
+    const uint32_t tok = blockIdx.x, half = d / 2;
+    const int pos = positions[tok], seq = seq_index[tok];
+    const float *cs = cos_sin + (size_t)pos * half * 2;
+    float *qt = q + (size_t)tok * n_heads * d;
+    for (uint32_t idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
+        uint32_t h = idx / half, i = idx % half;
+        float c = cs[2 * i], s = cs[2 * i + 1];
+        float a = qt[h * d + i], b = qt[h * d + half + i];
+        qt[h * d + i] = a * c - b * s;
+        qt[h * d + half + i] = b * c + a * s;
+    }
+    const float *kt = k + (size_t)tok * n_kv * d, *vt = v + (size_t)tok * n_kv * d;
+    for (uint32_t idx = threadIdx.x; idx < n_kv * half; idx += blockDim.x) {
+        uint32_t h = idx / half, i = idx % half;
+        float c = cs[2 * i], s = cs[2 * i + 1];
+        float a = kt[h * d + i], b = kt[h * d + half + i];
+        size_t row = (((size_t)seq * n_kv + h) * s_max + pos) * d;
+        store_from_float<KV>(cache_k, row + i, a * c - b * s);
+        store_from_float<KV>(cache_k, row + half + i, b * c + a * s);
+        store_from_float<KV>(cache_v, row + i, vt[h * d + i]);
+        store_from_float<KV>(cache_v, row + half + i, vt[h * d + half + i]);
+    }
+}
+
+// Split-KV decode attention: one query position per sequence against the cache.
+// grid (split, kv head, sequence); a block of 128 threads covers the keys
+// [split*chunk, min(len, (split+1)*chunk)) for all G = H/KV query heads of the kv head, so
+// each K/V row is read once per group.  Eight lanes share a key (d/8 channels each).
+// partial[(b, h, split)] = {m, l, o[d]}.
+constexpr int kDecThreads = 128;
+
+template <typename KV, int DPL, int GQ>  // DPL = channels per lane (8 lanes per key), GQ = query heads per block
+__global__ void __launch_bounds__(kDecThreads)
+decode_attention_kernel(const float *__restrict__ q, const KV *__restrict__ cache_k,
+                        const KV *__restrict__ cache_v, const int32_t *__restrict__ kv_len,
+                        float *__restrict__ partial, uint32_t n_heads, uint32_t n_kv, uint32_t d,
+                        uint32_t s_max, uint32_t chunk, uint32_t n_splits) {
+    const uint32_t group = n_heads / n_kv, subs = group / GQ;  // blocks per kv head
+    const uint32_t split = blockIdx.x, kvh = blockIdx.y / subs, hsub = blockIdx.y % subs;
+    const uint32_t b = blockIdx.z, h0 = kvh * group + hsub * GQ;
+    const int len = kv_len[b];
+    const int j_begin = split * chunk, j_end = min(len, (int)((split + 1) * chunk));
+    const uint32_t tid = threadIdx.x, sub = tid % 8, slot = tid / 8;  // 16 key slots per block
+    const unsigned gmask = 0xffu << ((tid % 32) / 8 * 8);  // the eight lanes sharing a key
+    const float scale = 1.0f / sqrtf((float)d);
+
+    float qr[GQ][DPL], m[GQ], l[GQ], o[GQ][DPL];
+#pragma unroll
+    for (int gq = 0; gq < GQ; ++gq) {
+        m[gq] = -INFINITY;
+        l[gq] = 0.f;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+            uint32_t c = sub * DPL + e;
+            qr[gq][e] = c < d ? q[((size_t)b * n_heads + h0 + gq) * d + c] : 0.f;
+            o[gq][e] = 0.f;
+        }
+    }
+    const KV *kb = cache_k + ((size_t)b * n_kv + kvh) * s_max * d;
+    const KV *vb = cache_v + ((size_t)b * n_kv + kvh) * s_max * d;
+    for (int j = j_begin + slot; j < j_end; j += kDecThreads / 8) {
+        float kk[DPL], vv[DPL];
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+            uint32_t c = sub * DPL + e;
+            kk[e] = c < d ? load_as_float<KV>(kb, (size_t)j * d + c) : 0.f;
+            vv[e] = c < d ? load_as_float<KV>(vb, (size_t)j * d + c) : 0.f;
+        }
+#pragma unroll
+        for (int gq = 0; gq < GQ; ++gq) {
+            float dot = 0.f;
+#pragma unroll
+            for (int e = 0; e < DPL; ++e) dot = fmaf(qr[gq][e], kk[e], dot);
+            dot += __shfl_xor_sync(gmask, dot, 1);
+            dot += __shfl_xor_sync(gmask, dot, 2);
+            dot += __shfl_xor_sync(gmask, dot, 4);
+            const float s = dot * scale;
+            const float m_new = fmaxf(m[gq], s);
+            const float alpha = expf(m[gq] - m_new), p = expf(s - m_new);
+            l[gq] = l[gq] * alpha + p;
+#pragma unroll
+            for (int e = 0; e < DPL; ++e) o[gq][e] = o[gq][e] * alpha + p * vv[e];
+            m[gq] = m_new;
+        }
+    }
+    // combine the 16 key slots of the block through shared memory
+    __shared__ float sm_m[kDecThreads / 8][GQ], sm_l[kDecThreads / 8][GQ];
+    extern __shared__ float sm_o[];  // [16 slots][GQ][d]
+#pragma unroll
+    for (int gq = 0; gq < GQ; ++gq) {
+        if (sub == 0) {
+            sm_m[slot][gq] = m[gq];
+            sm_l[slot][gq] = l[gq];
+        }
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+            uint32_t c = sub * DPL + e;
+            if (c < d) sm_o[((size_t)slot * GQ + gq) * d + c] = o[gq][e];
+        }
+    }
+    __syncthreads();
+    for (uint32_t idx = tid; idx < GQ * d; idx += kDecThreads) {
+        uint32_t gq = idx / d, c = idx % d;
+        float mm = -INFINITY;
+        for (int s2 = 0; s2 < kDecThreads / 8; ++s2) mm = fmaxf(mm, sm_m[s2][gq]);
+        float ll = 0.f, oo = 0.f;
+        for (int s2 = 0; s2 < kDecThreads / 8; ++s2) {
+            float w = mm == -INFINITY ? 0.f : expf(sm_m[s2][gq] - mm);
+            ll += sm_l[s2][gq] * w;
+            oo += sm_o[((size_t)s2 * GQ + gq) * d + c] * w;
+        }
+        float *out = partial + (((size_t)b * n_heads + h0 + gq) * n_splits + split) * (d + 2);
+        out[2 + c] = oo;
+        if (c == 0) {
+            out[0] = mm;
+            out[1] = ll;
+        }
+    }
+}
+
+// out[b, h, :] = sum_s o_s * exp(m_s - m) / sum_s l_s * exp(m_s - m).  One block per (b, h).
+__global__ void __launch_bounds__(128)
+decode_combine_kernel(const float *__restrict__ partial, float *__restrict__ out, uint32_t d,
+                      uint32_t n_splits) {
+    const float *p = partial + (size_t)blockIdx.x * n_splits * (d + 2);
+    float mm = -INFINITY;
+    for (uint32_t s = 0; s < n_splits; ++s) mm = fmaxf(mm, p[s * (d + 2)]);
+    float ll = 0.f;
+    for (uint32_t s = 0; s < n_splits; ++s) {
+        float ms = p[s * (d + 2)];
+        ll += ms == -INFINITY ? 0.f : p[s * (d + 2) + 1] * expf(ms - mm);
+    }
+    for (uint32_t c = threadIdx.x; c < d; c += blockDim.x) {
+        float oo = 0.f;
+        for (uint32_t s = 0; s < n_splits; ++s) {
+            float ms = p[s * (d + 2)];
+            if (ms != -INFINITY) oo += p[s * (d + 2) + 2 + c] * expf(ms - mm);
+        }
+        out[(size_t)blockIdx.x * d + c] = oo / ll;
+    }
+}
+
+__global__ void swiglu_kernel(const float *__restrict__ g, const float *__restrict__ u,
+                              float *__restrict__ out, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        float gv = g[i];
+        out[i] = gv * u[i] / (1.0f + expf(-gv));
+    }
+}
+
+__global__ void add_kernel(const float *__restrict__ a, const float *__restrict__ b,
+                           float *__restrict__ out, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = a[i] + b[i];
+}
+
+template <typename W>
+__global__ void embed_kernel(const W *__restrict__ table, const int32_t *__restrict__ ids,
+                             float *__restrict__ out, uint32_t d, uint32_t vocab) {
+    const int id = ids[blockIdx.x];
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x)
+        out[(size_t)blockIdx.x * d + i] =
+            (id >= 0 && (uint32_t)id < vocab) ? load_as_float<W>(table, (size_t)id * d + i) : 0.f;
+}
+
+// logits[t][v] = sum_i hidden[t][i] * W[v][i], float32 accumulation.  One warp per vocab row,
+// the row is streamed once per tile of TT tokens (it stays in L2 between tiles).
+template <typename W, int TT>
+__global__ void __launch_bounds__(256)
+lm_head_kernel(const float *__restrict__ hidden, const W *__restrict__ weight,
+               float *__restrict__ logits, uint32_t n_tokens, uint32_t vocab, uint32_t d,
+               uint32_t vocab_stride) {
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t v = blockIdx.x * 8 + warp;
+    if (v >= vocab) return;
+    for (uint32_t t0 = 0; t0 < n_tokens; t0 += TT) {
+        float acc[TT];
+#pragma unroll
+        for (int t = 0; t < TT; ++t) acc[t] = 0.f;
+        for (uint32_t i = lane * 4; i < d; i += 128) {
+            float w0 = load_as_float<W>(weight, (size_t)v * d + i);
+            float w1 = load_as_float<W>(weight, (size_t)v * d + i + 1);
+            float w2 = load_as_float<W>(weight, (size_t)v * d + i + 2);
+            float w3 = load_as_float<W>(weight, (size_t)v * d + i + 3);
+#pragma unroll
+            for (int t = 0; t < TT; ++t) {
+                if (t0 + t < n_tokens) {
+                    const float4 h = *reinterpret_cast<const float4 *>(hidden + (size_t)(t0 + t) * d + i);
+                    acc[t] = fmaf(h.x, w0, fmaf(h.y, w1, fmaf(h.z, w2, fmaf(h.w, w3, acc[t]))));
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+            float a = acc[t];
+            for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+            if (lane == 0 && t0 + t < n_tokens) logits[(size_t)(t0 + t) * vocab_stride + v] = a;
+        }
+    }
+}
+
+// First maximum of each row (sampler.rs:5-16: a later equal value does not win).
+// out_val/out_idx per token; idx is offset by `index_base` (for vocabulary shards).
+__global__ void __launch_bounds__(256)
+argmax_first_kernel(const float *__restrict__ logits, uint32_t vocab, uint32_t stride,
+                    int32_t index_base, float *__restrict__ out_val, int32_t *__restrict__ out_idx) {
+    __shared__ float sv[256];
+    __shared__ int si[256];
+    const float *row = logits + (size_t)blockIdx.x * stride;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (uint32_t i = threadIdx.x; i < vocab; i += blockDim.x) {
+        float v = row[i];
+        if (v > best || (v == best && (int)i < bi)) {
+            best = v;
+            bi = (int)i;
+        }
+    }
+    if (bi == 0x7fffffff) bi = 0;  // all NaN or -inf: the reference returns index 0
+    sv[threadIdx.x] = best;
+    si[threadIdx.x] = bi;
+    __syncthreads();
+    for (int off = 128; off > 0; off >>= 1) {
+        if ((int)threadIdx.x < off) {
+            float ov = sv[threadIdx.x + off];
+            int oi = si[threadIdx.x + off];
+            if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) {
+                sv[threadIdx.x] = ov;
+                si[threadIdx.x] = oi;
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        out_val[blockIdx.x] = sv[0];
+        out_idx[blockIdx.x] = si[0] + index_base;
+    }
+}
+
+qk_status enter(qk_ctx *ctx, qk_ctx **c) {
+    qk_status st = qk::resolve_ctx(ctx, c);
+    if (st != QK_OK) return st;
+    QK_CUDA(cudaSetDevice((*c)->device));
+    return QK_OK;
+}
+
+#define QK_LAUNCHED(c)            \
+    QK_CUDA(cudaGetLastError()); \
+    (c)->launches++;             \
+    return QK_OK
+
+}  // namespace
+
+extern "C" {
+
+qk_status qk_rmsnorm(qk_ctx *ctx, const float *x, const float *residual, const float *weight,
+                     size_t n_tokens, size_t d, float eps, int32_t serving_dtype, float *x_out,
+                     float *y) {
+    qk_ctx *c;
+    qk_status st = enter(ctx, &c);
+    if (st != QK_OK) return st;
+    if (n_tokens == 0) return QK_OK;
+    rmsnorm_kernel<<<(unsigned)n_tokens, 256, 0, c->stream>>>(x, residual, weight, x_out, y,
+                                                              (uint32_t)d, eps,
+                                                              serving_dtype == QK_BF16);
+    QK_LAUNCHED(c);
+}
+
+qk_status qk_rope_cache(qk_ctx *ctx, float *q, const float *k, const float *v,
+                        const float *cos_sin, const int32_t *positions, const int32_t *seq_index,
+                        void *cache_k, void *cache_v, int32_t kv_dtype, size_t n_tokens,
+                        size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t s_max) {
+    qk_ctx *c;
+    qk_status st = enter(ctx, &c);
+    if (st != QK_OK) return st;
+    if (head_dim % 2)
+        return qk::fail(QK_ERR_VALUE, "RoPE needs an even head_dim, got %zu", head_dim);
+    if (kv_dtype != QK_F32 && kv_dtype != QK_BF16)
+        return qk::fail(QK_ERR_VALUE, "KV cache dtype must be float32 or bfloat16, got tag %d",
+                        kv_dtype);
+    if (n_tokens == 0) return QK_OK;
+    if (kv_dtype == QK_F32)
+        rope_cache_kernel<float><<<(unsigned)n_tokens, 256, 0, c->stream>>>(
+            q, k, v, cos_sin, positions, seq_index, (float *)cache_k, (float *)cache_v,
+            (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)head_dim, (uint32_t)s_max);
+    else
+        rope_cache_kernel<uint16_t><<<(unsigned)n_tokens, 256, 0, c->stream>>>(
+            q, k, v, cos_sin, positions, seq_index, (uint16_t *)cache_k, (uint16_t *)cache_v,
+            (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)head_dim, (uint32_t)s_max);
+    QK_LAUNCHED(c);
+}
+
+size_t qk_decode_attention_scratch(size_t batch, size_t n_heads, size_t head_dim,
+                                   size_t n_splits) {
+    return batch * n_heads * n_splits * (head_dim + 2) * sizeof(float);
+}
+
+qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
+                              const void *cache_v, int32_t kv_dtype, const int32_t *kv_len,
+                              size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                              size_t s_max, size_t n_splits, float *scratch, float *out) {
+    qk_ctx *c;
+    qk_status st = enter(ctx, &c);
+    if (st != QK_OK) return st;
+    if (n_kv_heads == 0 || n_heads % n_kv_heads != 0)
+        return qk::fail(QK_ERR_VALUE, "n_kv_heads must divide n_heads: n_heads=%zu, n_kv_heads=%zu",
+                        n_heads, n_kv_heads);
+    const size_t group = n_heads / n_kv_heads;
+    if (head_dim > 256)
+        return qk::fail(QK_ERR_VALUE, "head_dim above 256 is not supported, got %zu", head_dim);
+    if (n_splits == 0 || batch == 0) return qk::fail(QK_ERR_VALUE, "empty decode attention");
+    if (kv_dtype != QK_F32 && kv_dtype != QK_BF16)
+        return qk::fail(QK_ERR_VALUE, "KV cache dtype must be float32 or bfloat16, got tag %d",
+                        kv_dtype);
+    const int gq = group % 4 == 0 ? 4 : group % 2 == 0 ? 2 : 1;  // query heads per block
+    const size_t chunk = qk::ceil_div(s_max, n_splits);
+    dim3 grid((unsigned)n_splits, (unsigned)(n_kv_heads * (group / gq)), (unsigned)batch);
+    const size_t smem = (kDecThreads / 8) * gq * head_dim * sizeof(float);
+    const int dpl = head_dim <= 64 ? 8 : head_dim <= 128 ? 16 : 32;
+#define QK_DEC(KV, DPL, GQ)                                                                      \
+    do {                                                                                         \
+        if (smem > 48 * 1024)                                                                    \
+            QK_CUDA(cudaFuncSetAttribute(decode_attention_kernel<KV, DPL, GQ>,                   \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        decode_attention_kernel<KV, DPL, GQ><<<grid, kDecThreads, smem, c->stream>>>(            \
+            q, (const KV *)cache_k, (const KV *)cache_v, kv_len, scratch, (uint32_t)n_heads,     \
+            (uint32_t)n_kv_heads, (uint32_t)head_dim, (uint32_t)s_max, (uint32_t)chunk,          \
+            (uint32_t)n_splits);                                                                 \
+    } while (0)
+#define QK_DEC_G(KV, DPL)                                                  \
+    do {                                                                   \
+        if (gq == 4) QK_DEC(KV, DPL, 4);                                   \
+        else if (gq == 2) QK_DEC(KV, DPL, 2);                              \
+        else QK_DEC(KV, DPL, 1);                                           \
+    } while (0)
+    if (kv_dtype == QK_F32) {
+        if (dpl == 8) QK_DEC_G(float, 8); else if (dpl == 16) QK_DEC_G(float, 16); else QK_DEC_G(float, 32);
+    } else {
+        if (dpl == 8) QK_DEC_G(uint16_t, 8); else if (dpl == 16) QK_DEC_G(uint16_t, 16); else QK_DEC_G(uint16_t, 32);
+    }
+#undef QK_DEC_G
+#undef QK_DEC
+    QK_CUDA(cudaGetLastError());
+    c->launches++;
+    decode_combine_kernel<<<(unsigned)(batch * n_heads), 128, 0, c->stream>>>(
+        scratch, out, (uint32_t)head_dim, (uint32_t)n_splits);
+    QK_LAUNCHED(c);
+}
+
+qk_status qk_swiglu(qk_ctx *ctx, const float *gate, const float *up, size_t n, float *out) {
+    qk_ctx *c;
+    qk_status st = enter(ctx, &c);
+    if (st != QK_OK) return st;
+    if (n == 0) return QK_OK;
+    swiglu_kernel<<<(unsigned)qk::ceil_div(n, 256), 256, 0, c->stream>>>(gate, up, out, n);
+    QK_LAUNCHED(c);
+}
+
+qk_status qk_add(qk_ctx *ctx, const float *a, const float *b, size_t n, float *out) {
+    qk_ctx *c;
+    qk_status st = enter(ctx, &c);
+    if (st != QK_OK) return st;
+    if (n == 0) return QK_OK;
+    add_kernel<<<(unsigned)qk::ceil_div(n, 256), 256, 0, c->stream>>>(a, b, out, n);
+    QK_LAUNCHED(c);
+}
+
+qk_status qk_embed(qk_ctx *ctx, const void *table, int32_t table_dtype, const int32_t *ids,
+                   size_t n_tokens, size_t d, size_t vocab, float *out) {
+    qk_ctx *c;
+    qk_status st = enter(ctx, &c);
+    if (st != QK_OK) return st;
+    if (n_tokens == 0) return QK_OK;
+    if (table_dtype == QK_F32)
+        embed_kernel<float><<<(unsigned)n_tokens, 256, 0, c->stream>>>(
+            (const float *)table, ids, out, (uint32_t)d, (uint32_t)vocab);
+    else if (table_dtype == QK_BF16)
+        embed_kernel<uint16_t><<<(unsigned)n_tokens, 256, 0, c->stream>>>(
+            (const uint16_t *)table, ids, out, (uint32_t)d, (uint32_t)vocab);
+    else
+        return qk::fail(QK_ERR_VALUE, "embedding dtype must be float32 or bfloat16, got tag %d",
+                        table_dtype);
+    QK_LAUNCHED(c);
+}
+
+qk_status qk_lm_head(qk_ctx *ctx, const float *hidden, const void *weight, int32_t weight_dtype,
+                     size_t n_tokens, size_t vocab, size_t d, size_t logits_stride,
+                     float *logits) {
+    qk_ctx *c;
+    qk_status st = enter(ctx, &c);
+    if (st != QK_OK) return st;
+    if (d % 4) return qk::fail(QK_ERR_VALUE, "d_model must be a multiple of 4, got %zu", d);
+    if (n_tokens == 0 || vocab == 0) return QK_OK;
+    const unsigned blocks = (unsigned)qk::ceil_div(vocab, 8);
+    if (weight_dtype == QK_F32) {
+        if (n_tokens == 1)
+            lm_head_kernel<float, 1><<<blocks, 256, 0, c->stream>>>(
+                hidden, (const float *)weight, logits, 1, (uint32_t)vocab, (uint32_t)d,
+                (uint32_t)logits_stride);
+        else
+            lm_head_kernel<float, 8><<<blocks, 256, 0, c->stream>>>(
+                hidden, (const float *)weight, logits, (uint32_t)n_tokens, (uint32_t)vocab,
+                (uint32_t)d, (uint32_t)logits_stride);
+    } else if (weight_dtype == QK_BF16) {
+        if (n_tokens == 1)
+            lm_head_kernel<uint16_t, 1><<<blocks, 256, 0, c->stream>>>(
+                hidden, (const uint16_t *)weight, logits, 1, (uint32_t)vocab, (uint32_t)d,
+                (uint32_t)logits_stride);
+        else
+            lm_head_kernel<uint16_t, 8><<<blocks, 256, 0, c->stream>>>(
+                hidden, (const uint16_t *)weight, logits, (uint32_t)n_tokens, (uint32_t)vocab,
+                (uint32_t)d, (uint32_t)logits_stride);
+    } else {
+        return qk::fail(QK_ERR_VALUE, "head dtype must be float32 or bfloat16, got tag %d",
+                        weight_dtype);
+    }
+    QK_LAUNCHED(c);
+}
+
+qk_status qk_argmax_first(qk_ctx *ctx, const float *logits, size_t n_tokens, size_t vocab,
+                          size_t logits_stride, int32_t index_base, float *out_val,
+                          int32_t *out_idx) {
+    qk_ctx *c;
+    qk_status st = enter(ctx, &c);
+    if (st != QK_OK) return st;
+    if (n_tokens == 0) return QK_OK;
+    argmax_first_kernel<<<(unsigned)n_tokens, 256, 0, c->stream>>>(
+        logits, (uint32_t)vocab, (uint32_t)logits_stride, index_base, out_val, out_idx);
+    QK_LAUNCHED(c);
+}
+
+}  // extern "C"

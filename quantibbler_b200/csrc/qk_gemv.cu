@@ -1069,6 +1069,51 @@ qk_status qk_group_create(qk_ctx *ctx, const qk_layer *const *layers, size_t n_l
     return QK_OK;
 }
 
+qk_status qk_plan_create(qk_ctx *ctx, const qk_layer *const *layers, const float *const *x_ptrs,
+                         float *const *y_ptrs, size_t n_inst, qk_group **out) {
+    if (!out) return qk::fail(QK_ERR_VALUE, "qk_plan_create: out is null");
+    *out = nullptr;
+    if (n_inst == 0 || !layers || !x_ptrs || !y_ptrs || !layers[0])
+        return qk::fail(QK_ERR_VALUE, "qk_plan_create: no instances");
+    if (n_inst > 65535)
+        return qk::fail(QK_ERR_VALUE, "%zu instances exceed one launch (65535)", n_inst);
+    qk_ctx *c;
+    qk_status st = qk::resolve_ctx(ctx, &c);
+    if (st != QK_OK) return st;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    if ((st = check_group(c, layers, n_inst)) != QK_OK) return st;
+    const qk_layer *l0 = layers[0];
+    qk_group *g = new qk_group();
+    g->device = c->device;
+    g->n_inst = n_inst;
+    g->shape = *l0;
+    const InstanceScratch sc = scratch_of(l0);
+    cudaError_t e = cudaMalloc(&g->scratch, n_inst * sc.total);
+    if (e == cudaSuccess) e = cudaMalloc(&g->params, 2 * n_inst * sizeof(StageParams));
+    if (e != cudaSuccess) {
+        qk_group_free(g);
+        return qk::fail(QK_ERR_ALLOC, "device allocation for a layer plan failed: %s",
+                        cudaGetErrorString(e));
+    }
+    std::vector<StageParams> h(2 * n_inst);
+    // fill_params writes {stage 1, stage 2} adjacently for n_inst == 1; regroup so that all
+    // stage-1 records come first
+    for (size_t k = 0; k < n_inst; ++k) {
+        StageParams pair[2];
+        const qk_layer *one = layers[k];
+        fill_params(pair, &one, 1, 1, x_ptrs[k], y_ptrs[k], (uint8_t *)g->scratch + k * sc.total,
+                    0, 0);
+        h[k] = pair[0];
+        h[n_inst + k] = pair[1];
+    }
+    QK_CUDA(cudaMemcpyAsync(g->params, h.data(), h.size() * sizeof(StageParams),
+                            cudaMemcpyHostToDevice, c->stream));
+    QK_CUDA(cudaStreamSynchronize(c->stream));
+    *out = g;
+    return QK_OK;
+}
+
 qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group) {
     if (!group) return qk::fail(QK_ERR_VALUE, "qk_group_apply: group is null");
     qk_ctx *c;

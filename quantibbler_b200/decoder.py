@@ -1,0 +1,297 @@
+"""A Llama-shaped decoder built from the factorized-linear and attention kernels.
+
+Mirrors the control flow of the reference's ``ModelWeights::transformer`` /
+``Engine::decode_step`` (crates/quantibbler-server/src/engine/mod.rs:878-945,
+:1461-1476) for batched single-token decode with device-resident state: per block
+RMSNorm -> q,k,v -> RoPE -> KV append -> GQA attention -> o + residual -> RMSNorm ->
+gate,up -> SwiGLU -> down + residual; final norm, LM head, greedy (first maximum).
+
+Every operation is one C-ABI call that only launches kernels on the current stream, so a
+whole step can be captured in a CUDA graph and replayed.  Under tensor parallelism each
+rank holds its shard (``tp.shard_model``) and the two partial sums per block are completed
+by ``torch.distributed.all_reduce`` (NCCL) on the output buffers.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib, tp
+from ._lib import QK_BF16, QK_F32, check
+from .gpu import GpuContext, LayerPlan, PackedLayer
+
+LINEARS = ("q", "k", "v", "o", "gate", "up", "down")
+
+
+@dataclass
+class DecoderConfig:
+    n_layers: int
+    d_model: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    d_ff: int
+    vocab: int
+    rms_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    serving: str = "float32"       # ServingDtype of the linears and norms
+    kv_dtype: str = "bfloat16"     # storage of the KV cache
+    max_seq: int = 4096
+    max_batch: int = 1
+    n_splits: int = 0              # key splits of the decode attention (0 = choose)
+
+
+def rope_table(cfg: DecoderConfig) -> np.ndarray:
+    """cos/sin per (position, i) as the reference forms them: the angle in float64, the
+    results cast to float32 (engine/mod.rs:1169-1184)."""
+    half = cfg.head_dim // 2
+    inv_freq = cfg.rope_theta ** (-(2.0 * np.arange(half, dtype=np.float64)) / cfg.head_dim)
+    ang = np.arange(cfg.max_seq, dtype=np.float64)[:, None] * inv_freq[None, :]
+    return np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+
+
+def random_layer(rng, dout, din, r, with_bias=False) -> dict:
+    """Synthetic factorized linear as BASELINE.json's configs prescribe: Bernoulli(0.5)
+    factors, scales |N(0,1)|*0.02 + 1e-3."""
+    ub = rng.integers(0, 256, size=(dout, (r + 7) // 8), dtype=np.uint8)
+    vbt = rng.integers(0, 256, size=(r, (din + 7) // 8), dtype=np.uint8)
+    if r % 8:
+        ub[:, -1] &= (1 << (r % 8)) - 1
+    if din % 8:
+        vbt[:, -1] &= (1 << (din % 8)) - 1
+    return dict(ub_rows=ub, vb_t_rows=vbt, dout=dout, din=din, r=r,
+                s1=(np.abs(rng.standard_normal(dout)) * 0.02 + 1e-3).astype(np.float32),
+                s2=(np.abs(rng.standard_normal(din)) * 0.02 + 1e-3).astype(np.float32),
+                bias=(rng.standard_normal(dout) * 0.01).astype(np.float32) if with_bias else None)
+
+
+def random_model(cfg: DecoderConfig, ranks: dict, seed: int = 0) -> dict:
+    """Random-init weights of the configured architecture (no checkpoint is involved)."""
+    rng = np.random.default_rng(seed)
+    d, hd = cfg.d_model, cfg.head_dim
+    shapes = {"q": (cfg.n_heads * hd, d), "k": (cfg.n_kv_heads * hd, d),
+              "v": (cfg.n_kv_heads * hd, d), "o": (d, cfg.n_heads * hd),
+              "gate": (cfg.d_ff, d), "up": (cfg.d_ff, d), "down": (d, cfg.d_ff)}
+    layers = []
+    for _ in range(cfg.n_layers):
+        lw = {name: random_layer(rng, shapes[name][0], shapes[name][1], ranks[name])
+              for name in LINEARS}
+        lw["input_norm"] = (1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+        lw["post_norm"] = (1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+        layers.append(lw)
+
+    def bf16_valued(a):
+        u = a.astype(np.float32).view(np.uint32).astype(np.uint64)
+        u = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+        return u.astype(np.uint32).view(np.float32)
+
+    return dict(layers=layers,
+                final_norm=(1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32),
+                embedding=bf16_valued(rng.standard_normal((cfg.vocab, d)) * 0.02),
+                lm_head=bf16_valued(rng.standard_normal((cfg.vocab, d)) * 0.02),
+                vocab_offset=0)
+
+
+def _p(t) -> ctypes.c_void_p:
+    return ctypes.c_void_p(t.data_ptr())
+
+
+class Decoder:
+    """Batched greedy decode on one GPU (one tensor-parallel rank)."""
+
+    def __init__(self, ctx: GpuContext, cfg: DecoderConfig, weights: dict, tp_rank: int = 0,
+                 tp_size: int = 1, group=None):
+        import torch
+        self.torch, self.ctx, self.cfg = torch, ctx, cfg
+        self.tp_rank, self.tp_size, self.group = tp_rank, tp_size, group
+        w = tp.shard_model(weights, cfg, tp_rank, tp_size)
+        self.vocab_offset = int(w.get("vocab_offset", 0))
+        dev = torch.device("cuda", torch.cuda.current_device())
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)  # order with torch's own work
+        B, d, hd = cfg.max_batch, cfg.d_model, cfg.head_dim
+        self.h_loc, self.kv_loc = cfg.n_heads // tp_size, cfg.n_kv_heads // tp_size
+        self.ff_loc, self.v_loc = cfg.d_ff // tp_size, cfg.vocab // tp_size
+        self.serving_tag = QK_F32 if cfg.serving == "float32" else QK_BF16
+        self.kv_tag = QK_F32 if cfg.kv_dtype == "float32" else QK_BF16
+        f32 = dict(dtype=torch.float32, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+
+        def dev_f32(a):
+            return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dev)
+
+        def dev_bf16(a):
+            return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dev).to(
+                torch.bfloat16)
+
+        # activations (static: the step is captured in a CUDA graph)
+        self.x = torch.zeros(B, d, **f32)
+        self.h = torch.zeros(B, d, **f32)
+        self.q = torch.zeros(B, self.h_loc * hd, **f32)
+        self.k = torch.zeros(B, self.kv_loc * hd, **f32)
+        self.v = torch.zeros(B, self.kv_loc * hd, **f32)
+        self.attn = torch.zeros(B, self.h_loc * hd, **f32)
+        self.delta = torch.zeros(B, d, **f32)      # o / down output, all-reduced under TP
+        self.g = torch.zeros(B, self.ff_loc, **f32)
+        self.u = torch.zeros(B, self.ff_loc, **f32)
+        self.a = torch.zeros(B, self.ff_loc, **f32)
+        self.logits = torch.zeros(B, self.v_loc, **f32)
+        self.best_val = torch.zeros(B, **f32)
+        self.best_idx = torch.zeros(B, **i32)
+        self.token_ids = torch.zeros(B, **i32)
+        self.positions = torch.zeros(B, **i32)
+        self.kv_len = torch.ones(B, **i32)
+        self.seq_index = torch.arange(B, **i32)
+        kv_t = torch.float32 if cfg.kv_dtype == "float32" else torch.bfloat16
+        self.cache_k = [torch.zeros(B, self.kv_loc, cfg.max_seq, hd, dtype=kv_t, device=dev)
+                        for _ in range(cfg.n_layers)]
+        self.cache_v = [torch.zeros(B, self.kv_loc, cfg.max_seq, hd, dtype=kv_t, device=dev)
+                        for _ in range(cfg.n_layers)]
+        self.n_splits = cfg.n_splits or max(1, min(64, (4 * 148) // max(1, B * self.kv_loc)))
+        scratch = _lib.lib().qk_decode_attention_scratch(B, self.h_loc, hd, self.n_splits)
+        self.att_scratch = torch.zeros(scratch // 4 + 4, **f32)
+        self.cos_sin = dev_f32(rope_table(cfg))
+        self.embedding = dev_bf16(w["embedding"]) if cfg.serving == "bfloat16" else dev_f32(
+            w["embedding"])
+        self.emb_tag = QK_BF16 if cfg.serving == "bfloat16" else QK_F32
+        # the LM head is stored in bfloat16 (BASELINE config 4) unless serving is float32
+        self.lm_head = dev_bf16(w["lm_head"]) if cfg.serving == "bfloat16" else dev_f32(
+            w["lm_head"])
+        self.final_norm = dev_f32(w["final_norm"])
+        self.norms, self.layers, self.plans = [], [], []
+        for lw in w["layers"]:
+            self.norms.append((dev_f32(lw["input_norm"]), dev_f32(lw["post_norm"])))
+            L = {n: PackedLayer(ctx, lw[n]["ub_rows"], lw[n]["vb_t_rows"], lw[n]["dout"],
+                                lw[n]["din"], lw[n]["r"], lw[n]["s1"], lw[n]["s2"],
+                                lw[n].get("bias"), serving=cfg.serving, name=n) for n in LINEARS}
+            self.layers.append(L)
+
+            def rows(t, b):
+                return t[b].data_ptr()
+
+            def inst(names, src, dsts):
+                return [(L[n], rows(src, b), rows(dst, b)) for b in range(B)
+                        for n, dst in zip(names, dsts)]
+
+            plan = {"q": LayerPlan(ctx, inst(["q"], self.h, [self.q])),
+                    "o": LayerPlan(ctx, inst(["o"], self.attn, [self.delta])),
+                    "down": LayerPlan(ctx, inst(["down"], self.a, [self.delta]))}
+            same_kv = all(lw["k"][f] == lw["v"][f] for f in ("dout", "din", "r"))
+            if same_kv:
+                plan["kv"] = LayerPlan(ctx, inst(["k", "v"], self.h, [self.k, self.v]))
+            else:
+                plan["k"] = LayerPlan(ctx, inst(["k"], self.h, [self.k]))
+                plan["v"] = LayerPlan(ctx, inst(["v"], self.h, [self.v]))
+            same_gu = all(lw["gate"][f] == lw["up"][f] for f in ("dout", "din", "r"))
+            if same_gu:
+                plan["gu"] = LayerPlan(ctx, inst(["gate", "up"], self.h, [self.g, self.u]))
+            else:
+                plan["gate"] = LayerPlan(ctx, inst(["gate"], self.h, [self.g]))
+                plan["up"] = LayerPlan(ctx, inst(["up"], self.h, [self.u]))
+            self.plans.append(plan)
+        self.graph = None
+
+    # ------------------------------------------------------------------ one step
+    def _all_reduce(self, t):
+        if self.tp_size > 1:
+            self.torch.distributed.all_reduce(t, group=self.group)
+
+    def step(self) -> None:
+        """One decode step for the whole batch: reads ``token_ids``/``positions``/``kv_len``,
+        appends to the KV cache, leaves the greedy tokens in ``best_idx``."""
+        lib, c, cfg, h = _lib.lib(), self.ctx.handle, self.cfg, self.ctx
+        B, d, hd = cfg.max_batch, cfg.d_model, cfg.head_dim
+        check(lib.qk_embed(c, _p(self.embedding), self.emb_tag, _p(self.token_ids), B, d, cfg.vocab,
+                           _p(self.x)))
+        residual = None
+        for li in range(cfg.n_layers):
+            in_w, post_w = self.norms[li]
+            plan = self.plans[li]
+            check(lib.qk_rmsnorm(c, _p(self.x), residual, _p(in_w), B, d, cfg.rms_eps,
+                                 self.serving_tag, _p(self.x), _p(self.h)))
+            for name in ("q", "kv", "k", "v"):
+                if name in plan:
+                    plan[name].apply()
+            check(lib.qk_rope_cache(c, _p(self.q), _p(self.k), _p(self.v), _p(self.cos_sin),
+                                    _p(self.positions), _p(self.seq_index), _p(self.cache_k[li]),
+                                    _p(self.cache_v[li]), self.kv_tag, B, self.h_loc, self.kv_loc,
+                                    hd, cfg.max_seq))
+            check(lib.qk_decode_attention(c, _p(self.q), _p(self.cache_k[li]), _p(self.cache_v[li]),
+                                          self.kv_tag, _p(self.kv_len), B, self.h_loc, self.kv_loc,
+                                          hd, cfg.max_seq, self.n_splits, _p(self.att_scratch),
+                                          _p(self.attn)))
+            plan["o"].apply()
+            self._all_reduce(self.delta)
+            check(lib.qk_rmsnorm(c, _p(self.x), _p(self.delta), _p(post_w), B, d, cfg.rms_eps,
+                                 self.serving_tag, _p(self.x), _p(self.h)))
+            for name in ("gu", "gate", "up"):
+                if name in plan:
+                    plan[name].apply()
+            check(lib.qk_swiglu(c, _p(self.g), _p(self.u), B * self.ff_loc, _p(self.a)))
+            plan["down"].apply()
+            self._all_reduce(self.delta)
+            residual = _p(self.delta)
+        check(lib.qk_rmsnorm(c, _p(self.x), residual, _p(self.final_norm), B, d, cfg.rms_eps,
+                             self.serving_tag, _p(self.x), _p(self.h)))
+        head_tag = QK_BF16 if cfg.serving == "bfloat16" else QK_F32
+        check(lib.qk_lm_head(c, _p(self.h), _p(self.lm_head), head_tag, B, self.v_loc, d,
+                             self.v_loc, _p(self.logits)))
+        check(lib.qk_argmax_first(c, _p(self.logits), B, self.v_loc, self.v_loc, self.vocab_offset,
+                                  _p(self.best_val), _p(self.best_idx)))
+        if self.tp_size > 1:
+            torch = self.torch
+            vals = [torch.empty_like(self.best_val) for _ in range(self.tp_size)]
+            idxs = [torch.empty_like(self.best_idx) for _ in range(self.tp_size)]
+            torch.distributed.all_gather(vals, self.best_val, group=self.group)
+            torch.distributed.all_gather(idxs, self.best_idx, group=self.group)
+            v = torch.stack(vals)              # [ranks, B]; shards are in vocabulary order,
+            win = torch.argmax(v, dim=0)       # and argmax returns the first maximum
+            self.best_idx.copy_(torch.stack(idxs).gather(0, win[None])[0])
+
+    def advance(self) -> None:
+        """Feed the greedy tokens back and move every sequence one position on."""
+        self.token_ids.copy_(self.best_idx)
+        self.positions.add_(1)
+        self.kv_len.add_(1)
+
+    def capture(self) -> None:
+        """Record step() + advance() into a CUDA graph (after a few eager warm-up steps)."""
+        torch = self.torch
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        saved = [t.clone() for t in (self.token_ids, self.positions, self.kv_len)]
+        with torch.cuda.stream(stream):
+            self.ctx.set_stream(stream.cuda_stream)
+            for _ in range(2):
+                self.step()
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):  # the context already launches on `stream`
+            self.step()
+            self.advance()
+        for t, s in zip((self.token_ids, self.positions, self.kv_len), saved):
+            t.copy_(s)
+        torch.cuda.synchronize()
+        self.graph = graph
+
+    def start(self, token_ids, positions) -> None:
+        torch = self.torch
+        self.token_ids.copy_(torch.as_tensor(token_ids, dtype=torch.int32))
+        self.positions.copy_(torch.as_tensor(positions, dtype=torch.int32))
+        self.kv_len.copy_(self.positions + 1)
+
+    def decode(self, n_steps: int) -> np.ndarray:
+        """Greedy decode; returns the [n_steps, batch] generated ids."""
+        out = []
+        for _ in range(n_steps):
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self.step()
+                self.advance()
+            out.append(self.token_ids.clone())
+        self.torch.cuda.synchronize()
+        return self.torch.stack(out).cpu().numpy()

@@ -263,5 +263,21 @@ class LayerGroup:
             pass
 
 
-__all__ = ["LayerGroup", "GpuContext", "AttentionShape", "PackedLayer", "apply_group", "gpu_available",
+class LayerPlan(LayerGroup):
+    """Instances (layer, x pointer, y pointer) of one shape bound once; ``apply`` is two
+    kernel launches (one when there are at least as many instances as SMs)."""
+
+    def __init__(self, ctx: GpuContext, instances):
+        self.ctx = ctx
+        self.layers = [i[0] for i in instances]
+        n = len(instances)
+        larr = (ctypes.c_void_p * n)(*[i[0].handle for i in instances])
+        xarr = (ctypes.c_void_p * n)(*[ctypes.c_void_p(i[1]) for i in instances])
+        yarr = (ctypes.c_void_p * n)(*[ctypes.c_void_p(i[2]) for i in instances])
+        h = ctypes.c_void_p()
+        check(_lib.lib().qk_plan_create(ctx.handle, larr, xarr, yarr, n, ctypes.byref(h)))
+        self._h = h
+
+
+__all__ = ["LayerPlan", "LayerGroup", "GpuContext", "AttentionShape", "PackedLayer", "apply_group", "gpu_available",
            "gpu_init_hint", "GPU_INDEX_CEILING", "KernelError", "DeviceError"]
