@@ -90,7 +90,14 @@ class GpuContext:
         return int(_lib.lib().qk_gpu_stream(self._h) or 0)
 
     def set_stream(self, cuda_stream: int | None) -> None:
-        check(_lib.lib().qk_gpu_set_stream(self._h, ctypes.c_void_p(cuda_stream or 0)))
+        """Launch on a caller-owned stream; ``None`` restores the context's own stream.
+        The legacy default stream has the numeric handle 0, which the C ABI reads as
+        "restore": pass it as cudaStreamLegacy (1) instead."""
+        if cuda_stream is None:
+            handle = 0
+        else:
+            handle = int(cuda_stream) or 1
+        check(_lib.lib().qk_gpu_set_stream(self._h, ctypes.c_void_p(handle)))
 
     def set_gemv_kernel(self, which: int) -> int:
         return int(_lib.lib().qk_set_gemv_kernel(self._h, int(which)))

@@ -10,6 +10,12 @@ from quantibbler_b200.decoder import Decoder, DecoderConfig, random_model
 
 pytestmark = pytest.mark.gpu
 
+@pytest.fixture(autouse=True)
+def _restore_stream(gpu_ctx):
+    yield
+    gpu_ctx.set_stream(None)
+
+
 RANKS = {n: 24 for n in ("q", "k", "v", "o", "gate", "up", "down")}
 
 
