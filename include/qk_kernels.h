@@ -169,6 +169,22 @@ void qk_layer_free(qk_layer *layer);
  * Asynchronous on the context's stream. */
 qk_status qk_layer_apply(qk_ctx *ctx, const qk_layer *layer, const float *x_dev, size_t n_tokens,
                          float *y_dev);
+/* One token through one layer without any allocation by the library.  It has no
+ * counterpart in the reference.  For callers that cannot let a library allocate device
+ * memory on their behalf: a server that gave all remaining device memory to its KV cache
+ * at start-up, or a request thread that must not run into cudaMalloc's device-wide
+ * synchronisation.  The intermediates live in a fixed array inside the library image
+ * (64.5 KB, held by every GPU that loads the library until the process exits), so the
+ * layer must have r <= 8192 and din <= 16384; larger layers are refused with
+ * QK_ERR_VALUE.  ctx must be an existing context (NULL is refused).  x_dev holds din and
+ * y_dev dout float32 values on the context's device; the call is asynchronous on the
+ * context's stream and gives the same values as qk_layer_apply.  The first call on each
+ * device looks up the array's device address (cudaGetSymbolAddress): make that first call
+ * before any stream capture begins.  All calls share the one array and it keeps the last
+ * call's contents (every call overwrites what it later reads, so nothing needs clearing);
+ * two calls that overlap on the GPU, from different streams or contexts, race on it. */
+qk_status qk_layer_apply_noalloc(qk_ctx *ctx, const qk_layer *layer, const float *x_dev,
+                                 float *y_dev);
 /* The same with host buffers: x is copied in, y is copied out, and the call returns
  * when y is complete.  This is the drop-in for PackedLayer::apply. */
 qk_status qk_layer_apply_host(qk_ctx *ctx, const qk_layer *layer, const float *x, size_t x_len,

@@ -1137,3 +1137,112 @@ void qk_group_free(qk_group *g) {
 }
 
 }  // extern "C"
+
+namespace {
+
+// ------------------------------------------------------------------ allocation-free apply
+// A server that hands every remaining byte of device memory to its KV cache at start-up,
+// or a request thread that must never run into cudaMalloc's implicit device-wide
+// synchronisation, cannot let this library allocate on its behalf.  For those callers the
+// scratch of one single-token layer apply (the float64 intermediate t and the two stage
+// records) lives in a fixed array inside the library image instead of in a buffer the
+// context grows on demand.  Every GPU that loads the library carries the array until the
+// process exits.
+constexpr size_t kNoAllocMaxRank = 8192;     // r: t is r doubles
+constexpr size_t kNoAllocMaxWidth = 16384;   // din and r must also fit the shared-memory table
+constexpr size_t kNoAllocScratchBytes = kNoAllocMaxRank * sizeof(double) + 512;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+// One stage of one instance with its parameters passed by value: nothing to stage through
+// device memory first.
+template <bool kRoundBf16, bool kFinal>
+__global__ void __launch_bounds__(512, 1)
+gemv_bitslice_value_kernel(const StageParams p, uint32_t n_rows, uint32_t n_bits, uint32_t n_groups,
+                           uint32_t n_steps, uint32_t groups_per_warp) {
+    extern __shared__ __align__(16) uint8_t smem_dyn[];
+    bitslice_stage<kRoundBf16, kFinal, true, false, false>(
+        p, smem_dyn, smem_dyn + (size_t)n_steps * 4096, nullptr, nullptr, n_rows, n_bits, n_groups,
+        n_steps, blockIdx.x, groups_per_warp, false);
+}
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+unsigned char *g_noalloc_ptr[kMaxDevices] = {};  // device address of the array, per device
+
+// The array's name is only a host-side handle; kernels need its device address, which is
+// looked up once per device with that device current.
+qk_status noalloc_scratch(int device, unsigned char **out) {
+    if (device < 0 || device >= kMaxDevices)
+        return qk::fail(QK_ERR_VALUE, "device index %d is outside the supported range", device);
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_ptr[device]) {
+        void *ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || !ptr)
+            return qk::fail(QK_ERR_CUDA, "cudaGetSymbolAddress for the built-in scratch failed: %s",
+                            cudaGetErrorString(e));
+        g_noalloc_ptr[device] = static_cast<unsigned char *>(ptr);
+    }
+    *out = g_noalloc_ptr[device];
+    return QK_OK;
+}
+
+template <bool kFinal>
+qk_status launch_value_stage(qk_ctx *c, const StageParams &p, const StageShape &s, bool bf16) {
+    const StagePlan pl = plan_stage(c, s, 1);
+    dim3 grid((unsigned)pl.blocks);
+    auto gemv = bf16 ? gemv_bitslice_value_kernel<true, kFinal>
+                     : gemv_bitslice_value_kernel<false, kFinal>;
+    QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kSmemBudget));
+    gemv<<<grid, (unsigned)pl.warps_per_block * 32, pl.smem, c->stream>>>(
+        p, (uint32_t)s.n_rows, (uint32_t)s.n_bits, (uint32_t)s.n_groups, (uint32_t)s.n_steps,
+        (uint32_t)pl.gpw);
+    QK_CUDA(cudaGetLastError());
+    c->launches++;
+    return QK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+qk_status qk_layer_apply_noalloc(qk_ctx *ctx, const qk_layer *layer, const float *x_dev,
+                                 float *y_dev) {
+    if (!layer) return qk::fail(QK_ERR_VALUE, "qk_layer_apply_noalloc: layer is null");
+    if (!ctx)
+        return qk::fail(QK_ERR_VALUE,
+                        "qk_layer_apply_noalloc needs an existing context: creating the default "
+                        "one would allocate");
+    if (layer->r > kNoAllocMaxRank || layer->din > kNoAllocMaxWidth ||
+        layer->r > kNoAllocMaxWidth)
+        return qk::fail(QK_ERR_VALUE,
+                        "layer (din=%zu, r=%zu) exceeds the built-in scratch: the allocation-free "
+                        "apply supports r <= %zu and din <= %zu; use qk_layer_apply",
+                        layer->din, layer->r, kNoAllocMaxRank, kNoAllocMaxWidth);
+    qk_ctx *c = ctx;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    if (layer->device != c->device)
+        return qk::fail(QK_ERR_VALUE, "layer lives on device %d, context on device %d",
+                        layer->device, c->device);
+    unsigned char *scratch = nullptr;
+    qk_status st = noalloc_scratch(c->device, &scratch);
+    if (st != QK_OK) return st;
+    const StageShape s1 = stage1_shape(layer), s2 = stage2_shape(layer);
+    if (!plan_stage(c, s1, 1).smem_digits || !plan_stage(c, s2, 1).smem_digits)
+        return qk::fail(QK_ERR_VALUE, "layer is too wide for the allocation-free apply");
+    // Layout of the array: [t: r doubles][two stage records].  Both are fully rewritten by
+    // every call before they are read, so nothing has to be cleared between calls.
+    void *t_buf = scratch;
+    StageMeta *meta = reinterpret_cast<StageMeta *>(scratch + kNoAllocMaxRank * sizeof(double));
+    const bool bf16 = layer->serving == QK_BF16;
+    StageParams a{layer->vbt, layer->vbt_tiles, x_dev, layer->s2, t_buf, nullptr, nullptr, nullptr,
+                  meta};
+    StageParams b{layer->ub, layer->ub_tiles, t_buf, nullptr, y_dev, layer->s1, layer->bias, nullptr,
+                  meta + 1};
+    if ((st = launch_value_stage<false>(c, a, s1, bf16)) != QK_OK) return st;
+    return launch_value_stage<true>(c, b, s2, bf16);
+}
+
+}  // extern "C"

@@ -236,6 +236,15 @@ class PackedLayer:
                                         int(n_tokens), ctypes.c_void_p(y_ptr)))
 
 
+def apply_noalloc(layer: PackedLayer, x_ptr: int, y_ptr: int) -> None:
+    """One token through ``layer`` with the library allocating nothing: for hosts that own
+    all device memory themselves (for example a server whose KV cache took what was left
+    at start-up).  Same values as ``apply_device(x, 1, y)``; limited to r <= 8192 and
+    din <= 16384; calls that overlap on the GPU share one built-in scratch and race."""
+    check(_lib.lib().qk_layer_apply_noalloc(layer.ctx.handle, layer.handle, ctypes.c_void_p(x_ptr),
+                                            ctypes.c_void_p(y_ptr)))
+
+
 def apply_group(ctx: GpuContext, layers, x_ptr: int, y_ptr: int) -> None:
     """Same-shape layers in one pair of launches; layer i reads x + i*din floats."""
     arr = (ctypes.c_void_p * len(layers))(*[l.handle for l in layers])
@@ -286,5 +295,5 @@ class LayerPlan(LayerGroup):
         self._h = h
 
 
-__all__ = ["LayerPlan", "LayerGroup", "GpuContext", "AttentionShape", "PackedLayer", "apply_group", "gpu_available",
+__all__ = ["apply_noalloc", "LayerPlan", "LayerGroup", "GpuContext", "AttentionShape", "PackedLayer", "apply_group", "gpu_available",
            "gpu_init_hint", "GPU_INDEX_CEILING", "KernelError", "DeviceError"]
