@@ -165,6 +165,84 @@ def run_reference(args, rank: int) -> None:
     }))
 
 
+# ranks that give ~0.55 bits/weight by the reference's own byte formula
+# (src/quantibbler/qpk1.py:287-313, rank_for_target_bpw with float16 scales)
+C4_RANKS = {"q": 1102, "o": 1102, "k": 431, "v": 431, "gate": 1724, "up": 1724, "down": 1733}
+C3_RANKS = {"q": 1102, "k": 1102, "v": 1102, "o": 1102, "gate": 1614, "up": 1614, "down": 1622}
+
+
+def run_decode(args, rank: int, local_rank: int, world: int) -> None:
+    """Greedy decode tok/s of a Llama-shaped stack of factorized linears (BASELINE configs
+    3 and 4), tensor-parallel over the ranks, one CUDA graph per step."""
+    import torch
+    import torch.distributed as dist
+
+    from quantibbler_b200.decoder import Decoder, DecoderConfig, random_model
+    from quantibbler_b200.gpu import GpuContext
+
+    torch.cuda.set_device(local_rank)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        group = dist.group.WORLD
+    B, ctx_len = args.batch, args.context
+    if args.model == "llama3-8b":
+        cfg = DecoderConfig(n_layers=args.n_layers or 32, d_model=4096, n_heads=32, n_kv_heads=8,
+                            head_dim=128, d_ff=14336, vocab=128256, rms_eps=1e-5,
+                            rope_theta=500000.0, serving="bfloat16", kv_dtype="bfloat16",
+                            max_seq=ctx_len + args.steps + args.warmup + 8, max_batch=B)
+        ranks = C4_RANKS
+    else:  # one Llama-2-7B-shaped layer (config 3)
+        cfg = DecoderConfig(n_layers=args.n_layers or 1, d_model=4096, n_heads=32, n_kv_heads=32,
+                            head_dim=128, d_ff=11008, vocab=32000, rms_eps=1e-5,
+                            rope_theta=10000.0, serving="bfloat16", kv_dtype="bfloat16",
+                            max_seq=ctx_len + args.steps + args.warmup + 8, max_batch=B)
+        ranks = C3_RANKS
+    ctx = GpuContext.init_at(local_rank)
+    weights = random_model(cfg, ranks, seed=0, device_tables=True)
+    dec = Decoder(ctx, cfg, weights, tp_rank=rank, tp_size=world, group=group)
+    del weights
+    # the prompt's KV cache: synthetic N(0,1) rows stand in for a prefill pass
+    gen = torch.Generator(device="cuda").manual_seed(1 + rank)
+    for li in range(cfg.n_layers):
+        for cache in (dec.cache_k[li], dec.cache_v[li]):
+            cache[:, :, :ctx_len].copy_(torch.randn(cache[:, :, :ctx_len].shape, device="cuda",
+                                                    generator=gen).to(cache.dtype))
+    ids = torch.randint(0, cfg.vocab, (B,), generator=torch.Generator().manual_seed(2)).tolist()
+    dec.capture()
+    dec.start(ids, [ctx_len] * B)
+    launches0 = ctx.launch_count
+    dec.decode(max(args.warmup, 3))
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        dec.graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    if rank == 0:
+        per_step = ms / args.steps
+        print(json.dumps({
+            "metric": "decode_tok_s", "value": B / (per_step * 1e-3), "unit": "tok/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.model} shape, {cfg.n_layers} layers, all linears "
+                                   f"binary-factorized at ~0.55 bpw, greedy decode, batch {B}, "
+                                   f"context {ctx_len} (synthetic KV cache), one CUDA graph per step",
+                       "parallelism": f"tp{world}, NCCL all-reduce per attention block and per "
+                                      f"MLP block", "ranks": ranks}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -176,6 +254,11 @@ def main() -> None:
     ap.add_argument("--shape", default="", help="dout,din,rank override (debug; not the metric)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--e2e-applies", type=int, default=296)
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "decode"])
+    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "llama2-7b-layer"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--n-layers", type=int, default=0)
     args = ap.parse_args()
 
     if args.shape:
@@ -188,6 +271,9 @@ def main() -> None:
 
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "decode":
+        run_decode(args, rank, local_rank, world)
         return
 
     import torch

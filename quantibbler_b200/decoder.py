@@ -68,8 +68,10 @@ def random_layer(rng, dout, din, r, with_bias=False) -> dict:
                 bias=(rng.standard_normal(dout) * 0.01).astype(np.float32) if with_bias else None)
 
 
-def random_model(cfg: DecoderConfig, ranks: dict, seed: int = 0) -> dict:
-    """Random-init weights of the configured architecture (no checkpoint is involved)."""
+def random_model(cfg: DecoderConfig, ranks: dict, seed: int = 0, device_tables: bool = False) -> dict:
+    """Random-init weights of the configured architecture (no checkpoint is involved).
+    With ``device_tables`` the embedding and LM head are drawn on the GPU (bfloat16
+    N(0, 0.02)), which is what a 128k-entry vocabulary needs to stay quick."""
     rng = np.random.default_rng(seed)
     d, hd = cfg.d_model, cfg.head_dim
     shapes = {"q": (cfg.n_heads * hd, d), "k": (cfg.n_kv_heads * hd, d),
@@ -88,11 +90,17 @@ def random_model(cfg: DecoderConfig, ranks: dict, seed: int = 0) -> dict:
         u = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
         return u.astype(np.uint32).view(np.float32)
 
+    if device_tables:
+        import torch
+        gen = torch.Generator(device="cuda").manual_seed(seed)
+        emb = (torch.randn(cfg.vocab, d, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+        head = (torch.randn(cfg.vocab, d, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+    else:
+        emb = bf16_valued(rng.standard_normal((cfg.vocab, d)) * 0.02)
+        head = bf16_valued(rng.standard_normal((cfg.vocab, d)) * 0.02)
     return dict(layers=layers,
                 final_norm=(1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32),
-                embedding=bf16_valued(rng.standard_normal((cfg.vocab, d)) * 0.02),
-                lm_head=bf16_valued(rng.standard_normal((cfg.vocab, d)) * 0.02),
-                vocab_offset=0)
+                embedding=emb, lm_head=head, vocab_offset=0)
 
 
 def _p(t) -> ctypes.c_void_p:
@@ -120,9 +128,13 @@ class Decoder:
         i32 = dict(dtype=torch.int32, device=dev)
 
         def dev_f32(a):
+            if isinstance(a, torch.Tensor):
+                return a.to(dev, torch.float32).contiguous()
             return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dev)
 
         def dev_bf16(a):
+            if isinstance(a, torch.Tensor):
+                return a.to(dev, torch.bfloat16).contiguous()
             return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dev).to(
                 torch.bfloat16)
 

@@ -64,6 +64,7 @@ def shard_model(weights: dict, cfg, rank: int, size: int) -> dict:
             s[name] = shard_row_parallel(lw[name], rank, size)
         out["layers"].append(s)
     lo, hi = _range(cfg.vocab, rank, size)
-    out["lm_head"] = np.ascontiguousarray(weights["lm_head"][lo:hi])
+    head = weights["lm_head"][lo:hi]
+    out["lm_head"] = np.ascontiguousarray(head) if isinstance(head, np.ndarray) else head
     out["vocab_offset"] = lo
     return out
