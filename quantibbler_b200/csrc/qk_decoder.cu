@@ -263,29 +263,56 @@ __global__ void embed_kernel(const W *__restrict__ table, const int32_t *__restr
 }
 
 // logits[t][v] = sum_i hidden[t][i] * W[v][i], float32 accumulation.  One warp per vocab row,
-// the row is streamed once per tile of TT tokens (it stays in L2 between tiles).
+// 16-byte loads of the row (8 bfloat16 or 4 float32 per lane); the row is streamed once per
+// tile of TT tokens (it stays in L2 between tiles).  HBM-bound: the head is vocab*d values.
+template <typename W> struct HeadVec;
+template <> struct HeadVec<uint16_t> {
+    static constexpr int kN = 8;
+    __device__ static void load(const uint16_t *p, float (&w)[8]) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(p);
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            w[2 * i] = __uint_as_float(u[i] << 16);
+            w[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+        }
+    }
+};
+template <> struct HeadVec<float> {
+    static constexpr int kN = 4;
+    __device__ static void load(const float *p, float (&w)[4]) {
+        const float4 v = *reinterpret_cast<const float4 *>(p);
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+    }
+};
+
 template <typename W, int TT>
 __global__ void __launch_bounds__(256)
 lm_head_kernel(const float *__restrict__ hidden, const W *__restrict__ weight,
                float *__restrict__ logits, uint32_t n_tokens, uint32_t vocab, uint32_t d,
                uint32_t vocab_stride) {
+    constexpr int N = HeadVec<W>::kN;
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t v = blockIdx.x * 8 + warp;
     if (v >= vocab) return;
+    const W *row = weight + (size_t)v * d;
     for (uint32_t t0 = 0; t0 < n_tokens; t0 += TT) {
         float acc[TT];
 #pragma unroll
         for (int t = 0; t < TT; ++t) acc[t] = 0.f;
-        for (uint32_t i = lane * 4; i < d; i += 128) {
-            float w0 = load_as_float<W>(weight, (size_t)v * d + i);
-            float w1 = load_as_float<W>(weight, (size_t)v * d + i + 1);
-            float w2 = load_as_float<W>(weight, (size_t)v * d + i + 2);
-            float w3 = load_as_float<W>(weight, (size_t)v * d + i + 3);
+        for (uint32_t i = lane * N; i < d; i += 32 * N) {
+            float w[N];
+            HeadVec<W>::load(row + i, w);
 #pragma unroll
             for (int t = 0; t < TT; ++t) {
                 if (t0 + t < n_tokens) {
-                    const float4 h = *reinterpret_cast<const float4 *>(hidden + (size_t)(t0 + t) * d + i);
-                    acc[t] = fmaf(h.x, w0, fmaf(h.y, w1, fmaf(h.z, w2, fmaf(h.w, w3, acc[t]))));
+                    const float *h = hidden + (size_t)(t0 + t) * d + i;
+#pragma unroll
+                    for (int e = 0; e < N; e += 4) {
+                        const float4 hv = *reinterpret_cast<const float4 *>(h + e);
+                        acc[t] = fmaf(hv.x, w[e], fmaf(hv.y, w[e + 1],
+                                 fmaf(hv.z, w[e + 2], fmaf(hv.w, w[e + 3], acc[t]))));
+                    }
                 }
             }
         }
@@ -488,7 +515,7 @@ qk_status qk_lm_head(qk_ctx *ctx, const float *hidden, const void *weight, int32
     qk_ctx *c;
     qk_status st = enter(ctx, &c);
     if (st != QK_OK) return st;
-    if (d % 4) return qk::fail(QK_ERR_VALUE, "d_model must be a multiple of 4, got %zu", d);
+    if (d % 8) return qk::fail(QK_ERR_VALUE, "d_model must be a multiple of 8, got %zu", d);
     if (n_tokens == 0 || vocab == 0) return QK_OK;
     const unsigned blocks = (unsigned)qk::ceil_div(vocab, 8);
     if (weight_dtype == QK_F32) {

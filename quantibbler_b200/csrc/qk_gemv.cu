@@ -334,6 +334,31 @@ digit_table_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32
     build_record(q8, ip, reinterpret_cast<uint4 *>(p.digits + ((size_t)ks * 64 + rec) * 8));
 }
 
+// Starts this warp's first kStages-1 chunks of a stage (item i of a warp goes to ring slot
+// i % kStages; here the items are the contiguous chunks of the warp's row groups).
+__device__ __forceinline__ void ring_prologue(const StageParams &p, uint8_t *ring_smem,
+                                              uint32_t n_groups, uint32_t n_steps,
+                                              uint32_t block_in_instance,
+                                              uint32_t groups_per_warp) {
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t group_begin =
+        min(n_groups, (block_in_instance * (blockDim.x / 32) + warp) * groups_per_warp);
+    const uint32_t group_end = min(n_groups, group_begin + groups_per_warp);
+    const uint32_t n_items = (group_end - group_begin) * n_steps;
+    uint4 *ring = reinterpret_cast<uint4 *>(ring_smem + (size_t)warp * kStages * kChunkBytes) + lane;
+    const uint4 *src = reinterpret_cast<const uint4 *>(p.w_tiles) + lane;
+#pragma unroll
+    for (int i = 0; i < kStages - 1; ++i) {
+        if ((uint32_t)i < n_items) {
+            uint4 *dst = ring + (size_t)i * (kChunkBytes / 16);
+            const uint4 *from = src + (size_t)(group_begin * n_steps + i) * (kChunkBytes / 16);
+#pragma unroll
+            for (int piece = 0; piece < 8; ++piece) cp_async16(dst + piece * 32, from + piece * 32);
+        }
+        cp_async_commit();
+    }
+}
+
 // out[row] = epilogue((2 * sum_{bit=1} q_k - sum q_k) * 2^-shift).
 //   kFinal = false: writes the float64 intermediate t;  true: y = float(u)*s1 + bias.
 //   kSmemDigits: the block builds the instance's digit table in shared memory itself,
@@ -351,38 +376,18 @@ digit_table_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32
 // table_smem: the digit table (kSmemDigits); ring_smem: warps x kStages x 4 KB.
 // prologue_issued: the caller already started this warp's first kStages-1 chunks with
 // ring_prologue (the fused kernel does so before the stage boundary barrier).
-__device__ __forceinline__ void ring_issue(uint4 *ring, const uint4 *src, uint32_t c,
-                                           uint32_t c_end) {
-    if (c < c_end) {
-        uint4 *dst = ring + (size_t)(c % kStages) * (kChunkBytes / 16);
-        const uint4 *from = src + (size_t)c * (kChunkBytes / 16);
-#pragma unroll
-        for (int piece = 0; piece < 8; ++piece) cp_async16(dst + piece * 32, from + piece * 32);
-    }
-    cp_async_commit();  // an empty group keeps the group count in step with c
-}
-
-__device__ __forceinline__ void ring_prologue(const StageParams &p, uint8_t *ring_smem,
-                                              uint32_t n_groups, uint32_t n_steps,
-                                              uint32_t block_in_instance,
-                                              uint32_t groups_per_warp) {
-    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const uint32_t group_begin =
-        min(n_groups, (block_in_instance * (blockDim.x / 32) + warp) * groups_per_warp);
-    const uint32_t group_end = min(n_groups, group_begin + groups_per_warp);
-    uint4 *ring = reinterpret_cast<uint4 *>(ring_smem + (size_t)warp * kStages * kChunkBytes) + lane;
-    const uint4 *src = reinterpret_cast<const uint4 *>(p.w_tiles) + lane;
-#pragma unroll
-    for (int s = 0; s < kStages - 1; ++s)
-        ring_issue(ring, src, group_begin * n_steps + s, group_end * n_steps);
-}
-
-template <bool kRoundBf16, bool kFinal, bool kSmemDigits, bool kInSmem, bool kOutSmem>
+// kSplitK: the block owns ONE row group (block_in_instance is the group) and its warps
+// share the group's k-steps (warp w takes k-steps w, w+W, ...); the partial int32 sums are
+// added through red_smem ([warps][16][32] ints) and warps 0..3 finish one 16-row tile each.
+// This is the low-latency form for a single small layer: every chunk of the factor is in
+// flight at once instead of eight per warp in sequence.
+template <bool kRoundBf16, bool kFinal, bool kSmemDigits, bool kInSmem, bool kOutSmem,
+          bool kSplitK = false>
 __device__ __forceinline__ void
 bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
                const double *in_smem, double *out_smem, uint32_t n_rows, uint32_t n_bits,
                uint32_t n_groups, uint32_t n_steps, uint32_t block_in_instance,
-               uint32_t groups_per_warp, bool prologue_issued) {
+               uint32_t groups_per_warp, bool prologue_issued, int *red_smem = nullptr) {
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t warps_per_block = blockDim.x / 32;
     const uint32_t g = lane / 4, t = lane % 4;
@@ -391,16 +396,32 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
         return load_input<kFinal, kRoundBf16>(p, k, n_bits);
     };
     const uint32_t group_begin =
-        min(n_groups, (block_in_instance * warps_per_block + warp) * groups_per_warp);
-    const uint32_t group_end = min(n_groups, group_begin + groups_per_warp);
-    const uint32_t c_begin = group_begin * n_steps, c_end = group_end * n_steps;
+        kSplitK ? block_in_instance
+                : min(n_groups, (block_in_instance * warps_per_block + warp) * groups_per_warp);
+    const uint32_t group_end = kSplitK ? group_begin + 1 : min(n_groups, group_begin + groups_per_warp);
+    // the chunks this warp consumes, as items 0..n_items-1
+    const uint32_t n_items =
+        kSplitK ? (warp < n_steps ? (n_steps - warp + warps_per_block - 1) / warps_per_block : 0)
+                : (group_end - group_begin) * n_steps;
+    auto chunk_of = [&](uint32_t i) -> uint32_t {
+        return kSplitK ? group_begin * n_steps + warp + i * warps_per_block
+                       : group_begin * n_steps + i;
+    };
 
     uint4 *ring = reinterpret_cast<uint4 *>(ring_smem + (size_t)warp * kStages * kChunkBytes) + lane;
     const uint4 *src = reinterpret_cast<const uint4 *>(p.w_tiles) + lane;
-    auto issue = [&](uint32_t c) { ring_issue(ring, src, c, c_end); };
+    auto issue = [&](uint32_t i) {  // item i goes to ring slot i % kStages
+        if (i < n_items) {
+            uint4 *dst = ring + (size_t)(i % kStages) * (kChunkBytes / 16);
+            const uint4 *from = src + (size_t)chunk_of(i) * (kChunkBytes / 16);
+#pragma unroll
+            for (int piece = 0; piece < 8; ++piece) cp_async16(dst + piece * 32, from + piece * 32);
+        }
+        cp_async_commit();  // an empty group keeps the group count in step with i
+    };
     if (!prologue_issued) {
 #pragma unroll
-        for (int s = 0; s < kStages - 1; ++s) issue(c_begin + s);
+        for (int s = 0; s < kStages - 1; ++s) issue(s);
     }
     // ---- the digit table of this instance (the weight ring is already filling)
     __shared__ double red_max[16];
@@ -495,11 +516,43 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
     const bool odirect = oexp > -1000 && oexp < 1000;
     const double oscale = odirect ? __hiloint2double((1023 + oexp) << 20, 0) : 0.0;
 
-    uint32_t ks = 0, group = group_begin;
-    for (uint32_t c = c_begin; c < c_end; ++c) {
-        issue(c + kStages - 1);          // refills the slot consumed one iteration ago
-        cp_async_wait<kStages - 1>();    // this lane's pieces of chunk c have landed
-        const uint4 *stage = ring + (size_t)(c % kStages) * (kChunkBytes / 16);
+    // Exact recombination of one 16-row tile.  Lane (g,t) holds digit columns 2t and 2t+1
+    // of rows g (a[0..1]) and g+8 (a[2..3]).  With X = sum_n c_n 256^n = 128 * S and
+    // T = sum q_k, the row's value is (X - 64 T) / 64 * 2^-shift.  X is kept as
+    // hi * 2^32 + lo (digits 4..7 and 0..3) and 64 T as th * 2^32 + tl, so the subtraction
+    // is exact in int64 and only the last conversion rounds.
+    auto finish_tile = [&](const int (&a)[4], uint32_t group, int m) {
+        long long pg = ((long long)a[0] << sh0) + ((long long)a[1] << (sh0 + 8));
+        long long ph = ((long long)a[2] << sh0) + ((long long)a[3] << (sh0 + 8));
+        pg += __shfl_xor_sync(0xffffffffu, pg, 1);  // t=0,1: low half; t=2,3: high half
+        ph += __shfl_xor_sync(0xffffffffu, ph, 1);
+        const long long og = __shfl_xor_sync(0xffffffffu, pg, 2);
+        const long long oh = __shfl_xor_sync(0xffffffffu, ph, 2);
+        const uint32_t row = group * kGroupRows + m * kTileRows + g + 8 * t;
+        if (t < 2 && row < n_rows) {
+            const long long lo = t == 0 ? pg : ph, hi = t == 0 ? og : oh;
+            double val = (double)(hi - th) * 4294967296.0 + (double)(lo - tl);
+            val = odirect ? val * oscale : ldexp(val, oexp);
+            if (meta.nonfinite) val = nan("");
+            if (kRoundBf16) val = (double)round_bf16((float)val);
+            if (kOutSmem) {
+                out_smem[row] = val;
+            } else if (kFinal) {
+                float y = (float)val;
+                if (p.out_scale) y = y * p.out_scale[row];
+                if (p.out_bias) y = y + p.out_bias[row];
+                static_cast<float *>(p.out)[row] = y;
+            } else {
+                static_cast<double *>(p.out)[row] = val;
+            }
+        }
+    };
+
+    uint32_t ks = kSplitK ? warp : 0, group = group_begin;
+    for (uint32_t i = 0; i < n_items; ++i) {
+        issue(i + kStages - 1);          // refills the slot consumed one iteration ago
+        cp_async_wait<kStages - 1>();    // this lane's pieces of item i have landed
+        const uint4 *stage = ring + (size_t)(i % kStages) * (kChunkBytes / 16);
         uint4 cur[kTilesPerWarp][2];
 #pragma unroll
         for (int m = 0; m < kTilesPerWarp; ++m) {
@@ -523,43 +576,34 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
                 }
             }
         }
+        if (kSplitK) {
+            ks += warps_per_block;
+            continue;
+        }
         if (++ks < n_steps) continue;
         ks = 0;
         // ---- the group's 64 rows are complete
-        // Exact recombination.  Lane (g,t) holds digit columns 2t and 2t+1 of rows g
-        // (acc[.][0..1]) and g+8 (acc[.][2..3]).  With X = sum_n c_n 256^n = 128 * S and
-        // T = sum q_k, the row's value is (X - 64 T) / 64 * 2^-shift.  X is kept as
-        // hi * 2^32 + lo (digits 4..7 and 0..3) and 64 T as th * 2^32 + tl, so the
-        // subtraction is exact in int64 and only the last conversion rounds.
 #pragma unroll
         for (int m = 0; m < kTilesPerWarp; ++m) {
-            long long pg = ((long long)acc[m][0] << sh0) + ((long long)acc[m][1] << (sh0 + 8));
-            long long ph = ((long long)acc[m][2] << sh0) + ((long long)acc[m][3] << (sh0 + 8));
-            pg += __shfl_xor_sync(0xffffffffu, pg, 1);  // t=0,1: low half; t=2,3: high half
-            ph += __shfl_xor_sync(0xffffffffu, ph, 1);
-            const long long og = __shfl_xor_sync(0xffffffffu, pg, 2);
-            const long long oh = __shfl_xor_sync(0xffffffffu, ph, 2);
+            finish_tile(acc[m], group, m);
             acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0;
-            const uint32_t row = group * kGroupRows + m * kTileRows + g + 8 * t;
-            if (t < 2 && row < n_rows) {
-                const long long lo = t == 0 ? pg : ph, hi = t == 0 ? og : oh;
-                double val = (double)(hi - th) * 4294967296.0 + (double)(lo - tl);
-                val = odirect ? val * oscale : ldexp(val, oexp);
-                if (meta.nonfinite) val = nan("");
-                if (kRoundBf16) val = (double)round_bf16((float)val);
-                if (kOutSmem) {
-                    out_smem[row] = val;
-                } else if (kFinal) {
-                    float y = (float)val;
-                    if (p.out_scale) y = y * p.out_scale[row];
-                    if (p.out_bias) y = y + p.out_bias[row];
-                    static_cast<float *>(p.out)[row] = y;
-                } else {
-                    static_cast<double *>(p.out)[row] = val;
-                }
-            }
         }
         ++group;
+    }
+    if (kSplitK) {
+        // add the warps' partial sums (integers: the order does not matter)
+#pragma unroll
+        for (int m = 0; m < kTilesPerWarp; ++m)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) red_smem[(warp * 16 + m * 4 + e) * 32 + lane] = acc[m][e];
+        __syncthreads();
+        if (warp < kTilesPerWarp) {
+            int sum[4] = {0, 0, 0, 0};
+            for (uint32_t w = 0; w < warps_per_block; ++w)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sum[e] += red_smem[(w * 16 + warp * 4 + e) * 32 + lane];
+            finish_tile(sum, group_begin, (int)warp);
+        }
     }
     cp_async_wait<0>();
 }
@@ -576,6 +620,21 @@ gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint
     bitslice_stage<kRoundBf16, kFinal, kSmemDigits, false, false>(
         p, smem_dyn, ring, nullptr, nullptr, n_rows, n_bits, n_groups, n_steps, blockIdx.x,
         groups_per_warp, false);
+}
+
+// Low-latency form for few instances: one block per (row group, instance), the block's
+// warps share the group's k-steps.  smem: [digit table][ring][reduction buffer].
+template <bool kRoundBf16, bool kFinal>
+__global__ void __launch_bounds__(256)
+gemv_bitslice_splitk_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint32_t n_bits,
+                            uint32_t n_groups, uint32_t n_steps) {
+    extern __shared__ __align__(16) uint8_t smem_dyn[];
+    const StageParams p = many[blockIdx.y];
+    uint8_t *ring = smem_dyn + (size_t)n_steps * 4096;
+    int *red = reinterpret_cast<int *>(ring + (size_t)(blockDim.x / 32) * kStages * kChunkBytes);
+    bitslice_stage<kRoundBf16, kFinal, true, false, false, true>(
+        p, smem_dyn, ring, nullptr, nullptr, n_rows, n_bits, n_groups, n_steps, blockIdx.x, 1, false,
+        red);
 }
 
 // Both stages of one layer instance in one block: t = Vb^T z stays in shared memory as
@@ -712,6 +771,24 @@ template <bool kFinal>
 qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, const StageShape &s,
                           bool bf16) {
     const StagePlan pl = plan_stage(c, s, n_inst);
+    // Few instances: the streaming form would leave most SMs idle and make each warp walk
+    // its chunks in sequence.  Give every row group a block whose warps split the k-steps.
+    size_t sk_warps = s.n_steps < 4 ? 4 : s.n_steps > 8 ? 8 : s.n_steps;
+    const size_t sk_smem = s.n_steps * 4096 + sk_warps * kRingPerWarp + sk_warps * 16 * 32 * 4;
+    if (c->gemv_kernel != 3 && pl.smem_digits && sk_smem <= kSmemBudget &&
+        n_inst * pl.blocks < (size_t)c->sm_count && s.n_groups <= 65535) {
+        dim3 grid((unsigned)s.n_groups, (unsigned)n_inst);
+        auto gemv = bf16 ? gemv_bitslice_splitk_kernel<true, kFinal>
+                         : gemv_bitslice_splitk_kernel<false, kFinal>;
+        QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)kSmemBudget));
+        gemv<<<grid, (unsigned)sk_warps * 32, sk_smem, c->stream>>>(
+            many, (uint32_t)s.n_rows, (uint32_t)s.n_bits, (uint32_t)s.n_groups,
+            (uint32_t)s.n_steps);
+        QK_CUDA(cudaGetLastError());
+        c->launches++;
+        return QK_OK;
+    }
     if (!pl.smem_digits) {
         // too wide for shared memory: the table is made in global memory first
         auto table = kFinal ? (bf16 ? digit_table_kernel<true, true> : digit_table_kernel<true, false>)
