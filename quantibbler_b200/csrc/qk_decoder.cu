@@ -220,20 +220,28 @@ decode_attention_kernel(const float *__restrict__ q, const KV *__restrict__ cach
 __global__ void __launch_bounds__(128)
 decode_combine_kernel(const float *__restrict__ partial, float *__restrict__ out, uint32_t d,
                       uint32_t n_splits) {
+    __shared__ float wgt[128];  // exp(m_s - m) / l per split (n_splits <= 128)
+    __shared__ float red[4];
     const float *p = partial + (size_t)blockIdx.x * n_splits * (d + 2);
-    float mm = -INFINITY;
-    for (uint32_t s = 0; s < n_splits; ++s) mm = fmaxf(mm, p[s * (d + 2)]);
-    float ll = 0.f;
-    for (uint32_t s = 0; s < n_splits; ++s) {
-        float ms = p[s * (d + 2)];
-        ll += ms == -INFINITY ? 0.f : p[s * (d + 2) + 1] * expf(ms - mm);
-    }
-    for (uint32_t c = threadIdx.x; c < d; c += blockDim.x) {
+    const uint32_t tid = threadIdx.x;
+    float ms = tid < n_splits ? p[tid * (d + 2)] : -INFINITY;
+    float ls = tid < n_splits ? p[tid * (d + 2) + 1] : 0.f;
+    float mm = ms;
+    for (int off = 16; off > 0; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
+    if (tid % 32 == 0) red[tid / 32] = mm;
+    __syncthreads();
+    mm = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    __syncthreads();
+    const float w = ms == -INFINITY ? 0.f : expf(ms - mm);
+    float ll = ls * w;
+    for (int off = 16; off > 0; off >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, off);
+    if (tid % 32 == 0) red[tid / 32] = ll;
+    wgt[tid] = w;
+    __syncthreads();
+    ll = red[0] + red[1] + red[2] + red[3];
+    for (uint32_t c = tid; c < d; c += blockDim.x) {
         float oo = 0.f;
-        for (uint32_t s = 0; s < n_splits; ++s) {
-            float ms = p[s * (d + 2)];
-            if (ms != -INFINITY) oo += p[s * (d + 2) + 2 + c] * expf(ms - mm);
-        }
+        for (uint32_t s = 0; s < n_splits; ++s) oo += p[s * (d + 2) + 2 + c] * wgt[s];
         out[(size_t)blockIdx.x * d + c] = oo / ll;
     }
 }
@@ -325,24 +333,13 @@ lm_head_kernel(const float *__restrict__ hidden, const W *__restrict__ weight,
     }
 }
 
-// First maximum of each row (sampler.rs:5-16: a later equal value does not win).
-// out_val/out_idx per token; idx is offset by `index_base` (for vocabulary shards).
-__global__ void __launch_bounds__(256)
-argmax_first_kernel(const float *__restrict__ logits, uint32_t vocab, uint32_t stride,
-                    int32_t index_base, float *__restrict__ out_val, int32_t *__restrict__ out_idx) {
+// First maximum of each row (sampler.rs:5-16: a later equal value does not win), in two
+// steps: grid (parts, tokens) blocks each reduce a slice to a (value, index) pair, then one
+// block per token reduces the pairs.  idx is offset by `index_base` (vocabulary shards).
+__device__ __forceinline__ void argmax_block_reduce(float best, int bi, float *out_val,
+                                                    int32_t *out_idx, int32_t offset) {
     __shared__ float sv[256];
     __shared__ int si[256];
-    const float *row = logits + (size_t)blockIdx.x * stride;
-    float best = -INFINITY;
-    int bi = 0x7fffffff;
-    for (uint32_t i = threadIdx.x; i < vocab; i += blockDim.x) {
-        float v = row[i];
-        if (v > best || (v == best && (int)i < bi)) {
-            best = v;
-            bi = (int)i;
-        }
-    }
-    if (bi == 0x7fffffff) bi = 0;  // all NaN or -inf: the reference returns index 0
     sv[threadIdx.x] = best;
     si[threadIdx.x] = bi;
     __syncthreads();
@@ -358,9 +355,44 @@ argmax_first_kernel(const float *__restrict__ logits, uint32_t vocab, uint32_t s
         __syncthreads();
     }
     if (threadIdx.x == 0) {
-        out_val[blockIdx.x] = sv[0];
-        out_idx[blockIdx.x] = si[0] + index_base;
+        *out_val = sv[0];
+        *out_idx = (si[0] == 0x7fffffff ? 0 : si[0]) + offset;  // nothing finite: index 0
     }
+}
+
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float *__restrict__ logits, uint32_t vocab, uint32_t stride,
+                      uint32_t slice, float *__restrict__ part_val, int32_t *__restrict__ part_idx) {
+    const float *row = logits + (size_t)blockIdx.y * stride;
+    const uint32_t lo = blockIdx.x * slice, hi = min(vocab, lo + slice);
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (uint32_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        float v = row[i];
+        if (v > best || (v == best && (int)i < bi)) {
+            best = v;
+            bi = (int)i;
+        }
+    }
+    const size_t o = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+    argmax_block_reduce(best, bi, part_val + o, part_idx + o, 0);
+}
+
+__global__ void __launch_bounds__(256)
+argmax_final_kernel(const float *__restrict__ part_val, const int32_t *__restrict__ part_idx,
+                    uint32_t parts, int32_t index_base, float *__restrict__ out_val,
+                    int32_t *__restrict__ out_idx) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (uint32_t i = threadIdx.x; i < parts; i += blockDim.x) {
+        float v = part_val[(size_t)blockIdx.x * parts + i];
+        int idx = part_idx[(size_t)blockIdx.x * parts + i];
+        if (v > best || (v == best && idx < bi)) {
+            best = v;
+            bi = idx;
+        }
+    }
+    argmax_block_reduce(best, bi, out_val + blockIdx.x, out_idx + blockIdx.x, index_base);
 }
 
 qk_status enter(qk_ctx *ctx, qk_ctx **c) {
@@ -435,6 +467,8 @@ qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
     if (head_dim > 256)
         return qk::fail(QK_ERR_VALUE, "head_dim above 256 is not supported, got %zu", head_dim);
     if (n_splits == 0 || batch == 0) return qk::fail(QK_ERR_VALUE, "empty decode attention");
+    if (n_splits > 128)
+        return qk::fail(QK_ERR_VALUE, "at most 128 key splits are supported, got %zu", n_splits);
     if (kv_dtype != QK_F32 && kv_dtype != QK_BF16)
         return qk::fail(QK_ERR_VALUE, "KV cache dtype must be float32 or bfloat16, got tag %d",
                         kv_dtype);
@@ -550,8 +584,21 @@ qk_status qk_argmax_first(qk_ctx *ctx, const float *logits, size_t n_tokens, siz
     qk_status st = enter(ctx, &c);
     if (st != QK_OK) return st;
     if (n_tokens == 0) return QK_OK;
-    argmax_first_kernel<<<(unsigned)n_tokens, 256, 0, c->stream>>>(
-        logits, (uint32_t)vocab, (uint32_t)logits_stride, index_base, out_val, out_idx);
+    // partial results live in the context's scratch; it is sized on the first call, so make
+    // that call before any stream capture
+    const size_t parts = vocab >= 65536 ? 64 : vocab >= 4096 ? 16 : 1;
+    const size_t slice = qk::ceil_div(vocab, parts);
+    if ((st = c->d_z.reserve(n_tokens * parts * 8)) != QK_OK) return st;
+    float *part_val = (float *)c->d_z.ptr;
+    int32_t *part_idx = (int32_t *)(part_val + n_tokens * parts);
+    dim3 grid((unsigned)parts, (unsigned)n_tokens);
+    argmax_partial_kernel<<<grid, 256, 0, c->stream>>>(logits, (uint32_t)vocab,
+                                                       (uint32_t)logits_stride, (uint32_t)slice,
+                                                       part_val, part_idx);
+    QK_CUDA(cudaGetLastError());
+    c->launches++;
+    argmax_final_kernel<<<(unsigned)n_tokens, 256, 0, c->stream>>>(
+        part_val, part_idx, (uint32_t)parts, index_base, out_val, out_idx);
     QK_LAUNCHED(c);
 }
 

@@ -625,7 +625,7 @@ gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint
 // Low-latency form for few instances: one block per (row group, instance), the block's
 // warps share the group's k-steps.  smem: [digit table][ring][reduction buffer].
 template <bool kRoundBf16, bool kFinal>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 gemv_bitslice_splitk_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint32_t n_bits,
                             uint32_t n_groups, uint32_t n_steps) {
     extern __shared__ __align__(16) uint8_t smem_dyn[];
@@ -773,8 +773,10 @@ qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, con
     const StagePlan pl = plan_stage(c, s, n_inst);
     // Few instances: the streaming form would leave most SMs idle and make each warp walk
     // its chunks in sequence.  Give every row group a block whose warps split the k-steps.
-    size_t sk_warps = s.n_steps < 4 ? 4 : s.n_steps > 8 ? 8 : s.n_steps;
-    const size_t sk_smem = s.n_steps * 4096 + sk_warps * kRingPerWarp + sk_warps * 16 * 32 * 4;
+    size_t sk_warps = s.n_steps < 4 ? 4 : s.n_steps > 16 ? 16 : s.n_steps;
+    auto sk_bytes = [&](size_t w) { return s.n_steps * 4096 + w * kRingPerWarp + w * 16 * 32 * 4; };
+    while (sk_warps > 4 && sk_bytes(sk_warps) > kSmemBudget) --sk_warps;
+    const size_t sk_smem = sk_bytes(sk_warps);
     if (c->gemv_kernel != 3 && pl.smem_digits && sk_smem <= kSmemBudget &&
         n_inst * pl.blocks < (size_t)c->sm_count && s.n_groups <= 65535) {
         dim3 grid((unsigned)s.n_groups, (unsigned)n_inst);

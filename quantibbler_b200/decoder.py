@@ -161,7 +161,9 @@ class Decoder:
                         for _ in range(cfg.n_layers)]
         self.cache_v = [torch.zeros(B, self.kv_loc, cfg.max_seq, hd, dtype=kv_t, device=dev)
                         for _ in range(cfg.n_layers)]
-        self.n_splits = cfg.n_splits or max(1, min(64, (4 * 148) // max(1, B * self.kv_loc)))
+        # enough blocks to cover the SMs about twice, but chunks of at least ~128 keys
+        self.n_splits = cfg.n_splits or max(1, min(32, (2 * 148) // max(1, B * self.kv_loc),
+                                                   max(1, cfg.max_seq // 128)))
         scratch = _lib.lib().qk_decode_attention_scratch(B, self.h_loc, hd, self.n_splits)
         self.att_scratch = torch.zeros(scratch // 4 + 4, **f32)
         self.cos_sin = dev_f32(rope_table(cfg))
