@@ -238,9 +238,14 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
                                    f"binary-factorized at ~0.55 bpw, greedy decode, batch {B}, "
                                    f"context {ctx_len} (synthetic KV cache), one CUDA graph per step",
                        "parallelism": f"tp{world}, NCCL all-reduce per attention block and per "
-                                      f"MLP block", "ranks": ranks}}))
+                                      f"MLP block", "ranks": ranks}}), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # A captured graph still holds NCCL kernels; tearing the communicator down under it
+        # can block at exit.  Everything is measured and printed: leave without the teardown.
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def main() -> None:
