@@ -37,6 +37,9 @@ DOUT = DIN = 4096
 RANK = 1024
 # bits of both factors + s1,s2 + x + y, float32 vectors
 BYTES_PER_APPLY = (DOUT * RANK + DIN * RANK) // 8 + 4 * (DOUT + DIN) + 4 * DIN + 4 * DOUT
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused-kernel launch over 296 layers
+# (profiles/layer_bitslice_fused_kernel_config0_stack296.md): 330.915 MB, i.e. per layer
+DRAM_TRAFFIC_PER_APPLY = 330.915e6 / 296
 METRIC = "factorized_gemv_hbm_gbs"
 UNIT = "GB/s"
 
@@ -380,8 +383,13 @@ def main() -> None:
                                     f"streamed per step",
                        "parallelism": f"independent layer stacks x{world}, no collective"},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": UNIT,
-                         "frac": per_gpu / peak, "traffic": None, "peak_source": peak_src,
-                         "kernel": "gemv stage kernel, 2 launches per step, average"},
+                         "frac": per_gpu / peak,
+                         "traffic": (DRAM_TRAFFIC_PER_APPLY * L
+                                     if (DOUT, DIN, RANK) == (4096, 4096, 1024) else None),
+                         "traffic_note": "bytes per launch, scaled by layers from an ncu capture "
+                                         "of a 296-layer launch",
+                         "peak_source": peak_src,
+                         "kernel": "layer_bitslice_fused_kernel, one launch per step"},
             "e2e": {"value": (world * n_e2e * BYTES_PER_APPLY / e2e_s / 1e9) if n_e2e else None,
                     "unit": UNIT,
                     "h2d_bytes_per_step": n_e2e * DIN * 4, "d2h_bytes_per_step": n_e2e * DOUT * 4,

@@ -169,6 +169,13 @@ void qk_layer_free(qk_layer *layer);
  * Asynchronous on the context's stream. */
 qk_status qk_layer_apply(qk_ctx *ctx, const qk_layer *layer, const float *x_dev, size_t n_tokens,
                          float *y_dev);
+/* Prefill: n_tokens at once through one bfloat16-serving layer on the tcgen05 tensor
+ * cores (core.rs:288-317 packed_matmul under the contract of engine/mod.rs:449-460: z, t
+ * and u each rounded once to bfloat16, float32 accumulation).  x_dev [n_tokens, din] and
+ * y_dev [n_tokens, dout] are float32 device buffers.  The call returns when y is complete;
+ * QK_ERR_TIMEOUT means a bounded in-kernel wait expired. */
+qk_status qk_layer_apply_prefill(qk_ctx *ctx, const qk_layer *layer, const float *x_dev,
+                                 size_t n_tokens, float *y_dev);
 /* One token through one layer without any allocation by the library.  It has no
  * counterpart in the reference.  For callers that cannot let a library allocate device
  * memory on their behalf: a server that gave all remaining device memory to its KV cache

@@ -230,6 +230,11 @@ class PackedLayer:
                                              y.ctypes.data, y.size))
         return y
 
+    def apply_prefill(self, x_ptr: int, n_tokens: int, y_ptr: int) -> None:
+        """Many tokens at once on the tensor cores (bfloat16 serving only); blocks until done."""
+        check(_lib.lib().qk_layer_apply_prefill(self.ctx.handle, self._h, ctypes.c_void_p(x_ptr),
+                                                int(n_tokens), ctypes.c_void_p(y_ptr)))
+
     def apply_device(self, x_ptr: int, n_tokens: int, y_ptr: int) -> None:
         """Asynchronous apply on device buffers (float32, row-major tokens)."""
         check(_lib.lib().qk_layer_apply(self.ctx.handle, self._h, ctypes.c_void_p(x_ptr),
