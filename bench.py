@@ -251,6 +251,56 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
         os._exit(0)
 
 
+def run_prefill(args, local_rank: int) -> None:
+    """BASELINE config 1: the three MLP linears of a Llama-3-8B block on 2048 tokens, bfloat16
+    activations, tensor-core prefill GEMM.  Reports dense-equivalent TFLOP/s."""
+    import torch
+
+    from quantibbler_b200.decoder import random_layer
+    from quantibbler_b200.gpu import GpuContext, PackedLayer
+
+    torch.cuda.set_device(local_rank)
+    ctx = GpuContext.init_at(local_rank)
+    T, r = args.tokens, 2560
+    rng = np.random.default_rng(0)
+    shapes = [("gate", 14336, 4096), ("up", 14336, 4096), ("down", 4096, 14336)]
+    layers, bufs, flop = [], [], 0.0
+    for name, dout, din in shapes:
+        w = random_layer(rng, dout, din, r)
+        layers.append(PackedLayer(ctx, w["ub_rows"], w["vb_t_rows"], dout, din, r, w["s1"], w["s2"],
+                                  None, serving="bfloat16", name=name))
+        x = torch.randn(T, din, device="cuda").to(torch.bfloat16).float()
+        y = torch.zeros(T, dout, device="cuda")
+        bufs.append((x, y))
+        flop += 2.0 * T * r * (din + dout)
+    torch.cuda.synchronize()
+
+    def step():
+        for layer, (x, y) in zip(layers, bufs):
+            layer.apply_prefill(x.data_ptr(), T, y.data_ptr())
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = json.load(open(peaks_path))["bf16_tflops"] if os.path.exists(peaks_path) else 1590.0
+    tf = flop / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "prefill_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"config1: gate, up 4096->14336 and down 14336->4096, r=2560, "
+                               f"{T} tokens, bf16 operands, f32 accumulate; host-timed, each "
+                               f"layer call blocks until its result is complete"},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s",
+                     "frac": tf / peak, "traffic": None}}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -262,7 +312,8 @@ def main() -> None:
     ap.add_argument("--shape", default="", help="dout,din,rank override (debug; not the metric)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--e2e-applies", type=int, default=296)
-    ap.add_argument("--workload", default="gemv", choices=["gemv", "decode"])
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "decode", "prefill"])
+    ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "llama2-7b-layer"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--context", type=int, default=2048)
@@ -282,6 +333,10 @@ def main() -> None:
         return
     if args.workload == "decode":
         run_decode(args, rank, local_rank, world)
+        return
+    if args.workload == "prefill":
+        if rank == 0:
+            run_prefill(args, local_rank)
         return
 
     import torch

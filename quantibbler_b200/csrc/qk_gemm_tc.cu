@@ -8,32 +8,40 @@
 // float32 accumulation, z, t and u each rounded once to bfloat16.
 //
 // tcgen05 has no 1-bit x bf16 mode, so the +-1 weights are expanded to bfloat16 on the fly:
-//   * the activation tile (128 tokens x 64 k) is copied to shared memory in the
-//     128-byte-swizzled K-major layout the UMMA descriptors expect;
-//   * producer threads read 64 weight bits per row and write the matching 64 bfloat16
-//     +-1 values (eight 16-byte pieces from a 256-entry byte -> 8 x bf16 table) into the
-//     same swizzled layout: 256 weight rows x 64 k = 32 KB per stage from 2 KB of bits;
-//   * one elected thread issues tcgen05.mma (M = 128 tokens, N = 256 weight rows, K = 16
-//     per instruction, four per stage) with the float32 accumulator in tensor memory
-//     (256 columns), and tcgen05.commit releases the stage to the producers;
-//   * the epilogue reads the accumulator with tcgen05.ld (one token row per thread),
-//     applies the stage's rounding / scale / bias and stores.
+// The weights take the M side of the MMA (128 weight rows per tile) and the tokens the N
+// side (up to 256 tokens), so that the costly operand - the one that has to be expanded -
+// is the narrow one:
+//   * the activation tile (up to 256 tokens x 64 k) is brought to shared memory by TMA
+//     (cp.async.bulk.tensor, 128-byte swizzle, one CTA per copy) in the K-major layout the
+//     UMMA descriptors expect; rows beyond the token count are zero-filled by the copy;
+//   * each of 128 producer threads owns one weight row: it reads the row's bits sixteen
+//     bytes at a time, two such loads ahead, and writes 64 bfloat16 +-1 values per stage
+//     (eight 16-byte pieces, each from two lookups in a conflict-free 16-entry nibble table)
+//     into the same swizzled layout: 16 KB per stage from 1 KB of bits;
+//   * one elected thread issues tcgen05.mma (M = 128, N = tokens, K = 16 per instruction,
+//     four per stage) with the float32 accumulator in tensor memory, and tcgen05.commit
+//     releases the stage to the producers;
+//   * the epilogue reads the accumulator with tcgen05.ld (one weight row per thread, so a
+//     warp's stores to the token-major output are contiguous), applies the stage's
+//     rounding / scale / bias and stores.
 // A four-deep ring of stages is synchronised with mbarriers.  Every wait is bounded: on
 // expiry the kernel records an error code, frees its tensor memory and returns, and the
 // host reports QK_ERR_TIMEOUT.
+#include <cuda.h>  // CUtensorMap types only; the encoder is fetched through the runtime
+
 #include <cstring>
 
 #include "qk_common.h"
 
 namespace {
 
-constexpr int kBM = 128;        // tokens per tile (UMMA M)
-constexpr int kBN = 256;        // weight rows per tile (UMMA N)
+constexpr int kBM = 128;        // weight rows per tile (UMMA M)
+constexpr int kBNMax = 256;     // tokens per tile (UMMA N): 128, 160, 192 or 256
 constexpr int kBK = 64;         // k per stage: one 128-byte swizzle row of bfloat16
 constexpr int kStages = 4;
 constexpr int kProducers = 128; // warps 0..3: producers, then epilogue
 constexpr int kThreads = kProducers + 32;  // + warp 4: MMA issue and tensor-memory owner
-constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = kBN * kBK * 2;
+constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = kBNMax * kBK * 2;  // A: weights, B: tokens
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kWaitLimit = 1u << 24;
 
@@ -61,12 +69,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     }
     return false;
 }
-__device__ __forceinline__ void cp_async16_zfill(void *smem, const void *gmem, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem)), "l"(gmem),
-                 "r"(src_bytes)
-                 : "memory");
-}
-
 // UMMA shared-memory descriptor for a K-major, 128-byte-swizzled tile whose rows are 128
 // bytes and whose 8-row groups are 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
@@ -77,50 +79,53 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
     return d;
 }
-// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = 256.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) |
-                            ((uint32_t)(kBM >> 4) << 24);
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = bn.
+__device__ __forceinline__ uint32_t umma_idesc(uint32_t bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
 
 struct GemmArgs {
-    const uint16_t *a;     // activations bf16 [m_rows][a_pitch], zero padded to a_pitch
     const uint8_t *w_rows; // weight bits, rows padded to w_stride bytes
-    const float *in_scale; // unused here (the activation is pre-scaled)
-    void *out;             // bf16 [m_rows][out_pitch] (stage 1) or float [m_rows][n_rows]
+    void *out;             // bf16 [tokens][out_pitch] (stage 1) or float [tokens][n_rows]
     const float *out_scale, *out_bias;
     int *error;
-    uint32_t m_rows, n_rows, k_chunks, a_pitch, w_stride, out_pitch;
+    uint32_t tokens, n_rows, k_chunks, w_stride, out_pitch, bn;  // bn: tokens per tile
 };
 
 // kFinal = false: out = bf16(acc) as the next stage's activation;  true: y = bf16(acc)*s1 + bias.
 template <bool kFinal>
-__global__ void __launch_bounds__(kThreads, 1) factorized_gemm_tc_kernel(GemmArgs g) {
+__global__ void __launch_bounds__(kThreads, 1)
+factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment of the tiles is what the swizzle pattern assumes
     uint8_t *tiles = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint4 *lut = reinterpret_cast<uint4 *>(tiles + kStages * kStageBytes);
-    uint64_t *full = reinterpret_cast<uint64_t *>(lut + 256);
+    uint2 *lut = reinterpret_cast<uint2 *>(tiles + kStages * kStageBytes);
+    uint64_t *full = reinterpret_cast<uint64_t *>(lut + 16);
     uint64_t *empty = full + kStages;
     uint64_t *acc_full = empty + kStages;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-    const uint32_t m0 = blockIdx.x * kBM, n0 = blockIdx.y * kBN;
+    const uint32_t kBN = g.bn;
+    const uint32_t n0 = blockIdx.x * kBM;   // first weight row of the tile
+    const uint32_t t0 = blockIdx.y * kBN;   // first token of the tile
 
-    // byte -> eight bfloat16 +-1 values (bit i of the byte is element i)
-    for (uint32_t b = tid; b < 256; b += kThreads) {
-        uint32_t w[4];
+    // nibble -> four bfloat16 +-1 values (bit i of the nibble is element i).  Entry e sits in
+    // banks 2e and 2e+1, so lookups of different entries never collide.
+    if (tid < 16) {
+        uint32_t w[2];
 #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            uint32_t lo = (b >> (2 * p)) & 1 ? 0x3F80u : 0xBF80u;
-            uint32_t hi = (b >> (2 * p + 1)) & 1 ? 0x3F80u : 0xBF80u;
+        for (int p = 0; p < 2; ++p) {
+            uint32_t lo = (tid >> (2 * p)) & 1 ? 0x3F80u : 0xBF80u;
+            uint32_t hi = (tid >> (2 * p + 1)) & 1 ? 0x3F80u : 0xBF80u;
             w[p] = lo | (hi << 16);
         }
-        lut[b] = make_uint4(w[0], w[1], w[2], w[3]);
+        lut[tid] = make_uint2(w[0], w[1]);
     }
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full[s], kProducers);
+            mbar_init(&full[s], kProducers + 1);  // every producer + the TMA issuer's expect_tx
             mbar_init(&empty[s], 1);
         }
         mbar_init(acc_full, 1);
@@ -130,7 +135,7 @@ __global__ void __launch_bounds__(kThreads, 1) factorized_gemm_tc_kernel(GemmArg
     if (warp == 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_u32(tmem_slot)),
-                     "r"((uint32_t)kBN)
+                     "r"((uint32_t)kBNMax)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -141,48 +146,58 @@ __global__ void __launch_bounds__(kThreads, 1) factorized_gemm_tc_kernel(GemmArg
 
     if (warp < 4) {
         // ------------------------------------------------------------ producers
-        for (uint32_t kc = 0; kc < g.k_chunks; ++kc) {
-            const uint32_t s = kc % kStages, it = kc / kStages;
-            if (!mbar_wait(&empty[s], (it & 1) ^ 1)) {
-                *abort_flag = 1;
-                break;
-            }
-            if (*abort_flag) break;
-            uint8_t *a_tile = tiles + s * kStageBytes, *b_tile = a_tile + kABytes;
-            // activations: 128 rows x 8 pieces of 16 bytes; piece c of row r goes to chunk c ^ (r & 7)
+        // thread tid expands weight row n0 + tid.  Its bits arrive 16 bytes (two k-chunks)
+        // per load, and the loads run two pairs ahead of the expansion.
+        const bool live = n0 + tid < g.n_rows;
+        const uint4 *wrow = reinterpret_cast<const uint4 *>(g.w_rows + (size_t)(n0 + tid) * g.w_stride);
+        const uint32_t n_pairs = (g.k_chunks + 1) / 2;
+        const uint4 zero4 = make_uint4(0, 0, 0, 0);
+        uint4 q0 = live && 0 < n_pairs ? wrow[0] : zero4;
+        uint4 q1 = live && 1 < n_pairs ? wrow[1] : zero4;
+        bool dead = false;
+        for (uint32_t pair = 0; pair < n_pairs && !dead; ++pair) {
+            const uint4 cur = q0;
+            q0 = q1;
+            q1 = live && pair + 2 < n_pairs ? wrow[pair + 2] : zero4;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t idx = tid + i * kProducers, r = idx / 8, c = idx % 8;
-                const uint32_t row = m0 + r;
-                const uint16_t *src = g.a + (size_t)(row < g.m_rows ? row : 0) * g.a_pitch +
-                                      (size_t)kc * kBK + c * 8;
-                cp_async16_zfill(a_tile + r * 128 + ((c ^ (r & 7)) * 16), src,
-                                 row < g.m_rows ? 16u : 0u);
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            // weights: two rows per thread, eight bytes of bits each -> 64 bfloat16 values
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const uint32_t r = tid + half * kProducers, row = n0 + r;
-                uint2 bits = make_uint2(0, 0);
-                const bool live = row < g.n_rows;
-                if (live)
-                    bits = *reinterpret_cast<const uint2 *>(g.w_rows + (size_t)row * g.w_stride +
-                                                            (size_t)kc * 8);
-                uint4 *dst = reinterpret_cast<uint4 *>(b_tile + r * 128);
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t kc = pair * 2 + h;
+                if (kc >= g.k_chunks) break;
+                const uint32_t s = kc % kStages, it = kc / kStages;
+                if (!mbar_wait(&empty[s], (it & 1) ^ 1) || *abort_flag) {
+                    *abort_flag = 1;
+                    dead = true;
+                    break;
+                }
+                uint8_t *a_tile = tiles + s * kStageBytes, *b_tile = a_tile + kABytes;
+                if (tid == 0) {
+                    // tokens: one TMA box of 64 k x bn tokens, completing on the full barrier
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+                                     smem_u32(&full[s])),
+                                 "r"(kBN * kBK * 2)
+                                 : "memory");
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+                        "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(b_tile)),
+                        "l"(&b_map), "r"(kc * kBK), "r"(t0), "r"(smem_u32(&full[s]))
+                        : "memory");
+                }
+                const uint32_t lo = h ? cur.z : cur.x, hi = h ? cur.w : cur.y;
+                uint4 *dst = reinterpret_cast<uint4 *>(a_tile + tid * 128);
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    const uint32_t byte = ((c < 4 ? bits.x : bits.y) >> (8 * (c & 3))) & 0xff;
-                    dst[c ^ (r & 7)] = live ? lut[byte] : make_uint4(0, 0, 0, 0);
+                    const uint32_t byte = ((c < 4 ? lo : hi) >> (8 * (c & 3))) & 0xff;
+                    const uint2 e0 = lut[byte & 15], e1 = lut[byte >> 4];
+                    dst[c ^ (tid & 7)] = live ? make_uint4(e0.x, e0.y, e1.x, e1.y) : zero4;
                 }
+                // generic-proxy writes must be visible to the tensor core's async proxy
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&full[s]);
             }
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            // generic-proxy writes must be visible to the tensor core's async proxy
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(&full[s]);
         }
     } else if (lane == 0) {
         // ------------------------------------------------------------ MMA issue (one thread)
+        const uint32_t idesc = umma_idesc(kBN);
         for (uint32_t kc = 0; kc < g.k_chunks; ++kc) {
             const uint32_t s = kc % kStages, it = kc / kStages;
             if (!mbar_wait(&full[s], it & 1)) {
@@ -199,7 +214,7 @@ __global__ void __launch_bounds__(kThreads, 1) factorized_gemm_tc_kernel(GemmArg
                 asm volatile(
                     "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
                     " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_base),
-                    "l"(ad), "l"(bd), "r"(kIdesc), "r"(accumulate)
+                    "l"(ad), "l"(bd), "r"(idesc), "r"(accumulate)
                     : "memory");
             }
             // the stage may be refilled once these MMAs have read it
@@ -215,15 +230,19 @@ __global__ void __launch_bounds__(kThreads, 1) factorized_gemm_tc_kernel(GemmArg
     }
 
     // ---------------------------------------------------------------- epilogue (warps 0..3)
+    // thread = weight row n (tensor-memory lane), columns = tokens
     if (warp < 4) {
         bool ok = !*abort_flag && mbar_wait(acc_full, 0);
         ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
         if (!ok) *abort_flag = 1;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t row = m0 + warp * 32 + lane;
+        const uint32_t n = n0 + warp * 32 + lane;
+        const bool n_live = kFinal ? n < g.n_rows : n < g.out_pitch;
+        const float scale = (kFinal && g.out_scale && n < g.n_rows) ? g.out_scale[n] : 1.f;
+        const float bias = (kFinal && g.out_bias && n < g.n_rows) ? g.out_bias[n] : 0.f;
         if (ok) {
-            for (uint32_t c0 = 0; c0 < (uint32_t)kBN; c0 += 32) {
-                if (n0 + c0 >= (kFinal ? g.n_rows : g.out_pitch)) break;  // warp-uniform
+            for (uint32_t c0 = 0; c0 < kBN; c0 += 32) {
+                if (t0 + c0 >= g.tokens) break;  // warp-uniform
                 uint32_t v[32];
                 const uint32_t taddr = tmem_base + ((warp * 32) << 16) + c0;
                 asm volatile(
@@ -240,24 +259,21 @@ __global__ void __launch_bounds__(kThreads, 1) factorized_gemm_tc_kernel(GemmArg
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < g.m_rows) {
+                if (n_live) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const uint32_t n = n0 + c0 + j;
+                        const uint32_t tok = t0 + c0 + j;
+                        if (tok >= g.tokens) break;
                         // one rounding to bfloat16, as packed_matmul's bf16 instantiation does
-                        uint32_t u = v[j];
-                        uint32_t rb = (u & 0x7fffffffu) > 0x7f800000u
-                                          ? ((u | 0x00400000u) & 0xffff0000u)
-                                          : ((u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u);
+                        const uint32_t u = v[j];
+                        const uint32_t rb = (u & 0x7fffffffu) > 0x7f800000u
+                                                ? ((u | 0x00400000u) & 0xffff0000u)
+                                                : ((u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u);
                         if (kFinal) {
-                            if (n < g.n_rows) {
-                                float y = __uint_as_float(rb);
-                                if (g.out_scale) y = y * g.out_scale[n];
-                                if (g.out_bias) y = y + g.out_bias[n];
-                                static_cast<float *>(g.out)[(size_t)row * g.n_rows + n] = y;
-                            }
-                        } else if (n < g.out_pitch) {
-                            static_cast<uint16_t *>(g.out)[(size_t)row * g.out_pitch + n] =
+                            static_cast<float *>(g.out)[(size_t)tok * g.n_rows + n] =
+                                __uint_as_float(rb) * scale + bias;
+                        } else {
+                            static_cast<uint16_t *>(g.out)[(size_t)tok * g.out_pitch + n] =
                                 n < g.n_rows ? (uint16_t)(rb >> 16) : (uint16_t)0;
                         }
                     }
@@ -269,7 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1) factorized_gemm_tc_kernel(GemmArg
     __syncthreads();
     if (warp == 4) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                     "r"((uint32_t)kBN)
+                     "r"((uint32_t)kBNMax)
                      : "memory");
     }
     if (tid == 0 && *abort_flag) atomicExch(g.error, 1);
@@ -292,7 +308,57 @@ __global__ void scale_to_bf16_kernel(const float *__restrict__ x, const float *_
     z[idx] = r;
 }
 
-constexpr size_t kSmemBytes = 1024 + kStages * kStageBytes + 256 * 16 + (2 * kStages + 1) * 8 + 16;
+constexpr size_t kSmemBytes = 1024 + kStages * kStageBytes + 16 * 8 + (2 * kStages + 1) * 8 + 16;
+
+// cuTensorMapEncodeTiled, obtained through the runtime so that the library does not link
+// against the driver library directly.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+qk_status encode_activation_map(const uint16_t *base, size_t rows, size_t pitch, uint32_t box_rows,
+                                CUtensorMap *out) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault,
+                                                &qres);
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !sym)
+            return qk::fail(QK_ERR_CUDA, "cuTensorMapEncodeTiled is not available: %s",
+                            cudaGetErrorString(e));
+        fn = (EncodeTiledFn)sym;
+    }
+    const cuuint64_t dims[2] = {pitch, rows};             // innermost first
+    const cuuint64_t strides[1] = {pitch * 2};            // bytes between rows
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void *)base, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return qk::fail(QK_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return QK_OK;
+}
+
+// The N tile that wastes the least of the last wave (ties go to the larger tile).
+uint32_t pick_bn(size_t row_tiles, size_t tokens, int sms) {
+    const uint32_t cands[4] = {256, 192, 160, 128};
+    uint32_t best = 256;
+    double best_cost = 1e30;
+    for (uint32_t bn : cands) {
+        size_t tiles = row_tiles * qk::ceil_div(tokens, bn);
+        size_t waves = qk::ceil_div(tiles, (size_t)sms);
+        // time ~ waves x (per-tile work ~ bn, plus a fixed cost per tile)
+        double cost = (double)waves * (bn + 24.0);
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
 
 }  // namespace
 
@@ -333,17 +399,22 @@ qk_status qk_layer_apply_prefill(qk_ctx *ctx, const qk_layer *layer, const float
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
     QK_CUDA(cudaFuncSetAttribute(factorized_gemm_tc_kernel<true>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-    GemmArgs g1{z, layer->vbt, nullptr, t, nullptr, nullptr, err, (uint32_t)n_tokens, (uint32_t)r,
-                (uint32_t)(kp1 / kBK), (uint32_t)kp1, (uint32_t)layer->vbt_stride, (uint32_t)kp2};
-    dim3 grid1((unsigned)qk::ceil_div(n_tokens, kBM), (unsigned)qk::ceil_div(kp2, kBN));
-    factorized_gemm_tc_kernel<false><<<grid1, kThreads, kSmemBytes, c->stream>>>(g1);
+    const size_t rows1 = qk::ceil_div(kp2, kBM), rows2 = qk::ceil_div(dout, kBM);
+    const uint32_t bn1 = pick_bn(rows1, n_tokens, c->sm_count);
+    const uint32_t bn2 = pick_bn(rows2, n_tokens, c->sm_count);
+    CUtensorMap map1, map2;
+    if ((st = encode_activation_map(z, n_tokens, kp1, bn1, &map1)) != QK_OK) return st;
+    if ((st = encode_activation_map(t, n_tokens, kp2, bn2, &map2)) != QK_OK) return st;
+    GemmArgs g1{layer->vbt, t, nullptr, nullptr, err, (uint32_t)n_tokens, (uint32_t)r,
+                (uint32_t)(kp1 / kBK), (uint32_t)layer->vbt_stride, (uint32_t)kp2, bn1};
+    dim3 grid1((unsigned)rows1, (unsigned)qk::ceil_div(n_tokens, bn1));
+    factorized_gemm_tc_kernel<false><<<grid1, kThreads, kSmemBytes, c->stream>>>(map1, g1);
     QK_CUDA(cudaGetLastError());
     c->launches++;
-    GemmArgs g2{t, layer->ub, nullptr, y_dev, layer->s1, layer->bias, err, (uint32_t)n_tokens,
-                (uint32_t)dout, (uint32_t)(kp2 / kBK), (uint32_t)kp2, (uint32_t)layer->ub_stride,
-                (uint32_t)dout};
-    dim3 grid2((unsigned)qk::ceil_div(n_tokens, kBM), (unsigned)qk::ceil_div(dout, kBN));
-    factorized_gemm_tc_kernel<true><<<grid2, kThreads, kSmemBytes, c->stream>>>(g2);
+    GemmArgs g2{layer->ub, y_dev, layer->s1, layer->bias, err, (uint32_t)n_tokens, (uint32_t)dout,
+                (uint32_t)(kp2 / kBK), (uint32_t)layer->ub_stride, (uint32_t)dout, bn2};
+    dim3 grid2((unsigned)rows2, (unsigned)qk::ceil_div(n_tokens, bn2));
+    factorized_gemm_tc_kernel<true><<<grid2, kThreads, kSmemBytes, c->stream>>>(map2, g2);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     int h_err = 0;
