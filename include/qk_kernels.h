@@ -172,8 +172,9 @@ qk_status qk_layer_apply(qk_ctx *ctx, const qk_layer *layer, const float *x_dev,
 /* Prefill: n_tokens at once through one bfloat16-serving layer on the tcgen05 tensor
  * cores (core.rs:288-317 packed_matmul under the contract of engine/mod.rs:449-460: z, t
  * and u each rounded once to bfloat16, float32 accumulation).  x_dev [n_tokens, din] and
- * y_dev [n_tokens, dout] are float32 device buffers.  The call returns when y is complete;
- * QK_ERR_TIMEOUT means a bounded in-kernel wait expired. */
+ * y_dev [n_tokens, dout] are float32 device buffers.  Asynchronous on the context's stream,
+ * like qk_layer_apply.  Every wait inside the kernels is bounded; if one expires the result
+ * is incomplete and the next qk_gpu_synchronize returns QK_ERR_TIMEOUT. */
 qk_status qk_layer_apply_prefill(qk_ctx *ctx, const qk_layer *layer, const float *x_dev,
                                  size_t n_tokens, float *y_dev);
 /* One token through one layer without any allocation by the library.  It has no

@@ -58,6 +58,9 @@ struct qk_ctx {
     qk_scratch d_packed, d_in, d_out;
     // intermediates of the factorized linear (z and t) and of grouped applies
     qk_scratch d_z, d_t, d_ptrs;
+    // error word of the asynchronous tensor-core kernels, read back by qk_gpu_synchronize
+    qk_scratch d_err;
+    bool err_armed = false;
     void *h_pinned = nullptr;
     size_t h_pinned_cap = 0;
     qk_status pinned(size_t bytes, void **out);

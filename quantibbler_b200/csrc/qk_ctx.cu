@@ -140,6 +140,7 @@ void qk_gpu_free(qk_ctx *ctx) {
     ctx->d_z.release();
     ctx->d_t.release();
     ctx->d_ptrs.release();
+    ctx->d_err.release();
     if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
     delete ctx;
 }
@@ -150,6 +151,19 @@ qk_status qk_gpu_synchronize(qk_ctx *ctx) {
     if (st != QK_OK) return st;
     QK_CUDA(cudaSetDevice(c->device));
     QK_CUDA(cudaStreamSynchronize(c->stream));
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (c->err_armed) {
+        // a tensor-core prefill ran since the last check: fetch its error word
+        int h_err = 0;
+        QK_CUDA(cudaMemcpyAsync(&h_err, c->d_err.ptr, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+        QK_CUDA(cudaStreamSynchronize(c->stream));
+        c->err_armed = false;
+        if (h_err) {
+            QK_CUDA(cudaMemsetAsync(c->d_err.ptr, 0, sizeof(int), c->stream));
+            return qk::fail(QK_ERR_TIMEOUT,
+                            "the tensor-core prefill gave up waiting on a pipeline barrier");
+        }
+    }
     return QK_OK;
 }
 

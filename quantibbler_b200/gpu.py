@@ -231,7 +231,8 @@ class PackedLayer:
         return y
 
     def apply_prefill(self, x_ptr: int, n_tokens: int, y_ptr: int) -> None:
-        """Many tokens at once on the tensor cores (bfloat16 serving only); blocks until done."""
+        """Many tokens at once on the tensor cores (bfloat16 serving only).  Asynchronous on the
+        context's stream; ``ctx.synchronize()`` reports an expired in-kernel wait."""
         check(_lib.lib().qk_layer_apply_prefill(self.ctx.handle, self._h, ctypes.c_void_p(x_ptr),
                                                 int(n_tokens), ctypes.c_void_p(y_ptr)))
 

@@ -21,6 +21,7 @@ def run_case(ctx, dout, din, r, n_tokens, seed, with_bias):
     y = torch.full((n_tokens, dout), float("nan"), device="cuda")
     torch.cuda.synchronize()
     layer.apply_prefill(x.data_ptr(), n_tokens, y.data_ptr())
+    ctx.synchronize()   # the call is asynchronous; this also reports an expired in-kernel wait
     got = y.cpu().numpy()
     assert np.isfinite(got).all()
     check = range(n_tokens) if n_tokens <= 16 else [0, 1, n_tokens // 2, n_tokens - 2, n_tokens - 1]
