@@ -14,10 +14,10 @@
 //   * warps 0..15, producers, in four groups of 128 threads; group g owns pipeline stage g
 //     and fills it for every fourth 64-wide k-chunk.  Thread i of a group owns weight row
 //     i of the tile: it reads the row's 64 bits of the chunk (two such loads ahead) and
-//     writes 64 bfloat16 +-1 values as eight 16-byte pieces, each one lookup in a 256-entry
-//     byte table.  The table is kept in eight interleaved copies, lane j of every 8 using
-//     copy j, so that the 16-byte lookups of a quarter-warp fall in eight different bank
-//     groups whatever the bytes are.  The pieces go to the 128-byte-swizzled K-major layout
+//     turns them into 64 bfloat16 +-1 values in registers (a multiply that spreads four
+//     bits to the tops of four bytes, one LOP3, two byte permutes per four weights: no
+//     table, because shared-memory bandwidth is what bounds this kernel), stored as eight
+//     16-byte pieces in the 128-byte-swizzled K-major layout
 //     the UMMA descriptors expect.  The group's first thread also starts the TMA copy
 //     (cp.async.bulk.tensor, one CTA per copy) of the chunk's activation tile, up to 256
 //     tokens x 64 k; rows beyond the token count are zero-filled by the copy;
@@ -54,7 +54,6 @@ constexpr int kEpilogueWarps = 4;
 constexpr int kThreads = (kEpilogueWarp0 + kEpilogueWarps) * 32;
 constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = kBNMax * kBK * 2;  // A: weights, B: tokens
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
-constexpr uint32_t kLutBytes = 256 * 8 * 16;  // byte table, eight interleaved copies
 constexpr uint32_t kTmemCols = 2 * kBNMax;    // two accumulators
 constexpr uint32_t kWaitLimit = 1u << 22;
 
@@ -109,6 +108,13 @@ __device__ __forceinline__ uint32_t round_bf16_hi(uint32_t u) {
                                            : ((u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u);
 }
 
+// Four weight bits (bit i of n = element i; 1 means +1) -> the four high bytes of their
+// bfloat16 values: 0x3F for +1.0, 0xBF for -1.0.  The multiply puts bit i at the top of byte
+// i (the four shifted copies of n do not overlap, so nothing carries); the rest is one LOP3.
+__device__ __forceinline__ uint32_t expand_nibble(uint32_t n) {
+    return ((n * 0x10204080u) & 0x80808080u) ^ 0xBFBFBFBFu;
+}
+
 struct GemmArgs {
     const uint8_t *w_rows; // weight bits, rows padded to w_stride bytes
     void *out;             // bf16 [tokens][out_pitch] (stage 1) or float [tokens][n_rows]
@@ -126,8 +132,7 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment of the tiles is what the swizzle pattern assumes
     uint8_t *tiles = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint4 *lut = reinterpret_cast<uint4 *>(tiles + kStages * kStageBytes);
-    uint64_t *full = reinterpret_cast<uint64_t *>(tiles + kStages * kStageBytes + kLutBytes);
+    uint64_t *full = reinterpret_cast<uint64_t *>(tiles + kStages * kStageBytes);
     uint64_t *empty = full + kStages;
     uint64_t *acc_full = empty + kStages;   // [2]
     uint64_t *acc_empty = acc_full + 2;     // [2]
@@ -139,19 +144,6 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
     // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...
     const uint32_t my_tiles = g.n_tiles > blockIdx.x ? (g.n_tiles - blockIdx.x - 1) / gridDim.x + 1 : 0;
 
-    // byte -> eight bfloat16 +-1 values (bit i of the byte is element i); copy j of entry e
-    // lives at 16-byte slot 8e + j.
-    for (uint32_t i = tid; i < 256 * 8; i += kThreads) {
-        const uint32_t e = i >> 3;
-        uint32_t w[4];
-#pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            const uint32_t lo = (e >> (2 * p)) & 1 ? 0x3F80u : 0xBF80u;
-            const uint32_t hi = (e >> (2 * p + 1)) & 1 ? 0x3F80u : 0xBF80u;
-            w[p] = lo | (hi << 16);
-        }
-        lut[i] = make_uint4(w[0], w[1], w[2], w[3]);
-    }
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full[s], kGroupThreads / 32 + 1);  // the group's warps + the expect_tx
@@ -186,7 +178,6 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
         uint8_t *a_tile = tiles + group * kStageBytes, *b_tile = a_tile + kABytes;
         uint64_t *my_full = &full[group], *my_empty = &empty[group];
         const uint32_t dst_base = smem_u32(a_tile) + row * 128, swz = (row & 7) << 4;
-        const uint32_t lut_lane = smem_u32(lut) + (lane & 7) * 16;
         const uint2 zero2 = make_uint2(0, 0);
         auto load_bits = [&](uint32_t gc) -> uint2 {
             if (gc >= total_chunks) return zero2;
@@ -221,16 +212,16 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
             }
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
-                const uint32_t word = c < 4 ? cur.x : cur.y;
-                // byte c of the chunk, times 128: the entry's offset in the interleaved table
-                const uint32_t off = (c & 3) == 0 ? (word << 7) & 0x7f80u
-                                                  : (word >> (8 * (c & 3) - 7)) & 0x7f80u;
-                uint32_t e0, e1, e2, e3;
-                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(e0), "=r"(e1), "=r"(e2), "=r"(e3)
-                             : "r"(lut_lane + off));
+                // byte c of the chunk -> eight bfloat16 +-1 values, in registers: shared memory
+                // is the contended resource of this kernel (TMA writes, tensor-core operand
+                // reads and these stores all go through its 128 bytes per clock)
+                const uint32_t byte = __byte_perm(c < 4 ? cur.x : cur.y, 0, 0x4440 + (c & 3));
+                const uint32_t h0 = expand_nibble(byte & 15u), h1 = expand_nibble(byte >> 4);
                 asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst_base + ((c << 4) ^ swz)),
-                             "r"(e0), "r"(e1), "r"(e2), "r"(e3)
+                             "r"(__byte_perm(h0, 0x80808080u, 0x1404)),
+                             "r"(__byte_perm(h0, 0x80808080u, 0x3424)),
+                             "r"(__byte_perm(h1, 0x80808080u, 0x1404)),
+                             "r"(__byte_perm(h1, 0x80808080u, 0x3424))
                              : "memory");
             }
             // generic-proxy writes must be visible to the tensor core's async proxy
@@ -376,8 +367,8 @@ __global__ void scale_to_bf16_kernel(const float *__restrict__ x, const float *_
     *reinterpret_cast<uint4 *>(z + (size_t)t * pitch + k) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-constexpr size_t kSmemBytes = 1024 + kStages * kStageBytes + kLutBytes + (2 * kStages + 4) * 8 + 16;
-static_assert(kSmemBytes <= 227 * 1024, "stages + table must fit the 227 KB a CTA may have");
+constexpr size_t kSmemBytes = 1024 + kStages * kStageBytes + (2 * kStages + 4) * 8 + 16;
+static_assert(kSmemBytes <= 227 * 1024, "the stages must fit the 227 KB a CTA may have");
 
 // cuTensorMapEncodeTiled, obtained through the runtime so that the library does not link
 // against the driver library directly.
