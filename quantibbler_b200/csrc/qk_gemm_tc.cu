@@ -122,10 +122,34 @@ struct GemmArgs {
     int *error;
     uint32_t tokens, n_rows, k_chunks, w_stride, out_pitch;
     uint32_t bn;           // tokens per tile
-    uint32_t row_tiles, n_tiles;  // tile t covers row tile t % row_tiles, token tile t / row_tiles
+    uint32_t row_tiles;    // tile t covers row tile t % row_tiles, token tile t / row_tiles
+    uint32_t units;        // tiles x k_chunks: the work that is dealt out evenly to the CTAs
+    float *partials;       // [CTAs][256][128] float32 accumulators of split tiles
+    uint32_t *flags;       // [CTAs] flags[i] == epoch: CTA i's partial is in place
+    uint32_t epoch;        // differs from launch to launch, so the flags need no reset
 };
 
-// kFinal = false: out = bf16(acc) as the next stage's activation;  true: y = bf16(acc)*s1 + bias.
+// CTA i of G works on units [i * units / G, (i + 1) * units / G), unit u being k-chunk
+// u % k_chunks of tile u / k_chunks.
+__device__ __forceinline__ uint32_t unit_begin(uint32_t i, uint32_t units, uint32_t ctas) {
+    return (uint32_t)((uint64_t)i * units / ctas);
+}
+
+// The epilogue of one output element: kFinal = false: out = bf16(acc) as the next stage's
+// activation (zero in the padding columns);  true: y = bf16(acc) * s1 + bias.
+template <bool kFinal>
+__device__ __forceinline__ void store_output(const GemmArgs &g, uint32_t tok, uint32_t n, uint32_t acc_bits,
+                                             float scale, float bias) {
+    // one rounding to bfloat16, as packed_matmul's bf16 instantiation does
+    const uint32_t rb = round_bf16_hi(acc_bits);
+    if (kFinal) {
+        static_cast<float *>(g.out)[(size_t)tok * g.n_rows + n] = __uint_as_float(rb) * scale + bias;
+    } else {
+        static_cast<uint16_t *>(g.out)[(size_t)tok * g.out_pitch + n] =
+            n < g.n_rows ? (uint16_t)(rb >> 16) : (uint16_t)0;
+    }
+}
+
 template <bool kFinal>
 __global__ void __launch_bounds__(kThreads, 1)
 factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g) {
@@ -136,13 +160,22 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
     uint64_t *empty = full + kStages;
     uint64_t *acc_full = empty + kStages;   // [2]
     uint64_t *acc_empty = acc_full + 2;     // [2]
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+    uint64_t *staged_bar = acc_empty + 2;   // a neighbour's partial accumulator has landed
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(staged_bar + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const uint32_t kBN = g.bn;
-    // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...
-    const uint32_t my_tiles = g.n_tiles > blockIdx.x ? (g.n_tiles - blockIdx.x - 1) / gridDim.x + 1 : 0;
+    // This CTA's share of the work.  It is a run of consecutive units, so it is cut into
+    // segments at tile borders: the rest of a tile another CTA began, whole tiles, the head of
+    // a tile.  Only the first segment can start inside a tile; its accumulator goes to
+    // partials[this CTA] and flags[this CTA] is raised.  A segment that starts a tile is
+    // finished here: if it stops short of the tile's end, the CTAs after this one hold the
+    // rest as THEIR first segments, which they computed at the very start of the kernel, so
+    // by now those partials are in place; they are added in CTA order (a fixed order, so the
+    // sum is reproducible) before the epilogue.  The wait on the flags is bounded all the same.
+    const uint32_t u_begin = unit_begin(blockIdx.x, g.units, gridDim.x);
+    const uint32_t u_end = unit_begin(blockIdx.x + 1, g.units, gridDim.x);
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -153,6 +186,7 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
             mbar_init(&acc_full[a], 1);
             mbar_init(&acc_empty[a], kEpilogueWarps);
         }
+        mbar_init(staged_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -167,12 +201,12 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t total_chunks = my_tiles * g.k_chunks;
+    const uint32_t total_chunks = u_end - u_begin;
 
     if (warp < kProducerWarps) {
         // ------------------------------------------------------------ producers
-        // The ring of stages runs on across tiles: chunk number gc (counted over all of this
-        // CTA's tiles) uses stage gc % 4 and belongs to group gc % 4.  Rows past the end of
+        // The ring of stages runs on across tiles: chunk number gc (counted from the CTA's
+        // first unit) uses stage gc % 4 and belongs to group gc % 4.  Rows past the end of
         // the factor re-read the last row: their accumulator lanes are never stored.
         const uint32_t group = tid / kGroupThreads, row = tid % kGroupThreads;
         uint8_t *a_tile = tiles + group * kStageBytes, *b_tile = a_tile + kABytes;
@@ -181,8 +215,7 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
         const uint2 zero2 = make_uint2(0, 0);
         auto load_bits = [&](uint32_t gc) -> uint2 {
             if (gc >= total_chunks) return zero2;
-            const uint32_t ti = gc / g.k_chunks, kc = gc - ti * g.k_chunks;
-            const uint32_t tile = blockIdx.x + ti * gridDim.x;
+            const uint32_t tile = (u_begin + gc) / g.k_chunks, kc = u_begin + gc - tile * g.k_chunks;
             const uint32_t n_src = min((tile % g.row_tiles) * kBM + row, g.n_rows - 1);
             return reinterpret_cast<const uint2 *>(g.w_rows + (size_t)n_src * g.w_stride)[kc];
         };
@@ -198,8 +231,8 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
             }
             if (row == 0) {
                 // tokens: one TMA box of 64 k x bn tokens, completing on the full barrier
-                const uint32_t ti = gc / g.k_chunks, kc = gc - ti * g.k_chunks;
-                const uint32_t t0 = ((blockIdx.x + ti * gridDim.x) / g.row_tiles) * kBN;
+                const uint32_t tile = (u_begin + gc) / g.k_chunks, kc = u_begin + gc - tile * g.k_chunks;
+                const uint32_t t0 = (tile / g.row_tiles) * kBN;
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
                                  smem_u32(my_full)),
                              "r"(kBN * kBK * 2)
@@ -237,16 +270,17 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
         const uint32_t idesc = umma_idesc(kBN);
         uint32_t gc = 0;
         bool dead = false;
-        for (uint32_t ti = 0; ti < my_tiles && !dead; ++ti) {
-            const uint32_t acc = ti & 1;
-            // the epilogue must have drained this accumulator (tile ti - 2)
-            if (!mbar_wait(&acc_empty[acc], ((ti >> 1) & 1) ^ 1, abort_flag)) {
+        for (uint32_t u = u_begin, seg = 0; u < u_end && !dead; ++seg) {
+            const uint32_t kc0 = u % g.k_chunks, kc1 = min(g.k_chunks, kc0 + (u_end - u));
+            const uint32_t acc = seg & 1;
+            // the epilogue must have drained this accumulator (segment seg - 2)
+            if (!mbar_wait(&acc_empty[acc], ((seg >> 1) & 1) ^ 1, abort_flag)) {
                 dead = true;
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t d_tmem = tmem_base + acc * kBNMax;
-            for (uint32_t kc = 0; kc < g.k_chunks; ++kc, ++gc) {
+            for (uint32_t kc = kc0; kc < kc1; ++kc, ++gc) {
                 const uint32_t s = gc % kStages;
                 if (!mbar_wait(&full[s], (gc / kStages) & 1, abort_flag)) {
                     dead = true;
@@ -258,7 +292,7 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k) {
                         const uint64_t ad = umma_desc(a_addr + k * 32), bd = umma_desc(b_addr + k * 32);
-                        const uint32_t accumulate = (kc | k) ? 1u : 0u;
+                        const uint32_t accumulate = (kc != kc0 || k != 0) ? 1u : 0u;
                         asm volatile(
                             "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
                             " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
@@ -271,6 +305,7 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
             }
             if (!dead && lane == 0) umma_commit(&acc_full[acc]);
             __syncwarp();
+            u += kc1 - kc0;
         }
         if (dead) *abort_flag = 1;
     } else {
@@ -278,12 +313,32 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
         // thread = weight row n (tensor-memory lane; a warp reaches the 32 lanes of its number
         // modulo 4), columns = tokens
         const uint32_t quarter = warp % 4;
-        for (uint32_t ti = 0; ti < my_tiles; ++ti) {
-            const uint32_t acc = ti & 1;
-            const uint32_t tile = blockIdx.x + ti * gridDim.x;
-            const uint32_t n = (tile % g.row_tiles) * kBM + quarter * 32 + lane;
+        const size_t slot_elems = (size_t)kBNMax * kBM;
+        bool dead = false;
+        for (uint32_t u = u_begin, seg = 0; u < u_end && !dead; ++seg) {
+            const uint32_t tile = u / g.k_chunks, kc0 = u - tile * g.k_chunks;
+            const uint32_t len = min(g.k_chunks - kc0, u_end - u);
+            const uint32_t acc = seg & 1;
+            const uint32_t n_local = quarter * 32 + lane;
+            const uint32_t n = (tile % g.row_tiles) * kBM + n_local;
             const uint32_t t0 = (tile / g.row_tiles) * kBN;
-            if (!mbar_wait(&acc_full[acc], (ti >> 1) & 1, abort_flag)) {
+            // CTAs [blockIdx.x + 1, last) hold the rest of this tile
+            uint32_t last = blockIdx.x + 1;
+            if (kc0 == 0 && len < g.k_chunks) {
+                const uint32_t hi = (tile + 1) * g.k_chunks;
+                while (last < gridDim.x && unit_begin(last, g.units, gridDim.x) < hi) ++last;
+                for (uint32_t j = blockIdx.x + 1; j < last && !dead; ++j) {
+                    uint32_t seen = 0;
+                    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(g.flags + j) : "memory");
+                        if (seen == g.epoch) break;
+                        if ((i & 255u) == 255u && *abort_flag) break;
+                        __nanosleep(64);
+                    }
+                    dead = seen != g.epoch;
+                }
+            }
+            if (dead || !mbar_wait(&acc_full[acc], (seg >> 1) & 1, abort_flag)) {
                 *abort_flag = 1;
                 break;
             }
@@ -291,6 +346,31 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
             const bool n_live = kFinal ? n < g.n_rows : n < g.out_pitch;
             const float scale = (kFinal && g.out_scale && n < g.n_rows) ? g.out_scale[n] : 1.f;
             const float bias = (kFinal && g.out_bias && n < g.n_rows) ? g.out_bias[n] : 0.f;
+            float *part = g.partials + (size_t)blockIdx.x * slot_elems;
+            // When this is the CTA's last segment the pipeline has drained and the stages are
+            // free: the next CTA's partial (contiguous, bn x 128 floats) comes in by one bulk
+            // copy instead of latency-bound loads.  Any further partials are read directly.
+            const bool staged = last > blockIdx.x + 1 && u + len == u_end;
+            if (staged) {
+                if (warp == kEpilogueWarp0 && lane == 0) {
+                    const uint32_t bytes = kBN * kBM * 4;
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+                                     smem_u32(staged_bar)),
+                                 "r"(bytes)
+                                 : "memory");
+                    asm volatile(
+                        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+                            "r"(smem_u32(tiles)),
+                        "l"(g.partials + (size_t)(blockIdx.x + 1) * slot_elems), "r"(bytes),
+                        "r"(smem_u32(staged_bar))
+                        : "memory");
+                }
+                if (!mbar_wait(staged_bar, 0, abort_flag)) {
+                    *abort_flag = 1;
+                    break;
+                }
+            }
+            const float *staged_part = reinterpret_cast<const float *>(tiles);
             for (uint32_t c0 = 0; c0 < kBN; c0 += 16) {
                 if (t0 + c0 >= g.tokens) break;  // warp-uniform
                 uint32_t v[16];
@@ -304,20 +384,31 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (kc0 != 0) {
+                    // the rest of a tile another CTA began: the raw accumulator,
+                    // [token column][weight row]
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        part[(size_t)(c0 + j) * kBM + n_local] = __uint_as_float(v[j]);
+                    continue;
+                }
+                if (staged) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        v[j] = __float_as_uint(__uint_as_float(v[j]) + staged_part[(c0 + j) * kBM + n_local]);
+                }
+                for (uint32_t p = blockIdx.x + 1 + (staged ? 1 : 0); p < last; ++p) {
+                    const float *src = g.partials + (size_t)p * slot_elems + (size_t)c0 * kBM + n_local;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(src + j * kBM));
+                }
                 if (n_live) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const uint32_t tok = t0 + c0 + j;
                         if (tok >= g.tokens) break;
-                        // one rounding to bfloat16, as packed_matmul's bf16 instantiation does
-                        const uint32_t rb = round_bf16_hi(v[j]);
-                        if (kFinal) {
-                            static_cast<float *>(g.out)[(size_t)tok * g.n_rows + n] =
-                                __uint_as_float(rb) * scale + bias;
-                        } else {
-                            static_cast<uint16_t *>(g.out)[(size_t)tok * g.out_pitch + n] =
-                                n < g.n_rows ? (uint16_t)(rb >> 16) : (uint16_t)0;
-                        }
+                        store_output<kFinal>(g, tok, n, v[j], scale, bias);
                     }
                 }
             }
@@ -325,6 +416,14 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[acc]);
+            if (kc0 != 0) {
+                // publish the partial: every writer fences, the four warps meet, one raises the flag
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
+                if (warp == kEpilogueWarp0 && lane == 0)
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(g.flags + blockIdx.x), "r"(g.epoch) : "memory");
+            }
+            u += len;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -367,7 +466,7 @@ __global__ void scale_to_bf16_kernel(const float *__restrict__ x, const float *_
     *reinterpret_cast<uint4 *>(z + (size_t)t * pitch + k) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-constexpr size_t kSmemBytes = 1024 + kStages * kStageBytes + (2 * kStages + 4) * 8 + 16;
+constexpr size_t kSmemBytes = 1024 + kStages * kStageBytes + (2 * kStages + 5) * 8 + 16;
 static_assert(kSmemBytes <= 227 * 1024, "the stages must fit the 227 KB a CTA may have");
 
 // cuTensorMapEncodeTiled, obtained through the runtime so that the library does not link
@@ -436,8 +535,8 @@ qk_status qk_layer_apply_prefill(qk_ctx *ctx, const qk_layer *layer, const float
     const size_t t_bytes = qk::ceil_div(n_tokens * kp2 * 2, 256) * 256;
     if ((st = c->d_z.reserve(z_bytes + t_bytes)) != QK_OK) return st;
     if (!c->d_err.ptr) {
-        if ((st = c->d_err.reserve(256)) != QK_OK) return st;
-        QK_CUDA(cudaMemsetAsync(c->d_err.ptr, 0, 256, c->stream));
+        if ((st = c->d_err.reserve(256 + 4096)) != QK_OK) return st;  // error word + CTA flags
+        QK_CUDA(cudaMemsetAsync(c->d_err.ptr, 0, 256 + 4096, c->stream));
     }
     uint16_t *z = (uint16_t *)c->d_z.ptr;
     uint16_t *t = (uint16_t *)((uint8_t *)c->d_z.ptr + z_bytes);
@@ -458,17 +557,25 @@ qk_status qk_layer_apply_prefill(qk_ctx *ctx, const qk_layer *layer, const float
     CUtensorMap map1, map2;
     if ((st = encode_activation_map(z, n_tokens, kp1, bn, &map1)) != QK_OK) return st;
     if ((st = encode_activation_map(t, n_tokens, kp2, bn, &map2)) != QK_OK) return st;
+    // every CTA gets the same number of (tile, k-chunk) units, at least eight of them
+    const auto ctas_for = [&](size_t units) {
+        return (unsigned)std::max<size_t>(1, std::min<size_t>((size_t)c->sm_count, units / 8));
+    };
+    const size_t units1 = rows1 * tok_tiles * (kp1 / kBK), units2 = rows2 * tok_tiles * (kp2 / kBK);
+    const unsigned grid1 = ctas_for(units1), grid2 = ctas_for(units2);
+    const size_t slot_bytes = (size_t)kBNMax * kBM * sizeof(float);
+    if ((st = c->d_t.reserve((size_t)std::max(grid1, grid2) * slot_bytes)) != QK_OK) return st;
+    float *partials = (float *)c->d_t.ptr;
+    uint32_t *flags = (uint32_t *)c->d_err.ptr + 64;  // after the error word's 256 bytes
     GemmArgs g1{layer->vbt, t, nullptr, nullptr, err, (uint32_t)n_tokens, (uint32_t)r,
                 (uint32_t)(kp1 / kBK), (uint32_t)layer->vbt_stride, (uint32_t)kp2, bn,
-                (uint32_t)rows1, (uint32_t)(rows1 * tok_tiles)};
-    const unsigned grid1 = (unsigned)std::min<size_t>(g1.n_tiles, (size_t)c->sm_count);
+                (uint32_t)rows1, (uint32_t)units1, partials, flags, ++c->tc_epoch};
     factorized_gemm_tc_kernel<false><<<grid1, kThreads, kSmemBytes, c->stream>>>(map1, g1);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     GemmArgs g2{layer->ub, y_dev, layer->s1, layer->bias, err, (uint32_t)n_tokens, (uint32_t)dout,
                 (uint32_t)(kp2 / kBK), (uint32_t)layer->ub_stride, (uint32_t)dout, bn,
-                (uint32_t)rows2, (uint32_t)(rows2 * tok_tiles)};
-    const unsigned grid2 = (unsigned)std::min<size_t>(g2.n_tiles, (size_t)c->sm_count);
+                (uint32_t)rows2, (uint32_t)units2, partials, flags, ++c->tc_epoch};
     factorized_gemm_tc_kernel<true><<<grid2, kThreads, kSmemBytes, c->stream>>>(map2, g2);
     QK_CUDA(cudaGetLastError());
     c->launches++;
