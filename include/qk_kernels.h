@@ -149,6 +149,19 @@ qk_status qk_gpu_attention_sage(qk_ctx *ctx, const qk_attention_shape *shape, co
                                 size_t q_len, const float *key, size_t k_len, const float *value,
                                 size_t v_len, int32_t causal, size_t block_size, float *out,
                                 size_t out_len);
+/* The two attention faces on device buffers (same layouts, float32), asynchronous on the
+ * context's stream: for callers whose q, k, v already live on the GPU (a resident prefill).
+ * Additive; the reference's API has only the host-slice forms above. */
+qk_status qk_gpu_attention_dev(qk_ctx *ctx, const qk_attention_shape *shape, const float *q_dev,
+                               const float *k_dev, const float *v_dev, int32_t causal,
+                               float *out_dev);
+qk_status qk_gpu_attention_sage_dev(qk_ctx *ctx, const qk_attention_shape *shape,
+                                    const float *q_dev, const float *k_dev, const float *v_dev,
+                                    int32_t causal, size_t block_size, float *out_dev);
+/* Which kernel the Sage face runs: 1 (default) the INT8 tensor-core kernel where the shape
+ * allows (head_dim == val_dim in {64, 128}, block_size in {32, 64, 128}), 0 always the dp4a
+ * kernel.  Returns the previous choice. */
+int32_t qk_set_sage_kernel(qk_ctx *ctx, int32_t which);
 
 /* ---- the factorized linear with device-resident factors ----------------------
  * Replaces crates/quantibbler-server/src/engine/mod.rs:313-381 (PackedLayer,

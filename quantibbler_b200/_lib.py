@@ -94,6 +94,11 @@ _SIGNATURES = {
     "qk_argmax_first": (c_int32, [c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_int32,
                                   c_void_p, c_void_p]),
     "qk_set_gemv_kernel": (c_int32, [c_void_p, c_int32]),
+    "qk_set_sage_kernel": (c_int32, [c_void_p, c_int32]),
+    "qk_gpu_attention_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
+                                       c_void_p]),
+    "qk_gpu_attention_sage_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                            c_int32, c_size_t, c_void_p]),
     "qk_gpu_launch_count": (c_uint64, [c_void_p]),
 }
 

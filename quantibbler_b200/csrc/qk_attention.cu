@@ -177,11 +177,23 @@ __global__ void sage_quant_k_kernel(const float *__restrict__ k, int8_t *__restr
     }
 }
 
+// Where key kk of a block sits in the tensor-core kernel's V tile.  That kernel feeds its P
+// codes to the PV MMA straight from the accumulator fragment of QK^T, in which a thread holds
+// columns 2t, 2t+1 of each 8-key tile; the MMA's A operand wants four consecutive k per
+// register.  Summation order over keys is free, so the keys of every 32-key slab are simply
+// renamed: tile j, column c of the slab becomes k index 16*(j/2) + 4*(c/2) + 2*(j%2) + c%2.
+__host__ __device__ inline uint32_t sage_tc_key_slot(uint32_t kk) {
+    const uint32_t slab = kk / 32, r = kk % 32, j = r / 8, c = r % 8;
+    return slab * 32 + (j / 2) * 16 + (c / 2) * 4 + (j % 2) * 2 + (c % 2);
+}
+
 // psi_V: one block per (b, kv head, key block): per-channel scale over the block's tokens,
-// codes stored channel-major with the block's keys contiguous: [blk][dv][bpad] int8.
+// codes stored channel-major with the block's keys contiguous: [blk][dv][bpad] int8
+// (permute: in the tensor-core kernel's key order).
 __global__ void sage_quant_v_kernel(const float *__restrict__ v, int8_t *__restrict__ codes,
                                     float *__restrict__ scale, uint32_t S, uint32_t dv,
-                                    uint32_t block, uint32_t bpad, uint32_t n_blocks) {
+                                    uint32_t block, uint32_t bpad, uint32_t n_blocks,
+                                    int permute) {
     const uint32_t plane = blockIdx.y, jb = blockIdx.x;
     const uint32_t j0 = jb * block, j1 = min(S, j0 + block);
     const float *vp = v + (size_t)plane * S * dv;
@@ -191,7 +203,8 @@ __global__ void sage_quant_v_kernel(const float *__restrict__ v, int8_t *__restr
         const float delta = peak > 0.f ? peak / 127.f : 1.f;
         int8_t *cr = codes + (((size_t)plane * n_blocks + jb) * dv + c) * bpad;
         for (uint32_t j = j0; j < j0 + bpad; ++j)
-            cr[j - j0] = j < j1 ? (int8_t)quant_code(vp[(size_t)j * dv + c], delta) : 0;
+            cr[permute ? sage_tc_key_slot(j - j0) : j - j0] =
+                j < j1 ? (int8_t)quant_code(vp[(size_t)j * dv + c], delta) : 0;
         scale[((size_t)plane * n_blocks + jb) * dv + c] = delta;
     }
 }
@@ -359,6 +372,236 @@ attention_sage_kernel(SageArgs a, AttnDims dm, int causal) {
     }
 }
 
+// ------------------------------------------------------------------ Sage on the tensor cores
+__device__ __forceinline__ void mma_s8(int (&c)[4], const int (&a)[4], int b0, int b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// The same arithmetic as attention_sage_kernel with both integer products on the INT8
+// tensor cores (mma.sync m16n8k32).  A block of four warps takes 64 queries, 16 per warp;
+// one key block (BLK = 32, 64 or 128 keys, the Sage block) is staged in shared memory at a
+// time: K codes [BLK][D + 16] and V codes [DV][BLK + 16] (the 16-byte pads make the
+// fragment loads bank-conflict free), the key scales, the channel scales and the mean.
+//   S = Qhat Khat^T: A = the warp's Q codes (kept in registers for the whole kernel),
+//       B = K codes; the int32 accumulator fragment holds rows g, g+8 and columns 2t, 2t+1
+//       of each 8-key tile;
+//   scores, row maximum (two shuffles within the quad), P = exp(s - m), l, P codes: all on
+//       the fragment, then the codes are packed four to a register in the key order of
+//       sage_tc_key_slot and are the A operand of
+//   PV = Phat Vhat: B = V codes in that same key order; one 8-channel tile at a time is
+//       folded into the float32 output fragment with alpha and dV / 127.
+// Because the whole block's scores are in registers the block is swept once, not twice.
+template <int D32, int DV8, int BLK32>
+__global__ void __launch_bounds__(128)
+attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
+    constexpr int D = 32 * D32, DV = 8 * DV8, BLK = 32 * BLK32, NT = BLK / 8;
+    constexpr int KP = D + 16, VP = BLK + 16;
+    extern __shared__ __align__(16) uint8_t sm_tc[];
+    uint8_t *Ks = sm_tc;                                   // [BLK][KP]
+    uint8_t *Vs = Ks + BLK * KP;                           // [DV][VP]
+    float *kscale = reinterpret_cast<float *>(Vs + DV * VP);  // [BLK]
+    float *vscale = kscale + BLK;                          // [DV]
+    float *mu = vscale + DV;                               // [D]
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
+    const int h = blockIdx.y, b = blockIdx.z, kvh = h / dm.group;
+    const size_t plane = (size_t)b * dm.KV + kvh;
+    // under causal masking the last query tiles have the most key blocks: start them first
+    const int q_tile = causal ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
+    const int q0 = q_tile * 64 + warp * 16;
+    const int i0 = q0 + g, i1 = i0 + 8;
+    const bool v0 = i0 < (int)dm.Sq, v1 = i1 < (int)dm.Sq;
+    const size_t row_base = ((size_t)b * dm.H + h) * dm.Sq;
+
+    int qa[D32][4];
+    {
+        const int *r0 = reinterpret_cast<const int *>(a.qc + (row_base + (v0 ? i0 : 0)) * a.dpad);
+        const int *r1 = reinterpret_cast<const int *>(a.qc + (row_base + (v1 ? i1 : 0)) * a.dpad);
+#pragma unroll
+        for (int ks = 0; ks < D32; ++ks) {
+            qa[ks][0] = v0 ? r0[8 * ks + t] : 0;
+            qa[ks][1] = v1 ? r1[8 * ks + t] : 0;
+            qa[ks][2] = v0 ? r0[8 * ks + 4 + t] : 0;
+            qa[ks][3] = v1 ? r1[8 * ks + 4 + t] : 0;
+        }
+    }
+    const float dq0 = v0 ? a.qs[row_base + i0] : 1.f, dq1 = v1 ? a.qs[row_base + i1] : 1.f;
+
+    float o[DV8][4];
+#pragma unroll
+    for (int nv = 0; nv < DV8; ++nv) o[nv][0] = o[nv][1] = o[nv][2] = o[nv][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    const int i_blk_max = min((int)dm.Sq - 1, q_tile * 64 + 63);
+    const int i_warp_max = min((int)dm.Sq - 1, q0 + 15);
+    const int jb_hi = causal ? i_blk_max / BLK + 1 : (int)a.n_blocks;
+
+    for (int jb = 0; jb < jb_hi; ++jb) {
+        const int j0 = jb * BLK, kj = min(BLK, (int)dm.Skv - j0);
+        __syncthreads();
+        {   // stage the key block
+            const uint4 zero = make_uint4(0, 0, 0, 0);
+            for (int idx = threadIdx.x; idx < BLK * (D / 16); idx += 128) {
+                const int key = idx / (D / 16), piece = idx % (D / 16);
+                uint4 w = zero;
+                if (key < kj)
+                    w = reinterpret_cast<const uint4 *>(a.kc + (plane * dm.Skv + j0 + key) * a.dpad)[piece];
+                *reinterpret_cast<uint4 *>(Ks + key * KP + piece * 16) = w;
+            }
+            const int8_t *vsrc = a.vc + (plane * a.n_blocks + jb) * (size_t)DV * a.bpad;
+            for (int idx = threadIdx.x; idx < DV * (BLK / 16); idx += 128) {
+                const int c = idx / (BLK / 16), piece = idx % (BLK / 16);
+                *reinterpret_cast<uint4 *>(Vs + c * VP + piece * 16) =
+                    reinterpret_cast<const uint4 *>(vsrc + (size_t)c * a.bpad)[piece];
+            }
+            for (int idx = threadIdx.x; idx < BLK; idx += 128)
+                kscale[idx] = idx < kj ? a.ks[plane * dm.Skv + j0 + idx] : 1.f;
+            for (int idx = threadIdx.x; idx < DV; idx += 128)
+                vscale[idx] = a.vs[(plane * a.n_blocks + jb) * DV + idx];
+            for (int idx = threadIdx.x; idx < D; idx += 128)
+                mu[idx] = a.kmean[(plane * a.n_blocks + jb) * D + idx];
+        }
+        __syncthreads();
+        if (causal && j0 > i_warp_max) continue;  // every key of the block is masked for this warp
+
+        // shift = (dQ * Qhat) . mean, per query row: each lane covers its own code bytes
+        float sh0 = 0.f, sh1 = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < D32; ++ks)
+#pragma unroll
+            for (int half = 0; half < 2; ++half)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float mv = mu[32 * ks + 16 * half + 4 * t + e];
+                    sh0 = fmaf((float)(int8_t)(qa[ks][2 * half] >> (8 * e)) * dq0, mv, sh0);
+                    sh1 = fmaf((float)(int8_t)(qa[ks][2 * half + 1] >> (8 * e)) * dq1, mv, sh1);
+                }
+        sh0 += __shfl_xor_sync(0xffffffffu, sh0, 1);
+        sh0 += __shfl_xor_sync(0xffffffffu, sh0, 2);
+        sh1 += __shfl_xor_sync(0xffffffffu, sh1, 1);
+        sh1 += __shfl_xor_sync(0xffffffffu, sh1, 2);
+
+        // S = Qhat Khat^T
+        int acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0;
+            const uint8_t *kr = Ks + (8 * nt + g) * KP + 4 * t;
+#pragma unroll
+            for (int ks = 0; ks < D32; ++ks)
+                mma_s8(acc[nt], qa[ks], *reinterpret_cast<const int *>(kr + 32 * ks),
+                       *reinterpret_cast<const int *>(kr + 32 * ks + 16));
+        }
+        // scores and the new row maxima.  Only the block on the diagonal, the last block of a
+        // ragged sequence and a warp with rows past the end need the per-element mask.
+        float mn0 = m0, mn1 = m1;
+        const bool masked = kj < BLK || !v0 || !v1 || (causal && j0 + BLK - 1 > q0);
+        if (masked) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int kk = 8 * nt + 2 * t + e, j = j0 + kk;
+                    const float ksc = kscale[kk];
+                    float s0 = (float)acc[nt][e] * dq0 * ksc + sh0;
+                    float s1 = (float)acc[nt][2 + e] * dq1 * ksc + sh1;
+                    if (kk >= kj || !v0 || (causal && j > i0)) s0 = -INFINITY;
+                    if (kk >= kj || !v1 || (causal && j > i1)) s1 = -INFINITY;
+                    acc[nt][e] = __float_as_int(s0);
+                    acc[nt][2 + e] = __float_as_int(s1);
+                    mn0 = fmaxf(mn0, s0);
+                    mn1 = fmaxf(mn1, s1);
+                }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const float2 ksc = *reinterpret_cast<const float2 *>(kscale + 8 * nt + 2 * t);
+                const float s00 = (float)acc[nt][0] * dq0 * ksc.x + sh0;
+                const float s01 = (float)acc[nt][1] * dq0 * ksc.y + sh0;
+                const float s10 = (float)acc[nt][2] * dq1 * ksc.x + sh1;
+                const float s11 = (float)acc[nt][3] * dq1 * ksc.y + sh1;
+                acc[nt][0] = __float_as_int(s00);
+                acc[nt][1] = __float_as_int(s01);
+                acc[nt][2] = __float_as_int(s10);
+                acc[nt][3] = __float_as_int(s11);
+                mn0 = fmaxf(mn0, fmaxf(s00, s01));
+                mn1 = fmaxf(mn1, fmaxf(s10, s11));
+            }
+        }
+        mn0 = fmaxf(mn0, __shfl_xor_sync(0xffffffffu, mn0, 1));
+        mn0 = fmaxf(mn0, __shfl_xor_sync(0xffffffffu, mn0, 2));
+        mn1 = fmaxf(mn1, __shfl_xor_sync(0xffffffffu, mn1, 1));
+        mn1 = fmaxf(mn1, __shfl_xor_sync(0xffffffffu, mn1, 2));
+        const float alpha0 = (mn0 == -INFINITY) ? 0.f : expf(m0 - mn0);
+        const float alpha1 = (mn1 == -INFINITY) ? 0.f : expf(m1 - mn1);
+        // P, its sum, its codes: pa[slab] is the A fragment of the slab's 32 keys
+        int pa[BLK32][4];
+        float es0 = 0.f, es1 = 0.f;
+#pragma unroll
+        for (int sl = 0; sl < BLK32; ++sl)
+#pragma unroll
+            for (int pair = 0; pair < 2; ++pair) {
+                int w0 = 0, w1 = 0;
+#pragma unroll
+                for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int nt = 4 * sl + 2 * pair + jj;
+                        const float p0 = (mn0 == -INFINITY) ? 0.f : expf(__int_as_float(acc[nt][e]) - mn0);
+                        const float p1 = (mn1 == -INFINITY) ? 0.f : expf(__int_as_float(acc[nt][2 + e]) - mn1);
+                        es0 += p0;
+                        es1 += p1;
+                        // p is in [0, 1]: 127 p needs no clamp, and the conversion rounds to
+                        // nearest even like rint
+                        const int c0 = __float2int_rn(p0 * 127.f);
+                        const int c1 = __float2int_rn(p1 * 127.f);
+                        w0 |= c0 << (8 * (2 * jj + e));
+                        w1 |= c1 << (8 * (2 * jj + e));
+                    }
+                pa[sl][2 * pair] = w0;
+                pa[sl][2 * pair + 1] = w1;
+            }
+        // PV, one 8-channel tile at a time
+#pragma unroll
+        for (int nv = 0; nv < DV8; ++nv) {
+            int pv[4] = {0, 0, 0, 0};
+            const uint8_t *vr = Vs + (8 * nv + g) * VP + 4 * t;
+#pragma unroll
+            for (int sl = 0; sl < BLK32; ++sl)
+                mma_s8(pv, pa[sl], *reinterpret_cast<const int *>(vr + 32 * sl),
+                       *reinterpret_cast<const int *>(vr + 32 * sl + 16));
+            const float vd0 = vscale[8 * nv + 2 * t], vd1 = vscale[8 * nv + 2 * t + 1];
+            o[nv][0] = alpha0 * o[nv][0] + (float)pv[0] * (1.0f / 127.0f) * vd0;
+            o[nv][1] = alpha0 * o[nv][1] + (float)pv[1] * (1.0f / 127.0f) * vd1;
+            o[nv][2] = alpha1 * o[nv][2] + (float)pv[2] * (1.0f / 127.0f) * vd0;
+            o[nv][3] = alpha1 * o[nv][3] + (float)pv[3] * (1.0f / 127.0f) * vd1;
+        }
+        l0 = alpha0 * l0 + es0;
+        l1 = alpha1 * l1 + es1;
+        if (mn0 != -INFINITY) m0 = mn0;
+        if (mn1 != -INFINITY) m1 = mn1;
+    }
+    // each lane summed P over its own columns only
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+#pragma unroll
+    for (int nv = 0; nv < DV8; ++nv) {
+        const int c = 8 * nv + 2 * t;
+        if (v0)
+            *reinterpret_cast<float2 *>(a.out + (row_base + i0) * DV + c) =
+                make_float2(o[nv][0] / l0, o[nv][1] / l0);
+        if (v1)
+            *reinterpret_cast<float2 *>(a.out + (row_base + i1) * DV + c) =
+                make_float2(o[nv][2] / l1, o[nv][3] / l1);
+    }
+}
+
 // ------------------------------------------------------------------ host side
 std::string shape_debug(const qk_attention_shape *s) {
     // Rust's `{:?}` of AttentionShape (gpu_attention.rs:402-411)
@@ -456,9 +699,102 @@ qk_status launch_sage(qk_ctx *c, const SageArgs &a, const AttnDims &dm, int caus
     return QK_OK;
 }
 
+template <int D32, int DV8, int BLK32>
+qk_status launch_sage_tc(qk_ctx *c, const SageArgs &a, const AttnDims &dm, int causal) {
+    constexpr int D = 32 * D32, DV = 8 * DV8, BLK = 32 * BLK32;
+    const size_t smem = BLK * (D + 16) + DV * (BLK + 16) + (BLK + DV + D) * sizeof(float);
+    if (smem > 48 * 1024)
+        QK_CUDA(cudaFuncSetAttribute(attention_sage_tc_kernel<D32, DV8, BLK32>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)qk::ceil_div(dm.Sq, 64), dm.H, dm.B);
+    attention_sage_tc_kernel<D32, DV8, BLK32><<<grid, 128, smem, c->stream>>>(a, dm, causal);
+    QK_CUDA(cudaGetLastError());
+    c->launches++;
+    return QK_OK;
+}
+
+// The tensor-core kernel is instantiated for the head sizes and Sage blocks that occur in
+// practice; anything else takes the dp4a kernel.
+bool sage_tc_eligible(const AttnDims &dm, size_t block) {
+    return (dm.d == 64 || dm.d == 128) && dm.dv == dm.d && (block == 32 || block == 64 || block == 128);
+}
+
+template <int D32>
+qk_status launch_sage_tc_block(qk_ctx *c, const SageArgs &a, const AttnDims &dm, int causal) {
+    if (a.block == 32) return launch_sage_tc<D32, 4 * D32, 1>(c, a, dm, causal);
+    if (a.block == 64) return launch_sage_tc<D32, 4 * D32, 2>(c, a, dm, causal);
+    return launch_sage_tc<D32, 4 * D32, 4>(c, a, dm, causal);
+}
+
 }  // namespace
 
 namespace qk {
+
+// Device-buffer form of the Sage face: quantisers, then the main kernel.  `scratch` holds the
+// codes and scales (sage_scratch_bytes of it).
+size_t sage_scratch_bytes(const qk_attention_shape *s, size_t block_size) {
+    const AttnDims dm = dims_of(s);
+    const size_t S = dm.Skv;
+    if (block_size > S) block_size = S;
+    const size_t n_blocks = qk::ceil_div(S, block_size);
+    const size_t widest = dm.d > dm.dv ? dm.d : dm.dv;
+    const size_t wpl = widest <= 16 ? 1 : widest <= 64 ? 4 : widest <= 128 ? 8 : 16;
+    const size_t dpad = wpl * 16, bpad = qk::ceil_div(block_size, kTK) * kTK;
+    const size_t planes = (size_t)dm.B * dm.KV, qrows = (size_t)dm.B * dm.H * dm.Sq;
+    auto up = [](size_t n) { return (n + 255) / 256 * 256; };
+    return up(qrows * dpad) + up(qrows * 4) + up(planes * S * dpad) + up(planes * S * 4) +
+           up(planes * n_blocks * dm.d * 4) + up(planes * n_blocks * dm.dv * bpad) +
+           up(planes * n_blocks * dm.dv * 4);
+}
+
+qk_status attention_sage_dev(qk_ctx *c, const float *dq, const float *dk, const float *dv,
+                             float *out, uint8_t *scratch, const qk_attention_shape *shape,
+                             int causal, size_t block_size) {
+    const AttnDims dm = dims_of(shape);
+    const size_t S = dm.Skv;
+    if (block_size > S) block_size = S;  // one block covers the whole sequence either way
+    const size_t n_blocks = qk::ceil_div(S, block_size);
+    const size_t widest = dm.d > dm.dv ? dm.d : dm.dv;
+    const size_t wpl = widest <= 16 ? 1 : widest <= 64 ? 4 : widest <= 128 ? 8 : 16;
+    const size_t dpad = wpl * 16;                       // four lanes x WPL words x four codes
+    const size_t bpad = qk::ceil_div(block_size, kTK) * kTK;  // keys of a block, padded to the tile
+    const size_t planes = (size_t)dm.B * dm.KV, qrows = (size_t)dm.B * dm.H * dm.Sq;
+    auto up = [](size_t n) { return (n + 255) / 256 * 256; };
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o2 = off; off += up(bytes); return o2; };
+    const size_t o_qc = take(qrows * dpad), o_qs = take(qrows * 4);
+    const size_t o_kc = take(planes * S * dpad), o_ks = take(planes * S * 4);
+    const size_t o_km = take(planes * n_blocks * dm.d * 4);
+    const size_t o_vc = take(planes * n_blocks * dm.dv * bpad), o_vs = take(planes * n_blocks * dm.dv * 4);
+    uint8_t *base = scratch;
+    const bool tc = c->sage_kernel != 0 && sage_tc_eligible(dm, block_size);
+    const float inv_sqrt_d = 1.0f / sqrtf((float)dm.d);  // gpu_attention.rs:720
+    sage_quant_q_kernel<<<(unsigned)qk::ceil_div(qrows, 8), 256, 0, c->stream>>>(
+        dq, (int8_t *)(base + o_qc), (float *)(base + o_qs), (uint32_t)qrows, dm.d, (uint32_t)dpad,
+        inv_sqrt_d);
+    QK_CUDA(cudaGetLastError());
+    dim3 kgrid((unsigned)n_blocks, (unsigned)planes);
+    sage_quant_k_kernel<<<kgrid, 128, dm.d * sizeof(float), c->stream>>>(
+        dk, (int8_t *)(base + o_kc), (float *)(base + o_ks), (float *)(base + o_km), (uint32_t)S,
+        dm.d, (uint32_t)dpad, (uint32_t)block_size, (uint32_t)n_blocks);
+    QK_CUDA(cudaGetLastError());
+    sage_quant_v_kernel<<<kgrid, 128, 0, c->stream>>>(
+        dv, (int8_t *)(base + o_vc), (float *)(base + o_vs), (uint32_t)S, dm.dv,
+        (uint32_t)block_size, (uint32_t)bpad, (uint32_t)n_blocks, tc ? 1 : 0);
+    QK_CUDA(cudaGetLastError());
+    c->launches += 3;
+    SageArgs a{(const int8_t *)(base + o_qc), (const float *)(base + o_qs),
+               (const int8_t *)(base + o_kc), (const float *)(base + o_ks),
+               (const float *)(base + o_km),  (const int8_t *)(base + o_vc),
+               (const float *)(base + o_vs),  out,
+               (uint32_t)dpad, (uint32_t)bpad, (uint32_t)block_size, (uint32_t)n_blocks};
+    if (tc)
+        return dm.d == 64 ? launch_sage_tc_block<2>(c, a, dm, causal) : launch_sage_tc_block<4>(c, a, dm, causal);
+    if (wpl == 1) return launch_sage<1>(c, a, dm, causal);
+    if (wpl == 4) return launch_sage<4>(c, a, dm, causal);
+    if (wpl == 8) return launch_sage<8>(c, a, dm, causal);
+    return launch_sage<16>(c, a, dm, causal);
+}
 
 // Device-buffer form of the exact face (also used by the decoder path).
 qk_status attention_exact_dev(qk_ctx *c, const float *q, const float *k, const float *v,
@@ -511,60 +847,67 @@ qk_status qk_gpu_attention_sage(qk_ctx *ctx, const qk_attention_shape *shape, co
     if ((st = qk::resolve_ctx(ctx, &c)) != QK_OK) return st;
     std::lock_guard<std::mutex> lock(c->mu);
     QK_CUDA(cudaSetDevice(c->device));
-    const AttnDims dm = dims_of(shape);
-    const size_t S = dm.Skv;
-    if (block_size > S) block_size = S;  // one block covers the whole sequence either way
-    const size_t n_blocks = qk::ceil_div(S, block_size);
-    const size_t widest = dm.d > dm.dv ? dm.d : dm.dv;
-    const size_t wpl = widest <= 16 ? 1 : widest <= 64 ? 4 : widest <= 128 ? 8 : 16;
-    const size_t dpad = wpl * 16;                       // four lanes x WPL words x four codes
-    const size_t bpad = qk::ceil_div(block_size, kTK) * kTK;  // keys of a block, padded to the tile
-    const size_t planes = (size_t)dm.B * dm.KV, qrows = (size_t)dm.B * dm.H * dm.Sq;
     auto up = [](size_t n) { return (n + 255) / 256 * 256; };
     const size_t qb = q_len * 4, kb = k_len * 4, vb = v_len * 4, ob = out_len * 4;
-    // scratch: inputs, then codes and scales
-    size_t off = 0;
-    auto take = [&](size_t bytes) { size_t o2 = off; off += up(bytes); return o2; };
-    const size_t o_q = take(qb), o_k = take(kb), o_v = take(vb);
-    const size_t o_qc = take(qrows * dpad), o_qs = take(qrows * 4);
-    const size_t o_kc = take(planes * S * dpad), o_ks = take(planes * S * 4);
-    const size_t o_km = take(planes * n_blocks * dm.d * 4);
-    const size_t o_vc = take(planes * n_blocks * dm.dv * bpad), o_vs = take(planes * n_blocks * dm.dv * 4);
-    if ((st = c->d_in.reserve(off)) != QK_OK) return st;
+    const size_t o_q = 0, o_k = up(qb), o_v = o_k + up(kb), o_scratch = o_v + up(vb);
+    if ((st = c->d_in.reserve(o_scratch + qk::sage_scratch_bytes(shape, block_size))) != QK_OK) return st;
     if ((st = c->d_out.reserve(ob)) != QK_OK) return st;
     uint8_t *base = (uint8_t *)c->d_in.ptr;
     float *dq = (float *)(base + o_q), *dk = (float *)(base + o_k), *dv = (float *)(base + o_v);
     QK_CUDA(cudaMemcpyAsync(dq, query, qb, cudaMemcpyHostToDevice, c->stream));
     QK_CUDA(cudaMemcpyAsync(dk, key, kb, cudaMemcpyHostToDevice, c->stream));
     QK_CUDA(cudaMemcpyAsync(dv, value, vb, cudaMemcpyHostToDevice, c->stream));
-    const float inv_sqrt_d = 1.0f / sqrtf((float)dm.d);  // gpu_attention.rs:720
-    sage_quant_q_kernel<<<(unsigned)qk::ceil_div(qrows, 8), 256, 0, c->stream>>>(
-        dq, (int8_t *)(base + o_qc), (float *)(base + o_qs), (uint32_t)qrows, dm.d, (uint32_t)dpad,
-        inv_sqrt_d);
-    QK_CUDA(cudaGetLastError());
-    dim3 kgrid((unsigned)n_blocks, (unsigned)planes);
-    sage_quant_k_kernel<<<kgrid, 128, dm.d * sizeof(float), c->stream>>>(
-        dk, (int8_t *)(base + o_kc), (float *)(base + o_ks), (float *)(base + o_km), (uint32_t)S,
-        dm.d, (uint32_t)dpad, (uint32_t)block_size, (uint32_t)n_blocks);
-    QK_CUDA(cudaGetLastError());
-    sage_quant_v_kernel<<<kgrid, 128, 0, c->stream>>>(
-        dv, (int8_t *)(base + o_vc), (float *)(base + o_vs), (uint32_t)S, dm.dv,
-        (uint32_t)block_size, (uint32_t)bpad, (uint32_t)n_blocks);
-    QK_CUDA(cudaGetLastError());
-    c->launches += 3;
-    SageArgs a{(const int8_t *)(base + o_qc), (const float *)(base + o_qs),
-               (const int8_t *)(base + o_kc), (const float *)(base + o_ks),
-               (const float *)(base + o_km),  (const int8_t *)(base + o_vc),
-               (const float *)(base + o_vs),  (float *)c->d_out.ptr,
-               (uint32_t)dpad, (uint32_t)bpad, (uint32_t)block_size, (uint32_t)n_blocks};
-    if (wpl == 1) st = launch_sage<1>(c, a, dm, causal != 0);
-    else if (wpl == 4) st = launch_sage<4>(c, a, dm, causal != 0);
-    else if (wpl == 8) st = launch_sage<8>(c, a, dm, causal != 0);
-    else st = launch_sage<16>(c, a, dm, causal != 0);
-    if (st != QK_OK) return st;
+    if ((st = qk::attention_sage_dev(c, dq, dk, dv, (float *)c->d_out.ptr, base + o_scratch, shape,
+                                     causal != 0, block_size)) != QK_OK)
+        return st;
     QK_CUDA(cudaMemcpyAsync(out, c->d_out.ptr, ob, cudaMemcpyDeviceToHost, c->stream));
     QK_CUDA(cudaStreamSynchronize(c->stream));
     return QK_OK;
+}
+
+qk_status qk_gpu_attention_dev(qk_ctx *ctx, const qk_attention_shape *shape, const float *q_dev,
+                               const float *k_dev, const float *v_dev, int32_t causal,
+                               float *out_dev) {
+    if (!shape) return qk::fail(QK_ERR_VALUE, "attention shape is null");
+    const size_t q_len = shape->batch * shape->n_heads * shape->seq_q * shape->head_dim;
+    const size_t k_len = shape->batch * shape->n_kv_heads * shape->seq_kv * shape->head_dim;
+    const size_t v_len = shape->batch * shape->n_kv_heads * shape->seq_kv * shape->val_dim;
+    const size_t o_len = shape->batch * shape->n_heads * shape->seq_q * shape->val_dim;
+    qk_status st = validate_attention(shape, q_len, k_len, v_len, false, 0, o_len);
+    if (st != QK_OK) return st;
+    qk_ctx *c;
+    if ((st = qk::resolve_ctx(ctx, &c)) != QK_OK) return st;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    return qk::attention_exact_dev(c, q_dev, k_dev, v_dev, out_dev, shape, causal != 0);
+}
+
+qk_status qk_gpu_attention_sage_dev(qk_ctx *ctx, const qk_attention_shape *shape,
+                                    const float *q_dev, const float *k_dev, const float *v_dev,
+                                    int32_t causal, size_t block_size, float *out_dev) {
+    if (!shape) return qk::fail(QK_ERR_VALUE, "attention shape is null");
+    const size_t q_len = shape->batch * shape->n_heads * shape->seq_q * shape->head_dim;
+    const size_t k_len = shape->batch * shape->n_kv_heads * shape->seq_kv * shape->head_dim;
+    const size_t v_len = shape->batch * shape->n_kv_heads * shape->seq_kv * shape->val_dim;
+    const size_t o_len = shape->batch * shape->n_heads * shape->seq_q * shape->val_dim;
+    qk_status st = validate_attention(shape, q_len, k_len, v_len, true, block_size, o_len);
+    if (st != QK_OK) return st;
+    qk_ctx *c;
+    if ((st = qk::resolve_ctx(ctx, &c)) != QK_OK) return st;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    if ((st = c->d_in.reserve(qk::sage_scratch_bytes(shape, block_size))) != QK_OK) return st;
+    return qk::attention_sage_dev(c, q_dev, k_dev, v_dev, out_dev, (uint8_t *)c->d_in.ptr, shape,
+                                  causal != 0, block_size);
+}
+
+int32_t qk_set_sage_kernel(qk_ctx *ctx, int32_t which) {
+    qk_ctx *c;
+    if (qk::resolve_ctx(ctx, &c) != QK_OK) return -1;
+    std::lock_guard<std::mutex> lock(c->mu);
+    const int32_t before = c->sage_kernel;
+    if (which == 0 || which == 1) c->sage_kernel = which;
+    return before;
 }
 
 }  // extern "C"

@@ -151,8 +151,31 @@ def _gpu_attention_sage(self, shape: AttentionShape, query, key, value, causal: 
     return _attention(self, "qk_gpu_attention_sage", shape, query, key, value, causal, block_size)
 
 
+def _gpu_attention_dev(self, shape: AttentionShape, q_ptr: int, k_ptr: int, v_ptr: int,
+                       causal: bool, out_ptr: int, block_size: int | None = None) -> None:
+    """Either attention face on float32 device buffers, asynchronous on the context's stream
+    (``block_size`` given: the Sage face)."""
+    st = _ShapeStruct(shape.batch, shape.n_heads, shape.n_kv_heads, shape.seq_q, shape.seq_kv,
+                      shape.head_dim, shape.val_dim)
+    ptrs = [ctypes.c_void_p(p) for p in (q_ptr, k_ptr, v_ptr)]
+    if block_size is None:
+        check(_lib.lib().qk_gpu_attention_dev(self._h, ctypes.byref(st), *ptrs, int(bool(causal)),
+                                              ctypes.c_void_p(out_ptr)))
+    else:
+        check(_lib.lib().qk_gpu_attention_sage_dev(self._h, ctypes.byref(st), *ptrs,
+                                                   int(bool(causal)), int(block_size),
+                                                   ctypes.c_void_p(out_ptr)))
+
+
+def _set_sage_kernel(self, which: int) -> int:
+    """1: INT8 tensor-core Sage kernel where the shape allows (default); 0: dp4a kernel."""
+    return int(_lib.lib().qk_set_sage_kernel(self._h, int(which)))
+
+
 GpuContext.attention = _gpu_attention
 GpuContext.attention_sage = _gpu_attention_sage
+GpuContext.attention_dev = _gpu_attention_dev
+GpuContext.set_sage_kernel = _set_sage_kernel
 
 
 class PackedLayer:

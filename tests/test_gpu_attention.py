@@ -180,3 +180,50 @@ def test_sage_config2_shape_row_sample(gpu_ctx):
                                     causal=True, rows=rows)
         cos, rel_l1, _ = anp.quality_metrics(gsub, exact)
         assert cos >= COS_MIN and rel_l1 <= REL_L1_MAX
+
+
+@pytest.mark.parametrize("case", [
+    # (batch, heads, kv heads, seq, head dim, block, causal)
+    (1, 4, 2, 200, 128, 64, True), (2, 2, 1, 129, 64, 32, True), (1, 2, 2, 300, 128, 128, False),
+    (1, 3, 1, 64, 64, 64, True), (1, 2, 1, 97, 128, 32, False)])
+def test_sage_tensor_core_kernel_matches_dp4a_kernel(gpu_ctx, case):
+    """The INT8 tensor-core Sage kernel and the dp4a kernel do the same arithmetic; only the
+    summation order of the float32 mean shift differs, which can move a P code on a tie."""
+    b, h, kvh, s, d, block, causal = case
+    rng = np.random.default_rng(sum(case[:6]))
+    q = rng.standard_normal((b, h, s, d), dtype=np.float32)
+    k = rng.standard_normal((b, kvh, s, d), dtype=np.float32) \
+        + (2.0 * rng.standard_normal((1, kvh, 1, d))).astype(np.float32)
+    v = rng.standard_normal((b, kvh, s, d), dtype=np.float32)
+    assert gpu_ctx.set_sage_kernel(0) == 1
+    try:
+        simt = run_sage(gpu_ctx, q, k, v, causal, block)
+    finally:
+        gpu_ctx.set_sage_kernel(1)
+    tc = run_sage(gpu_ctx, q, k, v, causal, block)
+    assert np.isfinite(tc).all()
+    assert np.median(np.abs(tc - simt)) <= 1e-6
+    assert np.abs(tc - simt).max() <= 2e-3 * np.abs(simt).max()
+    w32 = anp.attention_sage(q, k, v, causal=causal, block_size=block, ft=np.float32)
+    assert np.abs(tc - w32).max() <= 2e-3 * np.abs(w32).max()
+    assert np.array_equal(tc, run_sage(gpu_ctx, q, k, v, causal, block))
+
+
+def test_attention_on_device_buffers(gpu_ctx):
+    import torch
+    rng = np.random.default_rng(11)
+    b, h, kvh, s, d = 1, 4, 2, 160, 64
+    q = rng.standard_normal((b, h, s, d), dtype=np.float32)
+    k = rng.standard_normal((b, kvh, s, d), dtype=np.float32)
+    v = rng.standard_normal((b, kvh, s, d), dtype=np.float32)
+    sh = shape_of(q, k, v)
+    tq, tk, tv = (torch.from_numpy(x).cuda() for x in (q, k, v))
+    out = torch.zeros(b, h, s, d, device="cuda")
+    torch.cuda.synchronize()
+    gpu_ctx.attention_dev(sh, tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), True, out.data_ptr())
+    gpu_ctx.synchronize()
+    assert np.array_equal(out.cpu().numpy(), run_exact(gpu_ctx, q, k, v, True))
+    gpu_ctx.attention_dev(sh, tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), True, out.data_ptr(),
+                          block_size=32)
+    gpu_ctx.synchronize()
+    assert np.array_equal(out.cpu().numpy(), run_sage(gpu_ctx, q, k, v, True, 32))
