@@ -62,7 +62,6 @@ struct qk_ctx {
     // error word of the asynchronous tensor-core kernels, read back by qk_gpu_synchronize
     qk_scratch d_err;
     bool err_armed = false;
-    uint32_t tc_epoch = 0;  // launch counter of the tensor-core kernels (never 0 in a launch)
     void *h_pinned = nullptr;
     size_t h_pinned_cap = 0;
     qk_status pinned(size_t bytes, void **out);

@@ -120,6 +120,38 @@ rope_cache_kernel(float *__restrict__ q, const float *__restrict__ k, const floa
     }
 }
 
+// A lane's DPL consecutive channels of one cache row as floats.  When the row is a whole
+// number of 16-byte pieces per lane (head_dim 128 in bfloat16: two pieces) the slice comes
+// in with 16-byte loads; the cache rows are 16-byte aligned because head_dim * sizeof(KV) is.
+template <typename KV, int DPL>
+__device__ __forceinline__ void load_row_slice(const KV *__restrict__ row, uint32_t sub, uint32_t d,
+                                               float (&out)[DPL]) {
+    constexpr int kPer = 16 / sizeof(KV);  // elements per 16-byte piece
+    if (DPL % kPer == 0 && d == 8u * DPL) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(row + sub * DPL);
+#pragma unroll
+        for (int piece = 0; piece < DPL / kPer; ++piece) {
+            const uint4 w = src[piece];
+            const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (sizeof(KV) == 2) {
+                    out[piece * 8 + 2 * i] = __uint_as_float(words[i] << 16);
+                    out[piece * 8 + 2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+                } else {
+                    out[piece * 4 + i] = __uint_as_float(words[i]);
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+            const uint32_t c = sub * DPL + e;
+            out[e] = c < d ? load_as_float<KV>(row, c) : 0.f;
+        }
+    }
+}
+
 // Split-KV decode attention: one query position per sequence against the cache.
 // grid (split, kv head, sequence); a block of 128 threads covers the keys
 // [split*chunk, min(len, (split+1)*chunk)) for all G = H/KV query heads of the kv head, so
@@ -158,12 +190,8 @@ decode_attention_kernel(const float *__restrict__ q, const KV *__restrict__ cach
     const KV *vb = cache_v + ((size_t)b * n_kv + kvh) * s_max * d;
     for (int j = j_begin + slot; j < j_end; j += kDecThreads / 8) {
         float kk[DPL], vv[DPL];
-#pragma unroll
-        for (int e = 0; e < DPL; ++e) {
-            uint32_t c = sub * DPL + e;
-            kk[e] = c < d ? load_as_float<KV>(kb, (size_t)j * d + c) : 0.f;
-            vv[e] = c < d ? load_as_float<KV>(vb, (size_t)j * d + c) : 0.f;
-        }
+        load_row_slice<KV, DPL>(kb + (size_t)j * d, sub, d, kk);
+        load_row_slice<KV, DPL>(vb + (size_t)j * d, sub, d, vv);
 #pragma unroll
         for (int gq = 0; gq < GQ; ++gq) {
             float dot = 0.f;
@@ -409,6 +437,116 @@ qk_status enter(qk_ctx *ctx, qk_ctx **c) {
 
 }  // namespace
 
+// ------------------------------------------------------------------ LM head for a batch
+// logits[token][v] = sum_k h[token][k] * W[v][k] for up to 64 tokens per pass, W bfloat16:
+// the head is read ONCE for all tokens (the warp-per-row kernel above re-reads it for
+// every eight).  bf16 tensor cores (mma.sync m16n8k16): a warp owns 16 vocabulary rows (the
+// M side, streamed straight from global memory in 16-byte loads), the tokens are the N side,
+// staged chunk by chunk in shared memory.  The float32 hidden state is split into two
+// bfloat16 terms (hi = bf16(h), lo = bf16(h - hi)), so the products are exact to 2^-17 even
+// when h is not bfloat16-valued (for bfloat16 serving lo is zero).  The k order inside a
+// 32-wide group is renamed (slot 2t, 2t+1 <- k 8t, 8t+1; slot 8+2t <- 8t+2; second MMA
+// 8t+4..7) so that one 16-byte load feeds two MMAs on either operand.
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int kHeadPitch = 96;  // bfloat16 elements per staged token row: 64 k + 32 pad (192 B)
+
+template <int NT>  // token tiles of eight
+__global__ void __launch_bounds__(128)
+lm_head_mma_kernel(const float *__restrict__ hidden, const uint16_t *__restrict__ weight,
+                   float *__restrict__ logits, uint32_t n_tokens, uint32_t vocab, uint32_t d,
+                   uint32_t vocab_stride) {
+    extern __shared__ __align__(16) uint16_t sm_head[];  // [2 buffers][hi, lo][8 NT][kHeadPitch]
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
+    const uint32_t tok0 = blockIdx.y * (8 * NT);
+    const uint32_t v_lo = min(blockIdx.x * 64 + warp * 16 + g, vocab - 1);
+    const uint32_t v_hi = min(blockIdx.x * 64 + warp * 16 + g + 8, vocab - 1);
+    const uint4 *row_lo = reinterpret_cast<const uint4 *>(weight + (size_t)v_lo * d) + t;
+    const uint4 *row_hi = reinterpret_cast<const uint4 *>(weight + (size_t)v_hi * d) + t;
+    const uint32_t n_chunks = d / 64;
+    constexpr uint32_t kBuf = 2 * 8 * NT * kHeadPitch;  // elements per buffer (hi and lo)
+
+    auto stage = [&](uint32_t chunk, uint32_t buf) {
+        uint16_t *hi = sm_head + buf * kBuf, *lo = hi + 8 * NT * kHeadPitch;
+        for (uint32_t idx = threadIdx.x; idx < 8 * NT * 16; idx += 128) {
+            const uint32_t tok = idx / 16, kq = idx % 16;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (tok0 + tok < n_tokens)
+                x = *reinterpret_cast<const float4 *>(hidden + (size_t)(tok0 + tok) * d + chunk * 64 + kq * 4);
+            const float xs[4] = {x.x, x.y, x.z, x.w};
+            uint32_t h[4], l[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                h[i] = float_to_bf16_bits(xs[i]);
+                l[i] = float_to_bf16_bits(xs[i] - bf16_bits_to_float((uint16_t)h[i]));
+            }
+            *reinterpret_cast<uint2 *>(hi + tok * kHeadPitch + kq * 4) =
+                make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+            *reinterpret_cast<uint2 *>(lo + tok * kHeadPitch + kq * 4) =
+                make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
+        }
+    };
+
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    // the weights of the next chunk are in flight while this one is multiplied
+    uint4 wl[2], wh[2];
+    wl[0] = row_lo[0]; wl[1] = row_lo[4];
+    wh[0] = row_hi[0]; wh[1] = row_hi[4];
+    stage(0, 0);
+    __syncthreads();
+    for (uint32_t c = 0; c < n_chunks; ++c) {
+        const uint4 cl[2] = {wl[0], wl[1]}, ch[2] = {wh[0], wh[1]};
+        if (c + 1 < n_chunks) {
+            wl[0] = row_lo[(c + 1) * 8]; wl[1] = row_lo[(c + 1) * 8 + 4];
+            wh[0] = row_hi[(c + 1) * 8]; wh[1] = row_hi[(c + 1) * 8 + 4];
+            stage(c + 1, (c + 1) & 1);
+        }
+        const uint16_t *hi = sm_head + (c & 1) * kBuf, *lo = hi + 8 * NT * kHeadPitch;
+#pragma unroll
+        for (int gi = 0; gi < 2; ++gi) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint32_t off = (8 * nt + g) * kHeadPitch + gi * 32 + 8 * t;
+                const uint4 bh = *reinterpret_cast<const uint4 *>(hi + off);
+                const uint4 bl = *reinterpret_cast<const uint4 *>(lo + off);
+                mma_bf16(acc[nt], cl[gi].x, ch[gi].x, cl[gi].y, ch[gi].y, bh.x, bh.y);
+                mma_bf16(acc[nt], cl[gi].z, ch[gi].z, cl[gi].w, ch[gi].w, bh.z, bh.w);
+                mma_bf16(acc[nt], cl[gi].x, ch[gi].x, cl[gi].y, ch[gi].y, bl.x, bl.y);
+                mma_bf16(acc[nt], cl[gi].z, ch[gi].z, cl[gi].w, ch[gi].w, bl.z, bl.w);
+            }
+        }
+        __syncthreads();
+    }
+    const uint32_t v0 = blockIdx.x * 64 + warp * 16 + g;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const uint32_t tok = tok0 + 8 * nt + 2 * t + (e & 1), v = v0 + (e >> 1) * 8;
+            if (tok < n_tokens && v < vocab) logits[(size_t)tok * vocab_stride + v] = acc[nt][e];
+        }
+}
+
+template <int NT>
+void launch_lm_head_mma(qk_ctx *c, const float *hidden, const uint16_t *weight, float *logits,
+                        size_t n_tokens, size_t vocab, size_t d, size_t stride) {
+    const size_t smem = 2 * 2 * 8 * NT * kHeadPitch * sizeof(uint16_t);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(lm_head_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    dim3 grid((unsigned)qk::ceil_div(vocab, 64), (unsigned)qk::ceil_div(n_tokens, 8 * NT));
+    lm_head_mma_kernel<NT><<<grid, 128, smem, c->stream>>>(hidden, weight, logits, (uint32_t)n_tokens,
+                                                          (uint32_t)vocab, (uint32_t)d, (uint32_t)stride);
+}
+
 extern "C" {
 
 qk_status qk_rmsnorm(qk_ctx *ctx, const float *x, const float *residual, const float *weight,
@@ -561,6 +699,13 @@ qk_status qk_lm_head(qk_ctx *ctx, const float *hidden, const void *weight, int32
             lm_head_kernel<float, 8><<<blocks, 256, 0, c->stream>>>(
                 hidden, (const float *)weight, logits, (uint32_t)n_tokens, (uint32_t)vocab,
                 (uint32_t)d, (uint32_t)logits_stride);
+    } else if (weight_dtype == QK_BF16 && n_tokens >= 8 && d % 64 == 0) {
+        // a batch: one pass over the head on the bf16 tensor cores
+        const uint16_t *w = (const uint16_t *)weight;
+        if (n_tokens <= 8) launch_lm_head_mma<1>(c, hidden, w, logits, n_tokens, vocab, d, logits_stride);
+        else if (n_tokens <= 16) launch_lm_head_mma<2>(c, hidden, w, logits, n_tokens, vocab, d, logits_stride);
+        else if (n_tokens <= 32) launch_lm_head_mma<4>(c, hidden, w, logits, n_tokens, vocab, d, logits_stride);
+        else launch_lm_head_mma<8>(c, hidden, w, logits, n_tokens, vocab, d, logits_stride);
     } else if (weight_dtype == QK_BF16) {
         if (n_tokens == 1)
             lm_head_kernel<uint16_t, 1><<<blocks, 256, 0, c->stream>>>(

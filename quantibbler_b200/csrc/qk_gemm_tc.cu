@@ -125,8 +125,7 @@ struct GemmArgs {
     uint32_t row_tiles;    // tile t covers row tile t % row_tiles, token tile t / row_tiles
     uint32_t units;        // tiles x k_chunks: the work that is dealt out evenly to the CTAs
     float *partials;       // [CTAs][256][128] float32 accumulators of split tiles
-    uint32_t *flags;       // [CTAs] flags[i] == epoch: CTA i's partial is in place
-    uint32_t epoch;        // differs from launch to launch, so the flags need no reset
+    uint32_t *flags;       // [CTAs] flags[i] != 0: CTA i's partial is in place (its one reader clears it)
 };
 
 // CTA i of G works on units [i * units / G, (i + 1) * units / G), unit u being k-chunk
@@ -169,7 +168,7 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
     // This CTA's share of the work.  It is a run of consecutive units, so it is cut into
     // segments at tile borders: the rest of a tile another CTA began, whole tiles, the head of
     // a tile.  Only the first segment can start inside a tile; its accumulator goes to
-    // partials[this CTA] and flags[this CTA] is raised.  A segment that starts a tile is
+    // partials[this CTA] and flags[this CTA] is raised (its reader clears it again).  A segment that starts a tile is
     // finished here: if it stops short of the tile's end, the CTAs after this one hold the
     // rest as THEIR first segments, which they computed at the very start of the kernel, so
     // by now those partials are in place; they are added in CTA order (a fixed order, so the
@@ -331,11 +330,11 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
                     uint32_t seen = 0;
                     for (uint32_t i = 0; i < kWaitLimit; ++i) {
                         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(g.flags + j) : "memory");
-                        if (seen == g.epoch) break;
+                        if (seen) break;
                         if ((i & 255u) == 255u && *abort_flag) break;
                         __nanosleep(64);
                     }
-                    dead = seen != g.epoch;
+                    dead = seen == 0;
                 }
             }
             if (dead || !mbar_wait(&acc_full[acc], (seg >> 1) & 1, abort_flag)) {
@@ -416,12 +415,19 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[acc]);
+            if (last > blockIdx.x + 1) {
+                // every partial of this tile has been read: hand the flags back, cleared, for
+                // the next launch (this CTA is their only reader)
+                asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
+                if (warp == kEpilogueWarp0 && lane == 0)
+                    for (uint32_t j = blockIdx.x + 1; j < last; ++j) g.flags[j] = 0;
+            }
             if (kc0 != 0) {
                 // publish the partial: every writer fences, the four warps meet, one raises the flag
                 __threadfence();
                 asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
                 if (warp == kEpilogueWarp0 && lane == 0)
-                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(g.flags + blockIdx.x), "r"(g.epoch) : "memory");
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(g.flags + blockIdx.x), "r"(1u) : "memory");
             }
             u += len;
         }
@@ -569,13 +575,13 @@ qk_status qk_layer_apply_prefill(qk_ctx *ctx, const qk_layer *layer, const float
     uint32_t *flags = (uint32_t *)c->d_err.ptr + 64;  // after the error word's 256 bytes
     GemmArgs g1{layer->vbt, t, nullptr, nullptr, err, (uint32_t)n_tokens, (uint32_t)r,
                 (uint32_t)(kp1 / kBK), (uint32_t)layer->vbt_stride, (uint32_t)kp2, bn,
-                (uint32_t)rows1, (uint32_t)units1, partials, flags, ++c->tc_epoch};
+                (uint32_t)rows1, (uint32_t)units1, partials, flags};
     factorized_gemm_tc_kernel<false><<<grid1, kThreads, kSmemBytes, c->stream>>>(map1, g1);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     GemmArgs g2{layer->ub, y_dev, layer->s1, layer->bias, err, (uint32_t)n_tokens, (uint32_t)dout,
                 (uint32_t)(kp2 / kBK), (uint32_t)layer->ub_stride, (uint32_t)dout, bn,
-                (uint32_t)rows2, (uint32_t)units2, partials, flags, ++c->tc_epoch};
+                (uint32_t)rows2, (uint32_t)units2, partials, flags};
     factorized_gemm_tc_kernel<true><<<grid2, kThreads, kSmemBytes, c->stream>>>(map2, g2);
     QK_CUDA(cudaGetLastError());
     c->launches++;

@@ -42,6 +42,7 @@ class DecoderConfig:
     max_seq: int = 4096
     max_batch: int = 1
     n_splits: int = 0              # key splits of the decode attention (0 = choose)
+    gemm_min_batch: int = 16       # bfloat16 serving: batches this large take the tensor-core GEMM
 
 
 def rope_table(cfg: DecoderConfig) -> np.ndarray:
@@ -161,9 +162,10 @@ class Decoder:
                         for _ in range(cfg.n_layers)]
         self.cache_v = [torch.zeros(B, self.kv_loc, cfg.max_seq, hd, dtype=kv_t, device=dev)
                         for _ in range(cfg.n_layers)]
-        # enough blocks to cover the SMs about twice, but chunks of at least ~128 keys
-        self.n_splits = cfg.n_splits or max(1, min(32, (2 * 148) // max(1, B * self.kv_loc),
-                                                   max(1, cfg.max_seq // 128)))
+        # enough blocks of 128 threads to fill the SMs (about eight per SM), but chunks of at
+        # least ~128 keys
+        want = -(-8 * 148 // max(1, B * self.kv_loc))
+        self.n_splits = cfg.n_splits or max(1, min(32, want, max(1, cfg.max_seq // 128)))
         scratch = _lib.lib().qk_decode_attention_scratch(B, self.h_loc, hd, self.n_splits)
         self.att_scratch = torch.zeros(scratch // 4 + 4, **f32)
         self.cos_sin = dev_f32(rope_table(cfg))
@@ -205,12 +207,30 @@ class Decoder:
                 plan["gate"] = LayerPlan(ctx, inst(["gate"], self.h, [self.g]))
                 plan["up"] = LayerPlan(ctx, inst(["up"], self.h, [self.u]))
             self.plans.append(plan)
+        # a large enough batch is a real contraction: the tcgen05 GEMM expands each weight bit
+        # once for all tokens, the GEMV forms would do it once per token
+        self.use_gemm = cfg.serving == "bfloat16" and B >= cfg.gemm_min_batch
         self.graph = None
 
     # ------------------------------------------------------------------ one step
     def _all_reduce(self, t):
         if self.tp_size > 1:
             self.torch.distributed.all_reduce(t, group=self.group)
+
+    def _linears(self, li: int, names, src, dsts) -> None:
+        """The named linears of layer ``li`` from ``src`` into ``dsts`` for the whole batch."""
+        B = self.cfg.max_batch
+        if self.use_gemm:
+            for name, dst in zip(names, dsts):
+                self.layers[li][name].apply_prefill(src.data_ptr(), B, dst.data_ptr())
+            return
+        plan = self.plans[li]
+        joint = {("k", "v"): "kv", ("gate", "up"): "gu"}.get(tuple(names))
+        if joint in plan:
+            plan[joint].apply()
+        else:
+            for name in names:
+                plan[name].apply()
 
     def step(self) -> None:
         """One decode step for the whole batch: reads ``token_ids``/``positions``/``kv_len``,
@@ -225,9 +245,8 @@ class Decoder:
             plan = self.plans[li]
             check(lib.qk_rmsnorm(c, _p(self.x), residual, _p(in_w), B, d, cfg.rms_eps,
                                  self.serving_tag, _p(self.x), _p(self.h)))
-            for name in ("q", "kv", "k", "v"):
-                if name in plan:
-                    plan[name].apply()
+            self._linears(li, ["q"], self.h, [self.q])
+            self._linears(li, ["k", "v"], self.h, [self.k, self.v])
             check(lib.qk_rope_cache(c, _p(self.q), _p(self.k), _p(self.v), _p(self.cos_sin),
                                     _p(self.positions), _p(self.seq_index), _p(self.cache_k[li]),
                                     _p(self.cache_v[li]), self.kv_tag, B, self.h_loc, self.kv_loc,
@@ -236,15 +255,13 @@ class Decoder:
                                           self.kv_tag, _p(self.kv_len), B, self.h_loc, self.kv_loc,
                                           hd, cfg.max_seq, self.n_splits, _p(self.att_scratch),
                                           _p(self.attn)))
-            plan["o"].apply()
+            self._linears(li, ["o"], self.attn, [self.delta])
             self._all_reduce(self.delta)
             check(lib.qk_rmsnorm(c, _p(self.x), _p(self.delta), _p(post_w), B, d, cfg.rms_eps,
                                  self.serving_tag, _p(self.x), _p(self.h)))
-            for name in ("gu", "gate", "up"):
-                if name in plan:
-                    plan[name].apply()
+            self._linears(li, ["gate", "up"], self.h, [self.g, self.u])
             check(lib.qk_swiglu(c, _p(self.g), _p(self.u), B * self.ff_loc, _p(self.a)))
-            plan["down"].apply()
+            self._linears(li, ["down"], self.a, [self.delta])
             self._all_reduce(self.delta)
             residual = _p(self.delta)
         check(lib.qk_rmsnorm(c, _p(self.x), residual, _p(self.final_norm), B, d, cfg.rms_eps,

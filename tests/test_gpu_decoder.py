@@ -146,3 +146,63 @@ def test_lm_head_and_first_max(gpu_ctx):
     got = idx.cpu().numpy()
     assert got[0] == 110 and got[1] == 100
     assert np.array_equal(got[2:], np.argmax(lg.cpu().numpy()[2:], axis=1) + 100)
+
+
+@pytest.mark.parametrize("tokens,vocab,d", [(8, 1000, 256), (13, 777, 128), (64, 2048, 512),
+                                            (70, 300, 64)])
+def test_lm_head_batched_tensor_core_form(gpu_ctx, tokens, vocab, d):
+    """Eight tokens or more take the bf16 tensor-core kernel that reads the head once; the
+    hidden state is arbitrary float32 (not bfloat16-valued), which the hi/lo split covers."""
+    import ctypes
+    import torch
+    from quantibbler_b200 import _lib
+    rng = np.random.default_rng(tokens + vocab)
+    h = rng.standard_normal((tokens, d)).astype(np.float32)
+    w = decoder_np._bf16(rng.standard_normal((vocab, d)).astype(np.float32))
+    th = torch.from_numpy(h).cuda()
+    tw = torch.from_numpy(w).cuda().to(torch.bfloat16)
+    stride = vocab + 5
+    logits = torch.full((tokens, stride), -7.0, device="cuda")
+    torch.cuda.synchronize()
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    _lib.check(_lib.lib().qk_lm_head(gpu_ctx.handle, p(th), p(tw), _lib.QK_BF16, tokens, vocab, d,
+                                     stride, p(logits)))
+    gpu_ctx.synchronize()
+    got = logits.cpu().numpy()
+    want = h.astype(np.float64) @ w.astype(np.float64).T
+    assert np.abs(got[:, :vocab] - want).max() <= 2e-5 * np.abs(want).max()
+    assert (got[:, vocab:] == -7.0).all()
+
+
+def test_large_batch_takes_the_tensor_core_gemm_and_lm_head(gpu_ctx):
+    """bfloat16 serving with a batch of 16: every linear goes through the tcgen05 GEMM and
+    the head through the batched tensor-core kernel; the result must agree with the GEMV
+    forms (same rounding points) and replay identically from a CUDA graph."""
+    import torch
+    cfg = tiny_cfg(serving="bfloat16", kv_dtype="bfloat16", max_batch=16)
+    weights = random_model(cfg, RANKS, seed=9)
+    first = [(7 * i + 3) % cfg.vocab for i in range(16)]
+    gemm = Decoder(gpu_ctx, cfg, weights)
+    assert gemm.use_gemm
+    gemv = Decoder(gpu_ctx, tiny_cfg(serving="bfloat16", kv_dtype="bfloat16", max_batch=16,
+                                     gemm_min_batch=10 ** 6), weights)
+    assert not gemv.use_gemm
+    for dec in (gemm, gemv):
+        dec.start(first, [0] * 16)
+    for _ in range(4):
+        for dec in (gemm, gemv):
+            dec.step()
+        gpu_ctx.synchronize()
+        a, b = gemm.logits.cpu().numpy(), gemv.logits.cpu().numpy()
+        assert np.abs(a - b).max() <= 3e-2 * np.abs(b).max()
+        assert np.array_equal(gemm.best_idx.cpu().numpy(), gemv.best_idx.cpu().numpy())
+        for dec in (gemm, gemv):
+            dec.advance()
+    want_t, _ = reference_run(cfg, weights, first[:3], 2, decoder_np._bf16)
+    eager_tokens = gemm.decode(3)
+    graph = Decoder(gpu_ctx, cfg, weights)
+    graph.capture()
+    graph.start(first, [0] * 16)
+    got = graph.decode(2)
+    assert np.array_equal(got[:, :3], want_t)
+    del eager_tokens
