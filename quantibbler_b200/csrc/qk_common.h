@@ -61,6 +61,7 @@ struct qk_ctx {
     qk_scratch d_z, d_t, d_ptrs;
     // error word of the asynchronous tensor-core kernels, read back by qk_gpu_synchronize
     qk_scratch d_err;
+    qk_scratch d_head;  // the LM head's bfloat16 split of the hidden state
     bool err_armed = false;
     void *h_pinned = nullptr;
     size_t h_pinned_cap = 0;

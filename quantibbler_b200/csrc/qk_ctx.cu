@@ -141,6 +141,7 @@ void qk_gpu_free(qk_ctx *ctx) {
     ctx->d_t.release();
     ctx->d_ptrs.release();
     ctx->d_err.release();
+    ctx->d_head.release();
     if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
     delete ctx;
 }

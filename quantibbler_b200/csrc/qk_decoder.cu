@@ -120,37 +120,60 @@ rope_cache_kernel(float *__restrict__ q, const float *__restrict__ k, const floa
     }
 }
 
-// A lane's DPL consecutive channels of one cache row as floats.  When the row is a whole
-// number of 16-byte pieces per lane (head_dim 128 in bfloat16: two pieces) the slice comes
-// in with 16-byte loads; the cache rows are 16-byte aligned because head_dim * sizeof(KV) is.
+// A lane's DPL consecutive channels of one cache row.  When the slice is a whole number of
+// 16-byte pieces (head_dim 128: two pieces in bfloat16, four in float32) it is fetched with
+// 16-byte loads into `raw` and unpacked later, so that the next key's slice can be in
+// flight while this one is used; the cache rows are 16-byte aligned because
+// head_dim * sizeof(KV) is.  Otherwise element by element.
 template <typename KV, int DPL>
-__device__ __forceinline__ void load_row_slice(const KV *__restrict__ row, uint32_t sub, uint32_t d,
-                                               float (&out)[DPL]) {
-    constexpr int kPer = 16 / sizeof(KV);  // elements per 16-byte piece
-    if (DPL % kPer == 0 && d == 8u * DPL) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(row + sub * DPL);
+struct RowSlice {
+    static constexpr int kPer = 16 / sizeof(KV);  // elements per 16-byte piece
+    static constexpr bool kVec = DPL % kPer == 0;
+    static constexpr int kPieces = kVec ? DPL / kPer : 1;
+    uint4 raw[kPieces];
+    float scalar[kVec ? 1 : DPL];
+
+    __device__ __forceinline__ void load(const KV *__restrict__ row, uint32_t sub, uint32_t d, bool vec) {
+        if (kVec && vec) {
+            const uint4 *src = reinterpret_cast<const uint4 *>(row + sub * DPL);
 #pragma unroll
-        for (int piece = 0; piece < DPL / kPer; ++piece) {
-            const uint4 w = src[piece];
-            const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+            for (int piece = 0; piece < kPieces; ++piece) raw[piece] = src[piece];
+        } else if (!kVec) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if (sizeof(KV) == 2) {
-                    out[piece * 8 + 2 * i] = __uint_as_float(words[i] << 16);
-                    out[piece * 8 + 2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
-                } else {
-                    out[piece * 4 + i] = __uint_as_float(words[i]);
-                }
+            for (int e = 0; e < DPL; ++e) {
+                const uint32_t c = sub * DPL + e;
+                scalar[e] = c < d ? load_as_float<KV>(row, c) : 0.f;
             }
         }
-    } else {
+    }
+    __device__ __forceinline__ void unpack(const KV *__restrict__ row, uint32_t sub, uint32_t d, bool vec,
+                                           float (&out)[DPL]) const {
+        if (kVec && vec) {
 #pragma unroll
-        for (int e = 0; e < DPL; ++e) {
-            const uint32_t c = sub * DPL + e;
-            out[e] = c < d ? load_as_float<KV>(row, c) : 0.f;
+            for (int piece = 0; piece < kPieces; ++piece) {
+                const uint32_t words[4] = {raw[piece].x, raw[piece].y, raw[piece].z, raw[piece].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (sizeof(KV) == 2) {
+                        out[piece * 8 + 2 * i] = __uint_as_float(words[i] << 16);
+                        out[piece * 8 + 2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+                    } else {
+                        out[piece * 4 + i] = __uint_as_float(words[i]);
+                    }
+                }
+            }
+        } else if (kVec) {  // vector-capable type, but this head_dim is not 8 * DPL
+#pragma unroll
+            for (int e = 0; e < DPL; ++e) {
+                const uint32_t c = sub * DPL + e;
+                out[e] = c < d ? load_as_float<KV>(row, c) : 0.f;
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < DPL; ++e) out[e] = scalar[e];
         }
     }
-}
+};
 
 // Split-KV decode attention: one query position per sequence against the cache.
 // grid (split, kv head, sequence); a block of 128 threads covers the keys
@@ -188,10 +211,21 @@ decode_attention_kernel(const float *__restrict__ q, const KV *__restrict__ cach
     }
     const KV *kb = cache_k + ((size_t)b * n_kv + kvh) * s_max * d;
     const KV *vb = cache_v + ((size_t)b * n_kv + kvh) * s_max * d;
+    const bool vec = d == 8u * DPL;
+    RowSlice<KV, DPL> k_next, v_next;
+    if (j_begin + (int)slot < j_end) {
+        k_next.load(kb + (size_t)(j_begin + slot) * d, sub, d, vec);
+        v_next.load(vb + (size_t)(j_begin + slot) * d, sub, d, vec);
+    }
     for (int j = j_begin + slot; j < j_end; j += kDecThreads / 8) {
         float kk[DPL], vv[DPL];
-        load_row_slice<KV, DPL>(kb + (size_t)j * d, sub, d, kk);
-        load_row_slice<KV, DPL>(vb + (size_t)j * d, sub, d, vv);
+        k_next.unpack(kb + (size_t)j * d, sub, d, vec, kk);
+        v_next.unpack(vb + (size_t)j * d, sub, d, vec, vv);
+        const int jn = j + kDecThreads / 8;
+        if (jn < j_end) {  // the next key's slice is in flight during this key's arithmetic
+            k_next.load(kb + (size_t)jn * d, sub, d, vec);
+            v_next.load(vb + (size_t)jn * d, sub, d, vec);
+        }
 #pragma unroll
         for (int gq = 0; gq < GQ; ++gq) {
             float dot = 0.f;
@@ -458,9 +492,32 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 
 constexpr int kHeadPitch = 96;  // bfloat16 elements per staged token row: 64 k + 32 pad (192 B)
 
+// hidden [tokens][d] float32 -> hi, lo [tokens][d] bfloat16 (hi = bf16(h), lo = bf16(h - hi));
+// *any_lo is set when some lo is not zero, i.e. when the hidden state is not bfloat16-valued.
+__global__ void split_hidden_kernel(const float *__restrict__ hidden, uint16_t *__restrict__ hi,
+                                    uint16_t *__restrict__ lo, uint32_t *__restrict__ any_lo,
+                                    size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float x = hidden[i];
+    const uint16_t h = float_to_bf16_bits(x);
+    const uint16_t l = float_to_bf16_bits(x - bf16_bits_to_float(h));
+    hi[i] = h;
+    lo[i] = l;
+    if (l & 0x7fffu) *any_lo = 1u;
+}
+
+__device__ __forceinline__ void cp_async_16(void *smem, const void *gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                     (uint32_t)__cvta_generic_to_shared(smem)),
+                 "l"(gmem)
+                 : "memory");
+}
+
 template <int NT>  // token tiles of eight
 __global__ void __launch_bounds__(128)
-lm_head_mma_kernel(const float *__restrict__ hidden, const uint16_t *__restrict__ weight,
+lm_head_mma_kernel(const uint16_t *__restrict__ hid_hi, const uint16_t *__restrict__ hid_lo,
+                   const uint32_t *__restrict__ any_lo, const uint16_t *__restrict__ weight,
                    float *__restrict__ logits, uint32_t n_tokens, uint32_t vocab, uint32_t d,
                    uint32_t vocab_stride) {
     extern __shared__ __align__(16) uint16_t sm_head[];  // [2 buffers][hi, lo][8 NT][kHeadPitch]
@@ -472,26 +529,19 @@ lm_head_mma_kernel(const float *__restrict__ hidden, const uint16_t *__restrict_
     const uint4 *row_hi = reinterpret_cast<const uint4 *>(weight + (size_t)v_hi * d) + t;
     const uint32_t n_chunks = d / 64;
     constexpr uint32_t kBuf = 2 * 8 * NT * kHeadPitch;  // elements per buffer (hi and lo)
+    const bool with_lo = *any_lo != 0;  // bfloat16-valued hidden states need no second term
 
+    // chunk `chunk` of the tokens' hidden rows: 8 pieces of 16 bytes per token and term
     auto stage = [&](uint32_t chunk, uint32_t buf) {
         uint16_t *hi = sm_head + buf * kBuf, *lo = hi + 8 * NT * kHeadPitch;
-        for (uint32_t idx = threadIdx.x; idx < 8 * NT * 16; idx += 128) {
-            const uint32_t tok = idx / 16, kq = idx % 16;
-            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (tok0 + tok < n_tokens)
-                x = *reinterpret_cast<const float4 *>(hidden + (size_t)(tok0 + tok) * d + chunk * 64 + kq * 4);
-            const float xs[4] = {x.x, x.y, x.z, x.w};
-            uint32_t h[4], l[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                h[i] = float_to_bf16_bits(xs[i]);
-                l[i] = float_to_bf16_bits(xs[i] - bf16_bits_to_float((uint16_t)h[i]));
-            }
-            *reinterpret_cast<uint2 *>(hi + tok * kHeadPitch + kq * 4) =
-                make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
-            *reinterpret_cast<uint2 *>(lo + tok * kHeadPitch + kq * 4) =
-                make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
+        for (uint32_t idx = threadIdx.x; idx < 8 * NT * 8; idx += 128) {
+            const uint32_t tok = idx / 8, piece = idx % 8;
+            const uint32_t src_tok = min(tok0 + tok, n_tokens - 1);  // rows past the batch are never stored
+            const size_t src = (size_t)src_tok * d + chunk * 64 + piece * 8;
+            cp_async_16(hi + tok * kHeadPitch + piece * 8, hid_hi + src);
+            if (with_lo) cp_async_16(lo + tok * kHeadPitch + piece * 8, hid_lo + src);
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
     float acc[NT][4];
@@ -502,14 +552,17 @@ lm_head_mma_kernel(const float *__restrict__ hidden, const uint16_t *__restrict_
     wl[0] = row_lo[0]; wl[1] = row_lo[4];
     wh[0] = row_hi[0]; wh[1] = row_hi[4];
     stage(0, 0);
-    __syncthreads();
     for (uint32_t c = 0; c < n_chunks; ++c) {
         const uint4 cl[2] = {wl[0], wl[1]}, ch[2] = {wh[0], wh[1]};
         if (c + 1 < n_chunks) {
             wl[0] = row_lo[(c + 1) * 8]; wl[1] = row_lo[(c + 1) * 8 + 4];
             wh[0] = row_hi[(c + 1) * 8]; wh[1] = row_hi[(c + 1) * 8 + 4];
             stage(c + 1, (c + 1) & 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
+        __syncthreads();  // chunk c has landed for every thread
         const uint16_t *hi = sm_head + (c & 1) * kBuf, *lo = hi + 8 * NT * kHeadPitch;
 #pragma unroll
         for (int gi = 0; gi < 2; ++gi) {
@@ -517,14 +570,16 @@ lm_head_mma_kernel(const float *__restrict__ hidden, const uint16_t *__restrict_
             for (int nt = 0; nt < NT; ++nt) {
                 const uint32_t off = (8 * nt + g) * kHeadPitch + gi * 32 + 8 * t;
                 const uint4 bh = *reinterpret_cast<const uint4 *>(hi + off);
-                const uint4 bl = *reinterpret_cast<const uint4 *>(lo + off);
                 mma_bf16(acc[nt], cl[gi].x, ch[gi].x, cl[gi].y, ch[gi].y, bh.x, bh.y);
                 mma_bf16(acc[nt], cl[gi].z, ch[gi].z, cl[gi].w, ch[gi].w, bh.z, bh.w);
-                mma_bf16(acc[nt], cl[gi].x, ch[gi].x, cl[gi].y, ch[gi].y, bl.x, bl.y);
-                mma_bf16(acc[nt], cl[gi].z, ch[gi].z, cl[gi].w, ch[gi].w, bl.z, bl.w);
+                if (with_lo) {
+                    const uint4 bl = *reinterpret_cast<const uint4 *>(lo + off);
+                    mma_bf16(acc[nt], cl[gi].x, ch[gi].x, cl[gi].y, ch[gi].y, bl.x, bl.y);
+                    mma_bf16(acc[nt], cl[gi].z, ch[gi].z, cl[gi].w, ch[gi].w, bl.z, bl.w);
+                }
             }
         }
-        __syncthreads();
+        __syncthreads();  // the buffer may be refilled
     }
     const uint32_t v0 = blockIdx.x * 64 + warp * 16 + g;
 #pragma unroll
@@ -537,14 +592,16 @@ lm_head_mma_kernel(const float *__restrict__ hidden, const uint16_t *__restrict_
 }
 
 template <int NT>
-void launch_lm_head_mma(qk_ctx *c, const float *hidden, const uint16_t *weight, float *logits,
-                        size_t n_tokens, size_t vocab, size_t d, size_t stride) {
+void launch_lm_head_mma(qk_ctx *c, const uint16_t *hi, const uint16_t *lo, const uint32_t *any_lo,
+                        const uint16_t *weight, float *logits, size_t n_tokens, size_t vocab, size_t d,
+                        size_t stride) {
     const size_t smem = 2 * 2 * 8 * NT * kHeadPitch * sizeof(uint16_t);
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(lm_head_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     dim3 grid((unsigned)qk::ceil_div(vocab, 64), (unsigned)qk::ceil_div(n_tokens, 8 * NT));
-    lm_head_mma_kernel<NT><<<grid, 128, smem, c->stream>>>(hidden, weight, logits, (uint32_t)n_tokens,
-                                                          (uint32_t)vocab, (uint32_t)d, (uint32_t)stride);
+    lm_head_mma_kernel<NT><<<grid, 128, smem, c->stream>>>(hi, lo, any_lo, weight, logits,
+                                                          (uint32_t)n_tokens, (uint32_t)vocab,
+                                                          (uint32_t)d, (uint32_t)stride);
 }
 
 extern "C" {
@@ -702,10 +759,18 @@ qk_status qk_lm_head(qk_ctx *ctx, const float *hidden, const void *weight, int32
     } else if (weight_dtype == QK_BF16 && n_tokens >= 8 && d % 64 == 0) {
         // a batch: one pass over the head on the bf16 tensor cores
         const uint16_t *w = (const uint16_t *)weight;
-        if (n_tokens <= 8) launch_lm_head_mma<1>(c, hidden, w, logits, n_tokens, vocab, d, logits_stride);
-        else if (n_tokens <= 16) launch_lm_head_mma<2>(c, hidden, w, logits, n_tokens, vocab, d, logits_stride);
-        else if (n_tokens <= 32) launch_lm_head_mma<4>(c, hidden, w, logits, n_tokens, vocab, d, logits_stride);
-        else launch_lm_head_mma<8>(c, hidden, w, logits, n_tokens, vocab, d, logits_stride);
+        const size_t n = n_tokens * d, term = qk::ceil_div(n * 2, 256) * 256;
+        if ((st = c->d_head.reserve(2 * term + 256)) != QK_OK) return st;
+        uint16_t *hi = (uint16_t *)c->d_head.ptr, *lo = (uint16_t *)((uint8_t *)c->d_head.ptr + term);
+        uint32_t *any_lo = (uint32_t *)((uint8_t *)c->d_head.ptr + 2 * term);
+        QK_CUDA(cudaMemsetAsync(any_lo, 0, sizeof(uint32_t), c->stream));
+        split_hidden_kernel<<<(unsigned)qk::ceil_div(n, 256), 256, 0, c->stream>>>(hidden, hi, lo, any_lo, n);
+        QK_CUDA(cudaGetLastError());
+        c->launches++;
+        if (n_tokens <= 8) launch_lm_head_mma<1>(c, hi, lo, any_lo, w, logits, n_tokens, vocab, d, logits_stride);
+        else if (n_tokens <= 16) launch_lm_head_mma<2>(c, hi, lo, any_lo, w, logits, n_tokens, vocab, d, logits_stride);
+        else if (n_tokens <= 32) launch_lm_head_mma<4>(c, hi, lo, any_lo, w, logits, n_tokens, vocab, d, logits_stride);
+        else launch_lm_head_mma<8>(c, hi, lo, any_lo, w, logits, n_tokens, vocab, d, logits_stride);
     } else if (weight_dtype == QK_BF16) {
         if (n_tokens == 1)
             lm_head_kernel<uint16_t, 1><<<blocks, 256, 0, c->stream>>>(
