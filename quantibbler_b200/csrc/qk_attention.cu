@@ -373,6 +373,13 @@ attention_sage_kernel(SageArgs a, AttnDims dm, int causal) {
 }
 
 // ------------------------------------------------------------------ Sage on the tensor cores
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                     (uint32_t)__cvta_generic_to_shared(smem)),
+                 "l"(gmem)
+                 : "memory");
+}
+
 __device__ __forceinline__ void mma_s8(int (&c)[4], const int (&a)[4], int b0, int b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
@@ -396,17 +403,13 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], const int (&a)[4], int b0, i
 //       folded into the float32 output fragment with alpha and dV / 127.
 // Because the whole block's scores are in registers the block is swept once, not twice.
 template <int D32, int DV8, int BLK32>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
     constexpr int D = 32 * D32, DV = 8 * DV8, BLK = 32 * BLK32, NT = BLK / 8;
     constexpr int KP = D + 16, VP = BLK + 16;
+    // two buffers: the next key block is copied in (cp.async) while this one is used
+    constexpr int kBufBytes = BLK * KP + DV * VP + (BLK + DV + D) * (int)sizeof(float);
     extern __shared__ __align__(16) uint8_t sm_tc[];
-    uint8_t *Ks = sm_tc;                                   // [BLK][KP]
-    uint8_t *Vs = Ks + BLK * KP;                           // [DV][VP]
-    float *kscale = reinterpret_cast<float *>(Vs + DV * VP);  // [BLK]
-    float *vscale = kscale + BLK;                          // [DV]
-    float *mu = vscale + DV;                               // [D]
-
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
     const int h = blockIdx.y, b = blockIdx.z, kvh = h / dm.group;
     const size_t plane = (size_t)b * dm.KV + kvh;
@@ -440,33 +443,50 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
     const int i_warp_max = min((int)dm.Sq - 1, q0 + 15);
     const int jb_hi = causal ? i_blk_max / BLK + 1 : (int)a.n_blocks;
 
+    // A key block comes in by cp.async.  Keys past the end of the sequence re-read the last
+    // valid key (their scores are masked before use).
+    auto stage = [&](int jb, int buf) {
+        uint8_t *Ks = sm_tc + buf * kBufBytes, *Vs = Ks + BLK * KP;
+        float *kscale = reinterpret_cast<float *>(Vs + DV * VP), *vscale = kscale + BLK, *mu = vscale + DV;
+        const int j0 = jb * BLK, last = min(BLK, (int)dm.Skv - j0) - 1;
+        const int8_t *ksrc = a.kc + (plane * dm.Skv + j0) * a.dpad;
+        for (int idx = threadIdx.x; idx < BLK * (D / 16); idx += 128) {
+            const int key = idx / (D / 16), piece = idx % (D / 16);
+            cp_async16(Ks + key * KP + piece * 16, ksrc + (size_t)min(key, last) * a.dpad + piece * 16);
+        }
+        const int8_t *vsrc = a.vc + (plane * a.n_blocks + jb) * (size_t)DV * a.bpad;
+        for (int idx = threadIdx.x; idx < DV * (BLK / 16); idx += 128) {
+            const int c = idx / (BLK / 16), piece = idx % (BLK / 16);
+            cp_async16(Vs + c * VP + piece * 16, vsrc + (size_t)c * a.bpad + piece * 16);
+        }
+        for (int idx = threadIdx.x; idx < BLK; idx += 128)  // 4-byte copies: the offset need not be 16-byte aligned
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(
+                             (uint32_t)__cvta_generic_to_shared(kscale + idx)),
+                         "l"(a.ks + plane * dm.Skv + j0 + min(idx, last))
+                         : "memory");
+        for (int idx = threadIdx.x; idx < DV / 4; idx += 128)
+            cp_async16(vscale + idx * 4, a.vs + (plane * a.n_blocks + jb) * DV + idx * 4);
+        for (int idx = threadIdx.x; idx < D / 4; idx += 128)
+            cp_async16(mu + idx * 4, a.kmean + (plane * a.n_blocks + jb) * D + idx * 4);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    if (jb_hi > 0) stage(0, 0);
     for (int jb = 0; jb < jb_hi; ++jb) {
         const int j0 = jb * BLK, kj = min(BLK, (int)dm.Skv - j0);
-        __syncthreads();
-        {   // stage the key block
-            const uint4 zero = make_uint4(0, 0, 0, 0);
-            for (int idx = threadIdx.x; idx < BLK * (D / 16); idx += 128) {
-                const int key = idx / (D / 16), piece = idx % (D / 16);
-                uint4 w = zero;
-                if (key < kj)
-                    w = reinterpret_cast<const uint4 *>(a.kc + (plane * dm.Skv + j0 + key) * a.dpad)[piece];
-                *reinterpret_cast<uint4 *>(Ks + key * KP + piece * 16) = w;
-            }
-            const int8_t *vsrc = a.vc + (plane * a.n_blocks + jb) * (size_t)DV * a.bpad;
-            for (int idx = threadIdx.x; idx < DV * (BLK / 16); idx += 128) {
-                const int c = idx / (BLK / 16), piece = idx % (BLK / 16);
-                *reinterpret_cast<uint4 *>(Vs + c * VP + piece * 16) =
-                    reinterpret_cast<const uint4 *>(vsrc + (size_t)c * a.bpad)[piece];
-            }
-            for (int idx = threadIdx.x; idx < BLK; idx += 128)
-                kscale[idx] = idx < kj ? a.ks[plane * dm.Skv + j0 + idx] : 1.f;
-            for (int idx = threadIdx.x; idx < DV; idx += 128)
-                vscale[idx] = a.vs[(plane * a.n_blocks + jb) * DV + idx];
-            for (int idx = threadIdx.x; idx < D; idx += 128)
-                mu[idx] = a.kmean[(plane * a.n_blocks + jb) * D + idx];
+        if (jb + 1 < jb_hi) {
+            stage(jb + 1, (jb + 1) & 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
-        __syncthreads();
-        if (causal && j0 > i_warp_max) continue;  // every key of the block is masked for this warp
+        __syncthreads();  // block jb has landed for every thread
+        const uint8_t *Ks = sm_tc + (jb & 1) * kBufBytes, *Vs = Ks + BLK * KP;
+        const float *kscale = reinterpret_cast<const float *>(Vs + DV * VP), *vscale = kscale + BLK,
+                    *mu = vscale + DV;
+        // every key of the block may be masked for this warp: it still meets the barriers
+        const bool skip = causal && j0 > i_warp_max;
+        if (!skip) {
 
         // shift = (dQ * Qhat) . mean, per query row: each lane covers its own code bytes
         float sh0 = 0.f, sh1 = 0.f;
@@ -584,6 +604,8 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
         l1 = alpha1 * l1 + es1;
         if (mn0 != -INFINITY) m0 = mn0;
         if (mn1 != -INFINITY) m1 = mn1;
+        }
+        __syncthreads();  // the buffer may be refilled
     }
     // each lane summed P over its own columns only
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -702,7 +724,7 @@ qk_status launch_sage(qk_ctx *c, const SageArgs &a, const AttnDims &dm, int caus
 template <int D32, int DV8, int BLK32>
 qk_status launch_sage_tc(qk_ctx *c, const SageArgs &a, const AttnDims &dm, int causal) {
     constexpr int D = 32 * D32, DV = 8 * DV8, BLK = 32 * BLK32;
-    const size_t smem = BLK * (D + 16) + DV * (BLK + 16) + (BLK + DV + D) * sizeof(float);
+    const size_t smem = 2 * (BLK * (D + 16) + DV * (BLK + 16) + (BLK + DV + D) * sizeof(float));
     if (smem > 48 * 1024)
         QK_CUDA(cudaFuncSetAttribute(attention_sage_tc_kernel<D32, DV8, BLK32>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

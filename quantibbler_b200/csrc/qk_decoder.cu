@@ -63,14 +63,32 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
 }
 
 // h = x (+ residual); x_out = h; y = h * rsqrt(mean(h^2) + eps) * w.  One block per token.
-__global__ void __launch_bounds__(256)
+// The row stays in registers between the two passes (up to kRmsPerThread elements per thread;
+// wider rows re-read the overflow), so the kernel is one round of loads, one block-wide sum
+// and one round of stores: at batch 1 its duration is pure latency.
+constexpr int kRmsThreads = 512, kRmsPerThread = 16;
+__global__ void __launch_bounds__(kRmsThreads)
 rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
                const float *__restrict__ w, float *__restrict__ x_out, float *__restrict__ y,
                uint32_t d, float eps, int bf16) {
-    __shared__ float red[8];
+    __shared__ float red[kRmsThreads / 32];
     const size_t base = (size_t)blockIdx.x * d;
+    float keep[kRmsPerThread];
     float ss = 0.f;
-    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+#pragma unroll
+    for (int r = 0; r < kRmsPerThread; ++r) {
+        const uint32_t i = threadIdx.x + r * kRmsThreads;
+        float h = 0.f;
+        if (i < d) {
+            h = x[base + i];
+            if (residual) h += residual[base + i];
+            if (x_out) x_out[base + i] = h;
+            if (bf16) h = round_bf16f(h);
+        }
+        keep[r] = h;
+        ss += h * h;
+    }
+    for (uint32_t i = threadIdx.x + kRmsPerThread * kRmsThreads; i < d; i += kRmsThreads) {
         float h = x[base + i];
         if (residual) h += residual[base + i];
         if (x_out) x_out[base + i] = h;
@@ -78,11 +96,19 @@ rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
         ss += h * h;
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
-    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
-        float h = x[base + i];
-        if (residual) h += residual[base + i];
+#pragma unroll
+    for (int r = 0; r < kRmsPerThread; ++r) {
+        const uint32_t i = threadIdx.x + r * kRmsThreads;
+        if (i < d) {
+            const float o = keep[r] * inv * w[i];
+            y[base + i] = bf16 ? round_bf16f(o) : o;
+        }
+    }
+    for (uint32_t i = threadIdx.x + kRmsPerThread * kRmsThreads; i < d; i += kRmsThreads) {
+        // x_out (or x, when the sum was not written back) holds h
+        float h = x_out ? x_out[base + i] : x[base + i] + (residual ? residual[base + i] : 0.f);
         if (bf16) h = round_bf16f(h);
-        float o = h * inv * w[i];
+        const float o = h * inv * w[i];
         y[base + i] = bf16 ? round_bf16f(o) : o;
     }
 }
@@ -613,7 +639,7 @@ qk_status qk_rmsnorm(qk_ctx *ctx, const float *x, const float *residual, const f
     qk_status st = enter(ctx, &c);
     if (st != QK_OK) return st;
     if (n_tokens == 0) return QK_OK;
-    rmsnorm_kernel<<<(unsigned)n_tokens, 256, 0, c->stream>>>(x, residual, weight, x_out, y,
+    rmsnorm_kernel<<<(unsigned)n_tokens, kRmsThreads, 0, c->stream>>>(x, residual, weight, x_out, y,
                                                               (uint32_t)d, eps,
                                                               serving_dtype == QK_BF16);
     QK_LAUNCHED(c);
