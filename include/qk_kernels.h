@@ -178,6 +178,24 @@ qk_status qk_layer_create(qk_ctx *ctx, const uint8_t *ub_rows, size_t ub_len,
                           size_t r, const float *s1, const float *s2, const float *bias,
                           int32_t serving_dtype, qk_layer **out);
 void qk_layer_free(qk_layer *layer);
+/* ---- qpk1 layer stream ----------------------------------------------------------
+ * crates/quantibbler-qpk1/src/lib.rs:229-320 (parse) / src/quantibbler/qpk1.py:211-258
+ * (deserialize): header "QPK1", version (1: no bias, 2: bias), dtype tag (1 float16, 2
+ * float32), dout, din, r as u32 little-endian; s1, s2, bias; the Ub and Vb container bit
+ * streams.  The reader is fail-closed and keeps the reference's messages. */
+typedef struct qk_qpk1_info {
+    uint32_t version, dtype_tag;
+    size_t dout, din, r;
+    size_t s1_offset, s2_offset, bias_offset; /* bias_offset 0: a version-1 stream */
+    size_t ub_offset, ub_len, vb_offset, vb_len;
+} qk_qpk1_info;
+qk_status qk_qpk1_parse(const uint8_t *bytes, size_t len, qk_qpk1_info *info);
+/* s1[dout], s2[din], bias[dout] (may be NULL; zeros for a version-1 stream) as float32. */
+qk_status qk_qpk1_scales(const uint8_t *bytes, size_t len, float *s1, float *s2, float *bias);
+/* engine/mod.rs:342-381 (PackedLayer::from_layer) straight from the stream: parse, the
+ * loader's rank gate r <= min(dout, din), repack, upload. */
+qk_status qk_layer_from_qpk1(qk_ctx *ctx, const uint8_t *bytes, size_t len, int32_t serving_dtype,
+                             qk_layer **out);
 /* y[n_tokens x dout] = layer(x[n_tokens x din]), float32 row-major device buffers.
  * Asynchronous on the context's stream. */
 qk_status qk_layer_apply(qk_ctx *ctx, const qk_layer *layer, const float *x_dev, size_t n_tokens,

@@ -94,6 +94,9 @@ _SIGNATURES = {
     "qk_argmax_first": (c_int32, [c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_int32,
                                   c_void_p, c_void_p]),
     "qk_set_gemv_kernel": (c_int32, [c_void_p, c_int32]),
+    "qk_qpk1_parse": (c_int32, [c_void_p, c_size_t, c_void_p]),
+    "qk_qpk1_scales": (c_int32, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),
+    "qk_layer_from_qpk1": (c_int32, [c_void_p, c_void_p, c_size_t, c_int32, c_void_p]),
     "qk_set_sage_kernel": (c_int32, [c_void_p, c_int32]),
     "qk_gpu_attention_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
                                        c_void_p]),

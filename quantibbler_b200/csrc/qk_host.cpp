@@ -7,6 +7,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <vector>
 
 #include "qk_common.h"
 
@@ -216,6 +217,140 @@ qk_status qk_container_to_rows_transposed(const uint8_t *packed, size_t packed_l
             if ((packed[b >> 3] >> (b & 7)) & 1) out[k * rw + (j >> 3)] |= (uint8_t)(1u << (j & 7));
         }
     return QK_OK;
+}
+
+}  // extern "C"
+
+// ---- qpk1 layer stream (crates/quantibbler-qpk1/src/lib.rs:229-320, parse; the format is
+// src/quantibbler/qpk1.py:59,150-258): 24-byte header "QPK1", version, dtype tag, dout, din,
+// r (u32 little-endian), then s1[dout], s2[din], bias[dout] (version 2 only) in float16 or
+// float32, then the Ub and Vb container bit streams.  Fail-closed, with the reader's texts.
+namespace {
+
+uint32_t u32le(const uint8_t *p) {
+    return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
+}
+
+float half_to_float(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 0x1fu, man = h & 0x3ffu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else {  // subnormal: renormalise
+            int e = -1;
+            uint32_t m = man;
+            do {
+                ++e;
+                m <<= 1;
+            } while (!(m & 0x400u));
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | ((m & 0x3ffu) << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7f800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 127 - 15) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+void decode_scales(const uint8_t *src, size_t n, uint32_t tag, float *dst) {
+    for (size_t i = 0; i < n; ++i) {
+        if (tag == 1) {
+            dst[i] = half_to_float((uint16_t)(src[2 * i] | (src[2 * i + 1] << 8)));
+        } else {
+            const uint32_t bits = u32le(src + 4 * i);
+            memcpy(dst + i, &bits, 4);
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+qk_status qk_qpk1_parse(const uint8_t *bytes, size_t len, qk_qpk1_info *info) {
+    using qk::fail;
+    if (!info) return fail(QK_ERR_VALUE, "qk_qpk1_parse: info is null");
+    if (len < 24)
+        return fail(QK_ERR_VALUE, "stream is %zu bytes; shorter than the 24-byte header", len);
+    if (memcmp(bytes, "QPK1", 4) != 0)
+        return fail(QK_ERR_VALUE, "bad magic [%u, %u, %u, %u]; expected [81, 80, 75, 49]", bytes[0],
+                    bytes[1], bytes[2], bytes[3]);
+    const uint32_t version = u32le(bytes + 4), tag = u32le(bytes + 8);
+    if (version != 1 && version != 2)
+        return fail(QK_ERR_VALUE,
+                    "unsupported representation version %u; this reader implements version 1 "
+                    "(pre-bias legacy) and version 2 (current, with bias)",
+                    version);
+    if (tag != 1 && tag != 2)
+        return fail(QK_ERR_VALUE, "unknown dtype tag %u; expected 1 (float16) or 2 (float32)", tag);
+    const size_t dout = u32le(bytes + 12), din = u32le(bytes + 16), r = u32le(bytes + 20);
+    if (dout == 0 || din == 0 || r == 0)
+        return fail(QK_ERR_VALUE, "dout, din and r must all be >= 1, got (%zu, %zu, %zu)", dout, din, r);
+    const size_t item = tag == 1 ? 2 : 4;
+    const bool has_bias = version >= 2;
+    const size_t ub_len = qk::ceil_div(dout * r, 8), vb_len = qk::ceil_div(din * r, 8);
+    const size_t expected = 24 + ((has_bias ? 2 : 1) * dout + din) * item + ub_len + vb_len;
+    if (len < expected)
+        return fail(QK_ERR_VALUE, "truncated stream: %zu bytes; header declares %zu", len, expected);
+    if (len > expected)
+        return fail(QK_ERR_VALUE, "trailing garbage: %zu bytes; one layer at this header is %zu", len,
+                    expected);
+    info->version = version;
+    info->dtype_tag = tag;
+    info->dout = dout;
+    info->din = din;
+    info->r = r;
+    info->s1_offset = 24;
+    info->s2_offset = info->s1_offset + dout * item;
+    info->bias_offset = has_bias ? info->s2_offset + din * item : 0;
+    info->ub_offset = info->s2_offset + din * item + (has_bias ? dout * item : 0);
+    info->ub_len = ub_len;
+    info->vb_offset = info->ub_offset + ub_len;
+    info->vb_len = vb_len;
+    return QK_OK;
+}
+
+qk_status qk_qpk1_scales(const uint8_t *bytes, size_t len, float *s1, float *s2, float *bias) {
+    qk_qpk1_info info;
+    qk_status st = qk_qpk1_parse(bytes, len, &info);
+    if (st != QK_OK) return st;
+    decode_scales(bytes + info.s1_offset, info.dout, info.dtype_tag, s1);
+    decode_scales(bytes + info.s2_offset, info.din, info.dtype_tag, s2);
+    if (bias) {
+        if (info.bias_offset)
+            decode_scales(bytes + info.bias_offset, info.dout, info.dtype_tag, bias);
+        else
+            memset(bias, 0, info.dout * sizeof(float));  // a version-1 stream: the zero bias
+    }
+    return QK_OK;
+}
+
+qk_status qk_layer_from_qpk1(qk_ctx *ctx, const uint8_t *bytes, size_t len, int32_t serving_dtype,
+                             qk_layer **out) {
+    qk_qpk1_info info;
+    qk_status st = qk_qpk1_parse(bytes, len, &info);
+    if (st != QK_OK) return st;
+    // the model loader's rank gate (src/quantibbler/qpk1.py:129-138)
+    if (info.r > (info.dout < info.din ? info.dout : info.din))
+        return qk::fail(QK_ERR_VALUE, "r=%zu exceeds min(dout, din)=%zu", info.r,
+                        info.dout < info.din ? info.dout : info.din);
+    const size_t ub_words = qk::ceil_div(info.r, 8), vb_words = qk::ceil_div(info.din, 8);
+    std::vector<uint8_t> ub_rows(info.dout * ub_words), vbt_rows(info.r * vb_words);
+    std::vector<float> s1(info.dout), s2(info.din), bias(info.dout);
+    if ((st = qk_container_to_rows(bytes + info.ub_offset, info.ub_len, info.dout, info.r,
+                                   ub_rows.data(), ub_rows.size())) != QK_OK)
+        return st;
+    if ((st = qk_container_to_rows_transposed(bytes + info.vb_offset, info.vb_len, info.din, info.r,
+                                              vbt_rows.data(), vbt_rows.size())) != QK_OK)
+        return st;
+    if ((st = qk_qpk1_scales(bytes, len, s1.data(), s2.data(), bias.data())) != QK_OK) return st;
+    return qk_layer_create(ctx, ub_rows.data(), ub_rows.size(), vbt_rows.data(), vbt_rows.size(),
+                           info.dout, info.din, info.r, s1.data(), s2.data(),
+                           info.bias_offset ? bias.data() : nullptr, serving_dtype, out);
 }
 
 }  // extern "C"

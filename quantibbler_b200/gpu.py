@@ -226,6 +226,24 @@ class PackedLayer:
                                                          vb_t_rows.ctypes.data, vb_t_rows.size))
         return cls(ctx, ub_rows, vb_t_rows, dout, din, r, s1, s2, bias, serving, name)
 
+    @classmethod
+    def from_qpk1(cls, ctx, data, serving="float32", name=""):
+        """A layer straight from its qpk1 stream (crates/quantibbler-qpk1/src/lib.rs:229-320
+        parse + engine/mod.rs:342-381 from_layer); a malformed stream raises the reader's
+        ``ValueError`` text."""
+        from . import qpk1
+        raw = np.frombuffer(bytes(data), dtype=np.uint8)
+        info = qpk1.parse(raw)
+        self = cls.__new__(cls)
+        self.ctx, self.name, self.serving = ctx, name, serving
+        self.dout, self.din, self.r = info["dout"], info["din"], info["r"]
+        h = ctypes.c_void_p()
+        check(_lib.lib().qk_layer_from_qpk1(ctx.handle, raw.ctypes.data, raw.size,
+                                            QK_F32 if serving == "float32" else QK_BF16,
+                                            ctypes.byref(h)))
+        self._h = h
+        return self
+
     def close(self) -> None:
         if getattr(self, "_h", None):
             _lib.lib().qk_layer_free(self._h)
