@@ -160,7 +160,10 @@ def run_reference(args, rank: int) -> None:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64",
         "data": "synthetic",
-        "config": {"workload": "config0 factorized linear 4096x4096 r1024, 1 token, CPU sample",
+        "config": {"workload": f"config0 factorized linear 4096x4096 r1024, 1 token, stack of "
+                               f"{args.layers} distinct resident layers per GPU per step",
+                   "sample": f"bounded CPU sample of that workload: {per_step} layer-applies per "
+                             f"step over 16 distinct layers",
                    "layers_per_step": per_step},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": sample},

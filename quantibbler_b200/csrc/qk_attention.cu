@@ -380,6 +380,14 @@ __device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
                  : "memory");
 }
 
+// four codes (each already in [0, 127]) -> one register, code j in byte j
+__device__ __forceinline__ int pack_codes(const int (&c)[4]) {
+    int hi, w;
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(c[3]), "r"(c[2]), "r"(0));
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(c[1]), "r"(c[0]), "r"(hi));
+    return w;
+}
+
 __device__ __forceinline__ void mma_s8(int (&c)[4], const int (&a)[4], int b0, int b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
@@ -558,32 +566,38 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
         mn1 = fmaxf(mn1, __shfl_xor_sync(0xffffffffu, mn1, 2));
         const float alpha0 = (mn0 == -INFINITY) ? 0.f : expf(m0 - mn0);
         const float alpha1 = (mn1 == -INFINITY) ? 0.f : expf(m1 - mn1);
-        // P, its sum, its codes: pa[slab] is the A fragment of the slab's 32 keys
+        // P scaled by 127 (the static P scale): 127 exp(s - m) = exp2(s log2e - m log2e + log2 127),
+        // one FMA and one ex2 per score.  Its sum is 127 l and the output below is accumulated
+        // as 127 o, so the two factors cancel in o / l and no multiply by 1/127 is needed.
+        // pa[slab] is the A fragment of the slab's 32 keys.
+        constexpr float kLog2e = 1.4426950408889634f, kLog2_127 = 6.988684686772166f;
+        const float off0 = (mn0 == -INFINITY) ? -INFINITY : kLog2_127 - mn0 * kLog2e;
+        const float off1 = (mn1 == -INFINITY) ? -INFINITY : kLog2_127 - mn1 * kLog2e;
         int pa[BLK32][4];
         float es0 = 0.f, es1 = 0.f;
 #pragma unroll
         for (int sl = 0; sl < BLK32; ++sl)
 #pragma unroll
             for (int pair = 0; pair < 2; ++pair) {
-                int w0 = 0, w1 = 0;
+                int c0[4], c1[4];
 #pragma unroll
                 for (int jj = 0; jj < 2; ++jj)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int nt = 4 * sl + 2 * pair + jj;
-                        const float p0 = (mn0 == -INFINITY) ? 0.f : expf(__int_as_float(acc[nt][e]) - mn0);
-                        const float p1 = (mn1 == -INFINITY) ? 0.f : expf(__int_as_float(acc[nt][2 + e]) - mn1);
+                        // a masked score is -inf: exp2 gives 0; a fully masked row has off = -inf
+                        // and s = -inf, whose sum would be NaN, hence the guard in off
+                        const float s0 = __int_as_float(acc[nt][e]), s1 = __int_as_float(acc[nt][2 + e]);
+                        const float p0 = (mn0 == -INFINITY) ? 0.f : exp2f(fmaf(s0, kLog2e, off0));
+                        const float p1 = (mn1 == -INFINITY) ? 0.f : exp2f(fmaf(s1, kLog2e, off1));
                         es0 += p0;
                         es1 += p1;
-                        // p is in [0, 1]: 127 p needs no clamp, and the conversion rounds to
-                        // nearest even like rint
-                        const int c0 = __float2int_rn(p0 * 127.f);
-                        const int c1 = __float2int_rn(p1 * 127.f);
-                        w0 |= c0 << (8 * (2 * jj + e));
-                        w1 |= c1 << (8 * (2 * jj + e));
+                        // p is in [0, 127]: the conversion rounds to nearest even like rint
+                        c0[2 * jj + e] = __float2int_rn(p0);
+                        c1[2 * jj + e] = __float2int_rn(p1);
                     }
-                pa[sl][2 * pair] = w0;
-                pa[sl][2 * pair + 1] = w1;
+                pa[sl][2 * pair] = pack_codes(c0);
+                pa[sl][2 * pair + 1] = pack_codes(c1);
             }
         // PV, one 8-channel tile at a time
 #pragma unroll
@@ -595,10 +609,10 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
                 mma_s8(pv, pa[sl], *reinterpret_cast<const int *>(vr + 32 * sl),
                        *reinterpret_cast<const int *>(vr + 32 * sl + 16));
             const float vd0 = vscale[8 * nv + 2 * t], vd1 = vscale[8 * nv + 2 * t + 1];
-            o[nv][0] = alpha0 * o[nv][0] + (float)pv[0] * (1.0f / 127.0f) * vd0;
-            o[nv][1] = alpha0 * o[nv][1] + (float)pv[1] * (1.0f / 127.0f) * vd1;
-            o[nv][2] = alpha1 * o[nv][2] + (float)pv[2] * (1.0f / 127.0f) * vd0;
-            o[nv][3] = alpha1 * o[nv][3] + (float)pv[3] * (1.0f / 127.0f) * vd1;
+            o[nv][0] = fmaf(alpha0, o[nv][0], (float)pv[0] * vd0);
+            o[nv][1] = fmaf(alpha0, o[nv][1], (float)pv[1] * vd1);
+            o[nv][2] = fmaf(alpha1, o[nv][2], (float)pv[2] * vd0);
+            o[nv][3] = fmaf(alpha1, o[nv][3], (float)pv[3] * vd1);
         }
         l0 = alpha0 * l0 + es0;
         l1 = alpha1 * l1 + es1;
