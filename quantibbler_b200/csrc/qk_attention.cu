@@ -146,10 +146,15 @@ __global__ void sage_quant_q_kernel(const float *__restrict__ q, int8_t *__restr
 // gamma + psi_K: one block per (b, kv head, key block).  mean [blk][d] float32 (sequential
 // float32 sum over the block's tokens, then one division, as the reference kernel does),
 // codes [token][dpad], scale [token].
+// mean_digits (may be null) [blk][8][dpad] int8 + mean_scale [blk]: the mean as a 24-bit fixed
+// point number in three balanced base-256 digits, mean[c] = mean_scale * (65536 d0 + 256 d1
+// + d2); rows 3..7 are zero.  The tensor-core kernel appends these rows to the block's K codes,
+// so that (Qhat . mean) falls out of the same integer MMA as the scores.
 __global__ void sage_quant_k_kernel(const float *__restrict__ k, int8_t *__restrict__ codes,
                                     float *__restrict__ scale, float *__restrict__ mean,
                                     uint32_t S, uint32_t d, uint32_t dpad, uint32_t block,
-                                    uint32_t n_blocks) {
+                                    uint32_t n_blocks, int8_t *__restrict__ mean_digits,
+                                    float *__restrict__ mean_scale) {
     extern __shared__ float mu[];  // d floats
     const uint32_t plane = blockIdx.y, jb = blockIdx.x;
     const uint32_t j0 = jb * block, j1 = min(S, j0 + block), kj = j1 - j0;
@@ -162,6 +167,30 @@ __global__ void sage_quant_k_kernel(const float *__restrict__ k, int8_t *__restr
         mean[((size_t)plane * n_blocks + jb) * d + c] = mval;
     }
     __syncthreads();
+    if (mean_digits) {
+        __shared__ float peak_sh[4];
+        float peak = 0.f;
+        for (uint32_t c = threadIdx.x; c < d; c += blockDim.x) peak = fmaxf(peak, fabsf(mu[c]));
+        for (int off = 16; off > 0; off >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, off));
+        if (threadIdx.x % 32 == 0) peak_sh[threadIdx.x / 32] = peak;
+        __syncthreads();
+        peak = fmaxf(fmaxf(peak_sh[0], peak_sh[1]), fmaxf(peak_sh[2], peak_sh[3]));
+        const float unit = peak > 0.f ? peak / 8000000.f : 1.f;   // |fixed| <= 8e6 < 127 * 65536
+        int8_t *rows = mean_digits + ((size_t)plane * n_blocks + jb) * 8 * dpad;
+        for (uint32_t c = threadIdx.x; c < 8 * dpad; c += blockDim.x) rows[c] = 0;
+        __syncthreads();
+        for (uint32_t c = threadIdx.x; c < d; c += blockDim.x) {
+            int v = (int)rintf(mu[c] / unit);
+            const int d2 = ((v + 128) & 255) - 128;
+            v = (v - d2) >> 8;
+            const int d1 = ((v + 128) & 255) - 128;
+            v = (v - d1) >> 8;
+            rows[c] = (int8_t)v;
+            rows[dpad + c] = (int8_t)d1;
+            rows[2 * dpad + c] = (int8_t)d2;
+        }
+        if (threadIdx.x == 0) mean_scale[(size_t)plane * n_blocks + jb] = unit;
+    }
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, n_warps = blockDim.x / 32;
     for (uint32_t j = j0 + warp; j < j1; j += n_warps) {
         const float *kr = kp + (size_t)j * d;
@@ -215,6 +244,8 @@ struct SageArgs {
     const int8_t *kc;
     const float *ks;
     const float *kmean;
+    const int8_t *kmean_digits;  // tensor-core kernel: [blk][8][dpad]
+    const float *kmean_scale;    // [blk]
     const int8_t *vc;
     const float *vs;
     float *out;
@@ -416,7 +447,8 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
     constexpr int D = 32 * D32, DV = 8 * DV8, BLK = 32 * BLK32, NT = BLK / 8;
     constexpr int KP = D + 16, VP = BLK + 16;
     // two buffers: the next key block is copied in (cp.async) while this one is used
-    constexpr int kBufBytes = BLK * KP + DV * VP + (BLK + DV + D) * (int)sizeof(float);
+    // K tile: the block's keys, then eight rows of mean digits (three used)
+    constexpr int kBufBytes = (BLK + 8) * KP + DV * VP + (BLK + DV + 4) * (int)sizeof(float);
     extern __shared__ __align__(16) uint8_t sm_tc[];
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
     const int h = blockIdx.y, b = blockIdx.z, kvh = h / dm.group;
@@ -454,14 +486,24 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
     // A key block comes in by cp.async.  Keys past the end of the sequence re-read the last
     // valid key (their scores are masked before use).
     auto stage = [&](int jb, int buf) {
-        uint8_t *Ks = sm_tc + buf * kBufBytes, *Vs = Ks + BLK * KP;
-        float *kscale = reinterpret_cast<float *>(Vs + DV * VP), *vscale = kscale + BLK, *mu = vscale + DV;
+        uint8_t *Ks = sm_tc + buf * kBufBytes, *Vs = Ks + (BLK + 8) * KP;
+        float *kscale = reinterpret_cast<float *>(Vs + DV * VP), *vscale = kscale + BLK, *mscale = vscale + DV;
         const int j0 = jb * BLK, last = min(BLK, (int)dm.Skv - j0) - 1;
         const int8_t *ksrc = a.kc + (plane * dm.Skv + j0) * a.dpad;
         for (int idx = threadIdx.x; idx < BLK * (D / 16); idx += 128) {
             const int key = idx / (D / 16), piece = idx % (D / 16);
             cp_async16(Ks + key * KP + piece * 16, ksrc + (size_t)min(key, last) * a.dpad + piece * 16);
         }
+        const int8_t *msrc = a.kmean_digits + (plane * a.n_blocks + jb) * (size_t)8 * a.dpad;
+        for (int idx = threadIdx.x; idx < 8 * (D / 16); idx += 128) {
+            const int row = idx / (D / 16), piece = idx % (D / 16);
+            cp_async16(Ks + (BLK + row) * KP + piece * 16, msrc + (size_t)row * a.dpad + piece * 16);
+        }
+        if (threadIdx.x == 0)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(
+                             (uint32_t)__cvta_generic_to_shared(mscale)),
+                         "l"(a.kmean_scale + plane * a.n_blocks + jb)
+                         : "memory");
         const int8_t *vsrc = a.vc + (plane * a.n_blocks + jb) * (size_t)DV * a.bpad;
         for (int idx = threadIdx.x; idx < DV * (BLK / 16); idx += 128) {
             const int c = idx / (BLK / 16), piece = idx % (BLK / 16);
@@ -474,8 +516,6 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
                          : "memory");
         for (int idx = threadIdx.x; idx < DV / 4; idx += 128)
             cp_async16(vscale + idx * 4, a.vs + (plane * a.n_blocks + jb) * DV + idx * 4);
-        for (int idx = threadIdx.x; idx < D / 4; idx += 128)
-            cp_async16(mu + idx * 4, a.kmean + (plane * a.n_blocks + jb) * D + idx * 4);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
@@ -489,29 +529,33 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();  // block jb has landed for every thread
-        const uint8_t *Ks = sm_tc + (jb & 1) * kBufBytes, *Vs = Ks + BLK * KP;
+        const uint8_t *Ks = sm_tc + (jb & 1) * kBufBytes, *Vs = Ks + (BLK + 8) * KP;
         const float *kscale = reinterpret_cast<const float *>(Vs + DV * VP), *vscale = kscale + BLK,
-                    *mu = vscale + DV;
+                    *mscale = vscale + DV;
         // every key of the block may be masked for this warp: it still meets the barriers
         const bool skip = causal && j0 > i_warp_max;
         if (!skip) {
 
-        // shift = (dQ * Qhat) . mean, per query row: each lane covers its own code bytes
-        float sh0 = 0.f, sh1 = 0.f;
+        // shift = (dQ * Qhat) . mean, per query row, from the mean's three digit rows: columns 0,
+        // 1 (lane t = 0) and 2 (t = 1) of one more 8-column MMA tile
+        float sh0, sh1;
+        {
+            int accm[4] = {0, 0, 0, 0};
+            const uint8_t *mr = Ks + (BLK + g) * KP + 4 * t;
 #pragma unroll
-        for (int ks = 0; ks < D32; ++ks)
-#pragma unroll
-            for (int half = 0; half < 2; ++half)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float mv = mu[32 * ks + 16 * half + 4 * t + e];
-                    sh0 = fmaf((float)(int8_t)(qa[ks][2 * half] >> (8 * e)) * dq0, mv, sh0);
-                    sh1 = fmaf((float)(int8_t)(qa[ks][2 * half + 1] >> (8 * e)) * dq1, mv, sh1);
-                }
-        sh0 += __shfl_xor_sync(0xffffffffu, sh0, 1);
-        sh0 += __shfl_xor_sync(0xffffffffu, sh0, 2);
-        sh1 += __shfl_xor_sync(0xffffffffu, sh1, 1);
-        sh1 += __shfl_xor_sync(0xffffffffu, sh1, 2);
+            for (int ks = 0; ks < D32; ++ks)
+                mma_s8(accm, qa[ks], *reinterpret_cast<const int *>(mr + 32 * ks),
+                       *reinterpret_cast<const int *>(mr + 32 * ks + 16));
+            float p0 = t == 0 ? (float)accm[0] * 65536.f + (float)accm[1] * 256.f : t == 1 ? (float)accm[0] : 0.f;
+            float p1 = t == 0 ? (float)accm[2] * 65536.f + (float)accm[3] * 256.f : t == 1 ? (float)accm[2] : 0.f;
+            p0 += __shfl_xor_sync(0xffffffffu, p0, 1);
+            p0 += __shfl_xor_sync(0xffffffffu, p0, 2);
+            p1 += __shfl_xor_sync(0xffffffffu, p1, 1);
+            p1 += __shfl_xor_sync(0xffffffffu, p1, 2);
+            const float unit = mscale[0];
+            sh0 = p0 * unit * dq0;
+            sh1 = p1 * unit * dq1;
+        }
 
         // S = Qhat Khat^T
         int acc[NT][4];
@@ -535,8 +579,8 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
                 for (int e = 0; e < 2; ++e) {
                     const int kk = 8 * nt + 2 * t + e, j = j0 + kk;
                     const float ksc = kscale[kk];
-                    float s0 = (float)acc[nt][e] * dq0 * ksc + sh0;
-                    float s1 = (float)acc[nt][2 + e] * dq1 * ksc + sh1;
+                    float s0 = fmaf((float)acc[nt][e] * dq0, ksc, sh0);
+                    float s1 = fmaf((float)acc[nt][2 + e] * dq1, ksc, sh1);
                     if (kk >= kj || !v0 || (causal && j > i0)) s0 = -INFINITY;
                     if (kk >= kj || !v1 || (causal && j > i1)) s1 = -INFINITY;
                     acc[nt][e] = __float_as_int(s0);
@@ -548,10 +592,10 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const float2 ksc = *reinterpret_cast<const float2 *>(kscale + 8 * nt + 2 * t);
-                const float s00 = (float)acc[nt][0] * dq0 * ksc.x + sh0;
-                const float s01 = (float)acc[nt][1] * dq0 * ksc.y + sh0;
-                const float s10 = (float)acc[nt][2] * dq1 * ksc.x + sh1;
-                const float s11 = (float)acc[nt][3] * dq1 * ksc.y + sh1;
+                const float s00 = fmaf((float)acc[nt][0] * dq0, ksc.x, sh0);
+                const float s01 = fmaf((float)acc[nt][1] * dq0, ksc.y, sh0);
+                const float s10 = fmaf((float)acc[nt][2] * dq1, ksc.x, sh1);
+                const float s11 = fmaf((float)acc[nt][3] * dq1, ksc.y, sh1);
                 acc[nt][0] = __float_as_int(s00);
                 acc[nt][1] = __float_as_int(s01);
                 acc[nt][2] = __float_as_int(s10);
@@ -738,7 +782,7 @@ qk_status launch_sage(qk_ctx *c, const SageArgs &a, const AttnDims &dm, int caus
 template <int D32, int DV8, int BLK32>
 qk_status launch_sage_tc(qk_ctx *c, const SageArgs &a, const AttnDims &dm, int causal) {
     constexpr int D = 32 * D32, DV = 8 * DV8, BLK = 32 * BLK32;
-    const size_t smem = 2 * (BLK * (D + 16) + DV * (BLK + 16) + (BLK + DV + D) * sizeof(float));
+    const size_t smem = 2 * ((BLK + 8) * (D + 16) + DV * (BLK + 16) + (BLK + DV + 4) * sizeof(float));
     if (smem > 48 * 1024)
         QK_CUDA(cudaFuncSetAttribute(attention_sage_tc_kernel<D32, DV8, BLK32>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -780,7 +824,8 @@ size_t sage_scratch_bytes(const qk_attention_shape *s, size_t block_size) {
     auto up = [](size_t n) { return (n + 255) / 256 * 256; };
     return up(qrows * dpad) + up(qrows * 4) + up(planes * S * dpad) + up(planes * S * 4) +
            up(planes * n_blocks * dm.d * 4) + up(planes * n_blocks * dm.dv * bpad) +
-           up(planes * n_blocks * dm.dv * 4);
+           up(planes * n_blocks * dm.dv * 4) + up(planes * n_blocks * 8 * dpad) +
+           up(planes * n_blocks * 4);
 }
 
 qk_status attention_sage_dev(qk_ctx *c, const float *dq, const float *dk, const float *dv,
@@ -802,6 +847,7 @@ qk_status attention_sage_dev(qk_ctx *c, const float *dq, const float *dk, const 
     const size_t o_kc = take(planes * S * dpad), o_ks = take(planes * S * 4);
     const size_t o_km = take(planes * n_blocks * dm.d * 4);
     const size_t o_vc = take(planes * n_blocks * dm.dv * bpad), o_vs = take(planes * n_blocks * dm.dv * 4);
+    const size_t o_md = take(planes * n_blocks * 8 * dpad), o_ms = take(planes * n_blocks * 4);
     uint8_t *base = scratch;
     const bool tc = c->sage_kernel != 0 && sage_tc_eligible(dm, block_size);
     const float inv_sqrt_d = 1.0f / sqrtf((float)dm.d);  // gpu_attention.rs:720
@@ -812,7 +858,8 @@ qk_status attention_sage_dev(qk_ctx *c, const float *dq, const float *dk, const 
     dim3 kgrid((unsigned)n_blocks, (unsigned)planes);
     sage_quant_k_kernel<<<kgrid, 128, dm.d * sizeof(float), c->stream>>>(
         dk, (int8_t *)(base + o_kc), (float *)(base + o_ks), (float *)(base + o_km), (uint32_t)S,
-        dm.d, (uint32_t)dpad, (uint32_t)block_size, (uint32_t)n_blocks);
+        dm.d, (uint32_t)dpad, (uint32_t)block_size, (uint32_t)n_blocks,
+        tc ? (int8_t *)(base + o_md) : nullptr, (float *)(base + o_ms));
     QK_CUDA(cudaGetLastError());
     sage_quant_v_kernel<<<kgrid, 128, 0, c->stream>>>(
         dv, (int8_t *)(base + o_vc), (float *)(base + o_vs), (uint32_t)S, dm.dv,
@@ -821,7 +868,8 @@ qk_status attention_sage_dev(qk_ctx *c, const float *dq, const float *dk, const 
     c->launches += 3;
     SageArgs a{(const int8_t *)(base + o_qc), (const float *)(base + o_qs),
                (const int8_t *)(base + o_kc), (const float *)(base + o_ks),
-               (const float *)(base + o_km),  (const int8_t *)(base + o_vc),
+               (const float *)(base + o_km),  (const int8_t *)(base + o_md),
+               (const float *)(base + o_ms),  (const int8_t *)(base + o_vc),
                (const float *)(base + o_vs),  out,
                (uint32_t)dpad, (uint32_t)bpad, (uint32_t)block_size, (uint32_t)n_blocks};
     if (tc)
