@@ -17,9 +17,12 @@
 // full precision, P quantised at the static 1/127 scale, V per-channel INT8 per key block,
 // integer PV, O = alpha*O + pv*(1/127)*dV, O/l at the end.  Unlike the reference (one thread
 // per query row re-quantising every K/V tile into global scratch), the K, V and Q codes are
-// produced once per call by three small kernels and the main kernel takes its integer
-// dots with dp4a.  A key block's P codes all depend on the block's row maximum, so each
-// block is swept twice: once for the maximum, once for P and the PV product.
+// produced once per call by three small kernels.  Two main kernels share them:
+//   * attention_sage_tc_kernel: both integer products on the INT8 tensor cores (mma.sync
+//     m16n8k32), for head_dim = val_dim in {64, 128} and key blocks of 32, 64 or 128;
+//   * attention_sage_kernel: integer dots with dp4a, any shape.  A key block's P codes all
+//     depend on the block's row maximum, so each block is swept twice there: once for the
+//     maximum, once for P and the PV product.
 #include <cmath>
 #include <cstring>
 #include <string>
@@ -411,6 +414,20 @@ __device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
                  : "memory");
 }
 
+// Four (two) 8-row x 16-byte matrices from shared memory: lane l supplies the address of row
+// l % 8 of matrix l / 8; afterwards every thread (g, t) holds bytes 4t..4t+3 of row g of each
+// matrix, which is exactly the B fragment of the 8-bit m16n8k32 MMA.
+__device__ __forceinline__ void ldsm_x4(const void *row, int &r0, int &r1, int &r2, int &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"((uint32_t)__cvta_generic_to_shared(row)));
+}
+__device__ __forceinline__ void ldsm_x2(const void *row, int &r0, int &r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];"
+                 : "=r"(r0), "=r"(r1)
+                 : "r"((uint32_t)__cvta_generic_to_shared(row)));
+}
+
 // four codes (each already in [0, 127]) -> one register, code j in byte j
 __device__ __forceinline__ int pack_codes(const int (&c)[4]) {
     int hi, w;
@@ -541,11 +558,14 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
         float sh0, sh1;
         {
             int accm[4] = {0, 0, 0, 0};
-            const uint8_t *mr = Ks + (BLK + g) * KP + 4 * t;
+            const uint8_t *mr = Ks + (BLK + lane % 8) * KP + 16 * (lane / 8);
 #pragma unroll
-            for (int ks = 0; ks < D32; ++ks)
-                mma_s8(accm, qa[ks], *reinterpret_cast<const int *>(mr + 32 * ks),
-                       *reinterpret_cast<const int *>(mr + 32 * ks + 16));
+            for (int kp = 0; kp < D32 / 2; ++kp) {
+                int b[4];
+                ldsm_x4(mr + 64 * kp, b[0], b[1], b[2], b[3]);
+                mma_s8(accm, qa[2 * kp], b[0], b[1]);
+                mma_s8(accm, qa[2 * kp + 1], b[2], b[3]);
+            }
             float p0 = t == 0 ? (float)accm[0] * 65536.f + (float)accm[1] * 256.f : t == 1 ? (float)accm[0] : 0.f;
             float p1 = t == 0 ? (float)accm[2] * 65536.f + (float)accm[3] * 256.f : t == 1 ? (float)accm[2] : 0.f;
             p0 += __shfl_xor_sync(0xffffffffu, p0, 1);
@@ -562,11 +582,14 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0;
-            const uint8_t *kr = Ks + (8 * nt + g) * KP + 4 * t;
+            const uint8_t *kr = Ks + (8 * nt + lane % 8) * KP + 16 * (lane / 8);
 #pragma unroll
-            for (int ks = 0; ks < D32; ++ks)
-                mma_s8(acc[nt], qa[ks], *reinterpret_cast<const int *>(kr + 32 * ks),
-                       *reinterpret_cast<const int *>(kr + 32 * ks + 16));
+            for (int kp = 0; kp < D32 / 2; ++kp) {
+                int b[4];  // B fragments of k-steps 2 kp and 2 kp + 1
+                ldsm_x4(kr + 64 * kp, b[0], b[1], b[2], b[3]);
+                mma_s8(acc[nt], qa[2 * kp], b[0], b[1]);
+                mma_s8(acc[nt], qa[2 * kp + 1], b[2], b[3]);
+            }
         }
         // scores and the new row maxima.  Only the block on the diagonal, the last block of a
         // ragged sequence and a warp with rows past the end need the per-element mask.
@@ -647,11 +670,20 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
 #pragma unroll
         for (int nv = 0; nv < DV8; ++nv) {
             int pv[4] = {0, 0, 0, 0};
-            const uint8_t *vr = Vs + (8 * nv + g) * VP + 4 * t;
+            if (BLK32 == 1) {
+                int b[2];
+                ldsm_x2(Vs + (8 * nv + lane % 8) * VP + 16 * ((lane / 8) & 1), b[0], b[1]);
+                mma_s8(pv, pa[0], b[0], b[1]);
+            } else {
+                const uint8_t *vr = Vs + (8 * nv + lane % 8) * VP + 16 * (lane / 8);
 #pragma unroll
-            for (int sl = 0; sl < BLK32; ++sl)
-                mma_s8(pv, pa[sl], *reinterpret_cast<const int *>(vr + 32 * sl),
-                       *reinterpret_cast<const int *>(vr + 32 * sl + 16));
+                for (int sp = 0; sp < BLK32 / 2; ++sp) {
+                    int b[4];  // B fragments of slabs 2 sp and 2 sp + 1
+                    ldsm_x4(vr + 64 * sp, b[0], b[1], b[2], b[3]);
+                    mma_s8(pv, pa[2 * sp], b[0], b[1]);
+                    mma_s8(pv, pa[2 * sp + 1], b[2], b[3]);
+                }
+            }
             const float vd0 = vscale[8 * nv + 2 * t], vd1 = vscale[8 * nv + 2 * t + 1];
             o[nv][0] = fmaf(alpha0, o[nv][0], (float)pv[0] * vd0);
             o[nv][1] = fmaf(alpha0, o[nv][1], (float)pv[1] * vd1);
