@@ -347,22 +347,27 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
             const float bias = (kFinal && g.out_bias && n < g.n_rows) ? g.out_bias[n] : 0.f;
             float *part = g.partials + (size_t)blockIdx.x * slot_elems;
             // When this is the CTA's last segment the pipeline has drained and the stages are
-            // free: the next CTA's partial (contiguous, bn x 128 floats) comes in by one bulk
-            // copy instead of latency-bound loads.  Any further partials are read directly.
-            const bool staged = last > blockIdx.x + 1 && u + len == u_end;
+            // free: as many of the following CTAs' partials as fit there (each is contiguous,
+            // bn x 128 floats) come in by bulk copies instead of latency-bound loads.  Any
+            // further partials are read directly.
+            const uint32_t part_bytes = kBN * kBM * 4;
+            uint32_t n_staged = 0;
+            if (last > blockIdx.x + 1 && u + len == u_end)
+                n_staged = min(last - blockIdx.x - 1, (uint32_t)(kStages * kStageBytes) / part_bytes);
+            const bool staged = n_staged > 0;
             if (staged) {
                 if (warp == kEpilogueWarp0 && lane == 0) {
-                    const uint32_t bytes = kBN * kBM * 4;
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
                                      smem_u32(staged_bar)),
-                                 "r"(bytes)
+                                 "r"(n_staged * part_bytes)
                                  : "memory");
-                    asm volatile(
-                        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
-                            "r"(smem_u32(tiles)),
-                        "l"(g.partials + (size_t)(blockIdx.x + 1) * slot_elems), "r"(bytes),
-                        "r"(smem_u32(staged_bar))
-                        : "memory");
+                    for (uint32_t i = 0; i < n_staged; ++i)
+                        asm volatile(
+                            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+                                "r"(smem_u32(tiles) + i * part_bytes),
+                            "l"(g.partials + (size_t)(blockIdx.x + 1 + i) * slot_elems), "r"(part_bytes),
+                            "r"(smem_u32(staged_bar))
+                            : "memory");
                 }
                 if (!mbar_wait(staged_bar, 0, abort_flag)) {
                     *abort_flag = 1;
@@ -391,12 +396,13 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
                         part[(size_t)(c0 + j) * kBM + n_local] = __uint_as_float(v[j]);
                     continue;
                 }
-                if (staged) {
+                for (uint32_t i = 0; i < n_staged; ++i) {  // in CTA order
+                    const float *sp = staged_part + (size_t)i * (kBN * kBM) + c0 * kBM + n_local;
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        v[j] = __float_as_uint(__uint_as_float(v[j]) + staged_part[(c0 + j) * kBM + n_local]);
+                        v[j] = __float_as_uint(__uint_as_float(v[j]) + sp[j * kBM]);
                 }
-                for (uint32_t p = blockIdx.x + 1 + (staged ? 1 : 0); p < last; ++p) {
+                for (uint32_t p = blockIdx.x + 1 + n_staged; p < last; ++p) {
                     const float *src = g.partials + (size_t)p * slot_elems + (size_t)c0 * kBM + n_local;
 #pragma unroll
                     for (int j = 0; j < 16; ++j)

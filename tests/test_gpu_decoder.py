@@ -206,3 +206,49 @@ def test_large_batch_takes_the_tensor_core_gemm_and_lm_head(gpu_ctx):
     got = graph.decode(2)
     assert np.array_equal(got[:, :3], want_t)
     del eager_tokens
+
+
+@pytest.mark.parametrize("heads,kv_heads", [(8, 8), (8, 2), (16, 1), (12, 2)])
+def test_decode_attention_tensor_core_kernel(gpu_ctx, heads, kv_heads):
+    """bfloat16 cache, head_dim 128: the bf16 tensor-core kernel against the exact oracle and
+    against the scalar kernel, for MHA, GQA groups of 4 and 6, and a group of 16 (two blocks
+    of eight heads per kv head); ragged lengths including one key and a length that is not a
+    multiple of the 16-key step."""
+    import ctypes
+    import torch
+    from oracle import attention_np as anp
+    from quantibbler_b200 import _lib
+    rng = np.random.default_rng(heads * 10 + kv_heads)
+    B, d, S = 3, 128, 533
+    lens = np.array([533, 1, 250], np.int32)
+    q = rng.standard_normal((B, heads, d)).astype(np.float32)
+    k = decoder_np._bf16(rng.standard_normal((B, kv_heads, S, d)).astype(np.float32))
+    v = decoder_np._bf16(rng.standard_normal((B, kv_heads, S, d)).astype(np.float32))
+    tq = torch.from_numpy(q).cuda()
+    tk = torch.from_numpy(k).cuda().to(torch.bfloat16)
+    tv = torch.from_numpy(v).cuda().to(torch.bfloat16)
+    tl = torch.from_numpy(lens).cuda()
+    lib = _lib.lib()
+    n_splits = 3
+    scratch = torch.zeros(lib.qk_decode_attention_scratch(B, heads, d, n_splits) // 4 + 4, device="cuda")
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    outs = []
+    for which in (2, 0):
+        out = torch.zeros(B, heads, d, device="cuda")
+        torch.cuda.synchronize()
+        before = lib.qk_set_decode_attention_kernel(gpu_ctx.handle, which)
+        try:
+            _lib.check(lib.qk_decode_attention(gpu_ctx.handle, p(tq), p(tk), p(tv), _lib.QK_BF16, p(tl),
+                                               B, heads, kv_heads, d, S, n_splits, p(scratch), p(out)))
+            gpu_ctx.synchronize()
+        finally:
+            lib.qk_set_decode_attention_kernel(gpu_ctx.handle, before)
+        outs.append(out.cpu().numpy())
+    tc, scalar = outs
+    group = heads // kv_heads
+    for b in range(B):
+        n = lens[b]
+        want = anp.attention_exact(q[b][None, :, None, :], k[b][None, :, :n], v[b][None, :, :n],
+                                   causal=True)[0, :, 0]
+        assert np.abs(tc[b] - want).max() <= 1e-5 * max(1.0, np.abs(want).max()), (b, group)
+    assert np.abs(tc - scalar).max() <= 2e-5
