@@ -280,9 +280,13 @@ def run_prefill(args, local_rank: int) -> None:
     ctx.set_stream(stream.cuda_stream)
     torch.cuda.synchronize()
 
+    from quantibbler_b200.gpu import apply_prefill_many
+
     def step():
-        for layer, (x, y) in zip(layers, bufs):
-            layer.apply_prefill(x.data_ptr(), T, y.data_ptr())
+        # gate and up read the same activations: one call (one launch per stage) serves both
+        apply_prefill_many(layers[:2], bufs[0][0].data_ptr(), T,
+                           [bufs[0][1].data_ptr(), bufs[1][1].data_ptr()])
+        layers[2].apply_prefill(bufs[2][0].data_ptr(), T, bufs[2][1].data_ptr())
 
     warmup = max(args.warmup, 3)
     sampler = ClockSampler(local_rank)

@@ -212,6 +212,11 @@ qk_status qk_layer_apply(qk_ctx *ctx, const qk_layer *layer, const float *x_dev,
  * is incomplete and the next qk_gpu_synchronize returns QK_ERR_TIMEOUT. */
 qk_status qk_layer_apply_prefill(qk_ctx *ctx, const qk_layer *layer, const float *x_dev,
                                  size_t n_tokens, float *y_dev);
+/* The same for up to four layers that read the same x_dev (the q, k, v or the gate, up
+ * projections of a block): one scaling launch and one launch per stage serve them all,
+ * y_devs[i] [n_tokens, layers[i]->dout].  The layers must have the same din. */
+qk_status qk_layers_apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers,
+                                  const float *x_dev, size_t n_tokens, float *const *y_devs);
 /* One token through one layer without any allocation by the library.  It has no
  * counterpart in the reference.  For callers that cannot let a library allocate device
  * memory on their behalf: a server that gave all remaining device memory to its KV cache

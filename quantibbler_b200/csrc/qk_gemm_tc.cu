@@ -115,29 +115,51 @@ __device__ __forceinline__ uint32_t expand_nibble(uint32_t n) {
     return ((n * 0x10204080u) & 0x80808080u) ^ 0xBFBFBFBFu;
 }
 
-struct GemmArgs {
+// One launch can serve up to four factors that share the token count (the q, k, v or the
+// gate, up projections of a block): problem p owns the units [unit_begin, next unit_begin).
+constexpr int kMaxProblems = 4;
+struct Problem {
     const uint8_t *w_rows; // weight bits, rows padded to w_stride bytes
     void *out;             // bf16 [tokens][out_pitch] (stage 1) or float [tokens][n_rows]
     const float *out_scale, *out_bias;
+    uint32_t n_rows, k_chunks, w_stride, out_pitch;
+    uint32_t row_tiles;    // tile t of the problem covers row tile t % row_tiles, token tile t / row_tiles
+    uint32_t unit_begin;   // the problem's first unit; a tile is k_chunks consecutive units
+};
+struct GemmArgs {
+    Problem p[kMaxProblems];
+    uint32_t n_problems;
     int *error;
-    uint32_t tokens, n_rows, k_chunks, w_stride, out_pitch;
+    uint32_t tokens;
     uint32_t bn;           // tokens per tile
-    uint32_t row_tiles;    // tile t covers row tile t % row_tiles, token tile t / row_tiles
-    uint32_t units;        // tiles x k_chunks: the work that is dealt out evenly to the CTAs
+    uint32_t units;        // all tiles x their k_chunks: the work that is dealt out evenly to the CTAs
     float *partials;       // [CTAs][256][128] float32 accumulators of split tiles
     uint32_t *flags;       // [CTAs] flags[i] != 0: CTA i's partial is in place (its one reader clears it)
 };
 
-// CTA i of G works on units [i * units / G, (i + 1) * units / G), unit u being k-chunk
-// u % k_chunks of tile u / k_chunks.
+// CTA i of G works on units [i * units / G, (i + 1) * units / G).
 __device__ __forceinline__ uint32_t unit_begin(uint32_t i, uint32_t units, uint32_t ctas) {
     return (uint32_t)((uint64_t)i * units / ctas);
+}
+
+// Where unit u lies: which problem, which of its tiles, which k-chunk of the tile.
+struct UnitPos {
+    uint32_t problem, tile, kc, tile_begin;  // tile_begin: the unit number of the tile's chunk 0
+};
+__device__ __forceinline__ UnitPos locate(const GemmArgs &g, uint32_t u) {
+    uint32_t pi = 0;
+#pragma unroll
+    for (int i = 1; i < kMaxProblems; ++i)
+        if ((uint32_t)i < g.n_problems && u >= g.p[i].unit_begin) pi = i;
+    const uint32_t local = u - g.p[pi].unit_begin, k = g.p[pi].k_chunks;
+    const uint32_t tile = local / k;
+    return {pi, tile, local - tile * k, g.p[pi].unit_begin + tile * k};
 }
 
 // The epilogue of one output element: kFinal = false: out = bf16(acc) as the next stage's
 // activation (zero in the padding columns);  true: y = bf16(acc) * s1 + bias.
 template <bool kFinal>
-__device__ __forceinline__ void store_output(const GemmArgs &g, uint32_t tok, uint32_t n, uint32_t acc_bits,
+__device__ __forceinline__ void store_output(const Problem &g, uint32_t tok, uint32_t n, uint32_t acc_bits,
                                              float scale, float bias) {
     // one rounding to bfloat16, as packed_matmul's bf16 instantiation does
     const uint32_t rb = round_bf16_hi(acc_bits);
@@ -151,7 +173,9 @@ __device__ __forceinline__ void store_output(const GemmArgs &g, uint32_t tok, ui
 
 template <bool kFinal>
 __global__ void __launch_bounds__(kThreads, 1)
-factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g) {
+factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
+                          const __grid_constant__ CUtensorMap map2, const __grid_constant__ CUtensorMap map3,
+                          GemmArgs g) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment of the tiles is what the swizzle pattern assumes
     uint8_t *tiles = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -214,9 +238,10 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
         const uint2 zero2 = make_uint2(0, 0);
         auto load_bits = [&](uint32_t gc) -> uint2 {
             if (gc >= total_chunks) return zero2;
-            const uint32_t tile = (u_begin + gc) / g.k_chunks, kc = u_begin + gc - tile * g.k_chunks;
-            const uint32_t n_src = min((tile % g.row_tiles) * kBM + row, g.n_rows - 1);
-            return reinterpret_cast<const uint2 *>(g.w_rows + (size_t)n_src * g.w_stride)[kc];
+            const UnitPos at = locate(g, u_begin + gc);
+            const Problem &pr = g.p[at.problem];
+            const uint32_t n_src = min((at.tile % pr.row_tiles) * kBM + row, pr.n_rows - 1);
+            return reinterpret_cast<const uint2 *>(pr.w_rows + (size_t)n_src * pr.w_stride)[at.kc];
         };
         uint2 q0 = load_bits(group), q1 = load_bits(group + kGroups);
         uint32_t it = 0;
@@ -230,8 +255,10 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
             }
             if (row == 0) {
                 // tokens: one TMA box of 64 k x bn tokens, completing on the full barrier
-                const uint32_t tile = (u_begin + gc) / g.k_chunks, kc = u_begin + gc - tile * g.k_chunks;
-                const uint32_t t0 = (tile / g.row_tiles) * kBN;
+                const UnitPos at = locate(g, u_begin + gc);
+                const uint32_t kc = at.kc, t0 = (at.tile / g.p[at.problem].row_tiles) * kBN;
+                const CUtensorMap *b_map = at.problem == 0 ? &map0 : at.problem == 1 ? &map1
+                                         : at.problem == 2 ? &map2 : &map3;
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
                                  smem_u32(my_full)),
                              "r"(kBN * kBK * 2)
@@ -239,7 +266,7 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
                 asm volatile(
                     "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
                     "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(b_tile)),
-                    "l"(&b_map), "r"(kc * kBK), "r"(t0), "r"(smem_u32(my_full))
+                    "l"(b_map), "r"(kc * kBK), "r"(t0), "r"(smem_u32(my_full))
                     : "memory");
             }
 #pragma unroll
@@ -270,7 +297,8 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
         uint32_t gc = 0;
         bool dead = false;
         for (uint32_t u = u_begin, seg = 0; u < u_end && !dead; ++seg) {
-            const uint32_t kc0 = u % g.k_chunks, kc1 = min(g.k_chunks, kc0 + (u_end - u));
+            const UnitPos at = locate(g, u);
+            const uint32_t kc0 = at.kc, kc1 = min(g.p[at.problem].k_chunks, kc0 + (u_end - u));
             const uint32_t acc = seg & 1;
             // the epilogue must have drained this accumulator (segment seg - 2)
             if (!mbar_wait(&acc_empty[acc], ((seg >> 1) & 1) ^ 1, abort_flag)) {
@@ -315,16 +343,18 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
         const size_t slot_elems = (size_t)kBNMax * kBM;
         bool dead = false;
         for (uint32_t u = u_begin, seg = 0; u < u_end && !dead; ++seg) {
-            const uint32_t tile = u / g.k_chunks, kc0 = u - tile * g.k_chunks;
-            const uint32_t len = min(g.k_chunks - kc0, u_end - u);
+            const UnitPos at = locate(g, u);
+            const Problem &pr = g.p[at.problem];
+            const uint32_t tile = at.tile, kc0 = at.kc;
+            const uint32_t len = min(pr.k_chunks - kc0, u_end - u);
             const uint32_t acc = seg & 1;
             const uint32_t n_local = quarter * 32 + lane;
-            const uint32_t n = (tile % g.row_tiles) * kBM + n_local;
-            const uint32_t t0 = (tile / g.row_tiles) * kBN;
+            const uint32_t n = (tile % pr.row_tiles) * kBM + n_local;
+            const uint32_t t0 = (tile / pr.row_tiles) * kBN;
             // CTAs [blockIdx.x + 1, last) hold the rest of this tile
             uint32_t last = blockIdx.x + 1;
-            if (kc0 == 0 && len < g.k_chunks) {
-                const uint32_t hi = (tile + 1) * g.k_chunks;
+            if (kc0 == 0 && len < pr.k_chunks) {
+                const uint32_t hi = at.tile_begin + pr.k_chunks;
                 while (last < gridDim.x && unit_begin(last, g.units, gridDim.x) < hi) ++last;
                 for (uint32_t j = blockIdx.x + 1; j < last && !dead; ++j) {
                     uint32_t seen = 0;
@@ -342,9 +372,9 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const bool n_live = kFinal ? n < g.n_rows : n < g.out_pitch;
-            const float scale = (kFinal && g.out_scale && n < g.n_rows) ? g.out_scale[n] : 1.f;
-            const float bias = (kFinal && g.out_bias && n < g.n_rows) ? g.out_bias[n] : 0.f;
+            const bool n_live = kFinal ? n < pr.n_rows : n < pr.out_pitch;
+            const float scale = (kFinal && pr.out_scale && n < pr.n_rows) ? pr.out_scale[n] : 1.f;
+            const float bias = (kFinal && pr.out_bias && n < pr.n_rows) ? pr.out_bias[n] : 0.f;
             float *part = g.partials + (size_t)blockIdx.x * slot_elems;
             // When this is the CTA's last segment the pipeline has drained and the stages are
             // free: as many of the following CTAs' partials as fit there (each is contiguous,
@@ -413,7 +443,7 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
                     for (int j = 0; j < 16; ++j) {
                         const uint32_t tok = t0 + c0 + j;
                         if (tok >= g.tokens) break;
-                        store_output<kFinal>(g, tok, n, v[j], scale, bias);
+                        store_output<kFinal>(pr, tok, n, v[j], scale, bias);
                     }
                 }
             }
@@ -448,11 +478,17 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap b_map, GemmArgs g)
     if (tid == 0 && *abort_flag) atomicExch(g.error, 1);
 }
 
-// z = bf16(s2 * x) (float32 product, one rounding), zero padded to the pitch.  One thread
-// makes eight consecutive outputs (one 16-byte store).
-__global__ void scale_to_bf16_kernel(const float *__restrict__ x, const float *__restrict__ s2,
-                                     uint16_t *__restrict__ z, uint32_t n_tokens, uint32_t din,
-                                     uint32_t pitch, int vec) {
+// z_p = bf16(s2_p * x) (float32 product, one rounding), zero padded to the pitch, for each of
+// the problems of a launch (grid.y).  One thread makes eight consecutive outputs (one
+// 16-byte store).
+struct ScaleArgs {
+    const float *s2[kMaxProblems];
+    uint16_t *z[kMaxProblems];
+};
+__global__ void scale_to_bf16_kernel(const float *__restrict__ x, ScaleArgs a, uint32_t n_tokens,
+                                     uint32_t din, uint32_t pitch, int vec) {
+    const float *__restrict__ s2 = a.s2[blockIdx.y];
+    uint16_t *__restrict__ z = a.z[blockIdx.y];
     const uint32_t per_row = pitch / 8;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n_tokens * per_row) return;
@@ -460,12 +496,12 @@ __global__ void scale_to_bf16_kernel(const float *__restrict__ x, const float *_
     const float *xr = x + (size_t)t * din;
     float v[8];
     if (vec && k + 8 <= din) {
-        const float4 a = *reinterpret_cast<const float4 *>(xr + k);
-        const float4 b = *reinterpret_cast<const float4 *>(xr + k + 4);
-        const float4 c = *reinterpret_cast<const float4 *>(s2 + k);
-        const float4 d = *reinterpret_cast<const float4 *>(s2 + k + 4);
-        v[0] = c.x * a.x; v[1] = c.y * a.y; v[2] = c.z * a.z; v[3] = c.w * a.w;
-        v[4] = d.x * b.x; v[5] = d.y * b.y; v[6] = d.z * b.z; v[7] = d.w * b.w;
+        const float4 a0 = *reinterpret_cast<const float4 *>(xr + k);
+        const float4 b0 = *reinterpret_cast<const float4 *>(xr + k + 4);
+        const float4 c0 = *reinterpret_cast<const float4 *>(s2 + k);
+        const float4 d0 = *reinterpret_cast<const float4 *>(s2 + k + 4);
+        v[0] = c0.x * a0.x; v[1] = c0.y * a0.y; v[2] = c0.z * a0.z; v[3] = c0.w * a0.w;
+        v[4] = d0.x * b0.x; v[5] = d0.y * b0.y; v[6] = d0.z * b0.z; v[7] = d0.w * b0.w;
     } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = k + i < din ? s2[k + i] * xr[k + i] : 0.f;
@@ -524,75 +560,121 @@ uint32_t pick_bn(size_t tokens) {
 
 extern "C" {
 
-qk_status qk_layer_apply_prefill(qk_ctx *ctx, const qk_layer *layer, const float *x_dev,
-                                 size_t n_tokens, float *y_dev) {
-    if (!layer) return qk::fail(QK_ERR_VALUE, "qk_layer_apply_prefill: layer is null");
-    if (layer->serving != QK_BF16)
-        return qk::fail(QK_ERR_VALUE,
-                        "the tensor-core prefill computes in bfloat16 with float32 accumulation; "
-                        "it needs a layer created with the bfloat16 serving dtype");
+qk_status qk_layers_apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers,
+                                  const float *x_dev, size_t n_tokens, float *const *y_devs) {
+    if (n_layers == 0 || n_layers > (size_t)kMaxProblems)
+        return qk::fail(QK_ERR_VALUE, "between 1 and %d layers per call, got %zu", kMaxProblems, n_layers);
+    if (!layers || !y_devs) return qk::fail(QK_ERR_VALUE, "qk_layers_apply_prefill: null array");
+    for (size_t i = 0; i < n_layers; ++i) {
+        if (!layers[i]) return qk::fail(QK_ERR_VALUE, "qk_layers_apply_prefill: layer %zu is null", i);
+        if (layers[i]->serving != QK_BF16)
+            return qk::fail(QK_ERR_VALUE,
+                            "the tensor-core prefill computes in bfloat16 with float32 accumulation; "
+                            "it needs a layer created with the bfloat16 serving dtype");
+        if (layers[i]->din != layers[0]->din)
+            return qk::fail(QK_ERR_VALUE, "layers of one call share their input: layer %zu has din=%zu, "
+                            "layer 0 has din=%zu", i, layers[i]->din, layers[0]->din);
+    }
     if (n_tokens == 0) return QK_OK;
     qk_ctx *c;
     qk_status st = qk::resolve_ctx(ctx, &c);
     if (st != QK_OK) return st;
     std::lock_guard<std::mutex> lock(c->mu);
     QK_CUDA(cudaSetDevice(c->device));
-    if (layer->device != c->device)
-        return qk::fail(QK_ERR_VALUE, "layer lives on device %d, context on device %d",
-                        layer->device, c->device);
-    const size_t din = layer->din, r = layer->r, dout = layer->dout;
-    const size_t kp1 = qk::ceil_div(din, kBK) * kBK, kp2 = qk::ceil_div(r, kBK) * kBK;
-    // scratch: z [T][kp1] bf16, t [T][kp2] bf16; the error word lives for the context's life
+    for (size_t i = 0; i < n_layers; ++i)
+        if (layers[i]->device != c->device)
+            return qk::fail(QK_ERR_VALUE, "layer lives on device %d, context on device %d",
+                            layers[i]->device, c->device);
+    const size_t din = layers[0]->din;
+    const size_t kp1 = qk::ceil_div(din, kBK) * kBK;
+    // scratch: per layer z [T][kp1] and t [T][kp2] in bfloat16; the error word and the CTA
+    // flags live for the context's life
     const size_t z_bytes = qk::ceil_div(n_tokens * kp1 * 2, 256) * 256;
-    const size_t t_bytes = qk::ceil_div(n_tokens * kp2 * 2, 256) * 256;
-    if ((st = c->d_z.reserve(z_bytes + t_bytes)) != QK_OK) return st;
+    size_t kp2[kMaxProblems], t_off[kMaxProblems], need = n_layers * z_bytes;
+    for (size_t i = 0; i < n_layers; ++i) {
+        kp2[i] = qk::ceil_div(layers[i]->r, kBK) * kBK;
+        t_off[i] = need;
+        need += qk::ceil_div(n_tokens * kp2[i] * 2, 256) * 256;
+    }
+    if ((st = c->d_z.reserve(need)) != QK_OK) return st;
     if (!c->d_err.ptr) {
         if ((st = c->d_err.reserve(256 + 4096)) != QK_OK) return st;  // error word + CTA flags
         QK_CUDA(cudaMemsetAsync(c->d_err.ptr, 0, 256 + 4096, c->stream));
     }
-    uint16_t *z = (uint16_t *)c->d_z.ptr;
-    uint16_t *t = (uint16_t *)((uint8_t *)c->d_z.ptr + z_bytes);
+    uint8_t *base = (uint8_t *)c->d_z.ptr;
     int *err = (int *)c->d_err.ptr;
+    ScaleArgs sa{};
+    for (size_t i = 0; i < n_layers; ++i) {
+        sa.s2[i] = layers[i]->s2;
+        sa.z[i] = (uint16_t *)(base + i * z_bytes);
+    }
     const int vec = ((uintptr_t)x_dev & 15) == 0 && (din & 3) == 0;
     const size_t total = n_tokens * (kp1 / 8);
-    scale_to_bf16_kernel<<<(unsigned)qk::ceil_div(total, 256), 256, 0, c->stream>>>(
-        x_dev, layer->s2, z, (uint32_t)n_tokens, (uint32_t)din, (uint32_t)kp1, vec);
+    scale_to_bf16_kernel<<<dim3((unsigned)qk::ceil_div(total, 256), (unsigned)n_layers), 256, 0, c->stream>>>(
+        x_dev, sa, (uint32_t)n_tokens, (uint32_t)din, (uint32_t)kp1, vec);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     QK_CUDA(cudaFuncSetAttribute(factorized_gemm_tc_kernel<false>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
     QK_CUDA(cudaFuncSetAttribute(factorized_gemm_tc_kernel<true>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-    const size_t rows1 = qk::ceil_div(kp2, kBM), rows2 = qk::ceil_div(dout, kBM);
     const uint32_t bn = pick_bn(n_tokens);
     const size_t tok_tiles = qk::ceil_div(n_tokens, bn);
-    CUtensorMap map1, map2;
-    if ((st = encode_activation_map(z, n_tokens, kp1, bn, &map1)) != QK_OK) return st;
-    if ((st = encode_activation_map(t, n_tokens, kp2, bn, &map2)) != QK_OK) return st;
+    uint32_t *flags = (uint32_t *)c->d_err.ptr + 64;  // after the error word's 256 bytes
+    GemmArgs g1{}, g2{};
+    CUtensorMap maps1[kMaxProblems], maps2[kMaxProblems];
+    size_t units1 = 0, units2 = 0;
+    for (size_t i = 0; i < n_layers; ++i) {
+        const qk_layer *L = layers[i];
+        uint16_t *z = (uint16_t *)(base + i * z_bytes), *t = (uint16_t *)(base + t_off[i]);
+        if ((st = encode_activation_map(z, n_tokens, kp1, bn, &maps1[i])) != QK_OK) return st;
+        if ((st = encode_activation_map(t, n_tokens, kp2[i], bn, &maps2[i])) != QK_OK) return st;
+        const size_t rows1 = qk::ceil_div(kp2[i], kBM), rows2 = qk::ceil_div(L->dout, kBM);
+        g1.p[i] = Problem{L->vbt, t, nullptr, nullptr, (uint32_t)L->r, (uint32_t)(kp1 / kBK),
+                          (uint32_t)L->vbt_stride, (uint32_t)kp2[i], (uint32_t)rows1, (uint32_t)units1};
+        g2.p[i] = Problem{L->ub, y_devs[i], L->s1, L->bias, (uint32_t)L->dout, (uint32_t)(kp2[i] / kBK),
+                          (uint32_t)L->ub_stride, (uint32_t)L->dout, (uint32_t)rows2, (uint32_t)units2};
+        units1 += rows1 * tok_tiles * (kp1 / kBK);
+        units2 += rows2 * tok_tiles * (kp2[i] / kBK);
+    }
+    for (size_t i = n_layers; i < (size_t)kMaxProblems; ++i) {  // unused slots: valid descriptors
+        maps1[i] = maps1[0];
+        maps2[i] = maps2[0];
+    }
+    if (units1 >= (1ull << 32) || units2 >= (1ull << 32))
+        return qk::fail(QK_ERR_VALUE, "the work of one call must stay below 2^32 tile-chunks");
     // every CTA gets the same number of (tile, k-chunk) units, at least eight of them
     const auto ctas_for = [&](size_t units) {
         return (unsigned)std::max<size_t>(1, std::min<size_t>((size_t)c->sm_count, units / 8));
     };
-    const size_t units1 = rows1 * tok_tiles * (kp1 / kBK), units2 = rows2 * tok_tiles * (kp2 / kBK);
     const unsigned grid1 = ctas_for(units1), grid2 = ctas_for(units2);
     const size_t slot_bytes = (size_t)kBNMax * kBM * sizeof(float);
     if ((st = c->d_t.reserve((size_t)std::max(grid1, grid2) * slot_bytes)) != QK_OK) return st;
     float *partials = (float *)c->d_t.ptr;
-    uint32_t *flags = (uint32_t *)c->d_err.ptr + 64;  // after the error word's 256 bytes
-    GemmArgs g1{layer->vbt, t, nullptr, nullptr, err, (uint32_t)n_tokens, (uint32_t)r,
-                (uint32_t)(kp1 / kBK), (uint32_t)layer->vbt_stride, (uint32_t)kp2, bn,
-                (uint32_t)rows1, (uint32_t)units1, partials, flags};
-    factorized_gemm_tc_kernel<false><<<grid1, kThreads, kSmemBytes, c->stream>>>(map1, g1);
+    g1.n_problems = g2.n_problems = (uint32_t)n_layers;
+    g1.error = g2.error = err;
+    g1.tokens = g2.tokens = (uint32_t)n_tokens;
+    g1.bn = g2.bn = bn;
+    g1.units = (uint32_t)units1;
+    g2.units = (uint32_t)units2;
+    g1.partials = g2.partials = partials;
+    g1.flags = g2.flags = flags;
+    factorized_gemm_tc_kernel<false><<<grid1, kThreads, kSmemBytes, c->stream>>>(
+        maps1[0], maps1[1], maps1[2], maps1[3], g1);
     QK_CUDA(cudaGetLastError());
     c->launches++;
-    GemmArgs g2{layer->ub, y_dev, layer->s1, layer->bias, err, (uint32_t)n_tokens, (uint32_t)dout,
-                (uint32_t)(kp2 / kBK), (uint32_t)layer->ub_stride, (uint32_t)dout, bn,
-                (uint32_t)rows2, (uint32_t)units2, partials, flags};
-    factorized_gemm_tc_kernel<true><<<grid2, kThreads, kSmemBytes, c->stream>>>(map2, g2);
+    factorized_gemm_tc_kernel<true><<<grid2, kThreads, kSmemBytes, c->stream>>>(
+        maps2[0], maps2[1], maps2[2], maps2[3], g2);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     c->err_armed = true;
     return QK_OK;
+}
+
+qk_status qk_layer_apply_prefill(qk_ctx *ctx, const qk_layer *layer, const float *x_dev,
+                                 size_t n_tokens, float *y_dev) {
+    if (!layer) return qk::fail(QK_ERR_VALUE, "qk_layer_apply_prefill: layer is null");
+    return qk_layers_apply_prefill(ctx, &layer, 1, x_dev, n_tokens, &y_dev);
 }
 
 }  // extern "C"

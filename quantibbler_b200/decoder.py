@@ -21,7 +21,7 @@ import numpy as np
 
 from . import _lib, tp
 from ._lib import QK_BF16, QK_F32, check
-from .gpu import GpuContext, LayerPlan, PackedLayer
+from .gpu import GpuContext, LayerPlan, PackedLayer, apply_prefill_many
 
 LINEARS = ("q", "k", "v", "o", "gate", "up", "down")
 
@@ -221,8 +221,8 @@ class Decoder:
         """The named linears of layer ``li`` from ``src`` into ``dsts`` for the whole batch."""
         B = self.cfg.max_batch
         if self.use_gemm:
-            for name, dst in zip(names, dsts):
-                self.layers[li][name].apply_prefill(src.data_ptr(), B, dst.data_ptr())
+            apply_prefill_many([self.layers[li][n] for n in names], src.data_ptr(), B,
+                               [dst.data_ptr() for dst in dsts])
             return
         plan = self.plans[li]
         joint = {("k", "v"): "kv", ("gate", "up"): "gu"}.get(tuple(names))
@@ -245,8 +245,11 @@ class Decoder:
             plan = self.plans[li]
             check(lib.qk_rmsnorm(c, _p(self.x), residual, _p(in_w), B, d, cfg.rms_eps,
                                  self.serving_tag, _p(self.x), _p(self.h)))
-            self._linears(li, ["q"], self.h, [self.q])
-            self._linears(li, ["k", "v"], self.h, [self.k, self.v])
+            if self.use_gemm:
+                self._linears(li, ["q", "k", "v"], self.h, [self.q, self.k, self.v])
+            else:
+                self._linears(li, ["q"], self.h, [self.q])
+                self._linears(li, ["k", "v"], self.h, [self.k, self.v])
             check(lib.qk_rope_cache(c, _p(self.q), _p(self.k), _p(self.v), _p(self.cos_sin),
                                     _p(self.positions), _p(self.seq_index), _p(self.cache_k[li]),
                                     _p(self.cache_v[li]), self.kv_tag, B, self.h_loc, self.kv_loc,

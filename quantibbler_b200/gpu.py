@@ -283,6 +283,16 @@ class PackedLayer:
                                         int(n_tokens), ctypes.c_void_p(y_ptr)))
 
 
+def apply_prefill_many(layers, x_ptr: int, n_tokens: int, y_ptrs) -> None:
+    """Up to four bfloat16-serving layers that read the same input (q, k, v or gate, up) through
+    the tensor-core GEMM with one launch per stage for all of them.  Asynchronous."""
+    n = len(layers)
+    handles = (ctypes.c_void_p * n)(*[layer._h for layer in layers])
+    outs = (ctypes.c_void_p * n)(*[ctypes.c_void_p(p) for p in y_ptrs])
+    check(_lib.lib().qk_layers_apply_prefill(layers[0].ctx.handle, handles, n, ctypes.c_void_p(x_ptr),
+                                             int(n_tokens), outs))
+
+
 def apply_noalloc(layer: PackedLayer, x_ptr: int, y_ptr: int) -> None:
     """One token through ``layer`` with the library allocating nothing: for hosts that own
     all device memory themselves (for example a server whose KV cache took what was left

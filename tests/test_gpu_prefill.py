@@ -56,3 +56,47 @@ def test_prefill_needs_bf16_serving(gpu_ctx):
     layer = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], 32, 64, 16, L["s1"], L["s2"])
     with pytest.raises(ValueError, match="bfloat16 serving"):
         layer.apply_prefill(0, 4, 0)
+
+
+def test_several_layers_in_one_call(gpu_ctx):
+    """q, k, v style: three layers of different ranks and widths on the same input through
+    one launch per stage; each must agree with its own single-layer call (the work is dealt
+    out differently, so split tiles add their partial sums in another order: equal up to one
+    bfloat16 rounding of an intermediate) and with the oracle."""
+    import torch
+    from quantibbler_b200.gpu import apply_prefill_many
+    din, n_tokens = 320, 150
+    shapes = [(260, 70), (96, 33), (512, 200)]
+    rng = np.random.default_rng(3)
+    xs = rng.standard_normal((n_tokens, din)).astype(np.float32)
+    x = torch.from_numpy(xs).cuda()
+    params, layers, ys = [], [], []
+    for i, (dout, r) in enumerate(shapes):
+        L = make_layer(dout, din, r, seed=40 + i, with_bias=i == 1)
+        params.append(L)
+        layers.append(PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], dout, din, r, L["s1"], L["s2"],
+                                  L["bias"], serving="bfloat16"))
+        ys.append(torch.full((n_tokens, dout), float("nan"), device="cuda"))
+    torch.cuda.synchronize()
+    apply_prefill_many(layers, x.data_ptr(), n_tokens, [y.data_ptr() for y in ys])
+    gpu_ctx.synchronize()
+    for (dout, r), L, layer, y in zip(shapes, params, layers, ys):
+        got = y.cpu().numpy()
+        assert np.isfinite(got).all()
+        single = torch.zeros(n_tokens, dout, device="cuda")
+        layer.apply_prefill(x.data_ptr(), n_tokens, single.data_ptr())
+        gpu_ctx.synchronize()
+        ref = single.cpu().numpy()
+        assert np.abs(got - ref).max() <= 1e-2 * np.abs(ref).max()
+        assert np.mean(got == ref) >= 0.99
+        for t in (0, n_tokens - 1):
+            want = oracle.layer_apply(L["ub_rows"], L["vb_t_rows"], dout, din, r, L["s1"], L["s2"],
+                                      L["bias"], xs[t], serving="bfloat16")
+            assert np.abs(got[t] - want).max() <= 2e-2 * np.abs(want).max()
+        layer.close()
+    with pytest.raises(ValueError, match="share their input"):
+        a = make_layer(32, 64, 16, seed=1)
+        b = make_layer(32, 128, 16, seed=2)
+        la = PackedLayer(gpu_ctx, a["ub_rows"], a["vb_t_rows"], 32, 64, 16, a["s1"], a["s2"], None, serving="bfloat16")
+        lb = PackedLayer(gpu_ctx, b["ub_rows"], b["vb_t_rows"], 32, 128, 16, b["s1"], b["s2"], None, serving="bfloat16")
+        apply_prefill_many([la, lb], 0, 4, [0, 0])
