@@ -196,13 +196,15 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
         cfg = DecoderConfig(n_layers=args.n_layers or 32, d_model=4096, n_heads=32, n_kv_heads=8,
                             head_dim=128, d_ff=14336, vocab=128256, rms_eps=1e-5,
                             rope_theta=500000.0, serving="bfloat16", kv_dtype="bfloat16",
-                            max_seq=ctx_len + args.steps + args.warmup + 8, max_batch=B)
+                            max_seq=ctx_len + args.steps + args.warmup + 8, max_batch=B,
+                            fused_allreduce=args.allreduce == "fused")
         ranks = C4_RANKS
     else:  # one Llama-2-7B-shaped layer (config 3)
         cfg = DecoderConfig(n_layers=args.n_layers or 1, d_model=4096, n_heads=32, n_kv_heads=32,
                             head_dim=128, d_ff=11008, vocab=32000, rms_eps=1e-5,
                             rope_theta=10000.0, serving="bfloat16", kv_dtype="bfloat16",
-                            max_seq=ctx_len + args.steps + args.warmup + 8, max_batch=B)
+                            max_seq=ctx_len + args.steps + args.warmup + 8, max_batch=B,
+                            fused_allreduce=args.allreduce == "fused")
         ranks = C3_RANKS
     ctx = GpuContext.init_at(local_rank)
     weights = random_model(cfg, ranks, seed=0, device_tables=True)
@@ -243,8 +245,11 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
             "config": {"workload": f"{args.model} shape, {cfg.n_layers} layers, all linears "
                                    f"binary-factorized at ~0.55 bpw, greedy decode, batch {B}, "
                                    f"context {ctx_len} (synthetic KV cache), one CUDA graph per step",
-                       "parallelism": f"tp{world}, NCCL all-reduce per attention block and per "
-                                      f"MLP block", "ranks": ranks}}), flush=True)
+                       "parallelism": f"tp{world}, one all-reduce per attention block and per "
+                                      f"MLP block ("
+                                      + ("summed over NVLink peer memory inside the RMSNorm kernel"
+                                         if dec.fused_ar else "NCCL") + ")",
+                       "ranks": ranks}}), flush=True)
     if world > 1:
         # A captured graph still holds NCCL kernels; tearing the communicator down under it
         # can block at exit.  Everything is measured and printed: leave without the teardown.
@@ -434,6 +439,8 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--n-layers", type=int, default=0)
+    ap.add_argument("--allreduce", default="nccl", choices=["fused", "nccl"],
+                    help="decode workload under tensor parallelism")
     args = ap.parse_args()
 
     if args.shape:

@@ -264,6 +264,19 @@ void qk_group_free(qk_group *group);
 qk_status qk_rmsnorm(qk_ctx *ctx, const float *x, const float *residual, const float *weight,
                      size_t n_tokens, size_t d, float eps, int32_t serving_dtype, float *x_out,
                      float *y);
+/* Tensor parallel: RMSNorm whose residual input is the SUM over ranks of the row-parallel
+ * linears' partial outputs, read straight from the peers' memory (NVLink peer loads, summed
+ * in rank order: every rank gets the same bits) - the all-reduce after the o and down
+ * projections fused into the norm that follows it.  No reference counterpart (the reference
+ * has no parallelism).  peer_bufs[r] / peer_flags[r]: device addresses, valid on this GPU, of
+ * rank r's partial [n_tokens, d] float32 and of rank r's `world` flag words (zero at start);
+ * state_dev: two zero-initialised words of this rank (call count, block ticket).  Consecutive
+ * calls must alternate between two partial buffers.  Every wait is bounded; on expiry the next
+ * qk_gpu_synchronize returns QK_ERR_TIMEOUT.  x_out = x + sum, y = norm(x_out) * weight. */
+qk_status qk_allreduce_rmsnorm(qk_ctx *ctx, const uint64_t *peer_bufs, const uint64_t *peer_flags,
+                               uint32_t *state_dev, int32_t rank, int32_t world, const float *x,
+                               const float *weight, size_t n_tokens, size_t d, float eps,
+                               int32_t serving_dtype, float *x_out, float *y);
 /* engine/mod.rs:1169-1184 (rope_rotate) and :1204-1209 (KvCache::push).  Rotates q
  * [tokens, n_heads*d] in place and writes the rotated k and v [tokens, n_kv*d] into the
  * head-major cache [n_seq, n_kv, s_max, d] (float32 or bfloat16) at row positions[t] of

@@ -99,6 +99,8 @@ _SIGNATURES = {
     "qk_qpk1_scales": (c_int32, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),
     "qk_layer_from_qpk1": (c_int32, [c_void_p, c_void_p, c_size_t, c_int32, c_void_p]),
     "qk_set_sage_kernel": (c_int32, [c_void_p, c_int32]),
+    "qk_allreduce_rmsnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p,
+                                       c_void_p, c_size_t, c_size_t, c_float, c_int32, c_void_p, c_void_p]),
     "qk_set_decode_attention_kernel": (c_int32, [c_void_p, c_int32]),
     "qk_gpu_attention_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
                                        c_void_p]),

@@ -43,6 +43,8 @@ class DecoderConfig:
     max_batch: int = 1
     n_splits: int = 0              # key splits of the decode attention (0 = choose)
     gemm_min_batch: int = 16       # bfloat16 serving: batches this large take the tensor-core GEMM
+    fused_allreduce: bool = False  # tensor parallel: sum the partials over peer memory inside the norm
+                                   # (measured slower than NCCL + norm at these sizes)
 
 
 def rope_table(cfg: DecoderConfig) -> np.ndarray:
@@ -146,7 +148,13 @@ class Decoder:
         self.k = torch.zeros(B, self.kv_loc * hd, **f32)
         self.v = torch.zeros(B, self.kv_loc * hd, **f32)
         self.attn = torch.zeros(B, self.h_loc * hd, **f32)
-        self.delta = torch.zeros(B, d, **f32)      # o / down output, all-reduced under TP
+        # o / down outputs (one partial per rank under TP).  With the fused all-reduce the two
+        # are separate buffers in symmetric memory that every peer can read.
+        self.delta = torch.zeros(B, d, **f32)
+        self.delta_attn = self.delta_mlp = self.delta
+        self.fused_ar = False
+        if tp_size > 1 and cfg.fused_allreduce:
+            self._setup_fused_allreduce(B, d)
         self.g = torch.zeros(B, self.ff_loc, **f32)
         self.u = torch.zeros(B, self.ff_loc, **f32)
         self.a = torch.zeros(B, self.ff_loc, **f32)
@@ -192,8 +200,8 @@ class Decoder:
                         for n, dst in zip(names, dsts)]
 
             plan = {"q": LayerPlan(ctx, inst(["q"], self.h, [self.q])),
-                    "o": LayerPlan(ctx, inst(["o"], self.attn, [self.delta])),
-                    "down": LayerPlan(ctx, inst(["down"], self.a, [self.delta]))}
+                    "o": LayerPlan(ctx, inst(["o"], self.attn, [self.delta_attn])),
+                    "down": LayerPlan(ctx, inst(["down"], self.a, [self.delta_mlp]))}
             same_kv = all(lw["k"][f] == lw["v"][f] for f in ("dout", "din", "r"))
             if same_kv:
                 plan["kv"] = LayerPlan(ctx, inst(["k", "v"], self.h, [self.k, self.v]))
@@ -212,10 +220,55 @@ class Decoder:
         self.use_gemm = cfg.serving == "bfloat16" and B >= cfg.gemm_min_batch
         self.graph = None
 
-    # ------------------------------------------------------------------ one step
+    # ------------------------------------------------------------------ tensor parallel
+    def _setup_fused_allreduce(self, B: int, d: int) -> None:
+        """Partial-output buffers and flag words in symmetric memory (every rank maps every
+        peer's copy), for ``qk_allreduce_rmsnorm``.  If the peers cannot be mapped the decoder
+        keeps the NCCL all-reduce and says so in ``fused_ar``."""
+        torch = self.torch
+        try:
+            import torch.distributed._symmetric_memory as symm
+            dev = torch.device("cuda", torch.cuda.current_device())
+            self._sym_delta = symm.empty((2, B, d), dtype=torch.float32, device=dev)
+            self._sym_flags = symm.empty((64,), dtype=torch.int32, device=dev)
+            self._sym_delta.zero_()
+            self._sym_flags.zero_()
+            hd = symm.rendezvous(self._sym_delta, self.group)
+            hf = symm.rendezvous(self._sym_flags, self.group)
+            bufs, flags = list(hd.buffer_ptrs), list(hf.buffer_ptrs)
+        except Exception as exc:  # no peer access on this box: NCCL stays
+            self.fused_ar_error = repr(exc)
+            return
+        torch.cuda.synchronize()
+        torch.distributed.barrier(group=self.group)   # every rank's flags are zero before any signal
+        step_bytes = B * d * 4
+        self._peer_bufs = [np.array([b + which * step_bytes for b in bufs], dtype=np.uint64)
+                           for which in (0, 1)]
+        self._peer_flags = np.array(flags, dtype=np.uint64)
+        self._ar_state = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.delta_attn, self.delta_mlp = self._sym_delta[0], self._sym_delta[1]
+        self.fused_ar = True
+
     def _all_reduce(self, t):
-        if self.tp_size > 1:
+        if self.tp_size > 1 and not self.fused_ar:
             self.torch.distributed.all_reduce(t, group=self.group)
+
+    def _norm(self, pending, weight) -> None:
+        """x += pending partial outputs (summed over the ranks); h = RMSNorm(x) * weight.
+        ``pending``: None, 0 (attention block's o output) or 1 (MLP block's down output)."""
+        lib, c, cfg = _lib.lib(), self.ctx.handle, self.cfg
+        B, d = cfg.max_batch, cfg.d_model
+        if pending is not None and self.fused_ar:
+            check(lib.qk_allreduce_rmsnorm(
+                c, self._peer_bufs[pending].ctypes.data, self._peer_flags.ctypes.data,
+                _p(self._ar_state), self.tp_rank, self.tp_size, _p(self.x), _p(weight), B, d,
+                cfg.rms_eps, self.serving_tag, _p(self.x), _p(self.h)))
+            return
+        residual = None if pending is None else _p(self.delta_attn if pending == 0 else self.delta_mlp)
+        check(lib.qk_rmsnorm(c, _p(self.x), residual, _p(weight), B, d, cfg.rms_eps,
+                             self.serving_tag, _p(self.x), _p(self.h)))
+
+    # ------------------------------------------------------------------ one step
 
     def _linears(self, li: int, names, src, dsts) -> None:
         """The named linears of layer ``li`` from ``src`` into ``dsts`` for the whole batch."""
@@ -239,12 +292,10 @@ class Decoder:
         B, d, hd = cfg.max_batch, cfg.d_model, cfg.head_dim
         check(lib.qk_embed(c, _p(self.embedding), self.emb_tag, _p(self.token_ids), B, d, cfg.vocab,
                            _p(self.x)))
-        residual = None
+        pending = None
         for li in range(cfg.n_layers):
             in_w, post_w = self.norms[li]
-            plan = self.plans[li]
-            check(lib.qk_rmsnorm(c, _p(self.x), residual, _p(in_w), B, d, cfg.rms_eps,
-                                 self.serving_tag, _p(self.x), _p(self.h)))
+            self._norm(pending, in_w)
             if self.use_gemm:
                 self._linears(li, ["q", "k", "v"], self.h, [self.q, self.k, self.v])
             else:
@@ -258,17 +309,15 @@ class Decoder:
                                           self.kv_tag, _p(self.kv_len), B, self.h_loc, self.kv_loc,
                                           hd, cfg.max_seq, self.n_splits, _p(self.att_scratch),
                                           _p(self.attn)))
-            self._linears(li, ["o"], self.attn, [self.delta])
-            self._all_reduce(self.delta)
-            check(lib.qk_rmsnorm(c, _p(self.x), _p(self.delta), _p(post_w), B, d, cfg.rms_eps,
-                                 self.serving_tag, _p(self.x), _p(self.h)))
+            self._linears(li, ["o"], self.attn, [self.delta_attn])
+            self._all_reduce(self.delta_attn)
+            self._norm(0, post_w)
             self._linears(li, ["gate", "up"], self.h, [self.g, self.u])
             check(lib.qk_swiglu(c, _p(self.g), _p(self.u), B * self.ff_loc, _p(self.a)))
-            self._linears(li, ["down"], self.a, [self.delta])
-            self._all_reduce(self.delta)
-            residual = _p(self.delta)
-        check(lib.qk_rmsnorm(c, _p(self.x), residual, _p(self.final_norm), B, d, cfg.rms_eps,
-                             self.serving_tag, _p(self.x), _p(self.h)))
+            self._linears(li, ["down"], self.a, [self.delta_mlp])
+            self._all_reduce(self.delta_mlp)
+            pending = 1
+        self._norm(pending, self.final_norm)
         head_tag = QK_BF16 if cfg.serving == "bfloat16" else QK_F32
         check(lib.qk_lm_head(c, _p(self.h), _p(self.lm_head), head_tag, B, self.v_loc, d,
                              self.v_loc, _p(self.logits)))
