@@ -35,7 +35,7 @@ sys.path.insert(0, ROOT)
 
 DOUT = DIN = 4096
 RANK = 1024
-# bits of both factors + s1,s2 + x + y, float32 vectors
+# algorithmic bytes of one layer-apply: bits of both factors + s1,s2 + x + y, float32 vectors
 BYTES_PER_APPLY = (DOUT * RANK + DIN * RANK) // 8 + 4 * (DOUT + DIN) + 4 * DIN + 4 * DOUT
 # dram__bytes_read.sum + dram__bytes_write.sum of one fused-kernel launch over 296 layers
 # (profiles/layer_bitslice_fused_kernel_config0_stack296.md): 330.915 MB, i.e. per layer

@@ -44,7 +44,8 @@ class DecoderConfig:
     n_splits: int = 0              # key splits of the decode attention (0 = choose)
     gemm_min_batch: int = 16       # bfloat16 serving: batches this large take the tensor-core GEMM
     fused_allreduce: bool = False  # tensor parallel: sum the partials over peer memory inside the norm
-                                   # (measured slower than NCCL + norm at these sizes)
+                                   # (on two B200 it measured slower than NCCL followed by the norm:
+                                   # 5.13 against 4.55 ms per batch-1 step of the 32-layer model)
 
 
 def rope_table(cfg: DecoderConfig) -> np.ndarray:
