@@ -439,7 +439,7 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--n-layers", type=int, default=0)
-    ap.add_argument("--allreduce", default="nccl", choices=["fused", "nccl"],
+    ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
                     help="decode workload under tensor parallelism")
     args = ap.parse_args()
 

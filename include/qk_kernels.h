@@ -265,15 +265,17 @@ qk_status qk_rmsnorm(qk_ctx *ctx, const float *x, const float *residual, const f
                      size_t n_tokens, size_t d, float eps, int32_t serving_dtype, float *x_out,
                      float *y);
 /* Tensor parallel: RMSNorm whose residual input is the SUM over ranks of the row-parallel
- * linears' partial outputs, read straight from the peers' memory (NVLink peer loads, summed
- * in rank order: every rank gets the same bits) - the all-reduce after the o and down
- * projections fused into the norm that follows it.  No reference counterpart (the reference
- * has no parallelism).  peer_bufs[r] / peer_flags[r]: device addresses, valid on this GPU, of
- * rank r's partial [n_tokens, d] float32 and of rank r's `world` flag words (zero at start);
+ * linears' partial outputs - the all-reduce after the o and down projections fused into the
+ * norm that follows it.  Every rank pushes its partial into an inbox in each peer's memory
+ * (NVLink peer stores; every 8-byte word carries the value and the number of the all-reduce,
+ * so no flags and no fences are needed) and adds what arrives in its own inbox in rank order:
+ * every rank gets the same bits.  No reference counterpart (the reference has no parallelism).
+ * partial: this rank's [n_tokens, d] float32.  peer_inbox[r]: device address, valid on this
+ * GPU, of rank r's inbox for this call, world x n_tokens x d 8-byte words, zero at start.
  * state_dev: two zero-initialised words of this rank (call count, block ticket).  Consecutive
- * calls must alternate between two partial buffers.  Every wait is bounded; on expiry the next
+ * calls must alternate between two inboxes.  The polling is bounded; on expiry the next
  * qk_gpu_synchronize returns QK_ERR_TIMEOUT.  x_out = x + sum, y = norm(x_out) * weight. */
-qk_status qk_allreduce_rmsnorm(qk_ctx *ctx, const uint64_t *peer_bufs, const uint64_t *peer_flags,
+qk_status qk_allreduce_rmsnorm(qk_ctx *ctx, const float *partial, const uint64_t *peer_inbox,
                                uint32_t *state_dev, int32_t rank, int32_t world, const float *x,
                                const float *weight, size_t n_tokens, size_t d, float eps,
                                int32_t serving_dtype, float *x_out, float *y);

@@ -115,103 +115,128 @@ rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
 
 // ---- RMSNorm fused with the tensor-parallel all-reduce of its residual input
 // Row-parallel linears (o, down) leave one partial `delta` per rank.  Instead of an NCCL
-// all-reduce followed by the norm, every rank reads all the partials straight from its peers'
-// memory (NVLink peer loads) and adds them in rank order - the same order on every rank, so
-// all ranks get the same bits - while it forms h = x + sum and the norm.
-//   peers.buf[r]  : rank r's partial [n_tokens][d] float32 (this rank's own included)
-//   peers.flag[r] : rank r's flag words, one per rank; flag[r][q] = s says "rank q's partial
-//                   of all-reduce number s is complete"
-//   counter       : this rank's count of all-reduces done (device memory, so that a replayed
-//                   CUDA graph keeps counting)
-// Protocol of all-reduce number s (= *counter + 1): block 0 fences and writes s into its slot
-// of every peer's flags; every block waits until all of its own flags are >= s (a fast peer
-// may already be one ahead); the sum is read with loads that bypass L1; the last block to
-// finish stores s into the counter.  Two partial buffers are used alternately by the caller
-// (attention block, MLP block): a peer can only overwrite the buffer being read here after
-// this rank has signalled the next all-reduce, i.e. after it is done reading.
-// The wait is bounded: on expiry the error word is set and the block returns.
-struct PeerArgs {
-    const float *buf[8];
-    uint32_t *flag[8];
+// all-reduce followed by the norm, every rank PUSHES its partial into an inbox in each peer's
+// memory (NVLink peer stores) and then adds what has arrived in its own inbox, in rank order -
+// the same order on every rank, so all ranks get the same bits - while it forms h = x + sum
+// and the norm.  Every 8-byte inbox word carries {value, number of this all-reduce}: a word
+// is valid exactly when its tag is the current number, so there are no separate flags and no
+// fences (an aligned 8-byte store is seen whole).  This is what makes a small all-reduce
+// cheap: one posted store per element and peer, then local polling.
+//   inbox.at[r] : rank r's inbox for this buffer, [source rank][n_tokens * d] words
+//   counter     : this rank's count of all-reduces done (device memory, so that a replayed
+//                 CUDA graph keeps counting); the last block to finish advances it.
+// The caller alternates between two inboxes (attention block, MLP block): a peer can only
+// write all-reduce s + 2 into the inbox being read here after this rank has sent its part of
+// s + 1, i.e. after it is done reading s.  The polling is bounded: on expiry the error word is
+// set and the block returns.
+struct InboxArgs {
+    uint2 *at[8];
 };
 
 __global__ void __launch_bounds__(kRmsThreads)
-allreduce_rmsnorm_kernel(PeerArgs peers, uint32_t *__restrict__ counter, uint32_t *__restrict__ done,
-                         int rank, int world, const float *__restrict__ x,
-                         const float *__restrict__ w, float *__restrict__ x_out,
-                         float *__restrict__ y, uint32_t d, float eps, int bf16,
-                         int *__restrict__ error) {
+allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
+                         uint32_t *__restrict__ counter, uint32_t *__restrict__ done, int rank,
+                         int world, const float *__restrict__ x, const float *__restrict__ w,
+                         float *__restrict__ x_out, float *__restrict__ y, uint32_t d, float eps,
+                         int bf16, int *__restrict__ error) {
     __shared__ float red[kRmsThreads / 32];
     __shared__ int gave_up;
     const uint32_t step = *counter + 1;
     if (threadIdx.x == 0) gave_up = 0;
-    // (the partial was written by an earlier kernel on this stream, so it is already visible
-    // device-wide; the release store orders it before the flag for the peers)
-    if (blockIdx.x == 0 && threadIdx.x < (uint32_t)world)
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flag[threadIdx.x] + rank), "r"(step)
-                     : "memory");
     __syncthreads();
-    if (threadIdx.x < (uint32_t)world) {
-        uint32_t seen = 0;
-        const uint32_t *mine = peers.flag[rank] + threadIdx.x;
-        for (uint32_t i = 0; i < (1u << 22); ++i) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-            if ((int32_t)(seen - step) >= 0) break;
-            __nanosleep(20);
+    const size_t base = (size_t)blockIdx.x * d, total = (size_t)gridDim.x * d;
+    constexpr int kSlots = 8;  // elements per thread handled with peers (d <= 8 * 512 per pass)
+    float keep[kRmsPerThread];
+    float ss = 0.f;
+    for (uint32_t pass = 0; pass * kSlots * kRmsThreads < d; ++pass) {
+        float own[kSlots];
+        // ---- send: my partial, tagged, into every peer's inbox
+#pragma unroll
+        for (int sl = 0; sl < kSlots; ++sl) {
+            const uint32_t i = threadIdx.x + (pass * kSlots + sl) * kRmsThreads;
+            own[sl] = i < d ? partial[base + i] : 0.f;
+            if (i < d) {
+                const uint2 word = make_uint2(__float_as_uint(own[sl]), step);
+#pragma unroll
+                for (int p = 0; p < 8; ++p)
+                    if (p < world && p != rank)
+                        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(
+                                         inbox.at[p] + (size_t)rank * total + base + i),
+                                     "r"(word.x), "r"(word.y)
+                                     : "memory");
+            }
         }
-        if ((int32_t)(seen - step) < 0) gave_up = 1;
+        // ---- receive: poll my inbox until every word of this pass carries the tag
+        float got[kSlots][8];
+        bool ready = false;
+        for (uint32_t tries = 0; tries < (1u << 22) && !ready; ++tries) {
+            ready = true;
+#pragma unroll
+            for (int sl = 0; sl < kSlots; ++sl) {
+                const uint32_t i = threadIdx.x + (pass * kSlots + sl) * kRmsThreads;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    if (r < world && r != rank && i < d) {
+                        uint32_t v, tag;
+                        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];"
+                                     : "=r"(v), "=r"(tag)
+                                     : "l"(inbox.at[rank] + (size_t)r * total + base + i)
+                                     : "memory");
+                        got[sl][r] = __uint_as_float(v);
+                        if (tag != step) ready = false;
+                    } else {
+                        got[sl][r] = 0.f;
+                    }
+                }
+            }
+        }
+        if (!ready) gave_up = 1;
+        // ---- sum in rank order, residual add
+#pragma unroll
+        for (int sl = 0; sl < kSlots; ++sl) {
+            const uint32_t i = threadIdx.x + (pass * kSlots + sl) * kRmsThreads;
+            if (i < d) {
+                float sum = 0.f;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) sum += r == rank ? own[sl] : got[sl][r];
+                float h = x[base + i] + sum;
+                x_out[base + i] = h;
+                if (bf16) h = round_bf16f(h);
+                if (pass * kSlots + sl < (uint32_t)kRmsPerThread) keep[pass * kSlots + sl] = h;
+                ss += h * h;
+            }
+        }
     }
     __syncthreads();
     if (gave_up) {
         if (threadIdx.x == 0) atomicExch(error, 1);
         return;
     }
-    const size_t base = (size_t)blockIdx.x * d;
-    float keep[kRmsPerThread];
-    float ss = 0.f;
-    auto gather = [&](uint32_t i) -> float {
-        float h = x[base + i];
-        float sum = 0.f;
-        // L1 was invalidated when the kernel started and every element is read once, after the
-        // acquire of the flags: an L2-level load is enough
-        for (int r = 0; r < world; ++r) sum += __ldcg(peers.buf[r] + base + i);  // rank order
-        h += sum;
-        x_out[base + i] = h;
-        return bf16 ? round_bf16f(h) : h;
-    };
-#pragma unroll
-    for (int r = 0; r < kRmsPerThread; ++r) {
-        const uint32_t i = threadIdx.x + r * kRmsThreads;
-        const float h = i < d ? gather(i) : 0.f;
-        keep[r] = h;
-        ss += h * h;
-    }
-    for (uint32_t i = threadIdx.x + kRmsPerThread * kRmsThreads; i < d; i += kRmsThreads) {
-        const float h = gather(i);
-        ss += h * h;
-    }
     const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
-#pragma unroll
-    for (int r = 0; r < kRmsPerThread; ++r) {
+    for (uint32_t r = 0; threadIdx.x + r * kRmsThreads < d; ++r) {
         const uint32_t i = threadIdx.x + r * kRmsThreads;
-        if (i < d) {
-            const float o = keep[r] * inv * w[i];
-            y[base + i] = bf16 ? round_bf16f(o) : o;
+        float h;
+        if (r < (uint32_t)kRmsPerThread) {
+            h = keep[r];
+        } else {
+            h = x_out[base + i];
+            if (bf16) h = round_bf16f(h);
         }
-    }
-    for (uint32_t i = threadIdx.x + kRmsPerThread * kRmsThreads; i < d; i += kRmsThreads) {
-        float h = x_out[base + i];
-        if (bf16) h = round_bf16f(h);
         const float o = h * inv * w[i];
         y[base + i] = bf16 ? round_bf16f(o) : o;
     }
-    // the last block to finish records that this all-reduce is done
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        if (atomicAdd(done, 1u) == gridDim.x - 1) {
-            *done = 0;
-            *counter = step;
+    // the last block to finish records that this all-reduce is done (every block has read the
+    // counter by then); a single block needs no ticket
+    if (gridDim.x == 1) {
+        if (threadIdx.x == 0) *counter = step;
+    } else {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            if (atomicAdd(done, 1u) == gridDim.x - 1) {
+                *done = 0;
+                *counter = step;
+            }
         }
     }
 }
@@ -1158,7 +1183,7 @@ qk_status qk_argmax_first(qk_ctx *ctx, const float *logits, size_t n_tokens, siz
     QK_LAUNCHED(c);
 }
 
-qk_status qk_allreduce_rmsnorm(qk_ctx *ctx, const uint64_t *peer_bufs, const uint64_t *peer_flags,
+qk_status qk_allreduce_rmsnorm(qk_ctx *ctx, const float *partial, const uint64_t *peer_inbox,
                                uint32_t *state_dev, int32_t rank, int32_t world, const float *x,
                                const float *weight, size_t n_tokens, size_t d, float eps,
                                int32_t serving_dtype, float *x_out, float *y) {
@@ -1167,20 +1192,17 @@ qk_status qk_allreduce_rmsnorm(qk_ctx *ctx, const uint64_t *peer_bufs, const uin
     if (st != QK_OK) return st;
     if (world < 1 || world > 8 || rank < 0 || rank >= world)
         return qk::fail(QK_ERR_VALUE, "qk_allreduce_rmsnorm: rank %d of %d (1..8 ranks)", rank, world);
-    if (!peer_bufs || !peer_flags || !state_dev || !x_out)
+    if (!partial || !peer_inbox || !state_dev || !x_out)
         return qk::fail(QK_ERR_VALUE, "qk_allreduce_rmsnorm: null argument");
     if (n_tokens == 0) return QK_OK;
     if (!c->d_err.ptr) {
         if ((st = c->d_err.reserve(256 + 4096)) != QK_OK) return st;
         QK_CUDA(cudaMemsetAsync(c->d_err.ptr, 0, 256 + 4096, c->stream));
     }
-    PeerArgs peers{};
-    for (int r = 0; r < world; ++r) {
-        peers.buf[r] = reinterpret_cast<const float *>(peer_bufs[r]);
-        peers.flag[r] = reinterpret_cast<uint32_t *>(peer_flags[r]);
-    }
+    InboxArgs inbox{};
+    for (int r = 0; r < world; ++r) inbox.at[r] = reinterpret_cast<uint2 *>(peer_inbox[r]);
     allreduce_rmsnorm_kernel<<<(unsigned)n_tokens, kRmsThreads, 0, c->stream>>>(
-        peers, state_dev, state_dev + 1, rank, world, x, weight, x_out, y, (uint32_t)d, eps,
+        inbox, partial, state_dev, state_dev + 1, rank, world, x, weight, x_out, y, (uint32_t)d, eps,
         serving_dtype == QK_BF16, (int *)c->d_err.ptr);
     c->err_armed = true;
     QK_LAUNCHED(c);

@@ -43,9 +43,7 @@ class DecoderConfig:
     max_batch: int = 1
     n_splits: int = 0              # key splits of the decode attention (0 = choose)
     gemm_min_batch: int = 16       # bfloat16 serving: batches this large take the tensor-core GEMM
-    fused_allreduce: bool = False  # tensor parallel: sum the partials over peer memory inside the norm
-                                   # (on two B200 it measured slower than NCCL followed by the norm:
-                                   # 5.13 against 4.55 ms per batch-1 step of the 32-layer model)
+    fused_allreduce: bool = True   # tensor parallel: the all-reduce happens inside the norm, over peer memory
 
 
 def rope_table(cfg: DecoderConfig) -> np.ndarray:
@@ -223,31 +221,29 @@ class Decoder:
 
     # ------------------------------------------------------------------ tensor parallel
     def _setup_fused_allreduce(self, B: int, d: int) -> None:
-        """Partial-output buffers and flag words in symmetric memory (every rank maps every
-        peer's copy), for ``qk_allreduce_rmsnorm``.  If the peers cannot be mapped the decoder
-        keeps the NCCL all-reduce and says so in ``fused_ar``."""
+        """Two inboxes in symmetric memory (every rank maps every peer's copy) for
+        ``qk_allreduce_rmsnorm``.  If the peers cannot be mapped the decoder keeps the NCCL
+        all-reduce and says so in ``fused_ar``."""
         torch = self.torch
         try:
             import torch.distributed._symmetric_memory as symm
             dev = torch.device("cuda", torch.cuda.current_device())
-            self._sym_delta = symm.empty((2, B, d), dtype=torch.float32, device=dev)
-            self._sym_flags = symm.empty((64,), dtype=torch.int32, device=dev)
-            self._sym_delta.zero_()
-            self._sym_flags.zero_()
-            hd = symm.rendezvous(self._sym_delta, self.group)
-            hf = symm.rendezvous(self._sym_flags, self.group)
-            bufs, flags = list(hd.buffer_ptrs), list(hf.buffer_ptrs)
+            # [inbox][source rank][token][channel][value, tag]
+            self._sym_inbox = symm.empty((2, self.tp_size, B, d, 2), dtype=torch.int32, device=dev)
+            self._sym_inbox.zero_()
+            handle = symm.rendezvous(self._sym_inbox, self.group)
+            bases = list(handle.buffer_ptrs)
         except Exception as exc:  # no peer access on this box: NCCL stays
             self.fused_ar_error = repr(exc)
             return
         torch.cuda.synchronize()
-        torch.distributed.barrier(group=self.group)   # every rank's flags are zero before any signal
-        step_bytes = B * d * 4
-        self._peer_bufs = [np.array([b + which * step_bytes for b in bufs], dtype=np.uint64)
-                           for which in (0, 1)]
-        self._peer_flags = np.array(flags, dtype=np.uint64)
+        torch.distributed.barrier(group=self.group)   # every inbox is zero before anyone sends
+        inbox_bytes = self.tp_size * B * d * 8
+        self._peer_inbox = [np.array([b + which * inbox_bytes for b in bases], dtype=np.uint64)
+                            for which in (0, 1)]
         self._ar_state = torch.zeros(2, dtype=torch.int32, device=dev)
-        self.delta_attn, self.delta_mlp = self._sym_delta[0], self._sym_delta[1]
+        self.delta_attn = torch.zeros(B, d, dtype=torch.float32, device=dev)
+        self.delta_mlp = torch.zeros(B, d, dtype=torch.float32, device=dev)
         self.fused_ar = True
 
     def _all_reduce(self, t):
@@ -260,10 +256,11 @@ class Decoder:
         lib, c, cfg = _lib.lib(), self.ctx.handle, self.cfg
         B, d = cfg.max_batch, cfg.d_model
         if pending is not None and self.fused_ar:
+            partial = self.delta_attn if pending == 0 else self.delta_mlp
             check(lib.qk_allreduce_rmsnorm(
-                c, self._peer_bufs[pending].ctypes.data, self._peer_flags.ctypes.data,
-                _p(self._ar_state), self.tp_rank, self.tp_size, _p(self.x), _p(weight), B, d,
-                cfg.rms_eps, self.serving_tag, _p(self.x), _p(self.h)))
+                c, _p(partial), self._peer_inbox[pending].ctypes.data, _p(self._ar_state),
+                self.tp_rank, self.tp_size, _p(self.x), _p(weight), B, d, cfg.rms_eps,
+                self.serving_tag, _p(self.x), _p(self.h)))
             return
         residual = None if pending is None else _p(self.delta_attn if pending == 0 else self.delta_mlp)
         check(lib.qk_rmsnorm(c, _p(self.x), residual, _p(weight), B, d, cfg.rms_eps,
