@@ -44,6 +44,7 @@ class DecoderConfig:
     n_splits: int = 0              # key splits of the decode attention (0 = choose)
     gemm_min_batch: int = 16       # bfloat16 serving: batches this large take the tensor-core GEMM
     fused_allreduce: bool = True   # tensor parallel: the all-reduce happens inside the norm, over peer memory
+    fused_allreduce_max_bytes: int = 1 << 20   # ... while a rank pushes at most this much per all-reduce
 
 
 def rope_table(cfg: DecoderConfig) -> np.ndarray:
@@ -152,7 +153,11 @@ class Decoder:
         self.delta = torch.zeros(B, d, **f32)
         self.delta_attn = self.delta_mlp = self.delta
         self.fused_ar = False
-        if tp_size > 1 and cfg.fused_allreduce:
+        # The fused form is a one-shot push: every rank stores its whole partial to every peer.
+        # That wins while the pushed bytes are few (measured: batch 1 at 2 and 8 ranks, batch 64
+        # at 2 ranks) and loses to NCCL's bandwidth-optimal schedule when they are many (batch
+        # 64 at 8 ranks: 7 MB per rank and all-reduce, 9.1 against 8.7 ms per step).
+        if tp_size > 1 and cfg.fused_allreduce and B * d * 4 * (tp_size - 1) <= cfg.fused_allreduce_max_bytes:
             self._setup_fused_allreduce(B, d)
         self.g = torch.zeros(B, self.ff_loc, **f32)
         self.u = torch.zeros(B, self.ff_loc, **f32)
