@@ -166,40 +166,46 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
                                      : "memory");
             }
         }
-        // ---- receive: poll my inbox until every word of this pass carries the tag
-        float got[kSlots][8];
-        bool ready = false;
-        for (uint32_t tries = 0; tries < (1u << 22) && !ready; ++tries) {
-            ready = true;
+        // ---- receive and add in rank order: for each peer, poll my inbox until the thread's
+        // words of this pass all carry the tag (by the time the first peer's have arrived the
+        // others' usually have too)
+        float sum[kSlots];
 #pragma unroll
-            for (int sl = 0; sl < kSlots; ++sl) {
-                const uint32_t i = threadIdx.x + (pass * kSlots + sl) * kRmsThreads;
+        for (int sl = 0; sl < kSlots; ++sl) sum[sl] = 0.f;
+        for (int r = 0; r < world; ++r) {
+            if (r == rank) {
 #pragma unroll
-                for (int r = 0; r < 8; ++r) {
-                    if (r < world && r != rank && i < d) {
-                        uint32_t v, tag;
+                for (int sl = 0; sl < kSlots; ++sl) sum[sl] += own[sl];
+                continue;
+            }
+            const uint2 *src = inbox.at[rank] + (size_t)r * total + base;
+            float got[kSlots];
+            bool ready = false;
+            for (uint32_t tries = 0; tries < (1u << 22) && !ready; ++tries) {
+                ready = true;
+#pragma unroll
+                for (int sl = 0; sl < kSlots; ++sl) {
+                    const uint32_t i = threadIdx.x + (pass * kSlots + sl) * kRmsThreads;
+                    uint32_t v = 0, tag = step;
+                    if (i < d)
                         asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];"
                                      : "=r"(v), "=r"(tag)
-                                     : "l"(inbox.at[rank] + (size_t)r * total + base + i)
+                                     : "l"(src + i)
                                      : "memory");
-                        got[sl][r] = __uint_as_float(v);
-                        if (tag != step) ready = false;
-                    } else {
-                        got[sl][r] = 0.f;
-                    }
+                    got[sl] = __uint_as_float(v);
+                    if (tag != step) ready = false;
                 }
             }
+            if (!ready) gave_up = 1;
+#pragma unroll
+            for (int sl = 0; sl < kSlots; ++sl) sum[sl] += got[sl];
         }
-        if (!ready) gave_up = 1;
-        // ---- sum in rank order, residual add
+        // ---- residual add
 #pragma unroll
         for (int sl = 0; sl < kSlots; ++sl) {
             const uint32_t i = threadIdx.x + (pass * kSlots + sl) * kRmsThreads;
             if (i < d) {
-                float sum = 0.f;
-#pragma unroll
-                for (int r = 0; r < 8; ++r) sum += r == rank ? own[sl] : got[sl][r];
-                float h = x[base + i] + sum;
+                float h = x[base + i] + sum[sl];
                 x_out[base + i] = h;
                 if (bf16) h = round_bf16f(h);
                 if (pass * kSlots + sl < (uint32_t)kRmsPerThread) keep[pass * kSlots + sl] = h;
