@@ -473,6 +473,8 @@ __device__ __forceinline__ void split3(float x, uint32_t &hi, uint32_t &mid, uin
 }
 
 constexpr int kMmaDecWarps = 4;
+constexpr int kMmaDecKPitch = 320, kMmaDecVPitch = 272;  // bytes per staged key row (256 + pad)
+constexpr int kMmaDecBufBytes = 16 * (kMmaDecKPitch + kMmaDecVPitch);
 
 __global__ void __launch_bounds__(kMmaDecWarps * 32)
 decode_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict__ cache_k,
@@ -519,17 +521,48 @@ decode_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__restr
 
     const uint16_t *kb = cache_k + ((size_t)b * n_kv + kvh) * s_max * d;
     const uint16_t *vb = cache_v + ((size_t)b * n_kv + kvh) * s_max * d;
-    const uint4 zero4 = make_uint4(0, 0, 0, 0);
-    for (int j = j_begin + 16 * (int)warp; j < j_end; j += 16 * kMmaDecWarps) {
+    // Each warp streams its 16-key steps through two private shared-memory buffers with
+    // cp.async, so the next step's 8 KB of K and V are in flight while this one is multiplied.
+    // Row pitches 320 B (K) and 272 B (V) keep the 16-byte fragment reads conflict-free.
+    extern __shared__ __align__(16) uint8_t dec_smem[];
+    uint8_t *my_smem = dec_smem + warp * (2 * kMmaDecBufBytes);
+    auto fetch = [&](int j, int buf) {
+        uint8_t *kt = my_smem + buf * kMmaDecBufBytes, *vt = kt + 16 * kMmaDecKPitch;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int idx = (int)lane + 32 * q, key = idx / 16, piece = idx % 16;
+            const int src_key = min(j + key, j_end - 1);      // a valid address even when unused
+            const uint32_t bytes = j + key < j_end ? 16u : 0u;  // 0: the 16 bytes are zero-filled
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                             (uint32_t)__cvta_generic_to_shared(kt + key * kMmaDecKPitch + piece * 16)),
+                         "l"(kb + (size_t)src_key * d + piece * 8), "r"(bytes)
+                         : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                             (uint32_t)__cvta_generic_to_shared(vt + key * kMmaDecVPitch + piece * 16)),
+                         "l"(vb + (size_t)src_key * d + piece * 8), "r"(bytes)
+                         : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    int buf = 0;
+    if (j_begin + 16 * (int)warp < j_end) fetch(j_begin + 16 * (int)warp, 0);
+    for (int j = j_begin + 16 * (int)warp; j < j_end; j += 16 * kMmaDecWarps, buf ^= 1) {
+        if (j + 16 * kMmaDecWarps < j_end) {
+            fetch(j + 16 * kMmaDecWarps, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncwarp();  // every lane's pieces of this step have landed
+        const uint8_t *kt = my_smem + buf * kMmaDecBufBytes, *vt = kt + 16 * kMmaDecKPitch;
         // ---- S for 16 keys: two 8-key tiles
         float s[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-            const int key = j + 8 * nt + (int)g;
             uint4 kw[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-                kw[i] = key < j_end ? *reinterpret_cast<const uint4 *>(kb + (size_t)key * d + 32 * i + 8 * t) : zero4;
+                kw[i] = *reinterpret_cast<const uint4 *>(kt + (8 * nt + g) * kMmaDecKPitch + 64 * i + 16 * t);
             s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
             for (int i = 0; i < 4; ++i)
@@ -583,8 +616,8 @@ decode_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__restr
             uint4 vw[4];
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
-                const int key = j + 8 * (r >> 1) + 2 * (int)t + (r & 1);
-                vw[r] = key < j_end ? *reinterpret_cast<const uint4 *>(vb + (size_t)key * d + 64 * h + 8 * g) : zero4;
+                const int key = 8 * (r >> 1) + 2 * (int)t + (r & 1);  // within the step; rows past the end are zero
+                vw[r] = *reinterpret_cast<const uint4 *>(vt + key * kMmaDecVPitch + 128 * h + 16 * g);
             }
 #pragma unroll
             for (int jj = 0; jj < 8; ++jj) {
@@ -601,6 +634,7 @@ decode_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__restr
                 o[8 * h + jj][1] = acc[1];
             }
         }
+        __syncwarp();  // the buffer may be refilled by the next iteration's fetch
     }
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
@@ -1034,7 +1068,10 @@ qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
         const size_t gq8 = group < 8 ? group : 8, subs = qk::ceil_div(group, gq8);
         const size_t chunk8 = qk::ceil_div(s_max, n_splits);
         dim3 grid8((unsigned)n_splits, (unsigned)(n_kv_heads * subs), (unsigned)batch);
-        decode_attention_mma_kernel<<<grid8, kMmaDecWarps * 32, 0, c->stream>>>(
+        const size_t smem8 = (size_t)kMmaDecWarps * 2 * kMmaDecBufBytes;
+        QK_CUDA(cudaFuncSetAttribute(decode_attention_mma_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem8));
+        decode_attention_mma_kernel<<<grid8, kMmaDecWarps * 32, smem8, c->stream>>>(
             q, (const uint16_t *)cache_k, (const uint16_t *)cache_v, kv_len, scratch,
             (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)gq8, (uint32_t)s_max,
             (uint32_t)chunk8, (uint32_t)n_splits);
