@@ -163,8 +163,7 @@ qk_status qk_gpu_attention_sage_dev(qk_ctx *ctx, const qk_attention_shape *shape
  * kernel.  Returns the previous choice. */
 int32_t qk_set_sage_kernel(qk_ctx *ctx, int32_t which);
 /* Which kernel qk_decode_attention runs for a bfloat16 cache with head_dim 128: 1 (default)
- * the bf16 tensor-core kernel when a kv head serves three or more query heads, 2 always the
- * tensor-core kernel, 0 always the scalar kernel.  Returns the previous choice. */
+ * the bf16 tensor-core kernel, 0 the scalar kernel.  Returns the previous choice. */
 int32_t qk_set_decode_attention_kernel(qk_ctx *ctx, int32_t which);
 
 /* ---- the factorized linear with device-resident factors ----------------------

@@ -1060,11 +1060,11 @@ qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
     if (kv_dtype != QK_F32 && kv_dtype != QK_BF16)
         return qk::fail(QK_ERR_VALUE, "KV cache dtype must be float32 or bfloat16, got tag %d",
                         kv_dtype);
-    if (kv_dtype == QK_BF16 && head_dim == 128 &&
-        (c->decode_attention_kernel == 2 || (c->decode_attention_kernel == 1 && group >= 3))) {
-        // bfloat16 cache, head_dim 128, grouped queries: both products on the tensor cores.
-        // (With one or two query heads per kv head most of the 16-row MMA is padding and the
-        // scalar kernel is faster: measured 0.57 against 0.64 ms per step on the Llama-2-7B block.)
+    if (kv_dtype == QK_BF16 && head_dim == 128 && c->decode_attention_kernel != 0) {
+        // bfloat16 cache, head_dim 128: both products on the tensor cores.  (Even with one
+        // query head per kv head, where 15 of the MMA's 16 rows are padding, it measured a
+        // little faster than the scalar kernel: 0.471 against 0.480 ms per step on the
+        // Llama-2-7B block.)
         const size_t gq8 = group < 8 ? group : 8, subs = qk::ceil_div(group, gq8);
         const size_t chunk8 = qk::ceil_div(s_max, n_splits);
         dim3 grid8((unsigned)n_splits, (unsigned)(n_kv_heads * subs), (unsigned)batch);
@@ -1256,7 +1256,7 @@ int32_t qk_set_decode_attention_kernel(qk_ctx *ctx, int32_t which) {
     if (qk::resolve_ctx(ctx, &c) != QK_OK) return -1;
     std::lock_guard<std::mutex> lock(c->mu);
     const int32_t before = c->decode_attention_kernel;
-    if (which >= 0 && which <= 2) c->decode_attention_kernel = which;
+    if (which == 0 || which == 1) c->decode_attention_kernel = which;
     return before;
 }
 

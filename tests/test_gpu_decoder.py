@@ -233,7 +233,7 @@ def test_decode_attention_tensor_core_kernel(gpu_ctx, heads, kv_heads):
     scratch = torch.zeros(lib.qk_decode_attention_scratch(B, heads, d, n_splits) // 4 + 4, device="cuda")
     p = lambda t: ctypes.c_void_p(t.data_ptr())
     outs = []
-    for which in (2, 0):
+    for which in (1, 0):
         out = torch.zeros(B, heads, d, device="cuda")
         torch.cuda.synchronize()
         before = lib.qk_set_decode_attention_kernel(gpu_ctx.handle, which)
