@@ -76,6 +76,19 @@ qk_status qk_unpack_bits(const uint8_t *packed, size_t packed_len, size_t n_rows
                          int8_t *out, size_t out_len);
 /* core.rs:193-197 (sign_estimate). */
 qk_status qk_sign_estimate(const double *x, size_t n, int8_t *out);
+/* core.rs:327-424 (joint_itq) with its helpers :47-126; NumPy face
+ * src/quantibbler/kernels/__init__.py:345-512.  Alternating Procrustes over
+ * Z = [u_hat; v_hat] (row-major dout x rank and din x rank float64): R0 from splitmix64(seed)
+ * + modified Gram-Schmidt, then B <- sign(Z R), R <- Psi Phi^T from the SVD of B^T Z, until
+ * ||R_new - R_old||_F <= tol (only when tol > 0) or max_iter.  Writes the +-1 factors
+ * sign(Z R) to u_t (dout x rank) and v_t (din x rank), the iteration count and the
+ * convergence flag.  Host code, as in the reference; errors: "joint_itq expects non-empty
+ * factors", "joint_itq shape mismatch: ...", "joint_itq produced a degenerate zero column
+ * building R0". */
+qk_status qk_joint_itq(const double *u_hat, size_t u_len, const double *v_hat, size_t v_len,
+                       size_t dout, size_t din, size_t rank, size_t max_iter, double tol,
+                       uint64_t seed, int8_t *u_t, int8_t *v_t, size_t *n_iter,
+                       int32_t *converged);
 /* core.rs:223-240 (validate_packed). */
 qk_status qk_validate_packed(size_t packed_len, size_t n_rows, size_t n_bits, size_t *n_words);
 /* dtype.rs:106-119 (Dtype::from_name) and :121-128 (Dtype::name). */

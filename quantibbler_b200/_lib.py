@@ -38,6 +38,9 @@ _SIGNATURES = {
     "qk_pack_bits_f64": (c_int32, [c_void_p, c_size_t, c_size_t, c_size_t, c_void_p, c_size_t]),
     "qk_unpack_bits": (c_int32, [c_void_p, c_size_t, c_size_t, c_size_t, c_void_p, c_size_t]),
     "qk_sign_estimate": (c_int32, [c_void_p, c_size_t, c_void_p]),
+    "qk_joint_itq": (c_int32, [c_void_p, c_size_t, c_void_p, c_size_t, c_size_t, c_size_t, c_size_t,
+                               c_size_t, c_double, c_uint64, c_void_p, c_void_p,
+                               POINTER(c_size_t), POINTER(c_int32)]),
     "qk_validate_packed": (c_int32, [c_size_t, c_size_t, c_size_t, POINTER(c_size_t)]),
     "qk_dtype_from_name": (c_int32, [c_char_p, POINTER(c_int32)]),
     "qk_dtype_name": (c_char_p, [c_int32]),

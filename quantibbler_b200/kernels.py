@@ -17,8 +17,11 @@ from ._lib import DTYPE_TAGS, KernelError, check
 
 __all__ = [
     "backend_version", "pack_bits", "unpack_bits", "sign_estimate", "packed_matvec",
-    "packed_matmul", "packed_matvec_dtype", "packed_matmul_dtype",
+    "packed_matmul", "packed_matvec_dtype", "packed_matmul_dtype", "joint_itq",
 ]
+
+DEFAULT_MAX_ITER = 50     # core.rs DEFAULT_MAX_ITER
+DEFAULT_TOL = 1e-12       # core.rs DEFAULT_TOL
 
 
 def _ptr(a: np.ndarray):
@@ -127,3 +130,39 @@ def packed_matvec(packed, n_bits: int, vec) -> np.ndarray:
 
 def packed_matmul(packed, n_bits: int, mat) -> np.ndarray:
     return packed_matmul_dtype(packed, n_bits, mat, "float64")
+
+
+def _unsigned(value, what: str, bits: int) -> int:
+    v = int(value)
+    if v < 0:
+        raise OverflowError("can't convert negative int to unsigned")
+    if v >= 1 << bits:
+        raise OverflowError(f"{what} does not fit in {bits} bits")
+    return v
+
+
+def joint_itq(u_hat, v_hat, *, max_iter=None, tol=None, seed=None):
+    """Alternating Procrustes over ``Z = [u_hat; v_hat]`` (lib.rs:197-234, core.rs:327-424).
+
+    Returns ``(u_t, v_t, n_iter, converged)`` with int8 ±1 factors of the operands' row
+    counts.  As in the PyO3 face the defaults are 50 iterations, tolerance 1e-12 and seed 0.
+    Host work in the shared library (this is compressor-side code in the reference too).
+    """
+    import ctypes
+    u = _typed(u_hat, np.float64, "u_hat")
+    v = _typed(v_hat, np.float64, "v_hat")
+    dout, rank = _rows_cols(u.shape)
+    din, rank_v = _rows_cols(v.shape)
+    if rank != rank_v:
+        raise KernelError(f"joint_itq rank mismatch: u_hat r={rank}, v_hat r={rank_v}")
+    iters = DEFAULT_MAX_ITER if max_iter is None else _unsigned(max_iter, "max_iter", 64)
+    tolerance = DEFAULT_TOL if tol is None else float(tol)
+    seed64 = 0 if seed is None else _unsigned(seed, "seed", 64)
+    u_t = np.zeros((dout, rank), dtype=np.int8)
+    v_t = np.zeros((din, rank), dtype=np.int8)
+    n_iter = ctypes.c_size_t(0)
+    converged = ctypes.c_int32(0)
+    check(_lib.lib().qk_joint_itq(_ptr(u), u.size, _ptr(v), v.size, dout, din, rank, iters,
+                                  tolerance, seed64, _ptr(u_t), _ptr(v_t),
+                                  ctypes.byref(n_iter), ctypes.byref(converged)))
+    return u_t, v_t, int(n_iter.value), bool(converged.value)

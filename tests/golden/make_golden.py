@@ -4,6 +4,7 @@
 Run in a container that has the reference mounted:
 
     python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference joint_itq    # that family alone
 
 It does two things, and commits nothing by itself:
 
@@ -32,7 +33,49 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def main(ref_root: str) -> None:
+def joint_itq_cases(rk, load):
+    """The reference's four joint_itq fixtures plus seeded larger factors run through its
+    NumPy implementation (kernels/__init__.py:420-512)."""
+    NR = "numpy-reference"
+    itq: dict[str, np.ndarray] = {}
+    imeta: dict[str, dict] = {}
+    n = 0
+    for rec in load("joint_itq"):
+        key = f"itq{n}"
+        itq[key + "_u_hat"] = np.asarray(rec["inputs"]["u_hat"], dtype=np.float64)
+        itq[key + "_v_hat"] = np.asarray(rec["inputs"]["v_hat"], dtype=np.float64)
+        itq[key + "_u_t"] = np.asarray(rec["faces"][NR]["u_t"], dtype=np.int8)
+        itq[key + "_v_t"] = np.asarray(rec["faces"][NR]["v_t"], dtype=np.int8)
+        imeta[key] = {"scenario": rec["scenario"], "kwargs": rec["inputs"]["kwargs"],
+                      "n_iter": rec["faces"][NR]["n_iter"],
+                      "converged": rec["faces"][NR]["converged"]}
+        n += 1
+    # seeded: (dout, din, rank, kwargs); low-rank-plus-noise factors as a compressor sees them
+    seeded = [
+        (24, 17, 5, {"max_iter": 50, "tol": 1e-12, "seed": 7}),
+        (40, 33, 8, {"max_iter": 3, "tol": 1e-12, "seed": 123456789}),
+        (64, 48, 12, {"max_iter": 50, "tol": 1e-12, "seed": 0}),
+        (96, 80, 16, {"max_iter": 20, "tol": 0.0, "seed": 2**63 + 11}),
+        (1, 9, 2, {"max_iter": 50, "tol": 1e-12, "seed": 5}),
+        (6, 0, 3, {"max_iter": 50, "tol": 1e-12, "seed": 5}),
+        (30, 30, 6, {"max_iter": 0, "tol": 1e-12, "seed": 99}),
+    ]
+    for i, (dout, din, rank, kwargs) in enumerate(seeded):
+        rng = np.random.default_rng(7300 + i)
+        u_hat = rng.standard_normal((dout, rank))
+        v_hat = rng.standard_normal((din, rank))
+        u_t, v_t, n_iter, conv = rk.joint_itq(u_hat, v_hat, backend=NR, **kwargs)
+        # a golden sign is only useful if it does not hang on the last bit of Z R
+        key = f"itq{n}"
+        itq[key + "_u_hat"], itq[key + "_v_hat"] = u_hat, v_hat
+        itq[key + "_u_t"], itq[key + "_v_t"] = u_t, v_t
+        imeta[key] = {"scenario": f"seeded_{dout}+{din}x{rank}", "kwargs": kwargs,
+                      "n_iter": int(n_iter), "converged": bool(conv)}
+        n += 1
+    return itq, imeta
+
+
+def main(ref_root: str, only: str | None = None) -> None:
     sys.path.insert(0, os.path.join(ref_root, "src"))
     import quantibbler.kernels as rk
     from quantibbler.kernels.attention_sage import attention_sage
@@ -43,6 +86,16 @@ def main(ref_root: str) -> None:
     def load(name):
         with open(os.path.join(fx, name + ".json")) as f:
             return json.load(f)
+
+    def dump(name, arrays, m):
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **arrays)
+        with open(os.path.join(HERE, name + ".json"), "w") as f:
+            json.dump(m, f, indent=1, sort_keys=True)
+        print(name, len(arrays), "arrays")
+
+    if only == "joint_itq":   # this family alone (the others take minutes of Python loops)
+        dump("joint_itq", *joint_itq_cases(rk, load))
+        return
 
     NR = "numpy-reference"
     out: dict[str, np.ndarray] = {}
@@ -154,18 +207,7 @@ def main(ref_root: str) -> None:
                           "kind": "matmul", "dtype": dt}
             n += 1
 
-    # ------------------------------------------------------------ joint_itq
-    itq: dict[str, np.ndarray] = {}
-    imeta: dict[str, dict] = {}
-    for i, rec in enumerate(load("joint_itq")):
-        key = f"itq{i}"
-        itq[key + "_u_hat"] = np.asarray(rec["inputs"]["u_hat"], dtype=np.float64)
-        itq[key + "_v_hat"] = np.asarray(rec["inputs"]["v_hat"], dtype=np.float64)
-        itq[key + "_u_t"] = np.asarray(rec["faces"][NR]["u_t"], dtype=np.int8)
-        itq[key + "_v_t"] = np.asarray(rec["faces"][NR]["v_t"], dtype=np.int8)
-        imeta[key] = {"scenario": rec["scenario"], "kwargs": rec["inputs"]["kwargs"],
-                      "n_iter": rec["faces"][NR]["n_iter"],
-                      "converged": rec["faces"][NR]["converged"]}
+    itq, imeta = joint_itq_cases(rk, load)
 
     # ------------------------------------------------------------ factorized linear
     # engine/mod.rs:393-460 expressed through the reference's NumPy products.
@@ -267,12 +309,6 @@ def main(ref_root: str) -> None:
         ameta[key] = {"scenario": f"seeded_{b}x{h}/{kvh}x{s}x{d}->{dv}", "causal": causal,
                       "block_size": blk, "seed": 9200 + i}
 
-    def dump(name, arrays, m):
-        np.savez_compressed(os.path.join(HERE, name + ".npz"), **arrays)
-        with open(os.path.join(HERE, name + ".json"), "w") as f:
-            json.dump(m, f, indent=1, sort_keys=True)
-        print(name, len(arrays), "arrays")
-
     dump("bitplanes", out, meta)
     dump("products", prod, pmeta)
     dump("joint_itq", itq, imeta)
@@ -281,6 +317,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        raise SystemExit("usage: make_golden.py <path of the reference checkout>")
-    main(sys.argv[1])
+    if len(sys.argv) not in (2, 3):
+        raise SystemExit("usage: make_golden.py <path of the reference checkout> [joint_itq]")
+    main(*sys.argv[1:])

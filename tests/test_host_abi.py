@@ -138,7 +138,73 @@ def test_init_failure_is_typed_and_carries_the_hint():
 def test_drop_in_module_exposes_the_reference_names():
     import quantibbler_kernels as qk
     for name in ["backend_version", "pack_bits", "unpack_bits", "sign_estimate", "packed_matvec",
-                 "packed_matmul", "packed_matvec_dtype", "packed_matmul_dtype"]:
+                 "packed_matmul", "packed_matvec_dtype", "packed_matmul_dtype", "joint_itq"]:
         assert callable(getattr(qk, name)), name
     assert isinstance(qk.backend_version(), str)
     assert issubclass(KernelError, ValueError)
+
+
+def test_joint_itq_golden_signs_iterations_and_flags():
+    # crates/quantibbler-kernels/tests/fixtures/joint_itq.json (parity.rs reads it) and seeded
+    # cases run through the reference's NumPy face: int8 signs are pinned exactly
+    g = golden("joint_itq")
+    for key in g.cases("itq"):
+        meta = g.meta[key]
+        u_t, v_t, n_iter, converged = kernels.joint_itq(g[key + "_u_hat"], g[key + "_v_hat"],
+                                                        **meta["kwargs"])
+        assert u_t.dtype == np.int8 and v_t.dtype == np.int8
+        assert np.array_equal(u_t, g[key + "_u_t"]), meta["scenario"]
+        assert np.array_equal(v_t, g[key + "_v_t"]), meta["scenario"]
+        assert (n_iter, converged) == (meta["n_iter"], meta["converged"]), meta["scenario"]
+
+
+def test_joint_itq_matches_oracle_at_compressor_sizes_and_preserves_product():
+    # tests/test_kernels_parity.py:273-292 of the reference: every entry is +-1 and the result
+    # is a rotation of the inputs' signs, deterministic in the seed
+    from oracle import itq_np
+    rng = np.random.default_rng(31)
+    u_hat = rng.standard_normal((600, 48)) @ rng.standard_normal((48, 48))
+    v_hat = rng.standard_normal((420, 48))
+    want = itq_np.joint_itq(u_hat, v_hat, max_iter=12, seed=42, return_margin=True)
+    got = kernels.joint_itq(u_hat, v_hat, max_iter=12, seed=42)
+    assert got[2:] == want[2:4]
+    differ = np.concatenate([got[0], got[1]]) != np.concatenate([want[0], want[1]])
+    # a sign may differ only where Z R vanishes to rounding (the two SVDs differ in the last bits)
+    assert np.all(np.abs(want[4][differ]) < 1e-9)
+    assert differ.sum() <= 2
+    assert set(np.unique(got[0])) <= {-1, 1} and set(np.unique(got[1])) <= {-1, 1}
+    again = kernels.joint_itq(u_hat, v_hat, max_iter=12, seed=42)
+    assert np.array_equal(again[0], got[0]) and np.array_equal(again[1], got[1])
+    other = kernels.joint_itq(u_hat, v_hat, max_iter=12, seed=7)
+    assert not np.array_equal(other[0], got[0])
+    # defaults of the PyO3 face: 50 iterations, tolerance 1e-12, seed 0
+    a = kernels.joint_itq(u_hat[:40, :6].copy(), v_hat[:30, :6].copy())
+    b = kernels.joint_itq(u_hat[:40, :6].copy(), v_hat[:30, :6].copy(), max_iter=50, tol=1e-12,
+                          seed=0)
+    assert a[2:] == b[2:] and np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+
+
+def test_joint_itq_refusals():
+    # core.rs:337-346, lib.rs:211-216
+    u = np.zeros((4, 3))
+    with pytest.raises(KernelError, match="joint_itq rank mismatch: u_hat r=3, v_hat r=2"):
+        kernels.joint_itq(u, np.zeros((4, 2)))
+    with pytest.raises(KernelError, match="joint_itq expects non-empty factors"):
+        kernels.joint_itq(np.zeros((4, 0)), np.zeros((2, 0)))
+    with pytest.raises(KernelError, match="joint_itq expects non-empty factors"):
+        kernels.joint_itq(np.zeros((0, 3)), np.zeros((0, 3)))
+    with pytest.raises(OverflowError):
+        kernels.joint_itq(u, u, max_iter=-1)
+    with pytest.raises(TypeError):
+        kernels.joint_itq(u.astype(np.float32), u)
+    lib = _lib.lib()
+    out = np.zeros(12, dtype=np.int8)
+    n_iter, conv = ctypes.c_size_t(), ctypes.c_int32()
+    rc = lib.qk_joint_itq(u.ctypes.data, 11, u.ctypes.data, 12, 4, 4, 3, 5, 1e-12, 0,
+                          out.ctypes.data, out.ctypes.data, ctypes.byref(n_iter),
+                          ctypes.byref(conv))
+    assert rc == _lib.QK_ERR_VALUE
+    assert lib.qk_last_error().decode() == "joint_itq shape mismatch: u_hat 4x2, v_hat 4x3"
+    # all-zero factors: Z R = 0 everywhere, every sign is +1 (x >= 0), as in the reference
+    u_t, v_t, _, _ = kernels.joint_itq(u, u, max_iter=2)
+    assert np.all(u_t == 1) and np.all(v_t == 1)

@@ -177,3 +177,16 @@ def test_gqa_attention_scalar_matches_exact():
     v4 = vals.reshape(n_pos, n_kv, d).transpose(1, 0, 2)[None]
     want = anp.attention_exact(q.reshape(1, n_heads, 1, d), k4, v4, causal=True)
     assert np.abs(got - want.ravel()).max() < 1e-5
+
+
+def test_joint_itq_oracle_matches_reference():
+    from oracle import itq_np
+    g = golden("joint_itq")
+    assert len(g.cases("itq")) >= 11
+    for key in g.cases("itq"):
+        meta = g.meta[key]
+        u_t, v_t, n_iter, converged = itq_np.joint_itq(g[key + "_u_hat"], g[key + "_v_hat"],
+                                                       **meta["kwargs"])
+        assert np.array_equal(u_t, g[key + "_u_t"]), meta["scenario"]
+        assert np.array_equal(v_t, g[key + "_v_t"]), meta["scenario"]
+        assert (n_iter, converged) == (meta["n_iter"], meta["converged"]), meta["scenario"]
