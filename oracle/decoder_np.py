@@ -4,8 +4,9 @@ Follows crates/quantibbler-server/src/engine/mod.rs: transformer (:878-945), nor
 (:837-851), rms_norm_into (:1154-1160), rope_rotate (:1169-1184), gqa_attention_scalar
 (:1074-1121, through oracle.gqa_attention_scalar), logits (:788-800) and
 sampler.rs:5-16 (greedy).  The linears go through oracle.layer_apply, which is pinned to
-the reference's vectors; the remaining pieces are pinned only as restatements (the
-reference's model-level golden, tests/fixtures/parity-tiny, needs its container reader).
+the reference's vectors; the whole forward is pinned by the reference's model-level golden
+(tests/fixtures/parity-tiny: logits of eight teacher-forced positions, budget 1e-2 as in
+crates/quantibbler-server/tests/parity_tiny.rs:26), read through the model-directory reader.
 """
 
 from __future__ import annotations
@@ -30,6 +31,13 @@ def rms_norm(x, w, eps, serving):
     inv = np.float32(1.0) / np.sqrt(np.float32(ss + np.float32(eps)))
     out = (x * inv * w).astype(np.float32)
     return _bf16(out) if serving == "bfloat16" else out
+
+
+def per_head_norm(v, w, head_dim, eps, serving):
+    """One head_dim weight vector applied to every head's slice (engine/mod.rs:854-873)."""
+    v = np.asarray(v, np.float32)
+    return np.concatenate([rms_norm(v[i:i + head_dim], w, eps, serving)
+                           for i in range(0, len(v), head_dim)])
 
 
 def rope_rotate(v, head_dim, pos, theta):
@@ -68,6 +76,9 @@ class Session:
         for b, lw in enumerate(self.w["layers"]):
             normed = rms_norm(h, lw["input_norm"], cfg.rms_eps, sv)
             q, k, v = (apply(lw[n], normed, sv) for n in ("q", "k", "v"))
+            if "q_norm" in lw and "k_norm" in lw:   # per_head_norm, engine/mod.rs:854-873,908-911
+                q = per_head_norm(q, lw["q_norm"], cfg.head_dim, cfg.rms_eps, sv)
+                k = per_head_norm(k, lw["k_norm"], cfg.head_dim, cfg.rms_eps, sv)
             q = rope_rotate(q, cfg.head_dim, pos, cfg.rope_theta)
             k = rope_rotate(k, cfg.head_dim, pos, cfg.rope_theta)
             if self.kv_round:

@@ -148,6 +148,11 @@ class Decoder:
         self.k = torch.zeros(B, self.kv_loc * hd, **f32)
         self.v = torch.zeros(B, self.kv_loc * hd, **f32)
         self.attn = torch.zeros(B, self.h_loc * hd, **f32)
+        # per-head q/k norms (one head_dim vector each, engine/mod.rs:854-873) write here; the
+        # RoPE and the attention then read these instead of the projections' outputs
+        self.has_qk_norm = any("q_norm" in lw and "k_norm" in lw for lw in w["layers"])
+        self.qn = torch.zeros(B, self.h_loc * hd, **f32) if self.has_qk_norm else self.q
+        self.kn = torch.zeros(B, self.kv_loc * hd, **f32) if self.has_qk_norm else self.k
         # o / down outputs (one partial per rank under TP).  With the fused all-reduce the two
         # are separate buffers in symmetric memory that every peer can read.
         self.delta = torch.zeros(B, d, **f32)
@@ -188,9 +193,15 @@ class Decoder:
         self.lm_head = dev_bf16(w["lm_head"]) if cfg.serving == "bfloat16" else dev_f32(
             w["lm_head"])
         self.final_norm = dev_f32(w["final_norm"])
-        self.norms, self.layers, self.plans = [], [], []
+        self.norms, self.layers, self.plans, self.qk_norms = [], [], [], []
         for lw in w["layers"]:
             self.norms.append((dev_f32(lw["input_norm"]), dev_f32(lw["post_norm"])))
+            if "q_norm" in lw and "k_norm" in lw:
+                self.qk_norms.append((dev_f32(lw["q_norm"]), dev_f32(lw["k_norm"])))
+            elif self.has_qk_norm:
+                raise ValueError("q/k norms must be present in every block or in none")
+            else:
+                self.qk_norms.append(None)
             L = {n: PackedLayer(ctx, lw[n]["ub_rows"], lw[n]["vb_t_rows"], lw[n]["dout"],
                                 lw[n]["din"], lw[n]["r"], lw[n]["s1"], lw[n]["s2"],
                                 lw[n].get("bias"), serving=cfg.serving, name=n) for n in LINEARS}
@@ -304,11 +315,18 @@ class Decoder:
             else:
                 self._linears(li, ["q"], self.h, [self.q])
                 self._linears(li, ["k", "v"], self.h, [self.k, self.v])
-            check(lib.qk_rope_cache(c, _p(self.q), _p(self.k), _p(self.v), _p(self.cos_sin),
+            if self.qk_norms[li] is not None:
+                # every head is one row of head_dim values; x_out = x rewrites the projection
+                # unchanged (the kernel's usual in-place form)
+                for src, dst, wgt, heads in ((self.q, self.qn, self.qk_norms[li][0], self.h_loc),
+                                             (self.k, self.kn, self.qk_norms[li][1], self.kv_loc)):
+                    check(lib.qk_rmsnorm(c, _p(src), None, _p(wgt), B * heads, hd, cfg.rms_eps,
+                                         self.serving_tag, _p(src), _p(dst)))
+            check(lib.qk_rope_cache(c, _p(self.qn), _p(self.kn), _p(self.v), _p(self.cos_sin),
                                     _p(self.positions), _p(self.seq_index), _p(self.cache_k[li]),
                                     _p(self.cache_v[li]), self.kv_tag, B, self.h_loc, self.kv_loc,
                                     hd, cfg.max_seq))
-            check(lib.qk_decode_attention(c, _p(self.q), _p(self.cache_k[li]), _p(self.cache_v[li]),
+            check(lib.qk_decode_attention(c, _p(self.qn), _p(self.cache_k[li]), _p(self.cache_v[li]),
                                           self.kv_tag, _p(self.kv_len), B, self.h_loc, self.kv_loc,
                                           hd, cfg.max_seq, self.n_splits, _p(self.att_scratch),
                                           _p(self.attn)))

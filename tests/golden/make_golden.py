@@ -5,6 +5,7 @@ Run in a container that has the reference mounted:
 
     python tests/golden/make_golden.py /path/to/reference
     python tests/golden/make_golden.py /path/to/reference joint_itq    # that family alone
+    python tests/golden/make_golden.py /path/to/reference parity_tiny  # the model fixture alone
 
 It does two things, and commits nothing by itself:
 
@@ -17,7 +18,9 @@ It does two things, and commits nothing by itself:
    linear at a small and at the 4096x4096 rank-1024 shape, attention at shapes with
    ragged tiles) to produce further golden outputs.
 
-The tests only read the ``.npz`` files; the reference checkout is not needed to run
+3. Copies the reference's model-level fixture directory (``tests/fixtures/parity-tiny``).
+
+The tests only read the ``.npz`` files and that directory; the reference checkout is not needed to run
 them.
 """
 
@@ -75,6 +78,24 @@ def joint_itq_cases(rk, load):
     return itq, imeta
 
 
+def copy_parity_tiny(ref_root: str) -> None:
+    """The reference's model-level fixture (tests/fixtures/parity-tiny: a two-block model
+    directory with q/k norms and the logits its quantised HF original gives for eight
+    teacher-forced positions, budget 1e-2 in crates/quantibbler-server/tests/parity_tiny.rs)
+    copied as data; the tokenizer is not part of the forward and stays behind."""
+    import shutil
+    src = os.path.join(ref_root, "tests", "fixtures", "parity-tiny")
+    dst = os.path.join(HERE, "parity-tiny")
+    if os.path.isdir(dst):
+        shutil.rmtree(dst)
+    shutil.copytree(src, dst, ignore=shutil.ignore_patterns("tokenizer.json"))
+    for root, _dirs, files in os.walk(dst):   # the checkout may be read-only
+        os.chmod(root, 0o755)
+        for f in files:
+            os.chmod(os.path.join(root, f), 0o644)
+    print("parity-tiny", sum(len(f) for _r, _d, f in os.walk(dst)), "files")
+
+
 def main(ref_root: str, only: str | None = None) -> None:
     sys.path.insert(0, os.path.join(ref_root, "src"))
     import quantibbler.kernels as rk
@@ -93,6 +114,9 @@ def main(ref_root: str, only: str | None = None) -> None:
             json.dump(m, f, indent=1, sort_keys=True)
         print(name, len(arrays), "arrays")
 
+    if only == "parity_tiny":
+        copy_parity_tiny(ref_root)
+        return
     if only == "joint_itq":   # this family alone (the others take minutes of Python loops)
         dump("joint_itq", *joint_itq_cases(rk, load))
         return
@@ -314,9 +338,10 @@ def main(ref_root: str, only: str | None = None) -> None:
     dump("joint_itq", itq, imeta)
     dump("layer", lay, lmeta)
     dump("attention", att, ameta)
+    copy_parity_tiny(ref_root)
 
 
 if __name__ == "__main__":
     if len(sys.argv) not in (2, 3):
-        raise SystemExit("usage: make_golden.py <path of the reference checkout> [joint_itq]")
+        raise SystemExit("usage: make_golden.py <path of the reference checkout> [joint_itq|parity_tiny]")
     main(*sys.argv[1:])
