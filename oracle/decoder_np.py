@@ -101,3 +101,21 @@ class Session:
         hidden = self.transformer(self.w["embedding"][token])
         lg = self.logits(hidden)
         return int(np.argmax(lg)), lg  # np.argmax returns the first maximum, like greedy()
+
+
+def generate(cfg, weights, prompt_tokens, max_tokens, eos_token_id=None):
+    """engine/mod.rs:1377-1500 (decode_start, push_token, decode_step, generate) without the
+    text-side stop strings: returns (completion tokens, finish reason)."""
+    if len(prompt_tokens) == 0:
+        raise ValueError("prompt tokenized to zero tokens")
+    s = Session(cfg, weights)
+    for tok in prompt_tokens:
+        nxt, _ = s.step(int(tok))
+    out = []
+    while True:
+        if eos_token_id is not None and nxt == eos_token_id:
+            return out, "stop"
+        out.append(nxt)
+        if len(out) >= max_tokens:
+            return out, "length"
+        nxt, _ = s.step(nxt)

@@ -399,3 +399,48 @@ class Decoder:
             out.append(self.token_ids.clone())
         self.torch.cuda.synchronize()
         return self.torch.stack(out).cpu().numpy()
+
+    def generate(self, prompt_tokens, max_tokens: int, eos_token_id: int | None = None) -> dict:
+        """Greedy generation for one sequence, with the control flow of the reference's
+        ``Engine::decode_start`` / ``push_token`` / ``decode_step`` / ``generate``
+        (engine/mod.rs:1377-1500): the prompt goes through the trunk one position at a time
+        over the device-resident KV cache, the first token is the argmax at the last prompt
+        position, EOS ends the generation without being part of it (finish ``"stop"``), and
+        the completion ends at ``max_tokens`` tokens (finish ``"length"``; as in the
+        reference the first token is kept even when ``max_tokens`` is 0).  ``prompt_ms`` is the
+        prefill span rounded up to a whole millisecond, at least 1.  Stop strings are text-side
+        (they need the tokenizer) and stay with the caller.
+        """
+        import math
+        import time
+        prompt = [int(t) for t in prompt_tokens]
+        if not prompt:
+            raise ValueError("prompt tokenized to zero tokens")
+        if self.cfg.max_batch != 1:
+            raise ValueError("generate serves one sequence: build the decoder with max_batch=1")
+        if len(prompt) + max(int(max_tokens), 1) > self.cfg.max_seq:
+            raise ValueError(f"prompt of {len(prompt)} tokens plus {max_tokens} new tokens does "
+                             f"not fit the KV cache of {self.cfg.max_seq} positions")
+        for tok in prompt:
+            if not 0 <= tok < self.cfg.vocab:
+                raise ValueError(f"token id {tok} out of range (vocab_size {self.cfg.vocab})")
+        started = time.perf_counter()
+        for pos, tok in enumerate(prompt):
+            self.start([tok], [pos])
+            self.step()
+        self.ctx.synchronize()
+        prompt_ms = max(1, math.ceil((time.perf_counter() - started) * 1000.0))
+        out, finish = [], None
+        while finish is None:
+            nxt = int(self.best_idx[0].item())
+            if eos_token_id is not None and nxt == int(eos_token_id):
+                finish = "stop"
+                break
+            out.append(nxt)
+            if len(out) >= int(max_tokens):
+                finish = "length"
+                break
+            self.advance()
+            self.step()
+        return {"prompt_tokens": len(prompt), "completion_tokens": out, "finish": finish,
+                "prompt_ms": prompt_ms}

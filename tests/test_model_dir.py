@@ -169,3 +169,17 @@ def test_missing_projection_and_missing_required_slot(broken):
     with pytest.raises(ModelDirError, match='block 1: missing packed layer '
                                             '"layers.1.inner.self_attn.v_proj"'):
         model_dir.decoder_inputs(md)
+
+
+def test_generate_restatement_semantics():
+    # engine/mod.rs:1427-1456 (push_token): EOS is not part of the completion, the first
+    # token is kept even with max_tokens = 0, an empty prompt is refused
+    md = model_dir.load(FIXTURE)
+    cfg, w = model_dir.decoder_inputs(md, max_seq=64)
+    full, finish = decoder_np.generate(cfg, w, [5, 17, 3], 8, eos_token_id=md.eos_token_id)
+    assert finish == "length" and len(full) == 8
+    cut, finish = decoder_np.generate(cfg, w, [5, 17, 3], 8, eos_token_id=full[3])
+    assert finish == "stop" and cut == full[:3]
+    assert decoder_np.generate(cfg, w, [5, 17, 3], 0) == (full[:1], "length")
+    with pytest.raises(ValueError, match="prompt tokenized to zero tokens"):
+        decoder_np.generate(cfg, w, [], 4)

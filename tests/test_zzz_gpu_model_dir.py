@@ -85,3 +85,27 @@ def test_batched_decode_with_qk_norms_matches_the_restatement(gpu_ctx):
             if top2[1] - top2[0] > 1e-3:
                 assert dev_toks[b] == toks[b]
         toks = [int(t) for t in dev_toks]   # the restatement is fed what the device chose
+
+
+def test_generate_follows_the_engine_control_flow(gpu_ctx):
+    # engine/mod.rs:1377-1500: prefill position by position, first token from the last prompt
+    # position, EOS ends the run and is not returned, max_tokens ends it with "length"
+    md = model_dir.load(FIXTURE)
+    cfg, weights = model_dir.decoder_inputs(md, max_seq=64, max_batch=1)
+    dec = Decoder(gpu_ctx, cfg, weights)
+    for prompt in ([5, 17, 3], [1], [99, 42, 7, 0, 64]):
+        want, finish = decoder_np.generate(cfg, weights, prompt, 12, eos_token_id=md.eos_token_id)
+        got = dec.generate(prompt, 12, eos_token_id=md.eos_token_id)
+        assert got["completion_tokens"] == want and got["finish"] == finish
+        assert got["prompt_tokens"] == len(prompt) and got["prompt_ms"] >= 1
+    # a token the model does produce, declared as EOS: the run stops before it
+    want, finish = decoder_np.generate(cfg, weights, [5, 17, 3], 12, eos_token_id=29)
+    assert finish == "stop" and want == [73, 34, 38]
+    got = dec.generate([5, 17, 3], 12, eos_token_id=29)
+    assert (got["completion_tokens"], got["finish"]) == (want, "stop")
+    got = dec.generate([5, 17, 3], 0)
+    assert (got["completion_tokens"], got["finish"]) == ([73], "length")
+    with pytest.raises(ValueError, match="prompt tokenized to zero tokens"):
+        dec.generate([], 4)
+    with pytest.raises(ValueError, match="does not fit the KV cache"):
+        dec.generate([1] * 60, 8)
