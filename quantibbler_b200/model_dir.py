@@ -11,7 +11,8 @@ text starts with the offending file, as in the reference.
 ``load`` returns a ``ModelDirectory``; ``decoder_inputs`` turns it into the
 ``DecoderConfig`` and weight dictionary that ``quantibbler_b200.decoder.Decoder`` takes.
 A directory is always served in float32 (crates/quantibbler-server/src/model/mod.rs:725-734:
-bfloat16 serving is reachable only through single-file blobs, which are not read here).
+bfloat16 serving is reachable only through single-file blobs, which ``blob.py`` reads into the
+same ``ModelDirectory``).
 """
 
 from __future__ import annotations
@@ -312,10 +313,15 @@ def decoder_inputs(md: ModelDirectory, **overrides):
                                     f"{lw[short]['din']}, the geometry wants {dout}x{din}")
         blocks.append(lw)
     d_ff = blocks[0]["gate"]["dout"]
+    # model/mod.rs:725-734: a directory is always served in float32; a blob at the dtype its
+    # header declares
+    serving = ("bfloat16" if md.extras.get("source") == "blob" and md.remainder_dtype == "bf16"
+               else "float32")
+    settings = dict(serving=serving, kv_dtype="float32")
+    settings.update(overrides)
     cfg = DecoderConfig(n_layers=md.n_layers, d_model=d, n_heads=md.n_heads,
                         n_kv_heads=md.n_kv_heads, head_dim=hd, d_ff=d_ff, vocab=md.vocab_size,
-                        rms_eps=md.rms_norm_eps, rope_theta=md.rope_theta, serving="float32",
-                        kv_dtype="float32", **overrides)
+                        rms_eps=md.rms_norm_eps, rope_theta=md.rope_theta, **settings)
     weights = dict(layers=blocks, final_norm=md.norm_weights[md.n_layers * per_block:].copy(),
                    embedding=md.embedding,
                    lm_head=md.embedding if md.lm_head is None else md.lm_head, vocab_offset=0)

@@ -94,6 +94,15 @@ def copy_parity_tiny(ref_root: str) -> None:
         for f in files:
             os.chmod(os.path.join(root, f), 0o644)
     print("parity-tiny", sum(len(f) for _r, _d, f in os.walk(dst)), "files")
+    # the same model as single-file blobs, written by the reference's own writer
+    # (src/quantibbler/blob.py) at both remainder dtypes
+    from pathlib import Path
+
+    from quantibbler.blob import write_blob_from_directory
+    for dtype, name in (("fp32", "parity-tiny.qpk"), ("bf16", "parity-tiny-bf16.qpk")):
+        sha = write_blob_from_directory(Path(src), Path(HERE) / name, remainder_dtype=dtype,
+                                        created_by="make_golden")
+        print(name, sha[:16])
 
 
 def main(ref_root: str, only: str | None = None) -> None:
@@ -115,7 +124,7 @@ def main(ref_root: str, only: str | None = None) -> None:
         print(name, len(arrays), "arrays")
 
     if only == "parity_tiny":
-        copy_parity_tiny(ref_root)
+        copy_parity_tiny(ref_root)   # needs only the import path set above
         return
     if only == "joint_itq":   # this family alone (the others take minutes of Python loops)
         dump("joint_itq", *joint_itq_cases(rk, load))

@@ -109,3 +109,28 @@ def test_generate_follows_the_engine_control_flow(gpu_ctx):
         dec.generate([], 4)
     with pytest.raises(ValueError, match="does not fit the KV cache"):
         dec.generate([1] * 60, 8)
+
+
+def test_bf16_blob_is_served_in_bfloat16_on_the_device(gpu_ctx):
+    # the reference's writer packed parity-tiny at bf16; a blob is served at its declared
+    # dtype (model/mod.rs:725-734): bfloat16 linears, norms (incl. q/k norms) and head
+    from quantibbler_b200 import blob
+    md = blob.load_any(os.path.join(GOLDEN, "parity-tiny-bf16.qpk"))
+    cfg, weights = model_dir.decoder_inputs(md, max_seq=16, max_batch=1)
+    assert cfg.serving == "bfloat16"
+    with open(os.path.join(FIXTURE, "goldens.json")) as f:
+        g = json.load(f)
+    dec = Decoder(gpu_ctx, cfg, weights)
+    session = decoder_np.Session(cfg, weights)
+    worst_golden = worst_oracle = 0.0
+    for pos, tok in enumerate(g["input_ids"]):
+        dec.start([tok], [pos])
+        dec.step()
+        gpu_ctx.synchronize()
+        got = dec.logits.cpu().numpy()[0]
+        _, want = session.step(tok)
+        worst_oracle = max(worst_oracle, float(np.abs(got - want).max()))
+        worst_golden = max(worst_golden,
+                           float(np.abs(got - np.asarray(g["logits"][pos], np.float32)).max()))
+    assert worst_golden <= 1e-2          # the reference's budget, parity_tiny.rs:26
+    assert worst_oracle <= 1e-2          # bfloat16 roundings land on different ties
