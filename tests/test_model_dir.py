@@ -183,3 +183,56 @@ def test_generate_restatement_semantics():
     assert decoder_np.generate(cfg, w, [5, 17, 3], 0) == (full[:1], "length")
     with pytest.raises(ValueError, match="prompt tokenized to zero tokens"):
         decoder_np.generate(cfg, w, [], 4)
+
+
+def _patch_layer(dst, offset, value):
+    layer = dst / "layers/layers/0/inner/self_attn/q_proj.qpk1"
+    raw = bytearray(layer.read_bytes())
+    raw[offset:offset + len(value)] = value
+    layer.write_bytes(bytes(raw))
+
+
+@pytest.mark.parametrize("variant,needle", [
+    # the names and needles of the reference's corrupted-variant table
+    # (crates/quantibbler-server/tests/common/mod.rs:497-526), rebuilt on the parity-tiny copy
+    ("missing_manifest", "manifest.toml"),
+    ("missing_layer_file", "q_proj.qpk1"),
+    ("bad_magic", "q_proj.qpk1: bad magic"),
+    ("wrong_version", "q_proj.qpk1: unsupported representation version 7"),
+    ("unknown_dtype_tag", "q_proj.qpk1: unknown dtype tag 9"),
+    ("rank_zero", "q_proj.qpk1: dout, din and r must all be >= 1"),
+    ("trailing_bytes", "q_proj.qpk1: trailing garbage"),
+    ("missing_sidecar_block", "missing [sidecar] block"),
+    ("missing_norms_manifest", "missing field `norms`"),
+    ("missing_norms_file", "norms.bin"),
+    ("missing_geometry", "missing field `n_heads`"),
+])
+def test_reference_corrupted_variants(broken, variant, needle):
+    dst, edit = broken
+    q_proj = dst / "layers/layers/0/inner/self_attn/q_proj.qpk1"
+    if variant == "missing_manifest":
+        (dst / "manifest.toml").unlink()
+    elif variant == "missing_layer_file":
+        q_proj.unlink()
+    elif variant == "bad_magic":
+        _patch_layer(dst, 0, b"X")
+    elif variant == "wrong_version":
+        _patch_layer(dst, 4, (7).to_bytes(4, "little"))
+    elif variant == "unknown_dtype_tag":
+        _patch_layer(dst, 8, (9).to_bytes(4, "little"))     # magic, version, dtype tag, dout, din, r
+    elif variant == "rank_zero":
+        _patch_layer(dst, 20, (0).to_bytes(4, "little"))
+    elif variant == "trailing_bytes":
+        q_proj.write_bytes(q_proj.read_bytes() + b"\0")
+    elif variant == "missing_sidecar_block":
+        text = (dst / "manifest.toml").read_text()
+        (dst / "manifest.toml").write_text(text[:text.index("[sidecar]")])
+    elif variant == "missing_norms_manifest":
+        edit("manifest.toml", 'norms = "norms.bin"\n', "")
+    elif variant == "missing_norms_file":
+        (dst / "norms.bin").unlink()
+    elif variant == "missing_geometry":
+        edit("config.toml", "n_heads = 4\n", "")
+    with pytest.raises(ModelDirError) as info:
+        model_dir.load(str(dst))
+    assert needle in str(info.value)
