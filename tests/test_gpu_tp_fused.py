@@ -1,5 +1,6 @@
-"""Tensor-parallel decode on two GPUs: the all-reduce fused into the RMSNorm (peer-memory
-loads, rank-order sum) against the NCCL all-reduce, and against the single-GPU decoder.
+"""Tensor-parallel decode on two GPUs: the all-reduce fused into the RMSNorm (tagged stores
+into the peers' inboxes, sum in rank order) against the NCCL all-reduce, eagerly and through a
+CUDA graph.
 
 Needs two GPUs; skipped otherwise.  Ranks are child processes (one per GPU) that rendezvous
 on 127.0.0.1."""
