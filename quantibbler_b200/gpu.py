@@ -336,6 +336,43 @@ class LayerGroup:
             pass
 
 
+class HostLayerGroup:
+    """Same-shape layers applied to HOST inputs in one step: one upload of all inputs, the
+    group's launches, one download of all outputs.  The per-layer host call
+    (``PackedLayer.apply``, the shape of the reference's ``PackedLayer::apply``) pays two
+    copies, two launches and a synchronisation per layer; a caller that has many independent
+    applies ready (all layers of a step, or one layer for many requests) pays them once.
+    ``x_host`` is ``[n_layers, din]`` and ``y_host`` ``[n_layers, dout]`` float32 torch CPU
+    tensors; pinned memory makes both copies asynchronous DMA."""
+
+    def __init__(self, ctx: GpuContext, layers):
+        import torch
+        self.torch, self.ctx, self.layers = torch, ctx, list(layers)
+        first = self.layers[0]
+        n = len(self.layers)
+        self.x_dev = torch.zeros((n, first.din), dtype=torch.float32, device="cuda")
+        self.y_dev = torch.zeros((n, first.dout), dtype=torch.float32, device="cuda")
+        self.group = LayerGroup(ctx, self.layers, self.x_dev.data_ptr(), self.y_dev.data_ptr())
+
+    def apply(self, x_host, y_host) -> None:
+        """``y_host[i] = layer_i(x_host[i])`` for every layer; returns when ``y_host`` is valid."""
+        torch = self.torch
+        if tuple(x_host.shape) != tuple(self.x_dev.shape) or tuple(y_host.shape) != tuple(
+                self.y_dev.shape):
+            raise KernelError(f"host buffers must be {tuple(self.x_dev.shape)} and "
+                              f"{tuple(self.y_dev.shape)}, got {tuple(x_host.shape)} and "
+                              f"{tuple(y_host.shape)}")
+        stream = torch.cuda.ExternalStream(self.ctx.stream)   # the stream the kernels launch on
+        with torch.cuda.stream(stream):
+            self.x_dev.copy_(x_host, non_blocking=True)
+            self.group.apply()
+            y_host.copy_(self.y_dev, non_blocking=True)
+        stream.synchronize()
+
+    def close(self) -> None:
+        self.group.close()
+
+
 class LayerPlan(LayerGroup):
     """Instances (layer, x pointer, y pointer) of one shape bound once; ``apply`` is two
     kernel launches (one when there are at least as many instances as SMs)."""
@@ -352,5 +389,5 @@ class LayerPlan(LayerGroup):
         self._h = h
 
 
-__all__ = ["apply_noalloc", "LayerPlan", "LayerGroup", "GpuContext", "AttentionShape", "PackedLayer", "apply_group", "gpu_available",
+__all__ = ["apply_noalloc", "LayerPlan", "LayerGroup", "HostLayerGroup", "GpuContext", "AttentionShape", "PackedLayer", "apply_group", "gpu_available",
            "gpu_init_hint", "GPU_INDEX_CEILING", "KernelError", "DeviceError"]

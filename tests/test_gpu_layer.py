@@ -7,6 +7,7 @@ import pytest
 
 import oracle
 from conftest import golden, make_layer
+from quantibbler_b200._lib import KernelError
 from quantibbler_b200.gpu import PackedLayer, apply_group
 
 pytestmark = pytest.mark.gpu
@@ -230,3 +231,26 @@ def test_layer_validation(gpu_ctx):
     layer = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], 16, 24, 8, L["s1"], L["s2"])
     with pytest.raises(ValueError, match="expects input dim 24, got 23"):
         layer.apply(np.zeros(23, np.float32))
+
+
+def test_host_layer_group_matches_per_layer_host_apply(gpu_ctx):
+    # one upload, the group's launches, one download: same numbers as PackedLayer.apply per layer
+    import torch
+    from quantibbler_b200.gpu import HostLayerGroup
+    specs = [make_layer(192, 256, 64, seed=900 + i) for i in range(9)]
+    layers = [PackedLayer(gpu_ctx, s["ub_rows"], s["vb_t_rows"], 192, 256, 64, s["s1"], s["s2"],
+                          None) for s in specs]
+    x_host = torch.from_numpy(np.stack([s["x"] for s in specs])).pin_memory()
+    y_host = torch.empty((9, 192), dtype=torch.float32).pin_memory()
+    step = HostLayerGroup(gpu_ctx, layers)
+    for _ in range(2):       # the device buffers are reused
+        y_host.zero_()
+        step.apply(x_host, y_host)
+        for i, layer in enumerate(layers):
+            assert np.array_equal(y_host[i].numpy(), layer.apply(specs[i]["x"])), i
+    pageable = torch.empty((9, 192), dtype=torch.float32)
+    step.apply(x_host.clone(), pageable)            # ordinary host memory works too
+    assert np.array_equal(pageable.numpy(), y_host.numpy())
+    with pytest.raises(KernelError, match="host buffers must be"):
+        step.apply(x_host[:3], y_host)
+    step.close()
