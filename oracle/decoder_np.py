@@ -63,8 +63,10 @@ def apply(layer, x, serving):
 class Session:
     """One sequence: weights + an append-only KV cache (KvCache, engine/mod.rs:1189-1209)."""
 
-    def __init__(self, cfg, weights, kv_round=None):
-        self.cfg, self.w = cfg, weights
+    def __init__(self, cfg, weights, kv_round=None, reduce=None):
+        # ``reduce``: sums a rank's partial o / down output over the tensor-parallel ranks (the
+        # one all-reduce per sub-block); None on a single rank
+        self.cfg, self.w, self.reduce = cfg, weights, reduce or (lambda part: part)
         self.keys = [[] for _ in range(cfg.n_layers)]
         self.vals = [[] for _ in range(cfg.n_layers)]
         self.kv_round = kv_round  # optional storage rounding of the cache (bfloat16 cache)
@@ -87,11 +89,11 @@ class Session:
             self.vals[b].append(v)
             attn = oracle.gqa_attention_scalar(q, np.stack(self.keys[b]), np.stack(self.vals[b]),
                                                cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
-            h = (apply(lw["o"], attn, sv) + h).astype(np.float32)
+            h = (self.reduce(apply(lw["o"], attn, sv)) + h).astype(np.float32)
             normed = rms_norm(h, lw["post_norm"], cfg.rms_eps, sv)
             g, u = apply(lw["gate"], normed, sv), apply(lw["up"], normed, sv)
             hidden = (g * u / (np.float32(1.0) + np.exp(-g))).astype(np.float32)
-            h = (apply(lw["down"], hidden, sv) + h).astype(np.float32)
+            h = (self.reduce(apply(lw["down"], hidden, sv)) + h).astype(np.float32)
         return rms_norm(h, self.w["final_norm"], cfg.rms_eps, sv)
 
     def logits(self, hidden):

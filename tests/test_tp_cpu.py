@@ -96,3 +96,66 @@ def test_shard_model_shapes():
     assert s["lm_head"].shape == (64, 64) and s["vocab_offset"] == 64
     with pytest.raises(ValueError, match="must divide"):
         tp.shard_model(w, cfg, 0, 4)
+
+
+def _model_worker(rank, world, port, q):
+    """One tensor-parallel rank of the reference's parity-tiny model in NumPy: its shard of
+    every linear and of the head, local heads only, one gloo all-reduce per sub-block."""
+    import dataclasses
+    import json
+
+    import torch
+    import torch.distributed as dist
+
+    from conftest import GOLDEN
+    from oracle import decoder_np
+    from quantibbler_b200 import model_dir
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    fixture = os.path.join(GOLDEN, "parity-tiny")
+    cfg, weights = model_dir.decoder_inputs(model_dir.load(fixture), max_seq=16)
+    with open(os.path.join(fixture, "goldens.json")) as f:
+        g = json.load(f)
+    local = dataclasses.replace(cfg, n_heads=cfg.n_heads // world,
+                                n_kv_heads=cfg.n_kv_heads // world, d_ff=cfg.d_ff // world)
+
+    def reduce(part):
+        t = torch.from_numpy(np.ascontiguousarray(part, dtype=np.float32).copy())
+        dist.all_reduce(t)
+        return t.numpy()
+
+    mine = decoder_np.Session(local, tp.shard_model(weights, cfg, rank, world), reduce=reduce)
+    whole = decoder_np.Session(cfg, weights)
+    worst_whole = worst_golden = 0.0
+    for pos, tok in enumerate(g["input_ids"]):
+        _, part = mine.step(tok)                      # this rank's slice of the vocabulary
+        parts = [torch.zeros(cfg.vocab // world) for _ in range(world)]
+        dist.all_gather(parts, torch.from_numpy(part.copy()))
+        logits = torch.cat(parts).numpy()
+        _, want = whole.step(tok)
+        worst_whole = max(worst_whole, float(np.abs(logits - want).max()))
+        worst_golden = max(worst_golden, float(
+            np.abs(logits - np.asarray(g["logits"][pos], np.float32)).max()))
+    q.put((rank, worst_whole, worst_golden, "q_norm" in mine.w["layers"][0]))
+    dist.destroy_process_group()
+
+
+def test_two_rank_model_reproduces_the_reference_goldens():
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_model_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, worst_whole, worst_golden, has_qk_norm in results:
+        assert has_qk_norm, rank                    # the per-head norm vectors are replicated
+        assert worst_whole <= 2e-5, (rank, worst_whole)    # partial sums round differently
+        assert worst_golden <= 1e-2, (rank, worst_golden)  # parity_tiny.rs:26
