@@ -326,7 +326,8 @@ qk_status qk_argmax_first(qk_ctx *ctx, const float *logits, size_t n_tokens, siz
                           int32_t *out_idx);
 
 /* Which GEMV kernel qk_layer_apply uses: 0 = sign-select SIMT, 1 = bit-sliced INT8
- * tensor-core (default), 2 = the same with 16-warp fused blocks, 3 = the same without the split-k form.  Returns the previous value; values out of range leave it unchanged. */
+ * tensor-core (default), 2 = the same with 16-warp fused blocks, 3 = the same without the split-k form,
+ * 4 = the same with 4-warp fused blocks (a measurement variant).  Returns the previous value; values out of range leave it unchanged. */
 int32_t qk_set_gemv_kernel(qk_ctx *ctx, int32_t which);
 /* Number of kernels launched on this context since creation (for benchmarks). */
 uint64_t qk_gpu_launch_count(qk_ctx *ctx);

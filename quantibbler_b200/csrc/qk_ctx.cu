@@ -178,7 +178,7 @@ int32_t qk_set_gemv_kernel(qk_ctx *ctx, int32_t which) {
     qk_ctx *c;
     if (qk::resolve_ctx(ctx, &c) != QK_OK) return -1;
     int prev = c->gemv_kernel;
-    if (which >= 0 && which <= 3) c->gemv_kernel = which;
+    if (which >= 0 && which <= 4) c->gemv_kernel = which;
     return prev;
 }
 

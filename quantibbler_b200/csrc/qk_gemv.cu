@@ -826,8 +826,10 @@ bool fused_plan(const qk_ctx *c, const StageShape &s1, const StageShape &s2, siz
     *table_bytes = table;
     // two 8-warp blocks per SM overlap one block's serial phases (table builds, the stage
     // boundary) with the other's streaming: measured 3.4 vs 3.1 TB/s for 16-warp blocks
-    for (size_t w = (c->gemv_kernel == 2 || n_inst < 2 * (size_t)c->sm_count) ? 16 : 8; w >= 8;
-         w -= 4) {
+    // (selector 4, for measurement: 4-warp blocks, three of which fit an SM at config 0)
+    const size_t w_min = c->gemv_kernel == 4 ? 4 : 8;
+    for (size_t w = (c->gemv_kernel == 2 || n_inst < 2 * (size_t)c->sm_count) ? 16 : w_min;
+         w >= w_min; w -= 4) {
         if (*t_bytes + table + w * kRingPerWarp <= kSmemBudget) {
             *warps = w;
             *smem = *t_bytes + table + w * kRingPerWarp;
