@@ -10,6 +10,7 @@
 // which is the orthogonal polar factor of (B^T Z)^T and does not depend on the SVD
 // algorithm, so a one-sided Jacobi SVD is used here.
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdint>
 #include <thread>
@@ -123,36 +124,86 @@ void jacobi_svd(const std::vector<double> &a, size_t r, std::vector<double> &u,
         for (size_t j = 0; j < r; ++j) w[j * r + i] = a[i * r + j];
     for (size_t i = 0; i < r; ++i) vt[i * r + i] = 1.0;
     const double eps = 1e-15;
-    for (int sweep = 0; sweep < 60; ++sweep) {
-        bool rotated = false;
-        for (size_t p = 0; p + 1 < r; ++p) {
-            for (size_t q = p + 1; q < r; ++q) {
-                double *wp = &w[p * r], *wq = &w[q * r];
-                double alpha = 0.0, beta = 0.0, gamma = 0.0;
-                for (size_t t = 0; t < r; ++t) {
-                    alpha += wp[t] * wp[t];
-                    beta += wq[t] * wq[t];
-                    gamma += wp[t] * wq[t];
-                }
-                if (gamma == 0.0 || std::fabs(gamma) <= eps * std::sqrt(alpha * beta)) continue;
-                rotated = true;
-                double zeta = (beta - alpha) / (2.0 * gamma);
-                double tn = (zeta >= 0.0 ? 1.0 : -1.0) /
-                            (std::fabs(zeta) + std::sqrt(1.0 + zeta * zeta));
-                double c = 1.0 / std::sqrt(1.0 + tn * tn), s = c * tn;
-                double *vp = &vt[p * r], *vq = &vt[q * r];
-                for (size_t t = 0; t < r; ++t) {
-                    double x = wp[t], y = wq[t];
-                    wp[t] = c * x - s * y;
-                    wq[t] = s * x + c * y;
-                    x = vp[t];
-                    y = vq[t];
-                    vp[t] = c * x - s * y;
-                    vq[t] = s * x + c * y;
-                }
-            }
+    // One rotation: make rows p and q of w orthogonal, carry it to vt.  Returns false when the
+    // pair is already orthogonal to rounding.
+    auto rotate = [&](size_t p, size_t q) -> bool {
+        double *wp = &w[p * r], *wq = &w[q * r];
+        double alpha = 0.0, beta = 0.0, gamma = 0.0;
+        for (size_t t = 0; t < r; ++t) {
+            alpha += wp[t] * wp[t];
+            beta += wq[t] * wq[t];
+            gamma += wp[t] * wq[t];
         }
-        if (!rotated) break;
+        if (gamma == 0.0 || std::fabs(gamma) <= eps * std::sqrt(alpha * beta)) return false;
+        double zeta = (beta - alpha) / (2.0 * gamma);
+        double tn = (zeta >= 0.0 ? 1.0 : -1.0) / (std::fabs(zeta) + std::sqrt(1.0 + zeta * zeta));
+        double c = 1.0 / std::sqrt(1.0 + tn * tn), sn = c * tn;
+        double *vp = &vt[p * r], *vq = &vt[q * r];
+        for (size_t t = 0; t < r; ++t) {
+            double x = wp[t], y = wq[t];
+            wp[t] = c * x - sn * y;
+            wq[t] = sn * x + c * y;
+            x = vp[t];
+            y = vq[t];
+            vp[t] = c * x - sn * y;
+            vq[t] = sn * x + c * y;
+        }
+        return true;
+    };
+    // Round-robin ordering: a sweep is m - 1 rounds of m / 2 disjoint pairs (m = r rounded up
+    // to even; the extra player sits out), so the pairs of a round can be rotated by different
+    // threads.  A pair's rotation depends only on its two rows: the result does not depend on
+    // the number of threads.
+    const size_t m = r + (r & 1), half = m / 2;
+    auto pair_of = [&](size_t round, size_t i, size_t *p, size_t *q) {
+        size_t a = i == 0 ? m - 1 : (round + i) % (m - 1);
+        size_t b = i == 0 ? round : (round + (m - 1) - i) % (m - 1);
+        *p = a < b ? a : b;
+        *q = a < b ? b : a;
+    };
+    size_t n_threads = 1;
+    if (r >= 128) {
+        size_t hw = std::max<size_t>(1, std::thread::hardware_concurrency());
+        n_threads = std::min(hw, half / 8);
+    }
+    std::atomic<int> rotated{0};
+    std::atomic<size_t> arrived{0}, generation{0};
+    auto barrier = [&]() {
+        if (n_threads == 1) return;
+        size_t gen = generation.load(std::memory_order_acquire);
+        if (arrived.fetch_add(1, std::memory_order_acq_rel) + 1 == n_threads) {
+            arrived.store(0, std::memory_order_relaxed);
+            generation.fetch_add(1, std::memory_order_acq_rel);
+        } else {
+            while (generation.load(std::memory_order_acquire) == gen) std::this_thread::yield();
+        }
+    };
+    auto worker = [&](size_t tid) {
+        const size_t per = (half + n_threads - 1) / n_threads;
+        const size_t lo = std::min(half, tid * per), hi = std::min(half, lo + per);
+        for (int sweep = 0; sweep < 60; ++sweep) {
+            for (size_t round = 0; round + 1 < m; ++round) {
+                bool any = false;
+                for (size_t i = lo; i < hi; ++i) {
+                    size_t p, q;
+                    pair_of(round, i, &p, &q);
+                    if (q < r) any |= rotate(p, q);
+                }
+                if (any) rotated.store(1, std::memory_order_relaxed);
+                barrier();
+            }
+            const bool again = rotated.load(std::memory_order_relaxed) != 0;
+            barrier();
+            if (tid == 0) rotated.store(0, std::memory_order_relaxed);
+            barrier();
+            if (!again) break;
+        }
+    };
+    if (m >= 2) {
+        std::vector<std::thread> pool;
+        for (size_t t = 1; t < n_threads; ++t) pool.emplace_back(worker, t);
+        worker(0);
+        for (auto &t : pool) t.join();
     }
     // singular values = column norms; normalise, then complete the null columns
     std::vector<double> sigma(r);
