@@ -208,3 +208,19 @@ def test_joint_itq_refusals():
     # all-zero factors: Z R = 0 everywhere, every sign is +1 (x >= 0), as in the reference
     u_t, v_t, _, _ = kernels.joint_itq(u, u, max_iter=2)
     assert np.all(u_t == 1) and np.all(v_t == 1)
+
+
+def test_public_header_is_plain_c(tmp_path):
+    # the boundary is a C ABI: the header must compile as C99 and as C++ on its own
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "hdr.c"
+    src.write_text('#include "qk_kernels.h"\nint main(void) { return 0; }\n')
+    inc = os.path.join(ROOT, "include")
+    for flags in (["-std=c99", "-pedantic"], ["-x", "c++", "-std=c++17"]):
+        res = subprocess.run([gcc, *flags, "-Wall", "-Werror", "-fsyntax-only", "-I", inc, str(src)],
+                             capture_output=True, text=True)
+        assert res.returncode == 0, res.stderr
