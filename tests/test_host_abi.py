@@ -224,3 +224,23 @@ def test_public_header_is_plain_c(tmp_path):
         res = subprocess.run([gcc, *flags, "-Wall", "-Werror", "-fsyntax-only", "-I", inc, str(src)],
                              capture_output=True, text=True)
         assert res.returncode == 0, res.stderr
+
+
+def test_c_program_links_and_calls_the_host_entry_points(tmp_path):
+    # tests/abi/host_abi.c is a plain C99 caller: it is what a compiled host links against
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    lib_path = _build.build()
+    exe = tmp_path / "host_abi"
+    res = subprocess.run(
+        [gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"),
+         os.path.join(ROOT, "tests", "abi", "host_abi.c"), "-L", os.path.dirname(lib_path),
+         "-lqk_kernels", f"-Wl,-rpath,{os.path.dirname(lib_path)}", "-o", str(exe)],
+        capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0, run.stderr
+    assert "host ABI ok" in run.stdout
