@@ -531,7 +531,10 @@ def main() -> None:
         # end-to-end, the step with HOST buffers: all inputs of the step go up from pinned
         # memory, the same launches run, all outputs come back, then a synchronisation
         e2e_step_ms, e2e_step_error = float("nan"), None
+        n_e2e = min(args.e2e_applies, L)     # 0 switches both end-to-end legs off
         try:
+            if n_e2e == 0:
+                raise RuntimeError("end-to-end legs switched off (--e2e-applies 0)")
             from quantibbler_b200.gpu import HostLayerGroup
             host_step = HostLayerGroup(ctx, layers)
             for _ in range(3):
@@ -547,7 +550,6 @@ def main() -> None:
             e2e_step_error = f"{type(e).__name__}: {e}"
 
         # ... and the reference's call shape: PackedLayer.apply with host buffers, one call per layer
-        n_e2e = min(args.e2e_applies, L)
         xh = x_host.numpy()
         e2e_s = float("nan")
         if n_e2e > 0:
