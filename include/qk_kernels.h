@@ -14,7 +14,7 @@
  *    (crates/quantibbler-kernels/src/core.rs:31-44); a Python binding raises
  *    ValueError with it (crates/quantibbler-kernels/src/lib.rs:34-36).
  *  - Inputs are borrowed for the duration of the call and never retained, except by
- *    qk_layer_create / qk_model_* which copy them to the device.  Outputs are
+ *    qk_layer_create / qk_layer_from_qpk1, which copy them to the device.  Outputs are
  *    caller-allocated.
  *  - "host" pointers are ordinary process memory; "dev" pointers are CUDA device
  *    memory on the context's device.  bfloat16 travels as uint16_t bit patterns

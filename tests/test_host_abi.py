@@ -233,7 +233,8 @@ def test_c_program_links_and_calls_the_host_entry_points(tmp_path):
     gcc = shutil.which("gcc")
     if gcc is None:
         pytest.skip("no C compiler")
-    lib_path = _build.build()
+    _lib.lib()                      # builds the library only if it is missing
+    lib_path = _build.LIB_PATH
     exe = tmp_path / "host_abi"
     res = subprocess.run(
         [gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"),
@@ -244,3 +245,39 @@ def test_c_program_links_and_calls_the_host_entry_points(tmp_path):
     run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
     assert run.returncode == 0, run.stderr
     assert "host ABI ok" in run.stdout
+
+
+def _build_c_program(tmp_path, name):
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    _lib.lib()                      # builds the library only if it is missing
+    lib_path = _build.LIB_PATH
+    exe = tmp_path / name
+    res = subprocess.run(
+        [gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"),
+         os.path.join(ROOT, "tests", "abi", name + ".c"), "-L", os.path.dirname(lib_path),
+         "-lqk_kernels", "-lm", f"-Wl,-rpath,{os.path.dirname(lib_path)}", "-o", str(exe)],
+        capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    return exe
+
+
+def test_gpu_c_program_expectations_match_the_oracle(tmp_path):
+    # tests/abi/gpu_abi.c prints the checksums of its own expected values before it looks for
+    # a device: they must be the oracle's on the same inputs (rebuilt in tests/abi_inputs.py)
+    import subprocess
+
+    import abi_inputs
+    exe = _build_c_program(tmp_path, "gpu_abi")
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert run.returncode in (0, 77), run.stdout + run.stderr   # 77: no usable device
+    printed = dict(line.rsplit(" ", 1) for line in run.stdout.splitlines()
+                   if line.startswith("expected "))
+    want_mv, want_y = abi_inputs.expected_checksums()
+    assert float(printed["expected matvec checksum"]) == want_mv
+    assert float(printed["expected layer checksum"]) == want_y
+    if run.returncode == 77:
+        assert "no CPU fallback" in run.stdout
