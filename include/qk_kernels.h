@@ -162,6 +162,19 @@ qk_status qk_gpu_attention_sage(qk_ctx *ctx, const qk_attention_shape *shape, co
                                 size_t q_len, const float *key, size_t k_len, const float *value,
                                 size_t v_len, int32_t causal, size_t block_size, float *out,
                                 size_t out_len);
+/* The quantisers of the Sage face on their own: src/quantibbler/kernels/attention_sage.py
+ * :164-198 (quantize_per_token, quantize_per_channel, smooth_k_block) as the device path
+ * applies them (gpu_attention.rs:132-155, :197-260).  Runs exactly the kernels
+ * qk_gpu_attention_sage runs before its integer products and returns their INT8 codes and
+ * scales in plain layouts, so that a caller can compare them bit for bit with the reference's:
+ * q_codes [B,H,S,d] and q_scale [B,H,S] (of Q/sqrt(d), per token); k_codes [B,KV,S,d],
+ * k_scale [B,KV,S] (of K minus its key block's mean, per token), k_mean [B,KV,blocks,d];
+ * v_codes [B,KV,S,dv], v_scale [B,KV,blocks,dv] (per channel over the key block's tokens). */
+qk_status qk_gpu_sage_quantize(qk_ctx *ctx, const qk_attention_shape *shape, const float *query,
+                               size_t q_len, const float *key, size_t k_len, const float *value,
+                               size_t v_len, size_t block_size, int8_t *q_codes, float *q_scale,
+                               int8_t *k_codes, float *k_scale, float *k_mean, int8_t *v_codes,
+                               float *v_scale);
 /* The two attention faces on device buffers (same layouts, float32), asynchronous on the
  * context's stream: for callers whose q, k, v already live on the GPU (a resident prefill).
  * Additive; the reference's API has only the host-slice forms above. */
@@ -238,7 +251,8 @@ qk_status qk_layers_apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, si
  * layer must have r <= 8192 and din <= 16384; larger layers are refused with
  * QK_ERR_VALUE.  ctx must be an existing context (NULL is refused).  x_dev holds din and
  * y_dev dout float32 values on the context's device; the call is asynchronous on the
- * context's stream and gives the same values as qk_layer_apply.  The first call on each
+ * context's stream and gives the same values as qk_layer_apply with the default kernel
+ * selector (it always runs the bit-sliced kernel).  The first call on each
  * device looks up the array's device address (cudaGetSymbolAddress): make that first call
  * before any stream capture begins.  All calls share the one array and it keeps the last
  * call's contents (every call overwrites what it later reads, so nothing needs clearing);
@@ -285,8 +299,11 @@ qk_status qk_rmsnorm(qk_ctx *ctx, const float *x, const float *residual, const f
  * partial: this rank's [n_tokens, d] float32.  peer_inbox[r]: device address, valid on this
  * GPU, of rank r's inbox for this call, world x n_tokens x d 8-byte words, zero at start.
  * state_dev: two zero-initialised words of this rank (call count, block ticket).  Consecutive
- * calls must alternate between two inboxes.  The polling is bounded; on expiry the next
- * qk_gpu_synchronize returns QK_ERR_TIMEOUT.  x_out = x + sum, y = norm(x_out) * weight. */
+ * calls must alternate between two inboxes.  x_out = x + sum, y = norm(x_out) * weight.
+ * The polling is bounded (qk_set_wait_limit); on expiry y is not written and the next
+ * qk_gpu_synchronize returns QK_ERR_TIMEOUT.  The call that timed out still counts on this
+ * rank, but the ranks' counts may now differ: before the all-reduce is used again, every rank
+ * must (after a host-side barrier) zero its inboxes and its two state words. */
 qk_status qk_allreduce_rmsnorm(qk_ctx *ctx, const float *partial, const uint64_t *peer_inbox,
                                uint32_t *state_dev, int32_t rank, int32_t world, const float *x,
                                const float *weight, size_t n_tokens, size_t d, float eps,
@@ -294,11 +311,16 @@ qk_status qk_allreduce_rmsnorm(qk_ctx *ctx, const float *partial, const uint64_t
 /* engine/mod.rs:1169-1184 (rope_rotate) and :1204-1209 (KvCache::push).  Rotates q
  * [tokens, n_heads*d] in place and writes the rotated k and v [tokens, n_kv*d] into the
  * head-major cache [n_seq, n_kv, s_max, d] (float32 or bfloat16) at row positions[t] of
- * sequence seq_index[t].  cos_sin is [max_pos, d/2, 2] float32. */
+ * sequence seq_index[t].  cos_sin is [s_max, d/2, 2] float32.  The reference's cache is a
+ * growable Vec; this one is a fixed allocation, so a token whose position is not in
+ * [0, s_max) or whose sequence is not in [0, n_seq) is skipped on the device and the next
+ * qk_gpu_synchronize fails with QK_ERR_VALUE.  The first call on a context creates the
+ * context's error word: make it before any stream capture. */
 qk_status qk_rope_cache(qk_ctx *ctx, float *q, const float *k, const float *v,
                         const float *cos_sin, const int32_t *positions, const int32_t *seq_index,
                         void *cache_k, void *cache_v, int32_t kv_dtype, size_t n_tokens,
-                        size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t s_max);
+                        size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t s_max,
+                        size_t n_seq);
 /* engine/mod.rs:1074-1121 (gqa_attention_scalar): one query per sequence, q [batch,
  * n_heads, d], against kv_len[b] cached positions; out [batch, n_heads, d].  The keys are
  * split n_splits ways across blocks; scratch must hold qk_decode_attention_scratch bytes. */
@@ -329,6 +351,11 @@ qk_status qk_argmax_first(qk_ctx *ctx, const float *logits, size_t n_tokens, siz
  * tensor-core (default), 2 = the same with 16-warp fused blocks, 3 = the same without the split-k form,
  * 4 = the same with 4-warp fused blocks (a measurement variant).  Returns the previous value; values out of range leave it unchanged. */
 int32_t qk_set_gemv_kernel(qk_ctx *ctx, int32_t which);
+/* How many polls a device-side wait of this context's kernels (the prefill GEMM's pipeline
+ * barriers and split-tile flags, the fused all-reduce's inbox) makes before it gives up and
+ * the next qk_gpu_synchronize returns QK_ERR_TIMEOUT.  0 restores the default (2^22, seconds).
+ * Returns the previous value.  No reference counterpart. */
+uint32_t qk_set_wait_limit(qk_ctx *ctx, uint32_t polls);
 /* Number of kernels launched on this context since creation (for benchmarks). */
 uint64_t qk_gpu_launch_count(qk_ctx *ctx);
 

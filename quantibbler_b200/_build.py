@@ -42,8 +42,39 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+STAMP_PATH = os.path.join(LIB_DIR, "sources.sha256")
+
+
+def _inputs() -> list[str]:
+    headers = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith((".h", ".cuh"))]
+    headers.append(os.path.join(_PKG, "..", "include", "qk_kernels.h"))
+    return sources() + headers
+
+
+def _digest() -> str:
+    """Hash of everything the library is built from (contents, not modification times: a
+    copy of the tree to another machine must not look stale)."""
+    import hashlib
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    for path in _inputs():
+        with open(path, "rb") as f:
+            h.update(os.path.basename(path).encode() + b"\0" + f.read())
+    return h.hexdigest()
+
+
+def stale() -> bool:
+    """True when the library is missing or was built from other sources than the present ones."""
+    if not os.path.exists(LIB_PATH) or not os.path.exists(STAMP_PATH):
+        return True
+    with open(STAMP_PATH) as f:
+        return f.read().strip() != _digest()
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile every source under csrc/ and link the shared library."""
+    """Compile every source under csrc/ and link the shared library (nothing to do when the
+    library was built from exactly the present sources)."""
+    if not force and not verbose and not stale():
+        return LIB_PATH
     os.makedirs(OBJ_DIR, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(_PKG, "..", "include", "qk_kernels.h"))
@@ -70,6 +101,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError("link failed:\n" + res.stderr)
+    with open(STAMP_PATH, "w") as f:
+        f.write(_digest() + "\n")
     return LIB_PATH
 
 

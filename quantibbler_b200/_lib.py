@@ -84,7 +84,7 @@ _SIGNATURES = {
                              c_int32, c_void_p, c_void_p]),
     "qk_rope_cache": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_int32, c_size_t, c_size_t,
-                                c_size_t, c_size_t, c_size_t]),
+                                c_size_t, c_size_t, c_size_t, c_size_t]),
     "qk_decode_attention_scratch": (c_size_t, [c_size_t, c_size_t, c_size_t, c_size_t]),
     "qk_decode_attention": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p,
                                       c_size_t, c_size_t, c_size_t, c_size_t, c_size_t, c_size_t,
@@ -110,6 +110,10 @@ _SIGNATURES = {
     "qk_gpu_attention_sage_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_int32, c_size_t, c_void_p]),
     "qk_gpu_launch_count": (c_uint64, [c_void_p]),
+    "qk_gpu_sage_quantize": (c_int32, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_size_t,
+                                       c_void_p, c_size_t, c_size_t, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_void_p, c_void_p]),
+    "qk_set_wait_limit": (ctypes.c_uint32, [c_void_p, ctypes.c_uint32]),
 }
 
 _lib = None
@@ -121,18 +125,23 @@ def exported_symbols() -> list[str]:
 
 
 def lib() -> ctypes.CDLL:
-    """Load the shared library (building it first if the sources are newer)."""
+    """Load the shared library, rebuilding it first when a source is newer than it (the build
+    is incremental); a stale library that cannot be rebuilt is refused, not loaded."""
     global _lib
     if _lib is not None:
         return _lib
     path = _build.LIB_PATH
-    if not os.path.exists(path):
-        try:
-            _build.build()
-        except Exception as exc:  # no nvcc, or a compile error
+    try:
+        # incremental by modification time: a no-op when the library is newer than its sources
+        _build.build()
+    except Exception as exc:  # no nvcc, or a compile error
+        if not os.path.exists(path):
             raise ImportError(
                 f"libqk_kernels.so is not built ({path}); run `python -m quantibbler_b200._build` "
                 f"on a machine with nvcc. There is no CPU fallback. Cause: {exc}") from exc
+        if _build.stale():
+            raise ImportError(
+                f"{path} is older than its sources and could not be rebuilt: {exc}") from exc
     handle = ctypes.CDLL(path)
     for name, (restype, argtypes) in _SIGNATURES.items():
         fn = getattr(handle, name)

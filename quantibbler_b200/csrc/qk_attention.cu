@@ -860,55 +860,78 @@ size_t sage_scratch_bytes(const qk_attention_shape *s, size_t block_size) {
            up(planes * n_blocks * 4);
 }
 
+// Where each piece of the Sage scratch lies, and the padded sizes the kernels use.
+struct SageLayout {
+    size_t block, n_blocks, wpl, dpad, bpad, planes, qrows;
+    size_t o_qc, o_qs, o_kc, o_ks, o_km, o_vc, o_vs, o_md, o_ms;
+    bool tc;
+};
+SageLayout sage_layout(const qk_ctx *c, const AttnDims &dm, size_t block_size) {
+    SageLayout L{};
+    const size_t S = dm.Skv;
+    if (block_size > S) block_size = S;  // one block covers the whole sequence either way
+    L.block = block_size;
+    L.n_blocks = qk::ceil_div(S, block_size);
+    const size_t widest = dm.d > dm.dv ? dm.d : dm.dv;
+    L.wpl = widest <= 16 ? 1 : widest <= 64 ? 4 : widest <= 128 ? 8 : 16;
+    L.dpad = L.wpl * 16;                                   // four lanes x WPL words x four codes
+    L.bpad = qk::ceil_div(block_size, kTK) * kTK;          // keys of a block, padded to the tile
+    L.planes = (size_t)dm.B * dm.KV;
+    L.qrows = (size_t)dm.B * dm.H * dm.Sq;
+    auto up = [](size_t n) { return (n + 255) / 256 * 256; };
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o2 = off; off += up(bytes); return o2; };
+    L.o_qc = take(L.qrows * L.dpad), L.o_qs = take(L.qrows * 4);
+    L.o_kc = take(L.planes * S * L.dpad), L.o_ks = take(L.planes * S * 4);
+    L.o_km = take(L.planes * L.n_blocks * dm.d * 4);
+    L.o_vc = take(L.planes * L.n_blocks * dm.dv * L.bpad), L.o_vs = take(L.planes * L.n_blocks * dm.dv * 4);
+    L.o_md = take(L.planes * L.n_blocks * 8 * L.dpad), L.o_ms = take(L.planes * L.n_blocks * 4);
+    L.tc = c->sage_kernel != 0 && sage_tc_eligible(dm, block_size);
+    return L;
+}
+
+// The three quantisers (psi_Q, gamma + psi_K, psi_V) into `scratch`.
+qk_status sage_quantize_dev(qk_ctx *c, const float *dq, const float *dk, const float *dv,
+                            uint8_t *base, const AttnDims &dm, const SageLayout &L) {
+    const size_t S = dm.Skv;
+    const float inv_sqrt_d = 1.0f / sqrtf((float)dm.d);  // gpu_attention.rs:720
+    sage_quant_q_kernel<<<(unsigned)qk::ceil_div(L.qrows, 8), 256, 0, c->stream>>>(
+        dq, (int8_t *)(base + L.o_qc), (float *)(base + L.o_qs), (uint32_t)L.qrows, dm.d,
+        (uint32_t)L.dpad, inv_sqrt_d);
+    QK_CUDA(cudaGetLastError());
+    dim3 kgrid((unsigned)L.n_blocks, (unsigned)L.planes);
+    sage_quant_k_kernel<<<kgrid, 128, dm.d * sizeof(float), c->stream>>>(
+        dk, (int8_t *)(base + L.o_kc), (float *)(base + L.o_ks), (float *)(base + L.o_km), (uint32_t)S,
+        dm.d, (uint32_t)L.dpad, (uint32_t)L.block, (uint32_t)L.n_blocks,
+        L.tc ? (int8_t *)(base + L.o_md) : nullptr, (float *)(base + L.o_ms));
+    QK_CUDA(cudaGetLastError());
+    sage_quant_v_kernel<<<kgrid, 128, 0, c->stream>>>(
+        dv, (int8_t *)(base + L.o_vc), (float *)(base + L.o_vs), (uint32_t)S, dm.dv,
+        (uint32_t)L.block, (uint32_t)L.bpad, (uint32_t)L.n_blocks, L.tc ? 1 : 0);
+    QK_CUDA(cudaGetLastError());
+    c->launches += 3;
+    return QK_OK;
+}
+
 qk_status attention_sage_dev(qk_ctx *c, const float *dq, const float *dk, const float *dv,
                              float *out, uint8_t *scratch, const qk_attention_shape *shape,
                              int causal, size_t block_size) {
     const AttnDims dm = dims_of(shape);
-    const size_t S = dm.Skv;
-    if (block_size > S) block_size = S;  // one block covers the whole sequence either way
-    const size_t n_blocks = qk::ceil_div(S, block_size);
-    const size_t widest = dm.d > dm.dv ? dm.d : dm.dv;
-    const size_t wpl = widest <= 16 ? 1 : widest <= 64 ? 4 : widest <= 128 ? 8 : 16;
-    const size_t dpad = wpl * 16;                       // four lanes x WPL words x four codes
-    const size_t bpad = qk::ceil_div(block_size, kTK) * kTK;  // keys of a block, padded to the tile
-    const size_t planes = (size_t)dm.B * dm.KV, qrows = (size_t)dm.B * dm.H * dm.Sq;
-    auto up = [](size_t n) { return (n + 255) / 256 * 256; };
-    size_t off = 0;
-    auto take = [&](size_t bytes) { size_t o2 = off; off += up(bytes); return o2; };
-    const size_t o_qc = take(qrows * dpad), o_qs = take(qrows * 4);
-    const size_t o_kc = take(planes * S * dpad), o_ks = take(planes * S * 4);
-    const size_t o_km = take(planes * n_blocks * dm.d * 4);
-    const size_t o_vc = take(planes * n_blocks * dm.dv * bpad), o_vs = take(planes * n_blocks * dm.dv * 4);
-    const size_t o_md = take(planes * n_blocks * 8 * dpad), o_ms = take(planes * n_blocks * 4);
+    const SageLayout L = sage_layout(c, dm, block_size);
     uint8_t *base = scratch;
-    const bool tc = c->sage_kernel != 0 && sage_tc_eligible(dm, block_size);
-    const float inv_sqrt_d = 1.0f / sqrtf((float)dm.d);  // gpu_attention.rs:720
-    sage_quant_q_kernel<<<(unsigned)qk::ceil_div(qrows, 8), 256, 0, c->stream>>>(
-        dq, (int8_t *)(base + o_qc), (float *)(base + o_qs), (uint32_t)qrows, dm.d, (uint32_t)dpad,
-        inv_sqrt_d);
-    QK_CUDA(cudaGetLastError());
-    dim3 kgrid((unsigned)n_blocks, (unsigned)planes);
-    sage_quant_k_kernel<<<kgrid, 128, dm.d * sizeof(float), c->stream>>>(
-        dk, (int8_t *)(base + o_kc), (float *)(base + o_ks), (float *)(base + o_km), (uint32_t)S,
-        dm.d, (uint32_t)dpad, (uint32_t)block_size, (uint32_t)n_blocks,
-        tc ? (int8_t *)(base + o_md) : nullptr, (float *)(base + o_ms));
-    QK_CUDA(cudaGetLastError());
-    sage_quant_v_kernel<<<kgrid, 128, 0, c->stream>>>(
-        dv, (int8_t *)(base + o_vc), (float *)(base + o_vs), (uint32_t)S, dm.dv,
-        (uint32_t)block_size, (uint32_t)bpad, (uint32_t)n_blocks, tc ? 1 : 0);
-    QK_CUDA(cudaGetLastError());
-    c->launches += 3;
-    SageArgs a{(const int8_t *)(base + o_qc), (const float *)(base + o_qs),
-               (const int8_t *)(base + o_kc), (const float *)(base + o_ks),
-               (const float *)(base + o_km),  (const int8_t *)(base + o_md),
-               (const float *)(base + o_ms),  (const int8_t *)(base + o_vc),
-               (const float *)(base + o_vs),  out,
-               (uint32_t)dpad, (uint32_t)bpad, (uint32_t)block_size, (uint32_t)n_blocks};
-    if (tc)
+    qk_status st = sage_quantize_dev(c, dq, dk, dv, base, dm, L);
+    if (st != QK_OK) return st;
+    SageArgs a{(const int8_t *)(base + L.o_qc), (const float *)(base + L.o_qs),
+               (const int8_t *)(base + L.o_kc), (const float *)(base + L.o_ks),
+               (const float *)(base + L.o_km),  (const int8_t *)(base + L.o_md),
+               (const float *)(base + L.o_ms),  (const int8_t *)(base + L.o_vc),
+               (const float *)(base + L.o_vs),  out,
+               (uint32_t)L.dpad, (uint32_t)L.bpad, (uint32_t)L.block, (uint32_t)L.n_blocks};
+    if (L.tc)
         return dm.d == 64 ? launch_sage_tc_block<2>(c, a, dm, causal) : launch_sage_tc_block<4>(c, a, dm, causal);
-    if (wpl == 1) return launch_sage<1>(c, a, dm, causal);
-    if (wpl == 4) return launch_sage<4>(c, a, dm, causal);
-    if (wpl == 8) return launch_sage<8>(c, a, dm, causal);
+    if (L.wpl == 1) return launch_sage<1>(c, a, dm, causal);
+    if (L.wpl == 4) return launch_sage<4>(c, a, dm, causal);
+    if (L.wpl == 8) return launch_sage<8>(c, a, dm, causal);
     return launch_sage<16>(c, a, dm, causal);
 }
 
@@ -1015,6 +1038,59 @@ qk_status qk_gpu_attention_sage_dev(qk_ctx *ctx, const qk_attention_shape *shape
     if ((st = c->d_in.reserve(qk::sage_scratch_bytes(shape, block_size))) != QK_OK) return st;
     return qk::attention_sage_dev(c, q_dev, k_dev, v_dev, out_dev, (uint8_t *)c->d_in.ptr, shape,
                                   causal != 0, block_size);
+}
+
+qk_status qk_gpu_sage_quantize(qk_ctx *ctx, const qk_attention_shape *shape, const float *query,
+                               size_t q_len, const float *key, size_t k_len, const float *value,
+                               size_t v_len, size_t block_size, int8_t *q_codes, float *q_scale,
+                               int8_t *k_codes, float *k_scale, float *k_mean, int8_t *v_codes,
+                               float *v_scale) {
+    if (!shape) return qk::fail(QK_ERR_VALUE, "attention shape is null");
+    const size_t o_len = shape->batch * shape->n_heads * shape->seq_q * shape->val_dim;
+    qk_status st = validate_attention(shape, q_len, k_len, v_len, true, block_size, o_len);
+    if (st != QK_OK) return st;
+    if (!q_codes || !q_scale || !k_codes || !k_scale || !k_mean || !v_codes || !v_scale)
+        return qk::fail(QK_ERR_VALUE, "qk_gpu_sage_quantize: null output");
+    qk_ctx *c;
+    if ((st = qk::resolve_ctx(ctx, &c)) != QK_OK) return st;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    auto up = [](size_t n) { return (n + 255) / 256 * 256; };
+    const size_t qb = q_len * 4, kb = k_len * 4, vb = v_len * 4;
+    const size_t o_k = up(qb), o_v = o_k + up(kb), o_scratch = o_v + up(vb);
+    const size_t scratch_bytes = qk::sage_scratch_bytes(shape, block_size);
+    if ((st = c->d_in.reserve(o_scratch + scratch_bytes)) != QK_OK) return st;
+    uint8_t *base = (uint8_t *)c->d_in.ptr;
+    float *dq = (float *)base, *dk = (float *)(base + o_k), *dv = (float *)(base + o_v);
+    QK_CUDA(cudaMemcpyAsync(dq, query, qb, cudaMemcpyHostToDevice, c->stream));
+    QK_CUDA(cudaMemcpyAsync(dk, key, kb, cudaMemcpyHostToDevice, c->stream));
+    QK_CUDA(cudaMemcpyAsync(dv, value, vb, cudaMemcpyHostToDevice, c->stream));
+    const AttnDims dm = dims_of(shape);
+    const qk::SageLayout L = qk::sage_layout(c, dm, block_size);
+    if ((st = qk::sage_quantize_dev(c, dq, dk, dv, base + o_scratch, dm, L)) != QK_OK) return st;
+    std::vector<uint8_t> host(scratch_bytes);
+    QK_CUDA(cudaMemcpyAsync(host.data(), base + o_scratch, scratch_bytes, cudaMemcpyDeviceToHost,
+                            c->stream));
+    QK_CUDA(cudaStreamSynchronize(c->stream));
+    // un-pad and un-permute into the plain layouts of the reference's quantisers
+    const size_t S = dm.Skv, d = dm.d, dv_ = dm.dv;
+    const int8_t *qc = (const int8_t *)(host.data() + L.o_qc), *kc = (const int8_t *)(host.data() + L.o_kc);
+    const int8_t *vc = (const int8_t *)(host.data() + L.o_vc);
+    for (size_t r = 0; r < L.qrows; ++r) std::memcpy(q_codes + r * d, qc + r * L.dpad, d);
+    std::memcpy(q_scale, host.data() + L.o_qs, L.qrows * 4);
+    for (size_t r = 0; r < L.planes * S; ++r) std::memcpy(k_codes + r * d, kc + r * L.dpad, d);
+    std::memcpy(k_scale, host.data() + L.o_ks, L.planes * S * 4);
+    std::memcpy(k_mean, host.data() + L.o_km, L.planes * L.n_blocks * d * 4);
+    std::memcpy(v_scale, host.data() + L.o_vs, L.planes * L.n_blocks * dv_ * 4);
+    for (size_t p = 0; p < L.planes; ++p)
+        for (size_t jb = 0; jb < L.n_blocks; ++jb)
+            for (size_t ch = 0; ch < dv_; ++ch) {
+                const int8_t *row = vc + ((p * L.n_blocks + jb) * dv_ + ch) * L.bpad;
+                for (size_t kk = 0; kk < L.block && jb * L.block + kk < S; ++kk)
+                    v_codes[(p * S + jb * L.block + kk) * dv_ + ch] =
+                        row[L.tc ? sage_tc_key_slot((uint32_t)kk) : kk];
+            }
+    return QK_OK;
 }
 
 int32_t qk_set_sage_kernel(qk_ctx *ctx, int32_t which) {

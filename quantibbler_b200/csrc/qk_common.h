@@ -63,7 +63,8 @@ struct qk_ctx {
     // error word of the asynchronous tensor-core kernels, read back by qk_gpu_synchronize
     qk_scratch d_err;
     qk_scratch d_head;  // the LM head's bfloat16 split of the hidden state
-    bool err_armed = false;
+    bool err_armed = false;  // sticky: set by the first launch that can raise the error word
+    uint32_t wait_limit = 0;  // polls before a device-side wait gives up (0: the default)
     void *h_pinned = nullptr;
     size_t h_pinned_cap = 0;
     qk_status pinned(size_t bytes, void **out);
@@ -96,4 +97,7 @@ namespace qk {
 // Returns the context to use for a call: `ctx` itself, or the process-wide default on
 // device 0 (created on first use) when `ctx` is null.
 qk_status resolve_ctx(qk_ctx *ctx, qk_ctx **out);
+// Makes sure the context's error word (an int, bits: 1 a prefill pipeline wait, 2 an all-reduce
+// inbox wait, 4 a token outside the KV cache) and the prefill's CTA flags after it exist.
+qk_status error_word(qk_ctx *c);
 }  // namespace qk

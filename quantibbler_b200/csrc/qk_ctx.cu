@@ -63,6 +63,14 @@ qk_status resolve_ctx(qk_ctx *ctx, qk_ctx **out) {
     return QK_OK;
 }
 
+qk_status error_word(qk_ctx *c) {
+    if (c->d_err.ptr) return QK_OK;
+    qk_status st = c->d_err.reserve(256 + 4096);
+    if (st != QK_OK) return st;
+    QK_CUDA(cudaMemsetAsync(c->d_err.ptr, 0, 256 + 4096, c->stream));
+    return QK_OK;
+}
+
 }  // namespace qk
 
 extern "C" {
@@ -154,15 +162,21 @@ qk_status qk_gpu_synchronize(qk_ctx *ctx) {
     QK_CUDA(cudaStreamSynchronize(c->stream));
     std::lock_guard<std::mutex> lock(c->mu);
     if (c->err_armed) {
-        // a tensor-core prefill ran since the last check: fetch its error word
+        // Kernels that can raise the error word have been launched on this context (or captured
+        // into a graph that may be replayed at any time, which is why the check stays armed).
         int h_err = 0;
         QK_CUDA(cudaMemcpyAsync(&h_err, c->d_err.ptr, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
         QK_CUDA(cudaStreamSynchronize(c->stream));
-        c->err_armed = false;
         if (h_err) {
             QK_CUDA(cudaMemsetAsync(c->d_err.ptr, 0, sizeof(int), c->stream));
-            return qk::fail(QK_ERR_TIMEOUT,
-                            "the tensor-core prefill gave up waiting on a pipeline barrier");
+            if (h_err & 4)
+                return qk::fail(QK_ERR_VALUE,
+                                "a token's position or sequence index lies outside the KV cache; "
+                                "the token was skipped");
+            return qk::fail(QK_ERR_TIMEOUT, "a bounded device-side wait gave up:%s%s",
+                            (h_err & 1) ? " a pipeline barrier of the tensor-core prefill;" : "",
+                            (h_err & 2) ? " the inbox of a fused all-reduce (a peer did not send);"
+                                        : "");
         }
     }
     return QK_OK;
@@ -179,6 +193,15 @@ int32_t qk_set_gemv_kernel(qk_ctx *ctx, int32_t which) {
     if (qk::resolve_ctx(ctx, &c) != QK_OK) return -1;
     int prev = c->gemv_kernel;
     if (which >= 0 && which <= 4) c->gemv_kernel = which;
+    return prev;
+}
+
+uint32_t qk_set_wait_limit(qk_ctx *ctx, uint32_t polls) {
+    qk_ctx *c;
+    if (qk::resolve_ctx(ctx, &c) != QK_OK) return 0;
+    std::lock_guard<std::mutex> lock(c->mu);
+    const uint32_t prev = c->wait_limit;
+    c->wait_limit = polls;
     return prev;
 }
 

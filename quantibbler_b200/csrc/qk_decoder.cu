@@ -120,17 +120,22 @@ rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
 // the same order on every rank, so all ranks get the same bits - while it forms h = x + sum
 // and the norm.  Every 8-byte inbox word carries {value, number of this all-reduce}: a word
 // is valid exactly when its tag is the current number, so there are no separate flags and no
-// fences (an aligned 8-byte store is seen whole).  This is what makes a small all-reduce
-// cheap: one posted store per element and peer, then local polling.
+// fences: value and tag travel in ONE 64-bit scalar store and are read back by ONE 64-bit
+// scalar load (relaxed, system scope), which the PTX memory model makes single-copy atomic for
+// an aligned 8-byte access - a vector access of two 32-bit halves would not be.  This is what
+// makes a small all-reduce cheap: one posted store per element and peer, then local polling.
 //   inbox.at[r] : rank r's inbox for this buffer, [source rank][n_tokens * d] words
 //   counter     : this rank's count of all-reduces done (device memory, so that a replayed
 //                 CUDA graph keeps counting); the last block to finish advances it.
 // The caller alternates between two inboxes (attention block, MLP block): a peer can only
 // write all-reduce s + 2 into the inbox being read here after this rank has sent its part of
-// s + 1, i.e. after it is done reading s.  The polling is bounded: on expiry the error word is
-// set and the block returns.
+// s + 1, i.e. after it is done reading s.  The polling is bounded (`poll_limit` rounds per
+// peer): on expiry bit 1 of the error word is set, y is left unwritten, and the call is still
+// counted (ticket and counter advance as usual), so this rank's tags stay in step with its own
+// later calls; the peers' counts may then differ from it, which is why the caller has to
+// re-zero inboxes and state on every rank before it uses the all-reduce again.
 struct InboxArgs {
-    uint2 *at[8];
+    unsigned long long *at[8];
 };
 
 __global__ void __launch_bounds__(kRmsThreads)
@@ -138,7 +143,7 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
                          uint32_t *__restrict__ counter, uint32_t *__restrict__ done, int rank,
                          int world, const float *__restrict__ x, const float *__restrict__ w,
                          float *__restrict__ x_out, float *__restrict__ y, uint32_t d, float eps,
-                         int bf16, int *__restrict__ error) {
+                         int bf16, int *__restrict__ error, uint32_t poll_limit) {
     __shared__ float red[kRmsThreads / 32];
     __shared__ int gave_up;
     const uint32_t step = *counter + 1;
@@ -156,13 +161,14 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
             const uint32_t i = threadIdx.x + (pass * kSlots + sl) * kRmsThreads;
             own[sl] = i < d ? partial[base + i] : 0.f;
             if (i < d) {
-                const uint2 word = make_uint2(__float_as_uint(own[sl]), step);
+                const unsigned long long word =
+                    (unsigned long long)__float_as_uint(own[sl]) | ((unsigned long long)step << 32);
 #pragma unroll
                 for (int p = 0; p < 8; ++p)
                     if (p < world && p != rank)
-                        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(
+                        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(
                                          inbox.at[p] + (size_t)rank * total + base + i),
-                                     "r"(word.x), "r"(word.y)
+                                     "l"(word)
                                      : "memory");
             }
         }
@@ -178,22 +184,22 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
                 for (int sl = 0; sl < kSlots; ++sl) sum[sl] += own[sl];
                 continue;
             }
-            const uint2 *src = inbox.at[rank] + (size_t)r * total + base;
+            const unsigned long long *src = inbox.at[rank] + (size_t)r * total + base;
             float got[kSlots];
             bool ready = false;
-            for (uint32_t tries = 0; tries < (1u << 22) && !ready; ++tries) {
+            for (uint32_t tries = 0; tries < poll_limit && !ready; ++tries) {
                 ready = true;
 #pragma unroll
                 for (int sl = 0; sl < kSlots; ++sl) {
                     const uint32_t i = threadIdx.x + (pass * kSlots + sl) * kRmsThreads;
-                    uint32_t v = 0, tag = step;
+                    unsigned long long word = (unsigned long long)step << 32;
                     if (i < d)
-                        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];"
-                                     : "=r"(v), "=r"(tag)
+                        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];"
+                                     : "=l"(word)
                                      : "l"(src + i)
                                      : "memory");
-                    got[sl] = __uint_as_float(v);
-                    if (tag != step) ready = false;
+                    got[sl] = __uint_as_float((uint32_t)word);
+                    if ((uint32_t)(word >> 32) != step) ready = false;
                 }
             }
             if (!ready) gave_up = 1;
@@ -214,22 +220,22 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
         }
     }
     __syncthreads();
-    if (gave_up) {
-        if (threadIdx.x == 0) atomicExch(error, 1);
-        return;
-    }
-    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
-    for (uint32_t r = 0; threadIdx.x + r * kRmsThreads < d; ++r) {
-        const uint32_t i = threadIdx.x + r * kRmsThreads;
-        float h;
-        if (r < (uint32_t)kRmsPerThread) {
-            h = keep[r];
-        } else {
-            h = x_out[base + i];
-            if (bf16) h = round_bf16f(h);
+    const bool dead = gave_up != 0;  // the same in every thread of the block
+    if (dead && threadIdx.x == 0) atomicOr(error, 2);
+    if (!dead) {
+        const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
+        for (uint32_t r = 0; threadIdx.x + r * kRmsThreads < d; ++r) {
+            const uint32_t i = threadIdx.x + r * kRmsThreads;
+            float h;
+            if (r < (uint32_t)kRmsPerThread) {
+                h = keep[r];
+            } else {
+                h = x_out[base + i];
+                if (bf16) h = round_bf16f(h);
+            }
+            const float o = h * inv * w[i];
+            y[base + i] = bf16 ? round_bf16f(o) : o;
         }
-        const float o = h * inv * w[i];
-        y[base + i] = bf16 ? round_bf16f(o) : o;
     }
     // the last block to finish records that this all-reduce is done (every block has read the
     // counter by then); a single block needs no ticket
@@ -255,9 +261,16 @@ rope_cache_kernel(float *__restrict__ q, const float *__restrict__ k, const floa
                   const float *__restrict__ cos_sin, const int32_t *__restrict__ positions,
                   const int32_t *__restrict__ seq_index, KV *__restrict__ cache_k,
                   KV *__restrict__ cache_v, uint32_t n_heads, uint32_t n_kv, uint32_t d,
-                  uint32_t s_max) {
+                  uint32_t s_max, uint32_t n_seq, int *__restrict__ error) {
     const uint32_t tok = blockIdx.x, half = d / 2;
     const int pos = positions[tok], seq = seq_index[tok];
+    // The cache and the cos/sin table hold s_max positions and n_seq sequences.  A token
+    // outside them (a graph replayed past the end of the cache) is skipped and reported
+    // through the context's error word (bit 2) instead of writing over a neighbour's rows.
+    if (pos < 0 || (uint32_t)pos >= s_max || seq < 0 || (uint32_t)seq >= n_seq) {
+        if (threadIdx.x == 0 && error) atomicOr(error, 4);
+        return;
+    }
     const float *cs = cos_sin + (size_t)pos * half * 2;
     float *qt = q + (size_t)tok * n_heads * d;
     for (uint32_t idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
@@ -351,7 +364,7 @@ decode_attention_kernel(const float *__restrict__ q, const KV *__restrict__ cach
     const uint32_t group = n_heads / n_kv, subs = group / GQ;  // blocks per kv head
     const uint32_t split = blockIdx.x, kvh = blockIdx.y / subs, hsub = blockIdx.y % subs;
     const uint32_t b = blockIdx.z, h0 = kvh * group + hsub * GQ;
-    const int len = kv_len[b];
+    const int len = min(max(kv_len[b], 0), (int)s_max);  // never past the cache's rows
     const int j_begin = split * chunk, j_end = min(len, (int)((split + 1) * chunk));
     const uint32_t tid = threadIdx.x, sub = tid % 8, slot = tid / 8;  // 16 key slots per block
     const unsigned gmask = 0xffu << ((tid % 32) / 8 * 8);  // the eight lanes sharing a key
@@ -486,7 +499,7 @@ decode_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__restr
     const uint32_t split = blockIdx.x, kvh = blockIdx.y / subs, hsub = blockIdx.y % subs;
     const uint32_t b = blockIdx.z, h0 = kvh * group + hsub * gq;
     const uint32_t rows = min(gq, group - hsub * gq);  // query heads of this block
-    const int len = kv_len[b];
+    const int len = min(max(kv_len[b], 0), (int)s_max);  // never past the cache's rows
     const int j_begin = split * chunk, j_end = min(len, (int)((split + 1) * chunk));
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
     const float scale = 1.0f / sqrtf((float)d);
@@ -1015,7 +1028,8 @@ qk_status qk_rmsnorm(qk_ctx *ctx, const float *x, const float *residual, const f
 qk_status qk_rope_cache(qk_ctx *ctx, float *q, const float *k, const float *v,
                         const float *cos_sin, const int32_t *positions, const int32_t *seq_index,
                         void *cache_k, void *cache_v, int32_t kv_dtype, size_t n_tokens,
-                        size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t s_max) {
+                        size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t s_max,
+                        size_t n_seq) {
     qk_ctx *c;
     qk_status st = enter(ctx, &c);
     if (st != QK_OK) return st;
@@ -1025,14 +1039,21 @@ qk_status qk_rope_cache(qk_ctx *ctx, float *q, const float *k, const float *v,
         return qk::fail(QK_ERR_VALUE, "KV cache dtype must be float32 or bfloat16, got tag %d",
                         kv_dtype);
     if (n_tokens == 0) return QK_OK;
+    // out-of-range positions are reported through the error word; it is created on the first
+    // call, so make that call before any stream capture
+    if ((st = qk::error_word(c)) != QK_OK) return st;
+    int *err = (int *)c->d_err.ptr;
     if (kv_dtype == QK_F32)
         rope_cache_kernel<float><<<(unsigned)n_tokens, 256, 0, c->stream>>>(
             q, k, v, cos_sin, positions, seq_index, (float *)cache_k, (float *)cache_v,
-            (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)head_dim, (uint32_t)s_max);
+            (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)head_dim, (uint32_t)s_max,
+            (uint32_t)n_seq, err);
     else
         rope_cache_kernel<uint16_t><<<(unsigned)n_tokens, 256, 0, c->stream>>>(
             q, k, v, cos_sin, positions, seq_index, (uint16_t *)cache_k, (uint16_t *)cache_v,
-            (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)head_dim, (uint32_t)s_max);
+            (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)head_dim, (uint32_t)s_max,
+            (uint32_t)n_seq, err);
+    c->err_armed = true;
     QK_LAUNCHED(c);
 }
 
@@ -1238,15 +1259,12 @@ qk_status qk_allreduce_rmsnorm(qk_ctx *ctx, const float *partial, const uint64_t
     if (!partial || !peer_inbox || !state_dev || !x_out)
         return qk::fail(QK_ERR_VALUE, "qk_allreduce_rmsnorm: null argument");
     if (n_tokens == 0) return QK_OK;
-    if (!c->d_err.ptr) {
-        if ((st = c->d_err.reserve(256 + 4096)) != QK_OK) return st;
-        QK_CUDA(cudaMemsetAsync(c->d_err.ptr, 0, 256 + 4096, c->stream));
-    }
+    if ((st = qk::error_word(c)) != QK_OK) return st;
     InboxArgs inbox{};
-    for (int r = 0; r < world; ++r) inbox.at[r] = reinterpret_cast<uint2 *>(peer_inbox[r]);
+    for (int r = 0; r < world; ++r) inbox.at[r] = reinterpret_cast<unsigned long long *>(peer_inbox[r]);
     allreduce_rmsnorm_kernel<<<(unsigned)n_tokens, kRmsThreads, 0, c->stream>>>(
         inbox, partial, state_dev, state_dev + 1, rank, world, x, weight, x_out, y, (uint32_t)d, eps,
-        serving_dtype == QK_BF16, (int *)c->d_err.ptr);
+        serving_dtype == QK_BF16, (int *)c->d_err.ptr, c->wait_limit ? c->wait_limit : (1u << 22));
     c->err_armed = true;
     QK_LAUNCHED(c);
 }

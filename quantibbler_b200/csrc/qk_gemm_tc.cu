@@ -55,7 +55,7 @@ constexpr int kThreads = (kEpilogueWarp0 + kEpilogueWarps) * 32;
 constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = kBNMax * kBK * 2;  // A: weights, B: tokens
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kTmemCols = 2 * kBNMax;    // two accumulators
-constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr uint32_t kWaitLimitDefault = 1u << 22;  // polls; qk_set_wait_limit overrides it
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -67,10 +67,14 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait: false if the phase did not complete within the limit, or if another role of
-// the CTA has already given up.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+// the CTA has already given up.  The verdict is WARP-UNIFORM: every lane polls until it either
+// sees the phase or runs out of polls, then the warp votes, so that no lane can leave a loop
+// that the rest of its warp stays in (the instructions that follow a wait - tcgen05.ld,
+// __syncwarp, named barriers - need the whole warp).  Call it with all 32 lanes.
+__device__ __forceinline__ bool mbar_wait_lane(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                               uint32_t limit) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    for (uint32_t i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile(
             "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
@@ -82,6 +86,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
         if ((i & 255u) == 255u && *abort_flag) return false;
     }
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                          uint32_t limit) {
+    return __all_sync(0xffffffffu, mbar_wait_lane(bar, parity, abort_flag, limit)) != 0;
+}
+// The four epilogue warps agree on a verdict (named barrier 1 with an AND reduction): either
+// all of them go on, or all of them leave, so that none is left waiting at one of the
+// epilogue's own barriers for a warp that has gone.
+__device__ __forceinline__ bool epilogue_vote(bool ok, uint32_t n_threads) {
+    uint32_t all;
+    asm volatile(
+        "{\n .reg .pred p, q;\n setp.ne.b32 p, %1, 0;\n"
+        " barrier.cta.red.and.pred q, 1, %2, p;\n selp.u32 %0, 1, 0, q;\n}"
+        : "=r"(all)
+        : "r"((uint32_t)ok), "r"(n_threads)
+        : "memory");
+    return all != 0;
 }
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
@@ -135,6 +156,7 @@ struct GemmArgs {
     uint32_t units;        // all tiles x their k_chunks: the work that is dealt out evenly to the CTAs
     float *partials;       // [CTAs][256][128] float32 accumulators of split tiles
     uint32_t *flags;       // [CTAs] flags[i] != 0: CTA i's partial is in place (its one reader clears it)
+    uint32_t wait_limit;   // polls before a wait gives up
 };
 
 // CTA i of G works on units [i * units / G, (i + 1) * units / G).
@@ -249,7 +271,7 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
             const uint2 cur = q0;
             q0 = q1;
             q1 = load_bits(gc + 2 * kGroups);
-            if (!mbar_wait(my_empty, (it & 1) ^ 1, abort_flag)) {
+            if (!mbar_wait(my_empty, (it & 1) ^ 1, abort_flag, g.wait_limit)) {
                 *abort_flag = 1;
                 break;
             }
@@ -301,7 +323,7 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
             const uint32_t kc0 = at.kc, kc1 = min(g.p[at.problem].k_chunks, kc0 + (u_end - u));
             const uint32_t acc = seg & 1;
             // the epilogue must have drained this accumulator (segment seg - 2)
-            if (!mbar_wait(&acc_empty[acc], ((seg >> 1) & 1) ^ 1, abort_flag)) {
+            if (!mbar_wait(&acc_empty[acc], ((seg >> 1) & 1) ^ 1, abort_flag, g.wait_limit)) {
                 dead = true;
                 break;
             }
@@ -309,7 +331,7 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
             const uint32_t d_tmem = tmem_base + acc * kBNMax;
             for (uint32_t kc = kc0; kc < kc1; ++kc, ++gc) {
                 const uint32_t s = gc % kStages;
-                if (!mbar_wait(&full[s], (gc / kStages) & 1, abort_flag)) {
+                if (!mbar_wait(&full[s], (gc / kStages) & 1, abort_flag, g.wait_limit)) {
                     dead = true;
                     break;
                 }
@@ -358,17 +380,22 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
                 while (last < gridDim.x && unit_begin(last, g.units, gridDim.x) < hi) ++last;
                 for (uint32_t j = blockIdx.x + 1; j < last && !dead; ++j) {
                     uint32_t seen = 0;
-                    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+                    for (uint32_t i = 0; i < g.wait_limit; ++i) {
                         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(g.flags + j) : "memory");
                         if (seen) break;
                         if ((i & 255u) == 255u && *abort_flag) break;
                         __nanosleep(64);
                     }
-                    dead = seen == 0;
+                    // every lane made its own acquire load; the warp goes on only if all saw it
+                    dead = __all_sync(0xffffffffu, seen != 0) == 0;
                 }
             }
-            if (dead || !mbar_wait(&acc_full[acc], (seg >> 1) & 1, abort_flag)) {
+            if (!dead) dead = !mbar_wait(&acc_full[acc], (seg >> 1) & 1, abort_flag, g.wait_limit);
+            // one verdict for the four epilogue warps before any of them touches tensor memory
+            // or one of the epilogue's barriers
+            if (!epilogue_vote(!dead, kEpilogueWarps * 32)) {
                 *abort_flag = 1;
+                dead = true;
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -399,8 +426,10 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
                             "r"(smem_u32(staged_bar))
                             : "memory");
                 }
-                if (!mbar_wait(staged_bar, 0, abort_flag)) {
+                // (`staged` is the same in all four warps, so all of them take this vote)
+                if (!epilogue_vote(mbar_wait(staged_bar, 0, abort_flag, g.wait_limit), kEpilogueWarps * 32)) {
                     *abort_flag = 1;
+                    dead = true;
                     break;
                 }
             }
@@ -475,7 +504,7 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
                      "r"(kTmemCols)
                      : "memory");
     }
-    if (tid == 0 && *abort_flag) atomicExch(g.error, 1);
+    if (tid == 0 && *abort_flag) atomicOr(g.error, 1);
 }
 
 // z_p = bf16(s2_p * x) (float32 product, one rounding), zero padded to the pitch, for each of
@@ -597,10 +626,7 @@ qk_status qk_layers_apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, si
         need += qk::ceil_div(n_tokens * kp2[i] * 2, 256) * 256;
     }
     if ((st = c->d_z.reserve(need)) != QK_OK) return st;
-    if (!c->d_err.ptr) {
-        if ((st = c->d_err.reserve(256 + 4096)) != QK_OK) return st;  // error word + CTA flags
-        QK_CUDA(cudaMemsetAsync(c->d_err.ptr, 0, 256 + 4096, c->stream));
-    }
+    if ((st = qk::error_word(c)) != QK_OK) return st;  // error word + CTA flags
     uint8_t *base = (uint8_t *)c->d_z.ptr;
     int *err = (int *)c->d_err.ptr;
     ScaleArgs sa{};
@@ -659,6 +685,7 @@ qk_status qk_layers_apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, si
     g2.units = (uint32_t)units2;
     g1.partials = g2.partials = partials;
     g1.flags = g2.flags = flags;
+    g1.wait_limit = g2.wait_limit = c->wait_limit ? c->wait_limit : kWaitLimitDefault;
     factorized_gemm_tc_kernel<false><<<grid1, kThreads, kSmemBytes, c->stream>>>(
         maps1[0], maps1[1], maps1[2], maps1[3], g1);
     QK_CUDA(cudaGetLastError());

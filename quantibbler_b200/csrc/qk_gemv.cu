@@ -1291,6 +1291,8 @@ extern "C" {
 qk_status qk_layer_apply_noalloc(qk_ctx *ctx, const qk_layer *layer, const float *x_dev,
                                  float *y_dev) {
     if (!layer) return qk::fail(QK_ERR_VALUE, "qk_layer_apply_noalloc: layer is null");
+    if (!x_dev || !y_dev)
+        return qk::fail(QK_ERR_VALUE, "qk_layer_apply_noalloc: x_dev and y_dev must not be null");
     if (!ctx)
         return qk::fail(QK_ERR_VALUE,
                         "qk_layer_apply_noalloc needs an existing context: creating the default "

@@ -106,6 +106,22 @@ def random_model(cfg: DecoderConfig, ranks: dict, seed: int = 0, device_tables: 
                 embedding=emb, lm_head=head, vocab_offset=0)
 
 
+def check_cache_capacity(positions, n_steps: int, max_seq: int) -> None:
+    """Refuse work that would run past the KV cache: a token at position p needs row p of a
+    cache of ``max_seq`` rows, and ``n_steps`` further steps reach position p + n_steps - 1.
+    The reference's cache grows on demand (engine/mod.rs:1189-1209); this one is a fixed
+    allocation, so the host refuses instead (the device skips and reports such a token too)."""
+    pos = [int(p) for p in positions]
+    if not pos:
+        return
+    if min(pos) < 0:
+        raise ValueError(f"negative position {min(pos)}")
+    last = max(pos) + max(int(n_steps), 1) - 1
+    if last >= int(max_seq):
+        raise ValueError(f"position {last} does not fit the KV cache of {max_seq} positions "
+                         f"(start {max(pos)}, {n_steps} steps)")
+
+
 def _p(t) -> ctypes.c_void_p:
     return ctypes.c_void_p(t.data_ptr())
 
@@ -234,6 +250,7 @@ class Decoder:
         # once for all tokens, the GEMV forms would do it once per token
         self.use_gemm = cfg.serving == "bfloat16" and B >= cfg.gemm_min_batch
         self.graph = None
+        self._host_positions = [0] * B
 
     # ------------------------------------------------------------------ tensor parallel
     def _setup_fused_allreduce(self, B: int, d: int) -> None:
@@ -325,7 +342,7 @@ class Decoder:
             check(lib.qk_rope_cache(c, _p(self.qn), _p(self.kn), _p(self.v), _p(self.cos_sin),
                                     _p(self.positions), _p(self.seq_index), _p(self.cache_k[li]),
                                     _p(self.cache_v[li]), self.kv_tag, B, self.h_loc, self.kv_loc,
-                                    hd, cfg.max_seq))
+                                    hd, cfg.max_seq, B))
             check(lib.qk_decode_attention(c, _p(self.qn), _p(self.cache_k[li]), _p(self.cache_v[li]),
                                           self.kv_tag, _p(self.kv_len), B, self.h_loc, self.kv_loc,
                                           hd, cfg.max_seq, self.n_splits, _p(self.att_scratch),
@@ -383,12 +400,16 @@ class Decoder:
 
     def start(self, token_ids, positions) -> None:
         torch = self.torch
+        check_cache_capacity(positions, 1, self.cfg.max_seq)
+        self._host_positions = [int(p) for p in positions]
         self.token_ids.copy_(torch.as_tensor(token_ids, dtype=torch.int32))
         self.positions.copy_(torch.as_tensor(positions, dtype=torch.int32))
         self.kv_len.copy_(self.positions + 1)
 
     def decode(self, n_steps: int) -> np.ndarray:
         """Greedy decode; returns the [n_steps, batch] generated ids."""
+        check_cache_capacity(self._host_positions, n_steps, self.cfg.max_seq)
+        self._host_positions = [p + n_steps for p in self._host_positions]
         out = []
         for _ in range(n_steps):
             if self.graph is not None:
@@ -398,6 +419,7 @@ class Decoder:
                 self.advance()
             out.append(self.token_ids.clone())
         self.torch.cuda.synchronize()
+        self.ctx.synchronize()   # also reports a device-side wait that gave up or a skipped token
         return self.torch.stack(out).cpu().numpy()
 
     def generate(self, prompt_tokens, max_tokens: int, eos_token_id: int | None = None) -> dict:
@@ -442,5 +464,6 @@ class Decoder:
                 break
             self.advance()
             self.step()
+        self.ctx.synchronize()
         return {"prompt_tokens": len(prompt), "completion_tokens": out, "finish": finish,
                 "prompt_ms": prompt_ms}

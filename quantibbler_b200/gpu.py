@@ -172,10 +172,45 @@ def _set_sage_kernel(self, which: int) -> int:
     return int(_lib.lib().qk_set_sage_kernel(self._h, int(which)))
 
 
+def _gpu_sage_quantize(self, shape: AttentionShape, query, key, value, block_size: int) -> dict:
+    """The INT8 codes and scales the Sage face computes before its integer products
+    (attention_sage.py:164-198 as applied by gpu_attention.rs:132-260), in plain layouts:
+    ``q_codes [B,H,S,d]``, ``q_scale [B,H,S]``, ``k_codes [B,KV,S,d]``, ``k_scale [B,KV,S]``,
+    ``k_mean [B,KV,blocks,d]``, ``v_codes [B,KV,S,dv]``, ``v_scale [B,KV,blocks,dv]``."""
+    q = _f(query, np.float32).ravel()
+    k = _f(key, np.float32).ravel()
+    v = _f(value, np.float32).ravel()
+    st = _ShapeStruct(shape.batch, shape.n_heads, shape.n_kv_heads, shape.seq_q, shape.seq_kv,
+                      shape.head_dim, shape.val_dim)
+    B, H, KV, S, d, dv = (shape.batch, shape.n_heads, shape.n_kv_heads, shape.seq_kv,
+                          shape.head_dim, shape.val_dim)
+    blocks = -(-S // min(int(block_size), S)) if block_size > 0 and S > 0 else 0
+    out = dict(q_codes=np.zeros((B, H, S, d), np.int8), q_scale=np.zeros((B, H, S), np.float32),
+               k_codes=np.zeros((B, KV, S, d), np.int8), k_scale=np.zeros((B, KV, S), np.float32),
+               k_mean=np.zeros((B, KV, blocks, d), np.float32),
+               v_codes=np.zeros((B, KV, S, dv), np.int8),
+               v_scale=np.zeros((B, KV, blocks, dv), np.float32))
+    check(_lib.lib().qk_gpu_sage_quantize(
+        self._h, ctypes.byref(st), q.ctypes.data, q.size, k.ctypes.data, k.size, v.ctypes.data,
+        v.size, int(block_size), *[out[n].ctypes.data for n in (
+            "q_codes", "q_scale", "k_codes", "k_scale", "k_mean", "v_codes", "v_scale")]))
+    return out
+
+
+GpuContext.sage_quantize = _gpu_sage_quantize
 GpuContext.attention = _gpu_attention
 GpuContext.attention_sage = _gpu_attention_sage
 GpuContext.attention_dev = _gpu_attention_dev
 GpuContext.set_sage_kernel = _set_sage_kernel
+
+
+def _set_wait_limit(self, polls: int) -> int:
+    """Polls a device-side wait makes before it gives up (0: the default); returns the
+    previous value."""
+    return int(_lib.lib().qk_set_wait_limit(self._h, int(polls)))
+
+
+GpuContext.set_wait_limit = _set_wait_limit
 
 
 class PackedLayer:

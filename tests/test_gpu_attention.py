@@ -182,6 +182,83 @@ def test_sage_config2_shape_row_sample(gpu_ctx):
         assert cos >= COS_MIN and rel_l1 <= REL_L1_MAX
 
 
+def restated_codes(q, k, v, block, ft):
+    """The quantisers of src/quantibbler/kernels/attention_sage.py:164-198 over whole tensors,
+    in float type ``ft`` (float32 follows the device kernel's operation order:
+    gpu_attention.rs:132-155 and the sequential block mean of :197-209)."""
+    b, kvh, s, d = k.shape
+    nb = s // block
+    assert nb * block == s
+    inv = ft(1.0 / np.sqrt(d)) if ft is np.float64 else ft(1.0) / np.sqrt(ft(d))
+    qc, qs = anp.quantize_per_token(q.astype(ft) * inv, ft)
+    kb = k.astype(ft).reshape(b, kvh, nb, block, d)
+    if ft is np.float64:
+        mean = kb.mean(axis=-2, keepdims=True)
+    else:
+        ssum = np.zeros((b, kvh, nb, 1, d), dtype=ft)
+        for jj in range(block):
+            ssum = (ssum + kb[:, :, :, jj:jj + 1]).astype(ft)
+        mean = (ssum / ft(block)).astype(ft)
+    kc, ks = anp.quantize_per_token(kb - mean, ft)
+    vc, vs = anp.quantize_per_channel(v.astype(ft).reshape(b, kvh, nb, block, v.shape[3]), ft)
+    return dict(q_codes=qc, q_scale=qs[..., 0], k_codes=kc.reshape(b, kvh, s, d),
+                k_scale=ks.reshape(b, kvh, s), k_mean=mean[:, :, :, 0],
+                v_codes=vc.reshape(b, kvh, s, v.shape[3]), v_scale=vs[:, :, :, 0])
+
+
+def test_sage_at_config2_codes_and_rows(gpu_ctx):
+    """BASELINE config 2 at full size (32 query heads, 8 KV heads, 8192 tokens, head_dim 128,
+    causal, key block 64).  The INT8 codes and scales the device path computes are read back
+    and must equal the float32 restatement of the reference's quantisers bit for bit; against
+    the float64 reference a code may differ only where a value sits within a float32 rounding
+    of a tie, which is counted.  Output rows are then sampled against the quantized oracle
+    and the exact one."""
+    rng = np.random.default_rng(5)
+    b, h, kvh, s, d, block = 1, 32, 8, 8192, 128, 64
+    q = rng.standard_normal((b, h, s, d), dtype=np.float32)
+    k = rng.standard_normal((b, kvh, s, d), dtype=np.float32) \
+        + (2.0 * rng.standard_normal((1, kvh, 1, d))).astype(np.float32)
+    v = rng.standard_normal((b, kvh, s, d), dtype=np.float32)
+    sh = shape_of(q, k, v)
+    got = gpu_ctx.sage_quantize(sh, q, k, v, block)
+    w32 = restated_codes(q, k, v, block, np.float32)
+    for name in ("q_codes", "k_codes", "v_codes", "q_scale", "k_scale", "v_scale", "k_mean"):
+        assert np.array_equal(got[name], w32[name]), name   # 0 mismatches, codes and scales
+    w64 = restated_codes(q, k, v, block, np.float64)
+    for name in ("q_codes", "k_codes", "v_codes"):
+        rate = np.mean(got[name] != w64[name])
+        assert rate < 1e-3, (name, rate)
+        assert np.abs(got[name].astype(np.int16) - w64[name]).max() <= 1, name
+    out = run_sage(gpu_ctx, q, k, v, True, block)
+    assert np.isfinite(out).all()
+    rows = np.array([0, 63, 64, 1000, 4095, 8191])
+    for hh in (0, 13, 31):
+        kv = hh // (h // kvh)
+        w = anp.attention_sage(q[:, hh:hh + 1], k[:, kv:kv + 1], v[:, kv:kv + 1], causal=True,
+                               block_size=block, rows=rows, ft=np.float32)
+        gsub = out[:, hh:hh + 1][:, :, rows]
+        assert np.abs(gsub - w).max() <= 2e-3 * np.abs(w).max(), hh
+        exact = anp.attention_exact(q[:, hh:hh + 1], k[:, kv:kv + 1], v[:, kv:kv + 1],
+                                    causal=True, rows=rows)
+        cos, rel_l1, _ = anp.quality_metrics(gsub, exact)
+        assert cos >= COS_MIN and rel_l1 <= REL_L1_MAX, (hh, cos, rel_l1)
+
+
+def test_sage_quantize_ragged_block(gpu_ctx):
+    # a sequence that is not a whole number of key blocks, and the dp4a layout (head_dim 48)
+    rng = np.random.default_rng(6)
+    for (s, d, block) in ((100, 64, 32), (70, 48, 64)):
+        q = rng.standard_normal((1, 2, s, d), dtype=np.float32)
+        k = rng.standard_normal((1, 1, s, d), dtype=np.float32) + 1.5
+        v = rng.standard_normal((1, 1, s, d), dtype=np.float32)
+        got = gpu_ctx.sage_quantize(shape_of(q, k, v), q, k, v, block)
+        _, (q_hat, k_codes, v_codes) = anp.attention_sage(q, k, v, causal=False, block_size=block,
+                                                          ft=np.float32, return_codes=True)
+        assert np.array_equal(got["q_codes"], q_hat)
+        assert np.array_equal(got["k_codes"], np.concatenate(k_codes, axis=2))
+        assert np.array_equal(got["v_codes"], np.concatenate(v_codes, axis=2))
+
+
 @pytest.mark.parametrize("case", [
     # (batch, heads, kv heads, seq, head dim, block, causal)
     (1, 4, 2, 200, 128, 64, True), (2, 2, 1, 129, 64, 32, True), (1, 2, 2, 300, 128, 128, False),

@@ -1,0 +1,149 @@
+"""Failure paths that end in a status, not in a fault: a device-side wait that runs out,
+and a token that does not fit the KV cache.  Neither test makes the GPU fault, trap or hang:
+the wait is a bounded poll of ordinary memory that nothing writes, the out-of-range token is
+skipped by a bounds check."""
+
+import ctypes
+
+import numpy as np
+import pytest
+
+from quantibbler_b200 import _lib
+from quantibbler_b200._lib import DeviceError, KernelError
+
+pytestmark = pytest.mark.gpu
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def test_fused_allreduce_wait_runs_out_and_the_context_stays_usable(gpu_ctx):
+    """qk_allreduce_rmsnorm as rank 0 of 2 on ONE GPU: the "peer" inbox is another local buffer
+    and nobody ever writes this rank's inbox, so the poll for rank 1's words can only run out.
+    With the poll limit set to a few thousand rounds that takes milliseconds; the kernel
+    returns, qk_gpu_synchronize reports QK_ERR_TIMEOUT, and the same context then runs an
+    ordinary norm correctly."""
+    import torch
+    lib, c = _lib.lib(), gpu_ctx.handle
+    n_tokens, d, world = 3, 256, 2
+    rng = np.random.default_rng(0)
+    x = torch.from_numpy(rng.standard_normal((n_tokens, d)).astype(np.float32)).cuda()
+    partial = torch.from_numpy(rng.standard_normal((n_tokens, d)).astype(np.float32)).cuda()
+    w = torch.ones(d, device="cuda")
+    x_out = torch.zeros_like(x)
+    y = torch.full_like(x, float("nan"))
+    inboxes = torch.zeros(world, world, n_tokens, d, 2, dtype=torch.int32, device="cuda")
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    ptrs = np.array([inboxes[r].data_ptr() for r in range(world)], dtype=np.uint64)
+    torch.cuda.synchronize()
+    prev = gpu_ctx.set_wait_limit(4000)
+    try:
+        _lib.check(lib.qk_allreduce_rmsnorm(c, _p(partial), ptrs.ctypes.data, _p(state), 0, world,
+                                            _p(x), _p(w), n_tokens, d, 1e-5, _lib.QK_F32,
+                                            _p(x_out), _p(y)))
+        with pytest.raises(DeviceError, match="inbox of a fused all-reduce"):
+            gpu_ctx.synchronize()
+    finally:
+        gpu_ctx.set_wait_limit(prev)
+    # what the kernel did before giving up: it pushed its tagged partial to the peer's inbox,
+    # counted the call, and left y unwritten
+    torch.cuda.synchronize()
+    sent = inboxes[1, 0].cpu().numpy()          # rank 1's inbox, slot of source rank 0
+    assert np.array_equal(sent[..., 0].view(np.float32), partial.cpu().numpy())
+    assert (sent[..., 1] == 1).all()
+    assert int(state[0]) == 1 and int(state[1]) == 0
+    assert torch.isnan(y).all()
+    # the error word was cleared by the failing synchronize: the context works on
+    gpu_ctx.synchronize()
+    _lib.check(lib.qk_rmsnorm(c, _p(x), None, _p(w), n_tokens, d, 1e-5, _lib.QK_F32, None, _p(y)))
+    gpu_ctx.synchronize()
+    xn = x.cpu().numpy().astype(np.float64)
+    want = xn / np.sqrt((xn * xn).mean(axis=1, keepdims=True) + 1e-5)
+    assert np.abs(y.cpu().numpy() - want).max() <= 1e-5
+
+
+def test_single_rank_allreduce_is_the_plain_norm(gpu_ctx):
+    # world = 1: nothing to wait for; x_out = x + partial, y = norm
+    import torch
+    lib, c = _lib.lib(), gpu_ctx.handle
+    n_tokens, d = 2, 192
+    rng = np.random.default_rng(1)
+    x = torch.from_numpy(rng.standard_normal((n_tokens, d)).astype(np.float32)).cuda()
+    partial = torch.from_numpy(rng.standard_normal((n_tokens, d)).astype(np.float32)).cuda()
+    w = torch.from_numpy((1 + 0.1 * rng.standard_normal(d)).astype(np.float32)).cuda()
+    x_out, y = torch.zeros_like(x), torch.zeros_like(x)
+    inbox = torch.zeros(1, n_tokens, d, 2, dtype=torch.int32, device="cuda")
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    ptrs = np.array([inbox.data_ptr()], dtype=np.uint64)
+    torch.cuda.synchronize()
+    for step in (1, 2):
+        _lib.check(lib.qk_allreduce_rmsnorm(c, _p(partial), ptrs.ctypes.data, _p(state), 0, 1, _p(x),
+                                            _p(w), n_tokens, d, 1e-5, _lib.QK_F32, _p(x_out), _p(y)))
+        gpu_ctx.synchronize()
+        assert int(state[0]) == step
+    h = (x + partial).cpu().numpy().astype(np.float64)
+    assert np.array_equal(x_out.cpu().numpy(), (x + partial).cpu().numpy())
+    want = h / np.sqrt((h * h).mean(axis=1, keepdims=True) + 1e-5) * w.cpu().numpy()
+    assert np.abs(y.cpu().numpy() - want).max() <= 1e-5
+
+
+def test_token_outside_the_cache_is_skipped_and_reported(gpu_ctx):
+    """A position past the cache's last row (a graph replayed too often) must neither write
+    into a neighbour's rows nor read past the RoPE table: the token is skipped and the next
+    synchronize says so."""
+    import torch
+    lib, c = _lib.lib(), gpu_ctx.handle
+    n_seq, n_heads, n_kv, d, s_max = 2, 2, 1, 16, 8
+    rng = np.random.default_rng(2)
+    q = torch.from_numpy(rng.standard_normal((n_seq, n_heads * d)).astype(np.float32)).cuda()
+    k = torch.from_numpy(rng.standard_normal((n_seq, n_kv * d)).astype(np.float32)).cuda()
+    v = torch.from_numpy(rng.standard_normal((n_seq, n_kv * d)).astype(np.float32)).cuda()
+    cos_sin = torch.zeros(s_max, d // 2, 2, device="cuda")
+    cos_sin[..., 0] = 1.0
+    cache_k = torch.zeros(n_seq, n_kv, s_max, d, device="cuda")
+    cache_v = torch.zeros_like(cache_k)
+    seq_index = torch.arange(n_seq, dtype=torch.int32, device="cuda")
+
+    def run(positions):
+        pos = torch.tensor(positions, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        _lib.check(lib.qk_rope_cache(c, _p(q), _p(k), _p(v), _p(cos_sin), _p(pos), _p(seq_index),
+                                     _p(cache_k), _p(cache_v), _lib.QK_F32, n_seq, n_heads, n_kv,
+                                     d, s_max, n_seq))
+
+    run([s_max - 1, 3])
+    gpu_ctx.synchronize()                       # both in range: no complaint
+    assert np.array_equal(cache_v[0, 0, s_max - 1].cpu().numpy(), v[0].cpu().numpy())
+    before_k, before_v = cache_k.clone(), cache_v.clone()
+    run([s_max, 4])                             # sequence 0 is one past the end
+    with pytest.raises(KernelError, match="outside the KV cache"):
+        gpu_ctx.synchronize()
+    torch.cuda.synchronize()
+    # sequence 0 wrote nothing (in particular not into sequence 1's first row); sequence 1 did
+    assert np.array_equal(cache_k[0].cpu().numpy(), before_k[0].cpu().numpy())
+    assert np.array_equal(cache_v[1, 0, 4].cpu().numpy(), v[1].cpu().numpy())
+    assert np.array_equal(cache_v[1, 0, 0].cpu().numpy(), before_v[1, 0, 0].cpu().numpy())
+    gpu_ctx.synchronize()                       # reported once, then clear
+
+
+def test_decode_attention_clamps_the_length_to_the_cache(gpu_ctx):
+    # kv_len beyond s_max reads the s_max rows that exist, nothing more
+    import torch
+    lib, c = _lib.lib(), gpu_ctx.handle
+    B, H, KV, d, S = 1, 4, 2, 64, 40
+    rng = np.random.default_rng(3)
+    q = torch.from_numpy(rng.standard_normal((B, H, d)).astype(np.float32)).cuda()
+    k = torch.from_numpy(rng.standard_normal((B, KV, S, d)).astype(np.float32)).cuda()
+    v = torch.from_numpy(rng.standard_normal((B, KV, S, d)).astype(np.float32)).cuda()
+    outs = []
+    for length in (S, S + 1000):
+        kv_len = torch.tensor([length], dtype=torch.int32, device="cuda")
+        out = torch.zeros(B, H, d, device="cuda")
+        scratch = torch.zeros(lib.qk_decode_attention_scratch(B, H, d, 2) // 4 + 4, device="cuda")
+        torch.cuda.synchronize()
+        _lib.check(lib.qk_decode_attention(c, _p(q), _p(k), _p(v), _lib.QK_F32, _p(kv_len), B, H, KV,
+                                           d, S, 2, _p(scratch), _p(out)))
+        gpu_ctx.synchronize()
+        outs.append(out.cpu().numpy())
+    assert np.array_equal(outs[0], outs[1])

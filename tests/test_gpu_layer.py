@@ -186,6 +186,74 @@ def test_fused_layer_kernel_matches_two_stage_path(gpu_ctx, shape, serving):
     assert np.array_equal(y.cpu().numpy(), first)
 
 
+@pytest.mark.parametrize("serving", ["float32", "bfloat16"])
+def test_benchmarked_launch_shape_at_config0(gpu_ctx, serving):
+    """The launch bench.py times: one grouped apply of at least 2 x 148 config-0 instances
+    (4096 x 4096, rank 1024), which is the size at which the library picks the form it uses for
+    many independent layers.  Eight instances are checked against the oracle under the same
+    gates as a single layer, one of them against the reference's own config-0 vector."""
+    import torch
+    from quantibbler_b200.gpu import LayerGroup
+    g = golden("layer")
+    m = g.meta["config0"]
+    dout, din, r = m["dout"], m["din"], m["r"]
+    assert (dout, din, r) == (4096, 4096, 1024)
+    n_distinct, n_inst = 8, 304
+    specs = [make_layer(dout, din, r, m["seed"])]
+    rng = np.random.default_rng(20)
+    for i in range(1, n_distinct):
+        specs.append(dict(
+            ub_rows=rng.integers(0, 256, size=(dout, r // 8), dtype=np.uint8),
+            vb_t_rows=rng.integers(0, 256, size=(r, din // 8), dtype=np.uint8),
+            s1=(np.abs(rng.standard_normal(dout)) * 0.02 + 1e-3).astype(np.float32),
+            s2=(np.abs(rng.standard_normal(din)) * 0.02 + 1e-3).astype(np.float32),
+            bias=(rng.standard_normal(dout) * 0.1).astype(np.float32) if i % 2 else None,
+            dout=dout, din=din, r=r))
+    layers = [PackedLayer(gpu_ctx, s["ub_rows"], s["vb_t_rows"], dout, din, r, s["s1"], s["s2"],
+                          s.get("bias"), serving=serving) for s in specs]
+    xs = rng.standard_normal((n_inst, din)).astype(np.float32)
+    xs[0] = specs[0]["x"]
+    x = torch.from_numpy(xs).cuda()
+    y = torch.full((n_inst, dout), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    group = LayerGroup(gpu_ctx, [layers[i % n_distinct] for i in range(n_inst)], x.data_ptr(),
+                       y.data_ptr())
+    launches0 = gpu_ctx.launch_count
+    group.apply()
+    gpu_ctx.synchronize()
+    assert gpu_ctx.launch_count - launches0 == 1    # the single-launch form, as in the benchmark
+    got = y.cpu().numpy()
+    assert np.isfinite(got).all()
+    tol = F32_BACKWARD if serving == "float32" else BF16_BACKWARD
+    for i in (0, 1, 2, 3, 150, 297, 302, 303):
+        s = dict(specs[i % n_distinct], x=xs[i])
+        want = oracle.layer_apply(s["ub_rows"], s["vb_t_rows"], dout, din, r, s["s1"], s["s2"],
+                                  s.get("bias"), xs[i], serving=serving)
+        if s.get("bias") is None:
+            s["bias"] = None
+        _, t = exact_layer(s)
+        term_scale = np.abs(s["s1"].astype(np.float64)) * np.abs(t).sum()
+        err = np.abs(got[i].astype(np.float64) - want.astype(np.float64))
+        assert (err / term_scale).max() <= 2 * tol, (i, serving)
+        assert err.max() <= (2e-3 if serving == "float32" else 2e-2) * np.abs(want).max(), i
+        if serving == "float32":
+            ulp = np.spacing(np.abs(want).astype(np.float32)).astype(np.float64)
+            assert (err <= 2 * ulp + 1e-12 * term_scale).all(), i
+            assert np.mean(got[i] == want) >= 0.9, i
+        # the same instance through the single-layer call (another kernel form, also exact
+        # integer accumulation): identical bits
+        assert np.array_equal(layers[i % n_distinct].apply(xs[i]), got[i]), i
+    gold = g["config0_y_f32" if serving == "float32" else "config0_y_bf16"]
+    rel = np.abs(got[0].astype(np.float64) - gold).max() / np.abs(gold).max()
+    assert rel <= (2e-5 if serving == "float32" else 2e-2), rel
+    group.apply()
+    gpu_ctx.synchronize()
+    assert np.array_equal(y.cpu().numpy(), got)     # run-to-run bit identity
+    group.close()
+    for layer in layers:
+        layer.close()
+
+
 def test_multi_token_apply(gpu_ctx):
     import torch
     L = make_layer(96, 160, 72, seed=11, with_bias=True)

@@ -51,6 +51,16 @@ def test_prefill_matches_reference(gpu_ctx, shape):
     assert np.array_equal(got, again)
 
 
+@pytest.mark.parametrize("shape", [(14336, 4096, 2560), (4096, 14336, 2560)],
+                         ids=["gate_up", "down"])
+def test_prefill_at_config1(gpu_ctx, shape):
+    """BASELINE config 1 at full size: the Llama-3-8B MLP shapes at rank 2560 on 2048 tokens
+    (the case the prefill benchmark times, with tiles split between CTAs); five tokens are
+    checked against the oracle's per-token bfloat16 apply."""
+    dout, din, r = shape
+    run_case(gpu_ctx, dout, din, r, 2048, seed=dout // 7, with_bias=False)
+
+
 def test_prefill_needs_bf16_serving(gpu_ctx):
     L = make_layer(32, 64, 16, seed=1)
     layer = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], 32, 64, 16, L["s1"], L["s2"])

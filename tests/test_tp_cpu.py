@@ -159,3 +159,16 @@ def test_two_rank_model_reproduces_the_reference_goldens():
         assert has_qk_norm, rank                    # the per-head norm vectors are replicated
         assert worst_whole <= 2e-5, (rank, worst_whole)    # partial sums round differently
         assert worst_golden <= 1e-2, (rank, worst_golden)  # parity_tiny.rs:26
+
+
+def test_decoder_refuses_positions_beyond_the_cache():
+    # host-side refusal (the device skips and reports such a token as well)
+    from quantibbler_b200.decoder import check_cache_capacity
+    check_cache_capacity([0, 5], 3, 8)           # reaches position 7 of 8: fits
+    check_cache_capacity([], 3, 8)
+    with pytest.raises(ValueError, match="position 8 does not fit the KV cache of 8 positions"):
+        check_cache_capacity([0, 5], 4, 8)
+    with pytest.raises(ValueError, match="position 8 does not fit"):
+        check_cache_capacity([8], 1, 8)
+    with pytest.raises(ValueError, match="negative position -1"):
+        check_cache_capacity([-1], 1, 8)
