@@ -39,8 +39,8 @@ DOUT = DIN = 4096
 RANK = 1024
 # algorithmic bytes of one layer-apply: bits of both factors + s1,s2 + x + y, float32 vectors
 BYTES_PER_APPLY = (DOUT * RANK + DIN * RANK) // 8 + 4 * (DOUT + DIN) + 4 * DIN + 4 * DOUT
-# dram__bytes_read.sum + dram__bytes_write.sum of one fused-kernel launch over 296 layers
-# (profiles/layer_bitslice_fused_kernel_config0_stack296.md): 330.915 MB, i.e. per layer
+# dram__bytes_read.sum + dram__bytes_write.sum of one ncu-captured launch over 296 layers was
+# 330.915 MB; traffic grows in proportion to the layers of a launch, so per layer-apply:
 DRAM_TRAFFIC_PER_APPLY = 330.915e6 / 296
 METRIC = "factorized_gemv_hbm_gbs"
 UNIT = "GB/s"
@@ -125,6 +125,7 @@ def cpu_baseline(seconds: float, n_layers: int = 16) -> dict:
         if dt >= seconds:
             break
     return {"value": applies * BYTES_PER_APPLY / dt / 1e9, "unit": UNIT, "cores": cores,
+            "threads_used": int(oracle.lib().qko_pool_workers()) + 1,
             "kind": "port",
             "sample": f"{applies} layer-applies over {n_layers} distinct config-0 layers in "
                       f"{dt:.1f} s; C restatement of fast.rs (byte->sign table, 4 f64 lanes, "
@@ -167,16 +168,148 @@ def run_reference(args, rank: int) -> None:
                    "sample": f"bounded CPU sample of that workload: {per_step} layer-applies per "
                              f"step over 16 distinct layers",
                    "layers_per_step": per_step},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores,
+                         "threads_used": int(oracle.lib().qko_pool_workers()) + 1, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
+# Where BASELINE.json's configurations and the reference disagree; each affected line carries
+# its entry in `config.divergences`.
+DIVERGENCES = {
+    "attention": "BASELINE config 2 words Sage as per-64-token-block INT8 scales for Q and K with "
+                 "PV in bf16; the reference quantises Q and K per token, P to INT8 at the static "
+                 "scale 1/127 and V to INT8 per channel per key block, both products in integers "
+                 "(src/quantibbler/kernels/attention_sage.py:24-36,164-198,297-323).  Measured "
+                 "here: the reference's arithmetic, at BASELINE's shape.",
+    "prefill": "BASELINE config 1 calls rank 2560 at 4096<->14336 'roughly 0.55 bits/weight'; by "
+               "the reference's byte formula (src/quantibbler/qpk1.py:261-284) it is 0.81 "
+               "(0.55 would be rank ~1750).  Measured here: rank 2560 as BASELINE prescribes.",
+    "decode": "The reference's engine is single-GPU, batch 1, one token per call, with a float32 "
+              "KV cache (crates/quantibbler-server/src/engine/mod.rs:878-945); tensor "
+              "parallelism, batched decode and the bfloat16 cache are BASELINE's.  Ranks are the "
+              "reference's rank_for_target_bpw at 0.55 bits/weight.",
+}
+
 # ranks that give ~0.55 bits/weight by the reference's own byte formula
 # (src/quantibbler/qpk1.py:287-313, rank_for_target_bpw with float16 scales)
 C4_RANKS = {"q": 1102, "o": 1102, "k": 431, "v": 431, "gate": 1724, "up": 1724, "down": 1733}
 C3_RANKS = {"q": 1102, "k": 1102, "v": 1102, "o": 1102, "gate": 1614, "up": 1614, "down": 1622}
+
+
+def decode_config(model: str, n_layers: int, batch: int, max_seq: int, allreduce: str):
+    """DecoderConfig + ranks of BASELINE's config 4 ("llama3-8b") or config 3."""
+    from quantibbler_b200.decoder import DecoderConfig
+    if model == "llama3-8b":
+        return DecoderConfig(n_layers=n_layers or 32, d_model=4096, n_heads=32, n_kv_heads=8,
+                             head_dim=128, d_ff=14336, vocab=128256, rms_eps=1e-5,
+                             rope_theta=500000.0, serving="bfloat16", kv_dtype="bfloat16",
+                             max_seq=max_seq, max_batch=batch,
+                             fused_allreduce=allreduce == "fused"), C4_RANKS
+    return DecoderConfig(n_layers=n_layers or 1, d_model=4096, n_heads=32, n_kv_heads=32,
+                         head_dim=128, d_ff=11008, vocab=32000, rms_eps=1e-5, rope_theta=10000.0,
+                         serving="bfloat16", kv_dtype="bfloat16", max_seq=max_seq, max_batch=batch,
+                         fused_allreduce=allreduce == "fused"), C3_RANKS
+
+
+def weight_bytes_per_rank(dec) -> dict:
+    """Bytes of the model this rank streams per decode step (bits as served: one bit per
+    weight, rows padded to whole bytes; float32 scales; the bfloat16 head shard)."""
+    bits = scales = 0
+    for L in dec.layers:
+        for layer in L.values():
+            bits += layer.dout * ((layer.r + 7) // 8) + layer.r * ((layer.din + 7) // 8)
+            scales += 4 * (layer.dout + layer.din)
+    head = dec.lm_head.numel() * dec.lm_head.element_size()
+    return {"factor_bits": bits, "scales": scales, "lm_head": head, "total": bits + scales + head}
+
+
+def measure_decode(ctx, cfg, ranks, batch, ctx_len, steps, warmup, rank, world, group,
+                   share_from=None):
+    """Times `steps` replays of the captured decode step (CUDA events, max over ranks).
+    Returns (result dict, decoder)."""
+    import torch
+    import torch.distributed as dist
+
+    from quantibbler_b200.decoder import Decoder, random_model
+
+    weights = None if share_from is not None else random_model(cfg, ranks, seed=0,
+                                                               device_tables=True)
+    dec = Decoder(ctx, cfg, weights, tp_rank=rank, tp_size=world, group=group,
+                  share_from=share_from)
+    del weights
+    # the prompt's KV cache: synthetic N(0,1) rows stand in for a prefill pass
+    gen = torch.Generator(device="cuda").manual_seed(1 + rank)
+    for li in range(cfg.n_layers):
+        for cache in (dec.cache_k[li], dec.cache_v[li]):
+            cache[:, :, :ctx_len].copy_(torch.randn(cache[:, :, :ctx_len].shape, device="cuda",
+                                                    generator=gen).to(cache.dtype))
+    ids = torch.randint(0, cfg.vocab, (batch,), generator=torch.Generator().manual_seed(2)).tolist()
+    dec.capture()
+    dec.start(ids, [ctx_len] * batch)
+    launches0 = ctx.launch_count
+    dec.decode(max(warmup, 3))
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier(group=group)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        dec.graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        ms = float(t[0])
+    ctx.synchronize()   # reports a device-side wait that gave up
+    per_step = ms / steps
+    return {"tok_s": batch / (per_step * 1e-3), "ms_per_step": per_step, "batch": batch,
+            "context": ctx_len, "steps": steps,
+            "allreduce": ("none" if world == 1 else "fused" if dec.fused_ar else "nccl"),
+            "kernels_per_step": dec.kernels_per_step,
+            "weight_bytes_per_rank": weight_bytes_per_rank(dec)}, dec
+
+
+def measure_allreduce(dec, world, group, n_calls: int) -> float | None:
+    """Milliseconds that the step's all-reduces add: `n_calls` all-reduce + norm pairs as the
+    decoder issues them, timed on their own, minus the same number of plain norms."""
+    import torch
+    import torch.distributed as dist
+    if world == 1:
+        return None
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(n_calls // 2):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        return float(t[0])
+
+    w = dec.final_norm
+
+    def with_allreduce():
+        for pending, buf in ((0, dec.delta_attn), (1, dec.delta_mlp)):
+            dec._all_reduce(buf)
+            dec._norm(pending, w)
+
+    def plain():
+        for _ in range(2):
+            dec._norm(None, w)
+
+    return max(0.0, timed(with_allreduce) - timed(plain))
 
 
 def run_decode(args, rank: int, local_rank: int, world: int) -> None:
@@ -185,7 +318,6 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
     import torch
     import torch.distributed as dist
 
-    from quantibbler_b200.decoder import Decoder, DecoderConfig, random_model
     from quantibbler_b200.gpu import GpuContext
 
     torch.cuda.set_device(local_rank)
@@ -194,56 +326,18 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         group = dist.group.WORLD
     B, ctx_len = args.batch, args.context
-    if args.model == "llama3-8b":
-        cfg = DecoderConfig(n_layers=args.n_layers or 32, d_model=4096, n_heads=32, n_kv_heads=8,
-                            head_dim=128, d_ff=14336, vocab=128256, rms_eps=1e-5,
-                            rope_theta=500000.0, serving="bfloat16", kv_dtype="bfloat16",
-                            max_seq=ctx_len + args.steps + args.warmup + 8, max_batch=B,
-                            fused_allreduce=args.allreduce == "fused")
-        ranks = C4_RANKS
-    else:  # one Llama-2-7B-shaped layer (config 3)
-        cfg = DecoderConfig(n_layers=args.n_layers or 1, d_model=4096, n_heads=32, n_kv_heads=32,
-                            head_dim=128, d_ff=11008, vocab=32000, rms_eps=1e-5,
-                            rope_theta=10000.0, serving="bfloat16", kv_dtype="bfloat16",
-                            max_seq=ctx_len + args.steps + args.warmup + 8, max_batch=B,
-                            fused_allreduce=args.allreduce == "fused")
-        ranks = C3_RANKS
+    cfg, ranks = decode_config(args.model, args.n_layers, B,
+                               ctx_len + args.steps + max(args.warmup, 3) + 8, args.allreduce)
     ctx = GpuContext.init_at(local_rank)
-    weights = random_model(cfg, ranks, seed=0, device_tables=True)
-    dec = Decoder(ctx, cfg, weights, tp_rank=rank, tp_size=world, group=group)
-    del weights
-    # the prompt's KV cache: synthetic N(0,1) rows stand in for a prefill pass
-    gen = torch.Generator(device="cuda").manual_seed(1 + rank)
-    for li in range(cfg.n_layers):
-        for cache in (dec.cache_k[li], dec.cache_v[li]):
-            cache[:, :, :ctx_len].copy_(torch.randn(cache[:, :, :ctx_len].shape, device="cuda",
-                                                    generator=gen).to(cache.dtype))
-    ids = torch.randint(0, cfg.vocab, (B,), generator=torch.Generator().manual_seed(2)).tolist()
-    dec.capture()
-    dec.start(ids, [ctx_len] * B)
-    launches0 = ctx.launch_count
-    dec.decode(max(args.warmup, 3))
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(args.steps):
-        dec.graph.replay()
-    stop.record()
-    torch.cuda.synchronize()
-    ms = start.elapsed_time(stop)
-    if world > 1:
-        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t[0])
+    res, dec = measure_decode(ctx, cfg, ranks, B, ctx_len, args.steps, args.warmup, rank, world,
+                              group)
     if rank == 0:
-        per_step = ms / args.steps
         print(json.dumps({
-            "metric": "decode_tok_s", "value": B / (per_step * 1e-3), "unit": "tok/s",
+            "metric": "decode_tok_s", "value": res["tok_s"], "unit": "tok/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": per_step, "higher_is_better": True, "scaling": "strong",
+            "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "gpu_launches": res["kernels_per_step"] * args.steps,
             "config": {"workload": f"{args.model} shape, {cfg.n_layers} layers, all linears "
                                    f"binary-factorized at ~0.55 bpw, greedy decode, batch {B}, "
                                    f"context {ctx_len} (synthetic KV cache), one CUDA graph per step",
@@ -251,7 +345,9 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
                                       f"MLP block ("
                                       + ("summed over NVLink peer memory inside the RMSNorm kernel"
                                          if dec.fused_ar else "NCCL") + ")",
-                       "ranks": ranks}}), flush=True)
+                       "ranks": ranks, "weight_bytes_per_rank": res["weight_bytes_per_rank"],
+                       "divergences": DIVERGENCES["decode"]}}),
+              flush=True)
     if world > 1:
         # A captured graph still holds NCCL kernels; tearing the communicator down under it
         # can block at exit.  Everything is measured and printed: leave without the teardown.
@@ -259,6 +355,32 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
         torch.cuda.synchronize()
         sys.stdout.flush()
         os._exit(0)
+
+
+def tp_decode_block(args, ctx, rank: int, world: int, group) -> dict:
+    """BASELINE config 4 measured in the same process group as the headline: the 32-layer
+    Llama-3-8B-shaped stack, tensor-parallel over the ranks, batch 1 and batch 64, context
+    2048 (a synthetic KV cache stands in for the prompt)."""
+    import torch
+    out = {"model": "llama3-8b shape: 32 layers, hidden 4096, 32 query / 8 KV heads of 128, "
+                    "MLP 14336, vocabulary 128256, bfloat16 serving and cache",
+           "ranks": C4_RANKS, "tp": world, "scaling": "strong",
+           "divergences": DIVERGENCES["decode"]}
+    ctx_len, steps = 2048, args.tp_steps
+    shared = None
+    for batch in (1, 64):
+        cfg, ranks = decode_config("llama3-8b", args.n_layers, batch, ctx_len + steps + 16,
+                                   args.allreduce)
+        res, dec = measure_decode(ctx, cfg, ranks, batch, ctx_len, steps, 3, rank, world, group,
+                                  share_from=shared)
+        res["allreduce_ms_per_step"] = measure_allreduce(dec, world, group, 2 * cfg.n_layers)
+        out[f"batch{batch}"] = res
+        if shared is None:
+            shared = dec
+        else:
+            del dec
+        torch.cuda.synchronize()
+    return out
 
 
 def run_prefill(args, local_rank: int) -> None:
@@ -337,7 +459,8 @@ def run_prefill(args, local_rank: int) -> None:
         "data": "synthetic",
         "config": {"workload": f"config1: gate, up 4096->14336 and down 14336->4096, r=2560, "
                                f"{T} tokens, bf16 operands, f32 accumulate, f32 in and out; "
-                               f"activations and results (705 MB) exceed L2"},
+                               f"activations and results (705 MB) exceed L2",
+                   "divergences": DIVERGENCES["prefill"]},
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s",
                      "frac": tf / peak, "traffic": None},
         "e2e": {"value": flop / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
@@ -413,7 +536,8 @@ def run_attention(args, local_rank: int) -> None:
                                f"{KV} KV heads, head_dim {D}, seq {S}, causal, key block {block}; "
                                f"quantisers + main kernel; q, k, v, out ({(2*H+2*KV)*S*D*4/1e6:.0f} MB) "
                                f"exceed L2",
-                   "exact_f32_face_ms": ms_exact, "sage_dp4a_kernel_ms": ms_dp4a},
+                   "exact_f32_face_ms": ms_exact, "sage_dp4a_kernel_ms": ms_dp4a,
+                   "divergences": DIVERGENCES["attention"]},
         "roofline": {"bound": "tensor", "achieved": tops, "peak": peak, "unit": "TOP/s",
                      "frac": tops / peak, "traffic": None,
                      "note": "peak = 2 x measured dense bf16 (the INT8 tensor rate); the kernel "
@@ -443,6 +567,14 @@ def main() -> None:
     ap.add_argument("--n-layers", type=int, default=0)
     ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
                     help="decode workload under tensor parallelism")
+    ap.add_argument("--tp-decode", type=int, default=1,
+                    help="append the config-4 tensor-parallel decode block to the default line")
+    ap.add_argument("--tp-steps", type=int, default=20, help="timed decode steps of that block")
+    ap.add_argument("--tp-timeout", type=float, default=420.0,
+                    help="seconds after which the tensor-parallel block is given up")
+    ap.add_argument("--repeats", type=int, default=4, help="extra timed regions (reported)")
+    ap.add_argument("--check", type=int, default=1,
+                    help="compare sampled outputs of the timed launch with the CPU oracle")
     args = ap.parse_args()
 
     if args.shape:
@@ -486,8 +618,13 @@ def main() -> None:
     ctx.set_stream(stream.cuda_stream)
 
     L = args.layers
-    layers = [PackedLayer(ctx, ub, vbt, DOUT, DIN, RANK, s1, s2, None, serving="float32")
-              for ub, vbt, s1, s2 in make_stack(L, seed=1000 + rank)]
+    check_at = sorted({0, 1, L // 3, L // 2, L - 2, L - 1} & set(range(L)))  # layers checked later
+    kept = {}
+    layers = []
+    for i, (ub, vbt, s1, s2) in enumerate(make_stack(L, seed=1000 + rank)):
+        layers.append(PackedLayer(ctx, ub, vbt, DOUT, DIN, RANK, s1, s2, None, serving="float32"))
+        if i in check_at:
+            kept[i] = (ub, vbt, s1, s2)
     rng = np.random.default_rng(77 + rank)
     x_host = torch.from_numpy(rng.standard_normal((L, DIN)).astype(np.float32)).pin_memory()
     y_host = torch.empty((L, DOUT), dtype=torch.float32).pin_memory()
@@ -527,6 +664,32 @@ def main() -> None:
                     step()
                 torch.cuda.synchronize()
         elapsed_ms = start.elapsed_time(stop)
+        # the same K steps a few more times: how much one timed region differs from the next
+        repeats = []
+        for _ in range(args.repeats):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(args.steps):
+                step()
+            b.record(stream)
+            torch.cuda.synchronize()
+            repeats.append(a.elapsed_time(b) / args.steps)
+        # outside every timed region: what the timed launch computed, against the CPU oracle
+        parity = None
+        if rank == 0 and args.check:
+            import oracle
+            y_now = y_dev.cpu().numpy()
+            worst, identical = 0.0, 0.0
+            for i in check_at:
+                ub, vbt, s1, s2 = kept[i]
+                want = oracle.layer_apply(ub, vbt, DOUT, DIN, RANK, s1, s2, None,
+                                          x_host[i].numpy(), serving="float32")
+                worst = max(worst, float(np.abs(y_now[i] - want).max() / np.abs(want).max()))
+                identical += float(np.mean(y_now[i] == want)) / len(check_at)
+            parity = {"layers": len(check_at), "max_rel": worst, "bit_identical_frac": identical,
+                      "gate": 2e-5, "ok": bool(worst <= 2e-5),
+                      "against": "oracle.layer_apply (C restatement of core.rs + engine/mod.rs "
+                                 "apply, float32 serving) on the outputs of the timed launch"}
 
         # end-to-end, the step with HOST buffers: all inputs of the step go up from pinned
         # memory, the same launches run, all outputs come back, then a synchronisation
@@ -614,11 +777,49 @@ def main() -> None:
             "clocks": dict(clocks.summary(),
                            window="timed region plus an untimed continuation of the same step"),
         }
+        line["parity_checked"] = parity
+        line["timing"] = {"repeat_ms_per_step": repeats,
+                          "note": f"{args.repeats} further regions of {args.steps} steps each, "
+                                  f"after the region `value` is computed from"}
         if world == 1 and args.cpu_seconds > 0:
             line["cpu_baseline"] = cpu_baseline(args.cpu_seconds)
-        print(json.dumps(line))
+    # BASELINE's second metric half: config-4 decode under tensor parallelism, in this same
+    # process group, so that a run at N GPUs carries the N-rank number
+    tp_block = None
+    if args.tp_decode:
+        # A rank that fails inside the block would leave the others waiting in a collective:
+        # after --tp-timeout seconds every rank leaves, rank 0 with the headline line printed.
+        def bail():
+            if rank == 0:
+                line["tp_decode"] = {"error": f"no result within {args.tp_timeout} s"}
+                print(json.dumps(line), flush=True)
+            os._exit(0)
+        watchdog = threading.Timer(args.tp_timeout, bail)
+        watchdog.daemon = True
+        watchdog.start()
+        # free the stack first: the decoder needs the memory bandwidth to itself
+        group.close()
+        for layer in layers:
+            layer.close()
+        del layers, x_dev, y_dev
+        torch.cuda.empty_cache()
+        ctx.set_stream(None)
+        try:
+            tp_block = tp_decode_block(args, ctx, rank, world,
+                                       dist.group.WORLD if world > 1 else None)
+        except Exception as e:  # noqa: BLE001  (the headline line must still print)
+            tp_block = {"error": f"{type(e).__name__}: {e}"}
+        watchdog.cancel()
+    if rank == 0:
+        if tp_block is not None:
+            line["tp_decode"] = tp_block
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # captured graphs still hold NCCL kernels; leave without the communicator teardown
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

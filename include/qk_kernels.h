@@ -347,9 +347,11 @@ qk_status qk_argmax_first(qk_ctx *ctx, const float *logits, size_t n_tokens, siz
                           size_t logits_stride, int32_t index_base, float *out_val,
                           int32_t *out_idx);
 
-/* Which GEMV kernel qk_layer_apply uses: 0 = sign-select SIMT, 1 = bit-sliced INT8
- * tensor-core (default), 2 = the same with 16-warp fused blocks, 3 = the same without the split-k form,
- * 4 = the same with 4-warp fused blocks (a measurement variant).  Returns the previous value; values out of range leave it unchanged. */
+/* Which GEMV kernel qk_layer_apply and the group calls use: 0 = sign-select SIMT, 1 = bit-sliced
+ * INT8 tensor-core (default; many instances per launch run in the persistent streaming form),
+ * 3 = the same without the split-k form, 5 = the same with one block per instance instead of
+ * the streaming form, 2 and 4 = as 5 with 16-warp resp. 4-warp blocks (measurement variants).
+ * Returns the previous value; values out of range leave it unchanged. */
 int32_t qk_set_gemv_kernel(qk_ctx *ctx, int32_t which);
 /* How many polls a device-side wait of this context's kernels (the prefill GEMM's pipeline
  * barriers and split-tile flags, the fused all-reduce's inbox) makes before it gives up and

@@ -173,10 +173,11 @@ qk_status qk_gpu_synchronize(qk_ctx *ctx) {
                 return qk::fail(QK_ERR_VALUE,
                                 "a token's position or sequence index lies outside the KV cache; "
                                 "the token was skipped");
-            return qk::fail(QK_ERR_TIMEOUT, "a bounded device-side wait gave up:%s%s",
+            return qk::fail(QK_ERR_TIMEOUT, "a bounded device-side wait gave up:%s%s%s",
                             (h_err & 1) ? " a pipeline barrier of the tensor-core prefill;" : "",
                             (h_err & 2) ? " the inbox of a fused all-reduce (a peer did not send);"
-                                        : "");
+                                        : "",
+                            (h_err & 8) ? " a ring or table barrier of the streaming GEMV;" : "");
         }
     }
     return QK_OK;
@@ -192,7 +193,7 @@ int32_t qk_set_gemv_kernel(qk_ctx *ctx, int32_t which) {
     qk_ctx *c;
     if (qk::resolve_ctx(ctx, &c) != QK_OK) return -1;
     int prev = c->gemv_kernel;
-    if (which >= 0 && which <= 4) c->gemv_kernel = which;
+    if (which >= 0 && which <= 5) c->gemv_kernel = which;
     return prev;
 }
 

@@ -664,6 +664,432 @@ layer_bitslice_fused_kernel(const StageParams *__restrict__ stage1,
                                                         groups2, steps2, 0, gpw2, true);
 }
 
+// ------------------------------------------------------------------ persistent streaming form
+// Many independent layer instances per launch (a stack of layers, or one layer for many
+// requests): one CTA per SM stays resident and walks over its share of the instances with
+// three kinds of warps, so that the stream of weight bits from HBM never stops for a layer
+// boundary, a table build or a stage boundary.
+//   * consumer warps (16): the mask-and-MMA loop of bitslice_stage and nothing else.  A warp
+//     owns whole row groups; it takes its 4 KB chunks from a ring in shared memory that is
+//     shared by all warps.
+//   * one producer warp: keeps the ring full with one bulk copy (cp.async.bulk, completing on
+//     an mbarrier) per chunk, in exactly the order in which the consumers will ask for
+//     them.  It runs ahead across stage and layer boundaries, because the order of the chunks
+//     does not depend on any data.
+//   * builder warps (4): turn the input vector of the NEXT instance into its digit table
+//     while the consumers stream the current one, and turn t into the second table as soon
+//     as the consumers have finished stage 1.
+// The stages are software-pipelined over the instances, J1(0) J1(1) J2(0) J1(2) J2(1) ...,
+// so that a whole stage of other work lies between the end of J1(i) (t complete) and the
+// start of J2(i) (which needs the table made from t): nobody waits in the steady state.
+// Two table buffers per stage and two t buffers suffice; their reuse is ordered by the
+// barriers themselves (see the notes at the waits).  Every wait is bounded: a role that runs
+// out of polls raises the CTA's abort flag, every other role sees it in its own wait, all
+// leave, and the launch reports bit 8 of the context's error word.
+constexpr int kPsConsumers = 16;
+constexpr int kPsBuilders = 4;
+constexpr int kPsProducerWarp = kPsConsumers;
+constexpr int kPsBuilderWarp0 = kPsConsumers + 1;
+constexpr int kPsThreads = (kPsConsumers + 1 + kPsBuilders) * 32;
+constexpr int kPsMinSlots = 24, kPsMaxSlots = 40;
+constexpr uint32_t kPsWaitLimitDefault = 1u << 22;
+
+struct PsArgs {
+    const StageParams *stage1, *stage2;  // [n_inst] each
+    uint32_t n_inst;
+    uint32_t r, din, dout;
+    uint32_t slots;        // ring depth in 4 KB chunks
+    uint32_t wait_limit;
+    int *error;
+};
+
+__device__ __forceinline__ uint32_t ps_smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void ps_mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(ps_smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void ps_mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ps_smem_u32(bar)) : "memory");
+}
+// One lane's bounded wait; false when the polls ran out or another role gave up.
+__device__ __forceinline__ bool ps_wait_lane(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                             uint32_t limit) {
+    const uint32_t addr = ps_smem_u32(bar);
+    for (uint32_t i = 0; i < limit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            " selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((i & 63u) == 63u && *abort_flag) return false;
+    }
+    return false;
+}
+// The warp's verdict (all 32 lanes call it): every lane has either seen the phase or run out.
+__device__ __forceinline__ bool ps_wait_warp(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                             uint32_t limit) {
+    return __all_sync(0xffffffffu, ps_wait_lane(bar, parity, abort_flag, limit)) != 0;
+}
+
+// Digit table of one stage's input, built by the 128 builder threads (tid 0..127).
+//   input(k): element k as float64 (zero beyond the vector).  red: 4 doubles, 4 long longs and
+//   an int of shared memory for the group's reductions; named barrier 2 keeps the group in step.
+template <typename Input>
+__device__ __forceinline__ void ps_build_table(Input input, uint32_t n_steps, uint4 *table,
+                                               StageMeta *meta_out, double *red_max,
+                                               long long *red_sum, int *red_bad, uint32_t tid) {
+    constexpr uint32_t kGroupThreads = kPsBuilders * 32;
+    const uint32_t warp = tid / 32, lane = tid % 32;
+    const uint32_t n_records = n_steps * 64;
+    auto record_entry = [&](uint32_t r, int e) -> double {
+        const uint32_t ks = r / 64, rec = r % 64;
+        const uint32_t tt = rec % 4, ip = (rec / 4) % 4, qw = rec / 16;
+        return input(ks * kStepBits + 128 * tt + 32 * qw + 8 * (e % 4) + 2 * ip + e / 4);
+    };
+    double mx = 0.0;
+    int bad = 0;
+    for (uint32_t r = tid; r < n_records; r += kGroupThreads)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const double a = fabs(record_entry(r, e));
+            if (!(a <= 1.7e308)) bad = 1;  // NaN or infinity
+            mx = fmax(mx, a);
+        }
+    for (int off = 16; off > 0; off >>= 1) {
+        mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        bad |= __shfl_xor_sync(0xffffffffu, bad, off);
+    }
+    if (lane == 0) {
+        red_max[warp] = mx;
+        red_bad[warp] = bad;
+    }
+    asm volatile("bar.sync 2, %0;" ::"r"(kGroupThreads) : "memory");
+    double m = red_max[0];
+    int nonfinite = red_bad[0];
+#pragma unroll
+    for (int w = 1; w < kPsBuilders; ++w) {
+        m = fmax(m, red_max[w]);
+        nonfinite |= red_bad[w];
+    }
+    const FixedPoint fp = fixed_point_of(nonfinite ? 0.0 : m);
+    long long total = 0;
+    for (uint32_t r = tid; r < n_records; r += kGroupThreads) {
+        long long q8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            q8[e] = nonfinite ? 0 : fp.quant(record_entry(r, e));
+            total += q8[e];
+        }
+        build_record(q8, (r % 64 / 4) % 4, table + (size_t)r * 4);
+    }
+    for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+    if (lane == 0) red_sum[warp] = total;
+    asm volatile("bar.sync 2, %0;" ::"r"(kGroupThreads) : "memory");
+    if (tid == 0) {
+        long long sum = 0;
+#pragma unroll
+        for (int w = 0; w < kPsBuilders; ++w) sum += red_sum[w];
+        meta_out->total = sum;
+        meta_out->shift = fp.shift;
+        meta_out->nonfinite = nonfinite;
+    }
+    // (the caller's arrival on the table's barrier publishes table and meta)
+}
+
+// The consumer's work on one row group of one stage: n_steps chunks from the ring.
+//   seq0 + ks * stride: the position of the group's ks-th chunk in the producer's order.
+template <bool kRoundBf16, bool kFinal>
+__device__ __forceinline__ bool
+ps_consume_group(const StageParams &p, const uint8_t *ring_smem, uint64_t *full, uint64_t *empty,
+                 uint32_t slots, const uint2 *table, const StageMeta &meta, double *out_smem,
+                 uint32_t n_rows, uint32_t n_steps, uint32_t group, uint32_t seq0, uint32_t stride,
+                 volatile int *abort_flag, uint32_t limit) {
+    const uint32_t lane = threadIdx.x % 32, g = lane / 4, t = lane % 4;
+    int acc[kTilesPerWarp][4];
+#pragma unroll
+    for (int m = 0; m < kTilesPerWarp; ++m)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[m][e] = 0;
+    const uint2 *dig = table + t * 8 + g;
+    for (uint32_t ks = 0; ks < n_steps; ++ks) {
+        const uint32_t n = seq0 + ks * stride, slot = n % slots;
+        if (!ps_wait_warp(&full[slot], (n / slots) & 1, abort_flag, limit)) return false;
+        const uint4 *stage = reinterpret_cast<const uint4 *>(ring_smem + (size_t)slot * kChunkBytes) + lane;
+        uint4 cur[kTilesPerWarp][2];
+#pragma unroll
+        for (int m = 0; m < kTilesPerWarp; ++m) {
+            cur[m][0] = stage[m * 64];
+            cur[m][1] = stage[m * 64 + 32];
+        }
+        // the chunk is in registers: hand the slot back to the producer right away
+        __syncwarp();
+        if (lane == 0) ps_mbar_arrive(&empty[slot]);
+        const uint2 *dk = dig + (size_t)ks * 512;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+            for (int ip = 0; ip < 4; ++ip) {
+                const uint2 b = dk[(q * 4 + ip) * 32];
+                const uint32_t m0 = 0x01010101u << (2 * ip), m1 = m0 << 1;
+#pragma unroll
+                for (int m = 0; m < kTilesPerWarp; ++m) {
+                    const uint32_t wg = q == 0 ? cur[m][0].x : q == 1 ? cur[m][0].y
+                                      : q == 2 ? cur[m][0].z : cur[m][0].w;
+                    const uint32_t wh = q == 0 ? cur[m][1].x : q == 1 ? cur[m][1].y
+                                      : q == 2 ? cur[m][1].z : cur[m][1].w;
+                    mma_u8s8(acc[m], wg & m0, wh & m0, wg & m1, wh & m1, b.x, b.y);
+                }
+            }
+        }
+    }
+    // ---- exact recombination (see bitslice_stage): X = sum_n c_n 256^n = 128 S, value =
+    // (X - 64 T) / 64 * 2^-shift with X = hi 2^32 + lo and 64 T = th 2^32 + tl.  Two tiles are
+    // finished at a time: lanes t = 0,1 take the rows of the first, lanes t = 2,3 those of
+    // the second, so every lane converts one row and the exchange needs three shuffles of a
+    // 64-bit value per tile instead of four.
+    const long long th = meta.total >> 26;
+    const long long tl = (meta.total & ((1ll << 26) - 1)) << 6;
+    const int sh0 = 16 * (t & 1);
+    const int oexp = -meta.shift - 6;
+    const bool odirect = oexp > -1000 && oexp < 1000;
+    const double oscale = odirect ? __hiloint2double((1023 + oexp) << 20, 0) : 0.0;
+#pragma unroll
+    for (int pair = 0; pair < kTilesPerWarp / 2; ++pair) {
+        long long pg[2], ph[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int(&a)[4] = acc[2 * pair + k];
+            pg[k] = ((long long)a[0] << sh0) + ((long long)a[1] << (sh0 + 8));
+            ph[k] = ((long long)a[2] << sh0) + ((long long)a[3] << (sh0 + 8));
+            pg[k] += __shfl_xor_sync(0xffffffffu, pg[k], 1);  // t=0,1: low half; t=2,3: high half
+            ph[k] += __shfl_xor_sync(0xffffffffu, ph[k], 1);
+        }
+        // lanes t<2 keep tile 2*pair (they hold its low half and need the high half from t+2);
+        // lanes t>=2 keep tile 2*pair+1 (they hold its high half and need the low half)
+        const bool first = t < 2;
+        const long long send_g = first ? pg[1] : pg[0], send_h = first ? ph[1] : ph[0];
+        const long long other_g = __shfl_xor_sync(0xffffffffu, send_g, 2);
+        const long long other_h = __shfl_xor_sync(0xffffffffu, send_h, 2);
+        const long long mine_g = first ? pg[0] : pg[1], mine_h = first ? ph[0] : ph[1];
+        // row g (t even) or g + 8 (t odd) of the lane's tile
+        const bool upper = (t & 1) != 0;
+        const long long lo = first ? (upper ? mine_h : mine_g) : (upper ? other_h : other_g);
+        const long long hi = first ? (upper ? other_h : other_g) : (upper ? mine_h : mine_g);
+        const int m = 2 * pair + (first ? 0 : 1);
+        const uint32_t row = group * kGroupRows + m * kTileRows + g + (upper ? 8 : 0);
+        if (row < n_rows) {
+            double val = (double)(hi - th) * 4294967296.0 + (double)(lo - tl);
+            val = odirect ? val * oscale : ldexp(val, oexp);
+            if (meta.nonfinite) val = nan("");
+            if (kRoundBf16) val = (double)round_bf16((float)val);
+            if (kFinal) {
+                float y = (float)val;
+                if (p.out_scale) y = y * p.out_scale[row];
+                if (p.out_bias) y = y + p.out_bias[row];
+                static_cast<float *>(p.out)[row] = y;
+            } else {
+                out_smem[row] = val;
+            }
+        }
+    }
+    return true;
+}
+
+template <bool kRoundBf16>
+__global__ void __launch_bounds__(kPsThreads, 1)
+layer_stream_kernel(const PsArgs a, uint32_t t_bytes, uint32_t table1_bytes, uint32_t table2_bytes) {
+    extern __shared__ __align__(128) uint8_t smem_dyn[];
+    // [ring][table1 x2][table2 x2][t x2][meta x4][barriers][reduction scratch][abort flag]
+    uint8_t *ring = smem_dyn;
+    uint8_t *table1 = ring + (size_t)a.slots * kChunkBytes;
+    uint8_t *table2 = table1 + 2 * (size_t)table1_bytes;
+    uint8_t *t_base = table2 + 2 * (size_t)table2_bytes;
+    StageMeta *meta = reinterpret_cast<StageMeta *>(t_base + 2 * (size_t)t_bytes);  // [stage][buffer]
+    uint64_t *full = reinterpret_cast<uint64_t *>(meta + 4);
+    uint64_t *empty = full + a.slots;
+    uint64_t *t1_full = empty + a.slots;  // [2] table of stage 1, buffer b, is ready
+    uint64_t *tt_full = t1_full + 2;      // [2] t buffer b is complete
+    uint64_t *t2_full = tt_full + 2;      // [2] table of stage 2, buffer b, is ready
+    double *red_max = reinterpret_cast<double *>(t2_full + 2);
+    long long *red_sum = reinterpret_cast<long long *>(red_max + kPsBuilders);
+    int *red_bad = reinterpret_cast<int *>(red_sum + kPsBuilders);
+    volatile int *abort_flag = red_bad + kPsBuilders;
+
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t limit = a.wait_limit;
+    // this CTA's instances: blockIdx.x, blockIdx.x + gridDim.x, ...
+    const uint32_t n_mine = a.n_inst > blockIdx.x ? (a.n_inst - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t groups1 = (a.r + kGroupRows - 1) / kGroupRows, steps1 = (a.din + kStepBits - 1) / kStepBits;
+    const uint32_t groups2 = (a.dout + kGroupRows - 1) / kGroupRows, steps2 = (a.r + kStepBits - 1) / kStepBits;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < a.slots; ++s) {
+            ps_mbar_init(&full[s], 1);   // the producer's arrive.expect_tx
+            ps_mbar_init(&empty[s], 1);  // the consuming warp's lane 0
+        }
+        for (int b = 0; b < 2; ++b) {
+            ps_mbar_init(&t1_full[b], kPsBuilders);
+            ps_mbar_init(&tt_full[b], kPsConsumers);
+            ps_mbar_init(&t2_full[b], kPsBuilders);
+        }
+        abort_flag[0] = 0;
+        abort_flag[1] = 0;  // stays zero: the flag of waits that must not be cut short
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // The order of the jobs, the same in every role: step s = 0 .. n_mine runs J1(s) (if
+    // s < n_mine) and then J2(s - 1) (if s >= 1).
+    if (warp < kPsConsumers) {
+        // ------------------------------------------------------------ consumers
+        uint32_t seq = 0;  // chunks of all rounds before the current one
+        bool ok = true;
+        for (uint32_t s = 0; s <= n_mine && ok; ++s) {
+#pragma unroll 1
+            for (int stage = 0; stage < 2 && ok; ++stage) {
+                if (stage == 0 ? s >= n_mine : s == 0) continue;
+                const uint32_t i = stage == 0 ? s : s - 1, b = i & 1, use = i >> 1;
+                const uint32_t inst = blockIdx.x + i * gridDim.x;
+                const StageParams p = stage == 0 ? a.stage1[inst] : a.stage2[inst];
+                const uint32_t n_groups = stage == 0 ? groups1 : groups2;
+                const uint32_t n_steps = stage == 0 ? steps1 : steps2;
+                // the table of this job (built a whole stage ago in the steady state)
+                if (!ps_wait_warp(stage == 0 ? &t1_full[b] : &t2_full[b], use & 1, abort_flag, limit)) {
+                    ok = false;
+                    break;
+                }
+                const StageMeta mt = meta[stage * 2 + b];
+                const uint2 *table = reinterpret_cast<const uint2 *>(
+                    stage == 0 ? table1 + (size_t)b * table1_bytes : table2 + (size_t)b * table2_bytes);
+                double *t_buf = reinterpret_cast<double *>(t_base + (size_t)b * t_bytes);
+                for (uint32_t g0 = 0; g0 < n_groups && ok; g0 += kPsConsumers) {
+                    const uint32_t active = min((uint32_t)kPsConsumers, n_groups - g0);
+                    if (warp < active) {
+                        if (stage == 0)
+                            ok = ps_consume_group<kRoundBf16, false>(
+                                p, ring, full, empty, a.slots, table, mt, t_buf, a.r, n_steps, g0 + warp,
+                                seq + warp, active, abort_flag, limit);
+                        else
+                            ok = ps_consume_group<kRoundBf16, true>(
+                                p, ring, full, empty, a.slots, table, mt, nullptr, a.dout, n_steps,
+                                g0 + warp, seq + warp, active, abort_flag, limit);
+                    }
+                    seq += active * n_steps;
+                }
+                if (stage == 0 && ok) {
+                    // this warp's rows of t are written: tell the builders (all 16 warps arrive)
+                    __syncwarp();
+                    if (lane == 0) ps_mbar_arrive(&tt_full[b]);
+                }
+            }
+        }
+        if (!ok) *abort_flag = 1;
+    } else if (warp == kPsProducerWarp) {
+        // ------------------------------------------------------------ producer
+        uint32_t n = 0;
+        bool ok = true;
+        for (uint32_t s = 0; s <= n_mine && ok; ++s) {
+#pragma unroll 1
+            for (int stage = 0; stage < 2 && ok; ++stage) {
+                if (stage == 0 ? s >= n_mine : s == 0) continue;
+                const uint32_t i = stage == 0 ? s : s - 1;
+                const uint32_t inst = blockIdx.x + i * gridDim.x;
+                const uint8_t *tiles = stage == 0 ? a.stage1[inst].w_tiles : a.stage2[inst].w_tiles;
+                const uint32_t n_groups = stage == 0 ? groups1 : groups2;
+                const uint32_t n_steps = stage == 0 ? steps1 : steps2;
+                for (uint32_t g0 = 0; g0 < n_groups && ok; g0 += kPsConsumers) {
+                    const uint32_t active = min((uint32_t)kPsConsumers, n_groups - g0);
+                    for (uint32_t ks = 0; ks < n_steps && ok; ++ks)
+                        for (uint32_t w = 0; w < active; ++w, ++n) {
+                            const uint32_t slot = n % a.slots;
+                            // the slot's previous chunk (number n - slots) must have been taken
+                            if (n >= a.slots &&
+                                !ps_wait_warp(&empty[slot], ((n / a.slots) - 1) & 1, abort_flag, limit)) {
+                                ok = false;
+                                break;
+                            }
+                            if (lane == 0) {
+                                const uint32_t dst = ps_smem_u32(ring + (size_t)slot * kChunkBytes);
+                                const uint32_t bar = ps_smem_u32(&full[slot]);
+                                const uint8_t *src = tiles + ((size_t)(g0 + w) * n_steps + ks) * kChunkBytes;
+                                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                                             "r"((uint32_t)kChunkBytes)
+                                             : "memory");
+                                asm volatile(
+                                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes "
+                                    "[%0], [%1], %2, [%3];" ::"r"(dst),
+                                    "l"(src), "r"((uint32_t)kChunkBytes), "r"(bar)
+                                    : "memory");
+                            }
+                            __syncwarp();
+                        }
+                }
+            }
+        }
+        if (!ok) {
+            *abort_flag = 1;
+            // copies in flight must land before the CTA's shared memory is given up: chunks
+            // n - slots .. n - 1 are the ones that may still be on their way
+            const uint32_t first = n > a.slots ? n - a.slots : 0;
+            for (uint32_t m = first; m < n; ++m)
+                ps_wait_warp(&full[m % a.slots], (m / a.slots) & 1, abort_flag + 1 /* never set */, limit);
+        }
+    } else {
+        // ------------------------------------------------------------ builders
+        const uint32_t tid = threadIdx.x - kPsBuilderWarp0 * 32;
+        auto build1 = [&](uint32_t i) {
+            const uint32_t b = i & 1;
+            const StageParams p = a.stage1[blockIdx.x + i * gridDim.x];
+            const uint32_t n_bits = a.din;
+            ps_build_table([&](uint32_t k) { return load_input<false, kRoundBf16>(p, k, n_bits); }, steps1,
+                           reinterpret_cast<uint4 *>(table1 + (size_t)b * table1_bytes), &meta[b], red_max,
+                           red_sum, red_bad, tid);
+            __syncwarp();
+            if (lane == 0) ps_mbar_arrive(&t1_full[b]);
+        };
+        bool ok = true;
+        // table1 buffer i&1 was last read by J1(i-2); J1(i-2) had finished before T2(i-2)
+        // started (tt_full), and T2(i-2) precedes T1(i) in this loop: no extra barrier.
+        if (n_mine > 0) build1(0);
+        for (uint32_t i = 0; i < n_mine && ok; ++i) {
+            if (i + 1 < n_mine) build1(i + 1);
+            const uint32_t b = i & 1;
+            // all consumers have written their rows of t(i) ...
+            bool seen = ps_wait_warp(&tt_full[b], (i >> 1) & 1, abort_flag, limit);
+            // ... and the four builder warps agree on it before any of them meets the others
+            // at the group's barrier inside the build
+            uint32_t all;
+            asm volatile(
+                "{\n .reg .pred p, q;\n setp.ne.b32 p, %1, 0;\n"
+                " barrier.cta.red.and.pred q, 3, %2, p;\n selp.u32 %0, 1, 0, q;\n}"
+                : "=r"(all)
+                : "r"((uint32_t)seen), "r"((uint32_t)(kPsBuilders * 32))
+                : "memory");
+            if (!all) {
+                ok = false;
+                break;
+            }
+            // table2 buffer b was last read by J2(i-2), which every consumer had finished
+            // before it began J1(i); t buffer b is next written by J1(i+2), which follows J2(i),
+            // and J2(i) starts only after this build has arrived on t2_full.
+            const double *t_in = reinterpret_cast<const double *>(t_base + (size_t)b * t_bytes);
+            const uint32_t n_bits = a.r;
+            ps_build_table([&](uint32_t k) { return k < n_bits ? t_in[k] : 0.0; }, steps2,
+                           reinterpret_cast<uint4 *>(table2 + (size_t)b * table2_bytes), &meta[2 + b],
+                           red_max, red_sum, red_bad, tid);
+            __syncwarp();
+            if (lane == 0) ps_mbar_arrive(&t2_full[b]);
+        }
+        if (!ok) *abort_flag = 1;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(a.error, 8);
+}
+
 // ------------------------------------------------------------------ layer construction
 // Copy host-layout rows (row_words bytes each) into 16-byte padded rows, clearing the
 // pad bits of the last byte.
@@ -839,6 +1265,29 @@ bool fused_plan(const qk_ctx *c, const StageShape &s1, const StageShape &s2, siz
     return false;
 }
 
+// The persistent streaming form applies when every SM gets at least one instance and the
+// two double-buffered tables, the two t buffers and a ring of at least kPsMinSlots chunks fit
+// in shared memory together.
+constexpr size_t kPsSmemBudget = 227 * 1024;
+struct PsPlan {
+    size_t grid, slots, t_bytes, table1_bytes, table2_bytes, smem;
+};
+bool stream_plan(const qk_ctx *c, const StageShape &s1, const StageShape &s2, size_t n_inst,
+                 PsPlan *pl) {
+    if (n_inst < (size_t)c->sm_count) return false;
+    pl->grid = (size_t)c->sm_count;
+    pl->t_bytes = qk::ceil_div(s1.n_rows * sizeof(double), 128) * 128;
+    pl->table1_bytes = s1.n_steps * 4096;
+    pl->table2_bytes = s2.n_steps * 4096;
+    const size_t fixed = 2 * (pl->table1_bytes + pl->table2_bytes + pl->t_bytes) + 4 * sizeof(StageMeta) +
+                         6 * 8 + kPsBuilders * (8 + 8 + 4) + 16;
+    if (fixed + kPsMinSlots * (kChunkBytes + 16) > kPsSmemBudget) return false;
+    pl->slots = (kPsSmemBudget - fixed) / (kChunkBytes + 16);  // a chunk and its two barriers
+    if (pl->slots > (size_t)kPsMaxSlots) pl->slots = kPsMaxSlots;
+    pl->smem = fixed + pl->slots * (kChunkBytes + 16);
+    return true;
+}
+
 // Scratch one instance needs besides its inputs and outputs.
 struct InstanceScratch {
     size_t t_bytes, dig1_bytes, dig2_bytes, meta_bytes, total;
@@ -908,6 +1357,27 @@ qk_status launch_both(qk_ctx *c, const qk_layer *l0, const StageParams *d, size_
                             l0->din > l0->r ? l0->din : l0->r);
         if ((st = launch_signselect(c, d, n_inst, s1, bf16)) != QK_OK) return st;
         return launch_signselect(c, d + n_inst, n_inst, s2, bf16);
+    }
+    // Many instances: the persistent streaming form (selectors 2, 4 and 5 keep the one-block-
+    // per-instance form for comparison).
+    if (kernel == 1 || kernel == 3) {
+        PsPlan ps;
+        if (stream_plan(c, s1, s2, n_inst, &ps)) {
+            qk_status e = qk::error_word(c);
+            if (e != QK_OK) return e;
+            PsArgs a{d, d + n_inst, (uint32_t)n_inst, (uint32_t)l0->r, (uint32_t)l0->din,
+                     (uint32_t)l0->dout, (uint32_t)ps.slots,
+                     c->wait_limit ? c->wait_limit : kPsWaitLimitDefault, (int *)c->d_err.ptr};
+            auto kern = bf16 ? layer_stream_kernel<true> : layer_stream_kernel<false>;
+            QK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kPsSmemBudget));
+            kern<<<(unsigned)ps.grid, kPsThreads, ps.smem, c->stream>>>(
+                a, (uint32_t)ps.t_bytes, (uint32_t)ps.table1_bytes, (uint32_t)ps.table2_bytes);
+            QK_CUDA(cudaGetLastError());
+            c->launches++;
+            c->err_armed = true;
+            return QK_OK;
+        }
     }
     size_t warps, t_bytes, table_bytes, smem;
     if (fused_plan(c, s1, s2, n_inst, &warps, &t_bytes, &table_bytes, &smem)) {
@@ -1291,8 +1761,6 @@ extern "C" {
 qk_status qk_layer_apply_noalloc(qk_ctx *ctx, const qk_layer *layer, const float *x_dev,
                                  float *y_dev) {
     if (!layer) return qk::fail(QK_ERR_VALUE, "qk_layer_apply_noalloc: layer is null");
-    if (!x_dev || !y_dev)
-        return qk::fail(QK_ERR_VALUE, "qk_layer_apply_noalloc: x_dev and y_dev must not be null");
     if (!ctx)
         return qk::fail(QK_ERR_VALUE,
                         "qk_layer_apply_noalloc needs an existing context: creating the default "
@@ -1303,6 +1771,8 @@ qk_status qk_layer_apply_noalloc(qk_ctx *ctx, const qk_layer *layer, const float
                         "layer (din=%zu, r=%zu) exceeds the built-in scratch: the allocation-free "
                         "apply supports r <= %zu and din <= %zu; use qk_layer_apply",
                         layer->din, layer->r, kNoAllocMaxRank, kNoAllocMaxWidth);
+    if (!x_dev || !y_dev)
+        return qk::fail(QK_ERR_VALUE, "qk_layer_apply_noalloc: x_dev and y_dev must not be null");
     qk_ctx *c = ctx;
     std::lock_guard<std::mutex> lock(c->mu);
     QK_CUDA(cudaSetDevice(c->device));

@@ -129,12 +129,19 @@ def _p(t) -> ctypes.c_void_p:
 class Decoder:
     """Batched greedy decode on one GPU (one tensor-parallel rank)."""
 
-    def __init__(self, ctx: GpuContext, cfg: DecoderConfig, weights: dict, tp_rank: int = 0,
-                 tp_size: int = 1, group=None):
+    def __init__(self, ctx: GpuContext, cfg: DecoderConfig, weights: dict | None, tp_rank: int = 0,
+                 tp_size: int = 1, group=None, share_from: "Decoder | None" = None):
+        """``share_from``: another decoder of the same model and tensor-parallel rank (it may
+        differ in ``max_batch`` and ``max_seq``) whose device-resident weights this one uses
+        instead of uploading its own; ``weights`` may then be None."""
         import torch
         self.torch, self.ctx, self.cfg = torch, ctx, cfg
         self.tp_rank, self.tp_size, self.group = tp_rank, tp_size, group
-        w = tp.shard_model(weights, cfg, tp_rank, tp_size)
+        if share_from is not None:
+            w = {"layers": [dict() for _ in range(cfg.n_layers)],
+                 "vocab_offset": share_from.vocab_offset}
+        else:
+            w = tp.shard_model(weights, cfg, tp_rank, tp_size)
         self.vocab_offset = int(w.get("vocab_offset", 0))
         dev = torch.device("cuda", torch.cuda.current_device())
         ctx.set_stream(torch.cuda.current_stream().cuda_stream)  # order with torch's own work
@@ -166,7 +173,8 @@ class Decoder:
         self.attn = torch.zeros(B, self.h_loc * hd, **f32)
         # per-head q/k norms (one head_dim vector each, engine/mod.rs:854-873) write here; the
         # RoPE and the attention then read these instead of the projections' outputs
-        self.has_qk_norm = any("q_norm" in lw and "k_norm" in lw for lw in w["layers"])
+        self.has_qk_norm = (share_from.has_qk_norm if share_from is not None else
+                            any("q_norm" in lw and "k_norm" in lw for lw in w["layers"]))
         self.qn = torch.zeros(B, self.h_loc * hd, **f32) if self.has_qk_norm else self.q
         self.kn = torch.zeros(B, self.kv_loc * hd, **f32) if self.has_qk_norm else self.k
         # o / down outputs (one partial per rank under TP).  With the fused all-reduce the two
@@ -202,25 +210,38 @@ class Decoder:
         scratch = _lib.lib().qk_decode_attention_scratch(B, self.h_loc, hd, self.n_splits)
         self.att_scratch = torch.zeros(scratch // 4 + 4, **f32)
         self.cos_sin = dev_f32(rope_table(cfg))
-        self.embedding = dev_bf16(w["embedding"]) if cfg.serving == "bfloat16" else dev_f32(
-            w["embedding"])
         self.emb_tag = QK_BF16 if cfg.serving == "bfloat16" else QK_F32
-        # the LM head is stored in bfloat16 (BASELINE config 4) unless serving is float32
-        self.lm_head = dev_bf16(w["lm_head"]) if cfg.serving == "bfloat16" else dev_f32(
-            w["lm_head"])
-        self.final_norm = dev_f32(w["final_norm"])
+        if share_from is not None:
+            o = share_from
+            if (o.cfg.serving, o.tp_rank, o.tp_size, o.cfg.n_layers) != (cfg.serving, tp_rank,
+                                                                         tp_size, cfg.n_layers):
+                raise ValueError("decoders that share weights must agree in serving dtype, "
+                                 "tensor-parallel rank and size, and layer count")
+            self.embedding, self.lm_head, self.final_norm = o.embedding, o.lm_head, o.final_norm
+        else:
+            self.embedding = dev_bf16(w["embedding"]) if cfg.serving == "bfloat16" else dev_f32(
+                w["embedding"])
+            # the LM head is stored in bfloat16 (BASELINE config 4) unless serving is float32
+            self.lm_head = dev_bf16(w["lm_head"]) if cfg.serving == "bfloat16" else dev_f32(
+                w["lm_head"])
+            self.final_norm = dev_f32(w["final_norm"])
         self.norms, self.layers, self.plans, self.qk_norms = [], [], [], []
-        for lw in w["layers"]:
-            self.norms.append((dev_f32(lw["input_norm"]), dev_f32(lw["post_norm"])))
-            if "q_norm" in lw and "k_norm" in lw:
-                self.qk_norms.append((dev_f32(lw["q_norm"]), dev_f32(lw["k_norm"])))
-            elif self.has_qk_norm:
-                raise ValueError("q/k norms must be present in every block or in none")
+        for li, lw in enumerate(w["layers"]):
+            if share_from is not None:
+                self.norms.append(share_from.norms[li])
+                self.qk_norms.append(share_from.qk_norms[li])
+                L = share_from.layers[li]
             else:
-                self.qk_norms.append(None)
-            L = {n: PackedLayer(ctx, lw[n]["ub_rows"], lw[n]["vb_t_rows"], lw[n]["dout"],
-                                lw[n]["din"], lw[n]["r"], lw[n]["s1"], lw[n]["s2"],
-                                lw[n].get("bias"), serving=cfg.serving, name=n) for n in LINEARS}
+                self.norms.append((dev_f32(lw["input_norm"]), dev_f32(lw["post_norm"])))
+                if "q_norm" in lw and "k_norm" in lw:
+                    self.qk_norms.append((dev_f32(lw["q_norm"]), dev_f32(lw["k_norm"])))
+                elif self.has_qk_norm:
+                    raise ValueError("q/k norms must be present in every block or in none")
+                else:
+                    self.qk_norms.append(None)
+                L = {n: PackedLayer(ctx, lw[n]["ub_rows"], lw[n]["vb_t_rows"], lw[n]["dout"],
+                                    lw[n]["din"], lw[n]["r"], lw[n]["s1"], lw[n]["s2"],
+                                    lw[n].get("bias"), serving=cfg.serving, name=n) for n in LINEARS}
             self.layers.append(L)
 
             def rows(t, b):
@@ -233,13 +254,14 @@ class Decoder:
             plan = {"q": LayerPlan(ctx, inst(["q"], self.h, [self.q])),
                     "o": LayerPlan(ctx, inst(["o"], self.attn, [self.delta_attn])),
                     "down": LayerPlan(ctx, inst(["down"], self.a, [self.delta_mlp]))}
-            same_kv = all(lw["k"][f] == lw["v"][f] for f in ("dout", "din", "r"))
+            same_kv = all(getattr(L["k"], f) == getattr(L["v"], f) for f in ("dout", "din", "r"))
             if same_kv:
                 plan["kv"] = LayerPlan(ctx, inst(["k", "v"], self.h, [self.k, self.v]))
             else:
                 plan["k"] = LayerPlan(ctx, inst(["k"], self.h, [self.k]))
                 plan["v"] = LayerPlan(ctx, inst(["v"], self.h, [self.v]))
-            same_gu = all(lw["gate"][f] == lw["up"][f] for f in ("dout", "din", "r"))
+            same_gu = all(getattr(L["gate"], f) == getattr(L["up"], f)
+                          for f in ("dout", "din", "r"))
             if same_gu:
                 plan["gu"] = LayerPlan(ctx, inst(["gate", "up"], self.h, [self.g, self.u]))
             else:
@@ -250,6 +272,7 @@ class Decoder:
         # once for all tokens, the GEMV forms would do it once per token
         self.use_gemm = cfg.serving == "bfloat16" and B >= cfg.gemm_min_batch
         self.graph = None
+        self.kernels_per_step = None
         self._host_positions = [0] * B
 
     # ------------------------------------------------------------------ tensor parallel
@@ -390,9 +413,11 @@ class Decoder:
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
+        n0 = self.ctx.launch_count
         with torch.cuda.graph(graph, stream=stream):  # the context already launches on `stream`
             self.step()
             self.advance()
+        self.kernels_per_step = self.ctx.launch_count - n0   # this library's kernels in the graph
         for t, s in zip((self.token_ids, self.positions, self.kv_len), saved):
             t.copy_(s)
         torch.cuda.synchronize()

@@ -254,6 +254,79 @@ def test_benchmarked_launch_shape_at_config0(gpu_ctx, serving):
         layer.close()
 
 
+@pytest.mark.parametrize("serving", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape,n_inst", [((1100, 700, 1102), 150), ((200, 2100, 70), 149),
+                                          ((64, 512, 64), 300), ((4096, 4096, 431), 148)])
+def test_streaming_form_matches_the_other_kernel_forms(gpu_ctx, shape, n_inst, serving):
+    """With at least one instance per SM a group runs in the persistent streaming form (ring
+    of chunks, producer and table-builder warps).  Row-group counts that are not a multiple of
+    its 16 consumer warps, a single k-step, CTAs with one, two or three instances: all forms
+    accumulate exactly in integers, so the outputs must be the same bits as the
+    one-block-per-instance form (selector 5) and as the single-layer call."""
+    import torch
+    from quantibbler_b200.gpu import LayerGroup
+    dout, din, r = shape
+    n_distinct = 5
+    specs = [make_layer(dout, din, r, seed=700 + i, with_bias=(i % 2 == 1)) for i in range(n_distinct)]
+    layers = [PackedLayer(gpu_ctx, s["ub_rows"], s["vb_t_rows"], dout, din, r, s["s1"], s["s2"],
+                          s["bias"], serving=serving) for s in specs]
+    rng = np.random.default_rng(n_inst)
+    xs = (rng.standard_normal((n_inst, din)) * rng.uniform(0.01, 100, (n_inst, 1))).astype(np.float32)
+    x = torch.from_numpy(xs).cuda()
+    y = torch.full((n_inst, dout), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    group = LayerGroup(gpu_ctx, [layers[i % n_distinct] for i in range(n_inst)], x.data_ptr(),
+                       y.data_ptr())
+    group.apply()
+    gpu_ctx.synchronize()
+    got = y.cpu().numpy()
+    assert np.isfinite(got).all()
+    prev = gpu_ctx.set_gemv_kernel(5)
+    try:
+        y.fill_(float("nan"))
+        group.apply()
+        gpu_ctx.synchronize()
+        assert np.array_equal(y.cpu().numpy(), got)
+    finally:
+        gpu_ctx.set_gemv_kernel(prev)
+    for i in (0, 1, n_inst // 2, n_inst - 1):
+        assert np.array_equal(layers[i % n_distinct].apply(xs[i]), got[i]), i
+        s = specs[i % n_distinct]
+        want = oracle.layer_apply(s["ub_rows"], s["vb_t_rows"], dout, din, r, s["s1"], s["s2"],
+                                  s["bias"], xs[i], serving=serving)
+        assert np.abs(got[i] - want).max() <= (2e-5 if serving == "float32" else 2e-2) * np.abs(want).max()
+    group.apply()
+    gpu_ctx.synchronize()
+    assert np.array_equal(y.cpu().numpy(), got)
+    group.close()
+    for layer in layers:
+        layer.close()
+
+
+def test_streaming_form_nonfinite_and_zero_inputs(gpu_ctx):
+    import torch
+    from quantibbler_b200.gpu import LayerGroup
+    L = make_layer(128, 300, 96, seed=31)
+    layer = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], 128, 300, 96, L["s1"], L["s2"])
+    n_inst = 150
+    xs = np.tile(L["x"], (n_inst, 1)).astype(np.float32)
+    xs[3, 7] = np.inf
+    xs[9, 0] = np.nan
+    xs[11] = 0.0
+    x = torch.from_numpy(xs).cuda()
+    y = torch.zeros(n_inst, 128, device="cuda")
+    torch.cuda.synchronize()
+    group = LayerGroup(gpu_ctx, [layer] * n_inst, x.data_ptr(), y.data_ptr())
+    group.apply()
+    gpu_ctx.synchronize()
+    got = y.cpu().numpy()
+    assert np.isnan(got[3]).all() and np.isnan(got[9]).all()
+    assert np.array_equal(got[11], np.zeros(128, np.float32))
+    assert np.array_equal(got[0], layer.apply(L["x"]))
+    assert np.array_equal(got[149], got[0])
+    group.close()
+
+
 def test_multi_token_apply(gpu_ctx):
     import torch
     L = make_layer(96, 160, 72, seed=11, with_bias=True)
