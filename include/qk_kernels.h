@@ -273,10 +273,19 @@ qk_status qk_layers_apply_group(qk_ctx *ctx, const qk_layer *const *layers, size
 qk_status qk_group_create(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers,
                           const float *x_dev, float *y_dev, qk_group **out);
 /* The general form: instance k applies layers[k] to x_ptrs[k] (din floats) and writes
- * y_ptrs[k] (dout floats); all layers share one shape.  This is how a batch of tokens
- * shares q/k/v (same input pointers) or gate/up launches. */
+ * y_ptrs[k] (dout floats).  This is how a batch of tokens shares q/k/v (same input pointers)
+ * or gate/up launches.  The layers share one serving dtype; they may differ in shape (q beside
+ * k and v) as long as the plan is small enough for the few-instance kernel form, otherwise
+ * QK_ERR_VALUE. */
 qk_status qk_plan_create(qk_ctx *ctx, const qk_layer *const *layers, const float *const *x_ptrs,
                          float *const *y_ptrs, size_t n_inst, qk_group **out);
+/* The same with the SwiGLU of engine/mod.rs:931-935 as the input transform: instance k reads
+ * gate_ptrs[k] and up_ptrs[k] (din floats each) and applies layers[k] to
+ * g * u / (1 + exp(-g)), which is how the down projection follows gate and up without a
+ * separate activation pass. */
+qk_status qk_plan_create_gated(qk_ctx *ctx, const qk_layer *const *layers,
+                               const float *const *gate_ptrs, const float *const *up_ptrs,
+                               float *const *y_ptrs, size_t n_inst, qk_group **out);
 qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group);
 void qk_group_free(qk_group *group);
 /* ---- decoder-side kernels on device buffers -----------------------------------
@@ -353,6 +362,12 @@ qk_status qk_argmax_first(qk_ctx *ctx, const float *logits, size_t n_tokens, siz
  * the streaming form, 2 and 4 = as 5 with 16-warp resp. 4-warp blocks (measurement variants).
  * Returns the previous value; values out of range leave it unchanged. */
 int32_t qk_set_gemv_kernel(qk_ctx *ctx, int32_t which);
+/* Programmatic dependent launch for the decoder-path kernels (norms, GEMV stages, RoPE,
+ * decode attention, SwiGLU, head, argmax): 1 (default) lets each kernel begin its prologue -
+ * fetching weight bits, which depend on no other kernel - while the kernel before it on the
+ * stream finishes; 0 launches them strictly one after the other.  Results are identical.
+ * Returns the previous setting.  No reference counterpart. */
+int32_t qk_set_dependent_launch(qk_ctx *ctx, int32_t on);
 /* How many polls a device-side wait of this context's kernels (the prefill GEMM's pipeline
  * barriers and split-tile flags, the fused all-reduce's inbox) makes before it gives up and
  * the next qk_gpu_synchronize returns QK_ERR_TIMEOUT.  0 restores the default (2^22, seconds).

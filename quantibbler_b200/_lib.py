@@ -78,6 +78,9 @@ _SIGNATURES = {
                                   POINTER(c_void_p)]),
     "qk_plan_create": (c_int32, [c_void_p, POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p),
                                  c_size_t, POINTER(c_void_p)]),
+    "qk_plan_create_gated": (c_int32, [c_void_p, POINTER(c_void_p), POINTER(c_void_p),
+                                       POINTER(c_void_p), POINTER(c_void_p), c_size_t,
+                                       POINTER(c_void_p)]),
     "qk_group_apply": (c_int32, [c_void_p, c_void_p]),
     "qk_group_free": (None, [c_void_p]),
     "qk_rmsnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_float,
@@ -114,6 +117,7 @@ _SIGNATURES = {
                                        c_void_p, c_size_t, c_size_t, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_void_p, c_void_p]),
     "qk_set_wait_limit": (ctypes.c_uint32, [c_void_p, ctypes.c_uint32]),
+    "qk_set_dependent_launch": (c_int32, [c_void_p, c_int32]),
 }
 
 _lib = None

@@ -65,6 +65,7 @@ struct qk_ctx {
     qk_scratch d_head;  // the LM head's bfloat16 split of the hidden state
     bool err_armed = false;  // sticky: set by the first launch that can raise the error word
     uint32_t wait_limit = 0;  // polls before a device-side wait gives up (0: the default)
+    bool pdl = true;          // decoder-path kernels may overlap their prologue with the kernel before
     void *h_pinned = nullptr;
     size_t h_pinned_cap = 0;
     qk_status pinned(size_t bytes, void **out);
@@ -88,12 +89,43 @@ struct qk_layer {
 struct qk_group {
     int device = 0;
     size_t n_inst = 0;
-    qk_layer shape;          // dimensions/strides of the member layers
+    qk_layer shape;          // dimensions/strides of the member layers (the largest, if they differ)
+    bool mixed = false;      // the members differ in shape: few-instance form only
     void *scratch = nullptr; // per member: intermediate t, digit tables, stage metadata
     void *params = nullptr;  // device array of 2*n_inst stage parameter records
 };
 
 namespace qk {
+// Programmatic dependent launch.  A kernel launched through launch_pdl may start while the
+// kernel before it on the stream is still running; it reads nothing that kernel wrote, and
+// writes nothing at all, before it has executed pdl_wait() (griddepcontrol.wait returns when
+// the preceding kernel has completed and its writes are visible).  What comes before the wait
+// is work that depends on no other kernel: fetching weight bits, setting up shared memory.
+// Every such kernel calls pdl_wait() in every thread (so that its own completion implies the
+// completion of everything before it) and pdl_launch() as early as it can, which lets the
+// kernel after it begin its own prologue.  Inside a captured CUDA graph the same launches
+// become programmatic edges.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(bool allow_overlap, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                       cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = allow_overlap ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // Returns the context to use for a call: `ctx` itself, or the process-wide default on
 // device 0 (created on first use) when `ctx` is null.
 qk_status resolve_ctx(qk_ctx *ctx, qk_ctx **out);

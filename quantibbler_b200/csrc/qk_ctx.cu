@@ -197,6 +197,15 @@ int32_t qk_set_gemv_kernel(qk_ctx *ctx, int32_t which) {
     return prev;
 }
 
+int32_t qk_set_dependent_launch(qk_ctx *ctx, int32_t on) {
+    qk_ctx *c;
+    if (qk::resolve_ctx(ctx, &c) != QK_OK) return -1;
+    std::lock_guard<std::mutex> lock(c->mu);
+    const int32_t prev = c->pdl ? 1 : 0;
+    if (on == 0 || on == 1) c->pdl = on != 0;
+    return prev;
+}
+
 uint32_t qk_set_wait_limit(qk_ctx *ctx, uint32_t polls) {
     qk_ctx *c;
     if (qk::resolve_ctx(ctx, &c) != QK_OK) return 0;

@@ -71,6 +71,8 @@ __global__ void __launch_bounds__(kRmsThreads)
 rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
                const float *__restrict__ w, float *__restrict__ x_out, float *__restrict__ y,
                uint32_t d, float eps, int bf16) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     __shared__ float red[kRmsThreads / 32];
     const size_t base = (size_t)blockIdx.x * d;
     float keep[kRmsPerThread];
@@ -144,6 +146,8 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
                          int world, const float *__restrict__ x, const float *__restrict__ w,
                          float *__restrict__ x_out, float *__restrict__ y, uint32_t d, float eps,
                          int bf16, int *__restrict__ error, uint32_t poll_limit) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     __shared__ float red[kRmsThreads / 32];
     __shared__ int gave_up;
     const uint32_t step = *counter + 1;
@@ -262,6 +266,8 @@ rope_cache_kernel(float *__restrict__ q, const float *__restrict__ k, const floa
                   const int32_t *__restrict__ seq_index, KV *__restrict__ cache_k,
                   KV *__restrict__ cache_v, uint32_t n_heads, uint32_t n_kv, uint32_t d,
                   uint32_t s_max, uint32_t n_seq, int *__restrict__ error) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     const uint32_t tok = blockIdx.x, half = d / 2;
     const int pos = positions[tok], seq = seq_index[tok];
     // The cache and the cos/sin table hold s_max positions and n_seq sequences.  A token
@@ -361,6 +367,8 @@ decode_attention_kernel(const float *__restrict__ q, const KV *__restrict__ cach
                         const KV *__restrict__ cache_v, const int32_t *__restrict__ kv_len,
                         float *__restrict__ partial, uint32_t n_heads, uint32_t n_kv, uint32_t d,
                         uint32_t s_max, uint32_t chunk, uint32_t n_splits) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     const uint32_t group = n_heads / n_kv, subs = group / GQ;  // blocks per kv head
     const uint32_t split = blockIdx.x, kvh = blockIdx.y / subs, hsub = blockIdx.y % subs;
     const uint32_t b = blockIdx.z, h0 = kvh * group + hsub * GQ;
@@ -494,6 +502,8 @@ decode_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__restr
                             const uint16_t *__restrict__ cache_v, const int32_t *__restrict__ kv_len,
                             float *__restrict__ partial, uint32_t n_heads, uint32_t n_kv,
                             uint32_t gq, uint32_t s_max, uint32_t chunk, uint32_t n_splits) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     constexpr uint32_t d = 128;
     const uint32_t group = n_heads / n_kv, subs = (group + gq - 1) / gq;
     const uint32_t split = blockIdx.x, kvh = blockIdx.y / subs, hsub = blockIdx.y % subs;
@@ -688,6 +698,8 @@ decode_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__restr
 __global__ void __launch_bounds__(128)
 decode_combine_kernel(const float *__restrict__ partial, float *__restrict__ out, uint32_t d,
                       uint32_t n_splits) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     __shared__ float wgt[128];  // exp(m_s - m) / l per split (n_splits <= 128)
     __shared__ float red[4];
     const float *p = partial + (size_t)blockIdx.x * n_splits * (d + 2);
@@ -716,6 +728,8 @@ decode_combine_kernel(const float *__restrict__ partial, float *__restrict__ out
 
 __global__ void swiglu_kernel(const float *__restrict__ g, const float *__restrict__ u,
                               float *__restrict__ out, size_t n) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
         float gv = g[i];
@@ -725,6 +739,8 @@ __global__ void swiglu_kernel(const float *__restrict__ g, const float *__restri
 
 __global__ void add_kernel(const float *__restrict__ a, const float *__restrict__ b,
                            float *__restrict__ out, size_t n) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = a[i] + b[i];
 }
@@ -732,6 +748,8 @@ __global__ void add_kernel(const float *__restrict__ a, const float *__restrict_
 template <typename W>
 __global__ void embed_kernel(const W *__restrict__ table, const int32_t *__restrict__ ids,
                              float *__restrict__ out, uint32_t d, uint32_t vocab) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     const int id = ids[blockIdx.x];
     for (uint32_t i = threadIdx.x; i < d; i += blockDim.x)
         out[(size_t)blockIdx.x * d + i] =
@@ -767,6 +785,8 @@ __global__ void __launch_bounds__(256)
 lm_head_kernel(const float *__restrict__ hidden, const W *__restrict__ weight,
                float *__restrict__ logits, uint32_t n_tokens, uint32_t vocab, uint32_t d,
                uint32_t vocab_stride) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     constexpr int N = HeadVec<W>::kN;
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t v = blockIdx.x * 8 + warp;
@@ -831,6 +851,8 @@ __device__ __forceinline__ void argmax_block_reduce(float best, int bi, float *o
 __global__ void __launch_bounds__(256)
 argmax_partial_kernel(const float *__restrict__ logits, uint32_t vocab, uint32_t stride,
                       uint32_t slice, float *__restrict__ part_val, int32_t *__restrict__ part_idx) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     const float *row = logits + (size_t)blockIdx.y * stride;
     const uint32_t lo = blockIdx.x * slice, hi = min(vocab, lo + slice);
     float best = -INFINITY;
@@ -850,6 +872,8 @@ __global__ void __launch_bounds__(256)
 argmax_final_kernel(const float *__restrict__ part_val, const int32_t *__restrict__ part_idx,
                     uint32_t parts, int32_t index_base, float *__restrict__ out_val,
                     int32_t *__restrict__ out_idx) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     float best = -INFINITY;
     int bi = 0x7fffffff;
     for (uint32_t i = threadIdx.x; i < parts; i += blockDim.x) {
@@ -869,6 +893,11 @@ qk_status enter(qk_ctx *ctx, qk_ctx **c) {
     QK_CUDA(cudaSetDevice((*c)->device));
     return QK_OK;
 }
+
+// Launch on the context's stream as a programmatic dependent launch (the kernels above all
+// begin with pdl_launch / pdl_wait).  Variadic so that template arguments with commas pass.
+#define QK_PDL(c, kernel, grid, block, smem, ...) \
+    (void)qk::launch_pdl((c)->pdl, kernel, grid, block, smem, (c)->stream, __VA_ARGS__)
 
 #define QK_LAUNCHED(c)            \
     QK_CUDA(cudaGetLastError()); \
@@ -903,6 +932,8 @@ constexpr int kHeadPitch = 96;  // bfloat16 elements per staged token row: 64 k 
 __global__ void split_hidden_kernel(const float *__restrict__ hidden, uint16_t *__restrict__ hi,
                                     uint16_t *__restrict__ lo, uint32_t *__restrict__ any_lo,
                                     size_t n) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float x = hidden[i];
@@ -926,6 +957,8 @@ lm_head_mma_kernel(const uint16_t *__restrict__ hid_hi, const uint16_t *__restri
                    const uint32_t *__restrict__ any_lo, const uint16_t *__restrict__ weight,
                    float *__restrict__ logits, uint32_t n_tokens, uint32_t vocab, uint32_t d,
                    uint32_t vocab_stride) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     extern __shared__ __align__(16) uint16_t sm_head[];  // [2 buffers][hi, lo][8 NT][kHeadPitch]
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
     const uint32_t tok0 = blockIdx.y * (8 * NT);
@@ -1005,7 +1038,7 @@ void launch_lm_head_mma(qk_ctx *c, const uint16_t *hi, const uint16_t *lo, const
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(lm_head_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     dim3 grid((unsigned)qk::ceil_div(vocab, 64), (unsigned)qk::ceil_div(n_tokens, 8 * NT));
-    lm_head_mma_kernel<NT><<<grid, 128, smem, c->stream>>>(hi, lo, any_lo, weight, logits,
+    QK_PDL(c, (lm_head_mma_kernel<NT>), dim3(grid), dim3(128), smem, hi, lo, any_lo, weight, logits,
                                                           (uint32_t)n_tokens, (uint32_t)vocab,
                                                           (uint32_t)d, (uint32_t)stride);
 }
@@ -1019,7 +1052,7 @@ qk_status qk_rmsnorm(qk_ctx *ctx, const float *x, const float *residual, const f
     qk_status st = enter(ctx, &c);
     if (st != QK_OK) return st;
     if (n_tokens == 0) return QK_OK;
-    rmsnorm_kernel<<<(unsigned)n_tokens, kRmsThreads, 0, c->stream>>>(x, residual, weight, x_out, y,
+    QK_PDL(c, rmsnorm_kernel, dim3((unsigned)n_tokens), dim3(kRmsThreads), 0, x, residual, weight, x_out, y,
                                                               (uint32_t)d, eps,
                                                               serving_dtype == QK_BF16);
     QK_LAUNCHED(c);
@@ -1044,12 +1077,12 @@ qk_status qk_rope_cache(qk_ctx *ctx, float *q, const float *k, const float *v,
     if ((st = qk::error_word(c)) != QK_OK) return st;
     int *err = (int *)c->d_err.ptr;
     if (kv_dtype == QK_F32)
-        rope_cache_kernel<float><<<(unsigned)n_tokens, 256, 0, c->stream>>>(
+        QK_PDL(c, (rope_cache_kernel<float>), dim3((unsigned)n_tokens), dim3(256), 0, 
             q, k, v, cos_sin, positions, seq_index, (float *)cache_k, (float *)cache_v,
             (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)head_dim, (uint32_t)s_max,
             (uint32_t)n_seq, err);
     else
-        rope_cache_kernel<uint16_t><<<(unsigned)n_tokens, 256, 0, c->stream>>>(
+        QK_PDL(c, (rope_cache_kernel<uint16_t>), dim3((unsigned)n_tokens), dim3(256), 0, 
             q, k, v, cos_sin, positions, seq_index, (uint16_t *)cache_k, (uint16_t *)cache_v,
             (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)head_dim, (uint32_t)s_max,
             (uint32_t)n_seq, err);
@@ -1092,13 +1125,13 @@ qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
         const size_t smem8 = (size_t)kMmaDecWarps * 2 * kMmaDecBufBytes;
         QK_CUDA(cudaFuncSetAttribute(decode_attention_mma_kernel,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem8));
-        decode_attention_mma_kernel<<<grid8, kMmaDecWarps * 32, smem8, c->stream>>>(
+        QK_PDL(c, decode_attention_mma_kernel, dim3(grid8), dim3(kMmaDecWarps * 32), smem8, 
             q, (const uint16_t *)cache_k, (const uint16_t *)cache_v, kv_len, scratch,
             (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)gq8, (uint32_t)s_max,
             (uint32_t)chunk8, (uint32_t)n_splits);
         QK_CUDA(cudaGetLastError());
         c->launches++;
-        decode_combine_kernel<<<(unsigned)(batch * n_heads), 128, 0, c->stream>>>(
+        QK_PDL(c, decode_combine_kernel, dim3((unsigned)(batch * n_heads)), dim3(128), 0, 
             scratch, out, (uint32_t)head_dim, (uint32_t)n_splits);
         QK_LAUNCHED(c);
     }
@@ -1112,7 +1145,7 @@ qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
         if (smem > 48 * 1024)                                                                    \
             QK_CUDA(cudaFuncSetAttribute(decode_attention_kernel<KV, DPL, GQ>,                   \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        decode_attention_kernel<KV, DPL, GQ><<<grid, kDecThreads, smem, c->stream>>>(            \
+        QK_PDL(c, (decode_attention_kernel<KV, DPL, GQ>), dim3(grid), dim3(kDecThreads), smem,             \
             q, (const KV *)cache_k, (const KV *)cache_v, kv_len, scratch, (uint32_t)n_heads,     \
             (uint32_t)n_kv_heads, (uint32_t)head_dim, (uint32_t)s_max, (uint32_t)chunk,          \
             (uint32_t)n_splits);                                                                 \
@@ -1132,7 +1165,7 @@ qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
 #undef QK_DEC
     QK_CUDA(cudaGetLastError());
     c->launches++;
-    decode_combine_kernel<<<(unsigned)(batch * n_heads), 128, 0, c->stream>>>(
+    QK_PDL(c, decode_combine_kernel, dim3((unsigned)(batch * n_heads)), dim3(128), 0, 
         scratch, out, (uint32_t)head_dim, (uint32_t)n_splits);
     QK_LAUNCHED(c);
 }
@@ -1142,7 +1175,7 @@ qk_status qk_swiglu(qk_ctx *ctx, const float *gate, const float *up, size_t n, f
     qk_status st = enter(ctx, &c);
     if (st != QK_OK) return st;
     if (n == 0) return QK_OK;
-    swiglu_kernel<<<(unsigned)qk::ceil_div(n, 256), 256, 0, c->stream>>>(gate, up, out, n);
+    QK_PDL(c, swiglu_kernel, dim3((unsigned)qk::ceil_div(n, 256)), dim3(256), 0, gate, up, out, n);
     QK_LAUNCHED(c);
 }
 
@@ -1151,7 +1184,7 @@ qk_status qk_add(qk_ctx *ctx, const float *a, const float *b, size_t n, float *o
     qk_status st = enter(ctx, &c);
     if (st != QK_OK) return st;
     if (n == 0) return QK_OK;
-    add_kernel<<<(unsigned)qk::ceil_div(n, 256), 256, 0, c->stream>>>(a, b, out, n);
+    QK_PDL(c, add_kernel, dim3((unsigned)qk::ceil_div(n, 256)), dim3(256), 0, a, b, out, n);
     QK_LAUNCHED(c);
 }
 
@@ -1162,10 +1195,10 @@ qk_status qk_embed(qk_ctx *ctx, const void *table, int32_t table_dtype, const in
     if (st != QK_OK) return st;
     if (n_tokens == 0) return QK_OK;
     if (table_dtype == QK_F32)
-        embed_kernel<float><<<(unsigned)n_tokens, 256, 0, c->stream>>>(
+        QK_PDL(c, (embed_kernel<float>), dim3((unsigned)n_tokens), dim3(256), 0, 
             (const float *)table, ids, out, (uint32_t)d, (uint32_t)vocab);
     else if (table_dtype == QK_BF16)
-        embed_kernel<uint16_t><<<(unsigned)n_tokens, 256, 0, c->stream>>>(
+        QK_PDL(c, (embed_kernel<uint16_t>), dim3((unsigned)n_tokens), dim3(256), 0, 
             (const uint16_t *)table, ids, out, (uint32_t)d, (uint32_t)vocab);
     else
         return qk::fail(QK_ERR_VALUE, "embedding dtype must be float32 or bfloat16, got tag %d",
@@ -1184,11 +1217,11 @@ qk_status qk_lm_head(qk_ctx *ctx, const float *hidden, const void *weight, int32
     const unsigned blocks = (unsigned)qk::ceil_div(vocab, 8);
     if (weight_dtype == QK_F32) {
         if (n_tokens == 1)
-            lm_head_kernel<float, 1><<<blocks, 256, 0, c->stream>>>(
+            QK_PDL(c, (lm_head_kernel<float, 1>), dim3(blocks), dim3(256), 0, 
                 hidden, (const float *)weight, logits, 1, (uint32_t)vocab, (uint32_t)d,
                 (uint32_t)logits_stride);
         else
-            lm_head_kernel<float, 8><<<blocks, 256, 0, c->stream>>>(
+            QK_PDL(c, (lm_head_kernel<float, 8>), dim3(blocks), dim3(256), 0, 
                 hidden, (const float *)weight, logits, (uint32_t)n_tokens, (uint32_t)vocab,
                 (uint32_t)d, (uint32_t)logits_stride);
     } else if (weight_dtype == QK_BF16 && n_tokens >= 8 && d % 64 == 0) {
@@ -1199,7 +1232,7 @@ qk_status qk_lm_head(qk_ctx *ctx, const float *hidden, const void *weight, int32
         uint16_t *hi = (uint16_t *)c->d_head.ptr, *lo = (uint16_t *)((uint8_t *)c->d_head.ptr + term);
         uint32_t *any_lo = (uint32_t *)((uint8_t *)c->d_head.ptr + 2 * term);
         QK_CUDA(cudaMemsetAsync(any_lo, 0, sizeof(uint32_t), c->stream));
-        split_hidden_kernel<<<(unsigned)qk::ceil_div(n, 256), 256, 0, c->stream>>>(hidden, hi, lo, any_lo, n);
+        QK_PDL(c, split_hidden_kernel, dim3((unsigned)qk::ceil_div(n, 256)), dim3(256), 0, hidden, hi, lo, any_lo, n);
         QK_CUDA(cudaGetLastError());
         c->launches++;
         if (n_tokens <= 8) launch_lm_head_mma<1>(c, hi, lo, any_lo, w, logits, n_tokens, vocab, d, logits_stride);
@@ -1208,11 +1241,11 @@ qk_status qk_lm_head(qk_ctx *ctx, const float *hidden, const void *weight, int32
         else launch_lm_head_mma<8>(c, hi, lo, any_lo, w, logits, n_tokens, vocab, d, logits_stride);
     } else if (weight_dtype == QK_BF16) {
         if (n_tokens == 1)
-            lm_head_kernel<uint16_t, 1><<<blocks, 256, 0, c->stream>>>(
+            QK_PDL(c, (lm_head_kernel<uint16_t, 1>), dim3(blocks), dim3(256), 0, 
                 hidden, (const uint16_t *)weight, logits, 1, (uint32_t)vocab, (uint32_t)d,
                 (uint32_t)logits_stride);
         else
-            lm_head_kernel<uint16_t, 8><<<blocks, 256, 0, c->stream>>>(
+            QK_PDL(c, (lm_head_kernel<uint16_t, 8>), dim3(blocks), dim3(256), 0, 
                 hidden, (const uint16_t *)weight, logits, (uint32_t)n_tokens, (uint32_t)vocab,
                 (uint32_t)d, (uint32_t)logits_stride);
     } else {
@@ -1237,12 +1270,12 @@ qk_status qk_argmax_first(qk_ctx *ctx, const float *logits, size_t n_tokens, siz
     float *part_val = (float *)c->d_z.ptr;
     int32_t *part_idx = (int32_t *)(part_val + n_tokens * parts);
     dim3 grid((unsigned)parts, (unsigned)n_tokens);
-    argmax_partial_kernel<<<grid, 256, 0, c->stream>>>(logits, (uint32_t)vocab,
+    QK_PDL(c, argmax_partial_kernel, dim3(grid), dim3(256), 0, logits, (uint32_t)vocab,
                                                        (uint32_t)logits_stride, (uint32_t)slice,
                                                        part_val, part_idx);
     QK_CUDA(cudaGetLastError());
     c->launches++;
-    argmax_final_kernel<<<(unsigned)n_tokens, 256, 0, c->stream>>>(
+    QK_PDL(c, argmax_final_kernel, dim3((unsigned)n_tokens), dim3(256), 0, 
         part_val, part_idx, (uint32_t)parts, index_base, out_val, out_idx);
     QK_LAUNCHED(c);
 }
@@ -1262,7 +1295,7 @@ qk_status qk_allreduce_rmsnorm(qk_ctx *ctx, const float *partial, const uint64_t
     if ((st = qk::error_word(c)) != QK_OK) return st;
     InboxArgs inbox{};
     for (int r = 0; r < world; ++r) inbox.at[r] = reinterpret_cast<unsigned long long *>(peer_inbox[r]);
-    allreduce_rmsnorm_kernel<<<(unsigned)n_tokens, kRmsThreads, 0, c->stream>>>(
+    QK_PDL(c, allreduce_rmsnorm_kernel, dim3((unsigned)n_tokens), dim3(kRmsThreads), 0, 
         inbox, partial, state_dev, state_dev + 1, rank, world, x, weight, x_out, y, (uint32_t)d, eps,
         serving_dtype == QK_BF16, (int *)c->d_err.ptr, c->wait_limit ? c->wait_limit : (1u << 22));
     c->err_armed = true;

@@ -63,6 +63,8 @@ struct StageParams {
     const float *out_bias;   // bias or null
     uint2 *digits;           // tensor-core kernel: digit table of the input vector
     StageMeta *meta;
+    const float *in_gate_up; // not null: the input is SwiGLU(in, in_gate_up) = g * u / (1 + e^-g)
+    uint32_t n_rows, n_bits; // this instance's shape (the few-instance form mixes shapes)
 };
 
 __device__ __forceinline__ float round_bf16(float v) {
@@ -90,6 +92,8 @@ template <bool kRoundBf16>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 gemv_signselect_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint32_t n_bits,
                        uint32_t stride) {
+    qk::pdl_launch();
+    qk::pdl_wait();
     extern __shared__ float vs[];  // permuted copy of the input vector, zero padded
     const StageParams p = many[blockIdx.y];
     const float *in = static_cast<const float *>(p.in);
@@ -197,6 +201,7 @@ __device__ __forceinline__ double load_input(const StageParams &p, uint32_t k, u
     if (k >= n_bits) return 0.0;
     if (kInDouble) return static_cast<const double *>(p.in)[k];  // rounded by its producer
     float v = static_cast<const float *>(p.in)[k];
+    if (p.in_gate_up) v = v * p.in_gate_up[k] / (1.0f + expf(-v));  // the SwiGLU between gate/up and down
     if (p.in_scale) v = p.in_scale[k] * v;  // float32 product, as the reference forms z
     if (kRoundBf16) v = round_bf16(v);
     return (double)v;
@@ -276,6 +281,8 @@ __device__ __forceinline__ void build_record(const long long (&q8)[8], uint32_t 
 template <bool kInDouble, bool kRoundBf16>
 __global__ void __launch_bounds__(256)
 digit_table_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32_t n_steps) {
+    qk::pdl_launch();
+    qk::pdl_wait();
     const StageParams p = many[blockIdx.y];
     __shared__ double red_max[8];
     __shared__ long long red_sum[8];
@@ -423,6 +430,9 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
 #pragma unroll
         for (int s = 0; s < kStages - 1; ++s) issue(s);
     }
+    // The weight bits depend on no other kernel, the input vector does: from here on the
+    // kernel before this one on the stream must be complete.
+    qk::pdl_wait();
     // ---- the digit table of this instance (the weight ring is already filling)
     __shared__ double red_max[16];
     __shared__ long long red_sum[16];
@@ -614,7 +624,8 @@ template <bool kRoundBf16, bool kFinal, bool kSmemDigits>
 __global__ void __launch_bounds__(512, 1)
 gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint32_t n_bits,
                      uint32_t n_groups, uint32_t n_steps, uint32_t groups_per_warp) {
-    extern __shared__ __align__(16) uint8_t smem_dyn[];
+    qk::pdl_launch();  // (bitslice_stage waits for the kernel before, after its weight prologue)
+    extern __shared__ __align__(128) uint8_t smem_dyn[];
     const StageParams p = many[blockIdx.y];
     uint8_t *ring = smem_dyn + (kSmemDigits ? (size_t)n_steps * 4096 : 0);
     bitslice_stage<kRoundBf16, kFinal, kSmemDigits, false, false>(
@@ -624,12 +635,22 @@ gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint
 
 // Low-latency form for few instances: one block per (row group, instance), the block's
 // warps share the group's k-steps.  smem: [digit table][ring][reduction buffer].
+// The instances of one launch may differ in shape (q beside k and v): every instance brings
+// its own n_rows and n_bits, the grid covers the largest group count and the shared memory
+// the longest table; blocks beyond an instance's last row group have nothing to do.
 template <bool kRoundBf16, bool kFinal>
 __global__ void __launch_bounds__(512)
-gemv_bitslice_splitk_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint32_t n_bits,
-                            uint32_t n_groups, uint32_t n_steps) {
-    extern __shared__ __align__(16) uint8_t smem_dyn[];
+gemv_bitslice_splitk_kernel(const StageParams *__restrict__ many) {
+    qk::pdl_launch();  // (bitslice_stage waits for the kernel before, after its weight prologue)
+    extern __shared__ __align__(128) uint8_t smem_dyn[];
     const StageParams p = many[blockIdx.y];
+    const uint32_t n_rows = p.n_rows, n_bits = p.n_bits;
+    const uint32_t n_groups = (n_rows + kGroupRows - 1) / kGroupRows;
+    const uint32_t n_steps = (n_bits + kStepBits - 1) / kStepBits;
+    if (blockIdx.x >= n_groups) {
+        qk::pdl_wait();
+        return;
+    }
     uint8_t *ring = smem_dyn + (size_t)n_steps * 4096;
     int *red = reinterpret_cast<int *>(ring + (size_t)(blockDim.x / 32) * kStages * kChunkBytes);
     bitslice_stage<kRoundBf16, kFinal, true, false, false, true>(
@@ -648,7 +669,8 @@ layer_bitslice_fused_kernel(const StageParams *__restrict__ stage1,
                             const StageParams *__restrict__ stage2, uint32_t r, uint32_t din,
                             uint32_t dout, uint32_t t_bytes, uint32_t table_bytes, uint32_t gpw1,
                             uint32_t gpw2) {
-    extern __shared__ __align__(16) uint8_t smem_dyn[];
+    qk::pdl_launch();
+    extern __shared__ __align__(128) uint8_t smem_dyn[];
     double *t_smem = reinterpret_cast<double *>(smem_dyn);
     uint8_t *table = smem_dyn + t_bytes, *ring = table + table_bytes;
     const StageParams p1 = stage1[blockIdx.x], p2 = stage2[blockIdx.x];
@@ -902,6 +924,7 @@ ps_consume_group(const StageParams &p, const uint8_t *ring_smem, uint64_t *full,
 template <bool kRoundBf16>
 __global__ void __launch_bounds__(kPsThreads, 1)
 layer_stream_kernel(const PsArgs a, uint32_t t_bytes, uint32_t table1_bytes, uint32_t table2_bytes) {
+    qk::pdl_launch();
     extern __shared__ __align__(128) uint8_t smem_dyn[];
     // [ring][table1 x2][table2 x2][t x2][meta x4][barriers][reduction scratch][abort flag]
     uint8_t *ring = smem_dyn;
@@ -944,6 +967,7 @@ layer_stream_kernel(const PsArgs a, uint32_t t_bytes, uint32_t table1_bytes, uin
 
     // The order of the jobs, the same in every role: step s = 0 .. n_mine runs J1(s) (if
     // s < n_mine) and then J2(s - 1) (if s >= 1).
+    if (warp != kPsProducerWarp) qk::pdl_wait();  // inputs come from the kernel before; weight bits do not
     if (warp < kPsConsumers) {
         // ------------------------------------------------------------ consumers
         uint32_t seq = 0;  // chunks of all rounds before the current one
@@ -1152,8 +1176,8 @@ qk_status launch_signselect(qk_ctx *c, const StageParams *many, size_t n_inst, c
     auto kern = bf16 ? gemv_signselect_kernel<true> : gemv_signselect_kernel<false>;
     if (smem > 48 * 1024)
         QK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, kWarpsPerBlock * 32, smem, c->stream>>>(many, (uint32_t)s.n_rows,
-                                                         (uint32_t)s.n_bits, (uint32_t)s.row_stride);
+    (void)qk::launch_pdl(c->pdl, kern, grid, dim3(kWarpsPerBlock * 32), smem, c->stream, many,
+                         (uint32_t)s.n_rows, (uint32_t)s.n_bits, (uint32_t)s.row_stride);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     return QK_OK;
@@ -1210,9 +1234,7 @@ qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, con
                          : gemv_bitslice_splitk_kernel<false, kFinal>;
         QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)kSmemBudget));
-        gemv<<<grid, (unsigned)sk_warps * 32, sk_smem, c->stream>>>(
-            many, (uint32_t)s.n_rows, (uint32_t)s.n_bits, (uint32_t)s.n_groups,
-            (uint32_t)s.n_steps);
+        (void)qk::launch_pdl(c->pdl, gemv, grid, dim3((unsigned)sk_warps * 32), sk_smem, c->stream, many);
         QK_CUDA(cudaGetLastError());
         c->launches++;
         return QK_OK;
@@ -1223,7 +1245,8 @@ qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, con
                             : (bf16 ? digit_table_kernel<false, true>
                                     : digit_table_kernel<false, false>);
         dim3 tgrid((unsigned)qk::ceil_div(s.n_steps, 4), (unsigned)n_inst);
-        table<<<tgrid, 256, 0, c->stream>>>(many, (uint32_t)s.n_bits, (uint32_t)s.n_steps);
+        (void)qk::launch_pdl(c->pdl, table, tgrid, dim3(256), 0, c->stream, many, (uint32_t)s.n_bits,
+                             (uint32_t)s.n_steps);
         QK_CUDA(cudaGetLastError());
         c->launches++;
     }
@@ -1234,9 +1257,9 @@ qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, con
                                        : gemv_bitslice_kernel<false, kFinal, false>);
     QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kSmemBudget));
-    gemv<<<grid, (unsigned)pl.warps_per_block * 32, pl.smem, c->stream>>>(
-        many, (uint32_t)s.n_rows, (uint32_t)s.n_bits, (uint32_t)s.n_groups, (uint32_t)s.n_steps,
-        (uint32_t)pl.gpw);
+    (void)qk::launch_pdl(c->pdl, gemv, grid, dim3((unsigned)pl.warps_per_block * 32), pl.smem, c->stream,
+                         many, (uint32_t)s.n_rows, (uint32_t)s.n_bits, (uint32_t)s.n_groups,
+                         (uint32_t)s.n_steps, (uint32_t)pl.gpw);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     return QK_OK;
@@ -1325,28 +1348,64 @@ qk_status check_group(qk_ctx *c, const qk_layer *const *layers, size_t n_layers)
 // the k-th slice of `scratch`.
 void fill_params(StageParams *h, const qk_layer *const *layers, size_t n_layers, size_t n_tokens,
                  const float *x_dev, float *y_dev, uint8_t *scratch, size_t x_layer_stride,
-                 size_t y_layer_stride) {
+                 size_t y_layer_stride, const float *gate_up = nullptr, size_t scratch_stride = 0) {
     const size_t n_inst = n_layers * n_tokens;
-    const InstanceScratch sc = scratch_of(layers[0]);
+    InstanceScratch sc = scratch_of(layers[0]);
+    if (scratch_stride) sc.total = scratch_stride;
     for (size_t t = 0; t < n_tokens; ++t)
         for (size_t i = 0; i < n_layers; ++i) {
             const qk_layer *l = layers[i];
             size_t k = t * n_layers + i;
             uint8_t *base = scratch + k * sc.total;
+            const InstanceScratch own = scratch_of(l);  // the slice's inner layout follows the layer
             void *t_buf = base;
-            uint2 *dig1 = (uint2 *)(base + sc.t_bytes);
-            uint2 *dig2 = (uint2 *)(base + sc.t_bytes + sc.dig1_bytes);
-            StageMeta *meta = (StageMeta *)(base + sc.t_bytes + sc.dig1_bytes + sc.dig2_bytes);
+            uint2 *dig1 = (uint2 *)(base + own.t_bytes);
+            uint2 *dig2 = (uint2 *)(base + own.t_bytes + own.dig1_bytes);
+            StageMeta *meta = (StageMeta *)(base + own.t_bytes + own.dig1_bytes + own.dig2_bytes);
             const float *x = x_dev + i * x_layer_stride + t * l->din;
             float *y = y_dev + i * y_layer_stride + t * l->dout;
-            h[k] = StageParams{l->vbt, l->vbt_tiles, x, l->s2, t_buf, nullptr, nullptr, dig1, meta};
-            h[n_inst + k] =
-                StageParams{l->ub, l->ub_tiles, t_buf, nullptr, y, l->s1, l->bias, dig2, meta + 1};
+            h[k] = StageParams{l->vbt, l->vbt_tiles, x, l->s2, t_buf, nullptr, nullptr, dig1, meta,
+                               gate_up, (uint32_t)l->r, (uint32_t)l->din};
+            h[n_inst + k] = StageParams{l->ub, l->ub_tiles, t_buf, nullptr, y, l->s1, l->bias, dig2,
+                                        meta + 1, nullptr, (uint32_t)l->dout, (uint32_t)l->r};
         }
 }
 
+// A plan whose instances differ in shape runs in the few-instance (split-k) form only; `widest`
+// carries the largest dimensions over the instances (din, r, dout separately).
+bool mixed_plan_fits(const qk_ctx *c, const StageShape &s, size_t n_inst, size_t *warps, size_t *smem) {
+    size_t sk_warps = s.n_steps < 4 ? 4 : s.n_steps > 16 ? 16 : s.n_steps;
+    auto sk_bytes = [&](size_t w) { return s.n_steps * 4096 + w * kRingPerWarp + w * 16 * 32 * 4; };
+    while (sk_warps > 4 && sk_bytes(sk_warps) > kSmemBudget) --sk_warps;
+    *warps = sk_warps;
+    *smem = sk_bytes(sk_warps);
+    return *smem <= kSmemBudget && s.n_groups <= 65535 && n_inst <= 65535 &&
+           n_inst * s.n_groups <= 8 * (size_t)c->sm_count;
+}
+
+template <bool kFinal>
+qk_status launch_mixed_stage(qk_ctx *c, const StageParams *many, size_t n_inst, const StageShape &s,
+                             bool bf16) {
+    size_t warps, smem;
+    if (!mixed_plan_fits(c, s, n_inst, &warps, &smem))
+        return qk::fail(QK_ERR_VALUE, "a plan of mixed shapes must fit the few-instance form");
+    auto gemv = bf16 ? gemv_bitslice_splitk_kernel<true, kFinal> : gemv_bitslice_splitk_kernel<false, kFinal>;
+    QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    dim3 grid((unsigned)s.n_groups, (unsigned)n_inst);
+    (void)qk::launch_pdl(c->pdl, gemv, grid, dim3((unsigned)warps * 32), smem, c->stream, many);
+    QK_CUDA(cudaGetLastError());
+    c->launches++;
+    return QK_OK;
+}
+
 qk_status launch_both(qk_ctx *c, const qk_layer *l0, const StageParams *d, size_t n_inst,
-                      int kernel) {
+                      int kernel, bool mixed = false) {
+    if (mixed) {
+        // l0 holds the largest din, r and dout over the instances
+        qk_status e = launch_mixed_stage<false>(c, d, n_inst, stage1_shape(l0), l0->serving == QK_BF16);
+        if (e != QK_OK) return e;
+        return launch_mixed_stage<true>(c, d + n_inst, n_inst, stage2_shape(l0), l0->serving == QK_BF16);
+    }
     const bool bf16 = l0->serving == QK_BF16;
     const StageShape s1 = stage1_shape(l0), s2 = stage2_shape(l0);
     qk_status st;
@@ -1371,8 +1430,9 @@ qk_status launch_both(qk_ctx *c, const qk_layer *l0, const StageParams *d, size_
             auto kern = bf16 ? layer_stream_kernel<true> : layer_stream_kernel<false>;
             QK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)kPsSmemBudget));
-            kern<<<(unsigned)ps.grid, kPsThreads, ps.smem, c->stream>>>(
-                a, (uint32_t)ps.t_bytes, (uint32_t)ps.table1_bytes, (uint32_t)ps.table2_bytes);
+            (void)qk::launch_pdl(c->pdl, kern, dim3((unsigned)ps.grid), dim3(kPsThreads), ps.smem, c->stream,
+                                 a, (uint32_t)ps.t_bytes, (uint32_t)ps.table1_bytes,
+                                 (uint32_t)ps.table2_bytes);
             QK_CUDA(cudaGetLastError());
             c->launches++;
             c->err_armed = true;
@@ -1384,10 +1444,11 @@ qk_status launch_both(qk_ctx *c, const qk_layer *l0, const StageParams *d, size_
         auto fused = bf16 ? layer_bitslice_fused_kernel<true> : layer_bitslice_fused_kernel<false>;
         QK_CUDA(cudaFuncSetAttribute(fused, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)kSmemBudget));
-        fused<<<(unsigned)n_inst, (unsigned)warps * 32, smem, c->stream>>>(
-            d, d + n_inst, (uint32_t)l0->r, (uint32_t)l0->din, (uint32_t)l0->dout,
-            (uint32_t)t_bytes, (uint32_t)table_bytes, (uint32_t)qk::ceil_div(s1.n_groups, warps),
-            (uint32_t)qk::ceil_div(s2.n_groups, warps));
+        (void)qk::launch_pdl(c->pdl, fused, dim3((unsigned)n_inst), dim3((unsigned)warps * 32), smem,
+                             c->stream, d, d + n_inst, (uint32_t)l0->r, (uint32_t)l0->din,
+                             (uint32_t)l0->dout, (uint32_t)t_bytes, (uint32_t)table_bytes,
+                             (uint32_t)qk::ceil_div(s1.n_groups, warps),
+                             (uint32_t)qk::ceil_div(s2.n_groups, warps));
         QK_CUDA(cudaGetLastError());
         c->launches++;
         return QK_OK;
@@ -1620,8 +1681,9 @@ qk_status qk_group_create(qk_ctx *ctx, const qk_layer *const *layers, size_t n_l
     return QK_OK;
 }
 
-qk_status qk_plan_create(qk_ctx *ctx, const qk_layer *const *layers, const float *const *x_ptrs,
-                         float *const *y_ptrs, size_t n_inst, qk_group **out) {
+static qk_status plan_create(qk_ctx *ctx, const qk_layer *const *layers, const float *const *x_ptrs,
+                             const float *const *x2_ptrs, float *const *y_ptrs, size_t n_inst,
+                             qk_group **out) {
     if (!out) return qk::fail(QK_ERR_VALUE, "qk_plan_create: out is null");
     *out = nullptr;
     if (n_inst == 0 || !layers || !x_ptrs || !y_ptrs || !layers[0])
@@ -1633,14 +1695,43 @@ qk_status qk_plan_create(qk_ctx *ctx, const qk_layer *const *layers, const float
     if (st != QK_OK) return st;
     std::lock_guard<std::mutex> lock(c->mu);
     QK_CUDA(cudaSetDevice(c->device));
-    if ((st = check_group(c, layers, n_inst)) != QK_OK) return st;
     const qk_layer *l0 = layers[0];
+    // instances may differ in shape (q beside k and v) as long as they share the serving dtype
+    // and the whole plan fits the few-instance form
+    qk_layer widest = *l0;
+    bool mixed = false;
+    size_t slice = 0;
+    for (size_t i = 0; i < n_inst; ++i) {
+        const qk_layer *l = layers[i];
+        if (!l) return qk::fail(QK_ERR_VALUE, "layer %zu is null", i);
+        if (l->device != c->device)
+            return qk::fail(QK_ERR_VALUE, "layer %zu lives on device %d, context on device %d", i,
+                            l->device, c->device);
+        if (l->serving != l0->serving)
+            return qk::fail(QK_ERR_VALUE, "planned layers must share one serving dtype (layer %zu "
+                            "differs from layer 0)", i);
+        if (l->dout != l0->dout || l->din != l0->din || l->r != l0->r) mixed = true;
+        if (l->dout > widest.dout) widest.dout = l->dout;
+        if (l->din > widest.din) widest.din = l->din;
+        if (l->r > widest.r) widest.r = l->r;
+        const size_t need = scratch_of(l).total;
+        if (need > slice) slice = need;
+    }
+    if (mixed) {
+        size_t warps, smem;
+        if (!mixed_plan_fits(c, stage1_shape(&widest), n_inst, &warps, &smem) ||
+            !mixed_plan_fits(c, stage2_shape(&widest), n_inst, &warps, &smem))
+            return qk::fail(QK_ERR_VALUE,
+                            "planned layers of different shapes must fit the few-instance form "
+                            "(%zu instances, up to %zu x %zu rank %zu)",
+                            n_inst, widest.dout, widest.din, widest.r);
+    }
     qk_group *g = new qk_group();
     g->device = c->device;
     g->n_inst = n_inst;
-    g->shape = *l0;
-    const InstanceScratch sc = scratch_of(l0);
-    cudaError_t e = cudaMalloc(&g->scratch, n_inst * sc.total);
+    g->shape = widest;  // dimensions only (the largest over the instances); the pointers are not used
+    g->mixed = mixed;
+    cudaError_t e = cudaMalloc(&g->scratch, n_inst * slice);
     if (e == cudaSuccess) e = cudaMalloc(&g->params, 2 * n_inst * sizeof(StageParams));
     if (e != cudaSuccess) {
         qk_group_free(g);
@@ -1653,8 +1744,8 @@ qk_status qk_plan_create(qk_ctx *ctx, const qk_layer *const *layers, const float
     for (size_t k = 0; k < n_inst; ++k) {
         StageParams pair[2];
         const qk_layer *one = layers[k];
-        fill_params(pair, &one, 1, 1, x_ptrs[k], y_ptrs[k], (uint8_t *)g->scratch + k * sc.total,
-                    0, 0);
+        fill_params(pair, &one, 1, 1, x_ptrs[k], y_ptrs[k], (uint8_t *)g->scratch + k * slice, 0, 0,
+                    x2_ptrs ? x2_ptrs[k] : nullptr, slice);
         h[k] = pair[0];
         h[n_inst + k] = pair[1];
     }
@@ -1663,6 +1754,18 @@ qk_status qk_plan_create(qk_ctx *ctx, const qk_layer *const *layers, const float
     QK_CUDA(cudaStreamSynchronize(c->stream));
     *out = g;
     return QK_OK;
+}
+
+qk_status qk_plan_create(qk_ctx *ctx, const qk_layer *const *layers, const float *const *x_ptrs,
+                         float *const *y_ptrs, size_t n_inst, qk_group **out) {
+    return plan_create(ctx, layers, x_ptrs, nullptr, y_ptrs, n_inst, out);
+}
+
+qk_status qk_plan_create_gated(qk_ctx *ctx, const qk_layer *const *layers,
+                               const float *const *gate_ptrs, const float *const *up_ptrs,
+                               float *const *y_ptrs, size_t n_inst, qk_group **out) {
+    if (!up_ptrs) return qk::fail(QK_ERR_VALUE, "qk_plan_create_gated: up_ptrs is null");
+    return plan_create(ctx, layers, gate_ptrs, up_ptrs, y_ptrs, n_inst, out);
 }
 
 qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group) {
@@ -1676,7 +1779,7 @@ qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group) {
         return qk::fail(QK_ERR_VALUE, "group lives on device %d, context on device %d",
                         group->device, c->device);
     return launch_both(c, &group->shape, (const StageParams *)group->params, group->n_inst,
-                       c->gemv_kernel);
+                       c->gemv_kernel, group->mixed);
 }
 
 void qk_group_free(qk_group *g) {
@@ -1710,7 +1813,8 @@ template <bool kRoundBf16, bool kFinal>
 __global__ void __launch_bounds__(512, 1)
 gemv_bitslice_value_kernel(const StageParams p, uint32_t n_rows, uint32_t n_bits, uint32_t n_groups,
                            uint32_t n_steps, uint32_t groups_per_warp) {
-    extern __shared__ __align__(16) uint8_t smem_dyn[];
+    qk::pdl_launch();
+    extern __shared__ __align__(128) uint8_t smem_dyn[];
     bitslice_stage<kRoundBf16, kFinal, true, false, false>(
         p, smem_dyn, smem_dyn + (size_t)n_steps * 4096, nullptr, nullptr, n_rows, n_bits, n_groups,
         n_steps, blockIdx.x, groups_per_warp, false);
@@ -1746,9 +1850,9 @@ qk_status launch_value_stage(qk_ctx *c, const StageParams &p, const StageShape &
                      : gemv_bitslice_value_kernel<false, kFinal>;
     QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kSmemBudget));
-    gemv<<<grid, (unsigned)pl.warps_per_block * 32, pl.smem, c->stream>>>(
-        p, (uint32_t)s.n_rows, (uint32_t)s.n_bits, (uint32_t)s.n_groups, (uint32_t)s.n_steps,
-        (uint32_t)pl.gpw);
+    (void)qk::launch_pdl(c->pdl, gemv, grid, dim3((unsigned)pl.warps_per_block * 32), pl.smem, c->stream, p,
+                         (uint32_t)s.n_rows, (uint32_t)s.n_bits, (uint32_t)s.n_groups,
+                         (uint32_t)s.n_steps, (uint32_t)pl.gpw);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     return QK_OK;
@@ -1791,9 +1895,9 @@ qk_status qk_layer_apply_noalloc(qk_ctx *ctx, const qk_layer *layer, const float
     StageMeta *meta = reinterpret_cast<StageMeta *>(scratch + kNoAllocMaxRank * sizeof(double));
     const bool bf16 = layer->serving == QK_BF16;
     StageParams a{layer->vbt, layer->vbt_tiles, x_dev, layer->s2, t_buf, nullptr, nullptr, nullptr,
-                  meta};
+                  meta, nullptr, (uint32_t)layer->r, (uint32_t)layer->din};
     StageParams b{layer->ub, layer->ub_tiles, t_buf, nullptr, y_dev, layer->s1, layer->bias, nullptr,
-                  meta + 1};
+                  meta + 1, nullptr, (uint32_t)layer->dout, (uint32_t)layer->r};
     if ((st = launch_value_stage<false>(c, a, s1, bf16)) != QK_OK) return st;
     return launch_value_stage<true>(c, b, s2, bf16);
 }

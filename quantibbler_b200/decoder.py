@@ -20,7 +20,7 @@ from dataclasses import dataclass
 import numpy as np
 
 from . import _lib, tp
-from ._lib import QK_BF16, QK_F32, check
+from ._lib import QK_BF16, QK_F32, KernelError, check
 from .gpu import GpuContext, LayerPlan, PackedLayer, apply_prefill_many
 
 LINEARS = ("q", "k", "v", "o", "gate", "up", "down")
@@ -251,15 +251,22 @@ class Decoder:
                 return [(L[n], rows(src, b), rows(dst, b)) for b in range(B)
                         for n, dst in zip(names, dsts)]
 
-            plan = {"q": LayerPlan(ctx, inst(["q"], self.h, [self.q])),
-                    "o": LayerPlan(ctx, inst(["o"], self.attn, [self.delta_attn])),
-                    "down": LayerPlan(ctx, inst(["down"], self.a, [self.delta_mlp]))}
+            # down reads SwiGLU(gate, up) directly: no separate activation pass
+            plan = {"o": LayerPlan(ctx, inst(["o"], self.attn, [self.delta_attn])),
+                    "down": LayerPlan(ctx, [(L["down"], rows(self.g, b), rows(self.u, b),
+                                             rows(self.delta_mlp, b)) for b in range(B)], gated=True)}
             same_kv = all(getattr(L["k"], f) == getattr(L["v"], f) for f in ("dout", "din", "r"))
-            if same_kv:
-                plan["kv"] = LayerPlan(ctx, inst(["k", "v"], self.h, [self.k, self.v]))
-            else:
-                plan["k"] = LayerPlan(ctx, inst(["k"], self.h, [self.k]))
-                plan["v"] = LayerPlan(ctx, inst(["v"], self.h, [self.v]))
+            try:
+                # q, k and v in one pair of launches although q differs in shape: possible
+                # while the plan is small enough for the few-instance kernel form
+                plan["qkv"] = LayerPlan(ctx, inst(["q", "k", "v"], self.h, [self.q, self.k, self.v]))
+            except KernelError:
+                plan["q"] = LayerPlan(ctx, inst(["q"], self.h, [self.q]))
+                if same_kv:
+                    plan["kv"] = LayerPlan(ctx, inst(["k", "v"], self.h, [self.k, self.v]))
+                else:
+                    plan["k"] = LayerPlan(ctx, inst(["k"], self.h, [self.k]))
+                    plan["v"] = LayerPlan(ctx, inst(["v"], self.h, [self.v]))
             same_gu = all(getattr(L["gate"], f) == getattr(L["up"], f)
                           for f in ("dout", "din", "r"))
             if same_gu:
@@ -332,9 +339,12 @@ class Decoder:
                                [dst.data_ptr() for dst in dsts])
             return
         plan = self.plans[li]
-        joint = {("k", "v"): "kv", ("gate", "up"): "gu"}.get(tuple(names))
+        joint = {("q", "k", "v"): "qkv", ("k", "v"): "kv", ("gate", "up"): "gu"}.get(tuple(names))
         if joint in plan:
             plan[joint].apply()
+        elif tuple(names) == ("q", "k", "v"):
+            self._linears(li, ["q"], src, dsts[:1])
+            self._linears(li, ["k", "v"], src, dsts[1:])
         else:
             for name in names:
                 plan[name].apply()
@@ -350,11 +360,7 @@ class Decoder:
         for li in range(cfg.n_layers):
             in_w, post_w = self.norms[li]
             self._norm(pending, in_w)
-            if self.use_gemm:
-                self._linears(li, ["q", "k", "v"], self.h, [self.q, self.k, self.v])
-            else:
-                self._linears(li, ["q"], self.h, [self.q])
-                self._linears(li, ["k", "v"], self.h, [self.k, self.v])
+            self._linears(li, ["q", "k", "v"], self.h, [self.q, self.k, self.v])
             if self.qk_norms[li] is not None:
                 # every head is one row of head_dim values; x_out = x rewrites the projection
                 # unchanged (the kernel's usual in-place form)
@@ -374,7 +380,9 @@ class Decoder:
             self._all_reduce(self.delta_attn)
             self._norm(0, post_w)
             self._linears(li, ["gate", "up"], self.h, [self.g, self.u])
-            check(lib.qk_swiglu(c, _p(self.g), _p(self.u), B * self.ff_loc, _p(self.a)))
+            if self.use_gemm:
+                check(lib.qk_swiglu(c, _p(self.g), _p(self.u), B * self.ff_loc, _p(self.a)))
+            # (the GEMV path's down plan applies the SwiGLU to gate and up as it reads them)
             self._linears(li, ["down"], self.a, [self.delta_mlp])
             self._all_reduce(self.delta_mlp)
             pending = 1

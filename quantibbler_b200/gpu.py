@@ -213,6 +213,15 @@ def _set_wait_limit(self, polls: int) -> int:
 GpuContext.set_wait_limit = _set_wait_limit
 
 
+def _set_dependent_launch(self, on: bool) -> bool:
+    """Programmatic dependent launch of the decoder-path kernels (default on); returns the
+    previous setting."""
+    return bool(_lib.lib().qk_set_dependent_launch(self._h, int(bool(on))))
+
+
+GpuContext.set_dependent_launch = _set_dependent_launch
+
+
 class PackedLayer:
     """Device-resident factorized linear (engine/mod.rs:313-381).
 
@@ -409,18 +418,26 @@ class HostLayerGroup:
 
 
 class LayerPlan(LayerGroup):
-    """Instances (layer, x pointer, y pointer) of one shape bound once; ``apply`` is two
-    kernel launches (one when there are at least as many instances as SMs)."""
+    """Instances (layer, x pointer, y pointer) bound once; ``apply`` is two kernel launches
+    (one when there are at least as many instances as SMs).  The layers may differ in shape
+    while the plan is small (q beside k and v at a small batch).  With ``gated`` the instances
+    are (layer, gate pointer, up pointer, y pointer) and the layer is applied to
+    SwiGLU(gate, up)."""
 
-    def __init__(self, ctx: GpuContext, instances):
+    def __init__(self, ctx: GpuContext, instances, gated: bool = False):
         self.ctx = ctx
         self.layers = [i[0] for i in instances]
         n = len(instances)
         larr = (ctypes.c_void_p * n)(*[i[0].handle for i in instances])
         xarr = (ctypes.c_void_p * n)(*[ctypes.c_void_p(i[1]) for i in instances])
-        yarr = (ctypes.c_void_p * n)(*[ctypes.c_void_p(i[2]) for i in instances])
+        yarr = (ctypes.c_void_p * n)(*[ctypes.c_void_p(i[-1]) for i in instances])
         h = ctypes.c_void_p()
-        check(_lib.lib().qk_plan_create(ctx.handle, larr, xarr, yarr, n, ctypes.byref(h)))
+        if gated:
+            uarr = (ctypes.c_void_p * n)(*[ctypes.c_void_p(i[2]) for i in instances])
+            check(_lib.lib().qk_plan_create_gated(ctx.handle, larr, xarr, uarr, yarr, n,
+                                                  ctypes.byref(h)))
+        else:
+            check(_lib.lib().qk_plan_create(ctx.handle, larr, xarr, yarr, n, ctypes.byref(h)))
         self._h = h
 
 

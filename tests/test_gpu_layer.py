@@ -327,6 +327,58 @@ def test_streaming_form_nonfinite_and_zero_inputs(gpu_ctx):
     group.close()
 
 
+@pytest.mark.parametrize("serving", ["float32", "bfloat16"])
+def test_plan_of_mixed_shapes_and_gated_input(gpu_ctx, serving):
+    """q beside k and v in one plan although their shapes differ, and a plan whose input is
+    SwiGLU(gate, up): both must give the bits of the plain single-layer calls."""
+    import torch
+    from quantibbler_b200.gpu import LayerPlan
+    din = 1100
+    shapes = [(520, 300), (130, 70), (130, 70)]   # (dout, r): "q", "k", "v"
+    specs = [make_layer(dout, din, r, seed=60 + i, with_bias=(i == 1)) for i, (dout, r) in enumerate(shapes)]
+    layers = [PackedLayer(gpu_ctx, s["ub_rows"], s["vb_t_rows"], s["dout"], din, s["r"], s["s1"],
+                          s["s2"], s["bias"], serving=serving) for s in specs]
+    rng = np.random.default_rng(8)
+    n_tok = 2
+    xs = rng.standard_normal((n_tok, din)).astype(np.float32)
+    x = torch.from_numpy(xs).cuda()
+    outs = [torch.full((n_tok, s["dout"]), float("nan"), device="cuda") for s in specs]
+    torch.cuda.synchronize()
+    plan = LayerPlan(gpu_ctx, [(layers[i], x[b].data_ptr(), outs[i][b].data_ptr())
+                               for b in range(n_tok) for i in range(3)])
+    plan.apply()
+    gpu_ctx.synchronize()
+    for i in range(3):
+        for b in range(n_tok):
+            assert np.array_equal(outs[i][b].cpu().numpy(), layers[i].apply(xs[b])), (i, b)
+    # gated: "down" applied to SwiGLU(gate, up)
+    L = make_layer(96, 700, 130, seed=70)
+    down = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], 96, 700, 130, L["s1"], L["s2"], None,
+                       serving=serving)
+    gate = rng.standard_normal((n_tok, 700)).astype(np.float32) * 3
+    up = rng.standard_normal((n_tok, 700)).astype(np.float32)
+    tg, tu = torch.from_numpy(gate).cuda(), torch.from_numpy(up).cuda()
+    y = torch.full((n_tok, 96), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    gated = LayerPlan(gpu_ctx, [(down, tg[b].data_ptr(), tu[b].data_ptr(), y[b].data_ptr())
+                                for b in range(n_tok)], gated=True)
+    gated.apply()
+    gpu_ctx.synchronize()
+    act = (tg * tu / (1.0 + torch.exp(-tg))).cpu().numpy()   # float32, the order the kernels use
+    for b in range(n_tok):
+        want = down.apply(act[b])
+        got = y[b].cpu().numpy()
+        # torch's exp and the device's expf may differ in the last bit of an activation
+        assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max() + (2e-2 * np.abs(want).max() if serving == "bfloat16" else 0)
+        ref = oracle.layer_apply(L["ub_rows"], L["vb_t_rows"], 96, 700, 130, L["s1"], L["s2"], None,
+                                 act[b], serving=serving)
+        assert np.abs(got - ref).max() <= (2e-5 if serving == "float32" else 2e-2) * np.abs(ref).max()
+    # too many instances of different shapes do not fit the few-instance form
+    with pytest.raises(ValueError, match="few-instance form"):
+        big = [(layers[i % 3], x[0].data_ptr(), outs[i % 3][0].data_ptr()) for i in range(3000)]
+        LayerPlan(gpu_ctx, big)
+
+
 def test_multi_token_apply(gpu_ctx):
     import torch
     L = make_layer(96, 160, 72, seed=11, with_bias=True)
