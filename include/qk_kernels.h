@@ -288,6 +288,27 @@ qk_status qk_plan_create_gated(qk_ctx *ctx, const qk_layer *const *layers,
                                float *const *y_ptrs, size_t n_inst, qk_group **out);
 qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group);
 void qk_group_free(qk_group *group);
+/* ---- fed plans ------------------------------------------------------------------
+ * At a small batch the cost of a GEMV launch is not its weight bits but what every one of
+ * its blocks does first: scan the input vector, put it on a fixed-point grid, build the
+ * digit table it multiplies with.  A fed plan moves that work to where the vector is
+ * produced, once per vector: qk_plan_feed_targets turns a plan into a fed plan and returns a
+ * device array with one target per instance (in instance order); the *_feed forms of the
+ * norm, SwiGLU and decode-attention calls below take such arrays and write the tables of
+ * the plan's stage-1 inputs along with their own output; stage 1 hands over to stage 2 the
+ * same way (its last block to finish builds the table of the intermediate).  A fed plan's
+ * stage kernels never read the x pointers the plan was created with.  Every apply of a fed
+ * plan must be preceded, on the same stream, by a *_feed call that names its targets.  Plans
+ * too large for the few-instance kernel form are refused with QK_ERR_VALUE.  No reference
+ * counterpart (the reference recomputes nothing because it has no device). */
+typedef struct qk_feed {
+    const void *targets[4]; /* arrays returned by qk_plan_feed_targets */
+    size_t per_token[4];    /* consecutive targets of array i that read token t: [t*per_token, ...) */
+    size_t n_arrays;
+} qk_feed;
+qk_status qk_plan_feed_targets(qk_ctx *ctx, qk_group *plan, const void **targets_dev,
+                               size_t *n_targets);
+
 /* ---- decoder-side kernels on device buffers -----------------------------------
  * What one transformer block needs around its linears.  All are launch-only on the
  * context's stream (no allocation, no synchronisation), so a whole decode step can be
@@ -299,6 +320,10 @@ void qk_group_free(qk_group *group);
 qk_status qk_rmsnorm(qk_ctx *ctx, const float *x, const float *residual, const float *weight,
                      size_t n_tokens, size_t d, float eps, int32_t serving_dtype, float *x_out,
                      float *y);
+/* qk_rmsnorm that also writes the digit tables of the linears that read y (fed plans). */
+qk_status qk_rmsnorm_feed(qk_ctx *ctx, const float *x, const float *residual, const float *weight,
+                          size_t n_tokens, size_t d, float eps, int32_t serving_dtype, float *x_out,
+                          float *y, const qk_feed *feed);
 /* Tensor parallel: RMSNorm whose residual input is the SUM over ranks of the row-parallel
  * linears' partial outputs - the all-reduce after the o and down projections fused into the
  * norm that follows it.  Every rank pushes its partial into an inbox in each peer's memory
@@ -317,6 +342,10 @@ qk_status qk_allreduce_rmsnorm(qk_ctx *ctx, const float *partial, const uint64_t
                                uint32_t *state_dev, int32_t rank, int32_t world, const float *x,
                                const float *weight, size_t n_tokens, size_t d, float eps,
                                int32_t serving_dtype, float *x_out, float *y);
+qk_status qk_allreduce_rmsnorm_feed(qk_ctx *ctx, const float *partial, const uint64_t *peer_inbox,
+                                    uint32_t *state_dev, int32_t rank, int32_t world, const float *x,
+                                    const float *weight, size_t n_tokens, size_t d, float eps,
+                                    int32_t serving_dtype, float *x_out, float *y, const qk_feed *feed);
 /* engine/mod.rs:1169-1184 (rope_rotate) and :1204-1209 (KvCache::push).  Rotates q
  * [tokens, n_heads*d] in place and writes the rotated k and v [tokens, n_kv*d] into the
  * head-major cache [n_seq, n_kv, s_max, d] (float32 or bfloat16) at row positions[t] of
@@ -338,8 +367,32 @@ qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
                               const void *cache_v, int32_t kv_dtype, const int32_t *kv_len,
                               size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
                               size_t s_max, size_t n_splits, float *scratch, float *out);
+/* qk_decode_attention whose combine step also writes the digit tables of the linears that
+ * read `out` (the o projection of a fed plan); serving_dtype is that of those linears. */
+qk_status qk_decode_attention_feed(qk_ctx *ctx, const float *q, const void *cache_k,
+                                   const void *cache_v, int32_t kv_dtype, const int32_t *kv_len,
+                                   size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                                   size_t s_max, size_t n_splits, float *scratch, float *out,
+                                   int32_t serving_dtype, const qk_feed *feed);
+/* The attention of a batched prompt prefill: engine/mod.rs:1393-1413 feeds the prompt one
+ * position at a time through gqa_attention (:1074-1121); here n_tokens consecutive positions
+ * first_position .. first_position+n_tokens-1 of sequence `seq` attend causally, each to the
+ * cache rows 0 .. its own position (qk_rope_cache has already appended their keys and values).
+ * q and out are float32, token-major [n_tokens, n_heads*head_dim]; the cache is
+ * [n_seq, n_kv_heads, s_max, head_dim].  A bfloat16 cache with head_dim 128 runs on the bf16
+ * tensor cores (q and the softmax weights split into three bfloat16 terms each, float32
+ * accuracy); other shapes take a plain kernel. */
+qk_status qk_prefill_attention(qk_ctx *ctx, const float *q, const void *cache_k, const void *cache_v,
+                               int32_t kv_dtype, size_t seq, size_t first_position, size_t n_tokens,
+                               size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t s_max,
+                               float *out);
 /* engine/mod.rs:931-935: out = g*u/(1+exp(-g)). */
 qk_status qk_swiglu(qk_ctx *ctx, const float *gate, const float *up, size_t n, float *out);
+/* The same activation for n_tokens rows of n values, not written to memory but turned
+ * straight into the digit tables of the linears that consume it (the down projection of a
+ * fed plan). */
+qk_status qk_swiglu_feed(qk_ctx *ctx, const float *gate, const float *up, size_t n_tokens, size_t n,
+                         int32_t serving_dtype, const qk_feed *feed);
 /* engine/mod.rs:921-924: out = a + b. */
 qk_status qk_add(qk_ctx *ctx, const float *a, const float *b, size_t n, float *out);
 /* engine/mod.rs:768-777 (embed): out[t] = table[ids[t]] (float32 or bfloat16 table). */

@@ -82,6 +82,16 @@ _SIGNATURES = {
                                        POINTER(c_void_p), POINTER(c_void_p), c_size_t,
                                        POINTER(c_void_p)]),
     "qk_group_apply": (c_int32, [c_void_p, c_void_p]),
+    "qk_plan_feed_targets": (c_int32, [c_void_p, c_void_p, POINTER(c_void_p), POINTER(c_size_t)]),
+    "qk_rmsnorm_feed": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_float,
+                                  c_int32, c_void_p, c_void_p, c_void_p]),
+    "qk_allreduce_rmsnorm_feed": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
+                                            c_void_p, c_void_p, c_size_t, c_size_t, c_float, c_int32,
+                                            c_void_p, c_void_p, c_void_p]),
+    "qk_decode_attention_feed": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p,
+                                           c_size_t, c_size_t, c_size_t, c_size_t, c_size_t, c_size_t,
+                                           c_void_p, c_void_p, c_int32, c_void_p]),
+    "qk_swiglu_feed": (c_int32, [c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_int32, c_void_p]),
     "qk_group_free": (None, [c_void_p]),
     "qk_rmsnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_float,
                              c_int32, c_void_p, c_void_p]),
@@ -92,6 +102,9 @@ _SIGNATURES = {
     "qk_decode_attention": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p,
                                       c_size_t, c_size_t, c_size_t, c_size_t, c_size_t, c_size_t,
                                       c_void_p, c_void_p]),
+    "qk_prefill_attention": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_size_t,
+                                       c_size_t, c_size_t, c_size_t, c_size_t, c_size_t, c_size_t,
+                                       c_void_p]),
     "qk_swiglu": (c_int32, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "qk_add": (c_int32, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "qk_embed": (c_int32, [c_void_p, c_void_p, c_int32, c_void_p, c_size_t, c_size_t, c_size_t,

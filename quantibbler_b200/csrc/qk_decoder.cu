@@ -19,6 +19,7 @@
 #include <cmath>
 
 #include "qk_common.h"
+#include "qk_digits.cuh"
 
 namespace {
 
@@ -62,6 +63,36 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
     return total;
 }
 
+// Feeding the linears that consume a vector: the kernel that has the whole vector of a token
+// in front of it (norm, SwiGLU, attention combine) also writes the digit tables its consumers'
+// GEMV blocks multiply with - one table per consumer, because each has its own input scale s2
+// (z = s2 * v in float32, rounded to bfloat16 under bfloat16 serving, exactly what the GEMV's
+// own table build forms).  vals: the token's vector in shared memory.
+struct FeedArgs {
+    const FeedTarget *arr[4];   // arrays of targets, token-major: token t owns [t*per_token, (t+1)*per_token)
+    uint32_t per_token[4];
+    uint32_t n;
+};
+__device__ __forceinline__ void feed_consumers(const FeedArgs &feed, uint32_t token, const float *vals,
+                                               bool bf16) {
+    __shared__ double feed_max[32];
+    __shared__ long long feed_sum[32];
+    __shared__ int feed_bad;
+    for (uint32_t a = 0; a < feed.n; ++a)
+        for (uint32_t i = 0; i < feed.per_token[a]; ++i) {
+            const FeedTarget tg = feed.arr[a][(size_t)token * feed.per_token[a] + i];
+            block_build_table(
+                [&](uint32_t k) -> double {
+                    if (k >= tg.n_bits) return 0.0;
+                    float v = vals[k];
+                    if (tg.in_scale) v = tg.in_scale[k] * v;
+                    if (bf16) v = round_bf16f(v);
+                    return (double)v;
+                },
+                tg.n_steps, reinterpret_cast<uint4 *>(tg.digits), tg.meta, feed_max, feed_sum, &feed_bad);
+        }
+}
+
 // h = x (+ residual); x_out = h; y = h * rsqrt(mean(h^2) + eps) * w.  One block per token.
 // The row stays in registers between the two passes (up to kRmsPerThread elements per thread;
 // wider rows re-read the overflow), so the kernel is one round of loads, one block-wide sum
@@ -70,9 +101,10 @@ constexpr int kRmsThreads = 512, kRmsPerThread = 16;
 __global__ void __launch_bounds__(kRmsThreads)
 rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
                const float *__restrict__ w, float *__restrict__ x_out, float *__restrict__ y,
-               uint32_t d, float eps, int bf16) {
+               uint32_t d, float eps, int bf16, FeedArgs feed) {
     qk::pdl_launch();  // the next kernel may begin its prologue
     qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
+    extern __shared__ float norm_row[];  // the token's y (only when consumers are fed)
     __shared__ float red[kRmsThreads / 32];
     const size_t base = (size_t)blockIdx.x * d;
     float keep[kRmsPerThread];
@@ -102,16 +134,24 @@ rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
     for (int r = 0; r < kRmsPerThread; ++r) {
         const uint32_t i = threadIdx.x + r * kRmsThreads;
         if (i < d) {
-            const float o = keep[r] * inv * w[i];
-            y[base + i] = bf16 ? round_bf16f(o) : o;
+            float o = keep[r] * inv * w[i];
+            if (bf16) o = round_bf16f(o);
+            y[base + i] = o;
+            if (feed.n) norm_row[i] = o;
         }
     }
     for (uint32_t i = threadIdx.x + kRmsPerThread * kRmsThreads; i < d; i += kRmsThreads) {
         // x_out (or x, when the sum was not written back) holds h
         float h = x_out ? x_out[base + i] : x[base + i] + (residual ? residual[base + i] : 0.f);
         if (bf16) h = round_bf16f(h);
-        const float o = h * inv * w[i];
-        y[base + i] = bf16 ? round_bf16f(o) : o;
+        float o = h * inv * w[i];
+        if (bf16) o = round_bf16f(o);
+        y[base + i] = o;
+        if (feed.n) norm_row[i] = o;
+    }
+    if (feed.n) {
+        __syncthreads();
+        feed_consumers(feed, blockIdx.x, norm_row, bf16 != 0);
     }
 }
 
@@ -145,9 +185,10 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
                          uint32_t *__restrict__ counter, uint32_t *__restrict__ done, int rank,
                          int world, const float *__restrict__ x, const float *__restrict__ w,
                          float *__restrict__ x_out, float *__restrict__ y, uint32_t d, float eps,
-                         int bf16, int *__restrict__ error, uint32_t poll_limit) {
+                         int bf16, int *__restrict__ error, uint32_t poll_limit, FeedArgs feed) {
     qk::pdl_launch();  // the next kernel may begin its prologue
     qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
+    extern __shared__ float norm_row[];  // the token's y (only when consumers are fed)
     __shared__ float red[kRmsThreads / 32];
     __shared__ int gave_up;
     const uint32_t step = *counter + 1;
@@ -237,8 +278,14 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
                 h = x_out[base + i];
                 if (bf16) h = round_bf16f(h);
             }
-            const float o = h * inv * w[i];
-            y[base + i] = bf16 ? round_bf16f(o) : o;
+            float o = h * inv * w[i];
+            if (bf16) o = round_bf16f(o);
+            y[base + i] = o;
+            if (feed.n) norm_row[i] = o;
+        }
+        if (feed.n) {
+            __syncthreads();
+            feed_consumers(feed, blockIdx.x, norm_row, bf16 != 0);
         }
     }
     // the last block to finish records that this all-reduce is done (every block has read the
@@ -694,6 +741,287 @@ decode_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__restr
     }
 }
 
+// ------------------------------------------------------------------ prefill attention, tensor cores
+// Causal attention of T new positions of ONE sequence against the cache (which already holds
+// their own keys and values): the attention of a batched prompt prefill.  Same contract as the
+// decode kernels - exact softmax(q k^T / sqrt(d)) v in float32 accuracy, engine/mod.rs:1074-1121
+// applied at every position - with both products on the bf16 tensor cores (mma.sync m16n8k16):
+// the cache is bfloat16, so K and V are exact operands; q and P are float32 and are split
+// into three bfloat16 terms each (hi + mid + lo reproduces the value to 2^-25), one MMA per
+// term, which keeps the 1e-5 gate against the float64 oracle.
+//   q, out : float32, token-major [T][n_heads][128] (the decoder's activation layout)
+//   cache  : bfloat16 [n_seq][n_kv][s_max][128]; the queries are positions p0 .. p0+T-1 of
+//            sequence `seq`, query i sees keys 0 .. p0+i.
+// A CTA of four warps owns 64 query rows that share one kv head: `hw` = min(group, 4) query
+// heads times 4/hw blocks of 16 positions, one (head, position block) per warp, so that a K/V
+// tile staged in shared memory serves the whole GQA group.  Q is split once into its three
+// terms in shared memory; K/V tiles of 32 keys are double-buffered with cp.async; all
+// fragments come from ldmatrix (row pitch 272 bytes: conflict-free).
+constexpr int kPfKeys = 32, kPfPitch = 136;  // keys per tile; bf16 elements per staged row
+constexpr int kPfQBytes = 3 * 64 * kPfPitch * 2, kPfTileBytes = kPfKeys * kPfPitch * 2;
+constexpr int kPfSmem = kPfQBytes + 4 * kPfTileBytes;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_full(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(128)
+prefill_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict__ cache_k,
+                             const uint16_t *__restrict__ cache_v, float *__restrict__ out,
+                             uint32_t n_tokens, uint32_t p0, uint32_t seq, uint32_t n_heads, uint32_t n_kv,
+                             uint32_t hw, uint32_t s_max) {
+    qk::pdl_launch();
+    qk::pdl_wait();
+    constexpr uint32_t d = 128;
+    extern __shared__ __align__(16) uint8_t pf_smem[];
+    uint16_t *Qs = reinterpret_cast<uint16_t *>(pf_smem);                 // [3][64][pitch]
+    uint8_t *tiles = pf_smem + kPfQBytes;                                 // [2 buffers][K, V][32][pitch]
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
+    const uint32_t group = n_heads / n_kv, subs = group / hw;             // CTAs per kv head and position range
+    const uint32_t kvh = blockIdx.y / subs, hsub = blockIdx.y % subs;
+    const uint32_t pbs = 4 / hw;                                          // 16-position blocks per CTA
+    const uint32_t head = kvh * group + hsub * hw + warp % hw;
+    const uint32_t tok0 = (blockIdx.x * pbs + warp / hw) * 16;            // this warp's first token
+    const uint32_t cta_tok_end = min(n_tokens, (blockIdx.x + 1) * pbs * 16);
+    const uint32_t n_tiles = (p0 + cta_tok_end + kPfKeys - 1) / kPfKeys;  // keys 0 .. p0 + last token
+    const float scale = 1.0f / sqrtf((float)d);
+
+    const uint16_t *kb = cache_k + ((size_t)seq * n_kv + kvh) * s_max * d;
+    const uint16_t *vb = cache_v + ((size_t)seq * n_kv + kvh) * s_max * d;
+    auto fetch = [&](uint32_t jt, uint32_t buf) {
+        uint8_t *kt = tiles + buf * 2 * kPfTileBytes, *vt = kt + kPfTileBytes;
+        // 32 keys x 16 pieces of 16 bytes, for K and for V: 8 of each per thread
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t idx = threadIdx.x + 128 * i, key = idx / 16, piece = idx % 16;
+            const uint32_t j = jt * kPfKeys + key;
+            const uint32_t src_j = min(j, s_max - 1);              // a valid address even when unused
+            const uint32_t bytes = j < p0 + cta_tok_end ? 16u : 0u;  // 0: zero-filled
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                             (uint32_t)__cvta_generic_to_shared(kt + (key * kPfPitch + piece * 8) * 2)),
+                         "l"(kb + (size_t)src_j * d + piece * 8), "r"(bytes)
+                         : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                             (uint32_t)__cvta_generic_to_shared(vt + (key * kPfPitch + piece * 8) * 2)),
+                         "l"(vb + (size_t)src_j * d + piece * 8), "r"(bytes)
+                         : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(0, 0);
+
+    // ---- this warp's 16 query rows, scaled and split into three bfloat16 terms
+    for (uint32_t idx = lane; idx < 16 * (d / 4); idx += 32) {
+        const uint32_t r = idx / (d / 4), c4 = idx % (d / 4);
+        const uint32_t tok = min(tok0 + r, n_tokens - 1);
+        const float4 v = *reinterpret_cast<const float4 *>(q + ((size_t)tok * n_heads + head) * d + c4 * 4);
+        const float x[4] = {v.x * scale, v.y * scale, v.z * scale, v.w * scale};
+        uint32_t e[4][3];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) split3(x[i], e[i][0], e[i][1], e[i][2]);
+#pragma unroll
+        for (int term = 0; term < 3; ++term) {
+            uint2 packed = make_uint2(e[0][term] | (e[1][term] << 16), e[2][term] | (e[3][term] << 16));
+            *reinterpret_cast<uint2 *>(Qs + ((size_t)term * 64 + warp * 16 + r) * kPfPitch + c4 * 4) = packed;
+        }
+    }
+    __syncwarp();
+
+    float o[16][4];
+#pragma unroll
+    for (int nd = 0; nd < 16; ++nd) o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.f;
+    float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
+    const int pos_g = (int)(p0 + tok0 + g), pos_h = pos_g + 8;   // positions of rows g and g + 8
+    const uint32_t warp_last = p0 + min(tok0 + 15, n_tokens - 1);  // last key any row of this warp sees
+    const uint32_t q_addr0 = (uint32_t)__cvta_generic_to_shared(
+        Qs + ((size_t)warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kPfPitch + (lane >> 4) * 8);
+
+    for (uint32_t jt = 0; jt < n_tiles; ++jt) {
+        const uint32_t buf = jt & 1;
+        if (jt + 1 < n_tiles) {
+            fetch(jt + 1, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();  // tile jt has landed for every thread
+        const uint32_t j0 = jt * kPfKeys;
+        if (tok0 < n_tokens && j0 <= warp_last) {  // warp-uniform: the tile holds keys this warp sees
+            const uint32_t kt_addr = (uint32_t)__cvta_generic_to_shared(tiles + buf * 2 * kPfTileBytes);
+            const uint32_t vt_addr = kt_addr + kPfTileBytes;
+            // ---- S = q k^T for 32 keys: four 8-key tiles
+            float sacc[4][4];
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t kf[2][4];  // B fragments of key tiles (0,1) and (2,3) for this k-step
+#pragma unroll
+                for (int pair = 0; pair < 2; ++pair)
+                    ldsm_x4(kf[pair], kt_addr + (((2 * pair + (lane >> 4)) * 8 + (lane & 7)) * kPfPitch +
+                                                 ks * 16 + ((lane >> 3) & 1) * 8) * 2);
+#pragma unroll
+                for (int term = 0; term < 3; ++term) {
+                    uint32_t a[4];
+                    ldsm_x4(a, q_addr0 + (term * 64 * kPfPitch + ks * 16) * 2);
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt)
+                        mma_bf16_full(sacc[nt], a, kf[nt / 2][(nt % 2) * 2], kf[nt / 2][(nt % 2) * 2 + 1]);
+                }
+            }
+            // ---- causal mask and online softmax (rows g and g + 8; columns 2t, 2t+1 of each tile)
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = (int)j0 + 8 * nt + 2 * (int)t + (e & 1);
+                    const int pos = e < 2 ? pos_g : pos_h;
+                    if (j > pos) sacc[nt][e] = -INFINITY;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], sacc[nt][e]);
+                }
+            float alpha[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_row[r], mx[r]);
+                // a row that has seen no admissible key yet keeps m = -inf; exp(-inf - finite) = 0
+                alpha[r] = m_new == -INFINITY ? 1.f : expf(m_row[r] - m_new);
+                m_row[r] = m_new;
+            }
+            uint32_t pa[3][2][4];  // [term][16-key step][A fragment]
+            float psum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                float p[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float mr = m_row[e >> 1];
+                    p[e] = mr == -INFINITY ? 0.f : expf(sacc[nt][e] - mr);
+                    psum[e >> 1] += p[e];
+                }
+                uint32_t e0[3], e1[3], e2[3], e3[3];
+                split3(p[0], e0[0], e0[1], e0[2]);
+                split3(p[1], e1[0], e1[1], e1[2]);
+                split3(p[2], e2[0], e2[1], e2[2]);
+                split3(p[3], e3[0], e3[1], e3[2]);
+#pragma unroll
+                for (int term = 0; term < 3; ++term) {
+                    pa[term][nt / 2][(nt % 2) * 2] = e0[term] | (e1[term] << 16);      // row g
+                    pa[term][nt / 2][(nt % 2) * 2 + 1] = e2[term] | (e3[term] << 16);  // row g + 8
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) l_row[r] = l_row[r] * alpha[r] + psum[r];
+#pragma unroll
+            for (int nd = 0; nd < 16; ++nd) {
+                o[nd][0] *= alpha[0];
+                o[nd][1] *= alpha[0];
+                o[nd][2] *= alpha[1];
+                o[nd][3] *= alpha[1];
+            }
+            // ---- O += P V: two 16-key steps, sixteen 8-channel tiles
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+                for (int nd = 0; nd < 16; nd += 2) {
+                    uint32_t vf[4];  // B fragments of channel tiles nd and nd + 1
+                    ldsm_x4_trans(vf, vt_addr + ((kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * kPfPitch +
+                                                 (nd + (lane >> 4)) * 8) * 2);
+#pragma unroll
+                    for (int term = 0; term < 3; ++term) {
+                        mma_bf16_full(o[nd], pa[term][kk], vf[0], vf[1]);
+                        mma_bf16_full(o[nd + 1], pa[term][kk], vf[2], vf[3]);
+                    }
+                }
+        }
+        __syncthreads();  // the buffer may be refilled by the next iteration's fetch
+    }
+    // ---- normalise and store (token-major)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 1);
+        l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 2);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const uint32_t tok = tok0 + g + 8 * r;
+        if (tok >= n_tokens) continue;
+        float *orow = out + ((size_t)tok * n_heads + head) * d;
+        const float inv = 1.0f / l_row[r];
+#pragma unroll
+        for (int nd = 0; nd < 16; ++nd)
+            *reinterpret_cast<float2 *>(orow + nd * 8 + 2 * t) =
+                make_float2(o[nd][2 * r] * inv, o[nd][2 * r + 1] * inv);
+    }
+}
+
+// The same attention for any head size and cache dtype: one warp per (token, head), the
+// lanes share the channels, online softmax in float32.  The fallback of the tensor-core
+// kernel above (small models, float32 caches); not meant to be fast.
+template <typename KV>
+__global__ void __launch_bounds__(128)
+prefill_attention_simple_kernel(const float *__restrict__ q, const KV *__restrict__ cache_k,
+                                const KV *__restrict__ cache_v, float *__restrict__ out,
+                                uint32_t n_tokens, uint32_t p0, uint32_t seq, uint32_t n_heads,
+                                uint32_t n_kv, uint32_t d, uint32_t s_max) {
+    qk::pdl_launch();
+    qk::pdl_wait();
+    const uint32_t row = blockIdx.x * 4 + threadIdx.x / 32, lane = threadIdx.x % 32;
+    if (row >= n_tokens * n_heads) return;
+    const uint32_t tok = row / n_heads, head = row % n_heads, kvh = head / (n_heads / n_kv);
+    const float *qr = q + (size_t)row * d;
+    const KV *kb = cache_k + ((size_t)seq * n_kv + kvh) * s_max * d;
+    const KV *vb = cache_v + ((size_t)seq * n_kv + kvh) * s_max * d;
+    const float scale = 1.0f / sqrtf((float)d);
+    float qv[8], o[8];  // channels lane, lane + 32, ... (head_dim <= 256)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const uint32_t c = lane + 32 * e;
+        qv[e] = c < d ? qr[c] : 0.f;
+        o[e] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    for (uint32_t j = 0; j <= p0 + tok; ++j) {
+        float dot = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const uint32_t c = lane + 32 * e;
+            if (c < d) dot = fmaf(qv[e], load_as_float<KV>(kb, (size_t)j * d + c), dot);
+        }
+        for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+        const float sc = dot * scale, m_new = fmaxf(m, sc);
+        const float alpha = expf(m - m_new), pj = expf(sc - m_new);
+        l = l * alpha + pj;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const uint32_t c = lane + 32 * e;
+            if (c < d) o[e] = o[e] * alpha + pj * load_as_float<KV>(vb, (size_t)j * d + c);
+        }
+        m = m_new;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const uint32_t c = lane + 32 * e;
+        if (c < d) out[(size_t)row * d + c] = o[e] / l;
+    }
+}
+
 // out[b, h, :] = sum_s o_s * exp(m_s - m) / sum_s l_s * exp(m_s - m).  One block per (b, h).
 __global__ void __launch_bounds__(128)
 decode_combine_kernel(const float *__restrict__ partial, float *__restrict__ out, uint32_t d,
@@ -735,6 +1063,59 @@ __global__ void swiglu_kernel(const float *__restrict__ g, const float *__restri
         float gv = g[i];
         out[i] = gv * u[i] / (1.0f + expf(-gv));
     }
+}
+
+// SwiGLU of one token's gate and up vectors, kept in shared memory, and the digit tables of
+// the linears that consume it (the down projection): no activation vector goes to memory.
+__global__ void __launch_bounds__(512)
+swiglu_feed_kernel(const float *__restrict__ g, const float *__restrict__ u, uint32_t n, int bf16,
+                   FeedArgs feed) {
+    qk::pdl_launch();
+    qk::pdl_wait();
+    extern __shared__ float act_row[];
+    const size_t base = (size_t)blockIdx.x * n;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const float gv = g[base + i];
+        act_row[i] = gv * u[base + i] / (1.0f + expf(-gv));
+    }
+    __syncthreads();
+    feed_consumers(feed, blockIdx.x, act_row, bf16 != 0);
+}
+
+// The combine of the split-KV decode attention for ALL heads of one sequence in one block
+// (a warp per head at a time), followed by the digit tables of the linears that consume the
+// attention output (the o projection).
+__global__ void __launch_bounds__(512)
+decode_combine_feed_kernel(const float *__restrict__ partial, float *__restrict__ out, uint32_t n_heads,
+                           uint32_t d, uint32_t n_splits, int bf16, FeedArgs feed) {
+    qk::pdl_launch();
+    qk::pdl_wait();
+    extern __shared__ float attn_row[];  // [n_heads * d]
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, n_warps = blockDim.x / 32;
+    for (uint32_t h = warp; h < n_heads; h += n_warps) {
+        const float *p = partial + ((size_t)blockIdx.x * n_heads + h) * n_splits * (d + 2);
+        float mm = -INFINITY;
+        for (uint32_t s2 = lane; s2 < n_splits; s2 += 32) mm = fmaxf(mm, p[s2 * (d + 2)]);
+        for (int off = 16; off > 0; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
+        float ll = 0.f;
+        for (uint32_t s2 = lane; s2 < n_splits; s2 += 32) {
+            const float ms = p[s2 * (d + 2)];
+            ll += p[s2 * (d + 2) + 1] * (ms == -INFINITY ? 0.f : expf(ms - mm));
+        }
+        for (int off = 16; off > 0; off >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, off);
+        for (uint32_t c = lane; c < d; c += 32) {
+            float oo = 0.f;
+            for (uint32_t s2 = 0; s2 < n_splits; ++s2) {
+                const float ms = p[s2 * (d + 2)];
+                oo += p[s2 * (d + 2) + 2 + c] * (ms == -INFINITY ? 0.f : expf(ms - mm));
+            }
+            const float o = oo / ll;
+            out[((size_t)blockIdx.x * n_heads + h) * d + c] = o;
+            attn_row[h * d + c] = o;
+        }
+    }
+    __syncthreads();
+    feed_consumers(feed, blockIdx.x, attn_row, bf16 != 0);
 }
 
 __global__ void add_kernel(const float *__restrict__ a, const float *__restrict__ b,
@@ -899,6 +1280,20 @@ qk_status enter(qk_ctx *ctx, qk_ctx **c) {
 #define QK_PDL(c, kernel, grid, block, smem, ...) \
     (void)qk::launch_pdl((c)->pdl, kernel, grid, block, smem, (c)->stream, __VA_ARGS__)
 
+// The C ABI's qk_feed -> the kernels' FeedArgs (null: nothing is fed).
+qk_status feed_args(const qk_feed *feed, FeedArgs *out) {
+    *out = FeedArgs{};
+    if (!feed) return QK_OK;
+    if (feed->n_arrays > 4) return qk::fail(QK_ERR_VALUE, "at most 4 target arrays can be fed, got %zu", feed->n_arrays);
+    for (size_t i = 0; i < feed->n_arrays; ++i) {
+        if (!feed->targets[i]) return qk::fail(QK_ERR_VALUE, "feed target array %zu is null", i);
+        out->arr[i] = static_cast<const FeedTarget *>(feed->targets[i]);
+        out->per_token[i] = (uint32_t)feed->per_token[i];
+    }
+    out->n = (uint32_t)feed->n_arrays;
+    return QK_OK;
+}
+
 #define QK_LAUNCHED(c)            \
     QK_CUDA(cudaGetLastError()); \
     (c)->launches++;             \
@@ -1045,17 +1440,27 @@ void launch_lm_head_mma(qk_ctx *c, const uint16_t *hi, const uint16_t *lo, const
 
 extern "C" {
 
-qk_status qk_rmsnorm(qk_ctx *ctx, const float *x, const float *residual, const float *weight,
-                     size_t n_tokens, size_t d, float eps, int32_t serving_dtype, float *x_out,
-                     float *y) {
+qk_status qk_rmsnorm_feed(qk_ctx *ctx, const float *x, const float *residual, const float *weight,
+                          size_t n_tokens, size_t d, float eps, int32_t serving_dtype, float *x_out,
+                          float *y, const qk_feed *feed) {
     qk_ctx *c;
     qk_status st = enter(ctx, &c);
     if (st != QK_OK) return st;
+    FeedArgs fa;
+    if ((st = feed_args(feed, &fa)) != QK_OK) return st;
     if (n_tokens == 0) return QK_OK;
-    QK_PDL(c, rmsnorm_kernel, dim3((unsigned)n_tokens), dim3(kRmsThreads), 0, x, residual, weight, x_out, y,
-                                                              (uint32_t)d, eps,
-                                                              serving_dtype == QK_BF16);
+    const size_t smem = fa.n ? d * sizeof(float) : 0;
+    if (smem > 48 * 1024)
+        QK_CUDA(cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    QK_PDL(c, rmsnorm_kernel, dim3((unsigned)n_tokens), dim3(kRmsThreads), smem, x, residual, weight, x_out, y,
+           (uint32_t)d, eps, serving_dtype == QK_BF16, fa);
     QK_LAUNCHED(c);
+}
+
+qk_status qk_rmsnorm(qk_ctx *ctx, const float *x, const float *residual, const float *weight,
+                     size_t n_tokens, size_t d, float eps, int32_t serving_dtype, float *x_out,
+                     float *y) {
+    return qk_rmsnorm_feed(ctx, x, residual, weight, n_tokens, d, eps, serving_dtype, x_out, y, nullptr);
 }
 
 qk_status qk_rope_cache(qk_ctx *ctx, float *q, const float *k, const float *v,
@@ -1095,13 +1500,33 @@ size_t qk_decode_attention_scratch(size_t batch, size_t n_heads, size_t head_dim
     return batch * n_heads * n_splits * (head_dim + 2) * sizeof(float);
 }
 
-qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
-                              const void *cache_v, int32_t kv_dtype, const int32_t *kv_len,
-                              size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
-                              size_t s_max, size_t n_splits, float *scratch, float *out) {
+qk_status qk_decode_attention_feed(qk_ctx *ctx, const float *q, const void *cache_k,
+                                   const void *cache_v, int32_t kv_dtype, const int32_t *kv_len,
+                                   size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                                   size_t s_max, size_t n_splits, float *scratch, float *out,
+                                   int32_t serving_dtype, const qk_feed *feed) {
     qk_ctx *c;
     qk_status st = enter(ctx, &c);
     if (st != QK_OK) return st;
+    FeedArgs fa;
+    if ((st = feed_args(feed, &fa)) != QK_OK) return st;
+    // the combine step: per (sequence, head), or - when the consumers of the attention output
+    // are fed - one block per sequence that also writes their digit tables
+    auto combine = [&]() -> qk_status {
+        if (fa.n) {
+            const size_t smem = n_heads * head_dim * sizeof(float);
+            if (smem > 200 * 1024)
+                return qk::fail(QK_ERR_VALUE, "%zu attention outputs do not fit shared memory", n_heads * head_dim);
+            QK_CUDA(cudaFuncSetAttribute(decode_combine_feed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem));
+            QK_PDL(c, decode_combine_feed_kernel, dim3((unsigned)batch), dim3(512), smem, (const float *)scratch, out,
+                   (uint32_t)n_heads, (uint32_t)head_dim, (uint32_t)n_splits, serving_dtype == QK_BF16, fa);
+        } else {
+            QK_PDL(c, decode_combine_kernel, dim3((unsigned)(batch * n_heads)), dim3(128), 0, (const float *)scratch,
+                   out, (uint32_t)head_dim, (uint32_t)n_splits);
+        }
+        return QK_OK;
+    };
     if (n_kv_heads == 0 || n_heads % n_kv_heads != 0)
         return qk::fail(QK_ERR_VALUE, "n_kv_heads must divide n_heads: n_heads=%zu, n_kv_heads=%zu",
                         n_heads, n_kv_heads);
@@ -1131,8 +1556,7 @@ qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
             (uint32_t)chunk8, (uint32_t)n_splits);
         QK_CUDA(cudaGetLastError());
         c->launches++;
-        QK_PDL(c, decode_combine_kernel, dim3((unsigned)(batch * n_heads)), dim3(128), 0, 
-            scratch, out, (uint32_t)head_dim, (uint32_t)n_splits);
+        if ((st = combine()) != QK_OK) return st;
         QK_LAUNCHED(c);
     }
     const int gq = group % 4 == 0 ? 4 : group % 2 == 0 ? 2 : 1;  // query heads per block
@@ -1165,8 +1589,78 @@ qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
 #undef QK_DEC
     QK_CUDA(cudaGetLastError());
     c->launches++;
-    QK_PDL(c, decode_combine_kernel, dim3((unsigned)(batch * n_heads)), dim3(128), 0, 
-        scratch, out, (uint32_t)head_dim, (uint32_t)n_splits);
+    if ((st = combine()) != QK_OK) return st;
+    QK_LAUNCHED(c);
+}
+
+qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
+                              const void *cache_v, int32_t kv_dtype, const int32_t *kv_len,
+                              size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                              size_t s_max, size_t n_splits, float *scratch, float *out) {
+    return qk_decode_attention_feed(ctx, q, cache_k, cache_v, kv_dtype, kv_len, batch, n_heads, n_kv_heads,
+                                    head_dim, s_max, n_splits, scratch, out, QK_F32, nullptr);
+}
+
+qk_status qk_prefill_attention(qk_ctx *ctx, const float *q, const void *cache_k, const void *cache_v,
+                               int32_t kv_dtype, size_t seq, size_t first_position, size_t n_tokens,
+                               size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t s_max,
+                               float *out) {
+    qk_ctx *c;
+    qk_status st = enter(ctx, &c);
+    if (st != QK_OK) return st;
+    if (n_kv_heads == 0 || n_heads % n_kv_heads != 0)
+        return qk::fail(QK_ERR_VALUE, "n_kv_heads must divide n_heads: n_heads=%zu, n_kv_heads=%zu",
+                        n_heads, n_kv_heads);
+    const size_t group = n_heads / n_kv_heads;
+    if (kv_dtype != QK_F32 && kv_dtype != QK_BF16)
+        return qk::fail(QK_ERR_VALUE, "KV cache dtype must be float32 or bfloat16, got tag %d", kv_dtype);
+    if (head_dim > 256)
+        return qk::fail(QK_ERR_VALUE, "head_dim above 256 is not supported, got %zu", head_dim);
+    if (n_tokens == 0) return QK_OK;
+    if (first_position + n_tokens > s_max)
+        return qk::fail(QK_ERR_VALUE, "positions %zu..%zu do not fit the KV cache of %zu positions",
+                        first_position, first_position + n_tokens - 1, s_max);
+    if (kv_dtype != QK_BF16 || head_dim != 128 || (group != 1 && group != 2 && group % 4 != 0) ||
+        c->decode_attention_kernel == 0) {
+        // any other shape: the plain kernel
+        const unsigned blocks = (unsigned)qk::ceil_div(n_tokens * n_heads, 4);
+        if (kv_dtype == QK_F32)
+            QK_PDL(c, prefill_attention_simple_kernel<float>, dim3(blocks), dim3(128), 0, q,
+                   (const float *)cache_k, (const float *)cache_v, out, (uint32_t)n_tokens,
+                   (uint32_t)first_position, (uint32_t)seq, (uint32_t)n_heads, (uint32_t)n_kv_heads,
+                   (uint32_t)head_dim, (uint32_t)s_max);
+        else
+            QK_PDL(c, prefill_attention_simple_kernel<uint16_t>, dim3(blocks), dim3(128), 0, q,
+                   (const uint16_t *)cache_k, (const uint16_t *)cache_v, out, (uint32_t)n_tokens,
+                   (uint32_t)first_position, (uint32_t)seq, (uint32_t)n_heads, (uint32_t)n_kv_heads,
+                   (uint32_t)head_dim, (uint32_t)s_max);
+        QK_LAUNCHED(c);
+    }
+    const size_t hw = group < 4 ? group : 4, pbs = 4 / hw;
+    dim3 grid((unsigned)qk::ceil_div(n_tokens, 16 * pbs), (unsigned)(n_kv_heads * (group / hw)));
+    QK_CUDA(cudaFuncSetAttribute(prefill_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kPfSmem));
+    QK_PDL(c, prefill_attention_mma_kernel, grid, dim3(128), (size_t)kPfSmem, q, (const uint16_t *)cache_k,
+           (const uint16_t *)cache_v, out, (uint32_t)n_tokens, (uint32_t)first_position, (uint32_t)seq,
+           (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)hw, (uint32_t)s_max);
+    QK_LAUNCHED(c);
+}
+
+qk_status qk_swiglu_feed(qk_ctx *ctx, const float *gate, const float *up, size_t n_tokens, size_t n,
+                         int32_t serving_dtype, const qk_feed *feed) {
+    qk_ctx *c;
+    qk_status st = enter(ctx, &c);
+    if (st != QK_OK) return st;
+    FeedArgs fa;
+    if ((st = feed_args(feed, &fa)) != QK_OK) return st;
+    if (!fa.n) return qk::fail(QK_ERR_VALUE, "qk_swiglu_feed: nothing to feed");
+    if (n_tokens == 0 || n == 0) return QK_OK;
+    const size_t smem = n * sizeof(float);
+    if (smem > 200 * 1024)
+        return qk::fail(QK_ERR_VALUE, "a row of %zu activations does not fit shared memory", n);
+    QK_CUDA(cudaFuncSetAttribute(swiglu_feed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    QK_PDL(c, swiglu_feed_kernel, dim3((unsigned)n_tokens), dim3(512), smem, gate, up, (uint32_t)n,
+           serving_dtype == QK_BF16, fa);
     QK_LAUNCHED(c);
 }
 
@@ -1284,9 +1778,19 @@ qk_status qk_allreduce_rmsnorm(qk_ctx *ctx, const float *partial, const uint64_t
                                uint32_t *state_dev, int32_t rank, int32_t world, const float *x,
                                const float *weight, size_t n_tokens, size_t d, float eps,
                                int32_t serving_dtype, float *x_out, float *y) {
+    return qk_allreduce_rmsnorm_feed(ctx, partial, peer_inbox, state_dev, rank, world, x, weight, n_tokens, d,
+                                     eps, serving_dtype, x_out, y, nullptr);
+}
+
+qk_status qk_allreduce_rmsnorm_feed(qk_ctx *ctx, const float *partial, const uint64_t *peer_inbox,
+                                    uint32_t *state_dev, int32_t rank, int32_t world, const float *x,
+                                    const float *weight, size_t n_tokens, size_t d, float eps,
+                                    int32_t serving_dtype, float *x_out, float *y, const qk_feed *feed) {
     qk_ctx *c;
     qk_status st = enter(ctx, &c);
     if (st != QK_OK) return st;
+    FeedArgs fa;
+    if ((st = feed_args(feed, &fa)) != QK_OK) return st;
     if (world < 1 || world > 8 || rank < 0 || rank >= world)
         return qk::fail(QK_ERR_VALUE, "qk_allreduce_rmsnorm: rank %d of %d (1..8 ranks)", rank, world);
     if (!partial || !peer_inbox || !state_dev || !x_out)
@@ -1295,9 +1799,13 @@ qk_status qk_allreduce_rmsnorm(qk_ctx *ctx, const float *partial, const uint64_t
     if ((st = qk::error_word(c)) != QK_OK) return st;
     InboxArgs inbox{};
     for (int r = 0; r < world; ++r) inbox.at[r] = reinterpret_cast<unsigned long long *>(peer_inbox[r]);
-    QK_PDL(c, allreduce_rmsnorm_kernel, dim3((unsigned)n_tokens), dim3(kRmsThreads), 0, 
+    const size_t smem = fa.n ? d * sizeof(float) : 0;
+    if (smem > 48 * 1024)
+        QK_CUDA(cudaFuncSetAttribute(allreduce_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem));
+    QK_PDL(c, allreduce_rmsnorm_kernel, dim3((unsigned)n_tokens), dim3(kRmsThreads), smem,
         inbox, partial, state_dev, state_dev + 1, rank, world, x, weight, x_out, y, (uint32_t)d, eps,
-        serving_dtype == QK_BF16, (int *)c->d_err.ptr, c->wait_limit ? c->wait_limit : (1u << 22));
+        serving_dtype == QK_BF16, (int *)c->d_err.ptr, c->wait_limit ? c->wait_limit : (1u << 22), fa);
     c->err_armed = true;
     QK_LAUNCHED(c);
 }

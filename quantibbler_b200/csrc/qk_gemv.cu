@@ -42,15 +42,11 @@
 #include <cstring>
 
 #include "qk_common.h"
+#include "qk_digits.cuh"
 
 namespace {
 
 // ------------------------------------------------------------------ shared helpers
-struct StageMeta {
-    long long total;  // sum_k q_k
-    int shift;        // v_k ~ q_k * 2^-shift
-    int nonfinite;    // the input held a NaN or an infinity
-};
 
 // One (layer, token) instance of one stage.
 struct StageParams {
@@ -65,14 +61,14 @@ struct StageParams {
     StageMeta *meta;
     const float *in_gate_up; // not null: the input is SwiGLU(in, in_gate_up) = g * u / (1 + e^-g)
     uint32_t n_rows, n_bits; // this instance's shape (the few-instance form mixes shapes)
+    // "fed" plans: the digit table of a stage's input is written by whoever produces that
+    // input, so the GEMV blocks only stream.  For stage 1 that is the kernel before it (norm,
+    // SwiGLU, attention combine); for stage 2 it is stage 1 itself: the last of its blocks to
+    // finish (counted by `ticket`) turns t into next_digits / next_meta.
+    uint2 *next_digits;
+    StageMeta *next_meta;
+    uint32_t *ticket;
 };
-
-__device__ __forceinline__ float round_bf16(float v) {
-    uint32_t u = __float_as_uint(v);
-    if ((u & 0x7fffffffu) > 0x7f800000u) return __uint_as_float((u | 0x00400000u) & 0xffff0000u);
-    u = (u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u;
-    return __uint_as_float(u);
-}
 
 // ------------------------------------------------------------------ sign-select kernel
 constexpr int kWarpsPerBlock = 8;
@@ -165,13 +161,11 @@ gemv_signselect_kernel(const StageParams *__restrict__ many, uint32_t n_rows, ui
 
 // ------------------------------------------------------------------ tensor-core kernel
 constexpr int kTileRows = 16;
-constexpr int kStepBits = 512;      // bits of one row inside one tile
 constexpr int kTileBytes = 1024;
 constexpr int kTilesPerWarp = 4;    // row tiles of a group; they share every B fragment
 constexpr int kGroupRows = kTileRows * kTilesPerWarp;
 constexpr int kChunkBytes = kTileBytes * kTilesPerWarp;
 constexpr int kStages = 2;          // ring depth per warp (cp.async)
-constexpr int kQBits = 46;          // |q_k| < 2^(kQBits+1)
 
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -205,66 +199,6 @@ __device__ __forceinline__ double load_input(const StageParams &p, uint32_t k, u
     if (p.in_scale) v = p.in_scale[k] * v;  // float32 product, as the reference forms z
     if (kRoundBf16) v = round_bf16(v);
     return (double)v;
-}
-
-// Fixed-point grid of a vector whose largest magnitude is m: |v| * 2^shift < 2^(kQBits+1).
-struct FixedPoint {
-    int shift;
-    bool direct;   // 2^shift is a normal double
-    double pow2;
-    __device__ __forceinline__ long long quant(double v) const {
-        return __double2ll_rn(direct ? v * pow2 : ldexp(v, shift));
-    }
-};
-__device__ __forceinline__ FixedPoint fixed_point_of(double m) {
-    int e = 0;
-    if (m > 0.0) {
-        int biased = (__double2hiint(m) >> 20) & 0x7ff;  // m = f * 2^e, f in [0.5, 1)
-        if (biased) e = biased - 1022; else frexp(m, &e);
-    }
-    FixedPoint fp;
-    fp.shift = kQBits + 1 - e;
-    fp.direct = fp.shift > -1000 && fp.shift < 1000;
-    fp.pow2 = fp.direct ? __hiloint2double((1023 + fp.shift) << 20, 0) : 0.0;
-    return fp;
-}
-
-// Record rec = (qw*4 + ip)*4 + t of k-step ks: the eight uint2 B-fragment pairs (one per
-// digit column) built from the eight vector entries k = 512*ks + 128*t + 32*qw + 8*j + i,
-// i in {2*ip, 2*ip+1}, j in 0..3.  q8[which*4 + j] holds their fixed-point values.
-__device__ __forceinline__ void build_record(const long long (&q8)[8], uint32_t ip, uint4 *dst) {
-    // Balanced base-256 digits without a carry loop: adding 128 to every byte position and
-    // flipping each byte's top bit turns the two's-complement bytes into digits in
-    // [-128, 127] with sum_n d_n 256^n equal to the value.
-    const unsigned long long bias = 0x8080808080808080ull;
-    uint32_t w[2][4][2];  // [which][j][low digits 0-3 / high digits 4-7]
-#pragma unroll
-    for (int which = 0; which < 2; ++which)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            unsigned long long u =
-                (((unsigned long long)q8[which * 4 + j] << (7 - (2 * ip + which))) + bias) ^ bias;
-            w[which][j][0] = (uint32_t)u;
-            w[which][j][1] = (uint32_t)(u >> 32);
-        }
-    // 4x4 byte transposes: word n of the result holds digit n of the four entries j = 0..3
-    uint32_t out[2][8];
-#pragma unroll
-    for (int which = 0; which < 2; ++which)
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const uint32_t a = w[which][0][half], b2 = w[which][1][half];
-            const uint32_t c = w[which][2][half], d = w[which][3][half];
-            const uint32_t t0 = __byte_perm(a, b2, 0x5140), t1 = __byte_perm(c, d, 0x5140);
-            const uint32_t t2 = __byte_perm(a, b2, 0x7362), t3 = __byte_perm(c, d, 0x7362);
-            out[which][half * 4 + 0] = __byte_perm(t0, t1, 0x5410);
-            out[which][half * 4 + 1] = __byte_perm(t0, t1, 0x7632);
-            out[which][half * 4 + 2] = __byte_perm(t2, t3, 0x5410);
-            out[which][half * 4 + 3] = __byte_perm(t2, t3, 0x7632);
-        }
-#pragma unroll
-    for (int n = 0; n < 8; n += 2)
-        dst[n / 2] = make_uint4(out[0][n], out[1][n], out[0][n + 1], out[1][n + 1]);
 }
 
 // Converts one instance's input vector to its digit table.
@@ -638,7 +572,12 @@ gemv_bitslice_kernel(const StageParams *__restrict__ many, uint32_t n_rows, uint
 // The instances of one launch may differ in shape (q beside k and v): every instance brings
 // its own n_rows and n_bits, the grid covers the largest group count and the shared memory
 // the longest table; blocks beyond an instance's last row group have nothing to do.
-template <bool kRoundBf16, bool kFinal>
+//   kFed: the digit table and the stage record of the input are already in global memory
+//   (p.digits, p.meta), written by the kernel that produced the input; the block builds
+//   nothing, needs no shared memory for a table, and starts multiplying as soon as its first
+//   chunks have landed.  A stage-1 instance with a ticket then hands over to stage 2: the last
+//   of its blocks to finish builds the table of t.  smem: [ring][reduction buffer].
+template <bool kRoundBf16, bool kFinal, bool kFed = false>
 __global__ void __launch_bounds__(512)
 gemv_bitslice_splitk_kernel(const StageParams *__restrict__ many) {
     qk::pdl_launch();  // (bitslice_stage waits for the kernel before, after its weight prologue)
@@ -651,11 +590,32 @@ gemv_bitslice_splitk_kernel(const StageParams *__restrict__ many) {
         qk::pdl_wait();
         return;
     }
-    uint8_t *ring = smem_dyn + (size_t)n_steps * 4096;
+    uint8_t *ring = smem_dyn + (kFed ? 0 : (size_t)n_steps * 4096);
     int *red = reinterpret_cast<int *>(ring + (size_t)(blockDim.x / 32) * kStages * kChunkBytes);
-    bitslice_stage<kRoundBf16, kFinal, true, false, false, true>(
+    bitslice_stage<kRoundBf16, kFinal, !kFed, false, false, true>(
         p, smem_dyn, ring, nullptr, nullptr, n_rows, n_bits, n_groups, n_steps, blockIdx.x, 1, false,
         red);
+    if (kFed && !kFinal && p.ticket) {
+        // hand-over to stage 2: whoever finishes last has all of t in front of it
+        __shared__ double tail_max[32];
+        __shared__ long long tail_sum[32];
+        __shared__ int tail_bad, tail_last;
+        __threadfence();  // this block's rows of t are visible to the device
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const uint32_t ticket = atomicAdd(p.ticket, 1u);
+            tail_last = ticket == n_groups - 1;
+            if (tail_last) *p.ticket = 0;  // every block has drawn: ready for the next launch
+        }
+        __syncthreads();
+        if (tail_last) {
+            __threadfence();
+            const double *t_in = static_cast<const double *>(p.out);
+            block_build_table([&](uint32_t k) { return k < n_rows ? __ldcg(t_in + k) : 0.0; },
+                              (n_rows + kStepBits - 1) / kStepBits, reinterpret_cast<uint4 *>(p.next_digits),
+                              p.next_meta, tail_max, tail_sum, &tail_bad);
+        }
+    }
 }
 
 // Both stages of one layer instance in one block: t = Vb^T z stays in shared memory as
@@ -689,16 +649,15 @@ layer_bitslice_fused_kernel(const StageParams *__restrict__ stage1,
 // ------------------------------------------------------------------ persistent streaming form
 // Many independent layer instances per launch (a stack of layers, or one layer for many
 // requests): one CTA per SM stays resident and walks over its share of the instances with
-// three kinds of warps, so that the stream of weight bits from HBM never stops for a layer
+// two kinds of warps, so that the stream of weight bits from HBM never stops for a layer
 // boundary, a table build or a stage boundary.
 //   * consumer warps (16): the mask-and-MMA loop of bitslice_stage and nothing else.  A warp
-//     owns whole row groups; it takes its 4 KB chunks from a ring in shared memory that is
-//     shared by all warps.
-//   * one producer warp: keeps the ring full with one bulk copy (cp.async.bulk, completing on
-//     an mbarrier) per chunk, in exactly the order in which the consumers will ask for
-//     them.  It runs ahead across stage and layer boundaries, because the order of the chunks
-//     does not depend on any data.
-//   * builder warps (4): turn the input vector of the NEXT instance into its digit table
+//     owns whole row groups.  Its 4 KB chunks arrive in a private two-slot ring by bulk copies
+//     (cp.async.bulk completing on an mbarrier) that the warp starts itself, one instruction
+//     from one lane: the moment a chunk has been read into registers its slot is refilled
+//     with the chunk two ahead.  The sequence of a warp's chunks depends on no data, so the
+//     prefetch runs on across stage and layer boundaries.
+//   * builder warps (3): turn the input vector of the NEXT instance into its digit table
 //     while the consumers stream the current one, and turn t into the second table as soon
 //     as the consumers have finished stage 1.
 // The stages are software-pipelined over the instances, J1(0) J1(1) J2(0) J1(2) J2(1) ...,
@@ -709,18 +668,16 @@ layer_bitslice_fused_kernel(const StageParams *__restrict__ stage1,
 // out of polls raises the CTA's abort flag, every other role sees it in its own wait, all
 // leave, and the launch reports bit 8 of the context's error word.
 constexpr int kPsConsumers = 16;
-constexpr int kPsBuilders = 4;
-constexpr int kPsProducerWarp = kPsConsumers;
-constexpr int kPsBuilderWarp0 = kPsConsumers + 1;
-constexpr int kPsThreads = (kPsConsumers + 1 + kPsBuilders) * 32;
-constexpr int kPsMinSlots = 24, kPsMaxSlots = 40;
+constexpr int kPsBuilders = 3;
+constexpr int kPsBuilderWarp0 = kPsConsumers;
+constexpr int kPsThreads = (kPsConsumers + kPsBuilders) * 32;
+constexpr int kPsDepth = 2;  // ring slots per consumer warp
 constexpr uint32_t kPsWaitLimitDefault = 1u << 22;
 
 struct PsArgs {
     const StageParams *stage1, *stage2;  // [n_inst] each
     uint32_t n_inst;
     uint32_t r, din, dout;
-    uint32_t slots;        // ring depth in 4 KB chunks
     uint32_t wait_limit;
     int *error;
 };
@@ -757,9 +714,10 @@ __device__ __forceinline__ bool ps_wait_warp(uint64_t *bar, uint32_t parity, vol
     return __all_sync(0xffffffffu, ps_wait_lane(bar, parity, abort_flag, limit)) != 0;
 }
 
-// Digit table of one stage's input, built by the 128 builder threads (tid 0..127).
-//   input(k): element k as float64 (zero beyond the vector).  red: 4 doubles, 4 long longs and
-//   an int of shared memory for the group's reductions; named barrier 2 keeps the group in step.
+// Digit table of one stage's input, built by the builder threads (tid 0 .. 32*kPsBuilders-1).
+//   input(k): element k as float64 (zero beyond the vector).  red: kPsBuilders doubles, long
+//   longs and ints of shared memory for the group's reductions; named barrier 2 keeps the
+//   group in step.
 template <typename Input>
 __device__ __forceinline__ void ps_build_table(Input input, uint32_t n_steps, uint4 *table,
                                                StageMeta *meta_out, double *red_max,
@@ -822,103 +780,54 @@ __device__ __forceinline__ void ps_build_table(Input input, uint32_t n_steps, ui
     // (the caller's arrival on the table's barrier publishes table and meta)
 }
 
-// The consumer's work on one row group of one stage: n_steps chunks from the ring.
-//   seq0 + ks * stride: the position of the group's ks-th chunk in the producer's order.
-template <bool kRoundBf16, bool kFinal>
-__device__ __forceinline__ bool
-ps_consume_group(const StageParams &p, const uint8_t *ring_smem, uint64_t *full, uint64_t *empty,
-                 uint32_t slots, const uint2 *table, const StageMeta &meta, double *out_smem,
-                 uint32_t n_rows, uint32_t n_steps, uint32_t group, uint32_t seq0, uint32_t stride,
-                 volatile int *abort_flag, uint32_t limit) {
-    const uint32_t lane = threadIdx.x % 32, g = lane / 4, t = lane % 4;
-    int acc[kTilesPerWarp][4];
-#pragma unroll
-    for (int m = 0; m < kTilesPerWarp; ++m)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[m][e] = 0;
-    const uint2 *dig = table + t * 8 + g;
-    for (uint32_t ks = 0; ks < n_steps; ++ks) {
-        const uint32_t n = seq0 + ks * stride, slot = n % slots;
-        if (!ps_wait_warp(&full[slot], (n / slots) & 1, abort_flag, limit)) return false;
-        const uint4 *stage = reinterpret_cast<const uint4 *>(ring_smem + (size_t)slot * kChunkBytes) + lane;
-        uint4 cur[kTilesPerWarp][2];
-#pragma unroll
-        for (int m = 0; m < kTilesPerWarp; ++m) {
-            cur[m][0] = stage[m * 64];
-            cur[m][1] = stage[m * 64 + 32];
-        }
-        // the chunk is in registers: hand the slot back to the producer right away
-        __syncwarp();
-        if (lane == 0) ps_mbar_arrive(&empty[slot]);
-        const uint2 *dk = dig + (size_t)ks * 512;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-#pragma unroll
-            for (int ip = 0; ip < 4; ++ip) {
-                const uint2 b = dk[(q * 4 + ip) * 32];
-                const uint32_t m0 = 0x01010101u << (2 * ip), m1 = m0 << 1;
-#pragma unroll
-                for (int m = 0; m < kTilesPerWarp; ++m) {
-                    const uint32_t wg = q == 0 ? cur[m][0].x : q == 1 ? cur[m][0].y
-                                      : q == 2 ? cur[m][0].z : cur[m][0].w;
-                    const uint32_t wh = q == 0 ? cur[m][1].x : q == 1 ? cur[m][1].y
-                                      : q == 2 ? cur[m][1].z : cur[m][1].w;
-                    mma_u8s8(acc[m], wg & m0, wh & m0, wg & m1, wh & m1, b.x, b.y);
-                }
-            }
-        }
+// Where a consumer warp is in its sequence of chunks.  Job t of a CTA with n instances:
+//   t = 0: J1(0);  t = 2n-1: J2(n-1);  otherwise t odd: J1((t+1)/2), t even: J2(t/2 - 1)
+// which is the order J1(0) J1(1) J2(0) J1(2) J2(1) ... J2(n-1).  Within a job the warp takes
+// the row groups warp, warp + 16, ..., and within a group the k-steps in order.
+struct PsCursor {
+    uint32_t job, group, ks;
+};
+struct PsShape {
+    uint32_t n_mine, groups[2], steps[2];
+};
+__device__ __forceinline__ void ps_job(const PsShape &sh, uint32_t job, uint32_t *stage, uint32_t *inst) {
+    if (job == 0) {
+        *stage = 0;
+        *inst = 0;
+    } else if (job == 2 * sh.n_mine - 1) {
+        *stage = 1;
+        *inst = sh.n_mine - 1;
+    } else if (job & 1) {
+        *stage = 0;
+        *inst = (job + 1) / 2;
+    } else {
+        *stage = 1;
+        *inst = job / 2 - 1;
     }
-    // ---- exact recombination (see bitslice_stage): X = sum_n c_n 256^n = 128 S, value =
-    // (X - 64 T) / 64 * 2^-shift with X = hi 2^32 + lo and 64 T = th 2^32 + tl.  Two tiles are
-    // finished at a time: lanes t = 0,1 take the rows of the first, lanes t = 2,3 those of
-    // the second, so every lane converts one row and the exchange needs three shuffles of a
-    // 64-bit value per tile instead of four.
-    const long long th = meta.total >> 26;
-    const long long tl = (meta.total & ((1ll << 26) - 1)) << 6;
-    const int sh0 = 16 * (t & 1);
-    const int oexp = -meta.shift - 6;
-    const bool odirect = oexp > -1000 && oexp < 1000;
-    const double oscale = odirect ? __hiloint2double((1023 + oexp) << 20, 0) : 0.0;
-#pragma unroll
-    for (int pair = 0; pair < kTilesPerWarp / 2; ++pair) {
-        long long pg[2], ph[2];
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const int(&a)[4] = acc[2 * pair + k];
-            pg[k] = ((long long)a[0] << sh0) + ((long long)a[1] << (sh0 + 8));
-            ph[k] = ((long long)a[2] << sh0) + ((long long)a[3] << (sh0 + 8));
-            pg[k] += __shfl_xor_sync(0xffffffffu, pg[k], 1);  // t=0,1: low half; t=2,3: high half
-            ph[k] += __shfl_xor_sync(0xffffffffu, ph[k], 1);
+}
+// First chunk of the first job from `job` on in which this warp owns a row group.
+__device__ __forceinline__ bool ps_seek(const PsShape &sh, uint32_t warp, PsCursor *c) {
+    while (c->job < 2 * sh.n_mine) {
+        uint32_t stage, inst;
+        ps_job(sh, c->job, &stage, &inst);
+        if (warp < sh.groups[stage]) {
+            c->group = warp;
+            c->ks = 0;
+            return true;
         }
-        // lanes t<2 keep tile 2*pair (they hold its low half and need the high half from t+2);
-        // lanes t>=2 keep tile 2*pair+1 (they hold its high half and need the low half)
-        const bool first = t < 2;
-        const long long send_g = first ? pg[1] : pg[0], send_h = first ? ph[1] : ph[0];
-        const long long other_g = __shfl_xor_sync(0xffffffffu, send_g, 2);
-        const long long other_h = __shfl_xor_sync(0xffffffffu, send_h, 2);
-        const long long mine_g = first ? pg[0] : pg[1], mine_h = first ? ph[0] : ph[1];
-        // row g (t even) or g + 8 (t odd) of the lane's tile
-        const bool upper = (t & 1) != 0;
-        const long long lo = first ? (upper ? mine_h : mine_g) : (upper ? other_h : other_g);
-        const long long hi = first ? (upper ? other_h : other_g) : (upper ? mine_h : mine_g);
-        const int m = 2 * pair + (first ? 0 : 1);
-        const uint32_t row = group * kGroupRows + m * kTileRows + g + (upper ? 8 : 0);
-        if (row < n_rows) {
-            double val = (double)(hi - th) * 4294967296.0 + (double)(lo - tl);
-            val = odirect ? val * oscale : ldexp(val, oexp);
-            if (meta.nonfinite) val = nan("");
-            if (kRoundBf16) val = (double)round_bf16((float)val);
-            if (kFinal) {
-                float y = (float)val;
-                if (p.out_scale) y = y * p.out_scale[row];
-                if (p.out_bias) y = y + p.out_bias[row];
-                static_cast<float *>(p.out)[row] = y;
-            } else {
-                out_smem[row] = val;
-            }
-        }
+        ++c->job;
     }
-    return true;
+    return false;
+}
+__device__ __forceinline__ bool ps_next(const PsShape &sh, uint32_t warp, PsCursor *c) {
+    uint32_t stage, inst;
+    ps_job(sh, c->job, &stage, &inst);
+    if (++c->ks < sh.steps[stage]) return true;
+    c->ks = 0;
+    c->group += kPsConsumers;
+    if (c->group < sh.groups[stage]) return true;
+    ++c->job;
+    return ps_seek(sh, warp, c);
 }
 
 template <bool kRoundBf16>
@@ -926,17 +835,16 @@ __global__ void __launch_bounds__(kPsThreads, 1)
 layer_stream_kernel(const PsArgs a, uint32_t t_bytes, uint32_t table1_bytes, uint32_t table2_bytes) {
     qk::pdl_launch();
     extern __shared__ __align__(128) uint8_t smem_dyn[];
-    // [ring][table1 x2][table2 x2][t x2][meta x4][barriers][reduction scratch][abort flag]
+    // [rings: warp x depth x 4 KB][table1 x2][table2 x2][t x2][meta x4][barriers][reduction scratch][abort]
     uint8_t *ring = smem_dyn;
-    uint8_t *table1 = ring + (size_t)a.slots * kChunkBytes;
+    uint8_t *table1 = ring + (size_t)kPsConsumers * kPsDepth * kChunkBytes;
     uint8_t *table2 = table1 + 2 * (size_t)table1_bytes;
     uint8_t *t_base = table2 + 2 * (size_t)table2_bytes;
     StageMeta *meta = reinterpret_cast<StageMeta *>(t_base + 2 * (size_t)t_bytes);  // [stage][buffer]
-    uint64_t *full = reinterpret_cast<uint64_t *>(meta + 4);
-    uint64_t *empty = full + a.slots;
-    uint64_t *t1_full = empty + a.slots;  // [2] table of stage 1, buffer b, is ready
-    uint64_t *tt_full = t1_full + 2;      // [2] t buffer b is complete
-    uint64_t *t2_full = tt_full + 2;      // [2] table of stage 2, buffer b, is ready
+    uint64_t *full = reinterpret_cast<uint64_t *>(meta + 4);  // [warp][depth]
+    uint64_t *t1_full = full + kPsConsumers * kPsDepth;       // [2] table of stage 1, buffer b, is ready
+    uint64_t *tt_full = t1_full + 2;                          // [2] t buffer b is complete
+    uint64_t *t2_full = tt_full + 2;                          // [2] table of stage 2, buffer b, is ready
     double *red_max = reinterpret_cast<double *>(t2_full + 2);
     long long *red_sum = reinterpret_cast<long long *>(red_max + kPsBuilders);
     int *red_bad = reinterpret_cast<int *>(red_sum + kPsBuilders);
@@ -944,19 +852,20 @@ layer_stream_kernel(const PsArgs a, uint32_t t_bytes, uint32_t table1_bytes, uin
 
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t limit = a.wait_limit;
+    PsShape sh;
     // this CTA's instances: blockIdx.x, blockIdx.x + gridDim.x, ...
-    const uint32_t n_mine = a.n_inst > blockIdx.x ? (a.n_inst - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const uint32_t groups1 = (a.r + kGroupRows - 1) / kGroupRows, steps1 = (a.din + kStepBits - 1) / kStepBits;
-    const uint32_t groups2 = (a.dout + kGroupRows - 1) / kGroupRows, steps2 = (a.r + kStepBits - 1) / kStepBits;
+    sh.n_mine = a.n_inst > blockIdx.x ? (a.n_inst - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    sh.groups[0] = (a.r + kGroupRows - 1) / kGroupRows;
+    sh.steps[0] = (a.din + kStepBits - 1) / kStepBits;
+    sh.groups[1] = (a.dout + kGroupRows - 1) / kGroupRows;
+    sh.steps[1] = (a.r + kStepBits - 1) / kStepBits;
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < a.slots; ++s) {
-            ps_mbar_init(&full[s], 1);   // the producer's arrive.expect_tx
-            ps_mbar_init(&empty[s], 1);  // the consuming warp's lane 0
-        }
+        for (int s = 0; s < kPsConsumers * kPsDepth; ++s) ps_mbar_init(&full[s], 1);  // the copy's expect_tx
         for (int b = 0; b < 2; ++b) {
             ps_mbar_init(&t1_full[b], kPsBuilders);
-            ps_mbar_init(&tt_full[b], kPsConsumers);
+            // every consumer warp that owns a row group of stage 1 reports its rows of t
+            ps_mbar_init(&tt_full[b], min((uint32_t)kPsConsumers, sh.groups[0]));
             ps_mbar_init(&t2_full[b], kPsBuilders);
         }
         abort_flag[0] = 0;
@@ -965,111 +874,185 @@ layer_stream_kernel(const PsArgs a, uint32_t t_bytes, uint32_t table1_bytes, uin
     }
     __syncthreads();
 
-    // The order of the jobs, the same in every role: step s = 0 .. n_mine runs J1(s) (if
-    // s < n_mine) and then J2(s - 1) (if s >= 1).
-    if (warp != kPsProducerWarp) qk::pdl_wait();  // inputs come from the kernel before; weight bits do not
     if (warp < kPsConsumers) {
         // ------------------------------------------------------------ consumers
-        uint32_t seq = 0;  // chunks of all rounds before the current one
-        bool ok = true;
-        for (uint32_t s = 0; s <= n_mine && ok; ++s) {
-#pragma unroll 1
-            for (int stage = 0; stage < 2 && ok; ++stage) {
-                if (stage == 0 ? s >= n_mine : s == 0) continue;
-                const uint32_t i = stage == 0 ? s : s - 1, b = i & 1, use = i >> 1;
-                const uint32_t inst = blockIdx.x + i * gridDim.x;
-                const StageParams p = stage == 0 ? a.stage1[inst] : a.stage2[inst];
-                const uint32_t n_groups = stage == 0 ? groups1 : groups2;
-                const uint32_t n_steps = stage == 0 ? steps1 : steps2;
-                // the table of this job (built a whole stage ago in the steady state)
-                if (!ps_wait_warp(stage == 0 ? &t1_full[b] : &t2_full[b], use & 1, abort_flag, limit)) {
+        const uint32_t g = lane / 4, t = lane % 4;
+        uint8_t *my_ring = ring + (size_t)warp * kPsDepth * kChunkBytes;
+        uint64_t *my_full = full + warp * kPsDepth;
+        // the chunk a cursor points at: weight bits only, known without any input
+        // `after`: a value whose computation must precede the copy (zero): when a slot is refilled
+        // the shared-memory reads of its old contents must have returned first
+        auto issue = [&](const PsCursor &c, uint32_t slot, uint32_t after) {
+            if (lane == 0) {
+                uint32_t stage, inst;
+                ps_job(sh, c.job, &stage, &inst);
+                const size_t at = blockIdx.x + (size_t)inst * gridDim.x;
+                const uint8_t *tiles = stage == 0 ? a.stage1[at].w_tiles : a.stage2[at].w_tiles;
+                const uint8_t *src = tiles + ((size_t)c.group * sh.steps[stage] + c.ks) * kChunkBytes;
+                const uint32_t dst = ps_smem_u32(my_ring + (size_t)slot * kChunkBytes) + after;
+                const uint32_t bar = ps_smem_u32(&my_full[slot]);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                             "r"((uint32_t)kChunkBytes)
+                             : "memory");
+                asm volatile(
+                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                    "l"(src), "r"((uint32_t)kChunkBytes), "r"(bar)
+                    : "memory");
+            }
+        };
+        PsCursor fetch{0, 0, 0}, cur{0, 0, 0};
+        bool more = ps_seek(sh, warp, &fetch);
+        uint32_t n_issued = 0;
+        for (; n_issued < (uint32_t)kPsDepth && more; ++n_issued) {
+            issue(fetch, n_issued, 0u);
+            more = ps_next(sh, warp, &fetch);
+        }
+        qk::pdl_wait();  // from here on: inputs, which come from the kernel before this one
+        bool ok = true, have = ps_seek(sh, warp, &cur);
+        uint32_t n_done = 0, job_ready = 0xffffffffu;
+        StageMeta mt{};
+        const uint2 *dig = nullptr;
+        StageParams p{};
+        int acc[kTilesPerWarp][4];
+        while (have && ok) {
+            uint32_t stage, inst;
+            ps_job(sh, cur.job, &stage, &inst);
+            const uint32_t b = inst & 1, n_steps = sh.steps[stage];
+            if (job_ready != cur.job) {
+                // first chunk of a job: its table (built a whole stage ago in the steady state)
+                if (!ps_wait_warp(stage == 0 ? &t1_full[b] : &t2_full[b], (inst >> 1) & 1, abort_flag, limit)) {
                     ok = false;
                     break;
                 }
-                const StageMeta mt = meta[stage * 2 + b];
-                const uint2 *table = reinterpret_cast<const uint2 *>(
-                    stage == 0 ? table1 + (size_t)b * table1_bytes : table2 + (size_t)b * table2_bytes);
-                double *t_buf = reinterpret_cast<double *>(t_base + (size_t)b * t_bytes);
-                for (uint32_t g0 = 0; g0 < n_groups && ok; g0 += kPsConsumers) {
-                    const uint32_t active = min((uint32_t)kPsConsumers, n_groups - g0);
-                    if (warp < active) {
-                        if (stage == 0)
-                            ok = ps_consume_group<kRoundBf16, false>(
-                                p, ring, full, empty, a.slots, table, mt, t_buf, a.r, n_steps, g0 + warp,
-                                seq + warp, active, abort_flag, limit);
-                        else
-                            ok = ps_consume_group<kRoundBf16, true>(
-                                p, ring, full, empty, a.slots, table, mt, nullptr, a.dout, n_steps,
-                                g0 + warp, seq + warp, active, abort_flag, limit);
+                mt = meta[stage * 2 + b];
+                dig = reinterpret_cast<const uint2 *>(stage == 0 ? table1 + (size_t)b * table1_bytes
+                                                                 : table2 + (size_t)b * table2_bytes) + t * 8 + g;
+                p = stage == 0 ? a.stage1[blockIdx.x + (size_t)inst * gridDim.x]
+                               : a.stage2[blockIdx.x + (size_t)inst * gridDim.x];
+                job_ready = cur.job;
+            }
+            if (cur.ks == 0) {
+#pragma unroll
+                for (int m = 0; m < kTilesPerWarp; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0;
+            }
+            const uint32_t slot = n_done % kPsDepth;
+            if (!ps_wait_warp(&my_full[slot], (n_done / kPsDepth) & 1, abort_flag, limit)) {
+                ok = false;
+                break;
+            }
+            const uint4 *stage_ptr = reinterpret_cast<const uint4 *>(my_ring + (size_t)slot * kChunkBytes) + lane;
+            uint4 chunk[kTilesPerWarp][2];
+#pragma unroll
+            for (int m = 0; m < kTilesPerWarp; ++m) {
+                chunk[m][0] = stage_ptr[m * 64];
+                chunk[m][1] = stage_ptr[m * 64 + 32];
+            }
+            // the chunk is in registers: refill its slot with the chunk kPsDepth ahead
+            __syncwarp();
+            if (more) {
+                // (the last read of the slot feeds the copy's address: the copy cannot start
+                // before that read - issued by all lanes in one instruction - has returned)
+                issue(fetch, slot, chunk[kTilesPerWarp - 1][1].w & 0u);
+                more = ps_next(sh, warp, &fetch);
+            }
+            const uint2 *dk = dig + (size_t)cur.ks * 512;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+#pragma unroll
+                for (int ip = 0; ip < 4; ++ip) {
+                    const uint2 bq = dk[(q * 4 + ip) * 32];
+                    const uint32_t m0 = 0x01010101u << (2 * ip), m1 = m0 << 1;
+#pragma unroll
+                    for (int m = 0; m < kTilesPerWarp; ++m) {
+                        const uint32_t wg = q == 0 ? chunk[m][0].x : q == 1 ? chunk[m][0].y
+                                          : q == 2 ? chunk[m][0].z : chunk[m][0].w;
+                        const uint32_t wh = q == 0 ? chunk[m][1].x : q == 1 ? chunk[m][1].y
+                                          : q == 2 ? chunk[m][1].z : chunk[m][1].w;
+                        mma_u8s8(acc[m], wg & m0, wh & m0, wg & m1, wh & m1, bq.x, bq.y);
                     }
-                    seq += active * n_steps;
-                }
-                if (stage == 0 && ok) {
-                    // this warp's rows of t are written: tell the builders (all 16 warps arrive)
-                    __syncwarp();
-                    if (lane == 0) ps_mbar_arrive(&tt_full[b]);
                 }
             }
-        }
-        if (!ok) *abort_flag = 1;
-    } else if (warp == kPsProducerWarp) {
-        // ------------------------------------------------------------ producer
-        uint32_t n = 0;
-        bool ok = true;
-        for (uint32_t s = 0; s <= n_mine && ok; ++s) {
-#pragma unroll 1
-            for (int stage = 0; stage < 2 && ok; ++stage) {
-                if (stage == 0 ? s >= n_mine : s == 0) continue;
-                const uint32_t i = stage == 0 ? s : s - 1;
-                const uint32_t inst = blockIdx.x + i * gridDim.x;
-                const uint8_t *tiles = stage == 0 ? a.stage1[inst].w_tiles : a.stage2[inst].w_tiles;
-                const uint32_t n_groups = stage == 0 ? groups1 : groups2;
-                const uint32_t n_steps = stage == 0 ? steps1 : steps2;
-                for (uint32_t g0 = 0; g0 < n_groups && ok; g0 += kPsConsumers) {
-                    const uint32_t active = min((uint32_t)kPsConsumers, n_groups - g0);
-                    for (uint32_t ks = 0; ks < n_steps && ok; ++ks)
-                        for (uint32_t w = 0; w < active; ++w, ++n) {
-                            const uint32_t slot = n % a.slots;
-                            // the slot's previous chunk (number n - slots) must have been taken
-                            if (n >= a.slots &&
-                                !ps_wait_warp(&empty[slot], ((n / a.slots) - 1) & 1, abort_flag, limit)) {
-                                ok = false;
-                                break;
-                            }
-                            if (lane == 0) {
-                                const uint32_t dst = ps_smem_u32(ring + (size_t)slot * kChunkBytes);
-                                const uint32_t bar = ps_smem_u32(&full[slot]);
-                                const uint8_t *src = tiles + ((size_t)(g0 + w) * n_steps + ks) * kChunkBytes;
-                                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-                                             "r"((uint32_t)kChunkBytes)
-                                             : "memory");
-                                asm volatile(
-                                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes "
-                                    "[%0], [%1], %2, [%3];" ::"r"(dst),
-                                    "l"(src), "r"((uint32_t)kChunkBytes), "r"(bar)
-                                    : "memory");
-                            }
-                            __syncwarp();
+            ++n_done;
+            const bool group_done = cur.ks + 1 == n_steps;
+            const uint32_t group = cur.group, job = cur.job;
+            have = ps_next(sh, warp, &cur);
+            if (!group_done) continue;
+            // ---- exact recombination (see bitslice_stage): X = sum_n c_n 256^n = 128 S, value =
+            // (X - 64 T) / 64 * 2^-shift with X = hi 2^32 + lo and 64 T = th 2^32 + tl.  Two
+            // tiles are finished at a time: lanes t = 0,1 take the rows of the first, lanes
+            // t = 2,3 those of the second, so every lane converts one row.
+            {
+                const uint32_t n_rows = stage == 0 ? a.r : a.dout;
+                double *out_smem = reinterpret_cast<double *>(t_base + (size_t)b * t_bytes);
+                const long long th = mt.total >> 26;
+                const long long tl = (mt.total & ((1ll << 26) - 1)) << 6;
+                const int sh0 = 16 * (t & 1);
+                const int oexp = -mt.shift - 6;
+                const bool odirect = oexp > -1000 && oexp < 1000;
+                const double oscale = odirect ? __hiloint2double((1023 + oexp) << 20, 0) : 0.0;
+#pragma unroll
+                for (int pair = 0; pair < kTilesPerWarp / 2; ++pair) {
+                    long long pg[2], ph[2];
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const int(&c4)[4] = acc[2 * pair + k];
+                        pg[k] = ((long long)c4[0] << sh0) + ((long long)c4[1] << (sh0 + 8));
+                        ph[k] = ((long long)c4[2] << sh0) + ((long long)c4[3] << (sh0 + 8));
+                        pg[k] += __shfl_xor_sync(0xffffffffu, pg[k], 1);  // t=0,1: low half; t=2,3: high half
+                        ph[k] += __shfl_xor_sync(0xffffffffu, ph[k], 1);
+                    }
+                    // lanes t<2 keep tile 2*pair (they hold its low half and get the high half from
+                    // t+2); lanes t>=2 keep tile 2*pair+1 (they hold its high half and get the low)
+                    const bool first = t < 2;
+                    const long long send_g = first ? pg[1] : pg[0], send_h = first ? ph[1] : ph[0];
+                    const long long other_g = __shfl_xor_sync(0xffffffffu, send_g, 2);
+                    const long long other_h = __shfl_xor_sync(0xffffffffu, send_h, 2);
+                    const long long mine_g = first ? pg[0] : pg[1], mine_h = first ? ph[0] : ph[1];
+                    const bool upper = (t & 1) != 0;  // row g (t even) or g + 8 (t odd) of the lane's tile
+                    const long long lo = first ? (upper ? mine_h : mine_g) : (upper ? other_h : other_g);
+                    const long long hi = first ? (upper ? other_h : other_g) : (upper ? mine_h : mine_g);
+                    const int m = 2 * pair + (first ? 0 : 1);
+                    const uint32_t row = group * kGroupRows + m * kTileRows + g + (upper ? 8 : 0);
+                    if (row < n_rows) {
+                        double val = (double)(hi - th) * 4294967296.0 + (double)(lo - tl);
+                        val = odirect ? val * oscale : ldexp(val, oexp);
+                        if (mt.nonfinite) val = nan("");
+                        if (kRoundBf16) val = (double)round_bf16((float)val);
+                        if (stage == 1) {
+                            float y = (float)val;
+                            if (p.out_scale) y = y * p.out_scale[row];
+                            if (p.out_bias) y = y + p.out_bias[row];
+                            static_cast<float *>(p.out)[row] = y;
+                        } else {
+                            out_smem[row] = val;
                         }
+                    }
                 }
+            }
+            // the warp's last row group of a stage-1 job: its rows of t are written
+            if (stage == 0 && (!have || cur.job != job)) {
+                __syncwarp();
+                if (lane == 0) ps_mbar_arrive(&tt_full[b]);
             }
         }
         if (!ok) {
             *abort_flag = 1;
-            // copies in flight must land before the CTA's shared memory is given up: chunks
-            // n - slots .. n - 1 are the ones that may still be on their way
-            const uint32_t first = n > a.slots ? n - a.slots : 0;
-            for (uint32_t m = first; m < n; ++m)
-                ps_wait_warp(&full[m % a.slots], (m / a.slots) & 1, abort_flag + 1 /* never set */, limit);
+            // this warp's copies still in flight must land before the CTA gives up its shared
+            // memory: a bounded wait on both slots (a slot with nothing in flight answers at once
+            // for the parity of its last completed phase and runs out of polls for the other)
+            for (uint32_t slot = 0; slot < (uint32_t)kPsDepth; ++slot)
+                for (uint32_t parity = 0; parity < 2; ++parity)
+                    ps_wait_lane(&my_full[slot], parity, abort_flag + 1 /* never set */, 1u << 12);
         }
     } else {
         // ------------------------------------------------------------ builders
+        qk::pdl_wait();
         const uint32_t tid = threadIdx.x - kPsBuilderWarp0 * 32;
         auto build1 = [&](uint32_t i) {
             const uint32_t b = i & 1;
-            const StageParams p = a.stage1[blockIdx.x + i * gridDim.x];
+            const StageParams p = a.stage1[blockIdx.x + (size_t)i * gridDim.x];
             const uint32_t n_bits = a.din;
-            ps_build_table([&](uint32_t k) { return load_input<false, kRoundBf16>(p, k, n_bits); }, steps1,
+            ps_build_table([&](uint32_t k) { return load_input<false, kRoundBf16>(p, k, n_bits); }, sh.steps[0],
                            reinterpret_cast<uint4 *>(table1 + (size_t)b * table1_bytes), &meta[b], red_max,
                            red_sum, red_bad, tid);
             __syncwarp();
@@ -1078,14 +1061,14 @@ layer_stream_kernel(const PsArgs a, uint32_t t_bytes, uint32_t table1_bytes, uin
         bool ok = true;
         // table1 buffer i&1 was last read by J1(i-2); J1(i-2) had finished before T2(i-2)
         // started (tt_full), and T2(i-2) precedes T1(i) in this loop: no extra barrier.
-        if (n_mine > 0) build1(0);
-        for (uint32_t i = 0; i < n_mine && ok; ++i) {
-            if (i + 1 < n_mine) build1(i + 1);
+        if (sh.n_mine > 0) build1(0);
+        for (uint32_t i = 0; i < sh.n_mine && ok; ++i) {
+            if (i + 1 < sh.n_mine) build1(i + 1);
             const uint32_t b = i & 1;
             // all consumers have written their rows of t(i) ...
             bool seen = ps_wait_warp(&tt_full[b], (i >> 1) & 1, abort_flag, limit);
-            // ... and the four builder warps agree on it before any of them meets the others
-            // at the group's barrier inside the build
+            // ... and the builder warps agree on it before any of them meets the others at the
+            // group's barrier inside the build
             uint32_t all;
             asm volatile(
                 "{\n .reg .pred p, q;\n setp.ne.b32 p, %1, 0;\n"
@@ -1102,7 +1085,7 @@ layer_stream_kernel(const PsArgs a, uint32_t t_bytes, uint32_t table1_bytes, uin
             // and J2(i) starts only after this build has arrived on t2_full.
             const double *t_in = reinterpret_cast<const double *>(t_base + (size_t)b * t_bytes);
             const uint32_t n_bits = a.r;
-            ps_build_table([&](uint32_t k) { return k < n_bits ? t_in[k] : 0.0; }, steps2,
+            ps_build_table([&](uint32_t k) { return k < n_bits ? t_in[k] : 0.0; }, sh.steps[1],
                            reinterpret_cast<uint4 *>(table2 + (size_t)b * table2_bytes), &meta[2 + b],
                            red_max, red_sum, red_bad, tid);
             __syncwarp();
@@ -1289,8 +1272,8 @@ bool fused_plan(const qk_ctx *c, const StageShape &s1, const StageShape &s2, siz
 }
 
 // The persistent streaming form applies when every SM gets at least one instance and the
-// two double-buffered tables, the two t buffers and a ring of at least kPsMinSlots chunks fit
-// in shared memory together.
+// two double-buffered tables, the two t buffers and the consumer warps' rings fit in shared
+// memory together.
 constexpr size_t kPsSmemBudget = 227 * 1024;
 struct PsPlan {
     size_t grid, slots, t_bytes, table1_bytes, table2_bytes, smem;
@@ -1302,12 +1285,10 @@ bool stream_plan(const qk_ctx *c, const StageShape &s1, const StageShape &s2, si
     pl->t_bytes = qk::ceil_div(s1.n_rows * sizeof(double), 128) * 128;
     pl->table1_bytes = s1.n_steps * 4096;
     pl->table2_bytes = s2.n_steps * 4096;
-    const size_t fixed = 2 * (pl->table1_bytes + pl->table2_bytes + pl->t_bytes) + 4 * sizeof(StageMeta) +
-                         6 * 8 + kPsBuilders * (8 + 8 + 4) + 16;
-    if (fixed + kPsMinSlots * (kChunkBytes + 16) > kPsSmemBudget) return false;
-    pl->slots = (kPsSmemBudget - fixed) / (kChunkBytes + 16);  // a chunk and its two barriers
-    if (pl->slots > (size_t)kPsMaxSlots) pl->slots = kPsMaxSlots;
-    pl->smem = fixed + pl->slots * (kChunkBytes + 16);
+    pl->slots = (size_t)kPsConsumers * kPsDepth;
+    pl->smem = pl->slots * kChunkBytes + 2 * (pl->table1_bytes + pl->table2_bytes + pl->t_bytes) +
+               4 * sizeof(StageMeta) + (pl->slots + 6) * 8 + kPsBuilders * (8 + 8 + 4) + 16;
+    if (pl->smem > kPsSmemBudget) return false;
     return true;
 }
 
@@ -1365,9 +1346,10 @@ void fill_params(StageParams *h, const qk_layer *const *layers, size_t n_layers,
             const float *x = x_dev + i * x_layer_stride + t * l->din;
             float *y = y_dev + i * y_layer_stride + t * l->dout;
             h[k] = StageParams{l->vbt, l->vbt_tiles, x, l->s2, t_buf, nullptr, nullptr, dig1, meta,
-                               gate_up, (uint32_t)l->r, (uint32_t)l->din};
+                               gate_up, (uint32_t)l->r, (uint32_t)l->din, dig2, meta + 1, nullptr};
             h[n_inst + k] = StageParams{l->ub, l->ub_tiles, t_buf, nullptr, y, l->s1, l->bias, dig2,
-                                        meta + 1, nullptr, (uint32_t)l->dout, (uint32_t)l->r};
+                                        meta + 1, nullptr, (uint32_t)l->dout, (uint32_t)l->r,
+                                        nullptr, nullptr, nullptr};
         }
 }
 
@@ -1398,8 +1380,37 @@ qk_status launch_mixed_stage(qk_ctx *c, const StageParams *many, size_t n_inst, 
     return QK_OK;
 }
 
+// Fed plans: both stages in the few-instance form without a table of their own.
+bool fed_plan_fits(const qk_ctx *c, const StageShape &s, size_t n_inst, size_t *warps, size_t *smem) {
+    size_t sk_warps = s.n_steps < 4 ? 4 : s.n_steps > 16 ? 16 : s.n_steps;
+    *warps = sk_warps;
+    *smem = sk_warps * kRingPerWarp + sk_warps * 16 * 32 * 4;
+    return s.n_groups <= 65535 && n_inst <= 65535 && n_inst * s.n_groups <= 16 * (size_t)c->sm_count;
+}
+
+template <bool kFinal>
+qk_status launch_fed_stage(qk_ctx *c, const StageParams *many, size_t n_inst, const StageShape &s,
+                           bool bf16) {
+    size_t warps, smem;
+    if (!fed_plan_fits(c, s, n_inst, &warps, &smem))
+        return qk::fail(QK_ERR_VALUE, "a fed plan must fit the few-instance form");
+    auto gemv = bf16 ? gemv_bitslice_splitk_kernel<true, kFinal, true>
+                     : gemv_bitslice_splitk_kernel<false, kFinal, true>;
+    QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    dim3 grid((unsigned)s.n_groups, (unsigned)n_inst);
+    (void)qk::launch_pdl(c->pdl, gemv, grid, dim3((unsigned)warps * 32), smem, c->stream, many);
+    QK_CUDA(cudaGetLastError());
+    c->launches++;
+    return QK_OK;
+}
+
 qk_status launch_both(qk_ctx *c, const qk_layer *l0, const StageParams *d, size_t n_inst,
-                      int kernel, bool mixed = false) {
+                      int kernel, bool mixed = false, bool fed = false) {
+    if (fed) {
+        qk_status e = launch_fed_stage<false>(c, d, n_inst, stage1_shape(l0), l0->serving == QK_BF16);
+        if (e != QK_OK) return e;
+        return launch_fed_stage<true>(c, d + n_inst, n_inst, stage2_shape(l0), l0->serving == QK_BF16);
+    }
     if (mixed) {
         // l0 holds the largest din, r and dout over the instances
         qk_status e = launch_mixed_stage<false>(c, d, n_inst, stage1_shape(l0), l0->serving == QK_BF16);
@@ -1425,7 +1436,7 @@ qk_status launch_both(qk_ctx *c, const qk_layer *l0, const StageParams *d, size_
             qk_status e = qk::error_word(c);
             if (e != QK_OK) return e;
             PsArgs a{d, d + n_inst, (uint32_t)n_inst, (uint32_t)l0->r, (uint32_t)l0->din,
-                     (uint32_t)l0->dout, (uint32_t)ps.slots,
+                     (uint32_t)l0->dout,
                      c->wait_limit ? c->wait_limit : kPsWaitLimitDefault, (int *)c->d_err.ptr};
             auto kern = bf16 ? layer_stream_kernel<true> : layer_stream_kernel<false>;
             QK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1768,6 +1779,47 @@ qk_status qk_plan_create_gated(qk_ctx *ctx, const qk_layer *const *layers,
     return plan_create(ctx, layers, gate_ptrs, up_ptrs, y_ptrs, n_inst, out);
 }
 
+qk_status qk_plan_feed_targets(qk_ctx *ctx, qk_group *plan, const void **targets_dev,
+                               size_t *n_targets) {
+    if (!plan || !targets_dev || !n_targets)
+        return qk::fail(QK_ERR_VALUE, "qk_plan_feed_targets: null argument");
+    qk_ctx *c;
+    qk_status st = qk::resolve_ctx(ctx, &c);
+    if (st != QK_OK) return st;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    if (plan->device != c->device)
+        return qk::fail(QK_ERR_VALUE, "plan lives on device %d, context on device %d", plan->device,
+                        c->device);
+    const size_t n = plan->n_inst;
+    if (!plan->feed) {
+        size_t warps, smem;
+        if (!fed_plan_fits(c, stage1_shape(&plan->shape), n, &warps, &smem) ||
+            !fed_plan_fits(c, stage2_shape(&plan->shape), n, &warps, &smem))
+            return qk::fail(QK_ERR_VALUE, "a plan of %zu instances is too large to be fed: its "
+                            "stages must fit the few-instance form", n);
+        std::vector<StageParams> h(2 * n);
+        QK_CUDA(cudaMemcpy(h.data(), plan->params, h.size() * sizeof(StageParams), cudaMemcpyDeviceToHost));
+        cudaError_t e = cudaMalloc(&plan->feed, n * sizeof(FeedTarget));
+        if (e == cudaSuccess) e = cudaMalloc(&plan->tickets, n * sizeof(uint32_t));
+        if (e != cudaSuccess)
+            return qk::fail(QK_ERR_ALLOC, "device allocation for a fed plan failed: %s", cudaGetErrorString(e));
+        QK_CUDA(cudaMemset(plan->tickets, 0, n * sizeof(uint32_t)));
+        std::vector<FeedTarget> targets(n);
+        for (size_t k = 0; k < n; ++k) {
+            targets[k] = FeedTarget{h[k].in_scale, h[k].digits, h[k].meta, h[k].n_bits,
+                                    (uint32_t)qk::ceil_div(h[k].n_bits, kStepBits)};
+            h[k].ticket = (uint32_t *)plan->tickets + k;
+        }
+        QK_CUDA(cudaMemcpy(plan->feed, targets.data(), n * sizeof(FeedTarget), cudaMemcpyHostToDevice));
+        QK_CUDA(cudaMemcpy(plan->params, h.data(), h.size() * sizeof(StageParams), cudaMemcpyHostToDevice));
+        plan->fed = true;
+    }
+    *targets_dev = plan->feed;
+    *n_targets = n;
+    return QK_OK;
+}
+
 qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group) {
     if (!group) return qk::fail(QK_ERR_VALUE, "qk_group_apply: group is null");
     qk_ctx *c;
@@ -1779,7 +1831,7 @@ qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group) {
         return qk::fail(QK_ERR_VALUE, "group lives on device %d, context on device %d",
                         group->device, c->device);
     return launch_both(c, &group->shape, (const StageParams *)group->params, group->n_inst,
-                       c->gemv_kernel, group->mixed);
+                       c->gemv_kernel, group->mixed, group->fed);
 }
 
 void qk_group_free(qk_group *g) {
@@ -1787,6 +1839,8 @@ void qk_group_free(qk_group *g) {
     cudaSetDevice(g->device);
     if (g->scratch) cudaFree(g->scratch);
     if (g->params) cudaFree(g->params);
+    if (g->feed) cudaFree(g->feed);
+    if (g->tickets) cudaFree(g->tickets);
     delete g;
 }
 
@@ -1895,9 +1949,9 @@ qk_status qk_layer_apply_noalloc(qk_ctx *ctx, const qk_layer *layer, const float
     StageMeta *meta = reinterpret_cast<StageMeta *>(scratch + kNoAllocMaxRank * sizeof(double));
     const bool bf16 = layer->serving == QK_BF16;
     StageParams a{layer->vbt, layer->vbt_tiles, x_dev, layer->s2, t_buf, nullptr, nullptr, nullptr,
-                  meta, nullptr, (uint32_t)layer->r, (uint32_t)layer->din};
+                  meta, nullptr, (uint32_t)layer->r, (uint32_t)layer->din, nullptr, nullptr, nullptr};
     StageParams b{layer->ub, layer->ub_tiles, t_buf, nullptr, y_dev, layer->s1, layer->bias, nullptr,
-                  meta + 1, nullptr, (uint32_t)layer->dout, (uint32_t)layer->r};
+                  meta + 1, nullptr, (uint32_t)layer->dout, (uint32_t)layer->r, nullptr, nullptr, nullptr};
     if ((st = launch_value_stage<false>(c, a, s1, bf16)) != QK_OK) return st;
     return launch_value_stage<true>(c, b, s2, bf16);
 }

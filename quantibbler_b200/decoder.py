@@ -21,7 +21,7 @@ import numpy as np
 
 from . import _lib, tp
 from ._lib import QK_BF16, QK_F32, KernelError, check
-from .gpu import GpuContext, LayerPlan, PackedLayer, apply_prefill_many
+from .gpu import GpuContext, LayerPlan, PackedLayer, apply_prefill_many, make_feed
 
 LINEARS = ("q", "k", "v", "o", "gate", "up", "down")
 
@@ -45,6 +45,9 @@ class DecoderConfig:
     gemm_min_batch: int = 16       # bfloat16 serving: batches this large take the tensor-core GEMM
     fused_allreduce: bool = True   # tensor parallel: the all-reduce happens inside the norm, over peer memory
     fused_allreduce_max_bytes: int = 1 << 20   # ... while a rank pushes at most this much per all-reduce
+    feed_max_batch: int = 4        # batches this small: digit tables are built where a vector is produced
+    prefill_min_tokens: int = 16   # generate(): prompts this long go through the trunk in one pass
+    prefill_chunk: int = 2048      # ... in pieces of at most this many positions
 
 
 def rope_table(cfg: DecoderConfig) -> np.ndarray:
@@ -278,6 +281,25 @@ class Decoder:
         # a large enough batch is a real contraction: the tcgen05 GEMM expands each weight bit
         # once for all tokens, the GEMV forms would do it once per token
         self.use_gemm = cfg.serving == "bfloat16" and B >= cfg.gemm_min_batch
+        # A small batch is bound by what every GEMV block does before it can multiply (scan the
+        # input, build its digit table).  Fed plans move that to the kernel that produces the
+        # vector, once per vector: the norm feeds q,k,v and gate,up, the attention combine feeds
+        # o, the SwiGLU feeds down.
+        self.fed = (not self.use_gemm) and B <= cfg.feed_max_batch
+        self.feeds = []
+        if self.fed:
+            for plan in self.plans:
+                def group(keys):
+                    pairs = []
+                    for key, per_token in keys:
+                        if key in plan:
+                            pairs.append((plan[key], per_token))
+                    return make_feed(pairs)
+                self.feeds.append({
+                    "qkv": group([("qkv", 3), ("q", 1), ("kv", 2), ("k", 1), ("v", 1)]),
+                    "o": group([("o", 1)]),
+                    "gu": group([("gu", 2), ("gate", 1), ("up", 1)]),
+                    "down": group([("down", 1)])})
         self.graph = None
         self.kernels_per_step = None
         self._host_positions = [0] * B
@@ -313,21 +335,23 @@ class Decoder:
         if self.tp_size > 1 and not self.fused_ar:
             self.torch.distributed.all_reduce(t, group=self.group)
 
-    def _norm(self, pending, weight) -> None:
+    def _norm(self, pending, weight, feed=None) -> None:
         """x += pending partial outputs (summed over the ranks); h = RMSNorm(x) * weight.
-        ``pending``: None, 0 (attention block's o output) or 1 (MLP block's down output)."""
+        ``pending``: None, 0 (attention block's o output) or 1 (MLP block's down output).
+        ``feed``: the fed plans that read h (their digit tables are written here)."""
         lib, c, cfg = _lib.lib(), self.ctx.handle, self.cfg
         B, d = cfg.max_batch, cfg.d_model
+        fp = ctypes.byref(feed) if feed is not None else None
         if pending is not None and self.fused_ar:
             partial = self.delta_attn if pending == 0 else self.delta_mlp
-            check(lib.qk_allreduce_rmsnorm(
+            check(lib.qk_allreduce_rmsnorm_feed(
                 c, _p(partial), self._peer_inbox[pending].ctypes.data, _p(self._ar_state),
                 self.tp_rank, self.tp_size, _p(self.x), _p(weight), B, d, cfg.rms_eps,
-                self.serving_tag, _p(self.x), _p(self.h)))
+                self.serving_tag, _p(self.x), _p(self.h), fp))
             return
         residual = None if pending is None else _p(self.delta_attn if pending == 0 else self.delta_mlp)
-        check(lib.qk_rmsnorm(c, _p(self.x), residual, _p(weight), B, d, cfg.rms_eps,
-                             self.serving_tag, _p(self.x), _p(self.h)))
+        check(lib.qk_rmsnorm_feed(c, _p(self.x), residual, _p(weight), B, d, cfg.rms_eps,
+                                  self.serving_tag, _p(self.x), _p(self.h), fp))
 
     # ------------------------------------------------------------------ one step
 
@@ -359,7 +383,8 @@ class Decoder:
         pending = None
         for li in range(cfg.n_layers):
             in_w, post_w = self.norms[li]
-            self._norm(pending, in_w)
+            feeds = self.feeds[li] if self.fed else None
+            self._norm(pending, in_w, feeds["qkv"] if feeds else None)
             self._linears(li, ["q", "k", "v"], self.h, [self.q, self.k, self.v])
             if self.qk_norms[li] is not None:
                 # every head is one row of head_dim values; x_out = x rewrites the projection
@@ -372,15 +397,19 @@ class Decoder:
                                     _p(self.positions), _p(self.seq_index), _p(self.cache_k[li]),
                                     _p(self.cache_v[li]), self.kv_tag, B, self.h_loc, self.kv_loc,
                                     hd, cfg.max_seq, B))
-            check(lib.qk_decode_attention(c, _p(self.qn), _p(self.cache_k[li]), _p(self.cache_v[li]),
-                                          self.kv_tag, _p(self.kv_len), B, self.h_loc, self.kv_loc,
-                                          hd, cfg.max_seq, self.n_splits, _p(self.att_scratch),
-                                          _p(self.attn)))
+            check(lib.qk_decode_attention_feed(
+                c, _p(self.qn), _p(self.cache_k[li]), _p(self.cache_v[li]), self.kv_tag,
+                _p(self.kv_len), B, self.h_loc, self.kv_loc, hd, cfg.max_seq, self.n_splits,
+                _p(self.att_scratch), _p(self.attn), self.serving_tag,
+                ctypes.byref(feeds["o"]) if feeds else None))
             self._linears(li, ["o"], self.attn, [self.delta_attn])
             self._all_reduce(self.delta_attn)
-            self._norm(0, post_w)
+            self._norm(0, post_w, feeds["gu"] if feeds else None)
             self._linears(li, ["gate", "up"], self.h, [self.g, self.u])
-            if self.use_gemm:
+            if feeds:
+                check(lib.qk_swiglu_feed(c, _p(self.g), _p(self.u), B, self.ff_loc, self.serving_tag,
+                                         ctypes.byref(feeds["down"])))
+            elif self.use_gemm:
                 check(lib.qk_swiglu(c, _p(self.g), _p(self.u), B * self.ff_loc, _p(self.a)))
             # (the GEMV path's down plan applies the SwiGLU to gate and up as it reads them)
             self._linears(li, ["down"], self.a, [self.delta_mlp])
@@ -393,14 +422,136 @@ class Decoder:
         check(lib.qk_argmax_first(c, _p(self.logits), B, self.v_loc, self.v_loc, self.vocab_offset,
                                   _p(self.best_val), _p(self.best_idx)))
         if self.tp_size > 1:
-            torch = self.torch
-            vals = [torch.empty_like(self.best_val) for _ in range(self.tp_size)]
-            idxs = [torch.empty_like(self.best_idx) for _ in range(self.tp_size)]
-            torch.distributed.all_gather(vals, self.best_val, group=self.group)
-            torch.distributed.all_gather(idxs, self.best_idx, group=self.group)
-            v = torch.stack(vals)              # [ranks, B]; shards are in vocabulary order,
-            win = torch.argmax(v, dim=0)       # and argmax returns the first maximum
-            self.best_idx.copy_(torch.stack(idxs).gather(0, win[None])[0])
+            self._gather_argmax(self.best_val, self.best_idx)
+
+    # ------------------------------------------------------------------ batched prefill
+    def _prefill_buffers(self, n_tokens: int) -> dict:
+        """Activation buffers for ``n_tokens`` positions at once (kept and reused)."""
+        torch, cfg = self.torch, self.cfg
+        have = getattr(self, "_pf", None)
+        if have is not None and have["cap"] >= n_tokens:
+            return have
+        dev = self.x.device
+        f32 = dict(dtype=torch.float32, device=dev)
+        hd, d = cfg.head_dim, cfg.d_model
+        T = n_tokens
+        pf = dict(cap=T, x=torch.zeros(T, d, **f32), h=torch.zeros(T, d, **f32),
+                  q=torch.zeros(T, self.h_loc * hd, **f32), k=torch.zeros(T, self.kv_loc * hd, **f32),
+                  v=torch.zeros(T, self.kv_loc * hd, **f32), attn=torch.zeros(T, self.h_loc * hd, **f32),
+                  delta=torch.zeros(T, d, **f32), g=torch.zeros(T, self.ff_loc, **f32),
+                  u=torch.zeros(T, self.ff_loc, **f32), a=torch.zeros(T, self.ff_loc, **f32),
+                  ids=torch.zeros(T, dtype=torch.int32, device=dev),
+                  pos=torch.zeros(T, dtype=torch.int32, device=dev),
+                  seq=torch.zeros(T, dtype=torch.int32, device=dev))
+        if self.has_qk_norm:
+            pf["qn"], pf["kn"] = torch.zeros_like(pf["q"]), torch.zeros_like(pf["k"])
+        else:
+            pf["qn"], pf["kn"] = pf["q"], pf["k"]
+        self._pf = pf
+        return pf
+
+    def _prefill_linears(self, li: int, names, src, dsts, n_tokens: int) -> None:
+        """The named linears of layer ``li`` on ``n_tokens`` rows of ``src``: the tensor-core GEMM
+        for bfloat16 serving (every weight bit expanded once for all rows), otherwise one GEMV
+        instance per row (many rows run in the persistent streaming form)."""
+        layers = [self.layers[li][n] for n in names]
+        if self.cfg.serving == "bfloat16" and n_tokens >= self.cfg.gemm_min_batch:
+            apply_prefill_many(layers, src.data_ptr(), n_tokens, [t.data_ptr() for t in dsts])
+        else:
+            for layer, dst in zip(layers, dsts):
+                layer.apply_device(src.data_ptr(), n_tokens, dst.data_ptr())
+
+    def prefill(self, tokens, seq: int = 0, first_position: int = 0) -> None:
+        """All of ``tokens`` (consecutive positions ``first_position ...`` of sequence slot ``seq``)
+        through the trunk in one pass per ``prefill_chunk`` positions: the batched form of the
+        reference's prompt loop (engine/mod.rs:1393-1413, one ``transformer`` call per prompt
+        token).  Appends the keys and values of every position to the cache and leaves the
+        greedy token of the last position in ``best_idx[seq]``; ``advance()`` + ``step()`` then
+        continue the sequence.  Only the last position goes through the final norm and the head."""
+        torch, lib, c, cfg = self.torch, _lib.lib(), self.ctx.handle, self.cfg
+        toks = [int(t) for t in tokens]
+        if not toks:
+            raise ValueError("prefill needs at least one token")
+        if not 0 <= seq < cfg.max_batch:
+            raise ValueError(f"sequence slot {seq} outside the batch of {cfg.max_batch}")
+        check_cache_capacity([first_position], len(toks), cfg.max_seq)
+        B, d, hd = cfg.max_batch, cfg.d_model, cfg.head_dim
+        handle = self.ctx.stream
+        # (handles 0 and 1 are the legacy default stream, which torch wraps itself)
+        stream = torch.cuda.ExternalStream(handle) if handle > 2 else torch.cuda.default_stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for c0 in range(0, len(toks), cfg.prefill_chunk):
+                part = toks[c0:c0 + cfg.prefill_chunk]
+                T, p0 = len(part), first_position + c0
+                pf = self._prefill_buffers(min(len(toks), cfg.prefill_chunk))
+                pf["ids"][:T].copy_(torch.tensor(part, dtype=torch.int32), non_blocking=False)
+                pf["pos"][:T].copy_(torch.arange(p0, p0 + T, dtype=torch.int32))
+                pf["seq"][:T].fill_(seq)
+                check(lib.qk_embed(c, _p(self.embedding), self.emb_tag, _p(pf["ids"]), T, d, cfg.vocab,
+                                   _p(pf["x"])))
+                pending = None
+                for li in range(cfg.n_layers):
+                    in_w, post_w = self.norms[li]
+                    check(lib.qk_rmsnorm(c, _p(pf["x"]), pending, _p(in_w), T, d, cfg.rms_eps,
+                                         self.serving_tag, _p(pf["x"]), _p(pf["h"])))
+                    self._prefill_linears(li, ["q", "k", "v"], pf["h"], [pf["q"], pf["k"], pf["v"]], T)
+                    if self.qk_norms[li] is not None:
+                        for src, dst, wgt, heads in ((pf["q"], pf["qn"], self.qk_norms[li][0], self.h_loc),
+                                                     (pf["k"], pf["kn"], self.qk_norms[li][1], self.kv_loc)):
+                            check(lib.qk_rmsnorm(c, _p(src), None, _p(wgt), T * heads, hd, cfg.rms_eps,
+                                                 self.serving_tag, _p(src), _p(dst)))
+                    check(lib.qk_rope_cache(c, _p(pf["qn"]), _p(pf["kn"]), _p(pf["v"]), _p(self.cos_sin),
+                                            _p(pf["pos"]), _p(pf["seq"]), _p(self.cache_k[li]),
+                                            _p(self.cache_v[li]), self.kv_tag, T, self.h_loc,
+                                            self.kv_loc, hd, cfg.max_seq, B))
+                    check(lib.qk_prefill_attention(c, _p(pf["qn"]), _p(self.cache_k[li]),
+                                                   _p(self.cache_v[li]), self.kv_tag, seq, p0, T,
+                                                   self.h_loc, self.kv_loc, hd, cfg.max_seq,
+                                                   _p(pf["attn"])))
+                    self._prefill_linears(li, ["o"], pf["attn"], [pf["delta"]], T)
+                    if self.tp_size > 1:
+                        torch.distributed.all_reduce(pf["delta"][:T], group=self.group)
+                    check(lib.qk_rmsnorm(c, _p(pf["x"]), _p(pf["delta"]), _p(post_w), T, d, cfg.rms_eps,
+                                         self.serving_tag, _p(pf["x"]), _p(pf["h"])))
+                    self._prefill_linears(li, ["gate", "up"], pf["h"], [pf["g"], pf["u"]], T)
+                    check(lib.qk_swiglu(c, _p(pf["g"]), _p(pf["u"]), T * self.ff_loc, _p(pf["a"])))
+                    self._prefill_linears(li, ["down"], pf["a"], [pf["delta"]], T)
+                    if self.tp_size > 1:
+                        torch.distributed.all_reduce(pf["delta"][:T], group=self.group)
+                    pending = _p(pf["delta"])
+            # the last position alone: final norm, head, greedy choice
+            last_x, last_delta = pf["x"][T - 1:T], pf["delta"][T - 1:T]
+            check(lib.qk_rmsnorm(c, _p(last_x), _p(last_delta) if pending is not None else None,
+                                 _p(self.final_norm), 1, d, cfg.rms_eps, self.serving_tag, _p(last_x),
+                                 _p(self.h[seq:seq + 1])))
+            head_tag = QK_BF16 if cfg.serving == "bfloat16" else QK_F32
+            check(lib.qk_lm_head(c, _p(self.h[seq:seq + 1]), _p(self.lm_head), head_tag, 1, self.v_loc, d,
+                                 self.v_loc, _p(self.logits[seq:seq + 1])))
+            check(lib.qk_argmax_first(c, _p(self.logits[seq:seq + 1]), 1, self.v_loc, self.v_loc,
+                                      self.vocab_offset, _p(self.best_val[seq:seq + 1]),
+                                      _p(self.best_idx[seq:seq + 1])))
+            if self.tp_size > 1:
+                self._gather_argmax(self.best_val[seq:seq + 1], self.best_idx[seq:seq + 1])
+            last = first_position + len(toks) - 1
+            self.token_ids[seq:seq + 1].fill_(toks[-1])
+            self.positions[seq:seq + 1].fill_(last)
+            self.kv_len[seq:seq + 1].fill_(last + 1)
+        stream.synchronize()
+        torch.cuda.current_stream().wait_stream(stream)
+        self._host_positions[seq] = last
+        self.ctx.synchronize()
+
+    def _gather_argmax(self, best_val, best_idx) -> None:
+        """Vocabulary-parallel head: the first maximum over the ranks' shard winners."""
+        torch = self.torch
+        vals = [torch.empty_like(best_val) for _ in range(self.tp_size)]
+        idxs = [torch.empty_like(best_idx) for _ in range(self.tp_size)]
+        torch.distributed.all_gather(vals, best_val, group=self.group)
+        torch.distributed.all_gather(idxs, best_idx, group=self.group)
+        v = torch.stack(vals)              # [ranks, n]; shards are in vocabulary order,
+        win = torch.argmax(v, dim=0)       # and argmax returns the first maximum
+        best_idx.copy_(torch.stack(idxs).gather(0, win[None])[0])
 
     def advance(self) -> None:
         """Feed the greedy tokens back and move every sequence one position on."""
@@ -480,9 +631,12 @@ class Decoder:
             if not 0 <= tok < self.cfg.vocab:
                 raise ValueError(f"token id {tok} out of range (vocab_size {self.cfg.vocab})")
         started = time.perf_counter()
-        for pos, tok in enumerate(prompt):
-            self.start([tok], [pos])
-            self.step()
+        if len(prompt) >= self.cfg.prefill_min_tokens:
+            self.prefill(prompt, seq=0, first_position=0)   # the whole prompt in one pass
+        else:
+            for pos, tok in enumerate(prompt):
+                self.start([tok], [pos])
+                self.step()
         self.ctx.synchronize()
         prompt_ms = max(1, math.ceil((time.perf_counter() - started) * 1000.0))
         out, finish = [], None

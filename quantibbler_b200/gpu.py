@@ -417,6 +417,26 @@ class HostLayerGroup:
         self.group.close()
 
 
+class Feed(ctypes.Structure):
+    """The C ABI's ``qk_feed``: up to four arrays of feed targets and, for each, how many
+    consecutive targets read one token."""
+    _fields_ = [("targets", ctypes.c_void_p * 4), ("per_token", ctypes.c_size_t * 4),
+                ("n_arrays", ctypes.c_size_t)]
+
+
+def make_feed(pairs) -> Feed:
+    """``pairs``: [(fed LayerPlan, targets per token), ...]."""
+    f = Feed()
+    for i, (plan, per_token) in enumerate(pairs):
+        ptr, n = plan.feed_targets()
+        if n % per_token:
+            raise KernelError(f"a plan of {n} instances cannot be fed {per_token} per token")
+        f.targets[i] = ptr
+        f.per_token[i] = per_token
+    f.n_arrays = len(pairs)
+    return f
+
+
 class LayerPlan(LayerGroup):
     """Instances (layer, x pointer, y pointer) bound once; ``apply`` is two kernel launches
     (one when there are at least as many instances as SMs).  The layers may differ in shape
@@ -440,6 +460,15 @@ class LayerPlan(LayerGroup):
             check(_lib.lib().qk_plan_create(ctx.handle, larr, xarr, yarr, n, ctypes.byref(h)))
         self._h = h
 
+    def feed_targets(self):
+        """Turns the plan into a fed plan (the digit tables of its stage-1 inputs are then
+        written by the ``*_feed`` call that produces those inputs, and every ``apply`` must follow
+        such a call) and returns (device pointer to the per-instance targets, their number)."""
+        ptr, n = ctypes.c_void_p(), ctypes.c_size_t()
+        check(_lib.lib().qk_plan_feed_targets(self.ctx.handle, self._h, ctypes.byref(ptr),
+                                              ctypes.byref(n)))
+        return ptr.value, n.value
 
-__all__ = ["apply_noalloc", "LayerPlan", "LayerGroup", "HostLayerGroup", "GpuContext", "AttentionShape", "PackedLayer", "apply_group", "gpu_available",
+
+__all__ = ["apply_noalloc", "Feed", "make_feed", "LayerPlan", "LayerGroup", "HostLayerGroup", "GpuContext", "AttentionShape", "PackedLayer", "apply_group", "gpu_available",
            "gpu_init_hint", "GPU_INDEX_CEILING", "KernelError", "DeviceError"]

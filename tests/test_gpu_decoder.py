@@ -252,3 +252,105 @@ def test_decode_attention_tensor_core_kernel(gpu_ctx, heads, kv_heads):
                                    causal=True)[0, :, 0]
         assert np.abs(tc[b] - want).max() <= 1e-5 * max(1.0, np.abs(want).max()), (b, group)
     assert np.abs(tc - scalar).max() <= 2e-5
+
+
+@pytest.mark.parametrize("case", [
+    # (query heads, kv heads, head_dim, cache dtype, new tokens, first position)
+    (8, 2, 128, "bfloat16", 70, 37),     # GQA group 4: one CTA per 16 positions
+    (4, 4, 128, "bfloat16", 100, 0),     # MHA: four position blocks per CTA
+    (4, 2, 128, "bfloat16", 33, 5),      # group 2
+    (8, 1, 128, "bfloat16", 17, 200),    # group 8: two CTAs per kv head
+    (4, 2, 32, "float32", 21, 3),        # any other shape: the plain kernel
+    (6, 2, 128, "bfloat16", 19, 0)])     # group 3: the plain kernel as well
+def test_prefill_attention_against_exact_oracle(gpu_ctx, case):
+    """Causal attention of a run of new positions against the cache (bottom-right alignment,
+    gpu_attention.rs:451-570 / engine/mod.rs:1074-1121 per position): the tensor-core kernel and
+    the plain kernel against the float64 oracle under the exact face's 1e-5 gate."""
+    import ctypes
+    import torch
+    from oracle import attention_np as anp
+    from quantibbler_b200 import _lib
+    heads, kv_heads, d, kv_dtype, T, p0 = case
+    rng = np.random.default_rng(sum(case[:3]) + T)
+    n_seq, seq, s_max = 2, 1, p0 + T + 9
+    q = rng.standard_normal((T, heads, d)).astype(np.float32)
+    k = rng.standard_normal((n_seq, kv_heads, s_max, d)).astype(np.float32)
+    v = rng.standard_normal((n_seq, kv_heads, s_max, d)).astype(np.float32)
+    if kv_dtype == "bfloat16":
+        k, v = decoder_np._bf16(k), decoder_np._bf16(v)
+    tq = torch.from_numpy(q).cuda()
+    tdt = torch.bfloat16 if kv_dtype == "bfloat16" else torch.float32
+    tk, tv = torch.from_numpy(k).cuda().to(tdt), torch.from_numpy(v).cuda().to(tdt)
+    out = torch.full((T, heads, d), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    tag = _lib.QK_BF16 if kv_dtype == "bfloat16" else _lib.QK_F32
+    _lib.check(_lib.lib().qk_prefill_attention(gpu_ctx.handle, p(tq), p(tk), p(tv), tag, seq, p0, T,
+                                               heads, kv_heads, d, s_max, p(out)))
+    gpu_ctx.synchronize()
+    got = out.cpu().numpy()
+    n_keys = p0 + T
+    want = anp.attention_exact(q.transpose(1, 0, 2)[None], k[seq][None, :, :n_keys],
+                               v[seq][None, :, :n_keys], causal=True)[0].transpose(1, 0, 2)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("cfg_kw,tol", [
+    (dict(), 2e-4),                                                      # small heads, float32 everywhere
+    (dict(n_heads=8, n_kv_heads=2, head_dim=128, d_model=256, kv_dtype="bfloat16"), 2e-4),
+    (dict(n_heads=8, n_kv_heads=2, head_dim=128, d_model=256, kv_dtype="bfloat16",
+          serving="bfloat16"), 3e-2)])
+def test_batched_prefill_matches_the_token_by_token_path(gpu_ctx, cfg_kw, tol):
+    """Decoder.prefill puts the whole prompt through the trunk at once (tensor-core GEMM for
+    bfloat16 serving, one GEMV instance per position otherwise; tensor-core causal attention
+    for a bfloat16 cache with head_dim 128).  The logits of the last prompt position and the
+    tokens decoded after it must be those of the reference's one-position-at-a-time loop
+    (engine/mod.rs:1393-1413), here run on the device and through the NumPy restatement."""
+    cfg = tiny_cfg(max_batch=2, max_seq=96, **cfg_kw)
+    weights = random_model(cfg, RANKS, seed=21)
+    rng = np.random.default_rng(5)
+    prompt = [int(t) for t in rng.integers(0, cfg.vocab, 45)]
+    # token by token on the device, in slot 1 of the batch
+    step = Decoder(gpu_ctx, cfg, weights)
+    for pos, tok in enumerate(prompt):
+        step.start([0, tok], [0, pos])
+        step.step()
+    gpu_ctx.synchronize()
+    want_logits = step.logits.cpu().numpy()[1].copy()
+    # the same prompt in one pass (two chunks: 32 + 13 positions)
+    cfg2 = tiny_cfg(max_batch=2, max_seq=96, prefill_chunk=32, **cfg_kw)
+    fast = Decoder(gpu_ctx, cfg2, weights)
+    fast.prefill(prompt, seq=1)
+    got_logits = fast.logits.cpu().numpy()[1].copy()
+    scale = np.abs(want_logits).max()
+    assert np.abs(got_logits - want_logits).max() <= tol * scale
+    # the NumPy restatement of the reference's loop
+    kv_round = decoder_np._bf16 if cfg.kv_dtype == "bfloat16" else None
+    session = decoder_np.Session(cfg, weights, kv_round=kv_round)
+    for tok in prompt:
+        _, ref_logits = session.step(tok)
+    assert np.abs(got_logits - ref_logits).max() <= 5 * tol * np.abs(ref_logits).max()
+    # the cache the prefill left behind continues like the stepped one
+    top2 = np.sort(want_logits)[-2:]
+    if top2[1] - top2[0] > 10 * tol * scale:
+        assert int(fast.best_idx[1]) == int(step.best_idx[1])
+        for dec in (step, fast):
+            dec.advance()
+            dec.step()
+        gpu_ctx.synchronize()
+        a, b = fast.logits.cpu().numpy()[1], step.logits.cpu().numpy()[1]
+        assert np.abs(a - b).max() <= 2 * tol * np.abs(b).max()
+
+
+def test_generate_uses_the_batched_prefill_for_long_prompts(gpu_ctx):
+    cfg = tiny_cfg(max_batch=1, max_seq=128)
+    weights = random_model(cfg, RANKS, seed=22)
+    prompt = [int(t) for t in np.random.default_rng(6).integers(1, cfg.vocab, 40)]
+    want, finish = decoder_np.generate(cfg, weights, prompt, 6)
+    dec = Decoder(gpu_ctx, cfg, weights)
+    assert len(prompt) >= cfg.prefill_min_tokens
+    got = dec.generate(prompt, 6)
+    assert got["completion_tokens"] == want and got["finish"] == finish
+    with pytest.raises(ValueError, match="does not fit the KV cache"):
+        dec.prefill([1] * 200)
