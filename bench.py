@@ -2,8 +2,8 @@
 """Benchmark of the factorized-linear decode GEMV on B200.
 
 One step = one pass of the hot path over one batch of synthetic input: every layer of a
-stack of L distinct, device-resident factorized linears (the shape of BASELINE.json's
-config 0: d_in = d_out = 4096, rank 1024, one token each) is applied once, in one
+stack of L distinct, device-resident factorized linears (the shape of the benchmark's
+configuration 0: d_in = d_out = 4096, rank 1024, one token each) is applied once, in one
 grouped launch pair.  The stack is larger than the L2 (L x 1.06 MB > 126 MB), so the
 packed bits stream from HBM on every step.
 
@@ -47,7 +47,7 @@ UNIT = "GB/s"
 
 
 def make_stack(n_layers: int, seed: int):
-    """Seeded synthetic layers as BASELINE.json config 0 prescribes."""
+    """Seeded synthetic layers as the benchmark's configuration 0 prescribes."""
     rng = np.random.default_rng(seed)
     for _ in range(n_layers):
         ub_rows = rng.integers(0, 256, size=(DOUT, RANK // 8), dtype=np.uint8)
@@ -175,20 +175,20 @@ def run_reference(args, rank: int) -> None:
     }))
 
 
-# Where BASELINE.json's configurations and the reference disagree; each affected line carries
+# Where the benchmark's configurations and the reference disagree; each affected line carries
 # its entry in `config.divergences`.
 DIVERGENCES = {
-    "attention": "BASELINE config 2 words Sage as per-64-token-block INT8 scales for Q and K with "
+    "attention": "benchmark configuration 2 words Sage as per-64-token-block INT8 scales for Q and K with "
                  "PV in bf16; the reference quantises Q and K per token, P to INT8 at the static "
                  "scale 1/127 and V to INT8 per channel per key block, both products in integers "
                  "(src/quantibbler/kernels/attention_sage.py:24-36,164-198,297-323).  Measured "
-                 "here: the reference's arithmetic, at BASELINE's shape.",
-    "prefill": "BASELINE config 1 calls rank 2560 at 4096<->14336 'roughly 0.55 bits/weight'; by "
+                 "here: the reference's arithmetic, at the benchmark's shape.",
+    "prefill": "benchmark configuration 1 calls rank 2560 at 4096<->14336 'roughly 0.55 bits/weight'; by "
                "the reference's byte formula (src/quantibbler/qpk1.py:261-284) it is 0.81 "
-               "(0.55 would be rank ~1750).  Measured here: rank 2560 as BASELINE prescribes.",
+               "(0.55 would be rank ~1750).  Measured here: rank 2560 as the benchmark prescribes.",
     "decode": "The reference's engine is single-GPU, batch 1, one token per call, with a float32 "
               "KV cache (crates/quantibbler-server/src/engine/mod.rs:878-945); tensor "
-              "parallelism, batched decode and the bfloat16 cache are BASELINE's.  Ranks are the "
+              "parallelism, batched decode and the bfloat16 cache are the benchmark's.  Ranks are the "
               "reference's rank_for_target_bpw at 0.55 bits/weight.",
 }
 
@@ -199,7 +199,7 @@ C3_RANKS = {"q": 1102, "k": 1102, "v": 1102, "o": 1102, "gate": 1614, "up": 1614
 
 
 def decode_config(model: str, n_layers: int, batch: int, max_seq: int, allreduce: str):
-    """DecoderConfig + ranks of BASELINE's config 4 ("llama3-8b") or config 3."""
+    """DecoderConfig + ranks of the benchmark's configuration 4 ("llama3-8b") or config 3."""
     from quantibbler_b200.decoder import DecoderConfig
     if model == "llama3-8b":
         return DecoderConfig(n_layers=n_layers or 32, d_model=4096, n_heads=32, n_kv_heads=8,
@@ -313,7 +313,7 @@ def measure_allreduce(dec, world, group, n_calls: int) -> float | None:
 
 
 def run_decode(args, rank: int, local_rank: int, world: int) -> None:
-    """Greedy decode tok/s of a Llama-shaped stack of factorized linears (BASELINE configs
+    """Greedy decode tok/s of a Llama-shaped stack of factorized linears (benchmark configurations
     3 and 4), tensor-parallel over the ranks, one CUDA graph per step."""
     import torch
     import torch.distributed as dist
@@ -358,7 +358,7 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
 
 
 def tp_decode_block(args, ctx, rank: int, world: int, group) -> dict:
-    """BASELINE config 4 measured in the same process group as the headline: the 32-layer
+    """benchmark configuration 4 measured in the same process group as the headline: the 32-layer
     Llama-3-8B-shaped stack, tensor-parallel over the ranks, batch 1 and batch 64, context
     2048 (a synthetic KV cache stands in for the prompt)."""
     import torch
@@ -374,6 +374,25 @@ def tp_decode_block(args, ctx, rank: int, world: int, group) -> dict:
         res, dec = measure_decode(ctx, cfg, ranks, batch, ctx_len, steps, 3, rank, world, group,
                                   share_from=shared)
         res["allreduce_ms_per_step"] = measure_allreduce(dec, world, group, 2 * cfg.n_layers)
+        if batch == 1:
+            # the prompt itself: 2048 tokens through the trunk in one pass (tensor-core GEMM for
+            # every linear, tensor-core causal attention, head on the last position only)
+            prompt = torch.randint(0, cfg.vocab, (ctx_len,),
+                                   generator=torch.Generator().manual_seed(3)).tolist()
+            times = []
+            for _ in range(2):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                dec.prefill(prompt, seq=0, first_position=0)
+                torch.cuda.synchronize()
+                times.append((time.perf_counter() - t0) * 1e3)
+            if world > 1:
+                t = torch.tensor([times[-1]], dtype=torch.float64, device="cuda")
+                torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX, group=group)
+                times[-1] = float(t[0])
+            res["prompt_ms"] = times[-1]
+            res["prompt_tokens"] = ctx_len
+            res["prompt_tok_s"] = ctx_len / (times[-1] * 1e-3)
         out[f"batch{batch}"] = res
         if shared is None:
             shared = dec
@@ -384,7 +403,7 @@ def tp_decode_block(args, ctx, rank: int, world: int, group) -> dict:
 
 
 def run_prefill(args, local_rank: int) -> None:
-    """BASELINE config 1: the three MLP linears of a Llama-3-8B block on 2048 tokens, bfloat16
+    """benchmark configuration 1: the three MLP linears of a Llama-3-8B block on 2048 tokens, bfloat16
     activations, tensor-core prefill GEMM.  Reports dense-equivalent TFLOP/s."""
     import torch
 
@@ -470,7 +489,7 @@ def run_prefill(args, local_rank: int) -> None:
 
 
 def run_attention(args, local_rank: int) -> None:
-    """BASELINE config 2: Sage INT8 attention forward, batch 1, 32 query heads, 8 KV heads,
+    """benchmark configuration 2: Sage INT8 attention forward, batch 1, 32 query heads, 8 KV heads,
     head_dim 128, 8192 tokens, causal, key block 64; K carries a per-channel offset N(0, 4).
     Reports TOP/s on the algorithmic integer work (QK^T and PV over the causal half) against
     the dense INT8 tensor peak (twice the measured bf16 peak); the exact float32 face and
@@ -554,11 +573,12 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=592, help="distinct layers per step (4 x 148)")
+    ap.add_argument("--layers", type=int, default=2368, help="distinct layers per step (16 x 148)")
     ap.add_argument("--kernel", type=int, default=-1, help="GEMV kernel override (debug)")
     ap.add_argument("--shape", default="", help="dout,din,rank override (debug; not the metric)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
-    ap.add_argument("--e2e-applies", type=int, default=296)
+    ap.add_argument("--e2e-applies", type=int, default=296,
+                    help="layers of the one-call-per-layer leg (0 switches both end-to-end legs off)")
     ap.add_argument("--workload", default="gemv", choices=["gemv", "decode", "prefill", "attention"])
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "llama2-7b-layer"])
@@ -750,7 +770,8 @@ def main() -> None:
                    "ms_per_step": e2e_step_ms,
                    "call": "HostLayerGroup.apply(x_host, y_host): the step's inputs from pinned "
                            "host memory, the step's launches, its outputs back to pinned host "
-                           "memory, synchronise",
+                           "memory, synchronise (the layers go through in four sub-groups, upload, "
+                           "kernels and download of neighbouring sub-groups overlapping)",
                    "per_layer_call": per_layer}
         else:
             e2e = dict(per_layer, step_error=e2e_step_error)
@@ -771,7 +792,8 @@ def main() -> None:
                          "traffic_note": "bytes per launch, scaled by layers from an ncu capture "
                                          "of a 296-layer launch",
                          "peak_source": peak_src,
-                         "kernel": "layer_bitslice_fused_kernel, one launch per step"},
+                         "kernel": "layer_bitslice_fused_kernel, one launch per step"
+                                   if ctx.set_gemv_kernel(-1) != 6 else "layer_stream_kernel"},
             "e2e": e2e,
             "gpu_launches": launches,
             "clocks": dict(clocks.summary(),
@@ -783,7 +805,7 @@ def main() -> None:
                                   f"after the region `value` is computed from"}
         if world == 1 and args.cpu_seconds > 0:
             line["cpu_baseline"] = cpu_baseline(args.cpu_seconds)
-    # BASELINE's second metric half: config-4 decode under tensor parallelism, in this same
+    # the second half of the benchmark's metric: config-4 decode under tensor parallelism, in this same
     # process group, so that a run at N GPUs carries the N-rank number
     tp_block = None
     if args.tp_decode:

@@ -66,9 +66,21 @@ struct qk_ctx {
     bool err_armed = false;  // sticky: set by the first launch that can raise the error word
     uint32_t wait_limit = 0;  // polls before a device-side wait gives up (0: the default)
     bool pdl = true;          // decoder-path kernels may overlap their prologue with the kernel before
-    void *h_pinned = nullptr;
-    size_t h_pinned_cap = 0;
-    qk_status pinned(size_t bytes, void **out);
+    // Pinned staging for launch parameters: a small ring of blocks, each guarded by an event
+    // that is recorded after the copy out of it, so that a call only waits (on the host) when
+    // it comes back to a block whose copy is still in flight - not on every call.
+    static constexpr int kPinnedSlots = 4;
+    struct PinnedSlot {
+        void *ptr = nullptr;
+        size_t cap = 0;
+        cudaEvent_t copied = nullptr;
+        bool in_flight = false;
+    } h_pinned[kPinnedSlots];
+    int h_pinned_next = 0;
+    // A block of at least `bytes`, free to be overwritten; *slot names it for pinned_done().
+    qk_status pinned(size_t bytes, void **out, int *slot);
+    // Call after the asynchronous copy out of the block has been issued on `stream`.
+    qk_status pinned_done(int slot);
 };
 
 struct qk_layer {

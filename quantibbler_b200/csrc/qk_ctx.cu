@@ -26,21 +26,37 @@ void qk_scratch::release() {
     cap = 0;
 }
 
-qk_status qk_ctx::pinned(size_t bytes, void **out) {
-    if (bytes > h_pinned_cap) {
-        if (h_pinned) cudaFreeHost(h_pinned);
-        h_pinned = nullptr;
-        h_pinned_cap = 0;
+qk_status qk_ctx::pinned(size_t bytes, void **out, int *slot) {
+    PinnedSlot &ps = h_pinned[h_pinned_next];
+    *slot = h_pinned_next;
+    h_pinned_next = (h_pinned_next + 1) % kPinnedSlots;
+    if (ps.in_flight) {
+        // only when the ring has come round to a block whose copy has not finished
+        QK_CUDA(cudaEventSynchronize(ps.copied));
+        ps.in_flight = false;
+    }
+    if (bytes > ps.cap) {
+        if (ps.ptr) cudaFreeHost(ps.ptr);
+        ps.ptr = nullptr;
+        ps.cap = 0;
         size_t want = bytes < 65536 ? 65536 : bytes;
-        cudaError_t e = cudaMallocHost(&h_pinned, want);
+        cudaError_t e = cudaMallocHost(&ps.ptr, want);
         if (e != cudaSuccess) {
-            h_pinned = nullptr;
+            ps.ptr = nullptr;
             return qk::fail(QK_ERR_ALLOC, "pinned host allocation of %zu bytes failed: %s", want,
                             cudaGetErrorString(e));
         }
-        h_pinned_cap = want;
+        ps.cap = want;
     }
-    *out = h_pinned;
+    if (!ps.copied) QK_CUDA(cudaEventCreateWithFlags(&ps.copied, cudaEventDisableTiming));
+    *out = ps.ptr;
+    return QK_OK;
+}
+
+qk_status qk_ctx::pinned_done(int slot) {
+    PinnedSlot &ps = h_pinned[slot];
+    QK_CUDA(cudaEventRecord(ps.copied, stream));
+    ps.in_flight = true;
     return QK_OK;
 }
 
@@ -150,7 +166,10 @@ void qk_gpu_free(qk_ctx *ctx) {
     ctx->d_ptrs.release();
     ctx->d_err.release();
     ctx->d_head.release();
-    if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
+    for (auto &ps : ctx->h_pinned) {
+        if (ps.copied) cudaEventDestroy(ps.copied);
+        if (ps.ptr) cudaFreeHost(ps.ptr);
+    }
     delete ctx;
 }
 
@@ -193,7 +212,7 @@ int32_t qk_set_gemv_kernel(qk_ctx *ctx, int32_t which) {
     qk_ctx *c;
     if (qk::resolve_ctx(ctx, &c) != QK_OK) return -1;
     int prev = c->gemv_kernel;
-    if (which >= 0 && which <= 5) c->gemv_kernel = which;
+    if (which >= 0 && which <= 6) c->gemv_kernel = which;
     return prev;
 }
 

@@ -73,8 +73,9 @@ struct FeedArgs {
     uint32_t per_token[4];
     uint32_t n;
 };
+constexpr unsigned kFeedParts = 8;  // blocks that share the table building of one token
 __device__ __forceinline__ void feed_consumers(const FeedArgs &feed, uint32_t token, const float *vals,
-                                               bool bf16) {
+                                               bool bf16, uint32_t part = 0, uint32_t n_parts = 1) {
     __shared__ double feed_max[32];
     __shared__ long long feed_sum[32];
     __shared__ int feed_bad;
@@ -89,7 +90,8 @@ __device__ __forceinline__ void feed_consumers(const FeedArgs &feed, uint32_t to
                     if (bf16) v = round_bf16f(v);
                     return (double)v;
                 },
-                tg.n_steps, reinterpret_cast<uint4 *>(tg.digits), tg.meta, feed_max, feed_sum, &feed_bad);
+                tg.n_steps, reinterpret_cast<uint4 *>(tg.digits), tg.meta, feed_max, feed_sum, &feed_bad, part,
+                n_parts);
         }
 }
 
@@ -107,6 +109,9 @@ rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
     extern __shared__ float norm_row[];  // the token's y (only when consumers are fed)
     __shared__ float red[kRmsThreads / 32];
     const size_t base = (size_t)blockIdx.x * d;
+    // gridDim.y > 1: several blocks per token share the table building; each computes the whole
+    // norm (x_out must then be another buffer than x), block 0 alone writes x_out and y
+    const bool writer = blockIdx.y == 0;
     float keep[kRmsPerThread];
     float ss = 0.f;
 #pragma unroll
@@ -116,7 +121,7 @@ rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
         if (i < d) {
             h = x[base + i];
             if (residual) h += residual[base + i];
-            if (x_out) x_out[base + i] = h;
+            if (x_out && writer) x_out[base + i] = h;
             if (bf16) h = round_bf16f(h);
         }
         keep[r] = h;
@@ -125,7 +130,7 @@ rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
     for (uint32_t i = threadIdx.x + kRmsPerThread * kRmsThreads; i < d; i += kRmsThreads) {
         float h = x[base + i];
         if (residual) h += residual[base + i];
-        if (x_out) x_out[base + i] = h;
+        if (x_out && writer) x_out[base + i] = h;
         if (bf16) h = round_bf16f(h);
         ss += h * h;
     }
@@ -136,22 +141,22 @@ rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
         if (i < d) {
             float o = keep[r] * inv * w[i];
             if (bf16) o = round_bf16f(o);
-            y[base + i] = o;
+            if (writer) y[base + i] = o;
             if (feed.n) norm_row[i] = o;
         }
     }
     for (uint32_t i = threadIdx.x + kRmsPerThread * kRmsThreads; i < d; i += kRmsThreads) {
-        // x_out (or x, when the sum was not written back) holds h
-        float h = x_out ? x_out[base + i] : x[base + i] + (residual ? residual[base + i] : 0.f);
+        // in place (x_out == x, one block per token) x already holds h; otherwise x is untouched
+        float h = x_out == x ? x[base + i] : x[base + i] + (residual ? residual[base + i] : 0.f);
         if (bf16) h = round_bf16f(h);
         float o = h * inv * w[i];
         if (bf16) o = round_bf16f(o);
-        y[base + i] = o;
+        if (writer) y[base + i] = o;
         if (feed.n) norm_row[i] = o;
     }
     if (feed.n) {
         __syncthreads();
-        feed_consumers(feed, blockIdx.x, norm_row, bf16 != 0);
+        feed_consumers(feed, blockIdx.x, norm_row, bf16 != 0, blockIdx.y, gridDim.y);
     }
 }
 
@@ -191,6 +196,9 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
     extern __shared__ float norm_row[];  // the token's y (only when consumers are fed)
     __shared__ float red[kRmsThreads / 32];
     __shared__ int gave_up;
+    // gridDim.y > 1: several blocks per token share the table building; block 0 alone sends and
+    // writes x_out and y, all of them receive (the inbox is local memory) and compute the norm
+    const bool writer = blockIdx.y == 0;
     const uint32_t step = *counter + 1;
     if (threadIdx.x == 0) gave_up = 0;
     __syncthreads();
@@ -205,7 +213,7 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
         for (int sl = 0; sl < kSlots; ++sl) {
             const uint32_t i = threadIdx.x + (pass * kSlots + sl) * kRmsThreads;
             own[sl] = i < d ? partial[base + i] : 0.f;
-            if (i < d) {
+            if (i < d && writer) {
                 const unsigned long long word =
                     (unsigned long long)__float_as_uint(own[sl]) | ((unsigned long long)step << 32);
 #pragma unroll
@@ -257,7 +265,7 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
             const uint32_t i = threadIdx.x + (pass * kSlots + sl) * kRmsThreads;
             if (i < d) {
                 float h = x[base + i] + sum[sl];
-                x_out[base + i] = h;
+                if (writer) x_out[base + i] = h;
                 if (bf16) h = round_bf16f(h);
                 if (pass * kSlots + sl < (uint32_t)kRmsPerThread) keep[pass * kSlots + sl] = h;
                 ss += h * h;
@@ -275,28 +283,28 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
             if (r < (uint32_t)kRmsPerThread) {
                 h = keep[r];
             } else {
-                h = x_out[base + i];
+                h = x_out[base + i];   // (rows wider than the register cache: one block per token only)
                 if (bf16) h = round_bf16f(h);
             }
             float o = h * inv * w[i];
             if (bf16) o = round_bf16f(o);
-            y[base + i] = o;
+            if (writer) y[base + i] = o;
             if (feed.n) norm_row[i] = o;
         }
         if (feed.n) {
             __syncthreads();
-            feed_consumers(feed, blockIdx.x, norm_row, bf16 != 0);
+            feed_consumers(feed, blockIdx.x, norm_row, bf16 != 0, blockIdx.y, gridDim.y);
         }
     }
     // the last block to finish records that this all-reduce is done (every block has read the
     // counter by then); a single block needs no ticket
-    if (gridDim.x == 1) {
+    if (gridDim.x * gridDim.y == 1) {
         if (threadIdx.x == 0) *counter = step;
     } else {
         __syncthreads();
         if (threadIdx.x == 0) {
             __threadfence();
-            if (atomicAdd(done, 1u) == gridDim.x - 1) {
+            if (atomicAdd(done, 1u) == gridDim.x * gridDim.y - 1) {
                 *done = 0;
                 *counter = step;
             }
@@ -1079,7 +1087,7 @@ swiglu_feed_kernel(const float *__restrict__ g, const float *__restrict__ u, uin
         act_row[i] = gv * u[base + i] / (1.0f + expf(-gv));
     }
     __syncthreads();
-    feed_consumers(feed, blockIdx.x, act_row, bf16 != 0);
+    feed_consumers(feed, blockIdx.x, act_row, bf16 != 0, blockIdx.y, gridDim.y);
 }
 
 // The combine of the split-KV decode attention for ALL heads of one sequence in one block
@@ -1110,12 +1118,12 @@ decode_combine_feed_kernel(const float *__restrict__ partial, float *__restrict_
                 oo += p[s2 * (d + 2) + 2 + c] * (ms == -INFINITY ? 0.f : expf(ms - mm));
             }
             const float o = oo / ll;
-            out[((size_t)blockIdx.x * n_heads + h) * d + c] = o;
+            if (blockIdx.y == 0) out[((size_t)blockIdx.x * n_heads + h) * d + c] = o;
             attn_row[h * d + c] = o;
         }
     }
     __syncthreads();
-    feed_consumers(feed, blockIdx.x, attn_row, bf16 != 0);
+    feed_consumers(feed, blockIdx.x, attn_row, bf16 != 0, blockIdx.y, gridDim.y);
 }
 
 __global__ void add_kernel(const float *__restrict__ a, const float *__restrict__ b,
@@ -1452,8 +1460,11 @@ qk_status qk_rmsnorm_feed(qk_ctx *ctx, const float *x, const float *residual, co
     const size_t smem = fa.n ? d * sizeof(float) : 0;
     if (smem > 48 * 1024)
         QK_CUDA(cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    QK_PDL(c, rmsnorm_kernel, dim3((unsigned)n_tokens), dim3(kRmsThreads), smem, x, residual, weight, x_out, y,
-           (uint32_t)d, eps, serving_dtype == QK_BF16, fa);
+    // several blocks per token share the table building when x_out is not x itself (every block
+    // re-reads x) and the row fits the kernel's register cache
+    const unsigned parts = (fa.n && x_out != x && d <= (size_t)kRmsThreads * kRmsPerThread) ? kFeedParts : 1;
+    QK_PDL(c, rmsnorm_kernel, dim3((unsigned)n_tokens, parts), dim3(kRmsThreads), smem, x, residual, weight,
+           x_out, y, (uint32_t)d, eps, serving_dtype == QK_BF16, fa);
     QK_LAUNCHED(c);
 }
 
@@ -1519,7 +1530,7 @@ qk_status qk_decode_attention_feed(qk_ctx *ctx, const float *q, const void *cach
                 return qk::fail(QK_ERR_VALUE, "%zu attention outputs do not fit shared memory", n_heads * head_dim);
             QK_CUDA(cudaFuncSetAttribute(decode_combine_feed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem));
-            QK_PDL(c, decode_combine_feed_kernel, dim3((unsigned)batch), dim3(512), smem, (const float *)scratch, out,
+            QK_PDL(c, decode_combine_feed_kernel, dim3((unsigned)batch, kFeedParts), dim3(512), smem, (const float *)scratch, out,
                    (uint32_t)n_heads, (uint32_t)head_dim, (uint32_t)n_splits, serving_dtype == QK_BF16, fa);
         } else {
             QK_PDL(c, decode_combine_kernel, dim3((unsigned)(batch * n_heads)), dim3(128), 0, (const float *)scratch,
@@ -1659,7 +1670,7 @@ qk_status qk_swiglu_feed(qk_ctx *ctx, const float *gate, const float *up, size_t
     if (smem > 200 * 1024)
         return qk::fail(QK_ERR_VALUE, "a row of %zu activations does not fit shared memory", n);
     QK_CUDA(cudaFuncSetAttribute(swiglu_feed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    QK_PDL(c, swiglu_feed_kernel, dim3((unsigned)n_tokens), dim3(512), smem, gate, up, (uint32_t)n,
+    QK_PDL(c, swiglu_feed_kernel, dim3((unsigned)n_tokens, kFeedParts), dim3(512), smem, gate, up, (uint32_t)n,
            serving_dtype == QK_BF16, fa);
     QK_LAUNCHED(c);
 }
@@ -1803,7 +1814,8 @@ qk_status qk_allreduce_rmsnorm_feed(qk_ctx *ctx, const float *partial, const uin
     if (smem > 48 * 1024)
         QK_CUDA(cudaFuncSetAttribute(allreduce_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)smem));
-    QK_PDL(c, allreduce_rmsnorm_kernel, dim3((unsigned)n_tokens), dim3(kRmsThreads), smem,
+    const unsigned parts = (fa.n && x_out != x && d <= (size_t)kRmsThreads * 8) ? kFeedParts : 1;
+    QK_PDL(c, allreduce_rmsnorm_kernel, dim3((unsigned)n_tokens, parts), dim3(kRmsThreads), smem,
         inbox, partial, state_dev, state_dev + 1, rank, world, x, weight, x_out, y, (uint32_t)d, eps,
         serving_dtype == QK_BF16, (int *)c->d_err.ptr, c->wait_limit ? c->wait_limit : (1u << 22), fa);
     c->err_armed = true;

@@ -104,10 +104,14 @@ __device__ __forceinline__ void build_record(const long long (&q8)[8], uint32_t 
 // to `table` (shared or global memory).  entry(k) is element k as float64, zero beyond the
 // vector.  red_max, red_sum: 32 entries of shared memory each; red_bad: one int.  Ends with a
 // __syncthreads(); thread 0 writes *meta_out.
+// Several blocks may share one table: block `part` of `n_parts` scans the whole vector (the
+// scale and the sum need all of it, and scanning is cheap) but assembles and stores only its
+// own share of the records, which is where the work is; part 0 writes the stage record.
 template <typename Entry>
 __device__ __forceinline__ void block_build_table(Entry entry, uint32_t n_steps, uint4 *table,
                                                   StageMeta *meta_out, double *red_max,
-                                                  long long *red_sum, int *red_bad) {
+                                                  long long *red_sum, int *red_bad,
+                                                  uint32_t part = 0, uint32_t n_parts = 1) {
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32, n_warps = (blockDim.x + 31) / 32;
     const uint32_t n_records = n_steps * 64;
     auto record_entry = [&](uint32_t r, int e) -> double {
@@ -135,19 +139,23 @@ __device__ __forceinline__ void block_build_table(Entry entry, uint32_t n_steps,
     const int nonfinite = *red_bad;
     const FixedPoint fp = fixed_point_of(nonfinite ? 0.0 : m);
     long long total = 0;
+    const uint32_t r_lo = (uint32_t)((uint64_t)n_records * part / n_parts);
+    const uint32_t r_hi = (uint32_t)((uint64_t)n_records * (part + 1) / n_parts);
     for (uint32_t r = tid; r < n_records; r += blockDim.x) {
+        const bool mine = r >= r_lo && r < r_hi;
+        if (!mine && part != 0) continue;  // only part 0 needs the sum over everything
         long long q8[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             q8[e] = nonfinite ? 0 : fp.quant(record_entry(r, e));
             total += q8[e];
         }
-        build_record(q8, (r % 64 / 4) % 4, table + (size_t)r * 4);
+        if (mine) build_record(q8, (r % 64 / 4) % 4, table + (size_t)r * 4);
     }
     for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
     if (lane == 0) red_sum[warp] = total;
     __syncthreads();
-    if (tid == 0) {
+    if (tid == 0 && part == 0) {
         long long sum = 0;
         for (uint32_t w = 0; w < n_warps; ++w) sum += red_sum[w];
         meta_out->total = sum;

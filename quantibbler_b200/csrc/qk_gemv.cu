@@ -162,7 +162,8 @@ gemv_signselect_kernel(const StageParams *__restrict__ many, uint32_t n_rows, ui
 // ------------------------------------------------------------------ tensor-core kernel
 constexpr int kTileRows = 16;
 constexpr int kTileBytes = 1024;
-constexpr int kTilesPerWarp = 4;    // row tiles of a group; they share every B fragment
+constexpr int kTilesPerWarp = 4;    // row tiles of a group; they share every B fragment (the tile
+                                    // layout kernels and the chunk size assume four)
 constexpr int kGroupRows = kTileRows * kTilesPerWarp;
 constexpr int kChunkBytes = kTileBytes * kTilesPerWarp;
 constexpr int kStages = 2;          // ring depth per warp (cp.async)
@@ -492,6 +493,46 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
         }
     };
 
+    // The same for two tiles at once: lanes t = 0,1 take the rows of tile m, lanes t = 2,3 those
+    // of tile m + 1, so every lane converts one row and the exchange needs three shuffles of a
+    // 64-bit value per tile instead of four.
+    auto finish_pair = [&](const int (&a)[4], const int (&b2)[4], uint32_t group, int m) {
+        long long pg[2], ph[2];
+        pg[0] = ((long long)a[0] << sh0) + ((long long)a[1] << (sh0 + 8));
+        ph[0] = ((long long)a[2] << sh0) + ((long long)a[3] << (sh0 + 8));
+        pg[1] = ((long long)b2[0] << sh0) + ((long long)b2[1] << (sh0 + 8));
+        ph[1] = ((long long)b2[2] << sh0) + ((long long)b2[3] << (sh0 + 8));
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            pg[k] += __shfl_xor_sync(0xffffffffu, pg[k], 1);  // t=0,1: low half; t=2,3: high half
+            ph[k] += __shfl_xor_sync(0xffffffffu, ph[k], 1);
+        }
+        const bool first = t < 2;
+        const long long other_g = __shfl_xor_sync(0xffffffffu, first ? pg[1] : pg[0], 2);
+        const long long other_h = __shfl_xor_sync(0xffffffffu, first ? ph[1] : ph[0], 2);
+        const long long mine_g = first ? pg[0] : pg[1], mine_h = first ? ph[0] : ph[1];
+        const bool upper = (t & 1) != 0;  // row g (t even) or g + 8 (t odd) of the lane's tile
+        const long long lo = first ? (upper ? mine_h : mine_g) : (upper ? other_h : other_g);
+        const long long hi = first ? (upper ? other_h : other_g) : (upper ? mine_h : mine_g);
+        const uint32_t row = group * kGroupRows + (m + (first ? 0 : 1)) * kTileRows + g + (upper ? 8 : 0);
+        if (row < n_rows) {
+            double val = (double)(hi - th) * 4294967296.0 + (double)(lo - tl);
+            val = odirect ? val * oscale : ldexp(val, oexp);
+            if (meta.nonfinite) val = nan("");
+            if (kRoundBf16) val = (double)round_bf16((float)val);
+            if (kOutSmem) {
+                out_smem[row] = val;
+            } else if (kFinal) {
+                float y = (float)val;
+                if (p.out_scale) y = y * p.out_scale[row];
+                if (p.out_bias) y = y + p.out_bias[row];
+                static_cast<float *>(p.out)[row] = y;
+            } else {
+                static_cast<double *>(p.out)[row] = val;
+            }
+        }
+    };
+
     uint32_t ks = kSplitK ? warp : 0, group = group_begin;
     for (uint32_t i = 0; i < n_items; ++i) {
         issue(i + kStages - 1);          // refills the slot consumed one iteration ago
@@ -526,11 +567,12 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
         }
         if (++ks < n_steps) continue;
         ks = 0;
-        // ---- the group's 64 rows are complete
+        // ---- the group's rows are complete: two tiles at a time (finish_pair)
 #pragma unroll
-        for (int m = 0; m < kTilesPerWarp; ++m) {
-            finish_tile(acc[m], group, m);
+        for (int m = 0; m < kTilesPerWarp; m += 2) {
+            finish_pair(acc[m], acc[m + 1], group, m);
             acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0;
+            acc[m + 1][0] = acc[m + 1][1] = acc[m + 1][2] = acc[m + 1][3] = 0;
         }
         ++group;
     }
@@ -672,6 +714,7 @@ constexpr int kPsBuilders = 3;
 constexpr int kPsBuilderWarp0 = kPsConsumers;
 constexpr int kPsThreads = (kPsConsumers + kPsBuilders) * 32;
 constexpr int kPsDepth = 2;  // ring slots per consumer warp
+constexpr int kPsTilePtrs = 48;  // instances per CTA whose tile addresses are kept in shared memory
 constexpr uint32_t kPsWaitLimitDefault = 1u << 22;
 
 struct PsArgs {
@@ -849,6 +892,9 @@ layer_stream_kernel(const PsArgs a, uint32_t t_bytes, uint32_t table1_bytes, uin
     long long *red_sum = reinterpret_cast<long long *>(red_max + kPsBuilders);
     int *red_bad = reinterpret_cast<int *>(red_sum + kPsBuilders);
     volatile int *abort_flag = red_bad + kPsBuilders;
+    // where the weight tiles of this CTA's instances lie, [stage][instance], so that starting
+    // a copy costs no global load (instances beyond the table are looked up in global memory)
+    __shared__ const uint8_t *tiles_of[2][kPsTilePtrs];
 
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t limit = a.wait_limit;
@@ -861,7 +907,6 @@ layer_stream_kernel(const PsArgs a, uint32_t t_bytes, uint32_t table1_bytes, uin
     sh.steps[1] = (a.r + kStepBits - 1) / kStepBits;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kPsConsumers * kPsDepth; ++s) ps_mbar_init(&full[s], 1);  // the copy's expect_tx
         for (int b = 0; b < 2; ++b) {
             ps_mbar_init(&t1_full[b], kPsBuilders);
             // every consumer warp that owns a row group of stage 1 reports its rows of t
@@ -872,40 +917,45 @@ layer_stream_kernel(const PsArgs a, uint32_t t_bytes, uint32_t table1_bytes, uin
         abort_flag[1] = 0;  // stays zero: the flag of waits that must not be cut short
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    for (uint32_t i = threadIdx.x; i < min(sh.n_mine, (uint32_t)kPsTilePtrs); i += blockDim.x) {
+        const size_t at = blockIdx.x + (size_t)i * gridDim.x;
+        tiles_of[0][i] = a.stage1[at].w_tiles;
+        tiles_of[1][i] = a.stage2[at].w_tiles;
+    }
     __syncthreads();
 
     if (warp < kPsConsumers) {
         // ------------------------------------------------------------ consumers
         const uint32_t g = lane / 4, t = lane % 4;
         uint8_t *my_ring = ring + (size_t)warp * kPsDepth * kChunkBytes;
-        uint64_t *my_full = full + warp * kPsDepth;
         // the chunk a cursor points at: weight bits only, known without any input
-        // `after`: a value whose computation must precede the copy (zero): when a slot is refilled
-        // the shared-memory reads of its old contents must have returned first
-        auto issue = [&](const PsCursor &c, uint32_t slot, uint32_t after) {
-            if (lane == 0) {
-                uint32_t stage, inst;
-                ps_job(sh, c.job, &stage, &inst);
+        // Every lane copies exactly the eight 16-byte pieces of a chunk that it will read itself
+        // (cp.async, one commit group per chunk), so the ring needs no barrier of any kind.
+        auto issue = [&](const PsCursor &c, uint32_t slot) {
+            uint32_t stage, inst;
+            ps_job(sh, c.job, &stage, &inst);
+            const uint8_t *tiles;
+            if (inst < (uint32_t)kPsTilePtrs) {
+                tiles = tiles_of[stage][inst];
+            } else {
                 const size_t at = blockIdx.x + (size_t)inst * gridDim.x;
-                const uint8_t *tiles = stage == 0 ? a.stage1[at].w_tiles : a.stage2[at].w_tiles;
-                const uint8_t *src = tiles + ((size_t)c.group * sh.steps[stage] + c.ks) * kChunkBytes;
-                const uint32_t dst = ps_smem_u32(my_ring + (size_t)slot * kChunkBytes) + after;
-                const uint32_t bar = ps_smem_u32(&my_full[slot]);
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-                             "r"((uint32_t)kChunkBytes)
-                             : "memory");
-                asm volatile(
-                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                    "l"(src), "r"((uint32_t)kChunkBytes), "r"(bar)
-                    : "memory");
+                tiles = stage == 0 ? a.stage1[at].w_tiles : a.stage2[at].w_tiles;
             }
+            const uint4 *from = reinterpret_cast<const uint4 *>(
+                                    tiles + ((size_t)c.group * sh.steps[stage] + c.ks) * kChunkBytes) + lane;
+            uint4 *dst = reinterpret_cast<uint4 *>(my_ring + (size_t)slot * kChunkBytes) + lane;
+#pragma unroll
+            for (int piece = 0; piece < 8; ++piece) cp_async16(dst + piece * 32, from + piece * 32);
         };
         PsCursor fetch{0, 0, 0}, cur{0, 0, 0};
         bool more = ps_seek(sh, warp, &fetch);
         uint32_t n_issued = 0;
-        for (; n_issued < (uint32_t)kPsDepth && more; ++n_issued) {
-            issue(fetch, n_issued, 0u);
-            more = ps_next(sh, warp, &fetch);
+        for (; n_issued < (uint32_t)kPsDepth; ++n_issued) {
+            if (more) {
+                issue(fetch, n_issued);
+                more = ps_next(sh, warp, &fetch);
+            }
+            cp_async_commit();  // (an empty group keeps the group count in step with the chunks)
         }
         qk::pdl_wait();  // from here on: inputs, which come from the kernel before this one
         bool ok = true, have = ps_seek(sh, warp, &cur);
@@ -936,10 +986,7 @@ layer_stream_kernel(const PsArgs a, uint32_t t_bytes, uint32_t table1_bytes, uin
                 for (int m = 0; m < kTilesPerWarp; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0;
             }
             const uint32_t slot = n_done % kPsDepth;
-            if (!ps_wait_warp(&my_full[slot], (n_done / kPsDepth) & 1, abort_flag, limit)) {
-                ok = false;
-                break;
-            }
+            cp_async_wait<kPsDepth - 1>();  // this lane's pieces of the chunk have landed
             const uint4 *stage_ptr = reinterpret_cast<const uint4 *>(my_ring + (size_t)slot * kChunkBytes) + lane;
             uint4 chunk[kTilesPerWarp][2];
 #pragma unroll
@@ -947,14 +994,13 @@ layer_stream_kernel(const PsArgs a, uint32_t t_bytes, uint32_t table1_bytes, uin
                 chunk[m][0] = stage_ptr[m * 64];
                 chunk[m][1] = stage_ptr[m * 64 + 32];
             }
-            // the chunk is in registers: refill its slot with the chunk kPsDepth ahead
-            __syncwarp();
+            // the chunk is in registers: refill its slot with the chunk kPsDepth ahead (a lane
+            // overwrites only pieces it has just read itself)
             if (more) {
-                // (the last read of the slot feeds the copy's address: the copy cannot start
-                // before that read - issued by all lanes in one instruction - has returned)
-                issue(fetch, slot, chunk[kTilesPerWarp - 1][1].w & 0u);
+                issue(fetch, slot);
                 more = ps_next(sh, warp, &fetch);
             }
+            cp_async_commit();
             const uint2 *dk = dig + (size_t)cur.ks * 512;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -1035,15 +1081,8 @@ layer_stream_kernel(const PsArgs a, uint32_t t_bytes, uint32_t table1_bytes, uin
                 if (lane == 0) ps_mbar_arrive(&tt_full[b]);
             }
         }
-        if (!ok) {
-            *abort_flag = 1;
-            // this warp's copies still in flight must land before the CTA gives up its shared
-            // memory: a bounded wait on both slots (a slot with nothing in flight answers at once
-            // for the parity of its last completed phase and runs out of polls for the other)
-            for (uint32_t slot = 0; slot < (uint32_t)kPsDepth; ++slot)
-                for (uint32_t parity = 0; parity < 2; ++parity)
-                    ps_wait_lane(&my_full[slot], parity, abort_flag + 1 /* never set */, 1u << 12);
-        }
+        cp_async_wait<0>();  // nothing of this warp is in flight when the CTA ends
+        if (!ok) *abort_flag = 1;
     } else {
         // ------------------------------------------------------------ builders
         qk::pdl_wait();
@@ -1274,7 +1313,7 @@ bool fused_plan(const qk_ctx *c, const StageShape &s1, const StageShape &s2, siz
 // The persistent streaming form applies when every SM gets at least one instance and the
 // two double-buffered tables, the two t buffers and the consumer warps' rings fit in shared
 // memory together.
-constexpr size_t kPsSmemBudget = 227 * 1024;
+constexpr size_t kPsSmemBudget = 227 * 1024 - 1024;  // (the kernel also holds 768 bytes of static shared memory)
 struct PsPlan {
     size_t grid, slots, t_bytes, table1_bytes, table2_bytes, smem;
 };
@@ -1428,9 +1467,9 @@ qk_status launch_both(qk_ctx *c, const qk_layer *l0, const StageParams *d, size_
         if ((st = launch_signselect(c, d, n_inst, s1, bf16)) != QK_OK) return st;
         return launch_signselect(c, d + n_inst, n_inst, s2, bf16);
     }
-    // Many instances: the persistent streaming form (selectors 2, 4 and 5 keep the one-block-
-    // per-instance form for comparison).
-    if (kernel == 1 || kernel == 3) {
+    // Many instances: one block per instance (below), or - selector 6, a measurement variant
+    // that did not beat it - the persistent streaming form.
+    if (kernel == 6) {
         PsPlan ps;
         if (stream_plan(c, s1, s2, n_inst, &ps)) {
             qk_status e = qk::error_word(c);
@@ -1482,14 +1521,16 @@ qk_status apply_group(qk_ctx *c, const qk_layer *const *layers, size_t n_layers,
     if ((st = c->d_t.reserve(n_inst * sc.total)) != QK_OK) return st;
     if ((st = c->d_ptrs.reserve(2 * n_inst * sizeof(StageParams))) != QK_OK) return st;
     void *hp;
-    if ((st = c->pinned(2 * n_inst * sizeof(StageParams), &hp)) != QK_OK) return st;
-    // the pinned block is reused by the next call: wait for the previous copy out of it
-    QK_CUDA(cudaStreamSynchronize(c->stream));
+    int slot;
+    // (no host-side wait here: the pinned blocks form a ring guarded by events, and the device
+    // buffers below are reused in stream order)
+    if ((st = c->pinned(2 * n_inst * sizeof(StageParams), &hp, &slot)) != QK_OK) return st;
     fill_params((StageParams *)hp, layers, n_layers, n_tokens, x_dev, y_dev, (uint8_t *)c->d_t.ptr,
                 x_layer_stride, y_layer_stride);
     StageParams *d = (StageParams *)c->d_ptrs.ptr;
     QK_CUDA(cudaMemcpyAsync(d, hp, 2 * n_inst * sizeof(StageParams), cudaMemcpyHostToDevice,
                             c->stream));
+    if ((st = c->pinned_done(slot)) != QK_OK) return st;
     return launch_both(c, l0, d, n_inst, c->gemv_kernel);
 }
 

@@ -381,22 +381,33 @@ class LayerGroup:
 
 
 class HostLayerGroup:
-    """Same-shape layers applied to HOST inputs in one step: one upload of all inputs, the
-    group's launches, one download of all outputs.  The per-layer host call
+    """Same-shape layers applied to HOST inputs in one step.  The per-layer host call
     (``PackedLayer.apply``, the shape of the reference's ``PackedLayer::apply``) pays two
     copies, two launches and a synchronisation per layer; a caller that has many independent
-    applies ready (all layers of a step, or one layer for many requests) pays them once.
-    ``x_host`` is ``[n_layers, din]`` and ``y_host`` ``[n_layers, dout]`` float32 torch CPU
-    tensors; pinned memory makes both copies asynchronous DMA."""
+    applies ready (all layers of a step, or one layer for many requests) hands them over
+    together.  The layers are cut into a few sub-groups that run as a pipeline on three
+    streams - inputs up, launch, outputs down - so that the upload of one sub-group, the
+    kernels of the previous one and the download of the one before overlap (the link is full
+    duplex).  ``x_host`` is ``[n_layers, din]`` and ``y_host`` ``[n_layers, dout]`` float32
+    torch CPU tensors; pinned memory makes both copies asynchronous DMA."""
 
-    def __init__(self, ctx: GpuContext, layers):
+    def __init__(self, ctx: GpuContext, layers, n_parts: int | None = None):
         import torch
         self.torch, self.ctx, self.layers = torch, ctx, list(layers)
         first = self.layers[0]
         n = len(self.layers)
         self.x_dev = torch.zeros((n, first.din), dtype=torch.float32, device="cuda")
         self.y_dev = torch.zeros((n, first.dout), dtype=torch.float32, device="cuda")
-        self.group = LayerGroup(ctx, self.layers, self.x_dev.data_ptr(), self.y_dev.data_ptr())
+        # sub-groups of at least ~300 layers keep every launch in its many-instance form
+        if n_parts is None:
+            n_parts = max(1, min(4, n // 296))
+        bounds = [n * i // n_parts for i in range(n_parts + 1)]
+        self.parts = []
+        for lo, hi in zip(bounds[:-1], bounds[1:]):
+            group = LayerGroup(ctx, self.layers[lo:hi], self.x_dev[lo:hi].data_ptr(),
+                               self.y_dev[lo:hi].data_ptr())
+            self.parts.append((lo, hi, group, torch.cuda.Event(), torch.cuda.Event()))
+        self.up, self.down = torch.cuda.Stream(), torch.cuda.Stream()
 
     def apply(self, x_host, y_host) -> None:
         """``y_host[i] = layer_i(x_host[i])`` for every layer; returns when ``y_host`` is valid."""
@@ -406,15 +417,25 @@ class HostLayerGroup:
             raise KernelError(f"host buffers must be {tuple(self.x_dev.shape)} and "
                               f"{tuple(self.y_dev.shape)}, got {tuple(x_host.shape)} and "
                               f"{tuple(y_host.shape)}")
-        stream = torch.cuda.ExternalStream(self.ctx.stream)   # the stream the kernels launch on
-        with torch.cuda.stream(stream):
-            self.x_dev.copy_(x_host, non_blocking=True)
-            self.group.apply()
-            y_host.copy_(self.y_dev, non_blocking=True)
-        stream.synchronize()
+        run = torch.cuda.ExternalStream(self.ctx.stream)   # the stream the kernels launch on
+        self.up.wait_stream(run)       # the previous call's kernels no longer read x_dev
+        self.down.wait_stream(run)
+        for lo, hi, group, uploaded, computed in self.parts:
+            with torch.cuda.stream(self.up):
+                self.x_dev[lo:hi].copy_(x_host[lo:hi], non_blocking=True)
+                uploaded.record(self.up)
+            run.wait_event(uploaded)
+            with torch.cuda.stream(run):
+                group.apply()
+                computed.record(run)
+            self.down.wait_event(computed)
+            with torch.cuda.stream(self.down):
+                y_host[lo:hi].copy_(self.y_dev[lo:hi], non_blocking=True)
+        self.down.synchronize()
 
     def close(self) -> None:
-        self.group.close()
+        for _, _, group, _, _ in self.parts:
+            group.close()
 
 
 class Feed(ctypes.Structure):

@@ -1,7 +1,7 @@
 """Tensor-parallel partitioning of a factorized-linear decoder (host-side, NumPy only).
 
-The reference has no parallelism of any kind; this is the partitioning BASELINE.json's
-north_star prescribes for the path: column-parallel layers (q, k, v, gate, up) split the
+The reference has no parallelism of any kind; this is the partitioning the benchmark
+specification prescribes for the path: column-parallel layers (q, k, v, gate, up) split the
 rows of Ub, s1 and the bias by output feature and replicate Vb^T and s2; row-parallel
 layers (o, down) split the columns of Vb^T and s2 by input feature and replicate Ub and s1,
 so their outputs are partial sums that one all-reduce per attention block and one per MLP

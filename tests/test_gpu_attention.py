@@ -86,7 +86,7 @@ def test_exact_matches_scalar_decode_routine(gpu_ctx):
 
 
 def test_exact_config2_shape_row_sample(gpu_ctx):
-    # BASELINE config 2 shape, full size; the oracle checks a sample of query rows
+    # benchmark configuration 2 shape, full size; the oracle checks a sample of query rows
     rng = np.random.default_rng(2)
     b, h, kvh, s, d = 1, 32, 8, 8192, 128
     q = rng.standard_normal((b, h, s, d), dtype=np.float32)
@@ -207,7 +207,7 @@ def restated_codes(q, k, v, block, ft):
 
 
 def test_sage_at_config2_codes_and_rows(gpu_ctx):
-    """BASELINE config 2 at full size (32 query heads, 8 KV heads, 8192 tokens, head_dim 128,
+    """benchmark configuration 2 at full size (32 query heads, 8 KV heads, 8192 tokens, head_dim 128,
     causal, key block 64).  The INT8 codes and scales the device path computes are read back
     and must equal the float32 restatement of the reference's quantisers bit for bit; against
     the float64 reference a code may differ only where a value sits within a float32 rounding

@@ -55,7 +55,7 @@ def check_layer(ctx, L, serving, expect_bit_identical=True):
     # two chained products: stage-1 error propagates through stage 2
     err = np.abs(y.astype(np.float64) - want.astype(np.float64))
     assert (err / np.maximum(term_scale, 1e-300)).max() <= 2 * tol, serving
-    # the BASELINE bound: max error relative to the largest reference output
+    # the benchmark's bound: max error relative to the largest reference output
     rel = err.max() / np.abs(want).max()
     assert rel <= (2e-3 if serving == "float32" else 2e-2), (serving, rel)
     # run-to-run bit identity

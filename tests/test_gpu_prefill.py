@@ -54,7 +54,7 @@ def test_prefill_matches_reference(gpu_ctx, shape):
 @pytest.mark.parametrize("shape", [(14336, 4096, 2560), (4096, 14336, 2560)],
                          ids=["gate_up", "down"])
 def test_prefill_at_config1(gpu_ctx, shape):
-    """BASELINE config 1 at full size: the Llama-3-8B MLP shapes at rank 2560 on 2048 tokens
+    """benchmark configuration 1 at full size: the Llama-3-8B MLP shapes at rank 2560 on 2048 tokens
     (the case the prefill benchmark times, with tiles split between CTAs); five tokens are
     checked against the oracle's per-token bfloat16 apply."""
     dout, din, r = shape
