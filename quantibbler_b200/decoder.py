@@ -45,7 +45,11 @@ class DecoderConfig:
     gemm_min_batch: int = 16       # bfloat16 serving: batches this large take the tensor-core GEMM
     fused_allreduce: bool = True   # tensor parallel: the all-reduce happens inside the norm, over peer memory
     fused_allreduce_max_bytes: int = 1 << 20   # ... while a rank pushes at most this much per all-reduce
-    feed_max_batch: int = 4        # batches this small: digit tables are built where a vector is produced
+    # Batches up to this size build the digit tables of the linears' inputs where each vector is
+    # produced (fed plans) and read gate/up through the SwiGLU inside the down projection.  Both
+    # measured slower than the plain sequence on the Llama-3-8B shape at batch 1 (5.4 against
+    # 4.8 ms per step), so the default is off.
+    feed_max_batch: int = 0
     prefill_min_tokens: int = 16   # generate(): prompts this long go through the trunk in one pass
     prefill_chunk: int = 2048      # ... in pieces of at most this many positions
 
@@ -210,7 +214,7 @@ class Decoder:
         # enough blocks of 128 threads to fill the SMs (about eight per SM), but chunks of at
         # least ~128 keys
         want = -(-8 * 148 // max(1, B * self.kv_loc))
-        self.n_splits = cfg.n_splits or max(1, min(32, want, max(1, cfg.max_seq // 128)))
+        self.n_splits = cfg.n_splits or max(1, min(32, want, max(1, cfg.max_seq // 64)))
         scratch = _lib.lib().qk_decode_attention_scratch(B, self.h_loc, hd, self.n_splits)
         self.att_scratch = torch.zeros(scratch // 4 + 4, **f32)
         self.cos_sin = dev_f32(rope_table(cfg))
@@ -255,10 +259,13 @@ class Decoder:
                 return [(L[n], rows(src, b), rows(dst, b)) for b in range(B)
                         for n, dst in zip(names, dsts)]
 
-            # down reads SwiGLU(gate, up) directly: no separate activation pass
-            plan = {"o": LayerPlan(ctx, inst(["o"], self.attn, [self.delta_attn])),
-                    "down": LayerPlan(ctx, [(L["down"], rows(self.g, b), rows(self.u, b),
-                                             rows(self.delta_mlp, b)) for b in range(B)], gated=True)}
+            fed = cfg.serving in ("float32", "bfloat16") and B <= cfg.feed_max_batch
+            plan = {"o": LayerPlan(ctx, inst(["o"], self.attn, [self.delta_attn]))}
+            if fed:   # down reads SwiGLU(gate, up) directly: no separate activation pass
+                plan["down"] = LayerPlan(ctx, [(L["down"], rows(self.g, b), rows(self.u, b),
+                                                rows(self.delta_mlp, b)) for b in range(B)], gated=True)
+            else:
+                plan["down"] = LayerPlan(ctx, inst(["down"], self.a, [self.delta_mlp]))
             same_kv = all(getattr(L["k"], f) == getattr(L["v"], f) for f in ("dout", "din", "r"))
             try:
                 # q, k and v in one pair of launches although q differs in shape: possible
@@ -413,12 +420,11 @@ class Decoder:
             self._norm(0, post_w, feeds["gu"] if feeds else None, xa, xb)
             xa, xb = xb, xa
             self._linears(li, ["gate", "up"], self.h, [self.g, self.u])
-            if feeds:
+            if feeds:   # (the fed down plan needs no activation vector, only its digit table)
                 check(lib.qk_swiglu_feed(c, _p(self.g), _p(self.u), B, self.ff_loc, self.serving_tag,
                                          ctypes.byref(feeds["down"])))
-            elif self.use_gemm:
+            else:
                 check(lib.qk_swiglu(c, _p(self.g), _p(self.u), B * self.ff_loc, _p(self.a)))
-            # (the GEMV path's down plan applies the SwiGLU to gate and up as it reads them)
             self._linears(li, ["down"], self.a, [self.delta_mlp])
             self._all_reduce(self.delta_mlp)
             pending = 1

@@ -354,3 +354,35 @@ def test_generate_uses_the_batched_prefill_for_long_prompts(gpu_ctx):
     assert got["completion_tokens"] == want and got["finish"] == finish
     with pytest.raises(ValueError, match="does not fit the KV cache"):
         dec.prefill([1] * 200)
+
+
+@pytest.mark.parametrize("serving", ["float32", "bfloat16"])
+def test_fed_plans_reproduce_the_plain_step(gpu_ctx, serving):
+    """With fed plans the digit tables of the linears' inputs are written by the kernels that
+    produce those inputs (norm, attention combine, SwiGLU; several blocks per token share the
+    work) and stage 1 hands over to stage 2 through its last block.  The tables are the same
+    numbers and the accumulation is exact, so logits and tokens must be the plain step's bits."""
+    kv = "float32" if serving == "float32" else "bfloat16"
+    weights = random_model(tiny_cfg(serving=serving, kv_dtype=kv), RANKS, seed=31)
+    plain = Decoder(gpu_ctx, tiny_cfg(serving=serving, kv_dtype=kv), weights)
+    fed = Decoder(gpu_ctx, tiny_cfg(serving=serving, kv_dtype=kv, feed_max_batch=4), weights)
+    assert fed.fed and not plain.fed
+    first = [9, 41, 100]
+    for dec in (plain, fed):
+        dec.start(first, [0, 0, 0])
+    for _ in range(5):
+        for dec in (plain, fed):
+            dec.step()
+        gpu_ctx.synchronize()
+        a, b = fed.logits.cpu().numpy(), plain.logits.cpu().numpy()
+        # the SwiGLU is evaluated by two kernels (fed: inside the feeding kernel): same
+        # float32 expression, so the same bits
+        assert np.array_equal(a, b)
+        for dec in (plain, fed):
+            dec.advance()
+    graph = Decoder(gpu_ctx, tiny_cfg(serving=serving, kv_dtype=kv, feed_max_batch=4), weights)
+    graph.capture()
+    graph.start(first, [0, 0, 0])
+    eager = Decoder(gpu_ctx, tiny_cfg(serving=serving, kv_dtype=kv), weights)
+    eager.start(first, [0, 0, 0])
+    assert np.array_equal(graph.decode(6), eager.decode(6))
