@@ -198,8 +198,19 @@ C4_RANKS = {"q": 1102, "o": 1102, "k": 431, "v": 431, "gate": 1724, "up": 1724, 
 C3_RANKS = {"q": 1102, "k": 1102, "v": 1102, "o": 1102, "gate": 1614, "up": 1614, "down": 1622}
 
 
+DIRECT_MAX_BATCH = None   # --direct-max-batch: override of DecoderConfig.direct_max_batch
+
+
 def decode_config(model: str, n_layers: int, batch: int, max_seq: int, allreduce: str):
     """DecoderConfig + ranks of the benchmark's configuration 4 ("llama3-8b") or config 3."""
+    import dataclasses
+    cfg, ranks = _decode_config(model, n_layers, batch, max_seq, allreduce)
+    if DIRECT_MAX_BATCH is not None:
+        cfg = dataclasses.replace(cfg, direct_max_batch=DIRECT_MAX_BATCH)
+    return cfg, ranks
+
+
+def _decode_config(model: str, n_layers: int, batch: int, max_seq: int, allreduce: str):
     from quantibbler_b200.decoder import DecoderConfig
     if model == "llama3-8b":
         return DecoderConfig(n_layers=n_layers or 32, d_model=4096, n_heads=32, n_kv_heads=8,
@@ -587,6 +598,8 @@ def main() -> None:
     ap.add_argument("--n-layers", type=int, default=0)
     ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
                     help="decode workload under tensor parallelism")
+    ap.add_argument("--direct-max-batch", type=int, default=-1,
+                    help="decode: batches up to this size use the table-free direct GEMV (-1: the decoder's default)")
     ap.add_argument("--tp-decode", type=int, default=1,
                     help="append the config-4 tensor-parallel decode block to the default line")
     ap.add_argument("--tp-steps", type=int, default=20, help="timed decode steps of that block")
@@ -597,6 +610,9 @@ def main() -> None:
                     help="compare sampled outputs of the timed launch with the CPU oracle")
     args = ap.parse_args()
 
+    global DIRECT_MAX_BATCH
+    if args.direct_max_batch >= 0:
+        DIRECT_MAX_BATCH = args.direct_max_batch
     if args.shape:
         global DOUT, DIN, RANK, BYTES_PER_APPLY
         DOUT, DIN, RANK = (int(v) for v in args.shape.split(","))

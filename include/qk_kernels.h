@@ -288,6 +288,18 @@ qk_status qk_plan_create_gated(qk_ctx *ctx, const qk_layer *const *layers,
                                float *const *y_ptrs, size_t n_inst, qk_group **out);
 qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group);
 void qk_group_free(qk_group *group);
+/* ---- direct plans (single-token decode) -----------------------------------------
+ * Switches a small plan to the table-free form: the weight bits become bfloat16 +-1 MMA
+ * operands in registers and the vector rides as bfloat16 terms (one under bfloat16 serving - the
+ * operands and float32 accumulation of apply_bf16, engine/mod.rs:449-460 - and a three-term
+ * split that reproduces float32 under float32 serving), accumulated in float32 in a fixed
+ * order.  Each block then does nothing before it multiplies but copy the vector, which is
+ * what bounds a one-token step.  The result is the reference's float32 arithmetic class
+ * (within 1e-6 * sum|terms| of the exact sum, tests/parity.rs:795), not the bit-sliced form's
+ * exact integer sum, so it is opt-in per plan; qk_layer_apply and the group calls never use it.
+ * Plans too large for the few-instance kernel form, and fed plans, are refused with
+ * QK_ERR_VALUE. */
+qk_status qk_plan_use_direct(qk_ctx *ctx, qk_group *plan);
 /* ---- fed plans ------------------------------------------------------------------
  * At a small batch the cost of a GEMV launch is not its weight bits but what every one of
  * its blocks does first: scan the input vector, put it on a fixed-point grid, build the

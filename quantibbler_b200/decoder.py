@@ -50,6 +50,9 @@ class DecoderConfig:
     # measured slower than the plain sequence on the Llama-3-8B shape at batch 1 (5.4 against
     # 4.8 ms per step), so the default is off.
     feed_max_batch: int = 0
+    # Batches up to this size run their linears in the table-free direct form (LayerPlan.use_direct):
+    # float32 accumulation like the reference's own GEMV instead of the exact integer sum.
+    direct_max_batch: int = 0
     prefill_min_tokens: int = 16   # generate(): prompts this long go through the trunk in one pass
     prefill_chunk: int = 2048      # ... in pieces of at most this many positions
 
@@ -285,6 +288,9 @@ class Decoder:
             else:
                 plan["gate"] = LayerPlan(ctx, inst(["gate"], self.h, [self.g]))
                 plan["up"] = LayerPlan(ctx, inst(["up"], self.h, [self.u]))
+            if not fed and B <= cfg.direct_max_batch:
+                for pl in plan.values():
+                    pl.use_direct()
             self.plans.append(plan)
         # a large enough batch is a real contraction: the tcgen05 GEMM expands each weight bit
         # once for all tokens, the GEMV forms would do it once per token
