@@ -199,6 +199,7 @@ C3_RANKS = {"q": 1102, "k": 1102, "v": 1102, "o": 1102, "gate": 1614, "up": 1614
 
 
 DIRECT_MAX_BATCH = None   # --direct-max-batch: override of DecoderConfig.direct_max_batch
+FUSED_STEP_MAX_BATCH = None   # --fused-step-max-batch: override of DecoderConfig.fused_step_max_batch
 
 
 def decode_config(model: str, n_layers: int, batch: int, max_seq: int, allreduce: str):
@@ -207,6 +208,8 @@ def decode_config(model: str, n_layers: int, batch: int, max_seq: int, allreduce
     cfg, ranks = _decode_config(model, n_layers, batch, max_seq, allreduce)
     if DIRECT_MAX_BATCH is not None:
         cfg = dataclasses.replace(cfg, direct_max_batch=DIRECT_MAX_BATCH)
+    if FUSED_STEP_MAX_BATCH is not None:
+        cfg = dataclasses.replace(cfg, fused_step_max_batch=FUSED_STEP_MAX_BATCH)
     return cfg, ranks
 
 
@@ -600,6 +603,8 @@ def main() -> None:
                     help="decode workload under tensor parallelism")
     ap.add_argument("--direct-max-batch", type=int, default=-1,
                     help="decode: batches up to this size use the table-free direct GEMV (-1: the decoder's default)")
+    ap.add_argument("--fused-step-max-batch", type=int, default=-1,
+                    help="decode: batches up to this size run the blocks of a step as one kernel (-1: the decoder's default)")
     ap.add_argument("--tp-decode", type=int, default=1,
                     help="append the config-4 tensor-parallel decode block to the default line")
     ap.add_argument("--tp-steps", type=int, default=20, help="timed decode steps of that block")
@@ -610,9 +615,11 @@ def main() -> None:
                     help="compare sampled outputs of the timed launch with the CPU oracle")
     args = ap.parse_args()
 
-    global DIRECT_MAX_BATCH
+    global DIRECT_MAX_BATCH, FUSED_STEP_MAX_BATCH
     if args.direct_max_batch >= 0:
         DIRECT_MAX_BATCH = args.direct_max_batch
+    if args.fused_step_max_batch >= 0:
+        FUSED_STEP_MAX_BATCH = args.fused_step_max_batch
     if args.shape:
         global DOUT, DIN, RANK, BYTES_PER_APPLY
         DOUT, DIN, RANK = (int(v) for v in args.shape.split(","))

@@ -300,6 +300,48 @@ void qk_group_free(qk_group *group);
  * Plans too large for the few-instance kernel form, and fed plans, are refused with
  * QK_ERR_VALUE. */
 qk_status qk_plan_use_direct(qk_ctx *ctx, qk_group *plan);
+/* ---- the blocks of a decode step as one kernel ---------------------------------------
+ * transformer_forward (engine/mod.rs:878-945) runs, per block, norm -> q/k/v -> RoPE + cache
+ * append -> attention -> o -> norm -> gate/up -> SwiGLU -> down.  As separate launches that is
+ * about fourteen dependent kernels per block, each as long as its chain of memory round trips;
+ * qk_decode_step_run does ALL blocks of a step in one cooperative kernel (one CTA per SM, a
+ * bounded grid barrier between phases, the small operations folded into the phases that
+ * consume them, every block prefetching its next weight tiles before it waits).  The linears
+ * run in the direct form of qk_plan_use_direct, so a step equals, bit for bit, the same step
+ * made of qk_rmsnorm / direct plans / qk_rope_cache / qk_decode_attention / qk_swiglu calls.
+ * Limits: head_dim 128, bfloat16 cache, at most 8 tokens under bfloat16 serving and 2 under
+ * float32 serving, no per-head q/k norms; anything else is refused with QK_ERR_VALUE and the
+ * caller keeps the separate launches.
+ * Buffers (all float32 unless said, token-major): x holds the embedded tokens on entry and
+ * the residual stream before the last block's down output on exit (delta_mlp holds that
+ * output: the caller's final norm adds it); x2 is the stream's second buffer; q/k/v/attn/
+ * gate/up are [tokens][width] work buffers; att_scratch is qk_decode_attention_scratch bytes;
+ * cos_sin is [s_max][64][2]; positions, seq_index, kv_len as for qk_rope_cache and
+ * qk_decode_attention.  A token outside the cache is skipped and reported like there.
+ * A grid barrier that does not complete within the context's wait limit sets the error word
+ * (QK_ERR_TIMEOUT from the next qk_gpu_synchronize); the kernel still runs to its end. */
+typedef struct qk_step_block {
+    const qk_layer *q, *k, *v, *o, *gate, *up, *down;
+    const float *input_norm, *post_norm; /* d_model weights each */
+    void *cache_k, *cache_v;             /* bfloat16 [n_seq][n_kv_heads][s_max][128] */
+} qk_step_block;
+typedef struct qk_step_buffers {
+    float *x, *x2, *q, *k, *v, *attn, *delta_attn, *delta_mlp, *gate, *up, *att_scratch;
+    const float *cos_sin;
+    const int32_t *positions, *seq_index, *kv_len;
+} qk_step_buffers;
+typedef struct qk_step_desc {
+    size_t n_blocks, n_tokens, d_model, n_heads, n_kv_heads, head_dim, d_ff, s_max, n_seq, n_splits;
+    float rms_eps;
+    int32_t serving_dtype, kv_dtype;
+    const qk_step_block *blocks;
+    qk_step_buffers buf;
+} qk_step_desc;
+typedef struct qk_decode_step qk_decode_step;
+qk_status qk_decode_step_create(qk_ctx *ctx, const qk_step_desc *desc, qk_decode_step **out);
+qk_status qk_decode_step_run(qk_ctx *ctx, const qk_decode_step *step);
+void qk_decode_step_free(qk_decode_step *step);
+
 /* ---- fed plans ------------------------------------------------------------------
  * At a small batch the cost of a GEMV launch is not its weight bits but what every one of
  * its blocks does first: scan the input vector, put it on a fixed-point grid, build the

@@ -146,6 +146,7 @@ cudaError_t launch_pdl(bool allow_overlap, void (*kernel)(KArgs...), dim3 grid, 
 // device 0 (created on first use) when `ctx` is null.
 qk_status resolve_ctx(qk_ctx *ctx, qk_ctx **out);
 // Makes sure the context's error word (an int, bits: 1 a prefill pipeline wait, 2 an all-reduce
-// inbox wait, 4 a token outside the KV cache, 8 a wait of the streaming GEMV) and the prefill's CTA flags after it exist.
+// inbox wait, 4 a token outside the KV cache, 8 a wait of the streaming GEMV, 16 a grid barrier of the
+// whole-step decode kernel) and the prefill's CTA flags after it exist.
 qk_status error_word(qk_ctx *c);
 }  // namespace qk

@@ -192,11 +192,12 @@ qk_status qk_gpu_synchronize(qk_ctx *ctx) {
                 return qk::fail(QK_ERR_VALUE,
                                 "a token's position or sequence index lies outside the KV cache; "
                                 "the token was skipped");
-            return qk::fail(QK_ERR_TIMEOUT, "a bounded device-side wait gave up:%s%s%s",
+            return qk::fail(QK_ERR_TIMEOUT, "a bounded device-side wait gave up:%s%s%s%s",
                             (h_err & 1) ? " a pipeline barrier of the tensor-core prefill;" : "",
                             (h_err & 2) ? " the inbox of a fused all-reduce (a peer did not send);"
                                         : "",
-                            (h_err & 8) ? " a ring or table barrier of the streaming GEMV;" : "");
+                            (h_err & 8) ? " a ring or table barrier of the streaming GEMV;" : "",
+                            (h_err & 16) ? " a grid barrier of the whole-step decode kernel;" : "");
         }
     }
     return QK_OK;

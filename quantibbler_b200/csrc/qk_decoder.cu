@@ -20,48 +20,10 @@
 
 #include "qk_common.h"
 #include "qk_digits.cuh"
+#include "qk_decoder_dev.cuh"
 
 namespace {
 
-__device__ __forceinline__ float round_bf16f(float v) {
-    uint32_t u = __float_as_uint(v);
-    if ((u & 0x7fffffffu) > 0x7f800000u) return __uint_as_float((u | 0x00400000u) & 0xffff0000u);
-    u = (u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u;
-    return __uint_as_float(u);
-}
-__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) {
-    return __uint_as_float((uint32_t)b << 16);
-}
-__device__ __forceinline__ uint16_t float_to_bf16_bits(float v) {
-    return (uint16_t)(__float_as_uint(round_bf16f(v)) >> 16);
-}
-
-template <typename T> __device__ __forceinline__ float load_as_float(const T *p, size_t i);
-template <> __device__ __forceinline__ float load_as_float<float>(const float *p, size_t i) {
-    return p[i];
-}
-template <> __device__ __forceinline__ float load_as_float<uint16_t>(const uint16_t *p, size_t i) {
-    return bf16_bits_to_float(p[i]);
-}
-template <typename T> __device__ __forceinline__ void store_from_float(T *p, size_t i, float v);
-template <> __device__ __forceinline__ void store_from_float<float>(float *p, size_t i, float v) {
-    p[i] = v;
-}
-template <> __device__ __forceinline__ void store_from_float<uint16_t>(uint16_t *p, size_t i,
-                                                                       float v) {
-    p[i] = float_to_bf16_bits(v);
-}
-
-__device__ __forceinline__ float block_sum(float v, float *red) {
-    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, nw = blockDim.x / 32;
-    if (lane == 0) red[warp] = v;
-    __syncthreads();
-    float total = 0.f;
-    for (int w = 0; w < nw; ++w) total += red[w];
-    __syncthreads();
-    return total;
-}
 
 // Feeding the linears that consume a vector: the kernel that has the whole vector of a token
 // in front of it (norm, SwiGLU, attention combine) also writes the digit tables its consumers'
@@ -338,8 +300,8 @@ rope_cache_kernel(float *__restrict__ q, const float *__restrict__ k, const floa
         uint32_t h = idx / half, i = idx % half;
         float c = cs[2 * i], s = cs[2 * i + 1];
         float a = qt[h * d + i], b = qt[h * d + half + i];
-        qt[h * d + i] = a * c - b * s;
-        qt[h * d + half + i] = b * c + a * s;
+        qt[h * d + i] = rope_first(a, b, c, s);
+        qt[h * d + half + i] = rope_second(a, b, c, s);
     }
     const float *kt = k + (size_t)tok * n_kv * d, *vt = v + (size_t)tok * n_kv * d;
     for (uint32_t idx = threadIdx.x; idx < n_kv * half; idx += blockDim.x) {
@@ -347,8 +309,8 @@ rope_cache_kernel(float *__restrict__ q, const float *__restrict__ k, const floa
         float c = cs[2 * i], s = cs[2 * i + 1];
         float a = kt[h * d + i], b = kt[h * d + half + i];
         size_t row = (((size_t)seq * n_kv + h) * s_max + pos) * d;
-        store_from_float<KV>(cache_k, row + i, a * c - b * s);
-        store_from_float<KV>(cache_k, row + half + i, b * c + a * s);
+        store_from_float<KV>(cache_k, row + i, rope_first(a, b, c, s));
+        store_from_float<KV>(cache_k, row + half + i, rope_second(a, b, c, s));
         store_from_float<KV>(cache_v, row + i, vt[h * d + i]);
         store_from_float<KV>(cache_v, row + half + i, vt[h * d + half + i]);
     }
@@ -530,27 +492,6 @@ decode_attention_kernel(const float *__restrict__ q, const KV *__restrict__ cach
 //       64 h + 8 (column) + tile (tile = 0..7 within half h).
 // Partials {m, l, o[128]} per (sequence, head, split) as in decode_attention_kernel, so the
 // same combine kernel finishes.
-__device__ __forceinline__ void mma_bf16_top(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0,
-                                             uint32_t b1) {
-    // rows 8..15 of A are zero
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
-}
-
-// x = hi + mid + lo with each term a bfloat16 (to 2^-25 of x)
-__device__ __forceinline__ void split3(float x, uint32_t &hi, uint32_t &mid, uint32_t &lo) {
-    hi = float_to_bf16_bits(x);
-    const float r1 = x - bf16_bits_to_float((uint16_t)hi);
-    mid = float_to_bf16_bits(r1);
-    lo = float_to_bf16_bits(r1 - bf16_bits_to_float((uint16_t)mid));
-}
-
-constexpr int kMmaDecWarps = 4;
-constexpr int kMmaDecKPitch = 320, kMmaDecVPitch = 272;  // bytes per staged key row (256 + pad)
-constexpr int kMmaDecBufBytes = 16 * (kMmaDecKPitch + kMmaDecVPitch);
 
 __global__ void __launch_bounds__(kMmaDecWarps * 32)
 decode_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict__ cache_k,
@@ -559,195 +500,12 @@ decode_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__restr
                             uint32_t gq, uint32_t s_max, uint32_t chunk, uint32_t n_splits) {
     qk::pdl_launch();  // the next kernel may begin its prologue
     qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
-    constexpr uint32_t d = 128;
-    const uint32_t group = n_heads / n_kv, subs = (group + gq - 1) / gq;
-    const uint32_t split = blockIdx.x, kvh = blockIdx.y / subs, hsub = blockIdx.y % subs;
-    const uint32_t b = blockIdx.z, h0 = kvh * group + hsub * gq;
-    const uint32_t rows = min(gq, group - hsub * gq);  // query heads of this block
-    const int len = min(max(kv_len[b], 0), (int)s_max);  // never past the cache's rows
-    const int j_begin = split * chunk, j_end = min(len, (int)((split + 1) * chunk));
-    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
-    const float scale = 1.0f / sqrtf((float)d);
-
-    // A fragments of q: MMA m (0..7) contracts channels 32 (m/2) + 8 t + 4 (m%2) + {0,1 | 2,3}
-    uint32_t qa[3][8][2];
-    {
-        const float *qr = q + ((size_t)b * n_heads + h0 + min(g, rows - 1)) * d;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float4 lo4 = *reinterpret_cast<const float4 *>(qr + 32 * i + 8 * t);
-            const float4 hi4 = *reinterpret_cast<const float4 *>(qr + 32 * i + 8 * t + 4);
-            const float v[8] = {lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
-#pragma unroll
-            for (int half = 0; half < 2; ++half)
-#pragma unroll
-                for (int pr = 0; pr < 2; ++pr) {
-                    uint32_t e0[3], e1[3];
-                    const float x0 = g < rows ? v[4 * half + 2 * pr] * scale : 0.f;
-                    const float x1 = g < rows ? v[4 * half + 2 * pr + 1] * scale : 0.f;
-                    split3(x0, e0[0], e0[1], e0[2]);
-                    split3(x1, e1[0], e1[1], e1[2]);
-#pragma unroll
-                    for (int term = 0; term < 3; ++term) qa[term][2 * i + half][pr] = e0[term] | (e1[term] << 16);
-                }
-        }
-    }
-    float o[16][2];
-#pragma unroll
-    for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = 0.f;
-    float m = -INFINITY, l = 0.f;  // row g; l is this lane's share (its own key columns)
-
-    const uint16_t *kb = cache_k + ((size_t)b * n_kv + kvh) * s_max * d;
-    const uint16_t *vb = cache_v + ((size_t)b * n_kv + kvh) * s_max * d;
-    // Each warp streams its 16-key steps through two private shared-memory buffers with
-    // cp.async, so the next step's 8 KB of K and V are in flight while this one is multiplied.
-    // Row pitches 320 B (K) and 272 B (V) keep the 16-byte fragment reads conflict-free.
     extern __shared__ __align__(16) uint8_t dec_smem[];
-    uint8_t *my_smem = dec_smem + warp * (2 * kMmaDecBufBytes);
-    auto fetch = [&](int j, int buf) {
-        uint8_t *kt = my_smem + buf * kMmaDecBufBytes, *vt = kt + 16 * kMmaDecKPitch;
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            const int idx = (int)lane + 32 * q, key = idx / 16, piece = idx % 16;
-            const int src_key = min(j + key, j_end - 1);      // a valid address even when unused
-            const uint32_t bytes = j + key < j_end ? 16u : 0u;  // 0: the 16 bytes are zero-filled
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
-                             (uint32_t)__cvta_generic_to_shared(kt + key * kMmaDecKPitch + piece * 16)),
-                         "l"(kb + (size_t)src_key * d + piece * 8), "r"(bytes)
-                         : "memory");
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
-                             (uint32_t)__cvta_generic_to_shared(vt + key * kMmaDecVPitch + piece * 16)),
-                         "l"(vb + (size_t)src_key * d + piece * 8), "r"(bytes)
-                         : "memory");
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    int buf = 0;
-    if (j_begin + 16 * (int)warp < j_end) fetch(j_begin + 16 * (int)warp, 0);
-    for (int j = j_begin + 16 * (int)warp; j < j_end; j += 16 * kMmaDecWarps, buf ^= 1) {
-        if (j + 16 * kMmaDecWarps < j_end) {
-            fetch(j + 16 * kMmaDecWarps, buf ^ 1);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
-        __syncwarp();  // every lane's pieces of this step have landed
-        const uint8_t *kt = my_smem + buf * kMmaDecBufBytes, *vt = kt + 16 * kMmaDecKPitch;
-        // ---- S for 16 keys: two 8-key tiles
-        float s[2][4];
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            uint4 kw[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-                kw[i] = *reinterpret_cast<const uint4 *>(kt + (8 * nt + g) * kMmaDecKPitch + 64 * i + 16 * t);
-            s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int term = 0; term < 3; ++term) {
-                    mma_bf16_top(s[nt], qa[term][2 * i][0], qa[term][2 * i][1], kw[i].x, kw[i].y);
-                    mma_bf16_top(s[nt], qa[term][2 * i + 1][0], qa[term][2 * i + 1][1], kw[i].z, kw[i].w);
-                }
-        }
-        // ---- online softmax over the 16 keys (row g holds columns 2t, 2t+1 of each tile)
-        float mx = -INFINITY;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                if (j + 8 * nt + 2 * (int)t + e >= j_end) s[nt][e] = -INFINITY;
-                mx = fmaxf(mx, s[nt][e]);
-            }
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m, mx);  // finite: the step has at least one valid key
-        const float alpha = expf(m - m_new);
-        float p[2][2];
-        float psum = 0.f;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                p[nt][e] = expf(s[nt][e] - m_new);
-                psum += p[nt][e];
-            }
-        l = l * alpha + psum;
-        m = m_new;
-        uint32_t pa[3][2];
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            uint32_t e0[3], e1[3];
-            split3(p[nt][0], e0[0], e0[1], e0[2]);
-            split3(p[nt][1], e1[0], e1[1], e1[2]);
-#pragma unroll
-            for (int term = 0; term < 3; ++term) pa[term][nt] = e0[term] | (e1[term] << 16);
-        }
-#pragma unroll
-        for (int nt = 0; nt < 16; ++nt) {
-            o[nt][0] *= alpha;
-            o[nt][1] *= alpha;
-        }
-        // ---- O += P V: keys 2t, 2t+1 (first k half) and 8+2t, 8+2t+1 (second)
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            uint4 vw[4];
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                const int key = 8 * (r >> 1) + 2 * (int)t + (r & 1);  // within the step; rows past the end are zero
-                vw[r] = *reinterpret_cast<const uint4 *>(vt + key * kMmaDecVPitch + 128 * h + 16 * g);
-            }
-#pragma unroll
-            for (int jj = 0; jj < 8; ++jj) {
-                const uint32_t w0 = jj / 2 == 0 ? vw[0].x : jj / 2 == 1 ? vw[0].y : jj / 2 == 2 ? vw[0].z : vw[0].w;
-                const uint32_t w1 = jj / 2 == 0 ? vw[1].x : jj / 2 == 1 ? vw[1].y : jj / 2 == 2 ? vw[1].z : vw[1].w;
-                const uint32_t w2 = jj / 2 == 0 ? vw[2].x : jj / 2 == 1 ? vw[2].y : jj / 2 == 2 ? vw[2].z : vw[2].w;
-                const uint32_t w3 = jj / 2 == 0 ? vw[3].x : jj / 2 == 1 ? vw[3].y : jj / 2 == 2 ? vw[3].z : vw[3].w;
-                const uint32_t sel = jj % 2 ? 0x7632u : 0x5410u;
-                const uint32_t b0 = __byte_perm(w0, w1, sel), b1 = __byte_perm(w2, w3, sel);
-                float acc[4] = {o[8 * h + jj][0], o[8 * h + jj][1], 0.f, 0.f};
-#pragma unroll
-                for (int term = 0; term < 3; ++term) mma_bf16_top(acc, pa[term][0], pa[term][1], b0, b1);
-                o[8 * h + jj][0] = acc[0];
-                o[8 * h + jj][1] = acc[1];
-            }
-        }
-        __syncwarp();  // the buffer may be refilled by the next iteration's fetch
-    }
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-
-    // ---- combine the warps of the block
-    __shared__ float sm_m[kMmaDecWarps][8], sm_l[kMmaDecWarps][8];
-    __shared__ float sm_o[kMmaDecWarps][8][d];
-    if (t == 0) {
-        sm_m[warp][g] = m;
-        sm_l[warp][g] = l;
-    }
-#pragma unroll
-    for (int nt = 0; nt < 16; ++nt)
-#pragma unroll
-        for (int e = 0; e < 2; ++e)
-            sm_o[warp][g][64 * (nt / 8) + 8 * (2 * t + e) + nt % 8] = o[nt][e];
-    __syncthreads();
-    for (uint32_t idx = threadIdx.x; idx < rows * d; idx += blockDim.x) {
-        const uint32_t r = idx / d, c = idx % d;
-        float mm = -INFINITY;
-        for (int w = 0; w < kMmaDecWarps; ++w) mm = fmaxf(mm, sm_m[w][r]);
-        float ll = 0.f, oo = 0.f;
-        for (int w = 0; w < kMmaDecWarps; ++w) {
-            const float wt = sm_m[w][r] == -INFINITY ? 0.f : expf(sm_m[w][r] - mm);
-            ll += sm_l[w][r] * wt;
-            oo += sm_o[w][r][c] * wt;
-        }
-        float *out = partial + (((size_t)b * n_heads + h0 + r) * n_splits + split) * (d + 2);
-        out[2 + c] = oo;
-        if (c == 0) {
-            out[0] = mm;
-            out[1] = ll;
-        }
-    }
+    decode_attention_mma_body<false>(SubBlock{threadIdx.x, 0}, carve_dec_attn(dec_smem), q, cache_k, cache_v,
+                                     kv_len[blockIdx.z], partial, n_heads, n_kv, gq, s_max, chunk, n_splits,
+                                     blockIdx.x, blockIdx.y, blockIdx.z, FreshKey{});
 }
+
 
 // ------------------------------------------------------------------ prefill attention, tensor cores
 // Causal attention of T new positions of ONE sequence against the cache (which already holds
@@ -1038,29 +796,10 @@ decode_combine_kernel(const float *__restrict__ partial, float *__restrict__ out
     qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     __shared__ float wgt[128];  // exp(m_s - m) / l per split (n_splits <= 128)
     __shared__ float red[4];
-    const float *p = partial + (size_t)blockIdx.x * n_splits * (d + 2);
-    const uint32_t tid = threadIdx.x;
-    float ms = tid < n_splits ? p[tid * (d + 2)] : -INFINITY;
-    float ls = tid < n_splits ? p[tid * (d + 2) + 1] : 0.f;
-    float mm = ms;
-    for (int off = 16; off > 0; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
-    if (tid % 32 == 0) red[tid / 32] = mm;
-    __syncthreads();
-    mm = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-    __syncthreads();
-    const float w = ms == -INFINITY ? 0.f : expf(ms - mm);
-    float ll = ls * w;
-    for (int off = 16; off > 0; off >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, off);
-    if (tid % 32 == 0) red[tid / 32] = ll;
-    wgt[tid] = w;
-    __syncthreads();
-    ll = red[0] + red[1] + red[2] + red[3];
-    for (uint32_t c = tid; c < d; c += blockDim.x) {
-        float oo = 0.f;
-        for (uint32_t s = 0; s < n_splits; ++s) oo += p[s * (d + 2) + 2 + c] * wgt[s];
-        out[(size_t)blockIdx.x * d + c] = oo / ll;
-    }
+    decode_combine_body(SubBlock{threadIdx.x, 0}, wgt, red, partial + (size_t)blockIdx.x * n_splits * (d + 2),
+                        out + (size_t)blockIdx.x * d, d, n_splits);
 }
+
 
 __global__ void swiglu_kernel(const float *__restrict__ g, const float *__restrict__ u,
                               float *__restrict__ out, size_t n) {
@@ -1558,7 +1297,7 @@ qk_status qk_decode_attention_feed(qk_ctx *ctx, const float *q, const void *cach
         const size_t gq8 = group < 8 ? group : 8, subs = qk::ceil_div(group, gq8);
         const size_t chunk8 = qk::ceil_div(s_max, n_splits);
         dim3 grid8((unsigned)n_splits, (unsigned)(n_kv_heads * subs), (unsigned)batch);
-        const size_t smem8 = (size_t)kMmaDecWarps * 2 * kMmaDecBufBytes;
+        const size_t smem8 = kMmaDecSmemBytes;
         QK_CUDA(cudaFuncSetAttribute(decode_attention_mma_kernel,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem8));
         QK_PDL(c, decode_attention_mma_kernel, dim3(grid8), dim3(kMmaDecWarps * 32), smem8, 

@@ -43,6 +43,7 @@
 
 #include "qk_common.h"
 #include "qk_digits.cuh"
+#include "qk_direct.cuh"
 
 namespace {
 
@@ -689,52 +690,13 @@ layer_bitslice_fused_kernel(const StageParams *__restrict__ stage1,
 }
 
 // ------------------------------------------------------------------ small-batch direct form
-// One or a few tokens through a layer (single-token decode): the cost of a stage is not its
-// weight bits but the chain of dependent steps each block runs before it can multiply.  The
-// bit-sliced form's chain is: read the vector, reduce max|v|, quantise, build the digit table,
-// multiply, recombine.  This form has no table and no reduction over the vector at all:
-//   * the weight bits are expanded to bfloat16 +-1 in registers, two bits per A-fragment
-//     register (a field extract, a multiply that moves the two bits to the sign positions of
-//     the two halves, one LOP3), for mma.sync.m16n8k16 with float32 accumulation;
-//   * the vector is the B operand: under bfloat16 serving z = bf16(s2 * x) is one bfloat16 term
-//     (exactly the operands and the float32 accumulation of the reference's apply_bf16,
-//     engine/mod.rs:449-460); under float32 serving it is split into three bfloat16 terms
-//     (hi + mid + lo reproduces the float32 value to 2^-25) that ride as three of the MMA's
-//     eight N columns and are added at the end.
-// Accumulation is float32 in a fixed order (k-steps dealt to warps, partial sums added in
-// warp order), so results are reproducible; against the exact sum the error stays inside the
-// reference's float32 bound (1e-6 * sum|v_k|, tests/parity.rs:795) - it is NOT the bit-sliced
-// form's exact integer sum, which is why only the decoder's small-batch plans opt into it
-// (qk_plan_use_direct) and the layer entry points keep the exact form.  The intermediate t is
-// float32 here.  Same tile layout, same per-lane cp.async ring and k-split as the split-k form.
-// smem: [terms: n_terms x padded vector, bfloat16][ring][reduction buffer].
-constexpr int kDirectPadShift = 7;  // 4 elements of padding per 128: the four t-lanes hit different banks
-__device__ __forceinline__ uint32_t direct_index(uint32_t k) { return k + 4 * (k >> kDirectPadShift); }
-
-__device__ __forceinline__ void mma_bf16_f32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                             uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// Bits `pos`, `pos + 1` of w as two bfloat16 values (+1.0 for a set bit, -1.0 otherwise), the
-// lower bit in the low half.
-__device__ __forceinline__ uint32_t signs_bf16x2(uint32_t w, int pos) {
-    const uint32_t two = (w >> pos) & 3u;
-    // bit 0 -> bit 15 (and bit 30), bit 1 -> bit 31 (and bit 16): keep the two sign positions
-    return ((two * 0x40008000u) & 0x80008000u) ^ 0xBF80BF80u;
-}
-__device__ __forceinline__ uint16_t bf16_bits(float v) { return (uint16_t)(__float_as_uint(round_bf16(v)) >> 16); }
-
-constexpr int kDirectStages = 4;  // ring depth per warp, in tiles of 1 KB
-
+// The table-free form of qk_direct.cuh as a kernel over a plan's instances: grid (row groups,
+// instances), one token per instance.  The intermediate t is float32 here.
 template <bool kRoundBf16, bool kFinal>
-__global__ void __launch_bounds__(1024)
-gemv_direct_kernel(const StageParams *__restrict__ many, uint32_t term_stride) {
+__global__ void __launch_bounds__(qk_direct::kThreads)
+gemv_direct_kernel(const StageParams *__restrict__ many, uint32_t n_steps_max) {
     qk::pdl_launch();
     extern __shared__ __align__(128) uint8_t smem_dyn[];
-    constexpr int kTerms = kRoundBf16 ? 1 : 3;
     const StageParams p = many[blockIdx.y];
     const uint32_t n_rows = p.n_rows, n_bits = p.n_bits;
     const uint32_t n_groups = (n_rows + kGroupRows - 1) / kGroupRows;
@@ -743,32 +705,10 @@ gemv_direct_kernel(const StageParams *__restrict__ many, uint32_t term_stride) {
         qk::pdl_wait();
         return;
     }
-    // A work item is one 16-row tile of one k-step (1 KB).  Warp w owns tile w % 4 of the
-    // group's four and the k-steps w / 4, w / 4 + W / 4, ... (W, a multiple of four, warps).
-    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, n_warps = blockDim.x / 32;
-    const uint32_t m = warp % kTilesPerWarp, kl = warp / kTilesPerWarp, n_kl = n_warps / kTilesPerWarp;
-    const uint32_t g = lane / 4, t = lane % 4;
-    uint16_t *terms = reinterpret_cast<uint16_t *>(smem_dyn);  // [kTerms][term_stride]
-    uint8_t *ring_smem = smem_dyn + (size_t)kTerms * term_stride * 2;
-    float *red = reinterpret_cast<float *>(ring_smem + (size_t)n_warps * kDirectStages * kTileBytes);
-
-    const uint32_t n_items = kl < n_steps ? (n_steps - kl + n_kl - 1) / n_kl : 0;
-    uint4 *ring = reinterpret_cast<uint4 *>(ring_smem + (size_t)warp * kDirectStages * kTileBytes) + lane;
-    const uint4 *src = reinterpret_cast<const uint4 *>(p.w_tiles) + m * (kTileBytes / 16) + lane;
-    auto issue = [&](uint32_t i) {
-        if (i < n_items) {
-            uint4 *dst = ring + (size_t)(i % kDirectStages) * (kTileBytes / 16);
-            const uint4 *from = src + ((size_t)blockIdx.x * n_steps + kl + (size_t)i * n_kl) * (kChunkBytes / 16);
-            cp_async16(dst, from);            // row g:     bits 128 t .. 128 t + 127 of the k-step
-            cp_async16(dst + 32, from + 32);  // row g + 8
-        }
-        cp_async_commit();
-    };
-#pragma unroll
-    for (int st = 0; st < kDirectStages - 1; ++st) issue(st);
+    const qk_direct::Smem sm = qk_direct::carve(smem_dyn, n_steps_max, qk_direct::Terms<kRoundBf16>::kN);
+    const qk_direct::Work work{p.w_tiles, n_steps, blockIdx.x};
+    qk_direct::prefetch(sm, work);
     qk::pdl_wait();  // the weight bits depend on no other kernel, the input vector does
-
-    // ---- the input vector as bfloat16 terms (one pass, no reduction)
     for (uint32_t k = threadIdx.x; k < n_steps * kStepBits; k += blockDim.x) {
         float v = 0.f;
         if (k < n_bits) {
@@ -776,62 +716,12 @@ gemv_direct_kernel(const StageParams *__restrict__ many, uint32_t term_stride) {
             if (p.in_gate_up) v = v * p.in_gate_up[k] / (1.0f + expf(-v));
             if (p.in_scale) v = p.in_scale[k] * v;
         }
-        const uint32_t at = direct_index(k);
-        if (kRoundBf16) {
-            terms[at] = bf16_bits(v);  // z rounded once to bfloat16, as apply_bf16 does
-        } else {
-            const uint16_t hi = bf16_bits(v);
-            const float r1 = v - __uint_as_float((uint32_t)hi << 16);
-            const uint16_t mid = bf16_bits(r1);
-            const float r2 = r1 - __uint_as_float((uint32_t)mid << 16);
-            terms[at] = hi;
-            terms[term_stride + at] = mid;
-            terms[2 * term_stride + at] = bf16_bits(r2);
-        }
+        qk_direct::stage_value<kRoundBf16>(sm, 0, k, v);  // (bfloat16 serving: z rounded once, as apply_bf16 does)
     }
     __syncthreads();
-
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    // lane (g, t) feeds column g of B: term g of the vector (columns beyond the terms are zero)
-    const uint16_t *my_term = terms + (size_t)min(g, (uint32_t)kTerms - 1) * term_stride;
-    const bool live_col = g < (uint32_t)kTerms;
-    for (uint32_t i = 0; i < n_items; ++i) {
-        issue(i + kDirectStages - 1);
-        cp_async_wait<kDirectStages - 1>();
-        const uint4 *stage = ring + (size_t)(i % kDirectStages) * (kTileBytes / 16);
-        const uint4 lo = stage[0], hi = stage[32];
-        const uint32_t ks = kl + i * n_kl;
-        const uint16_t *bsrc = my_term + direct_index(ks * kStepBits + 128 * t);  // the lane's 128 k
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const uint32_t wg = q == 0 ? lo.x : q == 1 ? lo.y : q == 2 ? lo.z : lo.w;
-            const uint32_t wh = q == 0 ? hi.x : q == 1 ? hi.y : q == 2 ? hi.z : hi.w;
-#pragma unroll
-            for (int jj = 0; jj < 8; ++jj) {
-                // this MMA contracts the lane's k 32 q + 4 jj .. + 3 (and the other t-lanes'
-                // counterparts): B holds the vector's four values there
-                uint2 b = *reinterpret_cast<const uint2 *>(bsrc + 32 * q + 4 * jj);
-                if (!live_col) b = make_uint2(0u, 0u);
-                mma_bf16_f32(acc, signs_bf16x2(wg, 4 * jj), signs_bf16x2(wh, 4 * jj),
-                             signs_bf16x2(wg, 4 * jj + 2), signs_bf16x2(wh, 4 * jj + 2), b.x, b.y);
-            }
-        }
-    }
-    cp_async_wait<0>();
-    // ---- the terms' columns: lane t = 0 holds columns 0, 1 and lane t = 1 column 2 of rows g
-    // (acc[0..1]) and g + 8 (acc[2..3]); the other columns are zero
-    float sum_lo = acc[0] + acc[1], sum_hi = acc[2] + acc[3];
-    sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
-    sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
-    // ---- add the k-lanes' partial sums in order: red[k-lane][tile][row 0..15]
-    if (t == 0) {
-        red[(kl * kTilesPerWarp + m) * 16 + g] = sum_lo;
-        red[(kl * kTilesPerWarp + m) * 16 + g + 8] = sum_hi;
-    }
-    __syncthreads();
+    qk_direct::multiply(sm, work, qk_direct::Terms<kRoundBf16>::kN);
     if (threadIdx.x < kGroupRows) {
-        float sum = 0.f;
-        for (uint32_t w = 0; w < n_kl; ++w) sum += red[w * kGroupRows + threadIdx.x];
+        float sum = qk_direct::gather<kRoundBf16>(sm, threadIdx.x, 0);
         const uint32_t row = blockIdx.x * kGroupRows + threadIdx.x;
         if (row < n_rows) {
             if (kRoundBf16) sum = round_bf16(sum);  // t and u are rounded once to bfloat16
@@ -1600,20 +1490,8 @@ qk_status launch_fed_stage(qk_ctx *c, const StageParams *many, size_t n_inst, co
 }
 
 // Direct plans (gemv_direct_kernel): smem = terms + ring + reduction buffer for the widest input.
-bool direct_plan_fits(const qk_ctx *c, const StageShape &s, size_t n_inst, bool bf16, size_t *warps,
-                      size_t *smem, size_t *term_stride) {
-    // four warps (the four tiles of a row group) per k-lane; as many k-lanes as k-steps, up to 8
-    size_t lanes = s.n_steps < 1 ? 1 : s.n_steps > 8 ? 8 : s.n_steps;
-    const size_t padded = s.n_steps * kStepBits;
-    // (+16 elements: the terms then start on different banks)
-    *term_stride = padded + 4 * (padded >> kDirectPadShift) + 16;
-    const size_t terms = (bf16 ? 1 : 3) * *term_stride * 2;
-    auto bytes = [&](size_t kl) {
-        return terms + kl * kTilesPerWarp * ((size_t)kDirectStages * kTileBytes + 16 * 4);
-    };
-    while (lanes > 1 && bytes(lanes) > kSmemBudget) --lanes;
-    *warps = lanes * kTilesPerWarp;
-    *smem = bytes(lanes);
+bool direct_plan_fits(const qk_ctx *c, const StageShape &s, size_t n_inst, bool bf16, size_t *smem) {
+    *smem = qk_direct::smem_bytes((uint32_t)s.n_steps, bf16 ? 1 : 3);
     return *smem <= kSmemBudget && s.n_groups <= 65535 && n_inst <= 65535 &&
            n_inst * s.n_groups <= 16 * (size_t)c->sm_count;
 }
@@ -1621,14 +1499,14 @@ bool direct_plan_fits(const qk_ctx *c, const StageShape &s, size_t n_inst, bool 
 template <bool kFinal>
 qk_status launch_direct_stage(qk_ctx *c, const StageParams *many, size_t n_inst, const StageShape &s,
                               bool bf16) {
-    size_t warps, smem, term_stride;
-    if (!direct_plan_fits(c, s, n_inst, bf16, &warps, &smem, &term_stride))
+    size_t smem;
+    if (!direct_plan_fits(c, s, n_inst, bf16, &smem))
         return qk::fail(QK_ERR_VALUE, "a direct plan must fit the few-instance form");
     auto gemv = bf16 ? gemv_direct_kernel<true, kFinal> : gemv_direct_kernel<false, kFinal>;
     QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
     dim3 grid((unsigned)s.n_groups, (unsigned)n_inst);
-    (void)qk::launch_pdl(c->pdl, gemv, grid, dim3((unsigned)warps * 32), smem, c->stream, many,
-                         (uint32_t)term_stride);
+    (void)qk::launch_pdl(c->pdl, gemv, grid, dim3(qk_direct::kThreads), smem, c->stream, many,
+                         (uint32_t)s.n_steps);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     return QK_OK;
@@ -2024,9 +1902,9 @@ qk_status qk_plan_use_direct(qk_ctx *ctx, qk_group *plan) {
     std::lock_guard<std::mutex> lock(c->mu);
     if (plan->fed) return qk::fail(QK_ERR_VALUE, "a fed plan cannot take the direct form");
     const bool bf16 = plan->shape.serving == QK_BF16;
-    size_t warps, smem, stride;
-    if (!direct_plan_fits(c, stage1_shape(&plan->shape), plan->n_inst, bf16, &warps, &smem, &stride) ||
-        !direct_plan_fits(c, stage2_shape(&plan->shape), plan->n_inst, bf16, &warps, &smem, &stride))
+    size_t smem;
+    if (!direct_plan_fits(c, stage1_shape(&plan->shape), plan->n_inst, bf16, &smem) ||
+        !direct_plan_fits(c, stage2_shape(&plan->shape), plan->n_inst, bf16, &smem))
         return qk::fail(QK_ERR_VALUE, "a plan of %zu instances (up to %zu x %zu rank %zu) is too large "
                         "for the direct small-batch form", plan->n_inst, plan->shape.dout, plan->shape.din,
                         plan->shape.r);

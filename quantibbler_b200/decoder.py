@@ -21,7 +21,7 @@ import numpy as np
 
 from . import _lib, tp
 from ._lib import QK_BF16, QK_F32, KernelError, check
-from .gpu import GpuContext, LayerPlan, PackedLayer, apply_prefill_many, make_feed
+from .gpu import DecodeStep, GpuContext, LayerPlan, PackedLayer, apply_prefill_many, make_feed
 
 LINEARS = ("q", "k", "v", "o", "gate", "up", "down")
 
@@ -53,6 +53,11 @@ class DecoderConfig:
     # Batches up to this size run their linears in the table-free direct form (LayerPlan.use_direct):
     # float32 accumulation like the reference's own GEMV instead of the exact integer sum.
     direct_max_batch: int = 0
+    # Batches up to this size run all transformer blocks of a step as ONE cooperative kernel
+    # (gpu.DecodeStep; linears in the direct form, a grid barrier between phases instead of a
+    # kernel boundary).  Needs head_dim 128, a bfloat16 cache, no q/k norms, one GPU; other
+    # configurations keep the separate launches.
+    fused_step_max_batch: int = 0
     prefill_min_tokens: int = 16   # generate(): prompts this long go through the trunk in one pass
     prefill_chunk: int = 2048      # ... in pieces of at most this many positions
 
@@ -292,6 +297,23 @@ class Decoder:
                 for pl in plan.values():
                     pl.use_direct()
             self.plans.append(plan)
+        self.step_kernel = None
+        if (B <= cfg.fused_step_max_batch and tp_size == 1 and not self.has_qk_norm and hd == 128
+                and cfg.kv_dtype == "bfloat16" and B * (1 if cfg.serving == "bfloat16" else 3) <= 8):
+            blocks = [dict(L, input_norm=self.norms[li][0].data_ptr(), post_norm=self.norms[li][1].data_ptr(),
+                           cache_k=self.cache_k[li].data_ptr(), cache_v=self.cache_v[li].data_ptr())
+                      for li, L in enumerate(self.layers)]
+            bufs = dict(x=self.x, x2=self.x2, q=self.q, k=self.k, v=self.v, attn=self.attn,
+                        delta_attn=self.delta_attn, delta_mlp=self.delta_mlp, gate=self.g, up=self.u,
+                        att_scratch=self.att_scratch, cos_sin=self.cos_sin, positions=self.positions,
+                        seq_index=self.seq_index, kv_len=self.kv_len)
+            try:
+                self.step_kernel = DecodeStep(
+                    ctx, blocks, {n: t.data_ptr() for n, t in bufs.items()}, self.serving_tag, self.kv_tag,
+                    cfg.rms_eps, n_tokens=B, d_model=d, n_heads=self.h_loc, n_kv_heads=self.kv_loc,
+                    head_dim=hd, d_ff=self.ff_loc, s_max=cfg.max_seq, n_seq=B, n_splits=self.n_splits)
+            except KernelError:
+                self.step_kernel = None   # e.g. a model too wide for the kernel's shared memory
         # a large enough batch is a real contraction: the tcgen05 GEMM expands each weight bit
         # once for all tokens, the GEMV forms would do it once per token
         self.use_gemm = cfg.serving == "bfloat16" and B >= cfg.gemm_min_batch
@@ -399,7 +421,11 @@ class Decoder:
                            _p(self.x)))
         pending = None
         xa, xb = self.x, self.x2   # every norm reads the residual stream from xa and writes it to xb
-        for li in range(cfg.n_layers):
+        if self.step_kernel is not None:
+            # all blocks in one kernel; it leaves the stream in x and the last down output in delta_mlp
+            self.step_kernel.run()
+            pending = 1
+        for li in range(cfg.n_layers if self.step_kernel is None else 0):
             in_w, post_w = self.norms[li]
             feeds = self.feeds[li] if self.fed else None
             self._norm(pending, in_w, feeds["qkv"] if feeds else None, xa, xb)

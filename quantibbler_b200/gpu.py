@@ -458,6 +458,66 @@ def make_feed(pairs) -> Feed:
     return f
 
 
+class StepBlock(ctypes.Structure):
+    """The C ABI's ``qk_step_block``: one transformer block's layers, norm weights and caches."""
+    _fields_ = [(n, ctypes.c_void_p) for n in ("q", "k", "v", "o", "gate", "up", "down", "input_norm",
+                                               "post_norm", "cache_k", "cache_v")]
+
+
+class StepBuffers(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in ("x", "x2", "q", "k", "v", "attn", "delta_attn", "delta_mlp",
+                                               "gate", "up", "att_scratch", "cos_sin", "positions",
+                                               "seq_index", "kv_len")]
+
+
+class StepDesc(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_size_t) for n in ("n_blocks", "n_tokens", "d_model", "n_heads", "n_kv_heads",
+                                                "head_dim", "d_ff", "s_max", "n_seq", "n_splits")] +
+                [("rms_eps", ctypes.c_float), ("serving_dtype", ctypes.c_int32), ("kv_dtype", ctypes.c_int32),
+                 ("blocks", ctypes.POINTER(StepBlock)), ("buf", StepBuffers)])
+
+
+class DecodeStep:
+    """All transformer blocks of one decode step as one cooperative kernel
+    (``qk_decode_step_create`` / ``qk_decode_step_run``).  ``blocks``: per block a dict with the
+    seven PackedLayers under their names, ``input_norm`` / ``post_norm`` / ``cache_k`` / ``cache_v``
+    device pointers; ``buffers``: the names of ``StepBuffers`` mapped to device pointers;
+    ``dims``: the size fields of ``StepDesc``.  Raises KernelError when the configuration is
+    outside what the kernel takes."""
+
+    def __init__(self, ctx: GpuContext, blocks, buffers: dict, serving_tag: int, kv_tag: int, rms_eps: float,
+                 **dims):
+        self.ctx = ctx
+        self._keep = [b[n] for b in blocks for n in ("q", "k", "v", "o", "gate", "up", "down")]
+        arr = (StepBlock * len(blocks))()
+        for dst, b in zip(arr, blocks):
+            for n in ("q", "k", "v", "o", "gate", "up", "down"):
+                setattr(dst, n, b[n].handle)
+            for n in ("input_norm", "post_norm", "cache_k", "cache_v"):
+                setattr(dst, n, b[n])
+        desc = StepDesc(n_blocks=len(blocks), rms_eps=rms_eps, serving_dtype=serving_tag, kv_dtype=kv_tag,
+                        blocks=arr, **dims)
+        for n, _ in StepBuffers._fields_:
+            setattr(desc.buf, n, buffers[n])
+        h = ctypes.c_void_p()
+        check(_lib.lib().qk_decode_step_create(ctx.handle, ctypes.byref(desc), ctypes.byref(h)))
+        self._h = h
+
+    def run(self) -> None:
+        check(_lib.lib().qk_decode_step_run(self.ctx.handle, self._h))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            _lib.lib().qk_decode_step_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class LayerPlan(LayerGroup):
     """Instances (layer, x pointer, y pointer) bound once; ``apply`` is two kernel launches
     (one when there are at least as many instances as SMs).  The layers may differ in shape
@@ -498,5 +558,5 @@ class LayerPlan(LayerGroup):
         return ptr.value, n.value
 
 
-__all__ = ["apply_noalloc", "Feed", "make_feed", "LayerPlan", "LayerGroup", "HostLayerGroup", "GpuContext", "AttentionShape", "PackedLayer", "apply_group", "gpu_available",
+__all__ = ["apply_noalloc", "DecodeStep", "Feed", "make_feed", "LayerPlan", "LayerGroup", "HostLayerGroup", "GpuContext", "AttentionShape", "PackedLayer", "apply_group", "gpu_available",
            "gpu_init_hint", "GPU_INDEX_CEILING", "KernelError", "DeviceError"]

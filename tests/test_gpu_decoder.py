@@ -386,3 +386,72 @@ def test_fed_plans_reproduce_the_plain_step(gpu_ctx, serving):
     eager = Decoder(gpu_ctx, tiny_cfg(serving=serving, kv_dtype=kv), weights)
     eager.start(first, [0, 0, 0])
     assert np.array_equal(graph.decode(6), eager.decode(6))
+
+
+def step_cfg(**kw):
+    """A small model inside what the whole-step kernel takes: head_dim 128, bfloat16 cache,
+    ragged ranks and widths (several k-steps, partial row groups), four key splits."""
+    base = dict(n_layers=3, d_model=256, n_heads=4, n_kv_heads=2, head_dim=128, d_ff=640, vocab=192,
+                max_seq=96, max_batch=2, kv_dtype="bfloat16", serving="bfloat16", n_splits=4)
+    base.update(kw)
+    return DecoderConfig(**base)
+
+
+STEP_RANKS = {"q": 72, "k": 40, "v": 40, "o": 100, "gate": 130, "up": 130, "down": 90}
+
+
+@pytest.mark.parametrize("serving,batch", [("bfloat16", 1), ("bfloat16", 2), ("float32", 1), ("float32", 2)])
+def test_whole_step_kernel_reproduces_the_step_of_separate_launches(gpu_ctx, serving, batch):
+    """All blocks of a step in one cooperative kernel (norms, RoPE, cache append, combine and
+    SwiGLU folded into its phases) against the same step made of separate launches with direct
+    plans: the same device functions in the same order, so logits, tokens and cache contents
+    must agree bit for bit - over enough steps that the appended position crosses from one key
+    split into the next - and both must stay within the usual tolerance of the forward oracle."""
+    cfg = step_cfg(serving=serving, max_batch=batch)
+    weights = random_model(cfg, STEP_RANKS, seed=77)
+    plain = Decoder(gpu_ctx, step_cfg(serving=serving, max_batch=batch, direct_max_batch=batch), weights)
+    fused = Decoder(gpu_ctx, step_cfg(serving=serving, max_batch=batch, fused_step_max_batch=batch), weights)
+    assert fused.step_kernel is not None and plain.step_kernel is None
+    first = [9, 41][:batch]
+    want_t, want_l = reference_run(cfg, weights, first, 4, decoder_np._bf16)
+    for dec in (plain, fused):
+        dec.start(first, [0] * batch)
+    tol = 2e-4 if serving == "float32" else 3e-2
+    for step in range(30):
+        for dec in (plain, fused):
+            dec.step()
+        gpu_ctx.synchronize()
+        a, b = fused.logits.cpu().numpy(), plain.logits.cpu().numpy()
+        assert np.array_equal(a, b), step
+        if step < 4:
+            assert np.abs(a - want_l[step]).max() <= 5 * tol * np.abs(want_l).max()
+        for dec in (plain, fused):
+            dec.advance()
+        assert np.array_equal(fused.token_ids.cpu().numpy(), plain.token_ids.cpu().numpy())
+        if step < 4:
+            assert np.array_equal(fused.token_ids.cpu().numpy(), want_t[step])
+    for li in range(cfg.n_layers):
+        assert torch_equal(fused.cache_k[li], plain.cache_k[li]) and torch_equal(fused.cache_v[li], plain.cache_v[li])
+    # captured in a graph (a cooperative launch inside a CUDA graph) it replays the same tokens
+    graph = Decoder(gpu_ctx, step_cfg(serving=serving, max_batch=batch, fused_step_max_batch=batch), weights)
+    graph.capture()
+    graph.start(first, [0] * batch)
+    eager = Decoder(gpu_ctx, step_cfg(serving=serving, max_batch=batch, fused_step_max_batch=batch), weights)
+    eager.start(first, [0] * batch)
+    assert np.array_equal(graph.decode(12), eager.decode(12))
+    gpu_ctx.set_stream(None)
+
+
+def torch_equal(a, b):
+    import torch
+    return bool(torch.equal(a, b))
+
+
+def test_whole_step_kernel_is_refused_outside_its_limits(gpu_ctx):
+    """head_dim other than 128, a float32 cache or too many tokens keep the separate launches."""
+    weights = random_model(tiny_cfg(), RANKS, seed=5)
+    dec = Decoder(gpu_ctx, tiny_cfg(fused_step_max_batch=4), weights)   # head_dim 16, float32 cache
+    assert dec.step_kernel is None
+    cfg = step_cfg(serving="float32", max_batch=3, fused_step_max_batch=3)   # 3 tokens x 3 terms > 8 columns
+    dec = Decoder(gpu_ctx, cfg, random_model(cfg, STEP_RANKS, seed=6))
+    assert dec.step_kernel is None
