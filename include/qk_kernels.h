@@ -340,6 +340,11 @@ typedef struct qk_step_desc {
 typedef struct qk_decode_step qk_decode_step;
 qk_status qk_decode_step_create(qk_ctx *ctx, const qk_step_desc *desc, qk_decode_step **out);
 qk_status qk_decode_step_run(qk_ctx *ctx, const qk_decode_step *step);
+/* Diagnostic: later runs of the step write the device's nanosecond timer, as block 0 sees it,
+ * at kernel start, after every grid barrier and at the end into stamps_dev (capacity entries;
+ * 9 barriers per block of the model); NULL switches the trace off.  The differences are the
+ * durations of the phases. */
+qk_status qk_decode_step_trace(qk_decode_step *step, uint64_t *stamps_dev, size_t capacity);
 void qk_decode_step_free(qk_decode_step *step);
 
 /* ---- fed plans ------------------------------------------------------------------

@@ -87,6 +87,7 @@ _SIGNATURES = {
     "qk_decode_step_create": (c_int32, [c_void_p, c_void_p, POINTER(c_void_p)]),
     "qk_decode_step_run": (c_int32, [c_void_p, c_void_p]),
     "qk_decode_step_free": (None, [c_void_p]),
+    "qk_decode_step_trace": (c_int32, [c_void_p, c_void_p, c_size_t]),
     "qk_rmsnorm_feed": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_float,
                                   c_int32, c_void_p, c_void_p, c_void_p]),
     "qk_allreduce_rmsnorm_feed": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32,

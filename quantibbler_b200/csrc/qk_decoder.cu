@@ -794,12 +794,12 @@ decode_combine_kernel(const float *__restrict__ partial, float *__restrict__ out
                       uint32_t n_splits) {
     qk::pdl_launch();  // the next kernel may begin its prologue
     qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
-    __shared__ float wgt[128];  // exp(m_s - m) / l per split (n_splits <= 128)
-    __shared__ float red[4];
-    decode_combine_body(SubBlock{threadIdx.x, 0}, wgt, red, partial + (size_t)blockIdx.x * n_splits * (d + 2),
-                        out + (size_t)blockIdx.x * d, d, n_splits);
+    // warp w: channels 32 w + lane, + 128, ...
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    for (uint32_t c0 = 32 * warp; c0 < d; c0 += 128)
+        decode_combine_warp<1, 16>(lane, partial + (size_t)blockIdx.x * n_splits * (d + 2),
+                                   out + (size_t)blockIdx.x * d, d, n_splits, c0, 0);
 }
-
 
 __global__ void swiglu_kernel(const float *__restrict__ g, const float *__restrict__ u,
                               float *__restrict__ out, size_t n) {

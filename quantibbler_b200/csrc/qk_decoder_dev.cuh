@@ -355,34 +355,61 @@ __device__ __forceinline__ void decode_attention_mma_body(
     }
 }
 
-// out[h, :] = sum_s o_s * exp(m_s - m) / sum_s l_s * exp(m_s - m) for one (sequence, head):
-// p = that head's n_splits partials {m, l, o[d]}, `out` its d outputs.  128 threads;
-// wgt[128] and red[4] are the group's shared memory.
-__device__ __forceinline__ void decode_combine_body(const SubBlock sb, float *wgt, float *red,
-                                                    const float *__restrict__ p, float *__restrict__ out,
-                                                    uint32_t d, uint32_t n_splits) {
-    const uint32_t tid = sb.tid;
-    float ms = tid < n_splits ? __ldcg(p + tid * (d + 2)) : -INFINITY;
-    float ls = tid < n_splits ? __ldcg(p + tid * (d + 2) + 1) : 0.f;
-    float mm = ms;
-    for (int off = 16; off > 0; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
-    if (tid % 32 == 0) red[tid / 32] = mm;
-    sb.sync();
-    mm = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-    sb.sync();
-    const float w = ms == -INFINITY ? 0.f : expf(ms - mm);
-    float ll = ls * w;
-    for (int off = 16; off > 0; off >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, off);
-    if (tid % 32 == 0) red[tid / 32] = ll;
-    wgt[tid] = w;
-    sb.sync();
-    ll = red[0] + red[1] + red[2] + red[3];
-    for (uint32_t c = tid; c < d; c += 128) {
-        float oo = 0.f;
-        for (uint32_t s = 0; s < n_splits; ++s) oo += __ldcg(p + s * (d + 2) + 2 + c) * wgt[s];
-        out[c] = oo / ll;
+// out[c] = sum_s o_s[c] * exp(m_s - m) / sum_s l_s * exp(m_s - m) for one (sequence, head), by
+// ONE warp: p = that head's n_splits <= 128 partials {m, l, o[d]}; the warp produces the
+// channels c0 + lane + i * c_stride, i < kCh (those below d).  The loads of kBatch splits are
+// issued together, the products are added in split order, so the result does not depend on
+// kCh or kBatch.  No shared memory, no block barrier.
+template <int kCh, int kBatch>
+__device__ __forceinline__ void decode_combine_warp(uint32_t lane, const float *__restrict__ p,
+                                                    float *__restrict__ out, uint32_t d, uint32_t n_splits,
+                                                    uint32_t c0, uint32_t c_stride) {
+    float ms[4], ls[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t s = lane + 32 * i;
+        ms[i] = s < n_splits ? __ldcg(p + (size_t)s * (d + 2)) : -INFINITY;
+        ls[i] = s < n_splits ? __ldcg(p + (size_t)s * (d + 2) + 1) : 0.f;
     }
-    sb.sync();  // wgt and red may be reused
+    float mm = fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3]));
+    for (int off = 16; off > 0; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
+    float wv[4], ll = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        wv[i] = ms[i] == -INFINITY ? 0.f : expf(ms[i] - mm);
+        float part = ls[i] * wv[i];
+        for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+        ll = i == 0 ? part : ll + part;
+    }
+    float oo[kCh];
+#pragma unroll
+    for (int i = 0; i < kCh; ++i) oo[i] = 0.f;
+    for (uint32_t s0 = 0; s0 < n_splits; s0 += kBatch) {
+        float x[kBatch][kCh];
+#pragma unroll
+        for (int e = 0; e < kBatch; ++e)
+#pragma unroll
+            for (int i = 0; i < kCh; ++i) {
+                const uint32_t c = c0 + lane + i * c_stride;
+                x[e][i] = (s0 + e < n_splits && c < d) ? __ldcg(p + (size_t)(s0 + e) * (d + 2) + 2 + c) : 0.f;
+            }
+#pragma unroll
+        for (int e = 0; e < kBatch; ++e) {
+            const uint32_t s = s0 + e;
+            if (s < n_splits) {  // (the same for every lane)
+                const uint32_t q = s / 32;
+                const float mine = q == 0 ? wv[0] : q == 1 ? wv[1] : q == 2 ? wv[2] : wv[3];
+                const float w = __shfl_sync(0xffffffffu, mine, s % 32);
+#pragma unroll
+                for (int i = 0; i < kCh; ++i) oo[i] += x[e][i] * w;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kCh; ++i) {
+        const uint32_t c = c0 + lane + i * c_stride;
+        if (c < d) out[c] = oo[i] / ll;
+    }
 }
 
 }  // namespace

@@ -165,4 +165,109 @@ __device__ __forceinline__ void block_build_table(Entry entry, uint32_t n_steps,
     __syncthreads();
 }
 
+// ---- the same table without floating-point arithmetic --------------------------------
+// fp.quant(v) = round-to-nearest-even(v * 2^shift) of a finite value given by its bits:
+// v = (-1)^neg * mant * 2^exp_lsb.  The conversions and the float64 multiply of the
+// arithmetic form are slow, dependent instructions; shifts are not.  The result is the same
+// integer: v * 2^shift is exact in float64 (a power-of-two scaling), so its rounding to an
+// integer is the rounding of mant * 2^(exp_lsb + shift).
+__device__ __forceinline__ long long quant_bits(unsigned long long mant, int exp_lsb, bool neg, int shift) {
+    const int sh = exp_lsb + shift;
+    unsigned long long q;
+    if (sh >= 0) {
+        q = mant << (sh < 63 ? sh : 63);  // (|q| < 2^48 by the choice of shift whenever mant != 0)
+    } else {
+        const int r = -sh;
+        if (r >= 56) {
+            q = 0;  // mant < 2^53: below a quarter
+        } else {
+            q = mant >> r;
+            const unsigned long long rem = mant & ((1ull << r) - 1), half = 1ull << (r - 1);
+            if (rem > half || (rem == half && (q & 1))) ++q;
+        }
+    }
+    return neg ? -(long long)q : (long long)q;
+}
+template <typename T> struct FloatBits;
+template <> struct FloatBits<float> {
+    // |v| as an unsigned integer that orders like |v|; anything at or above `kBad` is NaN or infinity
+    static constexpr unsigned long long kBad = 0x7f800000ull;
+    __device__ static unsigned long long magnitude(float v) { return __float_as_uint(v) & 0x7fffffffu; }
+    __device__ static double as_double(unsigned long long mag) { return (double)__uint_as_float((uint32_t)mag); }
+    __device__ static long long quant(float v, int shift) {
+        const uint32_t u = __float_as_uint(v), ex = (u >> 23) & 0xffu;
+        const uint32_t mant = (u & 0x7fffffu) | (ex ? 0x800000u : 0u);
+        const int sh = (int)(ex ? ex : 1u) - 150 + shift;
+        if (sh >= 0) {  // the usual case (a value within 2^23 of the largest): a plain shift
+            const long long q = (long long)((unsigned long long)mant << (sh < 63 ? sh : 63));
+            return (u >> 31) ? -q : q;
+        }
+        return quant_bits(mant, (int)(ex ? ex : 1u) - 150, (u >> 31) != 0, shift);
+    }
+};
+template <> struct FloatBits<double> {
+    // the arithmetic form calls a value above 1.7e308 non-finite
+    static constexpr unsigned long long kBad = 0x7FEE42D130773B77ull;  // the bits after those of 1.7e308
+    __device__ static unsigned long long magnitude(double v) {
+        return (unsigned long long)__double_as_longlong(v) & 0x7fffffffffffffffull;
+    }
+    __device__ static double as_double(unsigned long long mag) { return __longlong_as_double((long long)mag); }
+    __device__ static long long quant(double v, int shift) {
+        const unsigned long long u = (unsigned long long)__double_as_longlong(v);
+        const uint32_t ex = (uint32_t)(u >> 52) & 0x7ffu;
+        return quant_bits((u & 0xfffffffffffffull) | (ex ? 1ull << 52 : 0ull), (int)(ex ? ex : 1u) - 1075,
+                          (u >> 63) != 0, shift);
+    }
+};
+
+// block_build_table for a vector that lies in shared memory (vec[k], k < n_bits; zero beyond):
+// the same table and the same stage record, by integer arithmetic on the bits of the values.
+// red_max, red_sum: 32 eight-byte entries of shared memory each; red_bad: one int.
+template <typename T>
+__device__ __forceinline__ void block_build_table_bits(const T *vec, uint32_t n_bits, uint32_t n_steps, uint4 *table,
+                                                       StageMeta *meta_out, unsigned long long *red_max,
+                                                       long long *red_sum, int *red_bad) {
+    const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32, n_warps = (blockDim.x + 31) / 32;
+    unsigned long long mx = 0;
+    for (uint32_t k = tid; k < n_bits; k += blockDim.x) {
+        const unsigned long long mag = FloatBits<T>::magnitude(vec[k]);
+        mx = mag > mx ? mag : mx;
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, mx, off);
+        mx = other > mx ? other : mx;
+    }
+    if (lane == 0) red_max[warp] = mx;
+    __syncthreads();
+    mx = red_max[0];
+    for (uint32_t w = 1; w < n_warps; ++w) mx = red_max[w] > mx ? red_max[w] : mx;
+    const int nonfinite = mx >= FloatBits<T>::kBad;
+    const FixedPoint fp = fixed_point_of(nonfinite ? 0.0 : FloatBits<T>::as_double(mx));
+    long long total = 0;
+    const uint32_t n_records = n_steps * 64;
+    for (uint32_t r = tid; r < n_records; r += blockDim.x) {
+        const uint32_t ks = r / 64, rec = r % 64;
+        const uint32_t tt = rec % 4, ip = (rec / 4) % 4, qw = rec / 16;
+        long long q8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const uint32_t k = ks * kStepBits + 128 * tt + 32 * qw + 8 * (e % 4) + 2 * ip + e / 4;
+            q8[e] = (nonfinite || k >= n_bits) ? 0 : FloatBits<T>::quant(vec[k], fp.shift);
+            total += q8[e];
+        }
+        build_record(q8, ip, table + (size_t)r * 4);
+    }
+    for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+    if (lane == 0) red_sum[warp] = total;
+    __syncthreads();
+    if (tid == 0) {
+        long long sum = 0;
+        for (uint32_t w = 0; w < n_warps; ++w) sum += red_sum[w];
+        meta_out->total = sum;
+        meta_out->shift = fp.shift;
+        meta_out->nonfinite = nonfinite;
+    }
+    __syncthreads();
+}
+
 }  // namespace

@@ -117,6 +117,73 @@ __device__ __forceinline__ void stage_value(const Smem &s, uint32_t tok, uint32_
     }
 }
 
+// Four consecutive elements k .. k + 3 (k a multiple of 4) of token `tok`'s vector.
+template <bool kRoundBf16>
+__device__ __forceinline__ void stage_four(const Smem &s, uint32_t tok, uint32_t k, float4 v) {
+    const uint32_t at = padded_index(k);  // k .. k + 3 share a padding group
+    uint16_t *col = s.cols + (size_t)tok * Terms<kRoundBf16>::kN * s.stride + at;
+    const float in[4] = {v.x, v.y, v.z, v.w};
+    uint16_t hi[4], mid[4], lo[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        hi[e] = bf16_bits(in[e]);
+        if (!kRoundBf16) {
+            const float r1 = in[e] - __uint_as_float((uint32_t)hi[e] << 16);
+            mid[e] = bf16_bits(r1);
+            lo[e] = bf16_bits(r1 - __uint_as_float((uint32_t)mid[e] << 16));
+        }
+    }
+    *reinterpret_cast<uint2 *>(col) = make_uint2(hi[0] | ((uint32_t)hi[1] << 16), hi[2] | ((uint32_t)hi[3] << 16));
+    if (!kRoundBf16) {
+        *reinterpret_cast<uint2 *>(col + s.stride) =
+            make_uint2(mid[0] | ((uint32_t)mid[1] << 16), mid[2] | ((uint32_t)mid[3] << 16));
+        *reinterpret_cast<uint2 *>(col + 2 * s.stride) =
+            make_uint2(lo[0] | ((uint32_t)lo[1] << 16), lo[2] | ((uint32_t)lo[3] << 16));
+    }
+}
+
+// Stages token `tok`'s vector of n_bits elements (zero beyond, up to n_steps k-steps).  All of a
+// thread's loads are issued before any value is used, so the whole vector costs one memory
+// round trip per 4096 elements (scalar form) or per 16384 (vector form), not one per element.
+//   value(k)  -> float   element k, k < n_bits
+//   value4(k) -> float4  elements k .. k + 3; only called when `vector_ok` (n_bits a multiple
+//                        of 4 and the sources 16-byte aligned), with k + 3 < n_bits
+template <bool kRoundBf16, class Value, class Value4>
+__device__ __forceinline__ void stage_vector(const Smem &s, uint32_t tok, uint32_t n_bits, uint32_t n_steps,
+                                             bool vector_ok, Value value, Value4 value4) {
+    const uint32_t padded = n_steps * kStepBits;
+    constexpr int kBatch = 8;
+    if (vector_ok) {
+        for (uint32_t base = 0; base < padded; base += kBatch * 4 * kThreads) {
+            float4 v[kBatch];
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const uint32_t k = base + 4 * (threadIdx.x + i * kThreads);
+                v[i] = k < n_bits ? value4(k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const uint32_t k = base + 4 * (threadIdx.x + i * kThreads);
+                if (k < padded) stage_four<kRoundBf16>(s, tok, k, v[i]);
+            }
+        }
+    } else {
+        for (uint32_t base = 0; base < padded; base += kBatch * kThreads) {
+            float v[kBatch];
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const uint32_t k = base + threadIdx.x + i * kThreads;
+                v[i] = k < n_bits ? value(k) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const uint32_t k = base + threadIdx.x + i * kThreads;
+                if (k < padded) stage_value<kRoundBf16>(s, tok, k, v[i]);
+            }
+        }
+    }
+}
+
 // One row group of one packed factor: tiles of 16 rows x 512 bits, four per 4 KB chunk,
 // chunks ordered [group][k-step].
 struct Work {

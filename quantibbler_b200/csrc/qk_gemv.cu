@@ -708,16 +708,40 @@ gemv_direct_kernel(const StageParams *__restrict__ many, uint32_t n_steps_max) {
     const qk_direct::Smem sm = qk_direct::carve(smem_dyn, n_steps_max, qk_direct::Terms<kRoundBf16>::kN);
     const qk_direct::Work work{p.w_tiles, n_steps, blockIdx.x};
     qk_direct::prefetch(sm, work);
-    qk::pdl_wait();  // the weight bits depend on no other kernel, the input vector does
-    for (uint32_t k = threadIdx.x; k < n_steps * kStepBits; k += blockDim.x) {
-        float v = 0.f;
-        if (k < n_bits) {
-            v = static_cast<const float *>(p.in)[k];  // x, or the float32 t of stage 1
-            if (p.in_gate_up) v = v * p.in_gate_up[k] / (1.0f + expf(-v));
-            if (p.in_scale) v = p.in_scale[k] * v;
-        }
-        qk_direct::stage_value<kRoundBf16>(sm, 0, k, v);  // (bfloat16 serving: z rounded once, as apply_bf16 does)
+    // what the epilogue needs of the layer itself is fetched now, not after the multiply
+    const uint32_t my_row = blockIdx.x * kGroupRows + threadIdx.x;
+    float out_scale = 1.f, out_bias = 0.f;
+    if (kFinal && threadIdx.x < kGroupRows && my_row < n_rows) {
+        if (p.out_scale) out_scale = p.out_scale[my_row];
+        if (p.out_bias) out_bias = p.out_bias[my_row];
     }
+    qk::pdl_wait();  // the weight bits depend on no other kernel, the input vector does
+    const float *in = static_cast<const float *>(p.in);  // x, or the float32 t of stage 1
+    const float *gate_up = p.in_gate_up, *scale = p.in_scale;
+    auto one = [&](uint32_t k) {
+        float v = in[k];
+        if (gate_up) v = v * gate_up[k] / (1.0f + expf(-v));
+        if (scale) v = scale[k] * v;
+        return v;
+    };
+    auto four = [&](uint32_t k) {
+        float4 v = *reinterpret_cast<const float4 *>(in + k);
+        if (gate_up) {
+            const float4 u = *reinterpret_cast<const float4 *>(gate_up + k);
+            v.x = v.x * u.x / (1.0f + expf(-v.x)), v.y = v.y * u.y / (1.0f + expf(-v.y));
+            v.z = v.z * u.z / (1.0f + expf(-v.z)), v.w = v.w * u.w / (1.0f + expf(-v.w));
+        }
+        if (scale) {
+            const float4 sc = *reinterpret_cast<const float4 *>(scale + k);
+            v.x = sc.x * v.x, v.y = sc.y * v.y, v.z = sc.z * v.z, v.w = sc.w * v.w;
+        }
+        return v;
+    };
+    const bool vector_ok = n_bits % 4 == 0 &&
+                           ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(gate_up) |
+                             reinterpret_cast<uintptr_t>(scale)) & 15) == 0;
+    // (bfloat16 serving: z is rounded once to bfloat16, as apply_bf16 does)
+    qk_direct::stage_vector<kRoundBf16>(sm, 0, n_bits, n_steps, vector_ok, one, four);
     __syncthreads();
     qk_direct::multiply(sm, work, qk_direct::Terms<kRoundBf16>::kN);
     if (threadIdx.x < kGroupRows) {
@@ -726,8 +750,8 @@ gemv_direct_kernel(const StageParams *__restrict__ many, uint32_t n_steps_max) {
         if (row < n_rows) {
             if (kRoundBf16) sum = round_bf16(sum);  // t and u are rounded once to bfloat16
             if (kFinal) {
-                if (p.out_scale) sum = sum * p.out_scale[row];
-                if (p.out_bias) sum = sum + p.out_bias[row];
+                if (p.out_scale) sum = sum * out_scale;
+                if (p.out_bias) sum = sum + out_bias;
             }
             static_cast<float *>(p.out)[row] = sum;
         }

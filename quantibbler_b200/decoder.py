@@ -54,9 +54,10 @@ class DecoderConfig:
     # float32 accumulation like the reference's own GEMV instead of the exact integer sum.
     direct_max_batch: int = 0
     # Batches up to this size run all transformer blocks of a step as ONE cooperative kernel
-    # (gpu.DecodeStep; linears in the direct form, a grid barrier between phases instead of a
-    # kernel boundary).  Needs head_dim 128, a bfloat16 cache, no q/k norms, one GPU; other
-    # configurations keep the separate launches.
+    # (gpu.DecodeStep: a grid barrier between phases instead of a kernel boundary; the same
+    # bits as the separate launches).  Needs head_dim 128, a bfloat16 cache, no q/k norms, one
+    # GPU and a model narrow enough for its shared memory; other configurations keep the
+    # separate launches.
     fused_step_max_batch: int = 0
     prefill_min_tokens: int = 16   # generate(): prompts this long go through the trunk in one pass
     prefill_chunk: int = 2048      # ... in pieces of at most this many positions
@@ -299,7 +300,7 @@ class Decoder:
             self.plans.append(plan)
         self.step_kernel = None
         if (B <= cfg.fused_step_max_batch and tp_size == 1 and not self.has_qk_norm and hd == 128
-                and cfg.kv_dtype == "bfloat16" and B * (1 if cfg.serving == "bfloat16" else 3) <= 8):
+                and cfg.kv_dtype == "bfloat16"):
             blocks = [dict(L, input_norm=self.norms[li][0].data_ptr(), post_norm=self.norms[li][1].data_ptr(),
                            cache_k=self.cache_k[li].data_ptr(), cache_v=self.cache_v[li].data_ptr())
                       for li, L in enumerate(self.layers)]

@@ -506,6 +506,11 @@ class DecodeStep:
     def run(self) -> None:
         check(_lib.lib().qk_decode_step_run(self.ctx.handle, self._h))
 
+    def trace(self, stamps_ptr: int | None, capacity: int = 0) -> None:
+        """Later runs record the device timer at kernel start, after every grid barrier and at
+        the end into ``capacity`` uint64 entries at ``stamps_ptr`` (None: off)."""
+        check(_lib.lib().qk_decode_step_trace(self._h, ctypes.c_void_p(stamps_ptr or 0), capacity))
+
     def close(self) -> None:
         if getattr(self, "_h", None):
             _lib.lib().qk_decode_step_free(self._h)

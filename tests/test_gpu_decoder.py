@@ -400,19 +400,20 @@ def step_cfg(**kw):
 STEP_RANKS = {"q": 72, "k": 40, "v": 40, "o": 100, "gate": 130, "up": 130, "down": 90}
 
 
-@pytest.mark.parametrize("serving,batch", [("bfloat16", 1), ("bfloat16", 2), ("float32", 1), ("float32", 2)])
+@pytest.mark.parametrize("serving,batch", [("bfloat16", 1), ("bfloat16", 2), ("float32", 1), ("float32", 3)])
 def test_whole_step_kernel_reproduces_the_step_of_separate_launches(gpu_ctx, serving, batch):
     """All blocks of a step in one cooperative kernel (norms, RoPE, cache append, combine and
-    SwiGLU folded into its phases) against the same step made of separate launches with direct
-    plans: the same device functions in the same order, so logits, tokens and cache contents
-    must agree bit for bit - over enough steps that the appended position crosses from one key
-    split into the next - and both must stay within the usual tolerance of the forward oracle."""
+    SwiGLU folded into its phases) against the same step made of separate launches: the same
+    exact integer sums and the same device functions in the same order, so logits, tokens and
+    cache contents must agree bit for bit - over enough steps that the appended position
+    crosses from one key split into the next - and stay within the usual tolerance of the
+    forward oracle."""
     cfg = step_cfg(serving=serving, max_batch=batch)
     weights = random_model(cfg, STEP_RANKS, seed=77)
-    plain = Decoder(gpu_ctx, step_cfg(serving=serving, max_batch=batch, direct_max_batch=batch), weights)
+    plain = Decoder(gpu_ctx, step_cfg(serving=serving, max_batch=batch), weights)
     fused = Decoder(gpu_ctx, step_cfg(serving=serving, max_batch=batch, fused_step_max_batch=batch), weights)
     assert fused.step_kernel is not None and plain.step_kernel is None
-    first = [9, 41][:batch]
+    first = [9, 41, 7][:batch]
     want_t, want_l = reference_run(cfg, weights, first, 4, decoder_np._bf16)
     for dec in (plain, fused):
         dec.start(first, [0] * batch)
@@ -452,6 +453,6 @@ def test_whole_step_kernel_is_refused_outside_its_limits(gpu_ctx):
     weights = random_model(tiny_cfg(), RANKS, seed=5)
     dec = Decoder(gpu_ctx, tiny_cfg(fused_step_max_batch=4), weights)   # head_dim 16, float32 cache
     assert dec.step_kernel is None
-    cfg = step_cfg(serving="float32", max_batch=3, fused_step_max_batch=3)   # 3 tokens x 3 terms > 8 columns
+    cfg = step_cfg(max_batch=9, fused_step_max_batch=9)   # more tokens than the kernel takes
     dec = Decoder(gpu_ctx, cfg, random_model(cfg, STEP_RANKS, seed=6))
     assert dec.step_kernel is None
