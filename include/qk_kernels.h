@@ -184,9 +184,13 @@ qk_status qk_gpu_attention_dev(qk_ctx *ctx, const qk_attention_shape *shape, con
 qk_status qk_gpu_attention_sage_dev(qk_ctx *ctx, const qk_attention_shape *shape,
                                     const float *q_dev, const float *k_dev, const float *v_dev,
                                     int32_t causal, size_t block_size, float *out_dev);
-/* Which kernel the Sage face runs: 1 (default) the INT8 tensor-core kernel where the shape
- * allows (head_dim == val_dim in {64, 128}, block_size in {32, 64, 128}), 0 always the dp4a
- * kernel.  Returns the previous choice. */
+/* Which kernel the Sage face runs: 2 (default) the tcgen05 kernel (kind::i8 products with
+ * the accumulators in tensor memory) where the shape allows (head_dim == val_dim == 128,
+ * block_size 64), else as 1; 1 the mma.sync INT8 tensor-core kernel where the shape allows
+ * (head_dim == val_dim in {64, 128}, block_size in {32, 64, 128}), else as 0; 0 always the
+ * dp4a kernel.  All three do the same arithmetic.  A bounded wait of the tcgen05 kernel that
+ * expires is reported by the next qk_gpu_synchronize as QK_ERR_TIMEOUT.  Returns the
+ * previous choice. */
 int32_t qk_set_sage_kernel(qk_ctx *ctx, int32_t which);
 /* Which kernel qk_decode_attention runs for a bfloat16 cache with head_dim 128: 1 (default)
  * the bf16 tensor-core kernel, 0 the scalar kernel.  Returns the previous choice. */

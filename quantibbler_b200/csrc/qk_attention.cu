@@ -28,6 +28,7 @@
 #include <string>
 
 #include "qk_common.h"
+#include "qk_umma.cuh"
 
 namespace {
 
@@ -714,6 +715,272 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
     }
 }
 
+// ------------------------------------------------------------------ Sage on tcgen05 (kind::i8)
+// The same arithmetic once more, with both integer products on the 5th-generation tensor
+// cores: tcgen05.mma kind::i8 (s8 x s8 -> s32) with the accumulators in tensor memory.  Built
+// for head_dim = val_dim = 128 and the Sage key block of 64 (benchmark configuration 2).
+//   * A CTA of 128 threads owns 128 queries; thread r is query row r and tensor-memory lane r,
+//     so everything per row (maximum, sum, the 128 output channels) lives in one thread and
+//     needs no shuffles.
+//   * One iteration covers TWO Sage blocks (128 keys): S = Qhat [Khat_a; Khat_b; mean digits]^T
+//     is one 128 x 144 x 128 product (the sixteen extra B rows are the digit rows of the two
+//     blocks' channel means, which give the per-row shift), then the online softmax runs block
+//     by block exactly as in the other kernels - block b's codes use the maximum after block a -
+//     and the two PV products (128 x 128 x 64 each, because V has one scale set per block) go
+//     to two accumulators that alias S, which has been read out by then.
+//   * Operands are staged by cp.async into 128-byte-swizzled K-major tiles (rows of 128 bytes:
+//     Q and K rows are 128 channels, P and V rows are the iteration's 128 keys, V_a and V_b
+//     side by side), double-buffered across iterations.  The P codes go from registers to
+//     shared memory and are the A operand of PV.
+//   * Two such CTAs share an SM (256 tensor-memory columns, ~106 KB of shared memory each), so
+//     one CTA's softmax overlaps the other's products.
+// All waits on the MMA barriers are bounded (bit 1 of the context's error word on expiry).
+constexpr int kUQ = 128, kUBlk = 64, kUKeys = 2 * kUBlk, kUD = 128;
+constexpr int kUSRows = kUKeys + 16;  // keys + 2 x 8 mean-digit rows: N of the S product
+constexpr uint32_t kUQBytes = kUQ * 128, kUKBytes = kUSRows * 128, kUVBytes = kUD * 128, kUPBytes = kUQ * 128;
+constexpr uint32_t kUScaleFloats = kUKeys + 2 * kUD + 16;  // key scales, two sets of channel scales, two mean units
+constexpr uint32_t kUSmemBytes = kUQBytes + 2 * kUKBytes + 2 * kUVBytes + kUPBytes + 2 * kUScaleFloats * 4 + 64;
+constexpr uint32_t kUTmemCols = 256;
+constexpr uint32_t kUWaitLimitDefault = 1u << 22;
+
+// s8 x s8 -> s32, both operands K-major, M = 128, N = n
+__device__ __forceinline__ uint32_t umma_idesc_i8(uint32_t n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((uint32_t)(kUQ >> 4) << 24);
+}
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(kUQ, 2)
+attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_limit, int *error) {
+    extern __shared__ __align__(1024) uint8_t sm_u_raw[];
+    // (the swizzled tiles want 1024-byte alignment; the launch asks for 1 KB more than kUSmemBytes)
+    uint8_t *sm_u = sm_u_raw + ((1024 - (smem_u32(sm_u_raw) & 1023)) & 1023);
+    uint8_t *Qs = sm_u, *Kb = Qs + kUQBytes, *Vb = Kb + 2 * kUKBytes, *Ps = Vb + 2 * kUVBytes;
+    float *scales = reinterpret_cast<float *>(Ps + kUPBytes);
+    uint64_t *bar_s = reinterpret_cast<uint64_t *>(scales + 2 * kUScaleFloats), *bar_pv = bar_s + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_pv + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t tid = threadIdx.x, warp = tid / 32;
+    const int h = blockIdx.y, b = blockIdx.z, kvh = h / dm.group;
+    const size_t plane = (size_t)b * dm.KV + kvh;
+    // under causal masking the last query tiles have the most key blocks: start them first
+    const int q_tile = causal ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
+    const int q0 = q_tile * kUQ, i = q0 + (int)tid;
+    const bool valid = i < (int)dm.Sq;
+    const size_t row_base = ((size_t)b * dm.H + h) * dm.Sq;
+    const int S = (int)dm.Skv, n_blocks = (int)a.n_blocks;
+
+    if (tid == 0) {
+        mbar_init(bar_s, 1);
+        mbar_init(bar_pv, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kUTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot, my_tmem = tmem_base + ((warp * 32) << 16);
+
+    // 16-byte piece `piece` of row `row` of a swizzled tile
+    auto swz = [](uint8_t *tile, int row, int piece) { return tile + row * 128 + ((piece ^ (row & 7)) << 4); };
+    // Iteration `it` (keys 128 it ..) into buffer `buf`.  Keys past the end of the sequence and
+    // blocks past the last one re-read the last valid ones (their scores are masked before use).
+    auto stage = [&](int it, int buf) {
+        uint8_t *Kt = Kb + buf * kUKBytes, *Vt = Vb + buf * kUVBytes;
+        float *kscale = scales + buf * kUScaleFloats, *vscale = kscale + kUKeys, *mscale = vscale + 2 * kUD;
+        const int j0 = it * kUKeys;
+        for (int idx = tid; idx < kUKeys * 8; idx += kUQ) {
+            const int key = idx / 8, piece = idx % 8;
+            cp_async16(swz(Kt, key, piece), a.kc + (plane * S + min(j0 + key, S - 1)) * a.dpad + piece * 16);
+        }
+        {   // 2 x 8 mean-digit rows, 8 pieces each: one piece per thread
+            const int blk = tid / 64, row = (tid / 8) % 8, piece = tid % 8;
+            const int jb = min(2 * it + blk, n_blocks - 1);
+            cp_async16(swz(Kt, kUKeys + 8 * blk + row, piece),
+                       a.kmean_digits + ((plane * n_blocks + jb) * 8 + row) * (size_t)a.dpad + piece * 16);
+        }
+        for (int idx = tid; idx < kUD * 8; idx += kUQ) {
+            const int ch = idx / 8, piece = idx % 8, blk = piece / 4;
+            const int jb = min(2 * it + blk, n_blocks - 1);
+            cp_async16(swz(Vt, ch, piece), a.vc + ((plane * n_blocks + jb) * (size_t)kUD + ch) * a.bpad + (piece % 4) * 16);
+        }
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(kscale + tid)),
+                     "l"(a.ks + plane * S + min(j0 + (int)tid, S - 1))
+                     : "memory");
+        if (tid < 64) {
+            const int blk = tid / 32, jb = min(2 * it + blk, n_blocks - 1);
+            cp_async16(vscale + blk * kUD + (tid % 32) * 4, a.vs + (plane * n_blocks + jb) * (size_t)kUD + (tid % 32) * 4);
+        }
+        if (tid < 2)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(mscale + tid)),
+                         "l"(a.kmean_scale + plane * n_blocks + min(2 * it + (int)tid, n_blocks - 1))
+                         : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    const int i_blk_max = min((int)dm.Sq - 1, q0 + kUQ - 1);
+    const int jb_hi = causal ? i_blk_max / kUBlk + 1 : n_blocks;
+    const int n_it = (jb_hi + 1) / 2;
+    for (int idx = tid; idx < kUQ * 8; idx += kUQ) {
+        const int row = idx / 8, piece = idx % 8;
+        cp_async16(swz(Qs, row, piece), a.qc + (row_base + min(q0 + row, (int)dm.Sq - 1)) * a.dpad + piece * 16);
+    }
+    if (n_it > 0) stage(0, 0);  // (in one group with Q)
+    const float dq = valid ? a.qs[row_base + i] : 1.f;
+
+    float o[kUD];
+#pragma unroll
+    for (int c = 0; c < kUD; ++c) o[c] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    const uint32_t idesc_s = umma_idesc_i8(kUSRows), idesc_pv = umma_idesc_i8(kUD);
+    const uint32_t limit = wait_limit ? wait_limit : kUWaitLimitDefault;
+    uint32_t phase = 0;
+    bool dead = false;
+    for (int it = 0; it < n_it && !dead; ++it) {
+        const int buf = it & 1;
+        if (it + 1 < n_it) {
+            stage(it + 1, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        // this thread's pieces have landed and its tensor-memory reads of the last iteration are
+        // complete; after the barrier that holds for the CTA, and the tiles may be read by the
+        // tensor core (async proxy)
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        uint8_t *Kt = Kb + buf * kUKBytes, *Vt = Vb + buf * kUVBytes;
+        const float *kscale = scales + buf * kUScaleFloats, *vscale = kscale + kUKeys, *mscale = vscale + 2 * kUD;
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int k = 0; k < kUD / 32; ++k)
+                umma_i8(tmem_base, umma_desc(smem_u32(Qs) + k * 32), umma_desc(smem_u32(Kt) + k * 32), idesc_s, k != 0);
+            umma_commit(bar_s);
+        }
+        __syncwarp();
+        // (the verdict is taken by the whole CTA: nobody goes on to a barrier the others have left)
+        if (!__syncthreads_and(mbar_wait(bar_s, phase, abort_flag, limit))) {
+            dead = true;
+            break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+        // ---- the two Sage blocks of the iteration, one after the other
+        float alpha[2];
+        uint32_t v[32];
+        tmem_ld32(my_tmem + kUKeys, v);  // the mean-digit columns (three per block are meaningful)
+        tmem_ld_wait();
+        float shift[2];
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk)
+            shift[blk] = (((float)(int)v[8 * blk] * 65536.f + (float)(int)v[8 * blk + 1] * 256.f) +
+                          (float)(int)v[8 * blk + 2]) * mscale[blk] * dq;
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            const int jb = 2 * it + blk, j0 = jb * kUBlk, kj = min(kUBlk, S - j0);
+            const bool live = jb < jb_hi;
+            float s[kUBlk];
+            float mn = m;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                tmem_ld32(my_tmem + kUBlk * blk + 32 * half, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const int kk = 32 * half + e, j = j0 + kk;
+                    float sc = fmaf((float)(int)v[e] * dq, kscale[kUBlk * blk + kk], shift[blk]);
+                    if (!live || kk >= kj || !valid || (causal && j > i)) sc = -INFINITY;
+                    s[kk] = sc;
+                    mn = fmaxf(mn, sc);
+                }
+            }
+            alpha[blk] = (mn == -INFINITY) ? 0.f : expf(m - mn);
+            // P scaled by 127 (the static P scale): 127 exp(s - m) = exp2(s log2e - m log2e + log2 127)
+            constexpr float kLog2e = 1.4426950408889634f, kLog2_127 = 6.988684686772166f;
+            const float off = (mn == -INFINITY) ? -INFINITY : kLog2_127 - mn * kLog2e;
+            float es = 0.f;
+#pragma unroll
+            for (int piece = 0; piece < 4; ++piece) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    int c[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float pe = (mn == -INFINITY) ? 0.f : exp2f(fmaf(s[16 * piece + 4 * q + e], kLog2e, off));
+                        es += pe;
+                        c[e] = __float2int_rn(pe);  // in [0, 127]: rounds to nearest even like rint
+                    }
+                    w[q] = pack_codes(c);
+                }
+                *reinterpret_cast<uint4 *>(swz(Ps, (int)tid, 4 * blk + piece)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l = alpha[blk] * l + es;
+            if (mn != -INFINITY) m = mn;
+        }
+        // ---- PV: S has been read out, the accumulators may take its place
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+                for (int k = 0; k < 2; ++k)
+                    umma_i8(tmem_base + kUD * blk, umma_desc(smem_u32(Ps) + (2 * blk + k) * 32),
+                            umma_desc(smem_u32(Vt) + (2 * blk + k) * 32), idesc_pv, k != 0);
+            umma_commit(bar_pv);
+        }
+        __syncwarp();
+        if (!__syncthreads_and(mbar_wait(bar_pv, phase, abort_flag, limit))) {
+            dead = true;
+            break;
+        }
+        phase ^= 1;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            if (2 * it + blk >= jb_hi) break;  // (the same for the whole CTA)
+#pragma unroll
+            for (int c0 = 0; c0 < kUD; c0 += 32) {
+                tmem_ld32(my_tmem + kUD * blk + c0, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e)
+                    o[c0 + e] = fmaf(alpha[blk], o[c0 + e], (float)(int)v[e] * vscale[kUD * blk + c0 + e]);
+            }
+        }
+    }
+    if (dead) *abort_flag = 1;
+    if (valid && !dead) {
+        float *dst = a.out + (row_base + i) * kUD;
+#pragma unroll
+        for (int c = 0; c < kUD; c += 4)
+            *reinterpret_cast<float4 *>(dst + c) = make_float4(o[c] / l, o[c + 1] / l, o[c + 2] / l, o[c + 3] / l);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kUTmemCols)
+                     : "memory");
+    if (tid == 0 && *abort_flag) atomicOr(error, 1);
+}
+
 // ------------------------------------------------------------------ host side
 std::string shape_debug(const qk_attention_shape *s) {
     // Rust's `{:?}` of AttentionShape (gpu_attention.rs:402-411)
@@ -864,7 +1131,8 @@ size_t sage_scratch_bytes(const qk_attention_shape *s, size_t block_size) {
 struct SageLayout {
     size_t block, n_blocks, wpl, dpad, bpad, planes, qrows;
     size_t o_qc, o_qs, o_kc, o_ks, o_km, o_vc, o_vs, o_md, o_ms;
-    bool tc;
+    bool tc;    // a tensor-core kernel runs: the mean digit rows are produced
+    bool umma;  // ... the tcgen05 one, which reads the V codes in plain key order
 };
 SageLayout sage_layout(const qk_ctx *c, const AttnDims &dm, size_t block_size) {
     SageLayout L{};
@@ -887,6 +1155,7 @@ SageLayout sage_layout(const qk_ctx *c, const AttnDims &dm, size_t block_size) {
     L.o_vc = take(L.planes * L.n_blocks * dm.dv * L.bpad), L.o_vs = take(L.planes * L.n_blocks * dm.dv * 4);
     L.o_md = take(L.planes * L.n_blocks * 8 * L.dpad), L.o_ms = take(L.planes * L.n_blocks * 4);
     L.tc = c->sage_kernel != 0 && sage_tc_eligible(dm, block_size);
+    L.umma = L.tc && c->sage_kernel == 2 && dm.d == kUD && dm.dv == kUD && block_size == kUBlk;
     return L;
 }
 
@@ -907,7 +1176,7 @@ qk_status sage_quantize_dev(qk_ctx *c, const float *dq, const float *dk, const f
     QK_CUDA(cudaGetLastError());
     sage_quant_v_kernel<<<kgrid, 128, 0, c->stream>>>(
         dv, (int8_t *)(base + L.o_vc), (float *)(base + L.o_vs), (uint32_t)S, dm.dv,
-        (uint32_t)L.block, (uint32_t)L.bpad, (uint32_t)L.n_blocks, L.tc ? 1 : 0);
+        (uint32_t)L.block, (uint32_t)L.bpad, (uint32_t)L.n_blocks, L.tc && !L.umma ? 1 : 0);
     QK_CUDA(cudaGetLastError());
     c->launches += 3;
     return QK_OK;
@@ -927,6 +1196,18 @@ qk_status attention_sage_dev(qk_ctx *c, const float *dq, const float *dk, const 
                (const float *)(base + L.o_ms),  (const int8_t *)(base + L.o_vc),
                (const float *)(base + L.o_vs),  out,
                (uint32_t)L.dpad, (uint32_t)L.bpad, (uint32_t)L.block, (uint32_t)L.n_blocks};
+    if (L.umma) {
+        if ((st = qk::error_word(c)) != QK_OK) return st;
+        c->err_armed = true;
+        QK_CUDA(cudaFuncSetAttribute(attention_sage_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)(kUSmemBytes + 1024)));
+        dim3 grid((unsigned)qk::ceil_div(dm.Sq, kUQ), dm.H, dm.B);
+        attention_sage_umma_kernel<<<grid, kUQ, kUSmemBytes + 1024, c->stream>>>(a, dm, causal, c->wait_limit,
+                                                                                 (int *)c->d_err.ptr);
+        QK_CUDA(cudaGetLastError());
+        c->launches++;
+        return QK_OK;
+    }
     if (L.tc)
         return dm.d == 64 ? launch_sage_tc_block<2>(c, a, dm, causal) : launch_sage_tc_block<4>(c, a, dm, causal);
     if (L.wpl == 1) return launch_sage<1>(c, a, dm, causal);
@@ -1088,7 +1369,7 @@ qk_status qk_gpu_sage_quantize(qk_ctx *ctx, const qk_attention_shape *shape, con
                 const int8_t *row = vc + ((p * L.n_blocks + jb) * dv_ + ch) * L.bpad;
                 for (size_t kk = 0; kk < L.block && jb * L.block + kk < S; ++kk)
                     v_codes[(p * S + jb * L.block + kk) * dv_ + ch] =
-                        row[L.tc ? sage_tc_key_slot((uint32_t)kk) : kk];
+                        row[L.tc && !L.umma ? sage_tc_key_slot((uint32_t)kk) : kk];
             }
     return QK_OK;
 }
@@ -1098,7 +1379,7 @@ int32_t qk_set_sage_kernel(qk_ctx *ctx, int32_t which) {
     if (qk::resolve_ctx(ctx, &c) != QK_OK) return -1;
     std::lock_guard<std::mutex> lock(c->mu);
     const int32_t before = c->sage_kernel;
-    if (which == 0 || which == 1) c->sage_kernel = which;
+    if (which >= 0 && which <= 2) c->sage_kernel = which;
     return before;
 }
 

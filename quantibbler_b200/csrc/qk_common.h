@@ -53,7 +53,7 @@ struct qk_ctx {
     std::mutex mu;  // serialises calls from several host threads
     int sm_count = 0;
     int gemv_kernel = 1;  // 0 sign-select, 1 bit-sliced INT8 tensor core
-    int sage_kernel = 1;  // 0 dp4a, 1 INT8 tensor core where the shape allows
+    int sage_kernel = 2;  // 0 dp4a, 1 INT8 tensor core (mma.sync), 2 tcgen05 kind::i8 where the shape allows, else 1
     int decode_attention_kernel = 1;  // 0 scalar, 1 bf16 tensor core where the cache allows
     std::atomic<uint64_t> launches{0};
     // staging for the host-buffer entry points

@@ -786,6 +786,7 @@ qk_status qk_decode_step_run(qk_ctx *ctx, const qk_decode_step *step) {
     if (step->device != c->device)
         return qk::fail(QK_ERR_VALUE, "the step lives on device %d, the context on %d", step->device, c->device);
     if ((st = qk::error_word(c)) != QK_OK) return st;
+    c->err_armed = true;
     StepArgs a = step->args;
     a.error = (int *)c->d_err.ptr;
     a.wait_limit = c->wait_limit ? c->wait_limit : kStepWaitLimitDefault;

@@ -38,6 +38,7 @@
 #include <cstring>
 
 #include "qk_common.h"
+#include "qk_umma.cuh"
 
 namespace {
 
@@ -57,40 +58,6 @@ constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kTmemCols = 2 * kBNMax;    // two accumulators
 constexpr uint32_t kWaitLimitDefault = 1u << 22;  // polls; qk_set_wait_limit overrides it
 
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait: false if the phase did not complete within the limit, or if another role of
-// the CTA has already given up.  The verdict is WARP-UNIFORM: every lane polls until it either
-// sees the phase or runs out of polls, then the warp votes, so that no lane can leave a loop
-// that the rest of its warp stays in (the instructions that follow a wait - tcgen05.ld,
-// __syncwarp, named barriers - need the whole warp).  Call it with all 32 lanes.
-__device__ __forceinline__ bool mbar_wait_lane(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                               uint32_t limit) {
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < limit; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-            " selp.u32 %0, 1, 0, p;\n}"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-        if ((i & 255u) == 255u && *abort_flag) return false;
-    }
-    return false;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                          uint32_t limit) {
-    return __all_sync(0xffffffffu, mbar_wait_lane(bar, parity, abort_flag, limit)) != 0;
-}
 // The four epilogue warps agree on a verdict (named barrier 1 with an AND reduction): either
 // all of them go on, or all of them leave, so that none is left waiting at one of the
 // epilogue's own barriers for a warp that has gone.
@@ -103,21 +70,6 @@ __device__ __forceinline__ bool epilogue_vote(bool ok, uint32_t n_threads) {
         : "r"((uint32_t)ok), "r"(n_threads)
         : "memory");
     return all != 0;
-}
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                     smem_u32(bar))
-                 : "memory");
-}
-// UMMA shared-memory descriptor for a K-major, 128-byte-swizzled tile whose rows are 128
-// bytes and whose 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);   // start address
-    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset: 8 rows
-    d |= (uint64_t)1 << 46;                        // descriptor version
-    d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
-    return d;
 }
 // Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = bn.
 __device__ __forceinline__ uint32_t umma_idesc(uint32_t bn) {

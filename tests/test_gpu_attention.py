@@ -272,18 +272,55 @@ def test_sage_tensor_core_kernel_matches_dp4a_kernel(gpu_ctx, case):
     k = rng.standard_normal((b, kvh, s, d), dtype=np.float32) \
         + (2.0 * rng.standard_normal((1, kvh, 1, d))).astype(np.float32)
     v = rng.standard_normal((b, kvh, s, d), dtype=np.float32)
-    assert gpu_ctx.set_sage_kernel(0) == 1
+    default = gpu_ctx.set_sage_kernel(0)
+    assert default == 2
     try:
         simt = run_sage(gpu_ctx, q, k, v, causal, block)
-    finally:
         gpu_ctx.set_sage_kernel(1)
-    tc = run_sage(gpu_ctx, q, k, v, causal, block)
-    assert np.isfinite(tc).all()
-    assert np.median(np.abs(tc - simt)) <= 1e-6
-    assert np.abs(tc - simt).max() <= 2e-3 * np.abs(simt).max()
+        tc = run_sage(gpu_ctx, q, k, v, causal, block)
+        assert np.isfinite(tc).all()
+        assert np.median(np.abs(tc - simt)) <= 1e-6
+        assert np.abs(tc - simt).max() <= 2e-3 * np.abs(simt).max()
+        w32 = anp.attention_sage(q, k, v, causal=causal, block_size=block, ft=np.float32)
+        assert np.abs(tc - w32).max() <= 2e-3 * np.abs(w32).max()
+        assert np.array_equal(tc, run_sage(gpu_ctx, q, k, v, causal, block))
+    finally:
+        gpu_ctx.set_sage_kernel(default)
+
+
+@pytest.mark.parametrize("case", [
+    # (batch, heads, kv heads, seq, causal): head_dim 128, key block 64, the shapes the tcgen05 kernel takes
+    (1, 4, 2, 200, True), (1, 2, 1, 320, False), (2, 8, 2, 1000, True), (1, 2, 2, 64, True), (1, 1, 1, 129, False)])
+def test_sage_tcgen05_kernel_matches_the_other_kernels(gpu_ctx, case):
+    """Sage with both integer products on tcgen05 (kind::i8, accumulators in tensor memory)
+    against the mma.sync kernel: the same scores, maxima and P codes, hence the same integer
+    PV sums; only the order in which a row's P values are added into l differs.  Ragged last
+    blocks, an odd number of key blocks (the second block of the last iteration is empty),
+    several query tiles, GQA, causal and not."""
+    b, h, kvh, s, causal = case
+    d, block = 128, 64
+    rng = np.random.default_rng(sum(case[:4]) + 7)
+    q = rng.standard_normal((b, h, s, d), dtype=np.float32)
+    k = rng.standard_normal((b, kvh, s, d), dtype=np.float32) \
+        + (2.0 * rng.standard_normal((1, kvh, 1, d))).astype(np.float32)
+    v = rng.standard_normal((b, kvh, s, d), dtype=np.float32)
+    default = gpu_ctx.set_sage_kernel(1)
+    try:
+        tc = run_sage(gpu_ctx, q, k, v, causal, block)
+        gpu_ctx.set_sage_kernel(2)
+        um = run_sage(gpu_ctx, q, k, v, causal, block)
+        gpu_ctx.synchronize()
+    finally:
+        gpu_ctx.set_sage_kernel(default)
+    assert np.isfinite(um).all()
+    assert np.abs(um - tc).max() <= 1e-5 * np.abs(tc).max()
     w32 = anp.attention_sage(q, k, v, causal=causal, block_size=block, ft=np.float32)
-    assert np.abs(tc - w32).max() <= 2e-3 * np.abs(w32).max()
-    assert np.array_equal(tc, run_sage(gpu_ctx, q, k, v, causal, block))
+    assert np.abs(um - w32).max() <= 2e-3 * np.abs(w32).max()
+    gpu_ctx.set_sage_kernel(2)
+    try:
+        assert np.array_equal(um, run_sage(gpu_ctx, q, k, v, causal, block))
+    finally:
+        gpu_ctx.set_sage_kernel(default)
 
 
 def test_attention_on_device_buffers(gpu_ctx):
