@@ -719,9 +719,12 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
 // The same arithmetic once more, with both integer products on the 5th-generation tensor
 // cores: tcgen05.mma kind::i8 (s8 x s8 -> s32) with the accumulators in tensor memory.  Built
 // for head_dim = val_dim = 128 and the Sage key block of 64 (benchmark configuration 2).
-//   * A CTA of 128 threads owns 128 queries; thread r is query row r and tensor-memory lane r,
-//     so everything per row (maximum, sum, the 128 output channels) lives in one thread and
-//     needs no shuffles.
+//   * A CTA owns 128 queries; query row r is tensor-memory lane r.  Its 512 threads are four
+//     groups of 128: thread (g, r) works on row r's score columns 32 g .. 32 g + 31 of the
+//     iteration (groups 0, 1: the first Sage block; 2, 3: the second) and on output channels
+//     32 g .. 32 g + 31.  What a row's four threads have to agree on (the blocks' maxima and
+//     sums of P) goes through shared memory; every thread then derives the same running
+//     maximum, alphas and l.
 //   * One iteration covers TWO Sage blocks (128 keys): S = Qhat [Khat_a; Khat_b; mean digits]^T
 //     is one 128 x 144 x 128 product (the sixteen extra B rows are the digit rows of the two
 //     blocks' channel means, which give the per-row shift), then the online softmax runs block
@@ -732,14 +735,14 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
 //     Q and K rows are 128 channels, P and V rows are the iteration's 128 keys, V_a and V_b
 //     side by side), double-buffered across iterations.  The P codes go from registers to
 //     shared memory and are the A operand of PV.
-//   * Two such CTAs share an SM (256 tensor-memory columns, ~106 KB of shared memory each), so
-//     one CTA's softmax overlaps the other's products.
 // All waits on the MMA barriers are bounded (bit 1 of the context's error word on expiry).
 constexpr int kUQ = 128, kUBlk = 64, kUKeys = 2 * kUBlk, kUD = 128;
+constexpr int kUThreads = 512, kUGroups = kUThreads / kUQ;
 constexpr int kUSRows = kUKeys + 16;  // keys + 2 x 8 mean-digit rows: N of the S product
 constexpr uint32_t kUQBytes = kUQ * 128, kUKBytes = kUSRows * 128, kUVBytes = kUD * 128, kUPBytes = kUQ * 128;
 constexpr uint32_t kUScaleFloats = kUKeys + 2 * kUD + 16;  // key scales, two sets of channel scales, two mean units
-constexpr uint32_t kUSmemBytes = kUQBytes + 2 * kUKBytes + 2 * kUVBytes + kUPBytes + 2 * kUScaleFloats * 4 + 64;
+constexpr uint32_t kUSmemBytes = kUQBytes + 2 * kUKBytes + 2 * kUVBytes + kUPBytes + 2 * kUScaleFloats * 4 +
+                                 2 * kUGroups * kUQ * 4 + 64;
 constexpr uint32_t kUTmemCols = 256;
 constexpr uint32_t kUWaitLimitDefault = 1u << 22;
 
@@ -755,23 +758,31 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
-__global__ void __launch_bounds__(kUQ, 2)
+__global__ void __launch_bounds__(kUThreads, 1)
 attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_limit, int *error) {
     extern __shared__ __align__(1024) uint8_t sm_u_raw[];
     // (the swizzled tiles want 1024-byte alignment; the launch asks for 1 KB more than kUSmemBytes)
     uint8_t *sm_u = sm_u_raw + ((1024 - (smem_u32(sm_u_raw) & 1023)) & 1023);
     uint8_t *Qs = sm_u, *Kb = Qs + kUQBytes, *Vb = Kb + 2 * kUKBytes, *Ps = Vb + 2 * kUVBytes;
     float *scales = reinterpret_cast<float *>(Ps + kUPBytes);
-    uint64_t *bar_s = reinterpret_cast<uint64_t *>(scales + 2 * kUScaleFloats), *bar_pv = bar_s + 1;
+    float *xm = scales + 2 * kUScaleFloats, *xe = xm + kUGroups * kUQ;  // [group][row]: block maxima, sums of P
+    uint64_t *bar_s = reinterpret_cast<uint64_t *>(xe + kUGroups * kUQ), *bar_pv = bar_s + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_pv + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t tid = threadIdx.x, warp = tid / 32;
+    const uint32_t g = tid / kUQ, r = tid % kUQ;  // column group, query row
+    const int my_blk = g / 2;
     const int h = blockIdx.y, b = blockIdx.z, kvh = h / dm.group;
     const size_t plane = (size_t)b * dm.KV + kvh;
     // under causal masking the last query tiles have the most key blocks: start them first
     const int q_tile = causal ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
-    const int q0 = q_tile * kUQ, i = q0 + (int)tid;
+    const int q0 = q_tile * kUQ, i = q0 + (int)r;
     const bool valid = i < (int)dm.Sq;
     const size_t row_base = ((size_t)b * dm.H + h) * dm.Sq;
     const int S = (int)dm.Skv, n_blocks = (int)a.n_blocks;
@@ -791,7 +802,8 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_base = *tmem_slot, my_tmem = tmem_base + ((warp * 32) << 16);
+    // a warp reaches the 32 lanes (rows) 32 (warp % 4) ..; the groups differ in their columns
+    const uint32_t tmem_base = *tmem_slot, my_tmem = tmem_base + (((warp % 4) * 32) << 16);
 
     // 16-byte piece `piece` of row `row` of a swizzled tile
     auto swz = [](uint8_t *tile, int row, int piece) { return tile + row * 128 + ((piece ^ (row & 7)) << 4); };
@@ -801,31 +813,32 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
         uint8_t *Kt = Kb + buf * kUKBytes, *Vt = Vb + buf * kUVBytes;
         float *kscale = scales + buf * kUScaleFloats, *vscale = kscale + kUKeys, *mscale = vscale + 2 * kUD;
         const int j0 = it * kUKeys;
-        for (int idx = tid; idx < kUKeys * 8; idx += kUQ) {
+        for (int idx = tid; idx < kUKeys * 8; idx += kUThreads) {
             const int key = idx / 8, piece = idx % 8;
             cp_async16(swz(Kt, key, piece), a.kc + (plane * S + min(j0 + key, S - 1)) * a.dpad + piece * 16);
         }
-        {   // 2 x 8 mean-digit rows, 8 pieces each: one piece per thread
+        if (tid < 128) {  // 2 x 8 mean-digit rows, 8 pieces each
             const int blk = tid / 64, row = (tid / 8) % 8, piece = tid % 8;
             const int jb = min(2 * it + blk, n_blocks - 1);
             cp_async16(swz(Kt, kUKeys + 8 * blk + row, piece),
                        a.kmean_digits + ((plane * n_blocks + jb) * 8 + row) * (size_t)a.dpad + piece * 16);
         }
-        for (int idx = tid; idx < kUD * 8; idx += kUQ) {
+        for (int idx = tid; idx < kUD * 8; idx += kUThreads) {
             const int ch = idx / 8, piece = idx % 8, blk = piece / 4;
             const int jb = min(2 * it + blk, n_blocks - 1);
             cp_async16(swz(Vt, ch, piece), a.vc + ((plane * n_blocks + jb) * (size_t)kUD + ch) * a.bpad + (piece % 4) * 16);
         }
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(kscale + tid)),
-                     "l"(a.ks + plane * S + min(j0 + (int)tid, S - 1))
-                     : "memory");
-        if (tid < 64) {
-            const int blk = tid / 32, jb = min(2 * it + blk, n_blocks - 1);
-            cp_async16(vscale + blk * kUD + (tid % 32) * 4, a.vs + (plane * n_blocks + jb) * (size_t)kUD + (tid % 32) * 4);
+        if (tid >= 128 && tid < 256)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(kscale + (tid - 128))),
+                         "l"(a.ks + plane * S + min(j0 + (int)tid - 128, S - 1))
+                         : "memory");
+        if (tid >= 256 && tid < 320) {
+            const int t2 = tid - 256, blk = t2 / 32, jb = min(2 * it + blk, n_blocks - 1);
+            cp_async16(vscale + blk * kUD + (t2 % 32) * 4, a.vs + (plane * n_blocks + jb) * (size_t)kUD + (t2 % 32) * 4);
         }
-        if (tid < 2)
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(mscale + tid)),
-                         "l"(a.kmean_scale + plane * n_blocks + min(2 * it + (int)tid, n_blocks - 1))
+        if (tid >= 320 && tid < 322)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(mscale + (tid - 320))),
+                         "l"(a.kmean_scale + plane * n_blocks + min(2 * it + (int)tid - 320, n_blocks - 1))
                          : "memory");
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -833,16 +846,16 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
     const int i_blk_max = min((int)dm.Sq - 1, q0 + kUQ - 1);
     const int jb_hi = causal ? i_blk_max / kUBlk + 1 : n_blocks;
     const int n_it = (jb_hi + 1) / 2;
-    for (int idx = tid; idx < kUQ * 8; idx += kUQ) {
+    for (int idx = tid; idx < kUQ * 8; idx += kUThreads) {
         const int row = idx / 8, piece = idx % 8;
         cp_async16(swz(Qs, row, piece), a.qc + (row_base + min(q0 + row, (int)dm.Sq - 1)) * a.dpad + piece * 16);
     }
     if (n_it > 0) stage(0, 0);  // (in one group with Q)
     const float dq = valid ? a.qs[row_base + i] : 1.f;
 
-    float o[kUD];
+    float o[32];  // channels 32 g .. 32 g + 31 of row r
 #pragma unroll
-    for (int c = 0; c < kUD; ++c) o[c] = 0.f;
+    for (int c = 0; c < 32; ++c) o[c] = 0.f;
     float m = -INFINITY, l = 0.f;
     const uint32_t idesc_s = umma_idesc_i8(kUSRows), idesc_pv = umma_idesc_i8(kUD);
     const uint32_t limit = wait_limit ? wait_limit : kUWaitLimitDefault;
@@ -879,59 +892,79 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-        // ---- the two Sage blocks of the iteration, one after the other
-        float alpha[2];
+        // ---- this thread's 32 scores of its Sage block
+        const int jb = 2 * it + my_blk, j0 = jb * kUBlk, kj = min(kUBlk, S - j0);
+        const bool live = jb < jb_hi;
         uint32_t v[32];
-        tmem_ld32(my_tmem + kUKeys, v);  // the mean-digit columns (three per block are meaningful)
-        tmem_ld_wait();
-        float shift[2];
-#pragma unroll
-        for (int blk = 0; blk < 2; ++blk)
-            shift[blk] = (((float)(int)v[8 * blk] * 65536.f + (float)(int)v[8 * blk + 1] * 256.f) +
-                          (float)(int)v[8 * blk + 2]) * mscale[blk] * dq;
-#pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-            const int jb = 2 * it + blk, j0 = jb * kUBlk, kj = min(kUBlk, S - j0);
-            const bool live = jb < jb_hi;
-            float s[kUBlk];
-            float mn = m;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                tmem_ld32(my_tmem + kUBlk * blk + 32 * half, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const int kk = 32 * half + e, j = j0 + kk;
-                    float sc = fmaf((float)(int)v[e] * dq, kscale[kUBlk * blk + kk], shift[blk]);
-                    if (!live || kk >= kj || !valid || (causal && j > i)) sc = -INFINITY;
-                    s[kk] = sc;
-                    mn = fmaxf(mn, sc);
-                }
-            }
-            alpha[blk] = (mn == -INFINITY) ? 0.f : expf(m - mn);
-            // P scaled by 127 (the static P scale): 127 exp(s - m) = exp2(s log2e - m log2e + log2 127)
-            constexpr float kLog2e = 1.4426950408889634f, kLog2_127 = 6.988684686772166f;
-            const float off = (mn == -INFINITY) ? -INFINITY : kLog2_127 - mn * kLog2e;
-            float es = 0.f;
-#pragma unroll
-            for (int piece = 0; piece < 4; ++piece) {
-                uint32_t w[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    int c[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float pe = (mn == -INFINITY) ? 0.f : exp2f(fmaf(s[16 * piece + 4 * q + e], kLog2e, off));
-                        es += pe;
-                        c[e] = __float2int_rn(pe);  // in [0, 127]: rounds to nearest even like rint
-                    }
-                    w[q] = pack_codes(c);
-                }
-                *reinterpret_cast<uint4 *>(swz(Ps, (int)tid, 4 * blk + piece)) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-            l = alpha[blk] * l + es;
-            if (mn != -INFINITY) m = mn;
+        float shift;
+        {
+            uint32_t c0, c1, c2, c3;
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
+                         : "r"(my_tmem + kUKeys + 8 * my_blk)
+                         : "memory");
+            tmem_ld32(my_tmem + 32 * g, v);
+            tmem_ld_wait();
+            (void)c3;
+            shift = (((float)(int)c0 * 65536.f + (float)(int)c1 * 256.f) + (float)(int)c2) * mscale[my_blk] * dq;
         }
+        // only the iteration on the diagonal, the last one of a ragged sequence, a tile with rows
+        // past the end and a missing second block need the per-element mask
+        const int it_j0 = it * kUKeys;
+        const bool masked = it_j0 + kUKeys > S || q0 + kUQ > (int)dm.Sq || !live || 2 * it + 1 >= jb_hi ||
+                            (causal && it_j0 + kUKeys - 1 > q0);
+        float s[32];
+        float bm = -INFINITY;
+        const float *ksc = kscale + 32 * g;
+        if (masked) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                const int kk = 32 * (int)(g % 2) + e, j = j0 + kk;
+                float sc = fmaf((float)(int)v[e] * dq, ksc[e], shift);
+                if (!live || kk >= kj || !valid || (causal && j > i)) sc = -INFINITY;
+                s[e] = sc;
+                bm = fmaxf(bm, sc);
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                s[e] = fmaf((float)(int)v[e] * dq, ksc[e], shift);
+                bm = fmaxf(bm, s[e]);
+            }
+        }
+        xm[g * kUQ + r] = bm;
+        __syncthreads();
+        // ---- the row's maxima after block a and after block b (the same in its four threads)
+        const float bm_a = fmaxf(xm[r], xm[kUQ + r]), bm_b = fmaxf(xm[2 * kUQ + r], xm[3 * kUQ + r]);
+        const float mn_a = fmaxf(m, bm_a);
+        const float alpha_a = (mn_a == -INFINITY) ? 0.f : expf(m - mn_a);
+        const float m_a = (mn_a == -INFINITY) ? m : mn_a;
+        const float mn_b = fmaxf(m_a, bm_b);
+        const float alpha_b = (mn_b == -INFINITY) ? 0.f : expf(m_a - mn_b);
+        const float m_b = (mn_b == -INFINITY) ? m_a : mn_b;
+        const float mn = my_blk ? mn_b : mn_a;
+        // P scaled by 127 (the static P scale): 127 exp(s - m) = exp2(s log2e - m log2e + log2 127)
+        constexpr float kLog2e = 1.4426950408889634f, kLog2_127 = 6.988684686772166f;
+        const float off = (mn == -INFINITY) ? -INFINITY : kLog2_127 - mn * kLog2e;
+        float es = 0.f;
+#pragma unroll
+        for (int piece = 0; piece < 2; ++piece) {
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                int c[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    // a masked score is -inf: ex2 gives 0; a row without any key so far has mn = -inf
+                    const float pe = (mn == -INFINITY) ? 0.f : ex2_approx(fmaf(s[16 * piece + 4 * q + e], kLog2e, off));
+                    es += pe;
+                    c[e] = __float2int_rn(pe);  // in [0, 127]: rounds to nearest even like rint
+                }
+                w[q] = pack_codes(c);
+            }
+            *reinterpret_cast<uint4 *>(swz(Ps, (int)r, 2 * g + piece)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        xe[g * kUQ + r] = es;
         // ---- PV: S has been read out, the accumulators may take its place
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -947,6 +980,9 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
             umma_commit(bar_pv);
         }
         __syncwarp();
+        l = alpha_a * l + (xe[r] + xe[kUQ + r]);
+        l = alpha_b * l + (xe[2 * kUQ + r] + xe[3 * kUQ + r]);
+        m = m_b;
         if (!__syncthreads_and(mbar_wait(bar_pv, phase, abort_flag, limit))) {
             dead = true;
             break;
@@ -956,21 +992,19 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
 #pragma unroll
         for (int blk = 0; blk < 2; ++blk) {
             if (2 * it + blk >= jb_hi) break;  // (the same for the whole CTA)
+            tmem_ld32(my_tmem + kUD * blk + 32 * g, v);
+            tmem_ld_wait();
+            const float al = blk ? alpha_b : alpha_a;
+            const float *vd = vscale + kUD * blk + 32 * g;
 #pragma unroll
-            for (int c0 = 0; c0 < kUD; c0 += 32) {
-                tmem_ld32(my_tmem + kUD * blk + c0, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int e = 0; e < 32; ++e)
-                    o[c0 + e] = fmaf(alpha[blk], o[c0 + e], (float)(int)v[e] * vscale[kUD * blk + c0 + e]);
-            }
+            for (int e = 0; e < 32; ++e) o[e] = fmaf(al, o[e], (float)(int)v[e] * vd[e]);
         }
     }
     if (dead) *abort_flag = 1;
     if (valid && !dead) {
-        float *dst = a.out + (row_base + i) * kUD;
+        float *dst = a.out + (row_base + i) * kUD + 32 * g;
 #pragma unroll
-        for (int c = 0; c < kUD; c += 4)
+        for (int c = 0; c < 32; c += 4)
             *reinterpret_cast<float4 *>(dst + c) = make_float4(o[c] / l, o[c + 1] / l, o[c + 2] / l, o[c + 3] / l);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -1202,7 +1236,7 @@ qk_status attention_sage_dev(qk_ctx *c, const float *dq, const float *dk, const 
         QK_CUDA(cudaFuncSetAttribute(attention_sage_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)(kUSmemBytes + 1024)));
         dim3 grid((unsigned)qk::ceil_div(dm.Sq, kUQ), dm.H, dm.B);
-        attention_sage_umma_kernel<<<grid, kUQ, kUSmemBytes + 1024, c->stream>>>(a, dm, causal, c->wait_limit,
+        attention_sage_umma_kernel<<<grid, kUThreads, kUSmemBytes + 1024, c->stream>>>(a, dm, causal, c->wait_limit,
                                                                                  (int *)c->d_err.ptr);
         QK_CUDA(cudaGetLastError());
         c->launches++;
