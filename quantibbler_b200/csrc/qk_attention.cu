@@ -733,17 +733,22 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
 //     to two accumulators that alias S, which has been read out by then.
 //   * Operands are staged by cp.async into 128-byte-swizzled K-major tiles (rows of 128 bytes:
 //     Q and K rows are 128 channels, P and V rows are the iteration's 128 keys, V_a and V_b
-//     side by side), double-buffered across iterations.  The P codes go from registers to
-//     shared memory and are the A operand of PV.
+//     side by side), two iterations ahead.  The P codes go from registers to shared memory and
+//     are the A operand of PV.
+//   * The products run beside the arithmetic: tensor memory holds two accumulator regions, S of
+//     iteration it + 1 is issued as soon as S of iteration it has been read out and runs while
+//     the threads exponentiate; PV of iteration it is issued at the end of the iteration and is
+//     folded into the output in the middle of the next one, after that one's scores.
 // All waits on the MMA barriers are bounded (bit 1 of the context's error word on expiry).
 constexpr int kUQ = 128, kUBlk = 64, kUKeys = 2 * kUBlk, kUD = 128;
 constexpr int kUThreads = 512, kUGroups = kUThreads / kUQ;
 constexpr int kUSRows = kUKeys + 16;  // keys + 2 x 8 mean-digit rows: N of the S product
 constexpr uint32_t kUQBytes = kUQ * 128, kUKBytes = kUSRows * 128, kUVBytes = kUD * 128, kUPBytes = kUQ * 128;
 constexpr uint32_t kUScaleFloats = kUKeys + 2 * kUD + 16;  // key scales, two sets of channel scales, two mean units
-constexpr uint32_t kUSmemBytes = kUQBytes + 2 * kUKBytes + 2 * kUVBytes + kUPBytes + 2 * kUScaleFloats * 4 +
+constexpr int kUBufs = 3;  // K / V / scale buffers: the tiles of an iteration are staged two iterations ahead
+constexpr uint32_t kUSmemBytes = kUQBytes + kUBufs * (kUKBytes + kUVBytes) + kUPBytes + kUBufs * kUScaleFloats * 4 +
                                  2 * kUGroups * kUQ * 4 + 64;
-constexpr uint32_t kUTmemCols = 256;
+constexpr uint32_t kUTmemCols = 512, kURegion = 256;  // two regions of S (then PV) accumulators
 constexpr uint32_t kUWaitLimitDefault = 1u << 22;
 
 // s8 x s8 -> s32, both operands K-major, M = 128, N = n
@@ -769,9 +774,9 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
     extern __shared__ __align__(1024) uint8_t sm_u_raw[];
     // (the swizzled tiles want 1024-byte alignment; the launch asks for 1 KB more than kUSmemBytes)
     uint8_t *sm_u = sm_u_raw + ((1024 - (smem_u32(sm_u_raw) & 1023)) & 1023);
-    uint8_t *Qs = sm_u, *Kb = Qs + kUQBytes, *Vb = Kb + 2 * kUKBytes, *Ps = Vb + 2 * kUVBytes;
+    uint8_t *Qs = sm_u, *Kb = Qs + kUQBytes, *Vb = Kb + kUBufs * kUKBytes, *Ps = Vb + kUBufs * kUVBytes;
     float *scales = reinterpret_cast<float *>(Ps + kUPBytes);
-    float *xm = scales + 2 * kUScaleFloats, *xe = xm + kUGroups * kUQ;  // [group][row]: block maxima, sums of P
+    float *xm = scales + kUBufs * kUScaleFloats, *xe = xm + kUGroups * kUQ;  // [group][row]: block maxima, sums of P
     uint64_t *bar_s = reinterpret_cast<uint64_t *>(xe + kUGroups * kUQ), *bar_pv = bar_s + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_pv + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -850,43 +855,53 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
         const int row = idx / 8, piece = idx % 8;
         cp_async16(swz(Qs, row, piece), a.qc + (row_base + min(q0 + row, (int)dm.Sq - 1)) * a.dpad + piece * 16);
     }
-    if (n_it > 0) stage(0, 0);  // (in one group with Q)
+    stage(0, 0);  // (in one group with Q; n_it >= 1)
+    if (n_it > 1) stage(1, 1);
     const float dq = valid ? a.qs[row_base + i] : 1.f;
 
     float o[32];  // channels 32 g .. 32 g + 31 of row r
 #pragma unroll
     for (int c = 0; c < 32; ++c) o[c] = 0.f;
     float m = -INFINITY, l = 0.f;
+    float prev_alpha_a = 0.f, prev_alpha_b = 0.f;  // of the iteration whose PV is still to be folded in
     const uint32_t idesc_s = umma_idesc_i8(kUSRows), idesc_pv = umma_idesc_i8(kUD);
     const uint32_t limit = wait_limit ? wait_limit : kUWaitLimitDefault;
-    uint32_t phase = 0;
     bool dead = false;
-    for (int it = 0; it < n_it && !dead; ++it) {
-        const int buf = it & 1;
-        if (it + 1 < n_it) {
-            stage(it + 1, buf ^ 1);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
-        // this thread's pieces have landed and its tensor-memory reads of the last iteration are
-        // complete; after the barrier that holds for the CTA, and the tiles may be read by the
-        // tensor core (async proxy)
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        uint8_t *Kt = Kb + buf * kUKBytes, *Vt = Vb + buf * kUVBytes;
-        const float *kscale = scales + buf * kUScaleFloats, *vscale = kscale + kUKeys, *mscale = vscale + 2 * kUD;
-        if (tid == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    uint32_t v[32];
+    auto issue_s = [&](int it) {  // S of iteration `it` into region it % 2 (one thread)
+        const uint32_t kt = smem_u32(Kb + (it % kUBufs) * kUKBytes);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int k = 0; k < kUD / 32; ++k)
-                umma_i8(tmem_base, umma_desc(smem_u32(Qs) + k * 32), umma_desc(smem_u32(Kt) + k * 32), idesc_s, k != 0);
-            umma_commit(bar_s);
+        for (int k = 0; k < kUD / 32; ++k)
+            umma_i8(tmem_base + (it & 1) * kURegion, umma_desc(smem_u32(Qs) + k * 32), umma_desc(kt + k * 32), idesc_s,
+                    k != 0);
+        umma_commit(bar_s);
+    };
+    // o = alpha * o + PV * dV for the blocks of iteration `it`, whose products have completed
+    auto fold_pv = [&](int it, float alpha_a, float alpha_b) {
+        const float *vscale = scales + (it % kUBufs) * kUScaleFloats + kUKeys;
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            if (2 * it + blk >= jb_hi) break;  // (the same for the whole CTA)
+            tmem_ld32(my_tmem + (it & 1) * kURegion + kUD * blk + 32 * g, v);
+            tmem_ld_wait();
+            const float al = blk ? alpha_b : alpha_a;
+            const float *vd = vscale + kUD * blk + 32 * g;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = fmaf(al, o[e], (float)(int)v[e] * vd[e]);
         }
-        __syncwarp();
-        // (the verdict is taken by the whole CTA: nobody goes on to a barrier the others have left)
-        if (!__syncthreads_and(mbar_wait(bar_s, phase, abort_flag, limit))) {
+    };
+    if (n_it > 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
+    else asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) issue_s(0);
+    __syncwarp();
+    for (int it = 0; it < n_it; ++it) {
+        const int buf = it % kUBufs;
+        const float *kscale = scales + buf * kUScaleFloats, *mscale = kscale + kUKeys + 2 * kUD;
+        // (the verdict of a wait is taken by the whole CTA: nobody goes on to a barrier the others have left)
+        if (!__syncthreads_and(mbar_wait(bar_s, it & 1, abort_flag, limit))) {
             dead = true;
             break;
         }
@@ -895,15 +910,14 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
         // ---- this thread's 32 scores of its Sage block
         const int jb = 2 * it + my_blk, j0 = jb * kUBlk, kj = min(kUBlk, S - j0);
         const bool live = jb < jb_hi;
-        uint32_t v[32];
         float shift;
         {
             uint32_t c0, c1, c2, c3;
             asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
                          : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
-                         : "r"(my_tmem + kUKeys + 8 * my_blk)
+                         : "r"(my_tmem + (it & 1) * kURegion + kUKeys + 8 * my_blk)
                          : "memory");
-            tmem_ld32(my_tmem + 32 * g, v);
+            tmem_ld32(my_tmem + (it & 1) * kURegion + 32 * g, v);
             tmem_ld_wait();
             (void)c3;
             shift = (((float)(int)c0 * 65536.f + (float)(int)c1 * 256.f) + (float)(int)c2) * mscale[my_blk] * dq;
@@ -933,7 +947,24 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
             }
         }
         xm[g * kUQ + r] = bm;
+        // ---- the products of the iteration before have had this long to finish: fold them in
+        if (it > 0) {
+            if (!__syncthreads_and(mbar_wait(bar_pv, (it - 1) & 1, abort_flag, limit))) {
+                dead = true;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            fold_pv(it - 1, prev_alpha_a, prev_alpha_b);
+        }
+        // the tiles of iteration it + 1 (staged an iteration ago) have landed; after the barrier
+        // every thread has read S of this iteration and PV of the last one out of tensor memory
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
+        if (it + 1 < n_it && tid == 0) issue_s(it + 1);  // runs while the threads exponentiate
+        __syncwarp();
+        if (it + 2 < n_it) stage(it + 2, (it + 2) % kUBufs);
         // ---- the row's maxima after block a and after block b (the same in its four threads)
         const float bm_a = fmaxf(xm[r], xm[kUQ + r]), bm_b = fmaxf(xm[2 * kUQ + r], xm[3 * kUQ + r]);
         const float mn_a = fmaxf(m, bm_a);
@@ -965,39 +996,33 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
             *reinterpret_cast<uint4 *>(swz(Ps, (int)r, 2 * g + piece)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
         xe[g * kUQ + r] = es;
-        // ---- PV: S has been read out, the accumulators may take its place
+        // ---- PV into the region S has been read out of
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
         if (tid == 0) {
+            const uint32_t vt = smem_u32(Vb + buf * kUVBytes);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk)
 #pragma unroll
                 for (int k = 0; k < 2; ++k)
-                    umma_i8(tmem_base + kUD * blk, umma_desc(smem_u32(Ps) + (2 * blk + k) * 32),
-                            umma_desc(smem_u32(Vt) + (2 * blk + k) * 32), idesc_pv, k != 0);
+                    umma_i8(tmem_base + (it & 1) * kURegion + kUD * blk, umma_desc(smem_u32(Ps) + (2 * blk + k) * 32),
+                            umma_desc(vt + (2 * blk + k) * 32), idesc_pv, k != 0);
             umma_commit(bar_pv);
         }
         __syncwarp();
         l = alpha_a * l + (xe[r] + xe[kUQ + r]);
         l = alpha_b * l + (xe[2 * kUQ + r] + xe[3 * kUQ + r]);
         m = m_b;
-        if (!__syncthreads_and(mbar_wait(bar_pv, phase, abort_flag, limit))) {
+        prev_alpha_a = alpha_a;
+        prev_alpha_b = alpha_b;
+    }
+    if (!dead) {
+        if (!__syncthreads_and(mbar_wait(bar_pv, (n_it - 1) & 1, abort_flag, limit))) {
             dead = true;
-            break;
-        }
-        phase ^= 1;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-            if (2 * it + blk >= jb_hi) break;  // (the same for the whole CTA)
-            tmem_ld32(my_tmem + kUD * blk + 32 * g, v);
-            tmem_ld_wait();
-            const float al = blk ? alpha_b : alpha_a;
-            const float *vd = vscale + kUD * blk + 32 * g;
-#pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = fmaf(al, o[e], (float)(int)v[e] * vd[e]);
+        } else {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            fold_pv(n_it - 1, prev_alpha_a, prev_alpha_b);
         }
     }
     if (dead) *abort_flag = 1;
