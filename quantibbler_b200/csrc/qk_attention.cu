@@ -138,6 +138,24 @@ __global__ void sage_quant_q_kernel(const float *__restrict__ q, int8_t *__restr
     uint32_t row = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32, lane = threadIdx.x % 32;
     if (row >= rows) return;
     const float *qr = q + (size_t)row * d;
+    if (d % 4 == 0 && dpad <= 128) {
+        // a lane owns four consecutive channels: one 16-byte load, one 4-byte store of codes
+        const uint32_t c = 4 * lane;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < d) x = *reinterpret_cast<const float4 *>(qr + c);
+        x.x *= inv_sqrt_d, x.y *= inv_sqrt_d, x.z *= inv_sqrt_d, x.w *= inv_sqrt_d;
+        float peak = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+        for (int off = 16; off > 0; off >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, off));
+        const float delta = peak > 0.f ? peak / 127.f : 1.f;
+        if (c < dpad) {
+            const uint32_t w = (uint32_t)(quant_code(x.x, delta) & 0xff) | ((uint32_t)(quant_code(x.y, delta) & 0xff) << 8) |
+                               ((uint32_t)(quant_code(x.z, delta) & 0xff) << 16) |
+                               ((uint32_t)(quant_code(x.w, delta) & 0xff) << 24);
+            *reinterpret_cast<uint32_t *>(codes + (size_t)row * dpad + c) = c < d ? w : 0u;
+        }
+        if (lane == 0) scale[row] = delta;
+        return;
+    }
     float peak = 0.f;
     for (uint32_t c = lane; c < d; c += 32) peak = fmaxf(peak, fabsf(qr[c] * inv_sqrt_d));
     for (int off = 16; off > 0; off >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, off));
@@ -231,10 +249,39 @@ __global__ void sage_quant_v_kernel(const float *__restrict__ v, int8_t *__restr
     const uint32_t j0 = jb * block, j1 = min(S, j0 + block);
     const float *vp = v + (size_t)plane * S * dv;
     for (uint32_t c = threadIdx.x; c < dv; c += blockDim.x) {
+        int8_t *cr = codes + (((size_t)plane * n_blocks + jb) * dv + c) * bpad;
+        if (bpad == 64 && !permute) {
+            // the block's 64 values of the channel stay in registers between the two passes,
+            // and the codes leave as four 16-byte stores
+            float x[64];
+            float peak = 0.f;
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+                x[j] = j0 + j < j1 ? vp[(size_t)(j0 + j) * dv + c] : 0.f;
+                peak = fmaxf(peak, fabsf(x[j]));
+            }
+            const float delta = peak > 0.f ? peak / 127.f : 1.f;
+#pragma unroll
+            for (int piece = 0; piece < 4; ++piece) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    w[q] = 0;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = 16 * piece + 4 * q + e;
+                        const int code = j0 + j < j1 ? quant_code(x[j], delta) : 0;
+                        w[q] |= (uint32_t)(code & 0xff) << (8 * e);
+                    }
+                }
+                *reinterpret_cast<uint4 *>(cr + 16 * piece) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            scale[((size_t)plane * n_blocks + jb) * dv + c] = delta;
+            continue;
+        }
         float peak = 0.f;
         for (uint32_t j = j0; j < j1; ++j) peak = fmaxf(peak, fabsf(vp[(size_t)j * dv + c]));
         const float delta = peak > 0.f ? peak / 127.f : 1.f;
-        int8_t *cr = codes + (((size_t)plane * n_blocks + jb) * dv + c) * bpad;
         for (uint32_t j = j0; j < j0 + bpad; ++j)
             cr[permute ? sage_tc_key_slot(j - j0) : j - j0] =
                 j < j1 ? (int8_t)quant_code(vp[(size_t)j * dv + c], delta) : 0;
