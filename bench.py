@@ -198,7 +198,6 @@ C4_RANKS = {"q": 1102, "o": 1102, "k": 431, "v": 431, "gate": 1724, "up": 1724, 
 C3_RANKS = {"q": 1102, "k": 1102, "v": 1102, "o": 1102, "gate": 1614, "up": 1614, "down": 1622}
 
 
-DIRECT_MAX_BATCH = None   # --direct-max-batch: override of DecoderConfig.direct_max_batch
 FUSED_STEP_MAX_BATCH = None   # --fused-step-max-batch: override of DecoderConfig.fused_step_max_batch
 
 
@@ -206,8 +205,6 @@ def decode_config(model: str, n_layers: int, batch: int, max_seq: int, allreduce
     """DecoderConfig + ranks of the benchmark's configuration 4 ("llama3-8b") or config 3."""
     import dataclasses
     cfg, ranks = _decode_config(model, n_layers, batch, max_seq, allreduce)
-    if DIRECT_MAX_BATCH is not None:
-        cfg = dataclasses.replace(cfg, direct_max_batch=DIRECT_MAX_BATCH)
     if FUSED_STEP_MAX_BATCH is not None:
         cfg = dataclasses.replace(cfg, fused_step_max_batch=FUSED_STEP_MAX_BATCH)
     return cfg, ranks
@@ -601,8 +598,6 @@ def main() -> None:
     ap.add_argument("--n-layers", type=int, default=0)
     ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
                     help="decode workload under tensor parallelism")
-    ap.add_argument("--direct-max-batch", type=int, default=-1,
-                    help="decode: batches up to this size use the table-free direct GEMV (-1: the decoder's default)")
     ap.add_argument("--fused-step-max-batch", type=int, default=-1,
                     help="decode: batches up to this size run the blocks of a step as one kernel (-1: the decoder's default)")
     ap.add_argument("--tp-decode", type=int, default=1,
@@ -615,9 +610,7 @@ def main() -> None:
                     help="compare sampled outputs of the timed launch with the CPU oracle")
     args = ap.parse_args()
 
-    global DIRECT_MAX_BATCH, FUSED_STEP_MAX_BATCH
-    if args.direct_max_batch >= 0:
-        DIRECT_MAX_BATCH = args.direct_max_batch
+    global FUSED_STEP_MAX_BATCH
     if args.fused_step_max_batch >= 0:
         FUSED_STEP_MAX_BATCH = args.fused_step_max_batch
     if args.shape:

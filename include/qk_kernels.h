@@ -292,18 +292,6 @@ qk_status qk_plan_create_gated(qk_ctx *ctx, const qk_layer *const *layers,
                                float *const *y_ptrs, size_t n_inst, qk_group **out);
 qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group);
 void qk_group_free(qk_group *group);
-/* ---- direct plans (single-token decode) -----------------------------------------
- * Switches a small plan to the table-free form: the weight bits become bfloat16 +-1 MMA
- * operands in registers and the vector rides as bfloat16 terms (one under bfloat16 serving - the
- * operands and float32 accumulation of apply_bf16, engine/mod.rs:449-460 - and a three-term
- * split that reproduces float32 under float32 serving), accumulated in float32 in a fixed
- * order.  Each block then does nothing before it multiplies but copy the vector, which is
- * what bounds a one-token step.  The result is the reference's float32 arithmetic class
- * (within 1e-6 * sum|terms| of the exact sum, tests/parity.rs:795), not the bit-sliced form's
- * exact integer sum, so it is opt-in per plan; qk_layer_apply and the group calls never use it.
- * Plans too large for the few-instance kernel form, and fed plans, are refused with
- * QK_ERR_VALUE. */
-qk_status qk_plan_use_direct(qk_ctx *ctx, qk_group *plan);
 /* ---- the blocks of a decode step as one kernel ---------------------------------------
  * transformer_forward (engine/mod.rs:878-945) runs, per block, norm -> q/k/v -> RoPE + cache
  * append -> attention -> o -> norm -> gate/up -> SwiGLU -> down.  As separate launches that is
@@ -311,11 +299,14 @@ qk_status qk_plan_use_direct(qk_ctx *ctx, qk_group *plan);
  * qk_decode_step_run does ALL blocks of a step in one cooperative kernel (one CTA per SM, a
  * bounded grid barrier between phases, the small operations folded into the phases that
  * consume them, every block prefetching its next weight tiles before it waits).  The linears
- * run in the direct form of qk_plan_use_direct, so a step equals, bit for bit, the same step
- * made of qk_rmsnorm / direct plans / qk_rope_cache / qk_decode_attention / qk_swiglu calls.
- * Limits: head_dim 128, bfloat16 cache, at most 8 tokens under bfloat16 serving and 2 under
- * float32 serving, no per-head q/k norms; anything else is refused with QK_ERR_VALUE and the
- * caller keeps the separate launches.
+ * are the exact bit-sliced form, so a step equals, bit for bit, the same step made of
+ * qk_rmsnorm / plans / qk_rope_cache / qk_decode_attention / qk_swiglu calls.  Measured on a
+ * Llama-3-8B-shaped stack it is SLOWER than those launches (5.1 against 4.4 ms per one-token
+ * step: with one CTA of eight warps per SM, the per-vector work that every block repeats -
+ * norm, SwiGLU, digit table - is not hidden), so callers opt in.
+ * Limits: head_dim 128, bfloat16 cache, at most 8 tokens, no per-head q/k norms, a model
+ * narrow enough for the kernel's shared memory; anything else is refused with QK_ERR_VALUE and
+ * the caller keeps the separate launches.
  * Buffers (all float32 unless said, token-major): x holds the embedded tokens on entry and
  * the residual stream before the last block's down output on exit (delta_mlp holds that
  * output: the caller's final norm adds it); x2 is the stream's second buffer; q/k/v/attn/

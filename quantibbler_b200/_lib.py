@@ -83,7 +83,6 @@ _SIGNATURES = {
                                        POINTER(c_void_p)]),
     "qk_group_apply": (c_int32, [c_void_p, c_void_p]),
     "qk_plan_feed_targets": (c_int32, [c_void_p, c_void_p, POINTER(c_void_p), POINTER(c_size_t)]),
-    "qk_plan_use_direct": (c_int32, [c_void_p, c_void_p]),
     "qk_decode_step_create": (c_int32, [c_void_p, c_void_p, POINTER(c_void_p)]),
     "qk_decode_step_run": (c_int32, [c_void_p, c_void_p]),
     "qk_decode_step_free": (None, [c_void_p]),

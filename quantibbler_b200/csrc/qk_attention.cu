@@ -824,8 +824,8 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
     uint8_t *Qs = sm_u, *Kb = Qs + kUQBytes, *Vb = Kb + kUBufs * kUKBytes, *Ps = Vb + kUBufs * kUVBytes;
     float *scales = reinterpret_cast<float *>(Ps + kUPBytes);
     float *xm = scales + kUBufs * kUScaleFloats, *xe = xm + kUGroups * kUQ;  // [group][row]: block maxima, sums of P
-    uint64_t *bar_s = reinterpret_cast<uint64_t *>(xe + kUGroups * kUQ), *bar_pv = bar_s + 1;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_pv + 1);
+    uint64_t *bar_s = reinterpret_cast<uint64_t *>(xe + kUGroups * kUQ), *bar_pv = bar_s + 1, *bar_drain = bar_s + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_drain + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t tid = threadIdx.x, warp = tid / 32;
     const uint32_t g = tid / kUQ, r = tid % kUQ;  // column group, query row
@@ -842,6 +842,7 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
     if (tid == 0) {
         mbar_init(bar_s, 1);
         mbar_init(bar_pv, 1);
+        mbar_init(bar_drain, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -1070,6 +1071,18 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
         } else {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             fold_pv(n_it - 1, prev_alpha_a, prev_alpha_b);
+        }
+    }
+    if (dead) {
+        // Given up: before tensor memory is handed back, the products that were issued must have
+        // finished.  A commit on a barrier of its own arrives when everything issued so far is
+        // done; it is waited for with the default (long) limit, not the one that just expired.
+        __syncthreads();
+        if (warp == 0) {
+            volatile int never = 0;
+            if (tid == 0) umma_commit(bar_drain);
+            __syncwarp();
+            (void)mbar_wait(bar_drain, 0, &never, kUWaitLimitDefault);
         }
     }
     if (dead) *abort_flag = 1;

@@ -103,7 +103,6 @@ struct qk_group {
     size_t n_inst = 0;
     qk_layer shape;          // dimensions/strides of the member layers (the largest, if they differ)
     bool mixed = false;      // the members differ in shape: few-instance form only
-    bool direct = false;     // small-batch direct form: bf16 +-1 MMA, float32 accumulation, no tables
     bool fed = false;        // the stage-1 tables are written by the kernels that produce the inputs
     void *feed = nullptr;    // device array of per-instance feed targets (fed plans)
     void *tickets = nullptr; // device array of per-instance block counters (fed plans)

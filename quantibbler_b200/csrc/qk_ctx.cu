@@ -193,7 +193,7 @@ qk_status qk_gpu_synchronize(qk_ctx *ctx) {
                                 "a token's position or sequence index lies outside the KV cache; "
                                 "the token was skipped");
             return qk::fail(QK_ERR_TIMEOUT, "a bounded device-side wait gave up:%s%s%s%s",
-                            (h_err & 1) ? " a pipeline barrier of the tensor-core prefill;" : "",
+                            (h_err & 1) ? " a pipeline barrier of a tcgen05 kernel (prefill GEMM, Sage attention);" : "",
                             (h_err & 2) ? " the inbox of a fused all-reduce (a peer did not send);"
                                         : "",
                             (h_err & 8) ? " a ring or table barrier of the streaming GEMV;" : "",

@@ -43,7 +43,6 @@
 
 #include "qk_common.h"
 #include "qk_digits.cuh"
-#include "qk_direct.cuh"
 
 namespace {
 
@@ -687,75 +686,6 @@ layer_bitslice_fused_kernel(const StageParams *__restrict__ stage1,
     __syncthreads();  // every row of t is in shared memory; the table can be rebuilt
     bitslice_stage<kRoundBf16, true, true, true, false>(p2, table, ring, t_smem, nullptr, dout, r,
                                                         groups2, steps2, 0, gpw2, true);
-}
-
-// ------------------------------------------------------------------ small-batch direct form
-// The table-free form of qk_direct.cuh as a kernel over a plan's instances: grid (row groups,
-// instances), one token per instance.  The intermediate t is float32 here.
-template <bool kRoundBf16, bool kFinal>
-__global__ void __launch_bounds__(qk_direct::kThreads)
-gemv_direct_kernel(const StageParams *__restrict__ many, uint32_t n_steps_max) {
-    qk::pdl_launch();
-    extern __shared__ __align__(128) uint8_t smem_dyn[];
-    const StageParams p = many[blockIdx.y];
-    const uint32_t n_rows = p.n_rows, n_bits = p.n_bits;
-    const uint32_t n_groups = (n_rows + kGroupRows - 1) / kGroupRows;
-    const uint32_t n_steps = (n_bits + kStepBits - 1) / kStepBits;
-    if (blockIdx.x >= n_groups) {
-        qk::pdl_wait();
-        return;
-    }
-    const qk_direct::Smem sm = qk_direct::carve(smem_dyn, n_steps_max, qk_direct::Terms<kRoundBf16>::kN);
-    const qk_direct::Work work{p.w_tiles, n_steps, blockIdx.x};
-    qk_direct::prefetch(sm, work);
-    // what the epilogue needs of the layer itself is fetched now, not after the multiply
-    const uint32_t my_row = blockIdx.x * kGroupRows + threadIdx.x;
-    float out_scale = 1.f, out_bias = 0.f;
-    if (kFinal && threadIdx.x < kGroupRows && my_row < n_rows) {
-        if (p.out_scale) out_scale = p.out_scale[my_row];
-        if (p.out_bias) out_bias = p.out_bias[my_row];
-    }
-    qk::pdl_wait();  // the weight bits depend on no other kernel, the input vector does
-    const float *in = static_cast<const float *>(p.in);  // x, or the float32 t of stage 1
-    const float *gate_up = p.in_gate_up, *scale = p.in_scale;
-    auto one = [&](uint32_t k) {
-        float v = in[k];
-        if (gate_up) v = v * gate_up[k] / (1.0f + expf(-v));
-        if (scale) v = scale[k] * v;
-        return v;
-    };
-    auto four = [&](uint32_t k) {
-        float4 v = *reinterpret_cast<const float4 *>(in + k);
-        if (gate_up) {
-            const float4 u = *reinterpret_cast<const float4 *>(gate_up + k);
-            v.x = v.x * u.x / (1.0f + expf(-v.x)), v.y = v.y * u.y / (1.0f + expf(-v.y));
-            v.z = v.z * u.z / (1.0f + expf(-v.z)), v.w = v.w * u.w / (1.0f + expf(-v.w));
-        }
-        if (scale) {
-            const float4 sc = *reinterpret_cast<const float4 *>(scale + k);
-            v.x = sc.x * v.x, v.y = sc.y * v.y, v.z = sc.z * v.z, v.w = sc.w * v.w;
-        }
-        return v;
-    };
-    const bool vector_ok = n_bits % 4 == 0 &&
-                           ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(gate_up) |
-                             reinterpret_cast<uintptr_t>(scale)) & 15) == 0;
-    // (bfloat16 serving: z is rounded once to bfloat16, as apply_bf16 does)
-    qk_direct::stage_vector<kRoundBf16>(sm, 0, n_bits, n_steps, vector_ok, one, four);
-    __syncthreads();
-    qk_direct::multiply(sm, work, qk_direct::Terms<kRoundBf16>::kN);
-    if (threadIdx.x < kGroupRows) {
-        float sum = qk_direct::gather<kRoundBf16>(sm, threadIdx.x, 0);
-        const uint32_t row = blockIdx.x * kGroupRows + threadIdx.x;
-        if (row < n_rows) {
-            if (kRoundBf16) sum = round_bf16(sum);  // t and u are rounded once to bfloat16
-            if (kFinal) {
-                if (p.out_scale) sum = sum * out_scale;
-                if (p.out_bias) sum = sum + out_bias;
-            }
-            static_cast<float *>(p.out)[row] = sum;
-        }
-    }
 }
 
 // ------------------------------------------------------------------ persistent streaming form
@@ -1513,36 +1443,8 @@ qk_status launch_fed_stage(qk_ctx *c, const StageParams *many, size_t n_inst, co
     return QK_OK;
 }
 
-// Direct plans (gemv_direct_kernel): smem = terms + ring + reduction buffer for the widest input.
-bool direct_plan_fits(const qk_ctx *c, const StageShape &s, size_t n_inst, bool bf16, size_t *smem) {
-    *smem = qk_direct::smem_bytes((uint32_t)s.n_steps, bf16 ? 1 : 3);
-    return *smem <= kSmemBudget && s.n_groups <= 65535 && n_inst <= 65535 &&
-           n_inst * s.n_groups <= 16 * (size_t)c->sm_count;
-}
-
-template <bool kFinal>
-qk_status launch_direct_stage(qk_ctx *c, const StageParams *many, size_t n_inst, const StageShape &s,
-                              bool bf16) {
-    size_t smem;
-    if (!direct_plan_fits(c, s, n_inst, bf16, &smem))
-        return qk::fail(QK_ERR_VALUE, "a direct plan must fit the few-instance form");
-    auto gemv = bf16 ? gemv_direct_kernel<true, kFinal> : gemv_direct_kernel<false, kFinal>;
-    QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-    dim3 grid((unsigned)s.n_groups, (unsigned)n_inst);
-    (void)qk::launch_pdl(c->pdl, gemv, grid, dim3(qk_direct::kThreads), smem, c->stream, many,
-                         (uint32_t)s.n_steps);
-    QK_CUDA(cudaGetLastError());
-    c->launches++;
-    return QK_OK;
-}
-
 qk_status launch_both(qk_ctx *c, const qk_layer *l0, const StageParams *d, size_t n_inst,
-                      int kernel, bool mixed = false, bool fed = false, bool direct = false) {
-    if (direct) {
-        qk_status e = launch_direct_stage<false>(c, d, n_inst, stage1_shape(l0), l0->serving == QK_BF16);
-        if (e != QK_OK) return e;
-        return launch_direct_stage<true>(c, d + n_inst, n_inst, stage2_shape(l0), l0->serving == QK_BF16);
-    }
+                      int kernel, bool mixed = false, bool fed = false) {
     if (fed) {
         qk_status e = launch_fed_stage<false>(c, d, n_inst, stage1_shape(l0), l0->serving == QK_BF16);
         if (e != QK_OK) return e;
@@ -1918,24 +1820,6 @@ qk_status qk_plan_create_gated(qk_ctx *ctx, const qk_layer *const *layers,
     return plan_create(ctx, layers, gate_ptrs, up_ptrs, y_ptrs, n_inst, out);
 }
 
-qk_status qk_plan_use_direct(qk_ctx *ctx, qk_group *plan) {
-    if (!plan) return qk::fail(QK_ERR_VALUE, "qk_plan_use_direct: plan is null");
-    qk_ctx *c;
-    qk_status st = qk::resolve_ctx(ctx, &c);
-    if (st != QK_OK) return st;
-    std::lock_guard<std::mutex> lock(c->mu);
-    if (plan->fed) return qk::fail(QK_ERR_VALUE, "a fed plan cannot take the direct form");
-    const bool bf16 = plan->shape.serving == QK_BF16;
-    size_t smem;
-    if (!direct_plan_fits(c, stage1_shape(&plan->shape), plan->n_inst, bf16, &smem) ||
-        !direct_plan_fits(c, stage2_shape(&plan->shape), plan->n_inst, bf16, &smem))
-        return qk::fail(QK_ERR_VALUE, "a plan of %zu instances (up to %zu x %zu rank %zu) is too large "
-                        "for the direct small-batch form", plan->n_inst, plan->shape.dout, plan->shape.din,
-                        plan->shape.r);
-    plan->direct = true;
-    return QK_OK;
-}
-
 qk_status qk_plan_feed_targets(qk_ctx *ctx, qk_group *plan, const void **targets_dev,
                                size_t *n_targets) {
     if (!plan || !targets_dev || !n_targets)
@@ -1949,7 +1833,6 @@ qk_status qk_plan_feed_targets(qk_ctx *ctx, qk_group *plan, const void **targets
         return qk::fail(QK_ERR_VALUE, "plan lives on device %d, context on device %d", plan->device,
                         c->device);
     const size_t n = plan->n_inst;
-    if (plan->direct) return qk::fail(QK_ERR_VALUE, "a direct plan has no digit tables to feed");
     if (!plan->feed) {
         size_t warps, smem;
         if (!fed_plan_fits(c, stage1_shape(&plan->shape), n, &warps, &smem) ||
@@ -1989,7 +1872,7 @@ qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group) {
         return qk::fail(QK_ERR_VALUE, "group lives on device %d, context on device %d",
                         group->device, c->device);
     return launch_both(c, &group->shape, (const StageParams *)group->params, group->n_inst,
-                       c->gemv_kernel, group->mixed, group->fed, group->direct);
+                       c->gemv_kernel, group->mixed, group->fed);
 }
 
 void qk_group_free(qk_group *g) {

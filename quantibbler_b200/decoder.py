@@ -50,14 +50,12 @@ class DecoderConfig:
     # measured slower than the plain sequence on the Llama-3-8B shape at batch 1 (5.4 against
     # 4.8 ms per step), so the default is off.
     feed_max_batch: int = 0
-    # Batches up to this size run their linears in the table-free direct form (LayerPlan.use_direct):
-    # float32 accumulation like the reference's own GEMV instead of the exact integer sum.
-    direct_max_batch: int = 0
     # Batches up to this size run all transformer blocks of a step as ONE cooperative kernel
     # (gpu.DecodeStep: a grid barrier between phases instead of a kernel boundary; the same
-    # bits as the separate launches).  Needs head_dim 128, a bfloat16 cache, no q/k norms, one
-    # GPU and a model narrow enough for its shared memory; other configurations keep the
-    # separate launches.
+    # bits as the separate launches).  Measured slower than the launches on the Llama-3-8B shape
+    # (5.1 against 4.4 ms per step), so the default is off.  Needs head_dim 128, a bfloat16
+    # cache, no q/k norms, one GPU and a model narrow enough for its shared memory; other
+    # configurations keep the separate launches.
     fused_step_max_batch: int = 0
     prefill_min_tokens: int = 16   # generate(): prompts this long go through the trunk in one pass
     prefill_chunk: int = 2048      # ... in pieces of at most this many positions
@@ -294,9 +292,6 @@ class Decoder:
             else:
                 plan["gate"] = LayerPlan(ctx, inst(["gate"], self.h, [self.g]))
                 plan["up"] = LayerPlan(ctx, inst(["up"], self.h, [self.u]))
-            if not fed and B <= cfg.direct_max_batch:
-                for pl in plan.values():
-                    pl.use_direct()
             self.plans.append(plan)
         self.step_kernel = None
         if (B <= cfg.fused_step_max_batch and tp_size == 1 and not self.has_qk_norm and hd == 128

@@ -546,13 +546,6 @@ class LayerPlan(LayerGroup):
             check(_lib.lib().qk_plan_create(ctx.handle, larr, xarr, yarr, n, ctypes.byref(h)))
         self._h = h
 
-    def use_direct(self):
-        """Switches the plan to the table-free small-batch form (float32 accumulation of
-        bfloat16 +-1 products; the reference's float32 arithmetic class rather than the exact
-        integer sum).  Raises KernelError when the plan is too large for it."""
-        check(_lib.lib().qk_plan_use_direct(self.ctx.handle, self._h))
-        return self
-
     def feed_targets(self):
         """Turns the plan into a fed plan (the digit tables of its stage-1 inputs are then
         written by the ``*_feed`` call that produces those inputs, and every ``apply`` must follow

@@ -147,3 +147,31 @@ def test_decode_attention_clamps_the_length_to_the_cache(gpu_ctx):
         gpu_ctx.synchronize()
         outs.append(out.cpu().numpy())
     assert np.array_equal(outs[0], outs[1])
+
+
+def test_grid_barrier_of_the_whole_step_kernel_runs_out_and_recovers(gpu_ctx):
+    """The whole-step decode kernel separates its phases by a grid barrier whose poll is bounded.
+    With the limit set to a single poll, blocks give up at the first barrier they reach before
+    the others: the kernel still runs to its end (every block keeps arriving, so the barrier
+    count stays whole), the step's results are meaningless, qk_gpu_synchronize reports
+    QK_ERR_TIMEOUT - and the same decoder, the same barrier counter, then decodes correctly."""
+    from quantibbler_b200.decoder import Decoder, DecoderConfig, random_model
+    ranks = {"q": 72, "k": 40, "v": 40, "o": 100, "gate": 130, "up": 130, "down": 90}
+    cfg = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=128, d_ff=640, vocab=192,
+               max_seq=64, max_batch=1, kv_dtype="bfloat16", serving="bfloat16", n_splits=2)
+    weights = random_model(DecoderConfig(**cfg), ranks, seed=5)
+    fused = Decoder(gpu_ctx, DecoderConfig(fused_step_max_batch=1, **cfg), weights)
+    plain = Decoder(gpu_ctx, DecoderConfig(**cfg), weights)
+    assert fused.step_kernel is not None
+    fused.start([7], [0])
+    prev = gpu_ctx.set_wait_limit(1)
+    try:
+        fused.step()
+        with pytest.raises(DeviceError, match="grid barrier of the whole-step decode kernel"):
+            gpu_ctx.synchronize()
+    finally:
+        gpu_ctx.set_wait_limit(prev)
+    gpu_ctx.synchronize()   # the error word was cleared
+    fused.start([7], [0])
+    plain.start([7], [0])
+    assert np.array_equal(fused.decode(10), plain.decode(10))
