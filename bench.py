@@ -546,9 +546,11 @@ def run_attention(args, local_rank: int) -> None:
         ms, launches = timed(sage, args.steps, warmup)
     clocks = sampler.summary()
     ms_exact, _ = timed(exact, 2, 1)
-    ctx.set_sage_kernel(0)
+    default_kernel = ctx.set_sage_kernel(0)
     ms_dp4a, _ = timed(sage, 2, 1)
     ctx.set_sage_kernel(1)
+    ms_mma_sync, _ = timed(sage, 3, 1)
+    ctx.set_sage_kernel(default_kernel)
     # end to end through the reference-facing call: host arrays in, host array out
     hq, hk, hv = (t.cpu().numpy() for t in (q, k, v))
     t0 = time.perf_counter()
@@ -567,11 +569,14 @@ def run_attention(args, local_rank: int) -> None:
                                f"quantisers + main kernel; q, k, v, out ({(2*H+2*KV)*S*D*4/1e6:.0f} MB) "
                                f"exceed L2",
                    "exact_f32_face_ms": ms_exact, "sage_dp4a_kernel_ms": ms_dp4a,
+                   "sage_mma_sync_kernel_ms": ms_mma_sync,
                    "divergences": DIVERGENCES["attention"]},
         "roofline": {"bound": "tensor", "achieved": tops, "peak": peak, "unit": "TOP/s",
                      "frac": tops / peak, "traffic": None,
-                     "note": "peak = 2 x measured dense bf16 (the INT8 tensor rate); the kernel "
-                             "uses mma.sync, the legacy tensor path"},
+                     "note": "peak = 2 x measured dense bf16 (the INT8 tensor rate); both products "
+                             "run on tcgen05 (kind::i8, accumulators in tensor memory); the kernel is "
+                             "bound by the per-score arithmetic between them, not by the tensor pipe",
+                     "kernel": "attention_sage_umma_kernel (+ three quantisers per call)"},
         "e2e": {"value": ops / (e2e_ms * 1e-3) / 1e12, "unit": "TOP/s",
                 "h2d_bytes_per_step": int((H + 2 * KV) * S * D * 4),
                 "d2h_bytes_per_step": int(H * S * D * 4)},
