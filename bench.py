@@ -342,8 +342,10 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
     ctx = GpuContext.init_at(local_rank)
     res, dec = measure_decode(ctx, cfg, ranks, B, ctx_len, args.steps, args.warmup, rank, world,
                               group)
+    phase_trace = step_phase_trace(ctx, dec, cfg) if dec.step_kernel is not None else None
     if rank == 0:
         print(json.dumps({
+            "phase_trace_us": phase_trace,
             "metric": "decode_tok_s", "value": res["tok_s"], "unit": "tok/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "strong",
@@ -366,6 +368,29 @@ def run_decode(args, rank: int, local_rank: int, world: int) -> None:
         torch.cuda.synchronize()
         sys.stdout.flush()
         os._exit(0)
+
+
+def step_phase_trace(ctx, dec, cfg) -> dict:
+    """Durations of the phases of the whole-step decode kernel (the device timer as block 0 sees
+    it after every grid barrier, qk_decode_step_trace), one eager step after the timed replays:
+    per phase the median over the model's blocks, and the sum per block."""
+    import numpy as np
+    import torch
+
+    n = 9 * cfg.n_layers
+    stamps = torch.zeros(n + 8, dtype=torch.int64, device="cuda")
+    dec.step_kernel.trace(stamps.data_ptr(), stamps.numel())
+    dec.step()
+    ctx.synchronize()
+    dec.step_kernel.trace(None)
+    t = stamps.cpu().numpy()
+    per = (np.diff(t[:n + 1]) / 1000.0).reshape(cfg.n_layers, 9)
+    names = ["qkv_stage1_with_norm", "qkv_stage2", "attention_rope_append_combine", "o_stage1", "o_stage2",
+             "gate_up_stage1_with_norm", "gate_up_stage2", "down_stage1_with_swiglu", "down_stage2"]
+    body = per[1:-1] if cfg.n_layers > 2 else per   # (block 0 is cold, the last block ends early for block 0)
+    return {"median_us_per_phase": {nm: float(np.median(body[:, i])) for i, nm in enumerate(names)},
+            "us_per_block_median": float(np.median(body.sum(axis=1))),
+            "note": "phase = from one grid barrier to the next as block 0 sees it (the slowest block decides)"}
 
 
 def tp_decode_block(args, ctx, rank: int, world: int, group) -> dict:
