@@ -421,6 +421,20 @@ qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
                               const void *cache_v, int32_t kv_dtype, const int32_t *kv_len,
                               size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
                               size_t s_max, size_t n_splits, float *scratch, float *out);
+/* RoPE + KV-cache append + decode attention + combine in ONE launch, for a bfloat16 cache and
+ * head_dim 128: what qk_rope_cache followed by qk_decode_attention does (the same bits in
+ * `out` and in the cache), except that q is read unrotated and left so.  k, v: this step's
+ * projections [batch][n_kv_heads][128] float32.  scratch: qk_decode_attention_rope_scratch
+ * bytes, ZEROED once by the caller before the first call (it holds the split partials and one
+ * counter per head group, which the kernel returns to zero).  Other configurations are refused
+ * with QK_ERR_VALUE: use the two separate calls. */
+size_t qk_decode_attention_rope_scratch(size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                                        size_t n_splits);
+qk_status qk_decode_attention_rope(qk_ctx *ctx, const float *q, const float *k, const float *v,
+                                   const float *cos_sin, const int32_t *positions, const int32_t *seq_index,
+                                   void *cache_k, void *cache_v, int32_t kv_dtype, const int32_t *kv_len,
+                                   size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                                   size_t s_max, size_t n_seq, size_t n_splits, float *scratch, float *out);
 /* qk_decode_attention whose combine step also writes the digit tables of the linears that
  * read `out` (the o projection of a fed plan); serving_dtype is that of those linears. */
 qk_status qk_decode_attention_feed(qk_ctx *ctx, const float *q, const void *cache_k,

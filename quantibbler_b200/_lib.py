@@ -83,6 +83,10 @@ _SIGNATURES = {
                                        POINTER(c_void_p)]),
     "qk_group_apply": (c_int32, [c_void_p, c_void_p]),
     "qk_plan_feed_targets": (c_int32, [c_void_p, c_void_p, POINTER(c_void_p), POINTER(c_size_t)]),
+    "qk_decode_attention_rope_scratch": (c_size_t, [c_size_t, c_size_t, c_size_t, c_size_t, c_size_t]),
+    "qk_decode_attention_rope": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_int32, c_void_p, c_size_t, c_size_t, c_size_t,
+                                           c_size_t, c_size_t, c_size_t, c_size_t, c_void_p, c_void_p]),
     "qk_decode_step_create": (c_int32, [c_void_p, c_void_p, POINTER(c_void_p)]),
     "qk_decode_step_run": (c_int32, [c_void_p, c_void_p]),
     "qk_decode_step_free": (None, [c_void_p]),

@@ -507,6 +507,57 @@ decode_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__restr
 }
 
 
+// RoPE + cache append + split-KV attention + combine in ONE launch (bfloat16 cache, head_dim 128):
+// what rope_cache_kernel, decode_attention_mma_kernel and decode_combine_kernel do in three.
+// The rotation of q happens in the fragment loader; the block whose keys include the position
+// being appended rotates k and writes k, v into the cache before it streams its keys; the last
+// split of a (sequence, kv-head block) to finish - found by a ticket, nobody waits - combines
+// the splits, a warp per head.  Same device functions, same bits.  q is left unrotated.
+// tickets: one zero-initialised counter per (sequence, kv-head block); the last block resets it.
+__global__ void __launch_bounds__(kMmaDecWarps * 32)
+decode_attention_rope_kernel(const float *__restrict__ q, const float *__restrict__ k,
+                             const float *__restrict__ v, const float *__restrict__ cos_sin,
+                             const int32_t *__restrict__ positions, const int32_t *__restrict__ seq_index,
+                             uint16_t *__restrict__ cache_k, uint16_t *__restrict__ cache_v,
+                             const int32_t *__restrict__ kv_len, float *__restrict__ partial,
+                             uint32_t *__restrict__ tickets, float *__restrict__ out, uint32_t n_heads,
+                             uint32_t n_kv, uint32_t gq, uint32_t s_max, uint32_t n_seq, uint32_t chunk,
+                             uint32_t n_splits, int *__restrict__ error) {
+    qk::pdl_launch();  // the next kernel may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
+    extern __shared__ __align__(16) uint8_t dec_smem[];
+    __shared__ int is_last;
+    const uint32_t split = blockIdx.x, ky = blockIdx.y, b = blockIdx.z;
+    const int pos = positions[b], seq = seq_index[b];
+    const bool valid = pos >= 0 && (uint32_t)pos < s_max && seq >= 0 && (uint32_t)seq < n_seq;
+    if (!valid && threadIdx.x == 0 && error) atomicOr(error, 4);  // skipped and reported, as rope_cache_kernel does
+    const int pos_in = min(max(pos, 0), (int)s_max - 1);
+    const FreshKey fresh{k, v, cache_k, cache_v, cos_sin + (size_t)pos_in * 128, pos, seq, valid};
+    const SubBlock sb{threadIdx.x, 0};
+    decode_attention_mma_body<true>(sb, carve_dec_attn(dec_smem), q, cache_k, cache_v, kv_len[b], partial, n_heads,
+                                    n_kv, gq, s_max, chunk, n_splits, split, ky, b, fresh);
+    __threadfence();
+    __syncthreads();
+    const uint32_t group = n_heads / n_kv, subs = (group + gq - 1) / gq;
+    if (threadIdx.x == 0) {
+        uint32_t *ticket = tickets + (size_t)b * n_kv * subs + ky;
+        const uint32_t old = atomicAdd(ticket, 1u);
+        is_last = old == n_splits - 1;
+        if (is_last) *ticket = 0;
+    }
+    __syncthreads();
+    if (is_last) {
+        __threadfence();
+        const uint32_t kvh = ky / subs, hsub = ky % subs, h0 = kvh * group + hsub * gq;
+        const uint32_t rows = min(gq, group - hsub * gq);
+        for (uint32_t r = threadIdx.x / 32; r < rows; r += kMmaDecWarps) {
+            const size_t head = (size_t)b * n_heads + h0 + r;
+            decode_combine_warp<4, 32>(threadIdx.x % 32, partial + head * n_splits * 130, out + head * 128, 128,
+                                       n_splits, 0, 32);
+        }
+    }
+}
+
 // ------------------------------------------------------------------ prefill attention, tensor cores
 // Causal attention of T new positions of ONE sequence against the cache (which already holds
 // their own keys and values): the attention of a batched prompt prefill.  Same contract as the
@@ -1349,6 +1400,46 @@ qk_status qk_decode_attention(qk_ctx *ctx, const float *q, const void *cache_k,
                               size_t s_max, size_t n_splits, float *scratch, float *out) {
     return qk_decode_attention_feed(ctx, q, cache_k, cache_v, kv_dtype, kv_len, batch, n_heads, n_kv_heads,
                                     head_dim, s_max, n_splits, scratch, out, QK_F32, nullptr);
+}
+
+size_t qk_decode_attention_rope_scratch(size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                                        size_t n_splits) {
+    // the partials, then one ticket per (sequence, kv-head block) - at most one per head
+    return qk_decode_attention_scratch(batch, n_heads, head_dim, n_splits) +
+           batch * (n_heads > n_kv_heads ? n_heads : n_kv_heads) * sizeof(uint32_t);
+}
+
+qk_status qk_decode_attention_rope(qk_ctx *ctx, const float *q, const float *k, const float *v,
+                                   const float *cos_sin, const int32_t *positions, const int32_t *seq_index,
+                                   void *cache_k, void *cache_v, int32_t kv_dtype, const int32_t *kv_len,
+                                   size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                                   size_t s_max, size_t n_seq, size_t n_splits, float *scratch, float *out) {
+    qk_ctx *c;
+    qk_status st = enter(ctx, &c);
+    if (st != QK_OK) return st;
+    if (kv_dtype != QK_BF16 || head_dim != 128)
+        return qk::fail(QK_ERR_VALUE, "the one-launch decode attention needs a bfloat16 cache and head_dim 128, "
+                        "got cache tag %d and head_dim %zu", kv_dtype, head_dim);
+    if (n_kv_heads == 0 || n_heads % n_kv_heads != 0)
+        return qk::fail(QK_ERR_VALUE, "n_kv_heads must divide n_heads: n_heads=%zu, n_kv_heads=%zu",
+                        n_heads, n_kv_heads);
+    if (n_splits == 0 || batch == 0) return qk::fail(QK_ERR_VALUE, "empty decode attention");
+    if (n_splits > 128)
+        return qk::fail(QK_ERR_VALUE, "at most 128 key splits are supported, got %zu", n_splits);
+    if ((st = qk::error_word(c)) != QK_OK) return st;
+    const size_t group = n_heads / n_kv_heads, gq8 = group < 8 ? group : 8, subs = qk::ceil_div(group, gq8);
+    const size_t chunk8 = qk::ceil_div(s_max, n_splits);
+    uint32_t *tickets = reinterpret_cast<uint32_t *>(
+        reinterpret_cast<uint8_t *>(scratch) + qk_decode_attention_scratch(batch, n_heads, head_dim, n_splits));
+    dim3 grid((unsigned)n_splits, (unsigned)(n_kv_heads * subs), (unsigned)batch);
+    QK_CUDA(cudaFuncSetAttribute(decode_attention_rope_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kMmaDecSmemBytes));
+    QK_PDL(c, decode_attention_rope_kernel, dim3(grid), dim3(kMmaDecWarps * 32), (size_t)kMmaDecSmemBytes, q, k, v,
+           cos_sin, positions, seq_index, (uint16_t *)cache_k, (uint16_t *)cache_v, kv_len, scratch, tickets, out,
+           (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)gq8, (uint32_t)s_max, (uint32_t)n_seq,
+           (uint32_t)chunk8, (uint32_t)n_splits, (int *)c->d_err.ptr);
+    c->err_armed = true;
+    QK_LAUNCHED(c);
 }
 
 qk_status qk_prefill_attention(qk_ctx *ctx, const float *q, const void *cache_k, const void *cache_v,

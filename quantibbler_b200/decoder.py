@@ -57,6 +57,12 @@ class DecoderConfig:
     # cache, no q/k norms, one GPU and a model narrow enough for its shared memory; other
     # configurations keep the separate launches.
     fused_step_max_batch: int = 0
+    # RoPE, cache append, attention and combine of a step in one launch instead of three
+    # (bfloat16 cache, head_dim 128; the same bits).  Pays at small batches, where the step is a
+    # chain of short launches (batch 1: 4.43 -> 4.36 ms); at batch 64 the combine by the last
+    # split of each head group costs more than the two launches it saves (10.96 -> 11.40 ms).
+    fused_attention: bool = True
+    fused_attention_max_batch: int = 8
     prefill_min_tokens: int = 16   # generate(): prompts this long go through the trunk in one pass
     prefill_chunk: int = 2048      # ... in pieces of at most this many positions
 
@@ -222,7 +228,13 @@ class Decoder:
         # least ~128 keys
         want = -(-8 * 148 // max(1, B * self.kv_loc))
         self.n_splits = cfg.n_splits or max(1, min(32, want, max(1, cfg.max_seq // 64)))
-        scratch = _lib.lib().qk_decode_attention_scratch(B, self.h_loc, hd, self.n_splits)
+        # (the one-launch form is the tensor-core attention; a context switched to the scalar
+        # kernel keeps the separate launches)
+        self.fused_attention = (cfg.fused_attention and B <= cfg.fused_attention_max_batch
+                                and cfg.kv_dtype == "bfloat16" and hd == 128
+                                and ctx.set_decode_attention_kernel(-1) != 0)
+        scratch = max(_lib.lib().qk_decode_attention_scratch(B, self.h_loc, hd, self.n_splits),
+                      _lib.lib().qk_decode_attention_rope_scratch(B, self.h_loc, self.kv_loc, hd, self.n_splits))
         self.att_scratch = torch.zeros(scratch // 4 + 4, **f32)
         self.cos_sin = dev_f32(rope_table(cfg))
         self.emb_tag = QK_BF16 if cfg.serving == "bfloat16" else QK_F32
@@ -434,15 +446,23 @@ class Decoder:
                                              (self.k, self.kn, self.qk_norms[li][1], self.kv_loc)):
                     check(lib.qk_rmsnorm(c, _p(src), None, _p(wgt), B * heads, hd, cfg.rms_eps,
                                          self.serving_tag, _p(src), _p(dst)))
-            check(lib.qk_rope_cache(c, _p(self.qn), _p(self.kn), _p(self.v), _p(self.cos_sin),
-                                    _p(self.positions), _p(self.seq_index), _p(self.cache_k[li]),
-                                    _p(self.cache_v[li]), self.kv_tag, B, self.h_loc, self.kv_loc,
-                                    hd, cfg.max_seq, B))
-            check(lib.qk_decode_attention_feed(
-                c, _p(self.qn), _p(self.cache_k[li]), _p(self.cache_v[li]), self.kv_tag,
-                _p(self.kv_len), B, self.h_loc, self.kv_loc, hd, cfg.max_seq, self.n_splits,
-                _p(self.att_scratch), _p(self.attn), self.serving_tag,
-                ctypes.byref(feeds["o"]) if feeds else None))
+            if self.fused_attention and not feeds:
+                # RoPE, cache append, attention and combine in one launch
+                check(lib.qk_decode_attention_rope(
+                    c, _p(self.qn), _p(self.kn), _p(self.v), _p(self.cos_sin), _p(self.positions),
+                    _p(self.seq_index), _p(self.cache_k[li]), _p(self.cache_v[li]), self.kv_tag,
+                    _p(self.kv_len), B, self.h_loc, self.kv_loc, hd, cfg.max_seq, B, self.n_splits,
+                    _p(self.att_scratch), _p(self.attn)))
+            else:
+                check(lib.qk_rope_cache(c, _p(self.qn), _p(self.kn), _p(self.v), _p(self.cos_sin),
+                                        _p(self.positions), _p(self.seq_index), _p(self.cache_k[li]),
+                                        _p(self.cache_v[li]), self.kv_tag, B, self.h_loc, self.kv_loc,
+                                        hd, cfg.max_seq, B))
+                check(lib.qk_decode_attention_feed(
+                    c, _p(self.qn), _p(self.cache_k[li]), _p(self.cache_v[li]), self.kv_tag,
+                    _p(self.kv_len), B, self.h_loc, self.kv_loc, hd, cfg.max_seq, self.n_splits,
+                    _p(self.att_scratch), _p(self.attn), self.serving_tag,
+                    ctypes.byref(feeds["o"]) if feeds else None))
             self._linears(li, ["o"], self.attn, [self.delta_attn])
             self._all_reduce(self.delta_attn)
             self._norm(0, post_w, feeds["gu"] if feeds else None, xa, xb)

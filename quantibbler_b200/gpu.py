@@ -168,8 +168,16 @@ def _gpu_attention_dev(self, shape: AttentionShape, q_ptr: int, k_ptr: int, v_pt
 
 
 def _set_sage_kernel(self, which: int) -> int:
-    """1: INT8 tensor-core Sage kernel where the shape allows (default); 0: dp4a kernel."""
+    """2: the tcgen05 Sage kernel where the shape allows (default), else as 1; 1: the mma.sync
+    INT8 tensor-core kernel where the shape allows, else as 0; 0: the dp4a kernel.  Returns the
+    previous choice."""
     return int(_lib.lib().qk_set_sage_kernel(self._h, int(which)))
+
+
+def _set_decode_attention_kernel(self, which: int) -> int:
+    """1: tensor-core decode attention where the cache allows (default); 0: the scalar kernel;
+    anything else only reads the choice.  Returns the previous choice."""
+    return int(_lib.lib().qk_set_decode_attention_kernel(self._h, int(which)))
 
 
 def _gpu_sage_quantize(self, shape: AttentionShape, query, key, value, block_size: int) -> dict:
@@ -202,6 +210,7 @@ GpuContext.attention = _gpu_attention
 GpuContext.attention_sage = _gpu_attention_sage
 GpuContext.attention_dev = _gpu_attention_dev
 GpuContext.set_sage_kernel = _set_sage_kernel
+GpuContext.set_decode_attention_kernel = _set_decode_attention_kernel
 
 
 def _set_wait_limit(self, polls: int) -> int:

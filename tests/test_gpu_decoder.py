@@ -456,3 +456,29 @@ def test_whole_step_kernel_is_refused_outside_its_limits(gpu_ctx):
     cfg = step_cfg(max_batch=9, fused_step_max_batch=9)   # more tokens than the kernel takes
     dec = Decoder(gpu_ctx, cfg, random_model(cfg, STEP_RANKS, seed=6))
     assert dec.step_kernel is None
+
+
+@pytest.mark.parametrize("serving", ["float32", "bfloat16"])
+def test_one_launch_attention_reproduces_the_three_launches(gpu_ctx, serving):
+    """RoPE + cache append + split attention + combine in one kernel (the rotation in the
+    fragment loader, the append by the block whose keys include the new position, the combine
+    by the last split to finish) against rope_cache + decode_attention + combine: the same
+    device functions, so logits, tokens and cache contents must be identical - over enough
+    steps that the appended position crosses from one key split into the next."""
+    cfg = step_cfg(serving=serving, max_batch=2)
+    weights = random_model(cfg, STEP_RANKS, seed=78)
+    three = Decoder(gpu_ctx, step_cfg(serving=serving, max_batch=2, fused_attention=False), weights)
+    one = Decoder(gpu_ctx, step_cfg(serving=serving, max_batch=2), weights)
+    assert one.fused_attention and not three.fused_attention
+    for dec in (three, one):
+        dec.start([9, 41], [0, 5])
+    for step in range(30):
+        for dec in (three, one):
+            dec.step()
+        gpu_ctx.synchronize()
+        assert np.array_equal(one.logits.cpu().numpy(), three.logits.cpu().numpy()), step
+        for dec in (three, one):
+            dec.advance()
+    # (sequence 1 started at position 5 over rows nobody wrote: both caches hold zeros there)
+    for li in range(cfg.n_layers):
+        assert torch_equal(one.cache_k[li], three.cache_k[li]) and torch_equal(one.cache_v[li], three.cache_v[li])
