@@ -896,6 +896,46 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
+    // The same for an iteration whose 128 keys and two blocks all exist (every one but possibly
+    // the last of the sequence): nothing to clamp, so a thread's source addresses are its
+    // addresses of iteration 0 plus a stride, and its destinations are constants of the buffer.
+    const int key_a = tid / 8, piece = tid % 8, pblk = piece / 4;
+    const uint32_t k_off_a = (uint32_t)(swz(Kb, key_a, piece) - Kb), k_off_b = (uint32_t)(swz(Kb, key_a + 64, piece) - Kb);
+    const uint32_t v_off_a = (uint32_t)(swz(Vb, key_a, piece) - Vb), v_off_b = (uint32_t)(swz(Vb, key_a + 64, piece) - Vb);
+    const int8_t *k_src = a.kc + (plane * S + key_a) * a.dpad + piece * 16;
+    const int8_t *v_src = a.vc + ((plane * n_blocks + pblk) * (size_t)kUD + key_a) * a.bpad + (piece % 4) * 16;
+    const int8_t *m_src = a.kmean_digits + ((plane * n_blocks + tid / 64) * 8 + (tid / 8) % 8) * (size_t)a.dpad + piece * 16;
+    const uint32_t m_off = tid < 128 ? (uint32_t)(swz(Kb, kUKeys + 8 * (int)(tid / 64) + (int)(tid / 8) % 8, piece) - Kb) : 0;
+    auto stage_full = [&](int it, int buf) {
+        uint8_t *Kt = Kb + buf * kUKBytes, *Vt = Vb + buf * kUVBytes;
+        float *kscale = scales + buf * kUScaleFloats, *vscale = kscale + kUKeys, *mscale = vscale + 2 * kUD;
+        const int8_t *ks = k_src + (size_t)it * kUKeys * a.dpad;
+        cp_async16(Kt + k_off_a, ks);
+        cp_async16(Kt + k_off_b, ks + (size_t)64 * a.dpad);
+        const int8_t *vs = v_src + (size_t)it * 2 * kUD * a.bpad;
+        cp_async16(Vt + v_off_a, vs);
+        cp_async16(Vt + v_off_b, vs + (size_t)64 * a.bpad);
+        if (tid < 128) {
+            cp_async16(Kt + m_off, m_src + (size_t)it * 2 * 8 * a.dpad);
+        } else if (tid < 256) {
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(kscale + (tid - 128))),
+                         "l"(a.ks + plane * S + it * kUKeys + (int)tid - 128)
+                         : "memory");
+        } else if (tid < 320) {
+            const int t2 = tid - 256;
+            cp_async16(vscale + t2 * 4, a.vs + (plane * n_blocks + 2 * it) * (size_t)kUD + t2 * 4);
+        } else if (tid < 322) {
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(mscale + (tid - 320))),
+                         "l"(a.kmean_scale + plane * n_blocks + 2 * it + (int)tid - 320)
+                         : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto stage_any = [&](int it, int buf) {
+        if ((it + 1) * kUKeys <= S && 2 * it + 1 < n_blocks) stage_full(it, buf);
+        else stage(it, buf);
+    };
+
     const int i_blk_max = min((int)dm.Sq - 1, q0 + kUQ - 1);
     const int jb_hi = causal ? i_blk_max / kUBlk + 1 : n_blocks;
     const int n_it = (jb_hi + 1) / 2;
@@ -903,8 +943,8 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
         const int row = idx / 8, piece = idx % 8;
         cp_async16(swz(Qs, row, piece), a.qc + (row_base + min(q0 + row, (int)dm.Sq - 1)) * a.dpad + piece * 16);
     }
-    stage(0, 0);  // (in one group with Q; n_it >= 1)
-    if (n_it > 1) stage(1, 1);
+    stage_any(0, 0);  // (in one group with Q; n_it >= 1)
+    if (n_it > 1) stage_any(1, 1);
     const float dq = valid ? a.qs[row_base + i] : 1.f;
 
     float o[32];  // channels 32 g .. 32 g + 31 of row r
@@ -948,18 +988,17 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
     for (int it = 0; it < n_it; ++it) {
         const int buf = it % kUBufs;
         const float *kscale = scales + buf * kUScaleFloats, *mscale = kscale + kUKeys + 2 * kUD;
-        // (the verdict of a wait is taken by the whole CTA: nobody goes on to a barrier the others have left)
-        if (!__syncthreads_and(mbar_wait(bar_s, it & 1, abort_flag, limit))) {
-            dead = true;
-            break;
-        }
+        // A warp whose wait gives up skips what needs the products and votes at the next CTA
+        // barrier: the verdict is taken by the whole CTA, nobody goes on to a barrier the others
+        // have left.
+        bool ok = mbar_wait(bar_s, it & 1, abort_flag, limit);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
         // ---- this thread's 32 scores of its Sage block
         const int jb = 2 * it + my_blk, j0 = jb * kUBlk, kj = min(kUBlk, S - j0);
         const bool live = jb < jb_hi;
-        float shift;
-        {
+        float shift = 0.f;
+        if (ok) {
             uint32_t c0, c1, c2, c3;
             asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
                          : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
@@ -996,23 +1035,25 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
         }
         xm[g * kUQ + r] = bm;
         // ---- the products of the iteration before have had this long to finish: fold them in
-        if (it > 0) {
-            if (!__syncthreads_and(mbar_wait(bar_pv, (it - 1) & 1, abort_flag, limit))) {
-                dead = true;
-                break;
+        if (it > 0 && ok) {
+            ok = mbar_wait(bar_pv, (it - 1) & 1, abort_flag, limit);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                fold_pv(it - 1, prev_alpha_a, prev_alpha_b);
             }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            fold_pv(it - 1, prev_alpha_a, prev_alpha_b);
         }
         // the tiles of iteration it + 1 (staged an iteration ago) have landed; after the barrier
         // every thread has read S of this iteration and PV of the last one out of tensor memory
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
+        if (!__syncthreads_and(ok)) {
+            dead = true;
+            break;
+        }
         if (it + 1 < n_it && tid == 0) issue_s(it + 1);  // runs while the threads exponentiate
         __syncwarp();
-        if (it + 2 < n_it) stage(it + 2, (it + 2) % kUBufs);
+        if (it + 2 < n_it) stage_any(it + 2, (it + 2) % kUBufs);
         // ---- the row's maxima after block a and after block b (the same in its four threads)
         const float bm_a = fmaxf(xm[r], xm[kUQ + r]), bm_b = fmaxf(xm[2 * kUQ + r], xm[3 * kUQ + r]);
         const float mn_a = fmaxf(m, bm_a);
@@ -1026,6 +1067,9 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
         constexpr float kLog2e = 1.4426950408889634f, kLog2_127 = 6.988684686772166f;
         const float off = (mn == -INFINITY) ? -INFINITY : kLog2_127 - mn * kLog2e;
         float es = 0.f;
+        // a masked score is -inf: ex2 gives 0.  A row without any key so far has mn = -inf, whose
+        // difference with a score of -inf would be NaN: only a masked iteration can have such rows
+        const bool empty_row = masked && mn == -INFINITY;
 #pragma unroll
         for (int piece = 0; piece < 2; ++piece) {
             uint32_t w[4];
@@ -1034,8 +1078,8 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
                 int c[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    // a masked score is -inf: ex2 gives 0; a row without any key so far has mn = -inf
-                    const float pe = (mn == -INFINITY) ? 0.f : ex2_approx(fmaf(s[16 * piece + 4 * q + e], kLog2e, off));
+                    float pe = ex2_approx(fmaf(s[16 * piece + 4 * q + e], kLog2e, off));
+                    if (masked) pe = empty_row ? 0.f : pe;  // (the branch is the same for the whole CTA)
                     es += pe;
                     c[e] = __float2int_rn(pe);  // in [0, 127]: rounds to nearest even like rint
                 }
