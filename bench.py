@@ -618,6 +618,8 @@ def main() -> None:
     ap.add_argument("--kernel", type=int, default=-1, help="GEMV kernel override (debug)")
     ap.add_argument("--shape", default="", help="dout,din,rank override (debug; not the metric)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--e2e-parts", type=int, default=0,
+                    help="sub-groups of the host-buffer pipeline (0: HostLayerGroup's own choice)")
     ap.add_argument("--e2e-applies", type=int, default=296,
                     help="layers of the one-call-per-layer leg (0 switches both end-to-end legs off)")
     ap.add_argument("--workload", default="gemv", choices=["gemv", "decode", "prefill", "attention"])
@@ -765,7 +767,7 @@ def main() -> None:
             if n_e2e == 0:
                 raise RuntimeError("end-to-end legs switched off (--e2e-applies 0)")
             from quantibbler_b200.gpu import HostLayerGroup
-            host_step = HostLayerGroup(ctx, layers)
+            host_step = HostLayerGroup(ctx, layers, n_parts=args.e2e_parts or None)
             for _ in range(3):
                 host_step.apply(x_host, y_host)
             torch.cuda.synchronize()   # no collective inside the guarded leg

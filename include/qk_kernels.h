@@ -291,6 +291,17 @@ qk_status qk_plan_create_gated(qk_ctx *ctx, const qk_layer *const *layers,
                                const float *const *gate_ptrs, const float *const *up_ptrs,
                                float *const *y_ptrs, size_t n_inst, qk_group **out);
 qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group);
+/* Many independent applies with HOST buffers as a pipeline: groups[p] (made by qk_group_create
+ * over rows first_row[p] .. first_row[p+1] of x_dev / y_dev) has its inputs copied up from
+ * x_host, runs, and has its outputs copied down to y_host, on three streams, so that the upload
+ * of one group, the kernels of the previous one and the download of the one before overlap (the
+ * link is full duplex).  x_host [rows][din] and y_host [rows][dout] should be pinned memory;
+ * returns when y_host is complete.  This is what a caller with all same-shape layers of a
+ * step, or one layer for many requests, uses instead of one qk_layer_apply_host per layer
+ * (PackedLayer::apply, engine/mod.rs:416-431). */
+qk_status qk_groups_apply_host(qk_ctx *ctx, const qk_group *const *groups, const size_t *first_row,
+                               size_t n_groups, const float *x_host, float *y_host, float *x_dev,
+                               float *y_dev, size_t din, size_t dout);
 void qk_group_free(qk_group *group);
 /* ---- the blocks of a decode step as one kernel ---------------------------------------
  * transformer_forward (engine/mod.rs:878-945) runs, per block, norm -> q/k/v -> RoPE + cache

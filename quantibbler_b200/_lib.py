@@ -87,6 +87,8 @@ _SIGNATURES = {
     "qk_decode_attention_rope": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                            c_void_p, c_void_p, c_int32, c_void_p, c_size_t, c_size_t, c_size_t,
                                            c_size_t, c_size_t, c_size_t, c_size_t, c_void_p, c_void_p]),
+    "qk_groups_apply_host": (c_int32, [c_void_p, POINTER(c_void_p), POINTER(c_size_t), c_size_t, c_void_p,
+                                       c_void_p, c_void_p, c_void_p, c_size_t, c_size_t]),
     "qk_decode_step_create": (c_int32, [c_void_p, c_void_p, POINTER(c_void_p)]),
     "qk_decode_step_run": (c_int32, [c_void_p, c_void_p]),
     "qk_decode_step_free": (None, [c_void_p]),

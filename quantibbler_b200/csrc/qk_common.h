@@ -77,6 +77,9 @@ struct qk_ctx {
         bool in_flight = false;
     } h_pinned[kPinnedSlots];
     int h_pinned_next = 0;
+    // the copy streams and events of the host-buffer pipeline (qk_groups_apply_host), made on first use
+    cudaStream_t up_stream = nullptr, down_stream = nullptr;
+    std::vector<cudaEvent_t> pipe_events;
     // A block of at least `bytes`, free to be overwritten; *slot names it for pinned_done().
     qk_status pinned(size_t bytes, void **out, int *slot);
     // Call after the asynchronous copy out of the block has been issued on `stream`.

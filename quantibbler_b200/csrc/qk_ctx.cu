@@ -158,6 +158,9 @@ void qk_gpu_free(qk_ctx *ctx) {
     cudaSetDevice(ctx->device);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+    if (ctx->up_stream) cudaStreamDestroy(ctx->up_stream);
+    if (ctx->down_stream) cudaStreamDestroy(ctx->down_stream);
+    for (cudaEvent_t e : ctx->pipe_events) cudaEventDestroy(e);
     ctx->d_packed.release();
     ctx->d_in.release();
     ctx->d_out.release();

@@ -1875,6 +1875,57 @@ qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group) {
                        c->gemv_kernel, group->mixed, group->fed);
 }
 
+qk_status qk_groups_apply_host(qk_ctx *ctx, const qk_group *const *groups, const size_t *first_row,
+                               size_t n_groups, const float *x_host, float *y_host, float *x_dev,
+                               float *y_dev, size_t din, size_t dout) {
+    if (!groups || !first_row || !x_host || !y_host || !x_dev || !y_dev || n_groups == 0)
+        return qk::fail(QK_ERR_VALUE, "qk_groups_apply_host: groups, rows and buffers must be given");
+    qk_ctx *c;
+    qk_status st = qk::resolve_ctx(ctx, &c);
+    if (st != QK_OK) return st;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    for (size_t p = 0; p < n_groups; ++p) {
+        if (!groups[p]) return qk::fail(QK_ERR_VALUE, "qk_groups_apply_host: group %zu is null", p);
+        if (groups[p]->device != c->device)
+            return qk::fail(QK_ERR_VALUE, "group lives on device %d, context on device %d",
+                            groups[p]->device, c->device);
+        if (first_row[p + 1] - first_row[p] != groups[p]->n_inst)
+            return qk::fail(QK_ERR_VALUE, "group %zu holds %zu instances, its rows say %zu", p,
+                            groups[p]->n_inst, first_row[p + 1] - first_row[p]);
+    }
+    if (!c->up_stream) QK_CUDA(cudaStreamCreateWithFlags(&c->up_stream, cudaStreamNonBlocking));
+    if (!c->down_stream) QK_CUDA(cudaStreamCreateWithFlags(&c->down_stream, cudaStreamNonBlocking));
+    while (c->pipe_events.size() < 2 * n_groups + 1) {
+        cudaEvent_t e;
+        QK_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        c->pipe_events.push_back(e);
+    }
+    // what is on the launch stream already (a previous step's kernels) no longer reads x_dev or
+    // writes y_dev once this event has passed
+    cudaEvent_t before = c->pipe_events[2 * n_groups];
+    QK_CUDA(cudaEventRecord(before, c->stream));
+    QK_CUDA(cudaStreamWaitEvent(c->up_stream, before, 0));
+    QK_CUDA(cudaStreamWaitEvent(c->down_stream, before, 0));
+    for (size_t p = 0; p < n_groups; ++p) {
+        const size_t lo = first_row[p], n = first_row[p + 1] - lo;
+        cudaEvent_t uploaded = c->pipe_events[2 * p], computed = c->pipe_events[2 * p + 1];
+        QK_CUDA(cudaMemcpyAsync(x_dev + lo * din, x_host + lo * din, n * din * sizeof(float),
+                                cudaMemcpyHostToDevice, c->up_stream));
+        QK_CUDA(cudaEventRecord(uploaded, c->up_stream));
+        QK_CUDA(cudaStreamWaitEvent(c->stream, uploaded, 0));
+        st = launch_both(c, &groups[p]->shape, (const StageParams *)groups[p]->params, groups[p]->n_inst,
+                         c->gemv_kernel, groups[p]->mixed, groups[p]->fed);
+        if (st != QK_OK) return st;
+        QK_CUDA(cudaEventRecord(computed, c->stream));
+        QK_CUDA(cudaStreamWaitEvent(c->down_stream, computed, 0));
+        QK_CUDA(cudaMemcpyAsync(y_host + lo * dout, y_dev + lo * dout, n * dout * sizeof(float),
+                                cudaMemcpyDeviceToHost, c->down_stream));
+    }
+    QK_CUDA(cudaStreamSynchronize(c->down_stream));
+    return QK_OK;
+}
+
 void qk_group_free(qk_group *g) {
     if (!g) return;
     cudaSetDevice(g->device);

@@ -408,42 +408,34 @@ class HostLayerGroup:
         self.x_dev = torch.zeros((n, first.din), dtype=torch.float32, device="cuda")
         self.y_dev = torch.zeros((n, first.dout), dtype=torch.float32, device="cuda")
         # sub-groups of at least ~300 layers keep every launch in its many-instance form
+        # (measured on 2368 config-0 layers: 4 parts 2200 GB/s, 8 parts 2550, 12 parts 2120)
         if n_parts is None:
-            n_parts = max(1, min(4, n // 296))
+            n_parts = max(1, min(8, n // 296))
         bounds = [n * i // n_parts for i in range(n_parts + 1)]
         self.parts = []
         for lo, hi in zip(bounds[:-1], bounds[1:]):
-            group = LayerGroup(ctx, self.layers[lo:hi], self.x_dev[lo:hi].data_ptr(),
-                               self.y_dev[lo:hi].data_ptr())
-            self.parts.append((lo, hi, group, torch.cuda.Event(), torch.cuda.Event()))
-        self.up, self.down = torch.cuda.Stream(), torch.cuda.Stream()
+            self.parts.append(LayerGroup(ctx, self.layers[lo:hi], self.x_dev[lo:hi].data_ptr(),
+                                         self.y_dev[lo:hi].data_ptr()))
+        self._groups = (ctypes.c_void_p * n_parts)(*[g._h for g in self.parts])
+        self._rows = (ctypes.c_size_t * (n_parts + 1))(*bounds)
 
     def apply(self, x_host, y_host) -> None:
-        """``y_host[i] = layer_i(x_host[i])`` for every layer; returns when ``y_host`` is valid."""
-        torch = self.torch
+        """``y_host[i] = layer_i(x_host[i])`` for every layer; returns when ``y_host`` is valid.
+        One library call (``qk_groups_apply_host``) queues the whole pipeline."""
         if tuple(x_host.shape) != tuple(self.x_dev.shape) or tuple(y_host.shape) != tuple(
                 self.y_dev.shape):
             raise KernelError(f"host buffers must be {tuple(self.x_dev.shape)} and "
                               f"{tuple(self.y_dev.shape)}, got {tuple(x_host.shape)} and "
                               f"{tuple(y_host.shape)}")
-        run = torch.cuda.ExternalStream(self.ctx.stream)   # the stream the kernels launch on
-        self.up.wait_stream(run)       # the previous call's kernels no longer read x_dev
-        self.down.wait_stream(run)
-        for lo, hi, group, uploaded, computed in self.parts:
-            with torch.cuda.stream(self.up):
-                self.x_dev[lo:hi].copy_(x_host[lo:hi], non_blocking=True)
-                uploaded.record(self.up)
-            run.wait_event(uploaded)
-            with torch.cuda.stream(run):
-                group.apply()
-                computed.record(run)
-            self.down.wait_event(computed)
-            with torch.cuda.stream(self.down):
-                y_host[lo:hi].copy_(self.y_dev[lo:hi], non_blocking=True)
-        self.down.synchronize()
+        if not (x_host.is_contiguous() and y_host.is_contiguous()):
+            raise KernelError("host buffers must be contiguous")
+        check(_lib.lib().qk_groups_apply_host(
+            self.ctx.handle, self._groups, self._rows, len(self.parts), ctypes.c_void_p(x_host.data_ptr()),
+            ctypes.c_void_p(y_host.data_ptr()), ctypes.c_void_p(self.x_dev.data_ptr()),
+            ctypes.c_void_p(self.y_dev.data_ptr()), self.layers[0].din, self.layers[0].dout))
 
     def close(self) -> None:
-        for _, _, group, _, _ in self.parts:
+        for group in self.parts:
             group.close()
 
 
