@@ -947,9 +947,12 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
     if (n_it > 1) stage_any(1, 1);
     const float dq = valid ? a.qs[row_base + i] : 1.f;
 
-    float o[32];  // channels 32 g .. 32 g + 31 of row r
+    // channels 32 g .. 32 g + 31 of row r, in pairs: the per-element arithmetic of this kernel
+    // runs on the packed float32 instructions (two IEEE operations per issue slot: the same
+    // results, half the instructions)
+    float2 o[16];
 #pragma unroll
-    for (int c = 0; c < 32; ++c) o[c] = 0.f;
+    for (int c = 0; c < 16; ++c) o[c] = make_float2(0.f, 0.f);
     float m = -INFINITY, l = 0.f;
     float prev_alpha_a = 0.f, prev_alpha_b = 0.f;  // of the iteration whose PV is still to be folded in
     const uint32_t idesc_s = umma_idesc_i8(kUSRows), idesc_pv = umma_idesc_i8(kUD);
@@ -974,9 +977,12 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
             tmem_ld32(my_tmem + (it & 1) * kURegion + kUD * blk + 32 * g, v);
             tmem_ld_wait();
             const float al = blk ? alpha_b : alpha_a;
-            const float *vd = vscale + kUD * blk + 32 * g;
+            const float2 al2 = make_float2(al, al);
+            const float2 *vd = reinterpret_cast<const float2 *>(vscale + kUD * blk + 32 * g);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = fmaf(al, o[e], (float)(int)v[e] * vd[e]);
+            for (int e = 0; e < 16; ++e)
+                o[e] = __ffma2_rn(al2, o[e],
+                                  __fmul2_rn(make_float2((float)(int)v[2 * e], (float)(int)v[2 * e + 1]), vd[e]));
         }
     };
     if (n_it > 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
@@ -1027,10 +1033,15 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
                 bm = fmaxf(bm, sc);
             }
         } else {
+            const float2 dq2 = make_float2(dq, dq), shift2 = make_float2(shift, shift);
+            const float2 *ksc2 = reinterpret_cast<const float2 *>(ksc);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-                s[e] = fmaf((float)(int)v[e] * dq, ksc[e], shift);
-                bm = fmaxf(bm, s[e]);
+            for (int e = 0; e < 16; ++e) {
+                const float2 sc = __ffma2_rn(
+                    __fmul2_rn(make_float2((float)(int)v[2 * e], (float)(int)v[2 * e + 1]), dq2), ksc2[e], shift2);
+                s[2 * e] = sc.x;
+                s[2 * e + 1] = sc.y;
+                bm = fmaxf(bm, fmaxf(sc.x, sc.y));
             }
         }
         xm[g * kUQ + r] = bm;
@@ -1066,10 +1077,11 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
         // P scaled by 127 (the static P scale): 127 exp(s - m) = exp2(s log2e - m log2e + log2 127)
         constexpr float kLog2e = 1.4426950408889634f, kLog2_127 = 6.988684686772166f;
         const float off = (mn == -INFINITY) ? -INFINITY : kLog2_127 - mn * kLog2e;
-        float es = 0.f;
         // a masked score is -inf: ex2 gives 0.  A row without any key so far has mn = -inf, whose
         // difference with a score of -inf would be NaN: only a masked iteration can have such rows
         const bool empty_row = masked && mn == -INFINITY;
+        const float2 log2e2 = make_float2(kLog2e, kLog2e), off2 = make_float2(off, off);
+        float2 es2 = make_float2(0.f, 0.f);  // the sums over the even and the odd columns
 #pragma unroll
         for (int piece = 0; piece < 2; ++piece) {
             uint32_t w[4];
@@ -1077,17 +1089,20 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
             for (int q = 0; q < 4; ++q) {
                 int c[4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float pe = ex2_approx(fmaf(s[16 * piece + 4 * q + e], kLog2e, off));
-                    if (masked) pe = empty_row ? 0.f : pe;  // (the branch is the same for the whole CTA)
-                    es += pe;
-                    c[e] = __float2int_rn(pe);  // in [0, 127]: rounds to nearest even like rint
+                for (int e = 0; e < 4; e += 2) {
+                    const int at = 16 * piece + 4 * q + e;
+                    const float2 arg = __ffma2_rn(make_float2(s[at], s[at + 1]), log2e2, off2);
+                    float2 pe = make_float2(ex2_approx(arg.x), ex2_approx(arg.y));
+                    if (masked && empty_row) pe = make_float2(0.f, 0.f);  // (`masked` is the same for the whole CTA)
+                    es2 = __fadd2_rn(es2, pe);
+                    c[e] = __float2int_rn(pe.x);  // in [0, 127]: rounds to nearest even like rint
+                    c[e + 1] = __float2int_rn(pe.y);
                 }
                 w[q] = pack_codes(c);
             }
             *reinterpret_cast<uint4 *>(swz(Ps, (int)r, 2 * g + piece)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
-        xe[g * kUQ + r] = es;
+        xe[g * kUQ + r] = es2.x + es2.y;
         // ---- PV into the region S has been read out of
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();
@@ -1133,8 +1148,9 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
     if (valid && !dead) {
         float *dst = a.out + (row_base + i) * kUD + 32 * g;
 #pragma unroll
-        for (int c = 0; c < 32; c += 4)
-            *reinterpret_cast<float4 *>(dst + c) = make_float4(o[c] / l, o[c + 1] / l, o[c + 2] / l, o[c + 3] / l);
+        for (int c = 0; c < 16; c += 2)
+            *reinterpret_cast<float4 *>(dst + 2 * c) =
+                make_float4(o[c].x / l, o[c].y / l, o[c + 1].x / l, o[c + 1].y / l);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
