@@ -818,7 +818,7 @@ def main() -> None:
                    "ms_per_step": e2e_step_ms,
                    "call": "HostLayerGroup.apply(x_host, y_host): the step's inputs from pinned "
                            "host memory, the step's launches, its outputs back to pinned host "
-                           "memory, synchronise (the layers go through in four sub-groups, upload, "
+                           "memory, synchronise (one library call; the layers go through in up to eight sub-groups, upload, "
                            "kernels and download of neighbouring sub-groups overlapping)",
                    "per_layer_call": per_layer}
         else:

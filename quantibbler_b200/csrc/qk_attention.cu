@@ -124,6 +124,23 @@ attention_exact_kernel(const float *__restrict__ q, const float *__restrict__ k,
 }
 
 // ------------------------------------------------------------------ Sage quantisers
+// The tcgen05 kernel (head_dim = val_dim = 128, key block 64) takes its operands as RECORDS: one
+// per (plane, pair of key blocks), laid out in global memory byte for byte as the kernel wants
+// them in shared memory, so that an iteration's operands arrive by one bulk copy:
+//   [K tile: 144 rows of 128 bytes: the 128 keys' codes, then 2 x 8 mean-digit rows]
+//   [V tile: 128 channel rows of 128 bytes: the codes of block a's 64 keys, then block b's]
+//   [scales: 128 key scales, 2 x 128 channel scales of V, 2 mean units (16 floats reserved)]
+// Tile rows are 128-byte-swizzled: the 16-byte piece p of row r sits at piece p ^ (r & 7).
+// What a ragged sequence leaves unwritten (keys past the end, a missing second block) is never
+// used: those scores are masked before the softmax and the second product is not folded in.
+constexpr uint32_t kURecKBytes = 144 * 128, kURecVBytes = 128 * 128;
+constexpr uint32_t kURecScaleOff = kURecKBytes + kURecVBytes, kURecScaleFloats = 128 + 2 * 128 + 16;
+constexpr uint32_t kURecBytes = kURecScaleOff + kURecScaleFloats * 4;  // what one bulk copy moves
+constexpr uint32_t kURecStride = (kURecBytes + 1023) / 1024 * 1024;
+__host__ __device__ inline uint32_t rec_tile_offset(uint32_t row, uint32_t byte) {
+    return row * 128 + (((byte >> 4) ^ (row & 7)) << 4) + (byte & 15);
+}
+
 __device__ __forceinline__ int quant_code(float x, float delta) {
     // rint half-to-even of x/delta, clamped to +-127 (gpu_attention.rs:132-155)
     float r = rintf(x / delta);
@@ -176,7 +193,7 @@ __global__ void sage_quant_k_kernel(const float *__restrict__ k, int8_t *__restr
                                     float *__restrict__ scale, float *__restrict__ mean,
                                     uint32_t S, uint32_t d, uint32_t dpad, uint32_t block,
                                     uint32_t n_blocks, int8_t *__restrict__ mean_digits,
-                                    float *__restrict__ mean_scale) {
+                                    float *__restrict__ mean_scale, uint8_t *__restrict__ rec) {
     extern __shared__ float mu[];  // d floats
     const uint32_t plane = blockIdx.y, jb = blockIdx.x;
     const uint32_t j0 = jb * block, j1 = min(S, j0 + block), kj = j1 - j0;
@@ -189,6 +206,48 @@ __global__ void sage_quant_k_kernel(const float *__restrict__ k, int8_t *__restr
         mean[((size_t)plane * n_blocks + jb) * d + c] = mval;
     }
     __syncthreads();
+    if (rec) {
+        // record form (d = dpad = 128, block = 64, 128 threads): thread c owns channel c of the
+        // digit rows, lane l of a warp owns channels 4 l .. 4 l + 3 of a key
+        __shared__ float peak_rec[4];
+        uint8_t *rc = rec + ((size_t)plane * ((n_blocks + 1) / 2) + jb / 2) * kURecStride;
+        const uint32_t half = jb % 2, c = threadIdx.x;
+        float peak = fabsf(mu[c]);
+        for (int off = 16; off > 0; off >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, off));
+        if (threadIdx.x % 32 == 0) peak_rec[threadIdx.x / 32] = peak;
+        __syncthreads();
+        peak = fmaxf(fmaxf(peak_rec[0], peak_rec[1]), fmaxf(peak_rec[2], peak_rec[3]));
+        const float unit = peak > 0.f ? peak / 8000000.f : 1.f;   // |fixed| <= 8e6 < 127 * 65536
+        int v = (int)rintf(mu[c] / unit);
+        const int d2 = ((v + 128) & 255) - 128;
+        v = (v - d2) >> 8;
+        const int d1 = ((v + 128) & 255) - 128;
+        v = (v - d1) >> 8;
+        const uint32_t row0 = 128 + 8 * half;
+        rc[rec_tile_offset(row0, c)] = (uint8_t)(int8_t)v;
+        rc[rec_tile_offset(row0 + 1, c)] = (uint8_t)(int8_t)d1;
+        rc[rec_tile_offset(row0 + 2, c)] = (uint8_t)(int8_t)d2;
+#pragma unroll
+        for (uint32_t dr = 3; dr < 8; ++dr) rc[rec_tile_offset(row0 + dr, c)] = 0;
+        float *scales = reinterpret_cast<float *>(rc + kURecScaleOff);
+        if (threadIdx.x == 0) scales[128 + 2 * 128 + half] = unit;
+        const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+        for (uint32_t j = j0 + warp; j < j1; j += 4) {
+            const float4 x = *reinterpret_cast<const float4 *>(kp + (size_t)j * d + 4 * lane);
+            const float4 mm = *reinterpret_cast<const float4 *>(mu + 4 * lane);
+            const float e0 = x.x - mm.x, e1 = x.y - mm.y, e2 = x.z - mm.z, e3 = x.w - mm.w;
+            float pk = fmaxf(fmaxf(fabsf(e0), fabsf(e1)), fmaxf(fabsf(e2), fabsf(e3)));
+            for (int off = 16; off > 0; off >>= 1) pk = fmaxf(pk, __shfl_xor_sync(0xffffffffu, pk, off));
+            const float delta = pk > 0.f ? pk / 127.f : 1.f;
+            const uint32_t w = (uint32_t)(quant_code(e0, delta) & 0xff) | ((uint32_t)(quant_code(e1, delta) & 0xff) << 8) |
+                               ((uint32_t)(quant_code(e2, delta) & 0xff) << 16) |
+                               ((uint32_t)(quant_code(e3, delta) & 0xff) << 24);
+            const uint32_t row = 64 * half + (j - j0);
+            *reinterpret_cast<uint32_t *>(rc + rec_tile_offset(row, 4 * lane)) = w;
+            if (lane == 0) scales[row] = delta;
+        }
+        return;
+    }
     if (mean_digits) {
         __shared__ float peak_sh[4];
         float peak = 0.f;
@@ -244,7 +303,7 @@ __host__ __device__ inline uint32_t sage_tc_key_slot(uint32_t kk) {
 __global__ void sage_quant_v_kernel(const float *__restrict__ v, int8_t *__restrict__ codes,
                                     float *__restrict__ scale, uint32_t S, uint32_t dv,
                                     uint32_t block, uint32_t bpad, uint32_t n_blocks,
-                                    int permute) {
+                                    int permute, uint8_t *__restrict__ rec) {
     const uint32_t plane = blockIdx.y, jb = blockIdx.x;
     const uint32_t j0 = jb * block, j1 = min(S, j0 + block);
     const float *vp = v + (size_t)plane * S * dv;
@@ -274,9 +333,20 @@ __global__ void sage_quant_v_kernel(const float *__restrict__ v, int8_t *__restr
                         w[q] |= (uint32_t)(code & 0xff) << (8 * e);
                     }
                 }
-                *reinterpret_cast<uint4 *>(cr + 16 * piece) = make_uint4(w[0], w[1], w[2], w[3]);
+                if (rec) {  // record form (dv = 128): row c of the pair's V tile, the block's half of it
+                    uint8_t *rc = rec + ((size_t)plane * ((n_blocks + 1) / 2) + jb / 2) * kURecStride + kURecKBytes;
+                    *reinterpret_cast<uint4 *>(rc + rec_tile_offset(c, 64 * (jb % 2) + 16 * piece)) =
+                        make_uint4(w[0], w[1], w[2], w[3]);
+                } else {
+                    *reinterpret_cast<uint4 *>(cr + 16 * piece) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
             }
-            scale[((size_t)plane * n_blocks + jb) * dv + c] = delta;
+            if (rec) {
+                uint8_t *rc = rec + ((size_t)plane * ((n_blocks + 1) / 2) + jb / 2) * kURecStride;
+                reinterpret_cast<float *>(rc + kURecScaleOff)[128 + 128 * (jb % 2) + c] = delta;
+            } else {
+                scale[((size_t)plane * n_blocks + jb) * dv + c] = delta;
+            }
             continue;
         }
         float peak = 0.f;
@@ -301,6 +371,7 @@ struct SageArgs {
     const float *vs;
     float *out;
     uint32_t dpad, bpad, block, n_blocks;
+    const uint8_t *rec;  // tcgen05 kernel: the records, [plane][pair of blocks][kURecStride]
 };
 
 // Main Sage kernel.  Lane (query, part) owns DPL = dpad/4 (resp. dvpad/4) channels; WPL
@@ -789,13 +860,17 @@ attention_sage_tc_kernel(SageArgs a, AttnDims dm, int causal) {
 // All waits on the MMA barriers are bounded (bit 1 of the context's error word on expiry).
 constexpr int kUQ = 128, kUBlk = 64, kUKeys = 2 * kUBlk, kUD = 128;
 constexpr int kUThreads = 512, kUGroups = kUThreads / kUQ;
+// The warps whose lane 0 issues the S products, the record copies and the PV products.  Each of
+// these instructions (tcgen05.mma, tcgen05.commit, the mbarrier operations, the bulk copy) takes
+// its thread a hundred cycles and more to issue, one after the other: spread over three warps
+// on three schedulers they overlap, and no warp falls far behind the others at the CTA barriers.
+constexpr uint32_t kUWarpS = 0, kUWarpRec = 5, kUWarpPV = 10;
 constexpr int kUSRows = kUKeys + 16;  // keys + 2 x 8 mean-digit rows: N of the S product
-constexpr uint32_t kUQBytes = kUQ * 128, kUKBytes = kUSRows * 128, kUVBytes = kUD * 128, kUPBytes = kUQ * 128;
-constexpr uint32_t kUScaleFloats = kUKeys + 2 * kUD + 16;  // key scales, two sets of channel scales, two mean units
-constexpr int kUBufs = 3;  // K / V / scale buffers: the tiles of an iteration are staged two iterations ahead
-constexpr uint32_t kUSmemBytes = kUQBytes + kUBufs * (kUKBytes + kUVBytes) + kUPBytes + kUBufs * kUScaleFloats * 4 +
-                                 2 * kUGroups * kUQ * 4 + 64;
-constexpr uint32_t kUTmemCols = 512, kURegion = 256;  // two regions of S (then PV) accumulators
+constexpr uint32_t kUQBytes = kUQ * 128, kUPBytes = kUQ * 128;
+constexpr int kUBufs = 3;  // record buffers: an iteration's record is fetched two iterations ahead
+static_assert(kURecKBytes == kUSRows * 128 && kURecVBytes == kUD * 128, "the record holds the kernel's tiles");
+constexpr uint32_t kUSmemBytes = kUQBytes + kUBufs * kURecStride + kUPBytes + 2 * kUGroups * kUQ * 4 + 64;
+constexpr uint32_t kUTmemCols = 512, kUPVCol = 256;  // S (144 columns) at column 0, the two PV accumulators from column 256
 constexpr uint32_t kUWaitLimitDefault = 1u << 22;
 
 // s8 x s8 -> s32, both operands K-major, M = 128, N = n
@@ -821,11 +896,11 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
     extern __shared__ __align__(1024) uint8_t sm_u_raw[];
     // (the swizzled tiles want 1024-byte alignment; the launch asks for 1 KB more than kUSmemBytes)
     uint8_t *sm_u = sm_u_raw + ((1024 - (smem_u32(sm_u_raw) & 1023)) & 1023);
-    uint8_t *Qs = sm_u, *Kb = Qs + kUQBytes, *Vb = Kb + kUBufs * kUKBytes, *Ps = Vb + kUBufs * kUVBytes;
-    float *scales = reinterpret_cast<float *>(Ps + kUPBytes);
-    float *xm = scales + kUBufs * kUScaleFloats, *xe = xm + kUGroups * kUQ;  // [group][row]: block maxima, sums of P
+    uint8_t *Qs = sm_u, *Rb = Qs + kUQBytes, *Ps = Rb + kUBufs * kURecStride;  // Q tile, record buffers, P tile
+    float *xm = reinterpret_cast<float *>(Ps + kUPBytes), *xe = xm + kUGroups * kUQ;  // [group][row]: block maxima, sums of P
     uint64_t *bar_s = reinterpret_cast<uint64_t *>(xe + kUGroups * kUQ), *bar_pv = bar_s + 1, *bar_drain = bar_s + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_drain + 1);
+    uint64_t *bar_rec = bar_s + 3;  // [kUBufs]: a record has landed in its buffer
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_rec + kUBufs);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t tid = threadIdx.x, warp = tid / 32;
     const uint32_t g = tid / kUQ, r = tid % kUQ;  // column group, query row
@@ -842,7 +917,8 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
     if (tid == 0) {
         mbar_init(bar_s, 1);
         mbar_init(bar_pv, 1);
-        mbar_init(bar_drain, 1);
+        mbar_init(bar_drain, 2);
+        for (int bi = 0; bi < kUBufs; ++bi) mbar_init(bar_rec + bi, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -860,80 +936,16 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
 
     // 16-byte piece `piece` of row `row` of a swizzled tile
     auto swz = [](uint8_t *tile, int row, int piece) { return tile + row * 128 + ((piece ^ (row & 7)) << 4); };
-    // Iteration `it` (keys 128 it ..) into buffer `buf`.  Keys past the end of the sequence and
-    // blocks past the last one re-read the last valid ones (their scores are masked before use).
-    auto stage = [&](int it, int buf) {
-        uint8_t *Kt = Kb + buf * kUKBytes, *Vt = Vb + buf * kUVBytes;
-        float *kscale = scales + buf * kUScaleFloats, *vscale = kscale + kUKeys, *mscale = vscale + 2 * kUD;
-        const int j0 = it * kUKeys;
-        for (int idx = tid; idx < kUKeys * 8; idx += kUThreads) {
-            const int key = idx / 8, piece = idx % 8;
-            cp_async16(swz(Kt, key, piece), a.kc + (plane * S + min(j0 + key, S - 1)) * a.dpad + piece * 16);
-        }
-        if (tid < 128) {  // 2 x 8 mean-digit rows, 8 pieces each
-            const int blk = tid / 64, row = (tid / 8) % 8, piece = tid % 8;
-            const int jb = min(2 * it + blk, n_blocks - 1);
-            cp_async16(swz(Kt, kUKeys + 8 * blk + row, piece),
-                       a.kmean_digits + ((plane * n_blocks + jb) * 8 + row) * (size_t)a.dpad + piece * 16);
-        }
-        for (int idx = tid; idx < kUD * 8; idx += kUThreads) {
-            const int ch = idx / 8, piece = idx % 8, blk = piece / 4;
-            const int jb = min(2 * it + blk, n_blocks - 1);
-            cp_async16(swz(Vt, ch, piece), a.vc + ((plane * n_blocks + jb) * (size_t)kUD + ch) * a.bpad + (piece % 4) * 16);
-        }
-        if (tid >= 128 && tid < 256)
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(kscale + (tid - 128))),
-                         "l"(a.ks + plane * S + min(j0 + (int)tid - 128, S - 1))
-                         : "memory");
-        if (tid >= 256 && tid < 320) {
-            const int t2 = tid - 256, blk = t2 / 32, jb = min(2 * it + blk, n_blocks - 1);
-            cp_async16(vscale + blk * kUD + (t2 % 32) * 4, a.vs + (plane * n_blocks + jb) * (size_t)kUD + (t2 % 32) * 4);
-        }
-        if (tid >= 320 && tid < 322)
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(mscale + (tid - 320))),
-                         "l"(a.kmean_scale + plane * n_blocks + min(2 * it + (int)tid - 320, n_blocks - 1))
-                         : "memory");
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-
-    // The same for an iteration whose 128 keys and two blocks all exist (every one but possibly
-    // the last of the sequence): nothing to clamp, so a thread's source addresses are its
-    // addresses of iteration 0 plus a stride, and its destinations are constants of the buffer.
-    const int key_a = tid / 8, piece = tid % 8, pblk = piece / 4;
-    const uint32_t k_off_a = (uint32_t)(swz(Kb, key_a, piece) - Kb), k_off_b = (uint32_t)(swz(Kb, key_a + 64, piece) - Kb);
-    const uint32_t v_off_a = (uint32_t)(swz(Vb, key_a, piece) - Vb), v_off_b = (uint32_t)(swz(Vb, key_a + 64, piece) - Vb);
-    const int8_t *k_src = a.kc + (plane * S + key_a) * a.dpad + piece * 16;
-    const int8_t *v_src = a.vc + ((plane * n_blocks + pblk) * (size_t)kUD + key_a) * a.bpad + (piece % 4) * 16;
-    const int8_t *m_src = a.kmean_digits + ((plane * n_blocks + tid / 64) * 8 + (tid / 8) % 8) * (size_t)a.dpad + piece * 16;
-    const uint32_t m_off = tid < 128 ? (uint32_t)(swz(Kb, kUKeys + 8 * (int)(tid / 64) + (int)(tid / 8) % 8, piece) - Kb) : 0;
-    auto stage_full = [&](int it, int buf) {
-        uint8_t *Kt = Kb + buf * kUKBytes, *Vt = Vb + buf * kUVBytes;
-        float *kscale = scales + buf * kUScaleFloats, *vscale = kscale + kUKeys, *mscale = vscale + 2 * kUD;
-        const int8_t *ks = k_src + (size_t)it * kUKeys * a.dpad;
-        cp_async16(Kt + k_off_a, ks);
-        cp_async16(Kt + k_off_b, ks + (size_t)64 * a.dpad);
-        const int8_t *vs = v_src + (size_t)it * 2 * kUD * a.bpad;
-        cp_async16(Vt + v_off_a, vs);
-        cp_async16(Vt + v_off_b, vs + (size_t)64 * a.bpad);
-        if (tid < 128) {
-            cp_async16(Kt + m_off, m_src + (size_t)it * 2 * 8 * a.dpad);
-        } else if (tid < 256) {
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(kscale + (tid - 128))),
-                         "l"(a.ks + plane * S + it * kUKeys + (int)tid - 128)
-                         : "memory");
-        } else if (tid < 320) {
-            const int t2 = tid - 256;
-            cp_async16(vscale + t2 * 4, a.vs + (plane * n_blocks + 2 * it) * (size_t)kUD + t2 * 4);
-        } else if (tid < 322) {
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(mscale + (tid - 320))),
-                         "l"(a.kmean_scale + plane * n_blocks + 2 * it + (int)tid - 320)
-                         : "memory");
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    auto stage_any = [&](int it, int buf) {
-        if ((it + 1) * kUKeys <= S && 2 * it + 1 < n_blocks) stage_full(it, buf);
-        else stage(it, buf);
+    // The record of iteration `it` (keys 128 it .., the key blocks 2 it and 2 it + 1) into its
+    // buffer: one bulk copy, started by one thread, which completes on the buffer's barrier.
+    const uint8_t *rec_src = a.rec + plane * (size_t)((n_blocks + 1) / 2) * kURecStride;
+    auto stage = [&](int it) {
+        const uint32_t bar = smem_u32(bar_rec + it % kUBufs);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kURecBytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                         smem_u32(Rb + (it % kUBufs) * kURecStride)),
+                     "l"(rec_src + (size_t)it * kURecStride), "r"(kURecBytes), "r"(bar)
+                     : "memory");
     };
 
     const int i_blk_max = min((int)dm.Sq - 1, q0 + kUQ - 1);
@@ -943,8 +955,7 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
         const int row = idx / 8, piece = idx % 8;
         cp_async16(swz(Qs, row, piece), a.qc + (row_base + min(q0 + row, (int)dm.Sq - 1)) * a.dpad + piece * 16);
     }
-    stage_any(0, 0);  // (in one group with Q; n_it >= 1)
-    if (n_it > 1) stage_any(1, 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
     const float dq = valid ? a.qs[row_base + i] : 1.f;
 
     // channels 32 g .. 32 g + 31 of row r, in pairs: the per-element arithmetic of this kernel
@@ -958,45 +969,55 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
     const uint32_t idesc_s = umma_idesc_i8(kUSRows), idesc_pv = umma_idesc_i8(kUD);
     const uint32_t limit = wait_limit ? wait_limit : kUWaitLimitDefault;
     bool dead = false;
+    int dead_it = n_it;  // the iteration that gave up
     uint32_t v[32];
-    auto issue_s = [&](int it) {  // S of iteration `it` into region it % 2 (one thread)
-        const uint32_t kt = smem_u32(Kb + (it % kUBufs) * kUKBytes);
+    auto issue_s = [&](int it) {  // S of iteration `it` (one thread)
+        const uint32_t kt = smem_u32(Rb + (it % kUBufs) * kURecStride);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int k = 0; k < kUD / 32; ++k)
-            umma_i8(tmem_base + (it & 1) * kURegion, umma_desc(smem_u32(Qs) + k * 32), umma_desc(kt + k * 32), idesc_s,
-                    k != 0);
+            umma_i8(tmem_base, umma_desc(smem_u32(Qs) + k * 32), umma_desc(kt + k * 32), idesc_s, k != 0);
         umma_commit(bar_s);
     };
-    // o = alpha * o + PV * dV for the blocks of iteration `it`, whose products have completed
-    auto fold_pv = [&](int it, float alpha_a, float alpha_b) {
-        const float *vscale = scales + (it % kUBufs) * kUScaleFloats + kUKeys;
+    // o = alpha * o + PV * dV for one key block: `v` holds the block's 32 integer sums of this
+    // thread's channels, `vd` points at their scales
+    auto fold_block = [&](float al, const float *vd) {
+        const float2 al2 = make_float2(al, al);
+        const float4 *vd4 = reinterpret_cast<const float4 *>(vd);
 #pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-            if (2 * it + blk >= jb_hi) break;  // (the same for the whole CTA)
-            tmem_ld32(my_tmem + (it & 1) * kURegion + kUD * blk + 32 * g, v);
-            tmem_ld_wait();
-            const float al = blk ? alpha_b : alpha_a;
-            const float2 al2 = make_float2(al, al);
-            const float2 *vd = reinterpret_cast<const float2 *>(vscale + kUD * blk + 32 * g);
-#pragma unroll
-            for (int e = 0; e < 16; ++e)
-                o[e] = __ffma2_rn(al2, o[e],
-                                  __fmul2_rn(make_float2((float)(int)v[2 * e], (float)(int)v[2 * e + 1]), vd[e]));
+        for (int e = 0; e < 8; ++e) {
+            const float4 d = vd4[e];
+            o[2 * e] = __ffma2_rn(al2, o[2 * e],
+                                  __fmul2_rn(make_float2((float)(int)v[4 * e], (float)(int)v[4 * e + 1]), make_float2(d.x, d.y)));
+            o[2 * e + 1] = __ffma2_rn(al2, o[2 * e + 1],
+                                      __fmul2_rn(make_float2((float)(int)v[4 * e + 2], (float)(int)v[4 * e + 3]),
+                                                 make_float2(d.z, d.w)));
         }
     };
-    if (n_it > 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
-    else asm volatile("cp.async.wait_group 0;" ::: "memory");
+    // the channel scales of V of iteration `it`, this thread's 32 channels of block a (block b: + kUD)
+    auto vscale_of = [&](int it) {
+        return reinterpret_cast<const float *>(Rb + (it % kUBufs) * kURecStride + kURecScaleOff) + kUKeys + 32 * g;
+    };
+    const bool lane0 = tid % 32 == 0;
+    if (warp == kUWarpRec && lane0) {
+        stage(0);
+        if (n_it > 1) stage(1);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");  // (the Q tile)
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) issue_s(0);
+    // (if this wait gives up, no product is issued and every wait below gives up in turn)
+    const bool first_landed = warp != kUWarpRec || mbar_wait(bar_rec, 0, abort_flag, limit);
+    if (__syncthreads_and(first_landed) && warp == kUWarpS && lane0) issue_s(0);
     __syncwarp();
     for (int it = 0; it < n_it; ++it) {
         const int buf = it % kUBufs;
-        const float *kscale = scales + buf * kUScaleFloats, *mscale = kscale + kUKeys + 2 * kUD;
+        const float *kscale = reinterpret_cast<const float *>(Rb + buf * kURecStride + kURecScaleOff);
+        const float *mscale = kscale + kUKeys + 2 * kUD;
         // A warp whose wait gives up skips what needs the products and votes at the next CTA
         // barrier: the verdict is taken by the whole CTA, nobody goes on to a barrier the others
         // have left.
+        // (one warp saw this iteration's record land before a CTA barrier that lies behind us,
+        // which makes the record's scales visible to this thread)
         bool ok = mbar_wait(bar_s, it & 1, abort_flag, limit);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
@@ -1008,9 +1029,9 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
             uint32_t c0, c1, c2, c3;
             asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
                          : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
-                         : "r"(my_tmem + (it & 1) * kURegion + kUKeys + 8 * my_blk)
+                         : "r"(my_tmem + kUKeys + 8 * my_blk)
                          : "memory");
-            tmem_ld32(my_tmem + (it & 1) * kURegion + 32 * g, v);
+            tmem_ld32(my_tmem + 32 * g, v);
             tmem_ld_wait();
             (void)c3;
             shift = (((float)(int)c0 * 65536.f + (float)(int)c1 * 256.f) + (float)(int)c2) * mscale[my_blk] * dq;
@@ -1034,37 +1055,31 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
             }
         } else {
             const float2 dq2 = make_float2(dq, dq), shift2 = make_float2(shift, shift);
-            const float2 *ksc2 = reinterpret_cast<const float2 *>(ksc);
+            const float4 *ksc4 = reinterpret_cast<const float4 *>(ksc);
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-                const float2 sc = __ffma2_rn(
-                    __fmul2_rn(make_float2((float)(int)v[2 * e], (float)(int)v[2 * e + 1]), dq2), ksc2[e], shift2);
-                s[2 * e] = sc.x;
-                s[2 * e + 1] = sc.y;
-                bm = fmaxf(bm, fmaxf(sc.x, sc.y));
+            for (int e = 0; e < 8; ++e) {
+                const float4 d = ksc4[e];
+                const float2 sa = __ffma2_rn(__fmul2_rn(make_float2((float)(int)v[4 * e], (float)(int)v[4 * e + 1]), dq2),
+                                             make_float2(d.x, d.y), shift2);
+                const float2 sb = __ffma2_rn(__fmul2_rn(make_float2((float)(int)v[4 * e + 2], (float)(int)v[4 * e + 3]), dq2),
+                                             make_float2(d.z, d.w), shift2);
+                s[4 * e] = sa.x, s[4 * e + 1] = sa.y, s[4 * e + 2] = sb.x, s[4 * e + 3] = sb.y;
+                bm = fmaxf(fmaxf(bm, fmaxf(sa.x, sa.y)), fmaxf(sb.x, sb.y));
             }
         }
         xm[g * kUQ + r] = bm;
-        // ---- the products of the iteration before have had this long to finish: fold them in
-        if (it > 0 && ok) {
-            ok = mbar_wait(bar_pv, (it - 1) & 1, abort_flag, limit);
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                fold_pv(it - 1, prev_alpha_a, prev_alpha_b);
-            }
-        }
-        // the tiles of iteration it + 1 (staged an iteration ago) have landed; after the barrier
-        // every thread has read S of this iteration and PV of the last one out of tensor memory
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // the record of the next iteration was asked for an iteration ago
+        if (warp == kUWarpRec && it + 1 < n_it && ok)
+            ok = mbar_wait(bar_rec + (it + 1) % kUBufs, ((it + 1) / kUBufs) & 1, abort_flag, limit);
+        // after the barrier every thread has read S of this iteration out of tensor memory
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         if (!__syncthreads_and(ok)) {
             dead = true;
+            dead_it = it;
             break;
         }
-        if (it + 1 < n_it && tid == 0) issue_s(it + 1);  // runs while the threads exponentiate
+        if (warp == kUWarpS && lane0 && it + 1 < n_it) issue_s(it + 1);  // runs while the threads exponentiate
         __syncwarp();
-        if (it + 2 < n_it) stage_any(it + 2, (it + 2) % kUBufs);
         // ---- the row's maxima after block a and after block b (the same in its four threads)
         const float bm_a = fmaxf(xm[r], xm[kUQ + r]), bm_b = fmaxf(xm[2 * kUQ + r], xm[3 * kUQ + r]);
         const float mn_a = fmaxf(m, bm_a);
@@ -1074,16 +1089,14 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
         const float alpha_b = (mn_b == -INFINITY) ? 0.f : expf(m_a - mn_b);
         const float m_b = (mn_b == -INFINITY) ? m_a : mn_b;
         const float mn = my_blk ? mn_b : mn_a;
-        // P scaled by 127 (the static P scale): 127 exp(s - m) = exp2(s log2e - m log2e + log2 127)
+        // P scaled by 127 (the static P scale): 127 exp(s - m) = exp2(s log2e - m log2e + log2 127).
+        // A masked score is -inf and so is `off` of a row without any key so far: their sum is
+        // -inf (never NaN), of which ex2 gives 0.
         constexpr float kLog2e = 1.4426950408889634f, kLog2_127 = 6.988684686772166f;
         const float off = (mn == -INFINITY) ? -INFINITY : kLog2_127 - mn * kLog2e;
-        // a masked score is -inf: ex2 gives 0.  A row without any key so far has mn = -inf, whose
-        // difference with a score of -inf would be NaN: only a masked iteration can have such rows
-        const bool empty_row = masked && mn == -INFINITY;
         const float2 log2e2 = make_float2(kLog2e, kLog2e), off2 = make_float2(off, off);
         float2 es2 = make_float2(0.f, 0.f);  // the sums over the even and the odd columns
-#pragma unroll
-        for (int piece = 0; piece < 2; ++piece) {
+        auto exp_piece = [&](int piece) {  // 16 of the thread's 32 columns: exponentiate, round, store the codes
             uint32_t w[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -1092,8 +1105,7 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
                 for (int e = 0; e < 4; e += 2) {
                     const int at = 16 * piece + 4 * q + e;
                     const float2 arg = __ffma2_rn(make_float2(s[at], s[at + 1]), log2e2, off2);
-                    float2 pe = make_float2(ex2_approx(arg.x), ex2_approx(arg.y));
-                    if (masked && empty_row) pe = make_float2(0.f, 0.f);  // (`masked` is the same for the whole CTA)
+                    const float2 pe = make_float2(ex2_approx(arg.x), ex2_approx(arg.y));
                     es2 = __fadd2_rn(es2, pe);
                     c[e] = __float2int_rn(pe.x);  // in [0, 127]: rounds to nearest even like rint
                     c[e + 1] = __float2int_rn(pe.y);
@@ -1101,21 +1113,55 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
                 w[q] = pack_codes(c);
             }
             *reinterpret_cast<uint4 *>(swz(Ps, (int)r, 2 * g + piece)) = make_uint4(w[0], w[1], w[2], w[3]);
+        };
+        // ---- the exponentials of this iteration (bound by the special-function unit) and, between
+        // them, the products of the iteration before folded into the output (bound by issue slots):
+        // with the warps of a scheduler at different places of this stretch the two overlap.  The
+        // PV accumulators have a tensor-memory region of their own, so they may stay there until
+        // the next PV product is issued after the second barrier.  (Both blocks of the iteration
+        // before exist: only the last iteration can lack its second block.)
+        bool pv_ok = true;
+        if (it > 0) {
+            pv_ok = mbar_wait(bar_pv, (it - 1) & 1, abort_flag, limit);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        const bool fold = it > 0 && pv_ok;
+        const float *vd_prev = vscale_of(it + kUBufs - 1);
+        if (fold) tmem_ld32(my_tmem + kUPVCol + 32 * g, v);
+        exp_piece(0);
+        if (fold) {
+            tmem_ld_wait();
+            fold_block(prev_alpha_a, vd_prev);
+            tmem_ld32(my_tmem + kUPVCol + kUD + 32 * g, v);
+        }
+        exp_piece(1);
+        if (fold) {
+            tmem_ld_wait();
+            fold_block(prev_alpha_b, vd_prev + kUD);
         }
         xe[g * kUQ + r] = es2.x + es2.y;
-        // ---- PV into the region S has been read out of
+        // ---- PV of this iteration: the P codes are in shared memory, the accumulators of the
+        // iteration before have been read out, and nobody reads that iteration's record any more
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncthreads();
-        if (tid == 0) {
-            const uint32_t vt = smem_u32(Vb + buf * kUVBytes);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        if (!__syncthreads_and(pv_ok)) {
+            dead = true;
+            dead_it = it;
+            break;
+        }
+        if (lane0) {
+            if (warp == kUWarpPV) {
+                const uint32_t vt = smem_u32(Rb + buf * kURecStride + kURecKBytes);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int blk = 0; blk < 2; ++blk)
+                for (int blk = 0; blk < 2; ++blk)
 #pragma unroll
-                for (int k = 0; k < 2; ++k)
-                    umma_i8(tmem_base + (it & 1) * kURegion + kUD * blk, umma_desc(smem_u32(Ps) + (2 * blk + k) * 32),
-                            umma_desc(vt + (2 * blk + k) * 32), idesc_pv, k != 0);
-            umma_commit(bar_pv);
+                    for (int k = 0; k < 2; ++k)
+                        umma_i8(tmem_base + kUPVCol + kUD * blk, umma_desc(smem_u32(Ps) + (2 * blk + k) * 32),
+                                umma_desc(vt + (2 * blk + k) * 32), idesc_pv, k != 0);
+                umma_commit(bar_pv);
+            }
+            if (warp == kUWarpRec && it + 2 < n_it) stage(it + 2);  // into the buffer of the iteration before
         }
         __syncwarp();
         l = alpha_a * l + (xe[r] + xe[kUQ + r]);
@@ -1129,19 +1175,32 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
             dead = true;
         } else {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            fold_pv(n_it - 1, prev_alpha_a, prev_alpha_b);
+            const float *vd_last = vscale_of(n_it - 1);
+            tmem_ld32(my_tmem + kUPVCol + 32 * g, v);
+            tmem_ld_wait();
+            fold_block(prev_alpha_a, vd_last);
+            if (2 * (n_it - 1) + 1 < jb_hi) {  // (the same for the whole CTA)
+                tmem_ld32(my_tmem + kUPVCol + kUD + 32 * g, v);
+                tmem_ld_wait();
+                fold_block(prev_alpha_b, vd_last + kUD);
+            }
         }
     }
     if (dead) {
         // Given up: before tensor memory is handed back, the products that were issued must have
         // finished.  A commit on a barrier of its own arrives when everything issued so far is
         // done; it is waited for with the default (long) limit, not the one that just expired.
+        // The same for the records still on their way into shared memory: the one of the
+        // iteration that gave up and the one after it (later ones have not been asked for).
         __syncthreads();
+        // (a commit covers the products its own thread has issued: both issuing threads commit)
+        if ((warp == kUWarpS || warp == kUWarpPV) && lane0) umma_commit(bar_drain);
+        __syncwarp();
         if (warp == 0) {
             volatile int never = 0;
-            if (tid == 0) umma_commit(bar_drain);
-            __syncwarp();
             (void)mbar_wait(bar_drain, 0, &never, kUWaitLimitDefault);
+            for (int k = dead_it; k < min(n_it, dead_it + 2); ++k)
+                (void)mbar_wait(bar_rec + k % kUBufs, (k / kUBufs) & 1, &never, kUWaitLimitDefault);
         }
     }
     if (dead) *abort_flag = 1;
@@ -1303,15 +1362,15 @@ size_t sage_scratch_bytes(const qk_attention_shape *s, size_t block_size) {
     return up(qrows * dpad) + up(qrows * 4) + up(planes * S * dpad) + up(planes * S * 4) +
            up(planes * n_blocks * dm.d * 4) + up(planes * n_blocks * dm.dv * bpad) +
            up(planes * n_blocks * dm.dv * 4) + up(planes * n_blocks * 8 * dpad) +
-           up(planes * n_blocks * 4);
+           up(planes * n_blocks * 4) + up(planes * ((n_blocks + 1) / 2) * kURecStride) + 1024;
 }
 
 // Where each piece of the Sage scratch lies, and the padded sizes the kernels use.
 struct SageLayout {
     size_t block, n_blocks, wpl, dpad, bpad, planes, qrows;
-    size_t o_qc, o_qs, o_kc, o_ks, o_km, o_vc, o_vs, o_md, o_ms;
+    size_t o_qc, o_qs, o_kc, o_ks, o_km, o_vc, o_vs, o_md, o_ms, o_rec;
     bool tc;    // a tensor-core kernel runs: the mean digit rows are produced
-    bool umma;  // ... the tcgen05 one, which reads the V codes in plain key order
+    bool umma;  // ... the tcgen05 one, whose K and V operands are written as records (o_rec) only
 };
 SageLayout sage_layout(const qk_ctx *c, const AttnDims &dm, size_t block_size) {
     SageLayout L{};
@@ -1333,15 +1392,23 @@ SageLayout sage_layout(const qk_ctx *c, const AttnDims &dm, size_t block_size) {
     L.o_km = take(L.planes * L.n_blocks * dm.d * 4);
     L.o_vc = take(L.planes * L.n_blocks * dm.dv * L.bpad), L.o_vs = take(L.planes * L.n_blocks * dm.dv * 4);
     L.o_md = take(L.planes * L.n_blocks * 8 * L.dpad), L.o_ms = take(L.planes * L.n_blocks * 4);
+    L.o_rec = take(L.planes * ((L.n_blocks + 1) / 2) * kURecStride);  // (+ up to 1023 bytes to align it)
     L.tc = c->sage_kernel != 0 && sage_tc_eligible(dm, block_size);
     L.umma = L.tc && c->sage_kernel == 2 && dm.d == kUD && dm.dv == kUD && block_size == kUBlk;
     return L;
 }
 
 // The three quantisers (psi_Q, gamma + psi_K, psi_V) into `scratch`.
+uint8_t *sage_records(uint8_t *base, const SageLayout &L) {
+    // bulk copies want 16-byte alignment; 1 KB keeps the records on the tiles' own boundary
+    uint8_t *p = base + L.o_rec;
+    return p + ((1024 - (reinterpret_cast<uintptr_t>(p) & 1023)) & 1023);
+}
+
 qk_status sage_quantize_dev(qk_ctx *c, const float *dq, const float *dk, const float *dv,
                             uint8_t *base, const AttnDims &dm, const SageLayout &L) {
     const size_t S = dm.Skv;
+    uint8_t *rec = L.umma ? sage_records(base, L) : nullptr;
     const float inv_sqrt_d = 1.0f / sqrtf((float)dm.d);  // gpu_attention.rs:720
     sage_quant_q_kernel<<<(unsigned)qk::ceil_div(L.qrows, 8), 256, 0, c->stream>>>(
         dq, (int8_t *)(base + L.o_qc), (float *)(base + L.o_qs), (uint32_t)L.qrows, dm.d,
@@ -1351,11 +1418,11 @@ qk_status sage_quantize_dev(qk_ctx *c, const float *dq, const float *dk, const f
     sage_quant_k_kernel<<<kgrid, 128, dm.d * sizeof(float), c->stream>>>(
         dk, (int8_t *)(base + L.o_kc), (float *)(base + L.o_ks), (float *)(base + L.o_km), (uint32_t)S,
         dm.d, (uint32_t)L.dpad, (uint32_t)L.block, (uint32_t)L.n_blocks,
-        L.tc ? (int8_t *)(base + L.o_md) : nullptr, (float *)(base + L.o_ms));
+        L.tc ? (int8_t *)(base + L.o_md) : nullptr, (float *)(base + L.o_ms), rec);
     QK_CUDA(cudaGetLastError());
     sage_quant_v_kernel<<<kgrid, 128, 0, c->stream>>>(
         dv, (int8_t *)(base + L.o_vc), (float *)(base + L.o_vs), (uint32_t)S, dm.dv,
-        (uint32_t)L.block, (uint32_t)L.bpad, (uint32_t)L.n_blocks, L.tc && !L.umma ? 1 : 0);
+        (uint32_t)L.block, (uint32_t)L.bpad, (uint32_t)L.n_blocks, L.tc && !L.umma ? 1 : 0, rec);
     QK_CUDA(cudaGetLastError());
     c->launches += 3;
     return QK_OK;
@@ -1374,7 +1441,8 @@ qk_status attention_sage_dev(qk_ctx *c, const float *dq, const float *dk, const 
                (const float *)(base + L.o_km),  (const int8_t *)(base + L.o_md),
                (const float *)(base + L.o_ms),  (const int8_t *)(base + L.o_vc),
                (const float *)(base + L.o_vs),  out,
-               (uint32_t)L.dpad, (uint32_t)L.bpad, (uint32_t)L.block, (uint32_t)L.n_blocks};
+               (uint32_t)L.dpad, (uint32_t)L.bpad, (uint32_t)L.block, (uint32_t)L.n_blocks,
+               L.umma ? sage_records(base, L) : nullptr};
     if (L.umma) {
         if ((st = qk::error_word(c)) != QK_OK) return st;
         c->err_armed = true;
@@ -1538,9 +1606,32 @@ qk_status qk_gpu_sage_quantize(qk_ctx *ctx, const qk_attention_shape *shape, con
     const int8_t *vc = (const int8_t *)(host.data() + L.o_vc);
     for (size_t r = 0; r < L.qrows; ++r) std::memcpy(q_codes + r * d, qc + r * L.dpad, d);
     std::memcpy(q_scale, host.data() + L.o_qs, L.qrows * 4);
+    std::memcpy(k_mean, host.data() + L.o_km, L.planes * L.n_blocks * d * 4);
+    if (L.umma) {
+        // the tcgen05 kernel's records: undo the row swizzle
+        const uint8_t *rec = host.data() + (qk::sage_records(base + o_scratch, L) - (base + o_scratch));
+        const size_t n_rec = (L.n_blocks + 1) / 2;
+        for (size_t p = 0; p < L.planes; ++p) {
+            for (size_t j = 0; j < S; ++j) {
+                const uint8_t *rc = rec + (p * n_rec + j / 128) * kURecStride;
+                for (size_t ch = 0; ch < d; ++ch)
+                    k_codes[(p * S + j) * d + ch] = (int8_t)rc[rec_tile_offset((uint32_t)(j % 128), (uint32_t)ch)];
+                std::memcpy(k_scale + p * S + j, rc + kURecScaleOff + 4 * (j % 128), 4);
+            }
+            for (size_t jb = 0; jb < L.n_blocks; ++jb) {
+                const uint8_t *rc = rec + (p * n_rec + jb / 2) * kURecStride;
+                std::memcpy(v_scale + (p * L.n_blocks + jb) * dv_, rc + kURecScaleOff + 4 * (128 + 128 * (jb % 2)),
+                            dv_ * 4);
+                for (size_t ch = 0; ch < dv_; ++ch)
+                    for (size_t kk = 0; kk < L.block && jb * L.block + kk < S; ++kk)
+                        v_codes[(p * S + jb * L.block + kk) * dv_ + ch] =
+                            (int8_t)rc[kURecKBytes + rec_tile_offset((uint32_t)ch, (uint32_t)(64 * (jb % 2) + kk))];
+            }
+        }
+        return QK_OK;
+    }
     for (size_t r = 0; r < L.planes * S; ++r) std::memcpy(k_codes + r * d, kc + r * L.dpad, d);
     std::memcpy(k_scale, host.data() + L.o_ks, L.planes * S * 4);
-    std::memcpy(k_mean, host.data() + L.o_km, L.planes * L.n_blocks * d * 4);
     std::memcpy(v_scale, host.data() + L.o_vs, L.planes * L.n_blocks * dv_ * 4);
     for (size_t p = 0; p < L.planes; ++p)
         for (size_t jb = 0; jb < L.n_blocks; ++jb)
