@@ -40,6 +40,7 @@
 // bfloat16 exactly where apply_bf16 does.
 #include <cmath>
 #include <cstring>
+#include <type_traits>
 
 #include "qk_common.h"
 #include "qk_digits.cuh"
@@ -202,78 +203,167 @@ __device__ __forceinline__ double load_input(const StageParams &p, uint32_t k, u
     return (double)v;
 }
 
+// kN entries of the input at once, k0, k0 + stride, ...: first every load (unconditional, the
+// index clamped into the vector), then the arithmetic.  A loop over load_input() keeps each
+// load behind its own bounds check, which the compiler cannot hoist a load across: the entries
+// then cost one memory latency EACH, and that, not the arithmetic, is what a digit table built
+// from global memory used to wait for.  Same values as load_input().
+template <bool kInDouble, bool kRoundBf16, int kN, typename Out, typename Index>
+__device__ __forceinline__ void load_inputs(const StageParams &p, Index index_of, uint32_t n_bits, bool live,
+                                            Out (&out)[kN]) {
+    uint32_t k[kN];
+#pragma unroll
+    for (int e = 0; e < kN; ++e) k[e] = index_of(e);
+    if (kInDouble) {
+        double raw[kN];
+#pragma unroll
+        for (int e = 0; e < kN; ++e) raw[e] = static_cast<const double *>(p.in)[min(k[e], n_bits - 1)];
+#pragma unroll
+        for (int e = 0; e < kN; ++e) out[e] = (live && k[e] < n_bits) ? (Out)raw[e] : (Out)0;
+        return;
+    }
+    const bool gated = p.in_gate_up != nullptr, scaled = p.in_scale != nullptr;
+    const float *up = gated ? p.in_gate_up : static_cast<const float *>(p.in);  // (a valid address either way)
+    const float *sc = scaled ? p.in_scale : static_cast<const float *>(p.in);
+    float v[kN], u[kN], w[kN];
+#pragma unroll
+    for (int e = 0; e < kN; ++e) {
+        const uint32_t kc = min(k[e], n_bits - 1);
+        v[e] = static_cast<const float *>(p.in)[kc];
+        u[e] = up[kc];
+        w[e] = sc[kc];
+    }
+#pragma unroll
+    for (int e = 0; e < kN; ++e) {
+        float x = v[e];
+        if (gated) x = x * u[e] / (1.0f + expf(-x));  // the SwiGLU between gate/up and down
+        if (scaled) x = w[e] * x;                      // float32 product, as the reference forms z
+        if (kRoundBf16) x = round_bf16(x);
+        out[e] = (live && k[e] < n_bits) ? (Out)x : (Out)0;  // (float or, exactly, double)
+    }
+}
+// ... the eight entries of record r of the digit table (see digit_table_kernel for the layout)
+template <bool kInDouble, bool kRoundBf16, typename Out>
+__device__ __forceinline__ void load_record(const StageParams &p, uint32_t r, uint32_t n_records, uint32_t n_bits,
+                                            Out (&out)[8]) {
+    const uint32_t ks = r / 64, rec = r % 64;
+    const uint32_t base = ks * kStepBits + 128 * (rec % 4) + 32 * (rec / 16) + 2 * ((rec / 4) % 4);
+    load_inputs<kInDouble, kRoundBf16, 8, Out>(p, [&](int e) { return base + 8 * (e % 4) + e / 4; }, n_bits,
+                                               r < n_records, out);
+}
+
 // Converts one instance's input vector to its digit table.
 //   kInDouble: the input is the float64 intermediate of the previous stage.
 // Table layout (uint2 units): record ((ks*4 + q)*4 + ip)*4 + t holds, for digit column n,
 // the B fragment pair of lane (g = n, t) for the MMA that consumes word q of k-step ks
 // under masks 2*ip (b0) and 2*ip+1 (b1); byte j of b0/b1 belongs to
 // k = 512*ks + 128*t + 32*q + 8*j + i.
-// grid.x covers the k-steps four at a time, grid.y is the instance.  Every block first
-// reduces max|v| over the whole vector (a few KB from L2), so blocks need no
-// communication; block 0 of each instance also forms sum_k q_k.  A thread then builds
-// one record for all eight digit columns from its eight vector entries and writes 64
-// contiguous bytes.
-template <bool kInDouble, bool kRoundBf16>
-__global__ void __launch_bounds__(256)
+// grid.x covers the k-steps four at a time (one record per thread), grid.y is the instance.
+// Every block first walks the whole vector - evaluating each entry once (scale, SwiGLU,
+// rounding) into shared memory and reducing max|v| - so blocks need no communication; block 0
+// of each instance also forms sum_k q_k.  A thread then builds one record for all eight digit
+// columns from its eight entries and writes 64 contiguous bytes.  All of it is integer
+// arithmetic on the bits of the values (FloatBits: the same integers as the float64 form); a
+// float32 input never becomes a double.  Dynamic shared memory: n_steps * 512 entries.
+constexpr int kTableThreads = 256;
+//   kCache = false: a vector too long for shared memory is evaluated again where it is needed.
+template <bool kInDouble, bool kRoundBf16, bool kCache = true>
+__global__ void __launch_bounds__(kTableThreads)
 digit_table_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32_t n_steps) {
+    using T = typename std::conditional<kInDouble, double, float>::type;
     qk::pdl_launch();
     qk::pdl_wait();
     const StageParams p = many[blockIdx.y];
-    __shared__ double red_max[8];
-    __shared__ long long red_sum[8];
-    __shared__ int sh_bad;
+    extern __shared__ __align__(16) uint8_t table_vec_raw[];
+    T *vec = reinterpret_cast<T *>(table_vec_raw);  // the evaluated entries, zero beyond n_bits
+    __shared__ unsigned long long red_max[kTableThreads / 32];
+    __shared__ long long red_sum[kTableThreads / 32];
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const uint32_t n_padded = n_steps * kStepBits;
 
-    double mx = 0.0;
-    int bad = 0;
-    for (uint32_t k = tid; k < n_bits; k += 256) {
-        double a = fabs(load_input<kInDouble, kRoundBf16>(p, k, n_bits));
-        if (!(a <= 1.7e308)) bad = 1;  // NaN or infinity
-        mx = fmax(mx, a);
+    // (eight entries per thread and round: their loads are in flight together)
+    constexpr int kScan = 8;
+    unsigned long long mx = 0;
+    for (uint32_t k0 = tid; k0 < n_padded; k0 += kTableThreads * kScan) {
+        T vals[kScan];
+        load_inputs<kInDouble, kRoundBf16, kScan, T>(p, [&](int u) { return k0 + kTableThreads * u; }, n_bits, true, vals);
+#pragma unroll
+        for (int u = 0; u < kScan; ++u) {
+            const uint32_t k = k0 + kTableThreads * u;
+            if (kCache && k < n_padded) vec[k] = vals[u];
+            const unsigned long long mag = FloatBits<T>::magnitude(vals[u]);
+            mx = mag > mx ? mag : mx;
+        }
     }
     for (int off = 16; off > 0; off >>= 1) {
-        mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-        bad |= __shfl_xor_sync(0xffffffffu, bad, off);
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, mx, off);
+        mx = other > mx ? other : mx;
     }
     if (lane == 0) red_max[warp] = mx;
-    if (tid == 0) sh_bad = 0;
-    __syncthreads();
-    if (lane == 0 && bad) sh_bad = 1;
-    __syncthreads();
-    double m = red_max[0];
+    __syncthreads();  // (also: vec is complete)
+    mx = red_max[0];
 #pragma unroll
-    for (int w = 1; w < 8; ++w) m = fmax(m, red_max[w]);
-    const bool nonfinite = sh_bad != 0;
-    const FixedPoint fp = fixed_point_of(nonfinite ? 0.0 : m);
+    for (int w = 1; w < kTableThreads / 32; ++w) mx = red_max[w] > mx ? red_max[w] : mx;
+    const bool nonfinite = mx >= FloatBits<T>::kBad;  // NaN or infinity somewhere
+    const FixedPoint fp = fixed_point_of(nonfinite ? 0.0 : FloatBits<T>::as_double(mx));
 
     if (blockIdx.x == 0) {
         long long total = 0;
-        if (!nonfinite)
-            for (uint32_t k = tid; k < n_bits; k += 256)
-                total += fp.quant(load_input<kInDouble, kRoundBf16>(p, k, n_bits));
+        if (!nonfinite && kCache)
+            for (uint32_t k = tid; k < n_bits; k += kTableThreads) total += FloatBits<T>::quant(vec[k], fp.shift);
+        if (!nonfinite && !kCache)
+            for (uint32_t k0 = tid; k0 < n_bits; k0 += kTableThreads * kScan) {
+                T vals[kScan];
+                load_inputs<kInDouble, kRoundBf16, kScan, T>(p, [&](int u) { return k0 + kTableThreads * u; }, n_bits, true,
+                                                             vals);
+#pragma unroll
+                for (int u = 0; u < kScan; ++u) total += FloatBits<T>::quant(vals[u], fp.shift);
+            }
         for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
         if (lane == 0) red_sum[warp] = total;
         __syncthreads();
         if (tid == 0) {
             long long sum = 0;
-            for (int w = 0; w < 8; ++w) sum += red_sum[w];
+            for (int w = 0; w < kTableThreads / 32; ++w) sum += red_sum[w];
             p.meta->total = sum;
             p.meta->shift = fp.shift;
             p.meta->nonfinite = nonfinite;
         }
     }
 
-    const uint32_t ks = blockIdx.x * 4 + tid / 64;
+    const uint32_t ks = blockIdx.x * (kTableThreads / 64) + tid / 64;
     if (ks >= n_steps) return;
     const uint32_t rec = tid % 64;  // (qw*4 + ip)*4 + t
-    const uint32_t t = rec % 4, ip = (rec / 4) % 4, qw = rec / 16;
+    const uint32_t tt = rec % 4, ip = (rec / 4) % 4, qw = rec / 16;
+    T entries[8];
+    if (kCache) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            entries[e] = vec[ks * kStepBits + 128 * tt + 32 * qw + 8 * (e % 4) + 2 * ip + e / 4];
+    } else {
+        load_record<kInDouble, kRoundBf16, T>(p, ks * 64 + rec, n_steps * 64, n_bits, entries);
+    }
     long long q8[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        uint32_t k = ks * kStepBits + 128 * t + 32 * qw + 8 * (e % 4) + 2 * ip + e / 4;
-        q8[e] = nonfinite ? 0 : fp.quant(load_input<kInDouble, kRoundBf16>(p, k, n_bits));
-    }
+    for (int e = 0; e < 8; ++e) q8[e] = nonfinite ? 0 : FloatBits<T>::quant(entries[e], fp.shift);
     build_record(q8, ip, reinterpret_cast<uint4 *>(p.digits + ((size_t)ks * 64 + rec) * 8));
+}
+// Launches it for n_inst instances of one stage.
+template <bool kFinal>
+qk_status launch_digit_table(qk_ctx *c, const StageParams *many, size_t n_inst, size_t n_bits, size_t n_steps,
+                             bool bf16) {
+    const size_t smem = n_steps * kStepBits * (kFinal ? 8 : 4);  // (stage 2 reads the float64 intermediate)
+    const bool cache = smem <= 200 * 1024;
+    auto table = cache ? (bf16 ? digit_table_kernel<kFinal, true, true> : digit_table_kernel<kFinal, false, true>)
+                       : (bf16 ? digit_table_kernel<kFinal, true, false> : digit_table_kernel<kFinal, false, false>);
+    if (cache && smem > 48 * 1024)
+        QK_CUDA(cudaFuncSetAttribute(table, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 tgrid((unsigned)qk::ceil_div(n_steps, kTableThreads / 64), (unsigned)n_inst);
+    (void)qk::launch_pdl(c->pdl, table, tgrid, dim3(kTableThreads), cache ? smem : 0, c->stream, many,
+                         (uint32_t)n_bits, (uint32_t)n_steps);
+    QK_CUDA(cudaGetLastError());
+    c->launches++;
+    return QK_OK;
 }
 
 // Starts this warp's first kStages-1 chunks of a stage (item i of a warp goes to ring slot
@@ -383,27 +473,38 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
             const uint32_t tt = rec % 4, ip = (rec / 4) % 4, qw = rec / 16;
             return input(ks * kStepBits + 128 * tt + 32 * qw + 8 * (e % 4) + 2 * ip + e / 4);
         };
+        // (from global memory a record's eight loads go out together: load_inputs)
+        auto record = [&](uint32_t r, double (&entries)[8]) {
+            if (kInSmem) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) entries[e] = r < n_records ? record_entry(r, e) : 0.0;
+            } else {
+                load_record<kFinal, kRoundBf16, double>(p, r, n_records, n_bits, entries);
+            }
+        };
         double cached[kCached][8];
         double mx = 0.0;
         int bad = 0;
 #pragma unroll
-        for (int sl = 0; sl < kCached; ++sl) {
-            const uint32_t r = threadIdx.x + sl * blockDim.x;
+        for (int sl = 0; sl < kCached; ++sl) record(threadIdx.x + sl * blockDim.x, cached[sl]);
+#pragma unroll
+        for (int sl = 0; sl < kCached; ++sl)
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                cached[sl][e] = r < n_records ? record_entry(r, e) : 0.0;
                 double a = fabs(cached[sl][e]);
                 if (!(a <= 1.7e308)) bad = 1;  // NaN or infinity
                 mx = fmax(mx, a);
             }
-        }
-        for (uint32_t r = threadIdx.x + kCached * blockDim.x; r < n_records; r += blockDim.x)
+        for (uint32_t r = threadIdx.x + kCached * blockDim.x; r < n_records; r += blockDim.x) {
+            double entries[8];
+            record(r, entries);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                double a = fabs(record_entry(r, e));
+                double a = fabs(entries[e]);
                 if (!(a <= 1.7e308)) bad = 1;
                 mx = fmax(mx, a);
             }
+        }
         for (int off = 16; off > 0; off >>= 1)
             mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, off));
         if (lane == 0) red_max[warp] = mx;
@@ -428,10 +529,12 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
             }
         }
         for (uint32_t r = threadIdx.x + kCached * blockDim.x; r < n_records; r += blockDim.x) {
+            double entries[8];
+            record(r, entries);
             long long q8[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                q8[e] = meta.nonfinite ? 0 : fp.quant(record_entry(r, e));
+                q8[e] = meta.nonfinite ? 0 : fp.quant(entries[e]);
                 total += q8[e];
             }
             build_record(q8, (r % 64 / 4) % 4, table + (size_t)r * 4);
@@ -1239,6 +1342,9 @@ StagePlan plan_stage(const qk_ctx *c, const StageShape &s, size_t n_inst) {
     return pl;
 }
 
+bool fed_plan_fits(const qk_ctx *c, const StageShape &s, size_t n_inst, size_t *warps, size_t *smem);
+constexpr size_t kSpreadTableSteps = 16;  // k-steps (of 512 inputs) from which the few-instance form gets its table made once
+
 template <bool kFinal>
 qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, const StageShape &s,
                           bool bf16) {
@@ -1249,8 +1355,25 @@ qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, con
     auto sk_bytes = [&](size_t w) { return s.n_steps * 4096 + w * kRingPerWarp + w * 16 * 32 * 4; };
     while (sk_warps > 4 && sk_bytes(sk_warps) > kSmemBudget) --sk_warps;
     const size_t sk_smem = sk_bytes(sk_warps);
-    if (c->gemv_kernel != 3 && pl.smem_digits && sk_smem <= kSmemBudget &&
-        n_inst * pl.blocks < (size_t)c->sm_count && s.n_groups <= 65535) {
+    const bool few = c->gemv_kernel != 3 && n_inst * pl.blocks < (size_t)c->sm_count && s.n_groups <= 65535;
+    // A long input vector (the down projection's 14336 entries): every block of the few-instance
+    // form would build the whole digit table for itself, about 10 us of the kernel's 16.  The
+    // table is built once instead, by a small grid of its own that shares out the records, and
+    // the stage's blocks only stream (the form fed plans use).  One more launch, half the time.
+    size_t fed_warps, fed_smem;
+    if (few && s.n_steps >= kSpreadTableSteps && n_inst <= 65535 && fed_plan_fits(c, s, n_inst, &fed_warps, &fed_smem)) {
+        qk_status ts = launch_digit_table<kFinal>(c, many, n_inst, s.n_bits, s.n_steps, bf16);
+        if (ts != QK_OK) return ts;
+        auto gemv = bf16 ? gemv_bitslice_splitk_kernel<true, kFinal, true>
+                         : gemv_bitslice_splitk_kernel<false, kFinal, true>;
+        QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+        dim3 grid((unsigned)s.n_groups, (unsigned)n_inst);
+        (void)qk::launch_pdl(c->pdl, gemv, grid, dim3((unsigned)fed_warps * 32), fed_smem, c->stream, many);
+        QK_CUDA(cudaGetLastError());
+        c->launches++;
+        return QK_OK;
+    }
+    if (few && pl.smem_digits && sk_smem <= kSmemBudget) {
         dim3 grid((unsigned)s.n_groups, (unsigned)n_inst);
         auto gemv = bf16 ? gemv_bitslice_splitk_kernel<true, kFinal>
                          : gemv_bitslice_splitk_kernel<false, kFinal>;
@@ -1263,14 +1386,8 @@ qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, con
     }
     if (!pl.smem_digits) {
         // too wide for shared memory: the table is made in global memory first
-        auto table = kFinal ? (bf16 ? digit_table_kernel<true, true> : digit_table_kernel<true, false>)
-                            : (bf16 ? digit_table_kernel<false, true>
-                                    : digit_table_kernel<false, false>);
-        dim3 tgrid((unsigned)qk::ceil_div(s.n_steps, 4), (unsigned)n_inst);
-        (void)qk::launch_pdl(c->pdl, table, tgrid, dim3(256), 0, c->stream, many, (uint32_t)s.n_bits,
-                             (uint32_t)s.n_steps);
-        QK_CUDA(cudaGetLastError());
-        c->launches++;
+        qk_status ts = launch_digit_table<kFinal>(c, many, n_inst, s.n_bits, s.n_steps, bf16);
+        if (ts != QK_OK) return ts;
     }
     dim3 grid((unsigned)pl.blocks, (unsigned)n_inst);
     auto gemv = pl.smem_digits ? (bf16 ? gemv_bitslice_kernel<true, kFinal, true>

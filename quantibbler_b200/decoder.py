@@ -63,6 +63,11 @@ class DecoderConfig:
     # split of each head group costs more than the two launches it saves (10.96 -> 11.40 ms).
     fused_attention: bool = True
     fused_attention_max_batch: int = 8
+    # Batches up to this size let the down projection read gate and up through the SwiGLU itself
+    # (the activation is evaluated where the projection's digit table is built) instead of a
+    # SwiGLU launch of its own: one kernel boundary less per block, the same bits.  Larger
+    # batches run more blocks per token, each of which would evaluate the whole activation.
+    gated_down_max_batch: int = 4
     prefill_min_tokens: int = 16   # generate(): prompts this long go through the trunk in one pass
     prefill_chunk: int = 2048      # ... in pieces of at most this many positions
 
@@ -279,8 +284,11 @@ class Decoder:
                         for n, dst in zip(names, dsts)]
 
             fed = cfg.serving in ("float32", "bfloat16") and B <= cfg.feed_max_batch
+            gemm = cfg.serving == "bfloat16" and B >= cfg.gemm_min_batch
+            self.gated_down = fed or (cfg.serving in ("float32", "bfloat16") and not gemm
+                                      and B <= cfg.gated_down_max_batch)
             plan = {"o": LayerPlan(ctx, inst(["o"], self.attn, [self.delta_attn]))}
-            if fed:   # down reads SwiGLU(gate, up) directly: no separate activation pass
+            if self.gated_down:   # down reads SwiGLU(gate, up) directly: no separate activation pass
                 plan["down"] = LayerPlan(ctx, [(L["down"], rows(self.g, b), rows(self.u, b),
                                                 rows(self.delta_mlp, b)) for b in range(B)], gated=True)
             else:
@@ -471,7 +479,7 @@ class Decoder:
             if feeds:   # (the fed down plan needs no activation vector, only its digit table)
                 check(lib.qk_swiglu_feed(c, _p(self.g), _p(self.u), B, self.ff_loc, self.serving_tag,
                                          ctypes.byref(feeds["down"])))
-            else:
+            elif not self.gated_down:
                 check(lib.qk_swiglu(c, _p(self.g), _p(self.u), B * self.ff_loc, _p(self.a)))
             self._linears(li, ["down"], self.a, [self.delta_mlp])
             self._all_reduce(self.delta_mlp)
