@@ -290,6 +290,16 @@ qk_status qk_plan_create(qk_ctx *ctx, const qk_layer *const *layers, const float
 qk_status qk_plan_create_gated(qk_ctx *ctx, const qk_layer *const *layers,
                                const float *const *gate_ptrs, const float *const *up_ptrs,
                                float *const *y_ptrs, size_t n_inst, qk_group **out);
+/* Makes a plan apply an RMSNorm to its input itself (engine/mod.rs:900-907 followed by the
+ * linears of :908-915 in one launch): instance k then reads x_ptrs[k] as the residual stream,
+ * adds residual_ptrs[k] (the array or an entry may be null), and applies its layer to
+ * (x + residual) * rsqrt(mean((x + residual)^2) + eps) * norm_weight - the bits of
+ * qk_rmsnorm followed by the plain plan.  Where x_out_ptrs[k] is not null the instance also
+ * writes x + residual there (give it for ONE instance per token, and not the input buffer:
+ * every block of the launch reads the input).  The plan must fit the few-instance kernel
+ * form with at most 8192 inputs, otherwise QK_ERR_VALUE and the plan is unchanged. */
+qk_status qk_plan_set_norm(qk_ctx *ctx, qk_group *plan, const float *const *residual_ptrs,
+                           const float *norm_weight, float eps, float *const *x_out_ptrs);
 qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group);
 /* Many independent applies with HOST buffers as a pipeline: groups[p] (made by qk_group_create
  * over rows first_row[p] .. first_row[p+1] of x_dev / y_dev) has its inputs copied up from

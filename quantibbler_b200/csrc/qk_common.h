@@ -107,6 +107,7 @@ struct qk_group {
     qk_layer shape;          // dimensions/strides of the member layers (the largest, if they differ)
     bool mixed = false;      // the members differ in shape: few-instance form only
     bool fed = false;        // the stage-1 tables are written by the kernels that produce the inputs
+    bool normed = false;     // stage 1 applies an RMSNorm to its input itself (qk_plan_set_norm)
     void *feed = nullptr;    // device array of per-instance feed targets (fed plans)
     void *tickets = nullptr; // device array of per-instance block counters (fed plans)
     void *scratch = nullptr; // per member: intermediate t, digit tables, stage metadata

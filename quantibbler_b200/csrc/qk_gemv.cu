@@ -69,6 +69,14 @@ struct StageParams {
     uint2 *next_digits;
     StageMeta *next_meta;
     uint32_t *ticket;
+    // "normed" plans (stage 1 of the few-instance form): `in` is the residual stream x and the
+    // stage's input is RMSNorm(x + in_residual) * norm_w, formed in the block itself exactly as
+    // the stand-alone norm kernel forms it (same thread count, same order of the sum).  Block 0
+    // of an instance with x_out writes the updated stream x + in_residual there.
+    const float *norm_w;
+    const float *in_residual;
+    float *x_out;
+    float norm_eps;
 };
 
 // ------------------------------------------------------------------ sign-select kernel
@@ -208,9 +216,11 @@ __device__ __forceinline__ double load_input(const StageParams &p, uint32_t k, u
 // load behind its own bounds check, which the compiler cannot hoist a load across: the entries
 // then cost one memory latency EACH, and that, not the arithmetic, is what a digit table built
 // from global memory used to wait for.  Same values as load_input().
-template <bool kInDouble, bool kRoundBf16, int kN, typename Out, typename Index>
+//   kNormed: the entries go through the RMSNorm first (StageParams::norm_w), norm_inv being
+//   1 / sqrt(mean square + eps) of the whole vector.
+template <bool kInDouble, bool kRoundBf16, int kN, typename Out, bool kNormed = false, typename Index>
 __device__ __forceinline__ void load_inputs(const StageParams &p, Index index_of, uint32_t n_bits, bool live,
-                                            Out (&out)[kN]) {
+                                            Out (&out)[kN], float norm_inv = 0.f) {
     uint32_t k[kN];
 #pragma unroll
     for (int e = 0; e < kN; ++e) k[e] = index_of(e);
@@ -225,17 +235,29 @@ __device__ __forceinline__ void load_inputs(const StageParams &p, Index index_of
     const bool gated = p.in_gate_up != nullptr, scaled = p.in_scale != nullptr;
     const float *up = gated ? p.in_gate_up : static_cast<const float *>(p.in);  // (a valid address either way)
     const float *sc = scaled ? p.in_scale : static_cast<const float *>(p.in);
-    float v[kN], u[kN], w[kN];
+    const bool residual = kNormed && p.in_residual != nullptr;
+    const float *res = residual ? p.in_residual : static_cast<const float *>(p.in);
+    float v[kN], u[kN], w[kN], rr[kNormed ? kN : 1], nw[kNormed ? kN : 1];
 #pragma unroll
     for (int e = 0; e < kN; ++e) {
         const uint32_t kc = min(k[e], n_bits - 1);
         v[e] = static_cast<const float *>(p.in)[kc];
         u[e] = up[kc];
         w[e] = sc[kc];
+        if (kNormed) {
+            rr[e] = res[kc];
+            nw[e] = p.norm_w[kc];
+        }
     }
 #pragma unroll
     for (int e = 0; e < kN; ++e) {
         float x = v[e];
+        if (kNormed) {  // (the roundings of the norm kernel under bfloat16 serving)
+            if (residual) x += rr[e];
+            if (kRoundBf16) x = round_bf16(x);
+            x = x * norm_inv * nw[e];
+            if (kRoundBf16) x = round_bf16(x);
+        }
         if (gated) x = x * u[e] / (1.0f + expf(-x));  // the SwiGLU between gate/up and down
         if (scaled) x = w[e] * x;                      // float32 product, as the reference forms z
         if (kRoundBf16) x = round_bf16(x);
@@ -245,11 +267,14 @@ __device__ __forceinline__ void load_inputs(const StageParams &p, Index index_of
 // ... the eight entries of record r of the digit table (see digit_table_kernel for the layout)
 template <bool kInDouble, bool kRoundBf16, typename Out>
 __device__ __forceinline__ void load_record(const StageParams &p, uint32_t r, uint32_t n_records, uint32_t n_bits,
-                                            Out (&out)[8]) {
+                                            Out (&out)[8], float norm_inv = 0.f) {
     const uint32_t ks = r / 64, rec = r % 64;
     const uint32_t base = ks * kStepBits + 128 * (rec % 4) + 32 * (rec / 16) + 2 * ((rec / 4) % 4);
-    load_inputs<kInDouble, kRoundBf16, 8, Out>(p, [&](int e) { return base + 8 * (e % 4) + e / 4; }, n_bits,
-                                               r < n_records, out);
+    auto index_of = [&](int e) { return base + 8 * (e % 4) + e / 4; };
+    if (!kInDouble && p.norm_w)
+        load_inputs<kInDouble, kRoundBf16, 8, Out, true>(p, index_of, n_bits, r < n_records, out, norm_inv);
+    else
+        load_inputs<kInDouble, kRoundBf16, 8, Out>(p, index_of, n_bits, r < n_records, out);
 }
 
 // Converts one instance's input vector to its digit table.
@@ -458,6 +483,34 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
     // The weight bits depend on no other kernel, the input vector does: from here on the
     // kernel before this one on the stream must be complete.
     qk::pdl_wait();
+    // ---- a normed plan's stage 1: the norm's scale over the whole vector, as rmsnorm_kernel
+    // forms it (512 threads, element i of a thread's sixteen is tid + 512 i, warp sums by
+    // shuffles, then the warps' sums in order), and the updated residual stream
+    float norm_inv = 0.f;
+    if (!kFinal && !kInSmem && p.norm_w) {
+        __shared__ float norm_red[16];
+        const float *xs = static_cast<const float *>(p.in);
+        const bool writer = p.x_out && block_in_instance == 0;
+        float ss = 0.f;
+#pragma unroll
+        for (int rr = 0; rr < 16; ++rr) {
+            const uint32_t i = threadIdx.x + rr * 512;
+            float h = 0.f;
+            if (i < n_bits) {
+                h = xs[i];
+                if (p.in_residual) h += p.in_residual[i];
+                if (writer) p.x_out[i] = h;
+                if (kRoundBf16) h = round_bf16(h);
+            }
+            ss += h * h;
+        }
+        for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        if (lane == 0) norm_red[warp] = ss;
+        __syncthreads();
+        float total = 0.f;
+        for (uint32_t w = 0; w < warps_per_block; ++w) total += norm_red[w];
+        norm_inv = 1.0f / sqrtf(total / (float)n_bits + p.norm_eps);
+    }
     // ---- the digit table of this instance (the weight ring is already filling)
     __shared__ double red_max[16];
     __shared__ long long red_sum[16];
@@ -479,7 +532,7 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
 #pragma unroll
                 for (int e = 0; e < 8; ++e) entries[e] = r < n_records ? record_entry(r, e) : 0.0;
             } else {
-                load_record<kFinal, kRoundBf16, double>(p, r, n_records, n_bits, entries);
+                load_record<kFinal, kRoundBf16, double>(p, r, n_records, n_bits, entries, norm_inv);
             }
         };
         double cached[kCached][8];
@@ -1560,8 +1613,35 @@ qk_status launch_fed_stage(qk_ctx *c, const StageParams *many, size_t n_inst, co
     return QK_OK;
 }
 
+// Stage 1 of a normed plan: the few-instance form with the norm kernel's 512 threads.
+bool normed_plan_fits(const qk_ctx *c, const StageShape &s, size_t n_inst, size_t *smem) {
+    constexpr size_t kWarps = 16;
+    *smem = s.n_steps * 4096 + kWarps * kRingPerWarp + kWarps * 16 * 32 * 4;
+    return *smem <= kSmemBudget && s.n_bits <= 16 * 512 && s.n_groups <= 65535 && n_inst <= 65535 &&
+           n_inst * s.n_groups <= 8 * (size_t)c->sm_count;
+}
+qk_status launch_normed_stage1(qk_ctx *c, const StageParams *many, size_t n_inst, const StageShape &s, bool bf16) {
+    size_t smem;
+    if (!normed_plan_fits(c, s, n_inst, &smem))
+        return qk::fail(QK_ERR_VALUE, "a normed plan must fit the few-instance form");
+    auto gemv = bf16 ? gemv_bitslice_splitk_kernel<true, false> : gemv_bitslice_splitk_kernel<false, false>;
+    QK_CUDA(cudaFuncSetAttribute(gemv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    dim3 grid((unsigned)s.n_groups, (unsigned)n_inst);
+    (void)qk::launch_pdl(c->pdl, gemv, grid, dim3(512), smem, c->stream, many);
+    QK_CUDA(cudaGetLastError());
+    c->launches++;
+    return QK_OK;
+}
+
 qk_status launch_both(qk_ctx *c, const qk_layer *l0, const StageParams *d, size_t n_inst,
-                      int kernel, bool mixed = false, bool fed = false) {
+                      int kernel, bool mixed = false, bool fed = false, bool normed = false) {
+    if (normed) {
+        const bool bf16 = l0->serving == QK_BF16;
+        qk_status e = launch_normed_stage1(c, d, n_inst, stage1_shape(l0), bf16);
+        if (e != QK_OK) return e;
+        if (mixed) return launch_mixed_stage<true>(c, d + n_inst, n_inst, stage2_shape(l0), bf16);
+        return launch_bitslice<true>(c, d + n_inst, n_inst, stage2_shape(l0), bf16);
+    }
     if (fed) {
         qk_status e = launch_fed_stage<false>(c, d, n_inst, stage1_shape(l0), l0->serving == QK_BF16);
         if (e != QK_OK) return e;
@@ -1937,6 +2017,42 @@ qk_status qk_plan_create_gated(qk_ctx *ctx, const qk_layer *const *layers,
     return plan_create(ctx, layers, gate_ptrs, up_ptrs, y_ptrs, n_inst, out);
 }
 
+qk_status qk_plan_set_norm(qk_ctx *ctx, qk_group *plan, const float *const *residual_ptrs,
+                           const float *norm_weight, float eps, float *const *x_out_ptrs) {
+    if (!plan || !norm_weight) return qk::fail(QK_ERR_VALUE, "qk_plan_set_norm: plan and norm_weight must be given");
+    qk_ctx *c;
+    qk_status st = qk::resolve_ctx(ctx, &c);
+    if (st != QK_OK) return st;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    if (plan->device != c->device)
+        return qk::fail(QK_ERR_VALUE, "plan lives on device %d, context on device %d", plan->device, c->device);
+    if (plan->fed) return qk::fail(QK_ERR_VALUE, "a fed plan takes its input from a producer: it cannot be normed");
+    if (plan->shape.serving != QK_F32 && plan->shape.serving != QK_BF16)
+        return qk::fail(QK_ERR_VALUE, "normed plans exist for float32 and bfloat16 serving");
+    const size_t n = plan->n_inst;
+    size_t smem;
+    if (!normed_plan_fits(c, stage1_shape(&plan->shape), n, &smem))
+        return qk::fail(QK_ERR_VALUE,
+                        "a plan of %zu instances over %zu inputs does not fit the normed form (the few-instance "
+                        "kernel with 512 threads, at most 8192 inputs)", n, plan->shape.din);
+    std::vector<StageParams> h(n);
+    QK_CUDA(cudaMemcpy(h.data(), plan->params, n * sizeof(StageParams), cudaMemcpyDeviceToHost));
+    for (size_t k = 0; k < n; ++k) {
+        if (h[k].in_gate_up) return qk::fail(QK_ERR_VALUE, "a gated plan cannot be normed");
+        h[k].norm_w = norm_weight;
+        h[k].in_residual = residual_ptrs ? residual_ptrs[k] : nullptr;
+        h[k].x_out = x_out_ptrs ? x_out_ptrs[k] : nullptr;
+        h[k].norm_eps = eps;
+        if (h[k].x_out && h[k].x_out == h[k].in)
+            return qk::fail(QK_ERR_VALUE, "a normed plan cannot update the residual stream in place (every "
+                            "block reads it): x_out must be another buffer than the input");
+    }
+    QK_CUDA(cudaMemcpy(plan->params, h.data(), n * sizeof(StageParams), cudaMemcpyHostToDevice));
+    plan->normed = true;
+    return QK_OK;
+}
+
 qk_status qk_plan_feed_targets(qk_ctx *ctx, qk_group *plan, const void **targets_dev,
                                size_t *n_targets) {
     if (!plan || !targets_dev || !n_targets)
@@ -1989,7 +2105,7 @@ qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group) {
         return qk::fail(QK_ERR_VALUE, "group lives on device %d, context on device %d",
                         group->device, c->device);
     return launch_both(c, &group->shape, (const StageParams *)group->params, group->n_inst,
-                       c->gemv_kernel, group->mixed, group->fed);
+                       c->gemv_kernel, group->mixed, group->fed, group->normed);
 }
 
 qk_status qk_groups_apply_host(qk_ctx *ctx, const qk_group *const *groups, const size_t *first_row,

@@ -68,6 +68,11 @@ class DecoderConfig:
     # SwiGLU launch of its own: one kernel boundary less per block, the same bits.  Larger
     # batches run more blocks per token, each of which would evaluate the whole activation.
     gated_down_max_batch: int = 4
+    # Batches up to this size (one GPU) let q,k,v and gate,up apply the RMSNorm in front of them
+    # themselves (every block of the first stage forms the norm of the 4096-entry stream, which
+    # costs it about a microsecond) instead of a norm launch of its own, which costs the step
+    # about ten: two kernel boundaries less per block, the same bits.
+    norm_fused_max_batch: int = 4
     prefill_min_tokens: int = 16   # generate(): prompts this long go through the trunk in one pass
     prefill_chunk: int = 2048      # ... in pieces of at most this many positions
 
@@ -312,6 +317,25 @@ class Decoder:
             else:
                 plan["gate"] = LayerPlan(ctx, inst(["gate"], self.h, [self.g]))
                 plan["up"] = LayerPlan(ctx, inst(["up"], self.h, [self.u]))
+            if (B <= cfg.norm_fused_max_batch and tp_size == 1 and not fed and not gemm
+                    and cfg.serving in ("float32", "bfloat16") and "qkv" in plan and "gu" in plan):
+                # the first norm of a block reads the stream from x and leaves it in x2, the second
+                # the other way round; what they add is the output of the linear before them
+                def normed(names, src, dsts, residual, weight, x_out):
+                    p = LayerPlan(ctx, inst(names, src, dsts))
+                    k = len(names)
+                    p.set_norm([None if residual is None else rows(residual, b) for b in range(B) for _ in names],
+                               weight.data_ptr(), cfg.rms_eps,
+                               [rows(x_out, b) if j == 0 else None for b in range(B) for j in range(k)])
+                    return p
+                try:
+                    in_w, post_w = self.norms[li]
+                    qkv_n = normed(["q", "k", "v"], self.x, [self.q, self.k, self.v],
+                                   None if li == 0 else self.delta_mlp, in_w, self.x2)
+                    gu_n = normed(["gate", "up"], self.x2, [self.g, self.u], self.delta_attn, post_w, self.x)
+                    plan["qkv_normed"], plan["gu_normed"] = qkv_n, gu_n
+                except KernelError:
+                    pass   # (a stream too wide for the normed form: the separate norm stays)
             self.plans.append(plan)
         self.step_kernel = None
         if (B <= cfg.fused_step_max_batch and tp_size == 1 and not self.has_qk_norm and hd == 128
@@ -444,9 +468,13 @@ class Decoder:
         for li in range(cfg.n_layers if self.step_kernel is None else 0):
             in_w, post_w = self.norms[li]
             feeds = self.feeds[li] if self.fed else None
-            self._norm(pending, in_w, feeds["qkv"] if feeds else None, xa, xb)
+            normed = (not self.use_gemm) and "qkv_normed" in self.plans[li]
+            if normed:   # (norm and q,k,v in one pair of launches)
+                self.plans[li]["qkv_normed"].apply()
+            else:
+                self._norm(pending, in_w, feeds["qkv"] if feeds else None, xa, xb)
+                self._linears(li, ["q", "k", "v"], self.h, [self.q, self.k, self.v])
             xa, xb = xb, xa
-            self._linears(li, ["q", "k", "v"], self.h, [self.q, self.k, self.v])
             if self.qk_norms[li] is not None:
                 # every head is one row of head_dim values; x_out = x rewrites the projection
                 # unchanged (the kernel's usual in-place form)
@@ -473,9 +501,12 @@ class Decoder:
                     ctypes.byref(feeds["o"]) if feeds else None))
             self._linears(li, ["o"], self.attn, [self.delta_attn])
             self._all_reduce(self.delta_attn)
-            self._norm(0, post_w, feeds["gu"] if feeds else None, xa, xb)
+            if normed:
+                self.plans[li]["gu_normed"].apply()
+            else:
+                self._norm(0, post_w, feeds["gu"] if feeds else None, xa, xb)
+                self._linears(li, ["gate", "up"], self.h, [self.g, self.u])
             xa, xb = xb, xa
-            self._linears(li, ["gate", "up"], self.h, [self.g, self.u])
             if feeds:   # (the fed down plan needs no activation vector, only its digit table)
                 check(lib.qk_swiglu_feed(c, _p(self.g), _p(self.u), B, self.ff_loc, self.serving_tag,
                                          ctypes.byref(feeds["down"])))

@@ -547,6 +547,18 @@ class LayerPlan(LayerGroup):
             check(_lib.lib().qk_plan_create(ctx.handle, larr, xarr, yarr, n, ctypes.byref(h)))
         self._h = h
 
+    def set_norm(self, residuals, norm_weight: int, eps: float, x_outs) -> None:
+        """Makes ``apply`` start with the RMSNorm of its input (``qk_plan_set_norm``): instance k
+        reads its x pointer as the residual stream, adds ``residuals[k]`` (a device pointer or
+        None) and applies its layer to the normed vector; where ``x_outs[k]`` is not None it
+        also writes the updated stream there (one instance per token; never the input buffer).
+        Raises KernelError, leaving the plan as it was, when the plan does not fit that form."""
+        n = len(self.layers)
+        rarr = (ctypes.c_void_p * n)(*[ctypes.c_void_p(r) for r in residuals])
+        oarr = (ctypes.c_void_p * n)(*[ctypes.c_void_p(o) for o in x_outs])
+        check(_lib.lib().qk_plan_set_norm(self.ctx.handle, self._h, rarr, ctypes.c_void_p(norm_weight),
+                                          ctypes.c_float(eps), oarr))
+
     def feed_targets(self):
         """Turns the plan into a fed plan (the digit tables of its stage-1 inputs are then
         written by the ``*_feed`` call that produces those inputs, and every ``apply`` must follow

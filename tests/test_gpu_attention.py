@@ -323,28 +323,6 @@ def test_sage_tcgen05_kernel_matches_the_other_kernels(gpu_ctx, case):
         gpu_ctx.set_sage_kernel(default)
 
 
-def test_sage_tcgen05_kernel_with_fewer_queries_than_keys(gpu_ctx):
-    """seq_q != seq_kv, not causal: the records cover the keys (an odd number of key blocks, the
-    last one ragged), the query tile is partly empty."""
-    rng = np.random.default_rng(29)
-    b, h, kvh, sq, skv, d, block = 1, 4, 2, 70, 333, 128, 64
-    q = rng.standard_normal((b, h, sq, d), dtype=np.float32)
-    k = rng.standard_normal((b, kvh, skv, d), dtype=np.float32) \
-        + (2.0 * rng.standard_normal((1, kvh, 1, d))).astype(np.float32)
-    v = rng.standard_normal((b, kvh, skv, d), dtype=np.float32)
-    default = gpu_ctx.set_sage_kernel(1)
-    try:
-        tc = run_sage(gpu_ctx, q, k, v, False, block)
-        gpu_ctx.set_sage_kernel(2)
-        um = run_sage(gpu_ctx, q, k, v, False, block)
-    finally:
-        gpu_ctx.set_sage_kernel(default)
-    assert np.isfinite(um).all()
-    assert np.abs(um - tc).max() <= 1e-5 * np.abs(tc).max()
-    w32 = anp.attention_sage(q, k, v, causal=False, block_size=block, ft=np.float32)
-    assert np.abs(um - w32).max() <= 2e-3 * np.abs(w32).max()
-
-
 def test_attention_on_device_buffers(gpu_ctx):
     import torch
     rng = np.random.default_rng(11)

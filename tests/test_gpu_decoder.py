@@ -482,3 +482,58 @@ def test_one_launch_attention_reproduces_the_three_launches(gpu_ctx, serving):
     # (sequence 1 started at position 5 over rows nobody wrote: both caches hold zeros there)
     for li in range(cfg.n_layers):
         assert torch_equal(one.cache_k[li], three.cache_k[li]) and torch_equal(one.cache_v[li], three.cache_v[li])
+
+
+@pytest.mark.parametrize("serving", ["float32", "bfloat16"])
+def test_norm_and_swiglu_inside_the_linears_reproduce_the_separate_launches(gpu_ctx, serving):
+    """At small batches q,k,v and gate,up form the RMSNorm of the residual stream themselves
+    (every block of their first stage, with the norm kernel's thread count and summation
+    order; one block also writes the updated stream) and the down projection reads gate and up
+    through the SwiGLU: three launches less per block.  Logits and residual stream must be the
+    bits of the separate norm and SwiGLU kernels."""
+    base = dict(serving=serving, max_batch=2)
+    weights = random_model(step_cfg(**base), STEP_RANKS, seed=79)
+    apart = Decoder(gpu_ctx, step_cfg(norm_fused_max_batch=0, gated_down_max_batch=0, **base), weights)
+    fused = Decoder(gpu_ctx, step_cfg(**base), weights)
+    assert "qkv_normed" in fused.plans[0] and "gu_normed" in fused.plans[0] and fused.gated_down
+    assert "qkv_normed" not in apart.plans[0] and not apart.gated_down
+    for dec in (apart, fused):
+        dec.start([3, 77], [0, 2])
+    for step in range(6):
+        for dec in (apart, fused):
+            dec.step()
+        gpu_ctx.synchronize()
+        assert np.array_equal(fused.logits.cpu().numpy(), apart.logits.cpu().numpy()), step
+        assert torch_equal(fused.x, apart.x) and torch_equal(fused.x2, apart.x2), step
+        for dec in (apart, fused):
+            dec.advance()
+
+
+def test_normed_plan_is_refused_outside_its_form(gpu_ctx):
+    """A stream wider than the norm kernel's sixteen entries per thread, an in-place update of
+    the stream and a gated plan are refused with the plan left as it was."""
+    import torch
+    from quantibbler_b200.decoder import random_layer
+    from quantibbler_b200.gpu import KernelError, LayerPlan, PackedLayer
+    rng = np.random.default_rng(5)
+    for dout, din, r in ((64, 8704, 32),):
+        spec = random_layer(rng, dout, din, r)
+        layer = PackedLayer(gpu_ctx, spec["ub_rows"], spec["vb_t_rows"], dout, din, r, spec["s1"], spec["s2"],
+                            None, serving="float32")
+        x, x2, y, w = (torch.zeros(n, device="cuda") for n in (din, din, dout, din))
+        plan = LayerPlan(gpu_ctx, [(layer, x.data_ptr(), y.data_ptr())])
+        with pytest.raises(KernelError):
+            plan.set_norm([None], w.data_ptr(), 1e-5, [x2.data_ptr()])
+    spec = random_layer(rng, 64, 512, 32)
+    layer = PackedLayer(gpu_ctx, spec["ub_rows"], spec["vb_t_rows"], 64, 512, 32, spec["s1"], spec["s2"], None,
+                        serving="float32")
+    x, u, y, w = (torch.ones(n, device="cuda") for n in (512, 512, 64, 512))
+    plan = LayerPlan(gpu_ctx, [(layer, x.data_ptr(), y.data_ptr())])
+    with pytest.raises(KernelError):
+        plan.set_norm([None], w.data_ptr(), 1e-5, [x.data_ptr()])       # in place
+    gated = LayerPlan(gpu_ctx, [(layer, x.data_ptr(), u.data_ptr(), y.data_ptr())], gated=True)
+    with pytest.raises(KernelError):
+        gated.set_norm([None], w.data_ptr(), 1e-5, [None])
+    plan.apply()   # still the plain plan
+    gpu_ctx.synchronize()
+    assert torch.isfinite(y).all()
