@@ -491,14 +491,23 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
         __shared__ float norm_red[16];
         const float *xs = static_cast<const float *>(p.in);
         const bool writer = p.x_out && block_in_instance == 0;
+        // (all loads first, unconditional, so that they are in flight together)
+        const float *rs = p.in_residual ? p.in_residual : xs;
+        float hx[16], hr[16];
+#pragma unroll
+        for (int rr = 0; rr < 16; ++rr) {
+            const uint32_t i = min(threadIdx.x + rr * 512, n_bits - 1);
+            hx[rr] = xs[i];
+            hr[rr] = rs[i];
+        }
         float ss = 0.f;
 #pragma unroll
         for (int rr = 0; rr < 16; ++rr) {
             const uint32_t i = threadIdx.x + rr * 512;
             float h = 0.f;
             if (i < n_bits) {
-                h = xs[i];
-                if (p.in_residual) h += p.in_residual[i];
+                h = hx[rr];
+                if (p.in_residual) h += hr[rr];
                 if (writer) p.x_out[i] = h;
                 if (kRoundBf16) h = round_bf16(h);
             }
