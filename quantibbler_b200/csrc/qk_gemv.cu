@@ -216,11 +216,14 @@ __device__ __forceinline__ double load_input(const StageParams &p, uint32_t k, u
 // load behind its own bounds check, which the compiler cannot hoist a load across: the entries
 // then cost one memory latency EACH, and that, not the arithmetic, is what a digit table built
 // from global memory used to wait for.  Same values as load_input().
-//   kNormed: the entries go through the RMSNorm first (StageParams::norm_w), norm_inv being
-//   1 / sqrt(mean square + eps) of the whole vector.
-template <bool kInDouble, bool kRoundBf16, int kN, typename Out, bool kNormed = false, typename Index>
+//   kNorm: 1 = the entries go through the RMSNorm first (StageParams::norm_w), norm_inv being
+//   1 / sqrt(mean square + eps) of the whole vector; 2 = they do if the instance has a norm
+//   weight (decided at run time, one copy of the code).
+template <bool kInDouble, bool kRoundBf16, int kN, typename Out, int kNorm = 0, typename Index>
 __device__ __forceinline__ void load_inputs(const StageParams &p, Index index_of, uint32_t n_bits, bool live,
                                             Out (&out)[kN], float norm_inv = 0.f) {
+    constexpr bool kNormed = kNorm != 0;
+    const bool normed = kNorm == 1 || (kNorm == 2 && p.norm_w != nullptr);
     uint32_t k[kN];
 #pragma unroll
     for (int e = 0; e < kN; ++e) k[e] = index_of(e);
@@ -235,8 +238,9 @@ __device__ __forceinline__ void load_inputs(const StageParams &p, Index index_of
     const bool gated = p.in_gate_up != nullptr, scaled = p.in_scale != nullptr;
     const float *up = gated ? p.in_gate_up : static_cast<const float *>(p.in);  // (a valid address either way)
     const float *sc = scaled ? p.in_scale : static_cast<const float *>(p.in);
-    const bool residual = kNormed && p.in_residual != nullptr;
+    const bool residual = normed && p.in_residual != nullptr;
     const float *res = residual ? p.in_residual : static_cast<const float *>(p.in);
+    const float *nwp = normed ? p.norm_w : static_cast<const float *>(p.in);
     float v[kN], u[kN], w[kN], rr[kNormed ? kN : 1], nw[kNormed ? kN : 1];
 #pragma unroll
     for (int e = 0; e < kN; ++e) {
@@ -246,13 +250,13 @@ __device__ __forceinline__ void load_inputs(const StageParams &p, Index index_of
         w[e] = sc[kc];
         if (kNormed) {
             rr[e] = res[kc];
-            nw[e] = p.norm_w[kc];
+            nw[e] = nwp[kc];
         }
     }
 #pragma unroll
     for (int e = 0; e < kN; ++e) {
         float x = v[e];
-        if (kNormed) {  // (the roundings of the norm kernel under bfloat16 serving)
+        if (kNormed && normed) {  // (the roundings of the norm kernel under bfloat16 serving)
             if (residual) x += rr[e];
             if (kRoundBf16) x = round_bf16(x);
             x = x * norm_inv * nw[e];
@@ -272,7 +276,7 @@ __device__ __forceinline__ void load_record(const StageParams &p, uint32_t r, ui
     const uint32_t base = ks * kStepBits + 128 * (rec % 4) + 32 * (rec / 16) + 2 * ((rec / 4) % 4);
     auto index_of = [&](int e) { return base + 8 * (e % 4) + e / 4; };
     if (!kInDouble && p.norm_w)
-        load_inputs<kInDouble, kRoundBf16, 8, Out, true>(p, index_of, n_bits, r < n_records, out, norm_inv);
+        load_inputs<kInDouble, kRoundBf16, 8, Out, 1>(p, index_of, n_bits, r < n_records, out, norm_inv);
     else
         load_inputs<kInDouble, kRoundBf16, 8, Out>(p, index_of, n_bits, r < n_records, out);
 }
@@ -524,7 +528,59 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
     __shared__ double red_max[16];
     __shared__ long long red_sum[16];
     StageMeta meta;
-    if (kSmemDigits) {
+    if (kSmemDigits && kSplitK && !kInSmem && !kFinal && red_smem &&
+        n_steps * kStepBits * 4 <= warps_per_block * 16 * 32 * 4) {
+        // The few-instance form's first stage.  A record's eight entries lie 8 and 128 floats
+        // apart: fetched from global memory record by record, a warp's load touches eight lines
+        // for 128 useful bytes, and the block spends microseconds in the load/store unit.  The
+        // vector is evaluated once instead, with coalesced loads (scale, norm, SwiGLU,
+        // rounding), into the buffer the k-split reduction uses later, and the records read
+        // it from there (the index is swizzled so that a warp's 32 reads fall into 32 banks).
+        float *zs = reinterpret_cast<float *>(red_smem);
+        auto swz = [](uint32_t k) { return k ^ (((k >> 7) & 3) << 3) ^ ((k >> 5) & 1); };
+        const uint32_t n_records = n_steps * 64, n_padded = n_steps * kStepBits;
+        double mx = 0.0;
+        int bad = 0;
+        for (uint32_t k0 = threadIdx.x; k0 < n_padded; k0 += 8 * blockDim.x) {
+            float vals[8];
+            load_inputs<false, kRoundBf16, 8, float, 2>(p, [&](int e) { return k0 + e * blockDim.x; }, n_bits, true,
+                                                        vals, norm_inv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const uint32_t k = k0 + e * blockDim.x;
+                if (k < n_padded) zs[swz(k)] = vals[e];
+                const double a = fabs((double)vals[e]);
+                if (!(a <= 1.7e308)) bad = 1;  // NaN or infinity
+                mx = fmax(mx, a);
+            }
+        }
+        for (int off = 16; off > 0; off >>= 1) mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        if (lane == 0) red_max[warp] = mx;
+        meta.nonfinite = __syncthreads_or(bad);  // (also: zs is complete)
+        double m = red_max[0];
+        for (uint32_t w = 1; w < warps_per_block; ++w) m = fmax(m, red_max[w]);
+        const FixedPoint fp = fixed_point_of(meta.nonfinite ? 0.0 : m);
+        meta.shift = fp.shift;
+        long long total = 0;
+        uint4 *table = reinterpret_cast<uint4 *>(table_smem);
+        for (uint32_t r = threadIdx.x; r < n_records; r += blockDim.x) {
+            const uint32_t ks = r / 64, rec = r % 64;
+            const uint32_t base = ks * kStepBits + 128 * (rec % 4) + 32 * (rec / 16) + 2 * ((rec / 4) % 4);
+            long long q8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                q8[e] = meta.nonfinite ? 0 : fp.quant((double)zs[swz(base + 8 * (e % 4) + e / 4)]);
+                total += q8[e];
+            }
+            build_record(q8, (rec / 4) % 4, table + (size_t)r * 4);
+        }
+        for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+        if (lane == 0) red_sum[warp] = total;
+        __syncthreads();  // the table and the partial totals are complete (zs is free again)
+        total = 0;
+        for (uint32_t w = 0; w < warps_per_block; ++w) total += red_sum[w];
+        meta.total = total;
+    } else if (kSmemDigits) {
         // Each thread owns whole records (eight vector entries each).  The first two
         // records of a thread stay in registers between the max pass and the
         // quantisation, so the input is read from memory once.
