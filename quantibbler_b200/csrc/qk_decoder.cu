@@ -524,10 +524,28 @@ decode_attention_rope_kernel(const float *__restrict__ q, const float *__restric
                              uint32_t n_kv, uint32_t gq, uint32_t s_max, uint32_t n_seq, uint32_t chunk,
                              uint32_t n_splits, int *__restrict__ error) {
     qk::pdl_launch();  // the next kernel may begin its prologue
+    const uint32_t split = blockIdx.x, ky = blockIdx.y, b = blockIdx.z;
+    {
+        // What this block streams - its split of the cache rows and the rotation's table row -
+        // was written by earlier steps, not by the kernel before this one (which makes q, k, v):
+        // ask for it before waiting for that kernel, so that the first touch (cold in L2 and in
+        // the TLB) overlaps its tail.
+        const uint32_t grp = n_heads / n_kv, sub_n = (grp + gq - 1) / gq, kvh = ky / sub_n;
+        const int len = min(kv_len[b], (int)s_max);
+        const int jb = (int)(split * chunk), je = min(len, (int)((split + 1) * chunk));
+        const uint16_t *kb = cache_k + (((size_t)b * n_kv + kvh) * s_max + jb) * 128;
+        const uint16_t *vb = cache_v + (((size_t)b * n_kv + kvh) * s_max + jb) * 128;
+        for (int line = threadIdx.x; line < 2 * (je - jb); line += blockDim.x) {  // (a row is two 128-byte lines)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(kb + (size_t)line * 64));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(vb + (size_t)line * 64));
+        }
+        const int p_in = min(max(positions[b], 0), (int)s_max - 1);
+        if (threadIdx.x < 4)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(cos_sin + (size_t)p_in * 128 + threadIdx.x * 32));
+    }
     qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     extern __shared__ __align__(16) uint8_t dec_smem[];
     __shared__ int is_last;
-    const uint32_t split = blockIdx.x, ky = blockIdx.y, b = blockIdx.z;
     const int pos = positions[b], seq = seq_index[b];
     const bool valid = pos >= 0 && (uint32_t)pos < s_max && seq >= 0 && (uint32_t)seq < n_seq;
     if (!valid && threadIdx.x == 0 && error) atomicOr(error, 4);  // skipped and reported, as rope_cache_kernel does

@@ -301,8 +301,13 @@ __global__ void __launch_bounds__(kTableThreads)
 digit_table_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32_t n_steps) {
     using T = typename std::conditional<kInDouble, double, float>::type;
     qk::pdl_launch();
-    qk::pdl_wait();
     const StageParams p = many[blockIdx.y];
+    // (the scale vector depends on no other kernel: its first touch, cold in caches and TLB,
+    // need not wait for the one before this)
+    if (!kInDouble && p.in_scale)
+        for (uint32_t line = threadIdx.x; line * 32 < n_bits; line += kTableThreads)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.in_scale + line * 32));
+    qk::pdl_wait();
     extern __shared__ __align__(16) uint8_t table_vec_raw[];
     T *vec = reinterpret_cast<T *>(table_vec_raw);  // the evaluated entries, zero beyond n_bits
     __shared__ unsigned long long red_max[kTableThreads / 32];
@@ -483,6 +488,26 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
     if (!prologue_issued) {
 #pragma unroll
         for (int s = 0; s < kStages - 1; ++s) issue(s);
+    }
+    if (kSplitK) {
+        // The few-instance form is a chain of latencies, and one of its links is the first
+        // touch of the small constant vectors (s2, the norm weight, s1, bias: a few KB each in
+        // allocations of their own, cold in the caches and in the TLB).  They depend on no
+        // other kernel either: ask for them before the wait.
+        auto ask = [](const float *v, uint32_t first, uint32_t n, uint32_t t, uint32_t t_n) {
+            // floats first .. first + n of v, one 128-byte line per thread t of t_n
+            for (uint32_t line = t; line * 32 < n; line += t_n)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(v + first + line * 32));
+        };
+        const uint32_t quarter = blockDim.x / 4, tq = threadIdx.x % quarter;
+        const uint32_t row0 = block_in_instance * kGroupRows;
+        const uint32_t rows = min((uint32_t)kGroupRows, n_rows - min(n_rows, row0));
+        switch (threadIdx.x / quarter) {
+            case 0: if (!kFinal && p.in_scale) ask(p.in_scale, 0, n_bits, tq, quarter); break;
+            case 1: if (!kFinal && p.norm_w) ask(p.norm_w, 0, n_bits, tq, quarter); break;
+            case 2: if (kFinal && p.out_scale) ask(p.out_scale, row0, rows, tq, quarter); break;
+            default: if (kFinal && p.out_bias) ask(p.out_bias, row0, rows, tq, quarter); break;
+        }
     }
     // The weight bits depend on no other kernel, the input vector does: from here on the
     // kernel before this one on the stream must be complete.
