@@ -382,10 +382,118 @@ digit_table_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32
     for (int e = 0; e < 8; ++e) q8[e] = nonfinite ? 0 : FloatBits<T>::quant(entries[e], fp.shift);
     build_record(q8, ip, reinterpret_cast<uint4 *>(p.digits + ((size_t)ks * 64 + rec) * 8));
 }
+// The same table by a thread-block CLUSTER per instance (float32 input, at most 32 k-steps):
+// CTA c of the cluster owns k-steps 4c .. 4c + 3, evaluates only ITS 2048 entries (coalesced
+// loads; scale, SwiGLU, rounding; into shared memory), and the CTAs agree on max|v| and on
+// sum q_k through each other's shared memory: every CTA pushes its maximum into a slot of
+// every CTA, a cluster barrier, every CTA reads its own slots; the partial sums go to CTA 0 the
+// same way.  Nothing is evaluated twice, which is what the one-vector-per-block form above
+// spends its time on (each of its blocks walks the whole vector).
+template <bool kRoundBf16>
+__global__ void __launch_bounds__(256)
+digit_table_cluster_kernel(const StageParams *__restrict__ many, uint32_t n_bits, uint32_t n_steps) {
+    qk::pdl_launch();
+    const StageParams p = many[blockIdx.y];
+    uint32_t rank, n_rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n_rank));
+    const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32, k_lo = rank * 4 * kStepBits;
+    // (the scale vector depends on no other kernel: its first touch need not wait)
+    if (p.in_scale && tid < 64 && k_lo + tid * 32 < n_bits)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.in_scale + k_lo + tid * 32));
+    qk::pdl_wait();
+    __shared__ float zs[4 * kStepBits];
+    __shared__ uint32_t cl_max[8], red_u[8];
+    __shared__ long long cl_total[8], red_s[8];
+    auto swz = [](uint32_t k) { return k ^ (((k >> 7) & 3) << 3) ^ ((k >> 5) & 1); };
+    auto cluster_sync = [] {
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    };
+    auto remote = [](const void *local, uint32_t cta) {  // the same shared-memory word in CTA `cta`
+        uint32_t r;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(cta));
+        return r;
+    };
+
+    float vals[8];
+    load_inputs<false, kRoundBf16, 8, float>(p, [&](int e) { return k_lo + tid + 256 * e; }, n_bits, true, vals);
+    uint32_t mx = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        zs[swz(tid + 256 * e)] = vals[e];
+        mx = max(mx, __float_as_uint(vals[e]) & 0x7fffffffu);
+    }
+    for (int off = 16; off > 0; off >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if (lane == 0) red_u[warp] = mx;
+    __syncthreads();  // (also: zs is complete)
+    if (tid < n_rank) {
+        uint32_t bm = red_u[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) bm = max(bm, red_u[w]);
+        asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote(&cl_max[rank], tid)), "r"(bm) : "memory");
+    }
+    cluster_sync();
+    mx = cl_max[0];
+    for (uint32_t c = 1; c < n_rank; ++c) mx = max(mx, cl_max[c]);
+    const bool nonfinite = mx >= 0x7f800000u;  // NaN or infinity somewhere in the vector
+    const FixedPoint fp = fixed_point_of(nonfinite ? 0.0 : (double)__uint_as_float(mx));
+
+    const uint32_t ks = rank * 4 + tid / 64, rec = tid % 64;
+    long long total = 0;
+    if (ks < n_steps) {
+        const uint32_t base = (tid / 64) * kStepBits + 128 * (rec % 4) + 32 * (rec / 16) + 2 * ((rec / 4) % 4);
+        long long q8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            q8[e] = nonfinite ? 0 : fp.quant((double)zs[swz(base + 8 * (e % 4) + e / 4)]);
+            total += q8[e];
+        }
+        build_record(q8, (rec / 4) % 4, reinterpret_cast<uint4 *>(p.digits + ((size_t)ks * 64 + rec) * 8));
+    }
+    for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+    if (lane == 0) red_s[warp] = total;
+    __syncthreads();
+    if (tid == 0) {
+        long long bt = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) bt += red_s[w];
+        asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(remote(&cl_total[rank], 0)), "l"(bt) : "memory");
+    }
+    cluster_sync();  // (nobody leaves while a peer may still write into its shared memory)
+    if (rank == 0 && tid == 0) {
+        long long sum = 0;
+        for (uint32_t c = 0; c < n_rank; ++c) sum += cl_total[c];
+        p.meta->total = sum;
+        p.meta->shift = fp.shift;
+        p.meta->nonfinite = nonfinite;
+    }
+}
+
 // Launches it for n_inst instances of one stage.
 template <bool kFinal>
 qk_status launch_digit_table(qk_ctx *c, const StageParams *many, size_t n_inst, size_t n_bits, size_t n_steps,
                              bool bf16) {
+    if (!kFinal && qk::ceil_div(n_steps, (size_t)4) <= 8 && n_inst <= 65535) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)qk::ceil_div(n_steps, (size_t)4), (unsigned)n_inst);
+        cfg.blockDim = dim3(256);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = c->stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = c->pdl ? 1 : 0;
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = cfg.gridDim.x;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
+        QK_CUDA(cudaLaunchKernelEx(&cfg, bf16 ? digit_table_cluster_kernel<true> : digit_table_cluster_kernel<false>,
+                                   many, (uint32_t)n_bits, (uint32_t)n_steps));
+        c->launches++;
+        return QK_OK;
+    }
     const size_t smem = n_steps * kStepBits * (kFinal ? 8 : 4);  // (stage 2 reads the float64 intermediate)
     const bool cache = smem <= 200 * 1024;
     auto table = cache ? (bf16 ? digit_table_kernel<kFinal, true, true> : digit_table_kernel<kFinal, false, true>)
