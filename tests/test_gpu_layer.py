@@ -447,3 +447,37 @@ def test_host_layer_group_matches_per_layer_host_apply(gpu_ctx):
     with pytest.raises(KernelError, match="host buffers must be"):
         step.apply(x_host[:3], y_host)
     step.close()
+
+
+@pytest.mark.parametrize("serving", ["float32", "bfloat16"])
+@pytest.mark.parametrize("din", [8192, 9000, 14336])
+def test_long_input_vector_in_the_few_instance_form(gpu_ctx, serving, din):
+    """A single instance over a long input (8192 entries and more, the down projection's kind):
+    its digit table is built once, by a thread-block cluster that shares out the k-steps, and the
+    stage's blocks only stream.  Ragged lengths (a partial k-step, a partial last CTA), plain and
+    through the SwiGLU, against the oracle; non-finite input gives NaN."""
+    import torch
+    from quantibbler_b200.gpu import LayerPlan
+    dout, r = 200, 150
+    L = make_layer(dout, din, r, seed=din % 97, with_bias=True)
+    y, want = check_layer(gpu_ctx, L, serving, expect_bit_identical=False)
+    layer = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], dout, din, r, L["s1"], L["s2"], L["bias"],
+                        serving=serving)
+    rng = np.random.default_rng(din)
+    gate = (rng.standard_normal(din) * 3).astype(np.float32)
+    up = rng.standard_normal(din).astype(np.float32)
+    tg, tu = torch.from_numpy(gate).cuda(), torch.from_numpy(up).cuda()
+    out = torch.full((dout,), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    gated = LayerPlan(gpu_ctx, [(layer, tg.data_ptr(), tu.data_ptr(), out.data_ptr())], gated=True)
+    gated.apply()
+    gpu_ctx.synchronize()
+    act = (tg * tu / (1.0 + torch.exp(-tg))).cpu().numpy()
+    ref = oracle.layer_apply(L["ub_rows"], L["vb_t_rows"], dout, din, r, L["s1"], L["s2"], L["bias"], act,
+                             serving=serving)
+    got = out.cpu().numpy()
+    assert np.abs(got - ref).max() <= (2e-5 if serving == "float32" else 2e-2) * np.abs(ref).max()
+    bad = L["x"].copy()
+    bad[din - 3] = np.inf
+    assert np.isnan(layer.apply(bad)).all()
+    layer.close()
