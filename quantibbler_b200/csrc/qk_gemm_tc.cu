@@ -150,6 +150,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                           const __grid_constant__ CUtensorMap map2, const __grid_constant__ CUtensorMap map3,
                           GemmArgs g) {
+    qk::pdl_launch();  // the kernel after this one may begin its prologue
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment of the tiles is what the swizzle pattern assumes
     uint8_t *tiles = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -197,6 +198,10 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // Barriers and tensor memory are set up; from here on the kernel reads what the kernel
+    // before it wrote (the activations, the partial-sum workspace and its flags).  Every thread
+    // waits, so that this kernel's completion implies the completion of everything before it.
+    qk::pdl_wait();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t total_chunks = u_end - u_begin;
 
@@ -468,6 +473,8 @@ struct ScaleArgs {
 };
 __global__ void scale_to_bf16_kernel(const float *__restrict__ x, ScaleArgs a, uint32_t n_tokens,
                                      uint32_t din, uint32_t pitch, int vec) {
+    qk::pdl_launch();  // the kernel after this one may begin its prologue
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     const float *__restrict__ s2 = a.s2[blockIdx.y];
     uint16_t *__restrict__ z = a.z[blockIdx.y];
     const uint32_t per_row = pitch / 8;
@@ -588,8 +595,9 @@ qk_status qk_layers_apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, si
     }
     const int vec = ((uintptr_t)x_dev & 15) == 0 && (din & 3) == 0;
     const size_t total = n_tokens * (kp1 / 8);
-    scale_to_bf16_kernel<<<dim3((unsigned)qk::ceil_div(total, 256), (unsigned)n_layers), 256, 0, c->stream>>>(
-        x_dev, sa, (uint32_t)n_tokens, (uint32_t)din, (uint32_t)kp1, vec);
+    (void)qk::launch_pdl(c->pdl, scale_to_bf16_kernel,
+                         dim3((unsigned)qk::ceil_div(total, 256), (unsigned)n_layers), dim3(256), 0, c->stream, x_dev,
+                         sa, (uint32_t)n_tokens, (uint32_t)din, (uint32_t)kp1, vec);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     QK_CUDA(cudaFuncSetAttribute(factorized_gemm_tc_kernel<false>,
@@ -638,12 +646,12 @@ qk_status qk_layers_apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, si
     g1.partials = g2.partials = partials;
     g1.flags = g2.flags = flags;
     g1.wait_limit = g2.wait_limit = c->wait_limit ? c->wait_limit : kWaitLimitDefault;
-    factorized_gemm_tc_kernel<false><<<grid1, kThreads, kSmemBytes, c->stream>>>(
-        maps1[0], maps1[1], maps1[2], maps1[3], g1);
+    (void)qk::launch_pdl(c->pdl, factorized_gemm_tc_kernel<false>, dim3(grid1), dim3(kThreads), kSmemBytes,
+                         c->stream, maps1[0], maps1[1], maps1[2], maps1[3], g1);
     QK_CUDA(cudaGetLastError());
     c->launches++;
-    factorized_gemm_tc_kernel<true><<<grid2, kThreads, kSmemBytes, c->stream>>>(
-        maps2[0], maps2[1], maps2[2], maps2[3], g2);
+    (void)qk::launch_pdl(c->pdl, factorized_gemm_tc_kernel<true>, dim3(grid2), dim3(kThreads), kSmemBytes,
+                         c->stream, maps2[0], maps2[1], maps2[2], maps2[3], g2);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     c->err_armed = true;
