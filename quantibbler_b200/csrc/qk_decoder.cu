@@ -169,7 +169,11 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
     float keep[kRmsPerThread];
     float ss = 0.f;
     for (uint32_t pass = 0; pass * kSlots * kRmsThreads < d; ++pass) {
-        float own[kSlots];
+        float own[kSlots], xv[kSlots];
+        // (the residual stream's elements are asked for now: they arrive while the peers' do)
+#pragma unroll
+        for (int sl = 0; sl < kSlots; ++sl)
+            xv[sl] = x[base + min(threadIdx.x + (pass * kSlots + sl) * kRmsThreads, d - 1)];
         // ---- send: my partial, tagged, into every peer's inbox
 #pragma unroll
         for (int sl = 0; sl < kSlots; ++sl) {
@@ -226,7 +230,7 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
         for (int sl = 0; sl < kSlots; ++sl) {
             const uint32_t i = threadIdx.x + (pass * kSlots + sl) * kRmsThreads;
             if (i < d) {
-                float h = x[base + i] + sum[sl];
+                float h = xv[sl] + sum[sl];
                 if (writer) x_out[base + i] = h;
                 if (bf16) h = round_bf16f(h);
                 if (pass * kSlots + sl < (uint32_t)kRmsPerThread) keep[pass * kSlots + sl] = h;
@@ -239,15 +243,29 @@ allreduce_rmsnorm_kernel(InboxArgs inbox, const float *__restrict__ partial,
     if (dead && threadIdx.x == 0) atomicOr(error, 2);
     if (!dead) {
         const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
-        for (uint32_t r = 0; threadIdx.x + r * kRmsThreads < d; ++r) {
-            const uint32_t i = threadIdx.x + r * kRmsThreads;
-            float h;
-            if (r < (uint32_t)kRmsPerThread) {
-                h = keep[r];
-            } else {
-                h = x_out[base + i];   // (rows wider than the register cache: one block per token only)
-                if (bf16) h = round_bf16f(h);
+        // (eight of a thread's sixteen elements at a time, the weight's loads issued together:
+        // one memory latency per eight instead of one per element)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            if ((uint32_t)half * (kRmsPerThread / 2) * kRmsThreads >= d) break;
+            float wv[kRmsPerThread / 2];
+#pragma unroll
+            for (int r = 0; r < kRmsPerThread / 2; ++r)
+                wv[r] = w[min(threadIdx.x + (half * (kRmsPerThread / 2) + r) * kRmsThreads, d - 1)];
+#pragma unroll
+            for (int r = 0; r < kRmsPerThread / 2; ++r) {
+                const uint32_t i = threadIdx.x + (half * (kRmsPerThread / 2) + r) * kRmsThreads;
+                if (i < d) {
+                    float o = keep[half * (kRmsPerThread / 2) + r] * inv * wv[r];
+                    if (bf16) o = round_bf16f(o);
+                    if (writer) y[base + i] = o;
+                    if (feed.n) norm_row[i] = o;
+                }
             }
+        }
+        for (uint32_t i = threadIdx.x + kRmsPerThread * kRmsThreads; i < d; i += kRmsThreads) {
+            float h = x_out[base + i];   // (rows wider than the register cache: one block per token only)
+            if (bf16) h = round_bf16f(h);
             float o = h * inv * w[i];
             if (bf16) o = round_bf16f(o);
             if (writer) y[base + i] = o;
