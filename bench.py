@@ -280,7 +280,9 @@ def measure_decode(ctx, cfg, ranks, batch, ctx_len, steps, warmup, rank, world, 
     per_step = ms / steps
     return {"tok_s": batch / (per_step * 1e-3), "ms_per_step": per_step, "batch": batch,
             "context": ctx_len, "steps": steps,
-            "allreduce": ("none" if world == 1 else "fused" if dec.fused_ar else "nccl"),
+            "allreduce": ("none" if world == 1 else
+                          "inside the GEMV plans (pushed to peer inboxes by o / down, summed by the norm inside "
+                          "gate,up / q,k,v)" if dec.allreduce_in_plans else "fused" if dec.fused_ar else "nccl"),
             "kernels_per_step": dec.kernels_per_step,
             "weight_bytes_per_rank": weight_bytes_per_rank(dec)}, dec
 
@@ -409,7 +411,9 @@ def tp_decode_block(args, ctx, rank: int, world: int, group) -> dict:
                                    args.allreduce)
         res, dec = measure_decode(ctx, cfg, ranks, batch, ctx_len, steps, 3, rank, world, group,
                                   share_from=shared)
-        res["allreduce_ms_per_step"] = measure_allreduce(dec, world, group, 2 * cfg.n_layers)
+        # (with the all-reduce inside the plans there is no all-reduce launch to time on its own)
+        res["allreduce_ms_per_step"] = (None if dec.allreduce_in_plans
+                                        else measure_allreduce(dec, world, group, 2 * cfg.n_layers))
         if batch == 1:
             # the prompt itself: 2048 tokens through the trunk in one pass (tensor-core GEMM for
             # every linear, tensor-core causal attention, head on the last position only)

@@ -300,6 +300,22 @@ qk_status qk_plan_create_gated(qk_ctx *ctx, const qk_layer *const *layers,
  * form with at most 8192 inputs, otherwise QK_ERR_VALUE and the plan is unchanged. */
 qk_status qk_plan_set_norm(qk_ctx *ctx, qk_group *plan, const float *const *residual_ptrs,
                            const float *norm_weight, float eps, float *const *x_out_ptrs);
+/* Tensor parallel: the all-reduce of a row-parallel linear's output inside the plans on either
+ * side of it (the reference has no parallelism; the partition is the benchmark's).  With
+ * gather = 0 the plan's last stage pushes every output it finishes, tagged with the number of
+ * the all-reduce, into the inbox of every rank (inbox_bases[0 .. world), peer memory, this
+ * rank's own included) instead of storing it.  With gather = 1 the plan - a normed plan over the
+ * stream of d <= 4096 entries - takes as the residual of its norm the sum, in rank order, of what
+ * has arrived in this rank's inbox (inbox_bases[0]); its blocks poll for the words they need
+ * with the context's wait limit (QK_ERR_TIMEOUT at the next qk_gpu_synchronize on expiry).  An
+ * inbox holds world x total_words 8-byte words {value, number}; instance k belongs to token
+ * token_of_instance[k] (words token * d ..).  state_dev: two zero-initialised uint32 shared by
+ * all plans and qk_allreduce_rmsnorm calls of the process group member, in call order: the
+ * number of all-reduces completed and a block ticket.  Same bits as qk_allreduce_rmsnorm
+ * between the plain plans.  Successive all-reduces must alternate between two inboxes. */
+qk_status qk_plan_set_allreduce(qk_ctx *ctx, qk_group *plan, int32_t gather, const uint64_t *inbox_bases,
+                                int32_t rank, int32_t world, size_t total_words, const uint32_t *token_of_instance,
+                                size_t d, uint32_t *state_dev);
 qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group);
 /* Many independent applies with HOST buffers as a pipeline: groups[p] (made by qk_group_create
  * over rows first_row[p] .. first_row[p+1] of x_dev / y_dev) has its inputs copied up from

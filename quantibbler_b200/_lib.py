@@ -83,6 +83,8 @@ _SIGNATURES = {
                                        POINTER(c_void_p)]),
     "qk_plan_set_norm": (c_int32, [c_void_p, c_void_p, POINTER(c_void_p), c_void_p, ctypes.c_float,
                                    POINTER(c_void_p)]),
+    "qk_plan_set_allreduce": (c_int32, [c_void_p, c_void_p, c_int32, c_void_p, c_int32, c_int32, c_size_t,
+                                        c_void_p, c_size_t, c_void_p]),
     "qk_group_apply": (c_int32, [c_void_p, c_void_p]),
     "qk_plan_feed_targets": (c_int32, [c_void_p, c_void_p, POINTER(c_void_p), POINTER(c_size_t)]),
     "qk_decode_attention_rope_scratch": (c_size_t, [c_size_t, c_size_t, c_size_t, c_size_t, c_size_t]),

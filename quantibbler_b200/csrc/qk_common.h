@@ -108,6 +108,8 @@ struct qk_group {
     bool mixed = false;      // the members differ in shape: few-instance form only
     bool fed = false;        // the stage-1 tables are written by the kernels that produce the inputs
     bool normed = false;     // stage 1 applies an RMSNorm to its input itself (qk_plan_set_norm)
+    bool pushed = false;     // the last stage pushes its outputs into all-reduce inboxes (qk_plan_set_allreduce)
+    bool gathered = false;   // the norm's residual is what an all-reduce left in this rank's inbox
     void *feed = nullptr;    // device array of per-instance feed targets (fed plans)
     void *tickets = nullptr; // device array of per-instance block counters (fed plans)
     void *scratch = nullptr; // per member: intermediate t, digit tables, stage metadata

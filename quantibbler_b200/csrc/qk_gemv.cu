@@ -77,6 +77,19 @@ struct StageParams {
     const float *in_residual;
     float *x_out;
     float norm_eps;
+    // Tensor parallel, the all-reduce inside the plans (few-instance form).  A row-parallel
+    // linear's last stage PUSHES each output it has finished, tagged with the number of this
+    // all-reduce, into the inbox of every rank (ar_push[p], peer memory; its own included)
+    // instead of storing it.  The normed plan that follows takes as its residual the sum, in
+    // rank order, of what has arrived in this rank's inbox (ar_inbox): every block of its first
+    // stage polls the words it needs (bounded; error bit 2 on expiry).  An inbox word is
+    // {value, all-reduce number}, read and written as one 64-bit access; word
+    // (source rank * ar_total + ar_offset + channel) belongs to this instance's token.
+    unsigned long long *ar_push[8];
+    const unsigned long long *ar_inbox;
+    uint32_t *ar_state;   // [0] all-reduces completed, [1] ticket of the consuming launch's blocks
+    int *ar_error;
+    uint32_t ar_rank, ar_world, ar_total, ar_offset, ar_poll_limit;
 };
 
 // ------------------------------------------------------------------ sign-select kernel
@@ -624,32 +637,73 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
     // forms it (512 threads, element i of a thread's sixteen is tid + 512 i, warp sums by
     // shuffles, then the warps' sums in order), and the updated residual stream
     float norm_inv = 0.f;
+    // the number of the all-reduce this launch sends (last stage) or receives (first stage)
+    const uint32_t ar_step = (kSplitK && (kFinal ? p.ar_world != 0 : p.ar_inbox != nullptr)) ? *p.ar_state + 1 : 0;
+    float hk[8];  // a normed instance's entries tid + 512 i after the residual add (rounded), i < 8
+    bool hk_valid = false;
     if (!kFinal && !kInSmem && p.norm_w) {
         __shared__ float norm_red[16];
         const float *xs = static_cast<const float *>(p.in);
         const bool writer = p.x_out && block_in_instance == 0;
-        // (all loads first, unconditional, so that they are in flight together)
+        // (eight of a thread's sixteen elements at a time: their loads go out together; the
+        // second eight only exist beyond 4096 entries, and adding their zeros changes nothing)
         const float *rs = p.in_residual ? p.in_residual : xs;
-        float hx[16], hr[16];
-#pragma unroll
-        for (int rr = 0; rr < 16; ++rr) {
-            const uint32_t i = min(threadIdx.x + rr * 512, n_bits - 1);
-            hx[rr] = xs[i];
-            hr[rr] = rs[i];
-        }
         float ss = 0.f;
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+            if (half * 8u * 512u >= n_bits) break;
+            float hx[8], hr[8];
 #pragma unroll
-        for (int rr = 0; rr < 16; ++rr) {
-            const uint32_t i = threadIdx.x + rr * 512;
-            float h = 0.f;
-            if (i < n_bits) {
-                h = hx[rr];
-                if (p.in_residual) h += hr[rr];
-                if (writer) p.x_out[i] = h;
-                if (kRoundBf16) h = round_bf16(h);
+            for (int rr = 0; rr < 8; ++rr) {
+                const uint32_t i = min(threadIdx.x + (8 * half + rr) * 512, n_bits - 1);
+                hx[rr] = xs[i];
+                hr[rr] = rs[i];
             }
-            ss += h * h;
+            const bool gathered = kSplitK && p.ar_inbox != nullptr;  // (only for vectors of at most 4096 entries)
+            if (gathered) {
+                // the residual is the sum over the ranks, in rank order, of what they pushed
+                // into this rank's inbox for this all-reduce
+#pragma unroll
+                for (int rr = 0; rr < 8; ++rr) hr[rr] = 0.f;
+                bool all_ready = true;
+                for (uint32_t r = 0; r < p.ar_world; ++r) {
+                    const unsigned long long *src = p.ar_inbox + (size_t)r * p.ar_total + p.ar_offset;
+                    float got[8];
+                    bool ready = false;
+                    for (uint32_t tries = 0; tries < p.ar_poll_limit && !ready; ++tries) {
+                        ready = true;
+#pragma unroll
+                        for (int rr = 0; rr < 8; ++rr) {
+                            const uint32_t i = threadIdx.x + rr * 512;
+                            unsigned long long word = (unsigned long long)ar_step << 32;
+                            if (i < n_bits)
+                                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(src + i) : "memory");
+                            got[rr] = __uint_as_float((uint32_t)word);
+                            if ((uint32_t)(word >> 32) != ar_step) ready = false;
+                        }
+                    }
+                    if (!ready) all_ready = false;
+#pragma unroll
+                    for (int rr = 0; rr < 8; ++rr) hr[rr] += got[rr];
+                }
+                if (!all_ready && p.ar_error) atomicOr(p.ar_error, 2);  // (reported at the next synchronise)
+            }
+            const bool add = gathered || p.in_residual != nullptr;
+#pragma unroll
+            for (int rr = 0; rr < 8; ++rr) {
+                const uint32_t i = threadIdx.x + (8 * half + rr) * 512;
+                float h = 0.f;
+                if (i < n_bits) {
+                    h = hx[rr];
+                    if (add) h += hr[rr];
+                    if (writer) p.x_out[i] = h;
+                    if (kRoundBf16) h = round_bf16(h);
+                }
+                if (half == 0) hk[rr] = h;
+                ss += h * h;
+            }
         }
+        hk_valid = n_bits <= 8u * 512u && blockDim.x == 512;
         for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
         if (lane == 0) norm_red[warp] = ss;
         __syncthreads();
@@ -676,8 +730,30 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
         int bad = 0;
         for (uint32_t k0 = threadIdx.x; k0 < n_padded; k0 += 8 * blockDim.x) {
             float vals[8];
-            load_inputs<false, kRoundBf16, 8, float, 2>(p, [&](int e) { return k0 + e * blockDim.x; }, n_bits, true,
-                                                        vals, norm_inv);
+            if (hk_valid) {
+                // a normed instance: the thread still holds its entries from the norm (the same
+                // elements tid + 512 e), so neither the stream nor the residual - which may have
+                // come out of the all-reduce inbox - is read again
+                const float *nwp = p.norm_w, *scp = p.in_scale ? p.in_scale : p.norm_w;
+                float nw[8], sc[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const uint32_t kc = min(k0 + e * 512, n_bits - 1);
+                    nw[e] = nwp[kc];
+                    sc[e] = scp[kc];
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    float x = hk[e] * norm_inv * nw[e];
+                    if (kRoundBf16) x = round_bf16(x);
+                    if (p.in_scale) x = sc[e] * x;
+                    if (kRoundBf16) x = round_bf16(x);
+                    vals[e] = k0 + e * 512 < n_bits ? x : 0.f;
+                }
+            } else {
+                load_inputs<false, kRoundBf16, 8, float, 2>(p, [&](int e) { return k0 + e * blockDim.x; }, n_bits,
+                                                            true, vals, norm_inv);
+            }
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const uint32_t k = k0 + e * blockDim.x;
@@ -840,7 +916,17 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
                 float y = (float)val;
                 if (p.out_scale) y = y * p.out_scale[row];
                 if (p.out_bias) y = y + p.out_bias[row];
-                static_cast<float *>(p.out)[row] = y;
+                if (kSplitK && p.ar_world) {
+                    // this rank's part of a row-parallel output: into every rank's inbox
+                    const unsigned long long word =
+                        (unsigned long long)__float_as_uint(y) | ((unsigned long long)ar_step << 32);
+                    const size_t at = (size_t)p.ar_rank * p.ar_total + p.ar_offset + row;
+                    for (uint32_t peer = 0; peer < p.ar_world; ++peer)
+                        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p.ar_push[peer] + at), "l"(word)
+                                     : "memory");
+                } else {
+                    static_cast<float *>(p.out)[row] = y;
+                }
             } else {
                 static_cast<double *>(p.out)[row] = val;
             }
@@ -982,8 +1068,23 @@ gemv_bitslice_splitk_kernel(const StageParams *__restrict__ many) {
     const uint32_t n_rows = p.n_rows, n_bits = p.n_bits;
     const uint32_t n_groups = (n_rows + kGroupRows - 1) / kGroupRows;
     const uint32_t n_steps = (n_bits + kStepBits - 1) / kStepBits;
+    // A launch that receives an all-reduce counts its blocks: the last one to finish records
+    // that the all-reduce is done (every block has read the number by then).
+    auto all_reduce_done = [&] {
+        if (kFinal || kFed || !p.ar_inbox) return;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const uint32_t step = *p.ar_state + 1;
+            __threadfence();
+            if (atomicAdd(p.ar_state + 1, 1u) == gridDim.x * gridDim.y - 1) {
+                p.ar_state[1] = 0;
+                p.ar_state[0] = step;
+            }
+        }
+    };
     if (blockIdx.x >= n_groups) {
         qk::pdl_wait();
+        all_reduce_done();
         return;
     }
     uint8_t *ring = smem_dyn + (kFed ? 0 : (size_t)n_steps * 4096);
@@ -991,6 +1092,7 @@ gemv_bitslice_splitk_kernel(const StageParams *__restrict__ many) {
     bitslice_stage<kRoundBf16, kFinal, !kFed, false, false, true>(
         p, smem_dyn, ring, nullptr, nullptr, n_rows, n_bits, n_groups, n_steps, blockIdx.x, 1, false,
         red);
+    all_reduce_done();
     if (kFed && !kFinal && p.ticket) {
         // hand-over to stage 2: whoever finishes last has all of t in front of it
         __shared__ double tail_max[32];
@@ -1598,7 +1700,7 @@ constexpr size_t kSpreadTableSteps = 16;  // k-steps (of 512 inputs) from which 
 
 template <bool kFinal>
 qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, const StageShape &s,
-                          bool bf16) {
+                          bool bf16, bool need_few = false) {
     const StagePlan pl = plan_stage(c, s, n_inst);
     // Few instances: the streaming form would leave most SMs idle and make each warp walk
     // its chunks in sequence.  Give every row group a block whose warps split the k-steps.
@@ -1624,6 +1726,8 @@ qk_status launch_bitslice(qk_ctx *c, const StageParams *many, size_t n_inst, con
         c->launches++;
         return QK_OK;
     }
+    if (need_few && !(few && pl.smem_digits && sk_smem <= kSmemBudget && s.n_steps < kSpreadTableSteps))
+        return qk::fail(QK_ERR_VALUE, "a plan that pushes its output into an all-reduce must fit the few-instance form");
     if (few && pl.smem_digits && sk_smem <= kSmemBudget) {
         dim3 grid((unsigned)s.n_groups, (unsigned)n_inst);
         auto gemv = bf16 ? gemv_bitslice_splitk_kernel<true, kFinal>
@@ -1832,7 +1936,17 @@ qk_status launch_normed_stage1(qk_ctx *c, const StageParams *many, size_t n_inst
 }
 
 qk_status launch_both(qk_ctx *c, const qk_layer *l0, const StageParams *d, size_t n_inst,
-                      int kernel, bool mixed = false, bool fed = false, bool normed = false) {
+                      int kernel, bool mixed = false, bool fed = false, bool normed = false, bool pushed = false) {
+    if (pushed && !normed && !fed) {
+        // (the last stage pushes into the all-reduce inboxes: only the few-instance kernel does)
+        const bool bf16 = l0->serving == QK_BF16;
+        qk_status e = mixed ? launch_mixed_stage<false>(c, d, n_inst, stage1_shape(l0), bf16)
+                            : launch_bitslice<false>(c, d, n_inst, stage1_shape(l0), bf16);
+        if (e != QK_OK) return e;
+        if (mixed) return launch_mixed_stage<true>(c, d + n_inst, n_inst, stage2_shape(l0), bf16);
+        return launch_bitslice<true>(c, d + n_inst, n_inst, stage2_shape(l0), bf16, true);
+    }
+    if (pushed) return qk::fail(QK_ERR_VALUE, "a normed or fed plan cannot push into an all-reduce");
     if (normed) {
         const bool bf16 = l0->serving == QK_BF16;
         qk_status e = launch_normed_stage1(c, d, n_inst, stage1_shape(l0), bf16);
@@ -2251,6 +2365,55 @@ qk_status qk_plan_set_norm(qk_ctx *ctx, qk_group *plan, const float *const *resi
     return QK_OK;
 }
 
+qk_status qk_plan_set_allreduce(qk_ctx *ctx, qk_group *plan, int32_t gather, const uint64_t *inbox_bases,
+                                int32_t rank, int32_t world, size_t total_words, const uint32_t *token_of_instance,
+                                size_t d, uint32_t *state_dev) {
+    if (!plan || !inbox_bases || !token_of_instance || !state_dev)
+        return qk::fail(QK_ERR_VALUE, "qk_plan_set_allreduce: plan, inboxes, tokens and state must be given");
+    if (world < 2 || world > 8 || rank < 0 || rank >= world)
+        return qk::fail(QK_ERR_VALUE, "qk_plan_set_allreduce: rank %d of %d (2 to 8 ranks)", rank, world);
+    qk_ctx *c;
+    qk_status st = qk::resolve_ctx(ctx, &c);
+    if (st != QK_OK) return st;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    if (plan->device != c->device)
+        return qk::fail(QK_ERR_VALUE, "plan lives on device %d, context on device %d", plan->device, c->device);
+    if ((st = qk::error_word(c)) != QK_OK) return st;
+    const size_t n = plan->n_inst;
+    if (total_words == 0 || d == 0 || total_words % d != 0 || (uint64_t)world * total_words >= (1ull << 32))
+        return qk::fail(QK_ERR_VALUE, "qk_plan_set_allreduce: %zu inbox words per rank for rows of %zu", total_words, d);
+    if (gather && (!plan->normed || d > 4096 || plan->shape.din != d))
+        return qk::fail(QK_ERR_VALUE, "a plan gathers an all-reduce as the residual of its norm: it must be a normed "
+                        "plan over the %zu-entry stream (at most 4096 entries)", d);
+    if (!gather && (plan->normed || plan->fed))
+        return qk::fail(QK_ERR_VALUE, "a normed or fed plan cannot push into an all-reduce");
+    std::vector<StageParams> h(2 * n);
+    QK_CUDA(cudaMemcpy(h.data(), plan->params, h.size() * sizeof(StageParams), cudaMemcpyDeviceToHost));
+    for (size_t k = 0; k < n; ++k) {
+        if ((size_t)token_of_instance[k] * d >= total_words)
+            return qk::fail(QK_ERR_VALUE, "instance %zu: token %u is outside the inbox", k, token_of_instance[k]);
+        StageParams &p = gather ? h[k] : h[n + k];
+        if (!gather && p.n_rows != d)
+            return qk::fail(QK_ERR_VALUE, "instance %zu writes %u outputs, the all-reduced stream has %zu", k, p.n_rows, d);
+        if (gather) {
+            p.ar_inbox = reinterpret_cast<const unsigned long long *>(inbox_bases[0]);
+        } else {
+            for (int r = 0; r < world; ++r) p.ar_push[r] = reinterpret_cast<unsigned long long *>(inbox_bases[r]);
+        }
+        p.ar_state = state_dev;
+        p.ar_error = (int *)c->d_err.ptr;
+        p.ar_rank = (uint32_t)rank;
+        p.ar_world = (uint32_t)world;
+        p.ar_total = (uint32_t)total_words;
+        p.ar_offset = (uint32_t)(token_of_instance[k] * d);
+        p.ar_poll_limit = c->wait_limit ? c->wait_limit : (1u << 22);
+    }
+    QK_CUDA(cudaMemcpy(plan->params, h.data(), h.size() * sizeof(StageParams), cudaMemcpyHostToDevice));
+    (gather ? plan->gathered : plan->pushed) = true;
+    return QK_OK;
+}
+
 qk_status qk_plan_feed_targets(qk_ctx *ctx, qk_group *plan, const void **targets_dev,
                                size_t *n_targets) {
     if (!plan || !targets_dev || !n_targets)
@@ -2302,8 +2465,15 @@ qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group) {
     if (group->device != c->device)
         return qk::fail(QK_ERR_VALUE, "group lives on device %d, context on device %d",
                         group->device, c->device);
+    if ((group->pushed || group->gathered) && (c->gemv_kernel == 0 || c->gemv_kernel == 3))
+        return qk::fail(QK_ERR_VALUE, "plans that take part in an all-reduce need the bit-sliced few-instance kernels");
+    if (group->pushed || group->gathered) {
+        qk_status e = qk::error_word(c);
+        if (e != QK_OK) return e;
+        c->err_armed = true;
+    }
     return launch_both(c, &group->shape, (const StageParams *)group->params, group->n_inst,
-                       c->gemv_kernel, group->mixed, group->fed, group->normed);
+                       c->gemv_kernel, group->mixed, group->fed, group->normed, group->pushed);
 }
 
 qk_status qk_groups_apply_host(qk_ctx *ctx, const qk_group *const *groups, const size_t *first_row,

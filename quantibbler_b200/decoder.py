@@ -213,6 +213,7 @@ class Decoder:
         self.delta = torch.zeros(B, d, **f32)
         self.delta_attn = self.delta_mlp = self.delta
         self.fused_ar = False
+        self.allreduce_in_plans = False   # (the row-parallel sums happen inside the GEMV plans)
         # The fused form is a one-shot push: every rank stores its whole partial to every peer.
         # That wins while the pushed bytes are few (measured: batch 1 at 2 and 8 ranks, batch 64
         # at 2 ranks) and loses to NCCL's bandwidth-optimal schedule when they are many (batch
@@ -321,7 +322,10 @@ class Decoder:
             else:
                 plan["gate"] = LayerPlan(ctx, inst(["gate"], self.h, [self.g]))
                 plan["up"] = LayerPlan(ctx, inst(["up"], self.h, [self.u]))
-            if (B <= cfg.norm_fused_max_batch and tp_size == 1 and not fed and not gemm
+            # (under tensor parallelism the norms are also where the row-parallel outputs are summed
+            # over the ranks: with the all-reduce over peer memory the plans do that themselves)
+            if (B <= cfg.norm_fused_max_batch and (tp_size == 1 or (self.fused_ar and d <= 4096))
+                    and not fed and not gemm
                     and cfg.serving in ("float32", "bfloat16") and "qkv" in plan and "gu" in plan):
                 # the first norm of a block reads the stream from x and leaves it in x2, the second
                 # the other way round; what they add is the output of the linear before them
@@ -334,11 +338,30 @@ class Decoder:
                     return p
                 try:
                     in_w, post_w = self.norms[li]
+                    sharded = tp_size > 1
                     qkv_n = normed(["q", "k", "v"], self.x, [self.q, self.k, self.v],
-                                   None if li == 0 else self.delta_mlp, in_w, self.x2)
-                    gu_n = normed(["gate", "up"], self.x2, [self.g, self.u], self.delta_attn, post_w, self.x)
+                                   None if (li == 0 or sharded) else self.delta_mlp, in_w, self.x2)
+                    gu_n = normed(["gate", "up"], self.x2, [self.g, self.u], None if sharded else self.delta_attn,
+                                  post_w, self.x)
+                    if sharded:
+                        # o pushes into inbox 0 and gate,up gathers from it; down pushes into inbox 1
+                        # and the next block's q,k,v gathers from it (the last block's down output
+                        # goes through the all-reduce of the final norm instead)
+                        ar = dict(rank=tp_rank, world=tp_size, total_words=B * d, d=d,
+                                  state_ptr=self._ar_state.data_ptr())
+                        own = lambda which: [int(self._peer_inbox[which][tp_rank])]
+                        every = lambda which: [int(a) for a in self._peer_inbox[which]]
+                        gu_n.set_allreduce(True, own(0), tokens=[b for b in range(B) for _ in range(2)], **ar)
+                        if li > 0:
+                            qkv_n.set_allreduce(True, own(1), tokens=[b for b in range(B) for _ in range(3)], **ar)
+                        plan["o"].set_allreduce(False, every(0), tokens=list(range(B)), **ar)
+                        if li + 1 < cfg.n_layers:
+                            plan["down"].set_allreduce(False, every(1), tokens=list(range(B)), **ar)
+                        self.allreduce_in_plans = True
                     plan["qkv_normed"], plan["gu_normed"] = qkv_n, gu_n
                 except KernelError:
+                    if tp_size > 1:
+                        raise   # (half-configured plans must not be used)
                     pass   # (a stream too wide for the normed form: the separate norm stays)
             self.plans.append(plan)
         self.step_kernel = None

@@ -559,6 +559,22 @@ class LayerPlan(LayerGroup):
         check(_lib.lib().qk_plan_set_norm(self.ctx.handle, self._h, rarr, ctypes.c_void_p(norm_weight),
                                           ctypes.c_float(eps), oarr))
 
+    def set_allreduce(self, gather: bool, inbox_bases, rank: int, world: int, total_words: int, tokens,
+                      d: int, state_ptr: int) -> None:
+        """Tensor parallel (``qk_plan_set_allreduce``).  ``gather=False``: the plan's last stage
+        pushes its outputs into the inboxes of all ranks (``inbox_bases``: one device address per
+        rank) instead of storing them.  ``gather=True``: this normed plan takes the sum of what
+        arrived in this rank's inbox (``inbox_bases[0]``) as the residual of its norm.
+        ``tokens[k]``: the token instance k belongs to; ``total_words``: tokens x d words per
+        source rank; ``state_ptr``: the two uint32 the process's all-reduces share."""
+        n = len(self.layers)
+        bases = np.ascontiguousarray(inbox_bases, dtype=np.uint64)
+        toks = np.ascontiguousarray(tokens, dtype=np.uint32)
+        assert toks.size == n
+        check(_lib.lib().qk_plan_set_allreduce(self.ctx.handle, self._h, 1 if gather else 0, bases.ctypes.data,
+                                               int(rank), int(world), int(total_words), toks.ctypes.data,
+                                               int(d), ctypes.c_void_p(state_ptr)))
+
     def feed_targets(self):
         """Turns the plan into a fed plan (the digit tables of its stage-1 inputs are then
         written by the ``*_feed`` call that produces those inputs, and every ``apply`` must follow

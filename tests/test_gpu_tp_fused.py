@@ -74,6 +74,27 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
                 toks.append(single.token_ids.cpu().numpy().copy())
             results[(serving, "single")] = (np.array(toks), np.array(logits))
         dist.barrier()
+    # The all-reduce INSIDE the plans (o / down push their outputs into the peers' inboxes, the
+    # norm inside gate,up / q,k,v sums what arrived) against the all-reduce + norm kernel between
+    # the plain plans: the same sum in the same rank order, so the same bits.
+    for serving in ("float32", "bfloat16"):
+        base = dict(n_layers=3, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16, d_ff=128,
+                    vocab=128, max_seq=32, max_batch=2, kv_dtype="float32", serving=serving)
+        for inside in (True, False):
+            cfg = DecoderConfig(norm_fused_max_batch=4 if inside else 0, **base)
+            dec = Decoder(ctx, cfg, random_model(cfg, RANKS, seed=12), tp_rank=rank, tp_size=world,
+                          group=dist.group.WORLD)
+            assert dec.fused_ar and dec.allreduce_in_plans == inside
+            dec.capture()
+            dec.start([7, 99], [0, 3])
+            logits = []
+            for _ in range(4):
+                dec.graph.replay()
+                ctx.synchronize()
+                logits.append(dec.logits.cpu().numpy().copy())
+                dec.advance()
+            results[(serving, f"inplan{int(inside)}")] = (np.array(logits), None)
+            dist.barrier()
     np.savez(os.path.join(out_dir, f"tp_rank{rank}.npz"),
              **{f"{s}_{f}_tok": v[0] for (s, f), v in results.items()},
              **{f"{s}_{f}_log": v[1] for (s, f), v in results.items() if v[1] is not None})
@@ -102,6 +123,9 @@ def test_fused_allreduce_matches_nccl(tmp_path):
     got, other = np.load(tmp_path / "tp_rank0.npz"), np.load(tmp_path / "tp_rank1.npz")
     from oracle import decoder_np
     from quantibbler_b200.decoder import DecoderConfig, random_model
+    for serving in ("float32", "bfloat16"):
+        for r in (got, other):
+            assert np.array_equal(r[f"{serving}_inplan1_tok"], r[f"{serving}_inplan0_tok"]), serving
     for serving, batch, tol in (("float32", 3, 2e-4), ("bfloat16", 16, 3e-2)):
         a, b = got[f"{serving}_True_log"], got[f"{serving}_False_log"]
         # NCCL adds the two partials in its own order; with two ranks a + b == b + a, so the
