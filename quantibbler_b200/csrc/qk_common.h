@@ -110,6 +110,7 @@ struct qk_group {
     bool normed = false;     // stage 1 applies an RMSNorm to its input itself (qk_plan_set_norm)
     bool pushed = false;     // the last stage pushes its outputs into all-reduce inboxes (qk_plan_set_allreduce)
     bool gathered = false;   // the norm's residual is what an all-reduce left in this rank's inbox
+    uint32_t ar_poll_limit = 0;  // ... and the poll limit its parameter records hold
     void *feed = nullptr;    // device array of per-instance feed targets (fed plans)
     void *tickets = nullptr; // device array of per-instance block counters (fed plans)
     void *scratch = nullptr; // per member: intermediate t, digit tables, stage metadata

@@ -2411,6 +2411,7 @@ qk_status qk_plan_set_allreduce(qk_ctx *ctx, qk_group *plan, int32_t gather, con
     }
     QK_CUDA(cudaMemcpy(plan->params, h.data(), h.size() * sizeof(StageParams), cudaMemcpyHostToDevice));
     (gather ? plan->gathered : plan->pushed) = true;
+    if (gather) plan->ar_poll_limit = c->wait_limit ? c->wait_limit : (1u << 22);
     return QK_OK;
 }
 
@@ -2471,6 +2472,17 @@ qk_status qk_group_apply(qk_ctx *ctx, const qk_group *group) {
         qk_status e = qk::error_word(c);
         if (e != QK_OK) return e;
         c->err_armed = true;
+    }
+    if (group->gathered) {
+        // the polls' limit lives in the plan's parameter records: follow qk_set_wait_limit
+        const uint32_t want = c->wait_limit ? c->wait_limit : (1u << 22);
+        if (group->ar_poll_limit != want) {
+            std::vector<StageParams> h(group->n_inst);
+            QK_CUDA(cudaMemcpy(h.data(), group->params, h.size() * sizeof(StageParams), cudaMemcpyDeviceToHost));
+            for (auto &p : h) p.ar_poll_limit = want;
+            QK_CUDA(cudaMemcpy(group->params, h.data(), h.size() * sizeof(StageParams), cudaMemcpyHostToDevice));
+            const_cast<qk_group *>(group)->ar_poll_limit = want;
+        }
     }
     return launch_both(c, &group->shape, (const StageParams *)group->params, group->n_inst,
                        c->gemv_kernel, group->mixed, group->fed, group->normed, group->pushed);

@@ -175,3 +175,75 @@ def test_grid_barrier_of_the_whole_step_kernel_runs_out_and_recovers(gpu_ctx):
     fused.start([7], [0])
     plain.start([7], [0])
     assert np.array_equal(fused.decode(10), plain.decode(10))
+
+
+def test_allreduce_inside_plans_on_one_gpu_and_its_wait_running_out(gpu_ctx):
+    """The all-reduce inside the plans with both "ranks" on ONE GPU, one after the other (no
+    kernel waits for another: rank 1's push plan runs to completion before rank 0's gathering
+    plan starts): a row-parallel plan pushes its outputs, tagged, into both inboxes; the normed
+    plan that follows sums what arrived in rank order as the residual of its norm.  Expected:
+    the bits of the all-reduce + norm kernel followed by the plain plan.  Then the same
+    gathering plan with nothing pushed for the next all-reduce: its polls run out (limit 4000),
+    the launch ends, qk_gpu_synchronize reports QK_ERR_TIMEOUT, the context works on."""
+    import torch
+    from quantibbler_b200.gpu import LayerPlan, PackedLayer
+    from tests.conftest import make_layer
+    lib, c = _lib.lib(), gpu_ctx.handle
+    d, n_tok, world = 512, 2, 2
+    rng = np.random.default_rng(3)
+    Lo = [make_layer(d, 384, 40, seed=30 + r) for r in range(world)]      # each rank's row-parallel o
+    Lq = make_layer(200, d, 48, seed=40)                                   # what follows the norm
+    o = [PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], d, 384, 40, L["s1"], L["s2"], None, serving="float32")
+         for L in Lo]
+    q = PackedLayer(gpu_ctx, Lq["ub_rows"], Lq["vb_t_rows"], 200, d, 48, Lq["s1"], Lq["s2"], None, serving="float32")
+    attn = [torch.from_numpy(rng.standard_normal((n_tok, 384)).astype(np.float32)).cuda() for _ in range(world)]
+    x = torch.from_numpy(rng.standard_normal((n_tok, d)).astype(np.float32)).cuda()
+    w = torch.from_numpy((1 + 0.1 * rng.standard_normal(d)).astype(np.float32)).cuda()
+    # reference: partial outputs stored, all-reduce + norm kernel per rank would give x + p0 + p1
+    part = [torch.zeros(n_tok, d, device="cuda") for _ in range(world)]
+    for r in range(world):
+        LayerPlan(gpu_ctx, [(o[r], attn[r][b].data_ptr(), part[r][b].data_ptr()) for b in range(n_tok)]).apply()
+    gpu_ctx.synchronize()
+    h_ref = x + (torch.zeros_like(x) + part[0] + part[1])   # the kernels' order: 0 + p0 + p1, then x + sum
+    hn = torch.zeros_like(x)
+    _lib.check(lib.qk_rmsnorm(c, _p(h_ref), None, _p(w), n_tok, d, 1e-5, _lib.QK_F32, None, _p(hn)))
+    y_ref = torch.zeros(n_tok, 200, device="cuda")
+    LayerPlan(gpu_ctx, [(q, hn[b].data_ptr(), y_ref[b].data_ptr()) for b in range(n_tok)]).apply()
+    gpu_ctx.synchronize()
+    # the same through the inboxes
+    inbox = torch.zeros(world, world, n_tok, d, 2, dtype=torch.int32, device="cuda")   # [owner][source]...
+    states = [torch.zeros(2, dtype=torch.int32, device="cuda") for _ in range(world)]
+    bases = [inbox[r].data_ptr() for r in range(world)]
+    dummy = torch.zeros(n_tok, d, device="cuda")
+    push = []
+    for r in range(world):
+        p = LayerPlan(gpu_ctx, [(o[r], attn[r][b].data_ptr(), dummy[b].data_ptr()) for b in range(n_tok)])
+        p.set_allreduce(False, bases, r, world, n_tok * d, list(range(n_tok)), d, states[r].data_ptr())
+        push.append(p)
+    x_out = torch.zeros_like(x)
+    y = torch.full((n_tok, 200), float("nan"), device="cuda")
+    gather = LayerPlan(gpu_ctx, [(q, x[b].data_ptr(), y[b].data_ptr()) for b in range(n_tok)])
+    gather.set_norm([None] * n_tok, w.data_ptr(), 1e-5, [x_out[b].data_ptr() for b in range(n_tok)])
+    gather.set_allreduce(True, [bases[0]], 0, world, n_tok * d, list(range(n_tok)), d, states[0].data_ptr())
+    torch.cuda.synchronize()
+    for p in push:
+        p.apply()
+    gpu_ctx.synchronize()
+    gather.apply()
+    gpu_ctx.synchronize()
+    assert torch.equal(x_out, h_ref)
+    assert torch.equal(y, y_ref)
+    assert int(states[0][0]) == 1 and int(states[0][1]) == 0
+    # all-reduce number 2: nobody pushes, so the gathering plan's polls can only run out
+    prev = gpu_ctx.set_wait_limit(4000)
+    try:
+        gather.apply()
+        with pytest.raises(DeviceError, match="all-reduce"):
+            gpu_ctx.synchronize()
+    finally:
+        gpu_ctx.set_wait_limit(prev)
+    gpu_ctx.synchronize()   # (the error word was cleared by the failing synchronize)
+    y2 = torch.zeros(n_tok, 200, device="cuda")
+    LayerPlan(gpu_ctx, [(q, hn[b].data_ptr(), y2[b].data_ptr()) for b in range(n_tok)]).apply()
+    gpu_ctx.synchronize()
+    assert torch.equal(y2, y_ref)
