@@ -607,8 +607,11 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
         cp_async_commit();  // an empty group keeps the group count in step with i
     };
     if (!prologue_issued) {
+        // (the few-instance form fills every slot of its ring before it waits for the kernel
+        // before it: a warp has one or two chunks, and both are then on their way; the slot of
+        // an item is refilled only after the item has been multiplied)
 #pragma unroll
-        for (int s = 0; s < kStages - 1; ++s) issue(s);
+        for (int s = 0; s < (kSplitK ? kStages : kStages - 1); ++s) issue(s);
     }
     if (kSplitK) {
         // The few-instance form is a chain of latencies, and one of its links is the first
@@ -975,8 +978,8 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
 
     uint32_t ks = kSplitK ? warp : 0, group = group_begin;
     for (uint32_t i = 0; i < n_items; ++i) {
-        issue(i + kStages - 1);          // refills the slot consumed one iteration ago
-        cp_async_wait<kStages - 1>();    // this lane's pieces of item i have landed
+        if (!kSplitK) issue(i + kStages - 1);  // refills the slot consumed one iteration ago
+        cp_async_wait<kStages - 1>();          // this lane's pieces of item i have landed
         const uint4 *stage = ring + (size_t)(i % kStages) * (kChunkBytes / 16);
         uint4 cur[kTilesPerWarp][2];
 #pragma unroll
@@ -1002,6 +1005,7 @@ bitslice_stage(const StageParams &p, uint8_t *table_smem, uint8_t *ring_smem,
             }
         }
         if (kSplitK) {
+            issue(i + kStages);  // (item i sits in registers and has been multiplied: its slot is free)
             ks += warps_per_block;
             continue;
         }
