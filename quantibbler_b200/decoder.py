@@ -65,9 +65,10 @@ class DecoderConfig:
     fused_attention_max_batch: int = 8
     # Batches up to this size let the down projection read gate and up through the SwiGLU itself
     # (the activation is evaluated where the projection's digit table is built) instead of a
-    # SwiGLU launch of its own: one kernel boundary less per block, the same bits.  Larger
-    # batches run more blocks per token, each of which would evaluate the whole activation.
-    gated_down_max_batch: int = 4
+    # SwiGLU launch of its own: one kernel boundary less per block, the same bits (measured up
+    # to batch 12, where it still pays: 8.04 -> 7.88 ms per step; from batch 16 on bfloat16
+    # serving takes the GEMM path, which has its own activation pass).
+    gated_down_max_batch: int = 15
     # Batches up to this size (one GPU) let q,k,v and gate,up apply the RMSNorm in front of them
     # themselves (every block of the first stage forms the norm of the 4096-entry stream, which
     # costs it about a microsecond) instead of a norm launch of its own, which costs the step
