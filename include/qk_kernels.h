@@ -184,6 +184,17 @@ qk_status qk_gpu_attention_dev(qk_ctx *ctx, const qk_attention_shape *shape, con
 qk_status qk_gpu_attention_sage_dev(qk_ctx *ctx, const qk_attention_shape *shape,
                                     const float *q_dev, const float *k_dev, const float *v_dev,
                                     int32_t causal, size_t block_size, float *out_dev);
+/* NOT the reference's arithmetic: the benchmark specification's wording of Sage on device
+ * buffers (self-attention, head_dim == val_dim == 128).  Q / sqrt(d) and K (after its 64-key
+ * block's channel mean has been removed; the mean's share of the scores is added back) are
+ * quantised to INT8 with ONE symmetric scale per 64-token block, the scores' product runs on
+ * tcgen05 kind::i8, the softmax in float32, and P and V go into the second product as
+ * bfloat16 (tcgen05 kind::f16, float32 accumulation in tensor memory).  The reference quantises
+ * per token, P and V to INT8 (gpu_attention.rs:67-397); this entry exists so that the
+ * specification's variant can be measured beside it.  Asynchronous on the context's stream;
+ * an expired in-kernel wait is reported by the next qk_gpu_synchronize as QK_ERR_TIMEOUT. */
+qk_status qk_gpu_attention_sage_block_dev(qk_ctx *ctx, const qk_attention_shape *shape, const float *q_dev,
+                                          const float *k_dev, const float *v_dev, int32_t causal, float *out_dev);
 /* Which kernel the Sage face runs: 2 (default) the tcgen05 kernel (kind::i8 products with
  * the accumulators in tensor memory) where the shape allows (head_dim == val_dim == 128,
  * block_size 64), else as 1; 1 the mma.sync INT8 tensor-core kernel where the shape allows

@@ -173,3 +173,65 @@ def quality_metrics(got, want):
     rel_l1 = float(np.abs(g - w).sum() / np.abs(w).sum())
     rmse = float(np.sqrt(np.mean((g - w) ** 2)))
     return cos, rel_l1, rmse
+
+
+def attention_sage_block(q, k, v, *, causal=False, rows=None):
+    """The benchmark specification's wording of Sage, restated: NOT the reference's arithmetic,
+    and pinned to nothing (the reference holds no implementation, fixture or golden vector of
+    it: parity unpinned).  "Q and K use per-64-token-block INT8 symmetric quantisation [with K
+    mean-smoothing]; PV is computed in bf16 with fp32 online-softmax accumulation."
+
+    Q / sqrt(d) gets one scale per block of 64 queries; K has its 64-key block's channel mean
+    removed (as the reference's gamma does per block, attention_sage.py:164-198) and then one
+    scale per block; scores = dQ dK (Qhat . Khat) + (dQ Qhat) . mean; the softmax is exact here
+    (float64), V is rounded to bfloat16, P is NOT rounded: what the device adds on top is the
+    bfloat16 rounding of P and float32 accumulation, which the test's tolerance covers.
+    float32 is used where the device forms the quantities that decide an INT8 code.
+    """
+    ft = np.float32
+    q = np.asarray(q, dtype=ft)
+    k = np.asarray(k, dtype=ft)
+    v = np.asarray(v, dtype=ft)
+    b, h, s, d = q.shape
+    kvh = k.shape[1]
+    assert k.shape[2] == s and v.shape[2] == s, "sage attention is self-attention"
+    group = h // kvh
+    kv_index = np.repeat(np.arange(kvh), group)
+    blk = 64
+    inv_sqrt_d = ft(1.0) / np.sqrt(ft(d))
+    qs = (q * inv_sqrt_d).astype(ft)
+    q_hat = np.zeros(q.shape, dtype=np.int32)
+    q_scale = np.zeros((b, h, s, 1), dtype=ft)
+    for i0 in range(0, s, blk):
+        part = qs[:, :, i0:i0 + blk]
+        peak = np.abs(part).max(axis=(-1, -2), keepdims=True)
+        delta = np.where(peak > 0, peak / ft(127.0), ft(1.0)).astype(ft)
+        q_hat[:, :, i0:i0 + blk] = np.clip(np.rint(part / delta), -INT8_MAX, INT8_MAX).astype(np.int32)
+        q_scale[:, :, i0:i0 + blk] = delta
+    q_deq = q_hat.astype(ft) * q_scale
+    idx = np.arange(s) if rows is None else np.asarray(rows)
+    scores = np.full((b, h, len(idx), s), -np.inf, dtype=np.float64)
+    for j0 in range(0, s, blk):
+        j1 = min(j0 + blk, s)
+        kb = k[:, :, j0:j1]
+        ssum = np.zeros(kb.shape[:2] + (1, d), dtype=ft)
+        for jj in range(kb.shape[2]):          # the device's order: token by token in float32
+            ssum = (ssum + kb[:, :, jj:jj + 1]).astype(ft)
+        k_mean = (ssum / ft(kb.shape[2])).astype(ft)
+        cen = (kb - k_mean).astype(ft)
+        peak = np.abs(cen).max(axis=(-1, -2), keepdims=True)
+        delta = np.where(peak > 0, peak / ft(127.0), ft(1.0)).astype(ft)
+        k_hat = np.clip(np.rint(cen / delta), -INT8_MAX, INT8_MAX).astype(np.int32)
+        dot = np.matmul(q_hat[:, :, idx], k_hat[:, kv_index].swapaxes(-1, -2))
+        sc = dot.astype(np.float64) * q_scale[:, :, idx].astype(np.float64) * delta[:, kv_index].astype(np.float64) \
+            + q_deq[:, :, idx].astype(np.float64) @ k_mean[:, kv_index].astype(np.float64).swapaxes(-1, -2)
+        scores[..., j0:j1] = sc
+    if causal:
+        scores = np.where(np.arange(s)[None, :] > idx[:, None], -np.inf, scores)
+    scores = scores - scores.max(axis=-1, keepdims=True)
+    p = np.exp(scores)
+    p /= p.sum(axis=-1, keepdims=True)
+    u = v.view(np.uint32).astype(np.uint64)     # V rounded to bfloat16 (ties to even)
+    u = ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+    v_bf = u.view(np.float32).astype(np.float64)
+    return np.matmul(p, v_bf[:, kv_index]).astype(np.float32)

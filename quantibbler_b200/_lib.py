@@ -139,6 +139,8 @@ _SIGNATURES = {
                                        c_void_p]),
     "qk_gpu_attention_sage_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_int32, c_size_t, c_void_p]),
+    "qk_gpu_attention_sage_block_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
+                                                  c_void_p]),
     "qk_gpu_launch_count": (c_uint64, [c_void_p]),
     "qk_gpu_sage_quantize": (c_int32, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_size_t,
                                        c_void_p, c_size_t, c_size_t, c_void_p, c_void_p, c_void_p,

@@ -137,10 +137,24 @@ constexpr uint32_t kURecKBytes = 144 * 128, kURecVBytes = 128 * 128;
 constexpr uint32_t kURecScaleOff = kURecKBytes + kURecVBytes, kURecScaleFloats = 128 + 2 * 128 + 16;
 constexpr uint32_t kURecBytes = kURecScaleOff + kURecScaleFloats * 4;  // what one bulk copy moves
 constexpr uint32_t kURecStride = (kURecBytes + 1023) / 1024 * 1024;
+// Records of the block-scale variant (attention_sage_block_kernel): the same K tile, a
+// bfloat16 V tile per key block ([128 channels][64 keys], 16 KB each, block a then block b),
+// 128 key scales (one value per 64-key block, repeated) and the two mean units.
+constexpr uint32_t kBRecKBytes = 144 * 128, kBRecVBytes = 2 * 128 * 128;
+constexpr uint32_t kBRecScaleOff = kBRecKBytes + kBRecVBytes, kBRecScaleFloats = 128 + 16;
+constexpr uint32_t kBRecBytes = kBRecScaleOff + kBRecScaleFloats * 4;
+constexpr uint32_t kBRecStride = (kBRecBytes + 1023) / 1024 * 1024;
 __host__ __device__ inline uint32_t rec_tile_offset(uint32_t row, uint32_t byte) {
     return row * 128 + (((byte >> 4) ^ (row & 7)) << 4) + (byte & 15);
 }
 
+// float32 -> nearest bfloat16 value (ties to even), as a float32
+__device__ __forceinline__ float round_bf16_value(float v) {
+    uint32_t u = __float_as_uint(v);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return __uint_as_float((u | 0x00400000u) & 0xffff0000u);
+    u = (u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u;
+    return __uint_as_float(u);
+}
 __device__ __forceinline__ int quant_code(float x, float delta) {
     // rint half-to-even of x/delta, clamped to +-127 (gpu_attention.rs:132-155)
     float r = rintf(x / delta);
@@ -193,7 +207,9 @@ __global__ void sage_quant_k_kernel(const float *__restrict__ k, int8_t *__restr
                                     float *__restrict__ scale, float *__restrict__ mean,
                                     uint32_t S, uint32_t d, uint32_t dpad, uint32_t block,
                                     uint32_t n_blocks, int8_t *__restrict__ mean_digits,
-                                    float *__restrict__ mean_scale, uint8_t *__restrict__ rec) {
+                                    float *__restrict__ mean_scale, uint8_t *__restrict__ rec,
+                                    uint32_t rec_stride = kURecStride, uint32_t rec_scale_off = kURecScaleOff,
+                                    uint32_t rec_mscale_at = 128 + 2 * 128, int block_scale = 0) {
     extern __shared__ float mu[];  // d floats
     const uint32_t plane = blockIdx.y, jb = blockIdx.x;
     const uint32_t j0 = jb * block, j1 = min(S, j0 + block), kj = j1 - j0;
@@ -210,7 +226,7 @@ __global__ void sage_quant_k_kernel(const float *__restrict__ k, int8_t *__restr
         // record form (d = dpad = 128, block = 64, 128 threads): thread c owns channel c of the
         // digit rows, lane l of a warp owns channels 4 l .. 4 l + 3 of a key
         __shared__ float peak_rec[4];
-        uint8_t *rc = rec + ((size_t)plane * ((n_blocks + 1) / 2) + jb / 2) * kURecStride;
+        uint8_t *rc = rec + ((size_t)plane * ((n_blocks + 1) / 2) + jb / 2) * rec_stride;
         const uint32_t half = jb % 2, c = threadIdx.x;
         float peak = fabsf(mu[c]);
         for (int off = 16; off > 0; off >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, off));
@@ -229,16 +245,32 @@ __global__ void sage_quant_k_kernel(const float *__restrict__ k, int8_t *__restr
         rc[rec_tile_offset(row0 + 2, c)] = (uint8_t)(int8_t)d2;
 #pragma unroll
         for (uint32_t dr = 3; dr < 8; ++dr) rc[rec_tile_offset(row0 + dr, c)] = 0;
-        float *scales = reinterpret_cast<float *>(rc + kURecScaleOff);
-        if (threadIdx.x == 0) scales[128 + 2 * 128 + half] = unit;
+        float *scales = reinterpret_cast<float *>(rc + rec_scale_off);
+        if (threadIdx.x == 0) scales[rec_mscale_at + half] = unit;
         const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+        float block_delta = 0.f;
+        if (block_scale) {
+            // one scale for the whole 64-key block (the benchmark specification's granularity)
+            __shared__ float block_peak[4];
+            float pk = 0.f;
+            for (uint32_t j = j0 + warp; j < j1; j += 4) {
+                const float4 x = *reinterpret_cast<const float4 *>(kp + (size_t)j * d + 4 * lane);
+                const float4 mm = *reinterpret_cast<const float4 *>(mu + 4 * lane);
+                pk = fmaxf(pk, fmaxf(fmaxf(fabsf(x.x - mm.x), fabsf(x.y - mm.y)), fmaxf(fabsf(x.z - mm.z), fabsf(x.w - mm.w))));
+            }
+            for (int off = 16; off > 0; off >>= 1) pk = fmaxf(pk, __shfl_xor_sync(0xffffffffu, pk, off));
+            if (lane == 0) block_peak[warp] = pk;
+            __syncthreads();
+            pk = fmaxf(fmaxf(block_peak[0], block_peak[1]), fmaxf(block_peak[2], block_peak[3]));
+            block_delta = pk > 0.f ? pk / 127.f : 1.f;
+        }
         for (uint32_t j = j0 + warp; j < j1; j += 4) {
             const float4 x = *reinterpret_cast<const float4 *>(kp + (size_t)j * d + 4 * lane);
             const float4 mm = *reinterpret_cast<const float4 *>(mu + 4 * lane);
             const float e0 = x.x - mm.x, e1 = x.y - mm.y, e2 = x.z - mm.z, e3 = x.w - mm.w;
             float pk = fmaxf(fmaxf(fabsf(e0), fabsf(e1)), fmaxf(fabsf(e2), fabsf(e3)));
             for (int off = 16; off > 0; off >>= 1) pk = fmaxf(pk, __shfl_xor_sync(0xffffffffu, pk, off));
-            const float delta = pk > 0.f ? pk / 127.f : 1.f;
+            const float delta = block_scale ? block_delta : pk > 0.f ? pk / 127.f : 1.f;
             const uint32_t w = (uint32_t)(quant_code(e0, delta) & 0xff) | ((uint32_t)(quant_code(e1, delta) & 0xff) << 8) |
                                ((uint32_t)(quant_code(e2, delta) & 0xff) << 16) |
                                ((uint32_t)(quant_code(e3, delta) & 0xff) << 24);
@@ -284,6 +316,65 @@ __global__ void sage_quant_k_kernel(const float *__restrict__ k, int8_t *__restr
         for (uint32_t c = lane; c < dpad; c += 32)
             cr[c] = c < d ? (int8_t)quant_code(kr[c] - mu[c], delta) : 0;
         if (lane == 0) scale[(size_t)plane * S + j] = delta;
+    }
+}
+
+// psi_Q with one scale per 64-query block (block-scale variant): a block of 256 threads per
+// (head, 64-row block), a warp takes eight rows, a lane four channels (d = dpad = 128).
+__global__ void __launch_bounds__(256)
+sage_quant_q_block_kernel(const float *__restrict__ q, int8_t *__restrict__ codes, float *__restrict__ scale,
+                          uint32_t Sq, float inv_sqrt_d) {
+    __shared__ float peaks[8];
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const size_t head_row0 = (size_t)blockIdx.y * Sq;
+    const uint32_t r0 = blockIdx.x * 64;
+    float4 x[8];
+    float peak = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t r = r0 + warp + 8 * i;
+        x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < Sq) x[i] = *reinterpret_cast<const float4 *>(q + (head_row0 + r) * 128 + 4 * lane);
+        x[i].x *= inv_sqrt_d, x[i].y *= inv_sqrt_d, x[i].z *= inv_sqrt_d, x[i].w *= inv_sqrt_d;
+        peak = fmaxf(peak, fmaxf(fmaxf(fabsf(x[i].x), fabsf(x[i].y)), fmaxf(fabsf(x[i].z), fabsf(x[i].w))));
+    }
+    for (int off = 16; off > 0; off >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, off));
+    if (lane == 0) peaks[warp] = peak;
+    __syncthreads();
+    peak = peaks[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) peak = fmaxf(peak, peaks[w]);
+    const float delta = peak > 0.f ? peak / 127.f : 1.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t r = r0 + warp + 8 * i;
+        if (r >= Sq) continue;
+        const uint32_t w = (uint32_t)(quant_code(x[i].x, delta) & 0xff) | ((uint32_t)(quant_code(x[i].y, delta) & 0xff) << 8) |
+                           ((uint32_t)(quant_code(x[i].z, delta) & 0xff) << 16) |
+                           ((uint32_t)(quant_code(x[i].w, delta) & 0xff) << 24);
+        *reinterpret_cast<uint32_t *>(codes + (head_row0 + r) * 128 + 4 * lane) = w;
+        if (lane == 0) scale[head_row0 + r] = delta;
+    }
+}
+
+// V of a key block as a bfloat16 tile of the block-scale variant's record: thread c writes
+// channel row c (64 keys = 128 bytes, eight swizzled 16-byte pieces); keys past the end are 0.
+__global__ void __launch_bounds__(128)
+sage_v_bf16_record_kernel(const float *__restrict__ v, uint8_t *__restrict__ rec, uint32_t S, uint32_t n_blocks) {
+    const uint32_t plane = blockIdx.y, jb = blockIdx.x, c = threadIdx.x;
+    const uint32_t j0 = jb * 64, j1 = min(S, j0 + 64);
+    const float *vp = v + (size_t)plane * S * 128;
+    uint8_t *tile = rec + ((size_t)plane * ((n_blocks + 1) / 2) + jb / 2) * kBRecStride + kBRecKBytes + (jb % 2) * 16384;
+#pragma unroll
+    for (int piece = 0; piece < 8; ++piece) {
+        uint32_t w[4];
+#pragma unroll
+        for (int qd = 0; qd < 4; ++qd) {
+            const uint32_t ja = j0 + 8 * piece + 2 * qd, jbb = ja + 1;
+            const float a = ja < j1 ? vp[(size_t)ja * 128 + c] : 0.f, b = jbb < j1 ? vp[(size_t)jbb * 128 + c] : 0.f;
+            w[qd] = (__float_as_uint(round_bf16_value(a)) >> 16) | (__float_as_uint(round_bf16_value(b)) & 0xffff0000u);
+        }
+        *reinterpret_cast<uint4 *>(tile + rec_tile_offset(c, 16 * piece)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
 }
 
@@ -1219,6 +1310,285 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
     if (tid == 0 && *abort_flag) atomicOr(error, 1);
 }
 
+// ------------------------------------------------------------------ the block-scale variant
+// The benchmark specification's wording of Sage, which is NOT the reference's arithmetic: Q and
+// K quantised to INT8 with ONE scale per 64-token block (K after its block's channel mean has
+// been removed, the mean's contribution added back through the digit rows as above), the
+// scores' product on tcgen05 kind::i8 exactly as in attention_sage_umma_kernel, and then P and
+// V in bfloat16: the PV product is tcgen05 kind::f16 with the output accumulator STAYING in
+// tensor memory over the whole key loop.  Nothing is folded per iteration; when a row's maximum
+// has grown by more than kBLazy since the accumulator's reference maximum was set, the row's
+// threads rescale their columns of the accumulator in place (tcgen05.ld, multiply, tcgen05.st)
+// and move the reference; otherwise the exponentials keep the old reference (they may exceed
+// 1 by a factor of up to e^kBLazy, which bfloat16 and the float32 sums hold without loss of
+// anything that matters).  Same thread layout, records, barriers and bounded waits as the
+// kernel above.  No reference implementation of this variant exists: its parity is against a
+// NumPy restatement of the wording only.
+constexpr uint32_t kBOCol = 256;  // the output accumulator: tensor-memory columns 256 .. 383
+constexpr uint32_t kBPBytes = 2 * kUQ * 128;  // P as two bfloat16 tiles (keys of block a, of block b)
+constexpr uint32_t kBSmemBytes = kUQBytes + kUBufs * kBRecStride + kBPBytes + 2 * kUGroups * kUQ * 4 + 64;
+constexpr float kBLazy = 5.5451774f;  // 8 / log2(e)
+static_assert(kBSmemBytes + 1024 <= 227 * 1024, "the block-scale kernel's shared memory");
+
+__device__ __forceinline__ uint32_t umma_idesc_bf16(uint32_t n) {  // bf16 x bf16 -> f32, K-major, M = 128
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((uint32_t)(kUQ >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
+        "%23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]),
+        "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
+        "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+
+__global__ void __launch_bounds__(kUThreads, 1)
+attention_sage_block_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_limit, int *error) {
+    extern __shared__ __align__(1024) uint8_t sm_b_raw[];
+    uint8_t *sm_b = sm_b_raw + ((1024 - (smem_u32(sm_b_raw) & 1023)) & 1023);
+    uint8_t *Qs = sm_b, *Rb = Qs + kUQBytes, *Ps = Rb + kUBufs * kBRecStride;  // Q tile, record buffers, two P tiles
+    float *xm = reinterpret_cast<float *>(Ps + kBPBytes), *xe = xm + kUGroups * kUQ;
+    uint64_t *bar_s = reinterpret_cast<uint64_t *>(xe + kUGroups * kUQ), *bar_pv = bar_s + 1, *bar_drain = bar_s + 2;
+    uint64_t *bar_rec = bar_s + 3;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_rec + kUBufs);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t tid = threadIdx.x, warp = tid / 32;
+    const uint32_t g = tid / kUQ, r = tid % kUQ;  // column group (32 keys of the iteration), query row
+    const int my_blk = g / 2;
+    const int h = blockIdx.y, b = blockIdx.z, kvh = h / dm.group;
+    const size_t plane = (size_t)b * dm.KV + kvh;
+    const int q_tile = causal ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
+    const int q0 = q_tile * kUQ, i = q0 + (int)r;
+    const bool valid = i < (int)dm.Sq;
+    const size_t row_base = ((size_t)b * dm.H + h) * dm.Sq;
+    const int S = (int)dm.Skv, n_blocks = (int)a.n_blocks;
+
+    if (tid == 0) {
+        mbar_init(bar_s, 1);
+        mbar_init(bar_pv, 1);
+        mbar_init(bar_drain, 2);
+        for (int bi = 0; bi < kUBufs; ++bi) mbar_init(bar_rec + bi, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kUTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot, my_tmem = tmem_base + (((warp % 4) * 32) << 16);
+
+    auto swz = [](uint8_t *tile, int row, int piece) { return tile + row * 128 + ((piece ^ (row & 7)) << 4); };
+    const uint8_t *rec_src = a.rec + plane * (size_t)((n_blocks + 1) / 2) * kBRecStride;
+    auto stage = [&](int it) {
+        const uint32_t bar = smem_u32(bar_rec + it % kUBufs);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kBRecBytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                         smem_u32(Rb + (it % kUBufs) * kBRecStride)),
+                     "l"(rec_src + (size_t)it * kBRecStride), "r"(kBRecBytes), "r"(bar)
+                     : "memory");
+    };
+
+    const int i_blk_max = min((int)dm.Sq - 1, q0 + kUQ - 1);
+    const int jb_hi = causal ? i_blk_max / kUBlk + 1 : n_blocks;
+    const int n_it = (jb_hi + 1) / 2;
+    for (int idx = tid; idx < kUQ * 8; idx += kUThreads) {
+        const int row = idx / 8, piece = idx % 8;
+        cp_async16(swz(Qs, row, piece), a.qc + (row_base + min(q0 + row, (int)dm.Sq - 1)) * a.dpad + piece * 16);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const float dq = valid ? a.qs[row_base + i] : 1.f;
+
+    float m = -INFINITY, mref = -INFINITY, l = 0.f;  // running maximum, the accumulator's reference, sum of P
+    const uint32_t idesc_s = umma_idesc_i8(kUSRows), idesc_o = umma_idesc_bf16(kUD);
+    const uint32_t limit = wait_limit ? wait_limit : kUWaitLimitDefault;
+    bool dead = false;
+    int dead_it = n_it;
+    uint32_t v[32];
+    auto issue_s = [&](int it) {
+        const uint32_t kt = smem_u32(Rb + (it % kUBufs) * kBRecStride);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int k = 0; k < kUD / 32; ++k)
+            umma_i8(tmem_base, umma_desc(smem_u32(Qs) + k * 32), umma_desc(kt + k * 32), idesc_s, k != 0);
+        umma_commit(bar_s);
+    };
+    const bool lane0 = tid % 32 == 0;
+    if (warp == kUWarpRec && lane0) {
+        stage(0);
+        if (n_it > 1) stage(1);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    const bool first_landed = warp != kUWarpRec || mbar_wait(bar_rec, 0, abort_flag, limit);
+    if (__syncthreads_and(first_landed) && warp == kUWarpS && lane0) issue_s(0);
+    __syncwarp();
+    constexpr float kLog2e = 1.4426950408889634f;
+    for (int it = 0; it < n_it; ++it) {
+        const int buf = it % kUBufs;
+        const float *kscale = reinterpret_cast<const float *>(Rb + buf * kBRecStride + kBRecScaleOff);
+        const float *mscale = kscale + kUKeys;
+        bool ok = mbar_wait(bar_s, it & 1, abort_flag, limit);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+        // ---- this thread's 32 scores
+        const int jb = 2 * it + my_blk, j0 = jb * kUBlk, kj = min(kUBlk, S - j0);
+        const bool live = jb < jb_hi;
+        float shift = 0.f;
+        if (ok) {
+            uint32_t c0, c1, c2, c3;
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
+                         : "r"(my_tmem + kUKeys + 8 * my_blk)
+                         : "memory");
+            tmem_ld32(my_tmem + 32 * g, v);
+            tmem_ld_wait();
+            (void)c3;
+            shift = (((float)(int)c0 * 65536.f + (float)(int)c1 * 256.f) + (float)(int)c2) * mscale[my_blk] * dq;
+        }
+        const float *ksc = kscale + 32 * g;
+        float s[32];
+        float bm = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+            const int kk = 32 * (int)(g % 2) + e, j = j0 + kk;
+            float sc = fmaf((float)(int)v[e] * dq, ksc[e], shift);
+            if (!live || kk >= kj || !valid || (causal && j > i)) sc = -INFINITY;
+            s[e] = sc;
+            bm = fmaxf(bm, sc);
+        }
+        xm[g * kUQ + r] = bm;
+        if (warp == kUWarpRec && it + 1 < n_it && ok)
+            ok = mbar_wait(bar_rec + (it + 1) % kUBufs, ((it + 1) / kUBufs) & 1, abort_flag, limit);
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        if (!__syncthreads_and(ok)) {
+            dead = true;
+            dead_it = it;
+            break;
+        }
+        if (warp == kUWarpS && lane0 && it + 1 < n_it) issue_s(it + 1);
+        __syncwarp();
+        // ---- the row's maximum, and whether the accumulator's reference has to move
+        const float mn = fmaxf(m, fmaxf(fmaxf(xm[r], xm[kUQ + r]), fmaxf(xm[2 * kUQ + r], xm[3 * kUQ + r])));
+        float alpha = 1.f;
+        if (mn > mref + kBLazy) {  // (also the first finite maximum: mref is -inf until then)
+            alpha = mref == -INFINITY ? 0.f : exp2f((mref - mn) * kLog2e);
+            mref = mn;
+        }
+        m = mn;
+        const float off = mref == -INFINITY ? 0.f : -mref * kLog2e;  // (a row without a key yet: every score is -inf)
+        // the product of the iteration before has read the P tiles and written the accumulator
+        bool pv_ok = true;
+        if (it > 0) {
+            pv_ok = mbar_wait(bar_pv, (it - 1) & 1, abort_flag, limit);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        // ---- P in bfloat16 into this thread's four 16-byte pieces of its block's tile
+        float es = 0.f;
+        uint8_t *ptile = Ps + my_blk * (kUQ * 128);
+#pragma unroll
+        for (int piece = 0; piece < 4; ++piece) {
+            uint32_t w[4];
+#pragma unroll
+            for (int qd = 0; qd < 4; ++qd) {
+                const int at = 8 * piece + 2 * qd;
+                const float p0 = ex2_approx(fmaf(s[at], kLog2e, off)), p1 = ex2_approx(fmaf(s[at + 1], kLog2e, off));
+                es += p0 + p1;
+                asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[qd]) : "f"(p1), "f"(p0));
+            }
+            *reinterpret_cast<uint4 *>(swz(ptile, (int)r, 4 * (int)(g % 2) + piece)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        xe[g * kUQ + r] = es;
+        // ---- the accumulator moves to the new reference where a row of this warp needs it
+        if (it > 0 && pv_ok && __any_sync(0xffffffffu, alpha != 1.f)) {
+            tmem_ld32(my_tmem + kBOCol + 32 * g, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+            tmem_st32(my_tmem + kBOCol + 32 * g, v);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        if (!__syncthreads_and(pv_ok)) {
+            dead = true;
+            dead_it = it;
+            break;
+        }
+        if (lane0) {
+            if (warp == kUWarpPV) {
+                const uint32_t vt = smem_u32(Rb + buf * kBRecStride + kBRecKBytes);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t acc = it > 0;
+#pragma unroll
+                for (int blk = 0; blk < 2; ++blk) {
+                    if (2 * it + blk >= jb_hi) break;  // (a block that does not exist: its V tile is not defined)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        umma_bf16(tmem_base + kBOCol, umma_desc(smem_u32(Ps) + blk * (kUQ * 128) + k * 32),
+                                  umma_desc(vt + blk * (kUD * 128) + k * 32), idesc_o, acc);
+                        acc = 1;
+                    }
+                }
+                umma_commit(bar_pv);
+            }
+            if (warp == kUWarpRec && it + 2 < n_it) stage(it + 2);
+        }
+        __syncwarp();
+        l = alpha * l + ((xe[r] + xe[kUQ + r]) + (xe[2 * kUQ + r] + xe[3 * kUQ + r]));
+    }
+    if (!dead) {
+        if (!__syncthreads_and(mbar_wait(bar_pv, (n_it - 1) & 1, abort_flag, limit))) {
+            dead = true;
+        } else {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            tmem_ld32(my_tmem + kBOCol + 32 * g, v);
+            tmem_ld_wait();
+        }
+    }
+    if (dead) {
+        __syncthreads();
+        if ((warp == kUWarpS || warp == kUWarpPV) && lane0) umma_commit(bar_drain);
+        __syncwarp();
+        if (warp == 0) {
+            volatile int never = 0;
+            (void)mbar_wait(bar_drain, 0, &never, kUWaitLimitDefault);
+            for (int k = dead_it; k < min(n_it, dead_it + 2); ++k)
+                (void)mbar_wait(bar_rec + k % kUBufs, (k / kUBufs) & 1, &never, kUWaitLimitDefault);
+        }
+        *abort_flag = 1;
+    }
+    if (valid && !dead) {
+        float *dst = a.out + (row_base + i) * kUD + 32 * g;
+#pragma unroll
+        for (int c = 0; c < 32; c += 4)
+            *reinterpret_cast<float4 *>(dst + c) =
+                make_float4(__uint_as_float(v[c]) / l, __uint_as_float(v[c + 1]) / l, __uint_as_float(v[c + 2]) / l,
+                            __uint_as_float(v[c + 3]) / l);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kUTmemCols)
+                     : "memory");
+    if (tid == 0 && *abort_flag) atomicOr(error, 1);
+}
+
 // ------------------------------------------------------------------ host side
 std::string shape_debug(const qk_attention_shape *s) {
     // Rust's `{:?}` of AttentionShape (gpu_attention.rs:402-411)
@@ -1463,6 +1833,58 @@ qk_status attention_sage_dev(qk_ctx *c, const float *dq, const float *dk, const 
     return launch_sage<16>(c, a, dm, causal);
 }
 
+// The block-scale variant on device buffers: its three preparation kernels and the main kernel.
+// scratch: sage_block_scratch_bytes of it.
+size_t sage_block_scratch_bytes(const qk_attention_shape *s) {
+    const AttnDims dm = dims_of(s);
+    const size_t n_blocks = qk::ceil_div((size_t)dm.Skv, (size_t)kUBlk), planes = (size_t)dm.B * dm.KV;
+    const size_t qrows = (size_t)dm.B * dm.H * dm.Sq;
+    auto up = [](size_t n) { return (n + 255) / 256 * 256; };
+    return up(qrows * 128) + up(qrows * 4) + up(planes * n_blocks * 128 * 4) +
+           up(planes * ((n_blocks + 1) / 2) * kBRecStride) + 1024;
+}
+qk_status attention_sage_block_dev(qk_ctx *c, const float *dq, const float *dk, const float *dv, float *out,
+                                   uint8_t *scratch, const qk_attention_shape *shape, int causal) {
+    const AttnDims dm = dims_of(shape);
+    if (dm.d != (uint32_t)kUD || dm.dv != (uint32_t)kUD || dm.Sq != dm.Skv)
+        return qk::fail(QK_ERR_VALUE, "the block-scale Sage variant is built for self-attention with head_dim = "
+                        "val_dim = 128 (got head_dim %u, val_dim %u, seq_q %u, seq_kv %u)", dm.d, dm.dv, dm.Sq, dm.Skv);
+    const size_t S = dm.Skv, n_blocks = qk::ceil_div(S, (size_t)kUBlk), planes = (size_t)dm.B * dm.KV;
+    const size_t qrows = (size_t)dm.B * dm.H * dm.Sq;
+    auto up = [](size_t n) { return (n + 255) / 256 * 256; };
+    uint8_t *qc = scratch, *qs = qc + up(qrows * 128), *km = qs + up(qrows * 4);
+    uint8_t *rec = km + up(planes * n_blocks * 128 * 4);
+    rec += (1024 - (reinterpret_cast<uintptr_t>(rec) & 1023)) & 1023;
+    qk_status st = qk::error_word(c);
+    if (st != QK_OK) return st;
+    const float inv_sqrt_d = 1.0f / sqrtf((float)dm.d);
+    sage_quant_q_block_kernel<<<dim3((unsigned)qk::ceil_div((size_t)dm.Sq, (size_t)64), dm.B * dm.H), 256, 0, c->stream>>>(
+        dq, (int8_t *)qc, (float *)qs, dm.Sq, inv_sqrt_d);
+    QK_CUDA(cudaGetLastError());
+    dim3 kgrid((unsigned)n_blocks, (unsigned)planes);
+    sage_quant_k_kernel<<<kgrid, 128, dm.d * sizeof(float), c->stream>>>(
+        dk, nullptr, nullptr, (float *)km, (uint32_t)S, dm.d, 128u, (uint32_t)kUBlk, (uint32_t)n_blocks, nullptr, nullptr,
+        rec, kBRecStride, kBRecScaleOff, (uint32_t)kUKeys, 1);
+    QK_CUDA(cudaGetLastError());
+    sage_v_bf16_record_kernel<<<kgrid, 128, 0, c->stream>>>(dv, rec, (uint32_t)S, (uint32_t)n_blocks);
+    QK_CUDA(cudaGetLastError());
+    SageArgs a{};
+    a.qc = (const int8_t *)qc;
+    a.qs = (const float *)qs;
+    a.out = out;
+    a.dpad = 128, a.bpad = 64, a.block = kUBlk, a.n_blocks = (uint32_t)n_blocks;
+    a.rec = rec;
+    c->err_armed = true;
+    QK_CUDA(cudaFuncSetAttribute(attention_sage_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)(kBSmemBytes + 1024)));
+    dim3 grid((unsigned)qk::ceil_div((size_t)dm.Sq, (size_t)kUQ), dm.H, dm.B);
+    attention_sage_block_kernel<<<grid, kUThreads, kBSmemBytes + 1024, c->stream>>>(a, dm, causal, c->wait_limit,
+                                                                                  (int *)c->d_err.ptr);
+    QK_CUDA(cudaGetLastError());
+    c->launches += 4;
+    return QK_OK;
+}
+
 // Device-buffer form of the exact face (also used by the decoder path).
 qk_status attention_exact_dev(qk_ctx *c, const float *q, const float *k, const float *v,
                               float *out, const qk_attention_shape *s, int causal) {
@@ -1566,6 +1988,24 @@ qk_status qk_gpu_attention_sage_dev(qk_ctx *ctx, const qk_attention_shape *shape
     if ((st = c->d_in.reserve(qk::sage_scratch_bytes(shape, block_size))) != QK_OK) return st;
     return qk::attention_sage_dev(c, q_dev, k_dev, v_dev, out_dev, (uint8_t *)c->d_in.ptr, shape,
                                   causal != 0, block_size);
+}
+
+qk_status qk_gpu_attention_sage_block_dev(qk_ctx *ctx, const qk_attention_shape *shape, const float *q_dev,
+                                          const float *k_dev, const float *v_dev, int32_t causal, float *out_dev) {
+    if (!shape) return qk::fail(QK_ERR_VALUE, "attention shape is null");
+    const size_t q_len = shape->batch * shape->n_heads * shape->seq_q * shape->head_dim;
+    const size_t k_len = shape->batch * shape->n_kv_heads * shape->seq_kv * shape->head_dim;
+    const size_t v_len = shape->batch * shape->n_kv_heads * shape->seq_kv * shape->val_dim;
+    const size_t o_len = shape->batch * shape->n_heads * shape->seq_q * shape->val_dim;
+    qk_status st = validate_attention(shape, q_len, k_len, v_len, true, 64, o_len);
+    if (st != QK_OK) return st;
+    if (!q_dev || !k_dev || !v_dev || !out_dev) return qk::fail(QK_ERR_VALUE, "qk_gpu_attention_sage_block_dev: null buffer");
+    qk_ctx *c;
+    if ((st = qk::resolve_ctx(ctx, &c)) != QK_OK) return st;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    if ((st = c->d_in.reserve(qk::sage_block_scratch_bytes(shape))) != QK_OK) return st;
+    return qk::attention_sage_block_dev(c, q_dev, k_dev, v_dev, out_dev, (uint8_t *)c->d_in.ptr, shape, causal != 0);
 }
 
 qk_status qk_gpu_sage_quantize(qk_ctx *ctx, const qk_attention_shape *shape, const float *query,

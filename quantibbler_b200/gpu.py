@@ -167,6 +167,17 @@ def _gpu_attention_dev(self, shape: AttentionShape, q_ptr: int, k_ptr: int, v_pt
                                                    ctypes.c_void_p(out_ptr)))
 
 
+def _gpu_attention_sage_block_dev(self, shape: AttentionShape, q_ptr: int, k_ptr: int, v_ptr: int,
+                                  causal: bool, out_ptr: int) -> None:
+    """The benchmark specification's Sage variant (one INT8 scale per 64-token block for Q and K,
+    bfloat16 P and V) on float32 device buffers; NOT the reference's arithmetic.  Asynchronous."""
+    st = _ShapeStruct(shape.batch, shape.n_heads, shape.n_kv_heads, shape.seq_q, shape.seq_kv,
+                      shape.head_dim, shape.val_dim)
+    check(_lib.lib().qk_gpu_attention_sage_block_dev(
+        self._h, ctypes.byref(st), ctypes.c_void_p(q_ptr), ctypes.c_void_p(k_ptr), ctypes.c_void_p(v_ptr),
+        int(bool(causal)), ctypes.c_void_p(out_ptr)))
+
+
 def _set_sage_kernel(self, which: int) -> int:
     """2: the tcgen05 Sage kernel where the shape allows (default), else as 1; 1: the mma.sync
     INT8 tensor-core kernel where the shape allows, else as 0; 0: the dp4a kernel.  Returns the
@@ -209,6 +220,7 @@ GpuContext.sage_quantize = _gpu_sage_quantize
 GpuContext.attention = _gpu_attention
 GpuContext.attention_sage = _gpu_attention_sage
 GpuContext.attention_dev = _gpu_attention_dev
+GpuContext.attention_sage_block_dev = _gpu_attention_sage_block_dev
 GpuContext.set_sage_kernel = _set_sage_kernel
 GpuContext.set_decode_attention_kernel = _set_decode_attention_kernel
 

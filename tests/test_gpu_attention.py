@@ -341,3 +341,41 @@ def test_attention_on_device_buffers(gpu_ctx):
                           block_size=32)
     gpu_ctx.synchronize()
     assert np.array_equal(out.cpu().numpy(), run_sage(gpu_ctx, q, k, v, True, 32))
+
+
+@pytest.mark.parametrize("case", [
+    # (batch, heads, kv heads, seq, causal)
+    (1, 4, 2, 200, True), (1, 2, 1, 320, False), (2, 8, 2, 1000, True), (1, 2, 2, 64, True), (1, 1, 1, 129, False)])
+def test_sage_block_scale_variant_against_its_restatement(gpu_ctx, case):
+    """The benchmark specification's Sage variant (one INT8 scale per 64-token block for Q and
+    K, bfloat16 P and V, the output accumulated in tensor memory and rescaled lazily): not the
+    reference's arithmetic and pinned to nothing; checked against the NumPy restatement of the
+    wording (exact softmax of the same quantised scores, V rounded to bfloat16), within what the
+    bfloat16 rounding of P and float32 accumulation add, and against the exact attention within
+    what INT8 block scales cost.  Ragged last blocks, an odd number of key blocks, several query
+    tiles, GQA, causal and not; run twice for bit identity."""
+    import torch
+    b, h, kvh, s, causal = case
+    d = 128
+    rng = np.random.default_rng(sum(case[:4]) + 11)
+    q = rng.standard_normal((b, h, s, d), dtype=np.float32)
+    k = rng.standard_normal((b, kvh, s, d), dtype=np.float32) \
+        + (2.0 * rng.standard_normal((1, kvh, 1, d))).astype(np.float32)
+    v = rng.standard_normal((b, kvh, s, d), dtype=np.float32)
+    sh = shape_of(q, k, v)
+    tq, tk, tv = (torch.from_numpy(x).cuda() for x in (q, k, v))
+    outs = []
+    for _ in range(2):
+        out = torch.full((b, h, s, d), float("nan"), device="cuda")
+        torch.cuda.synchronize()
+        gpu_ctx.attention_sage_block_dev(sh, tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), causal, out.data_ptr())
+        gpu_ctx.synchronize()
+        outs.append(out.cpu().numpy())
+    got = outs[0]
+    assert np.isfinite(got).all()
+    assert np.array_equal(got, outs[1])
+    want = anp.attention_sage_block(q, k, v, causal=causal)
+    assert np.abs(got - want).max() <= 6e-3 * np.abs(want).max()
+    exact = anp.attention_exact(q, k, v, causal=causal) if hasattr(anp, "attention_exact") else None
+    if exact is not None:
+        assert np.abs(got - exact).max() <= 5e-2 * np.abs(exact).max()
