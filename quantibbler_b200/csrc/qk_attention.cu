@@ -1317,17 +1317,17 @@ attention_sage_umma_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_li
 // scores' product on tcgen05 kind::i8 exactly as in attention_sage_umma_kernel, and then P and
 // V in bfloat16: the PV product is tcgen05 kind::f16 with the output accumulator STAYING in
 // tensor memory over the whole key loop.  Nothing is folded per iteration; when a row's maximum
-// has grown by more than kBLazy since the accumulator's reference maximum was set, the row's
+// has grown by more than a factor 2^kBLazy since the accumulator's reference maximum was set, the row's
 // threads rescale their columns of the accumulator in place (tcgen05.ld, multiply, tcgen05.st)
 // and move the reference; otherwise the exponentials keep the old reference (they may exceed
-// 1 by a factor of up to e^kBLazy, which bfloat16 and the float32 sums hold without loss of
+// 1 by a factor of up to 2^kBLazy, which bfloat16 and the float32 sums hold without loss of
 // anything that matters).  Same thread layout, records, barriers and bounded waits as the
 // kernel above.  No reference implementation of this variant exists: its parity is against a
 // NumPy restatement of the wording only.
 constexpr uint32_t kBOCol = 256;  // the output accumulator: tensor-memory columns 256 .. 383
 constexpr uint32_t kBPBytes = 2 * kUQ * 128;  // P as two bfloat16 tiles (keys of block a, of block b)
 constexpr uint32_t kBSmemBytes = kUQBytes + kUBufs * kBRecStride + kBPBytes + 2 * kUGroups * kUQ * 4 + 64;
-constexpr float kBLazy = 5.5451774f;  // 8 / log2(e)
+constexpr float kBLazy = 8.0f;  // in the log2 domain the kernel keeps its scores in: a factor of 256
 static_assert(kBSmemBytes + 1024 <= 227 * 1024, "the block-scale kernel's shared memory");
 
 __device__ __forceinline__ uint32_t umma_idesc_bf16(uint32_t n) {  // bf16 x bf16 -> f32, K-major, M = 128
@@ -1461,16 +1461,33 @@ attention_sage_block_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_l
             (void)c3;
             shift = (((float)(int)c0 * 65536.f + (float)(int)c1 * 256.f) + (float)(int)c2) * mscale[my_blk] * dq;
         }
-        const float *ksc = kscale + 32 * g;
+        // Scores in the log2 domain: one scale per (query block, key block), so a thread's 32
+        // scores are one fused multiply-add each: t = dot * (dQ dK log2 e) + shift log2 e.
+        // Only the iteration on the diagonal, the last one of a ragged sequence, a tile with
+        // rows past the end and a missing second block need the per-element mask.
+        const float kk2 = dq * kscale[32 * g] * kLog2e, shift2 = shift * kLog2e;
+        const int it_j0 = it * kUKeys;
+        const bool masked = it_j0 + kUKeys > S || q0 + kUQ > (int)dm.Sq || !live || 2 * it + 1 >= jb_hi ||
+                            (causal && it_j0 + kUKeys - 1 > q0);
         float s[32];
         float bm = -INFINITY;
+        if (masked) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-            const int kk = 32 * (int)(g % 2) + e, j = j0 + kk;
-            float sc = fmaf((float)(int)v[e] * dq, ksc[e], shift);
-            if (!live || kk >= kj || !valid || (causal && j > i)) sc = -INFINITY;
-            s[e] = sc;
-            bm = fmaxf(bm, sc);
+            for (int e = 0; e < 32; ++e) {
+                const int kk = 32 * (int)(g % 2) + e, j = j0 + kk;
+                float sc = fmaf((float)(int)v[e], kk2, shift2);
+                if (!live || kk >= kj || !valid || (causal && j > i)) sc = -INFINITY;
+                s[e] = sc;
+                bm = fmaxf(bm, sc);
+            }
+        } else {
+            const float2 k2 = make_float2(kk2, kk2), sh2 = make_float2(shift2, shift2);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                const float2 sc = __ffma2_rn(make_float2((float)(int)v[2 * e], (float)(int)v[2 * e + 1]), k2, sh2);
+                s[2 * e] = sc.x, s[2 * e + 1] = sc.y;
+                bm = fmaxf(bm, fmaxf(sc.x, sc.y));
+            }
         }
         xm[g * kUQ + r] = bm;
         if (warp == kUWarpRec && it + 1 < n_it && ok)
@@ -1487,11 +1504,11 @@ attention_sage_block_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_l
         const float mn = fmaxf(m, fmaxf(fmaxf(xm[r], xm[kUQ + r]), fmaxf(xm[2 * kUQ + r], xm[3 * kUQ + r])));
         float alpha = 1.f;
         if (mn > mref + kBLazy) {  // (also the first finite maximum: mref is -inf until then)
-            alpha = mref == -INFINITY ? 0.f : exp2f((mref - mn) * kLog2e);
+            alpha = mref == -INFINITY ? 0.f : ex2_approx(mref - mn);
             mref = mn;
         }
         m = mn;
-        const float off = mref == -INFINITY ? 0.f : -mref * kLog2e;  // (a row without a key yet: every score is -inf)
+        const float off = mref == -INFINITY ? 0.f : -mref;  // (a row without a key yet: every score is -inf)
         // the product of the iteration before has read the P tiles and written the accumulator
         bool pv_ok = true;
         if (it > 0) {
@@ -1507,7 +1524,8 @@ attention_sage_block_kernel(SageArgs a, AttnDims dm, int causal, uint32_t wait_l
 #pragma unroll
             for (int qd = 0; qd < 4; ++qd) {
                 const int at = 8 * piece + 2 * qd;
-                const float p0 = ex2_approx(fmaf(s[at], kLog2e, off)), p1 = ex2_approx(fmaf(s[at + 1], kLog2e, off));
+                const float2 arg = __fadd2_rn(make_float2(s[at], s[at + 1]), make_float2(off, off));
+                const float p0 = ex2_approx(arg.x), p1 = ex2_approx(arg.y);
                 es += p0 + p1;
                 asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[qd]) : "f"(p1), "f"(p0));
             }
