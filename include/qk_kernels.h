@@ -14,7 +14,7 @@
  *    (crates/quantibbler-kernels/src/core.rs:31-44); a Python binding raises
  *    ValueError with it (crates/quantibbler-kernels/src/lib.rs:34-36).
  *  - Inputs are borrowed for the duration of the call and never retained, except by
- *    qk_layer_create / qk_layer_from_qpk1, which copy them to the device.  Outputs are
+ *    qk_layer_create / qk_layer_create_from_streams / qk_layer_from_qpk1, which copy them to the device.  Outputs are
  *    caller-allocated.
  *  - "host" pointers are ordinary process memory; "dev" pointers are CUDA device
  *    memory on the context's device.  bfloat16 travels as uint16_t bit patterns
@@ -221,6 +221,22 @@ qk_status qk_layer_create(qk_ctx *ctx, const uint8_t *ub_rows, size_t ub_len,
                           const uint8_t *vb_t_rows, size_t vb_t_len, size_t dout, size_t din,
                           size_t r, const float *s1, const float *s2, const float *bias,
                           int32_t serving_dtype, qk_layer **out);
+/* engine/mod.rs:342-381 (PackedLayer::from_layer) with the repack of :258-289 done on the
+ * device: ub_stream and vb_stream are the container's bit streams of Ub (dout x r) and Vb
+ * (din x r), ceil(rows * r / 8) bytes each, uploaded as they are; kernels separate the rows
+ * of Ub and of Vb^T, pad and tile them.  Same layer, bit for bit, as qk_layer_create on the
+ * output of qk_container_to_rows / qk_container_to_rows_transposed; a wrong stream length is
+ * refused with the same text. */
+qk_status qk_layer_create_from_streams(qk_ctx *ctx, const uint8_t *ub_stream, size_t ub_len,
+                                       const uint8_t *vb_stream, size_t vb_len, size_t dout,
+                                       size_t din, size_t r, const float *s1, const float *s2,
+                                       const float *bias, int32_t serving_dtype, qk_layer **out);
+/* The device's repack alone, result back in host memory in the layout of
+ * qk_container_to_rows (transposed == 0: n_rows rows of ceil(r/8) bytes) or of
+ * qk_container_to_rows_transposed (transposed != 0: r rows of ceil(n_rows/8) bytes). */
+qk_status qk_gpu_container_to_rows(qk_ctx *ctx, const uint8_t *stream, size_t stream_len,
+                                   size_t n_rows, size_t r, int32_t transposed, uint8_t *out,
+                                   size_t out_len);
 void qk_layer_free(qk_layer *layer);
 /* ---- qpk1 layer stream ----------------------------------------------------------
  * crates/quantibbler-qpk1/src/lib.rs:229-320 (parse) / src/quantibbler/qpk1.py:211-258
@@ -237,7 +253,7 @@ qk_status qk_qpk1_parse(const uint8_t *bytes, size_t len, qk_qpk1_info *info);
 /* s1[dout], s2[din], bias[dout] (may be NULL; zeros for a version-1 stream) as float32. */
 qk_status qk_qpk1_scales(const uint8_t *bytes, size_t len, float *s1, float *s2, float *bias);
 /* engine/mod.rs:342-381 (PackedLayer::from_layer) straight from the stream: parse, the
- * loader's rank gate r <= min(dout, din), repack, upload. */
+ * loader's rank gate r <= min(dout, din), upload, repack on the device. */
 qk_status qk_layer_from_qpk1(qk_ctx *ctx, const uint8_t *bytes, size_t len, int32_t serving_dtype,
                              qk_layer **out);
 /* y[n_tokens x dout] = layer(x[n_tokens x din]), float32 row-major device buffers.

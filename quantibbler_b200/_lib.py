@@ -130,6 +130,11 @@ _SIGNATURES = {
     "qk_set_gemv_kernel": (c_int32, [c_void_p, c_int32]),
     "qk_qpk1_parse": (c_int32, [c_void_p, c_size_t, c_void_p]),
     "qk_qpk1_scales": (c_int32, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),
+    "qk_layer_create_from_streams": (c_int32, [c_void_p, c_void_p, c_size_t, c_void_p, c_size_t,
+                                               c_size_t, c_size_t, c_size_t, c_void_p, c_void_p,
+                                               c_void_p, c_int32, POINTER(c_void_p)]),
+    "qk_gpu_container_to_rows": (c_int32, [c_void_p, c_void_p, c_size_t, c_size_t, c_size_t,
+                                           c_int32, c_void_p, c_size_t]),
     "qk_layer_from_qpk1": (c_int32, [c_void_p, c_void_p, c_size_t, c_int32, c_void_p]),
     "qk_set_sage_kernel": (c_int32, [c_void_p, c_int32]),
     "qk_allreduce_rmsnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p,

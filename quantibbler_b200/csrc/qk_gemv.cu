@@ -1614,6 +1614,54 @@ __global__ void pad_rows_kernel(const uint8_t *__restrict__ src, uint8_t *__rest
     dst[gid] = v;
 }
 
+// Container bit stream -> padded rows on the device (engine/mod.rs:258-273,
+// container_to_rows): the stream holds the n_rows x r sign matrix row-major with no padding
+// between rows, bit b of the stream in byte b / 8 at bit b % 8; row i of the result starts at
+// a byte and ends with zero bits.  One thread per 16-byte piece of the padded result.
+__global__ void stream_rows_kernel(const uint8_t *__restrict__ stream, size_t stream_len,
+                                   uint8_t *__restrict__ dst, uint32_t n_rows, uint32_t r,
+                                   uint32_t stride) {
+    const uint32_t pieces = stride / 16;
+    uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= (uint64_t)n_rows * pieces) return;
+    const uint32_t i = (uint32_t)(gid / pieces), p = (uint32_t)(gid % pieces);
+    uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (uint32_t q = 0; q < 16; ++q) {
+        const uint32_t j = p * 128 + q * 8;  // first column of this byte
+        if (j >= r) break;
+        const uint64_t bit = (uint64_t)i * r + j;
+        const size_t at = (size_t)(bit >> 3);
+        uint32_t two = stream[at];
+        if (at + 1 < stream_len) two |= (uint32_t)stream[at + 1] << 8;
+        uint32_t v = (two >> (uint32_t)(bit & 7)) & 0xffu;
+        if (r - j < 8) v &= (1u << (r - j)) - 1u;
+        w[q >> 2] |= v << (8 * (q & 3));
+    }
+    reinterpret_cast<uint4 *>(dst)[gid] = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// The same for the transposed factor (engine/mod.rs:275-289, container_to_rows_transposed):
+// the stream holds the din x r matrix row-major; row k of the result is column k, i.e. bit j
+// of row k is stream bit j * r + k.  One thread per 16-byte piece (128 values of j); threads
+// next to each other take neighbouring k, so a warp's 32 reads of one j fall into 4-5 bytes.
+__global__ void stream_rows_transposed_kernel(const uint8_t *__restrict__ stream,
+                                              uint8_t *__restrict__ dst, uint32_t din, uint32_t r,
+                                              uint32_t stride) {
+    const uint32_t pieces = stride / 16;
+    uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= (uint64_t)r * pieces) return;
+    const uint32_t k = (uint32_t)(gid % r), p = (uint32_t)(gid / r);
+    uint32_t w[4] = {0, 0, 0, 0};
+    for (uint32_t q = 0; q < 128; ++q) {
+        const uint32_t j = p * 128 + q;
+        if (j >= din) break;
+        const uint64_t bit = (uint64_t)j * r + k;
+        w[q >> 5] |= (uint32_t)((stream[bit >> 3] >> (uint32_t)(bit & 7)) & 1u) << (q & 31);
+    }
+    reinterpret_cast<uint4 *>(dst + (size_t)k * stride)[p] = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // Padded rows -> 4 KB chunks of four 16 x 512 tiles (one thread per 16-byte piece).
 __global__ void tile_rows_kernel(const uint8_t *__restrict__ rows, uint8_t *__restrict__ tiles,
                                  uint32_t n_rows, uint32_t stride, uint32_t n_groups,
@@ -2047,8 +2095,13 @@ qk_status apply_group(qk_ctx *c, const qk_layer *const *layers, size_t n_layers,
     return launch_both(c, l0, d, n_inst, c->gemv_kernel);
 }
 
+// What the host hands over for one factor: its rows already separated (row_words bytes each),
+// or the container's bit stream of the factor / of its transpose.
+enum FactorForm { kFormRows, kFormStream, kFormStreamTransposed };
+
 qk_status upload_factor(qk_ctx *c, const uint8_t *host, size_t len, size_t n_rows, size_t n_bits,
-                        uint8_t **rows_out, size_t *stride_out, uint8_t **tiles_out) {
+                        uint8_t **rows_out, size_t *stride_out, uint8_t **tiles_out,
+                        FactorForm form = kFormRows) {
     size_t row_words = qk::ceil_div(n_bits, 8);
     size_t stride = qk::ceil_div(row_words, 16) * 16;
     size_t n_groups = qk::ceil_div(n_rows, kGroupRows), n_steps = qk::ceil_div(n_bits, kStepBits);
@@ -2067,9 +2120,19 @@ qk_status upload_factor(qk_ctx *c, const uint8_t *host, size_t len, size_t n_row
     *stride_out = stride;
     QK_CUDA(cudaMemcpyAsync(c->d_packed.ptr, host, len, cudaMemcpyHostToDevice, c->stream));
     size_t total = n_rows * stride;
-    pad_rows_kernel<<<(unsigned)qk::ceil_div(total, 256), 256, 0, c->stream>>>(
-        (const uint8_t *)c->d_packed.ptr, rows, (uint32_t)n_rows, (uint32_t)n_bits,
-        (uint32_t)row_words, (uint32_t)stride);
+    if (form == kFormRows)
+        pad_rows_kernel<<<(unsigned)qk::ceil_div(total, 256), 256, 0, c->stream>>>(
+            (const uint8_t *)c->d_packed.ptr, rows, (uint32_t)n_rows, (uint32_t)n_bits,
+            (uint32_t)row_words, (uint32_t)stride);
+    else if (form == kFormStream)
+        stream_rows_kernel<<<(unsigned)qk::ceil_div(total / 16, 256), 256, 0, c->stream>>>(
+            (const uint8_t *)c->d_packed.ptr, len, rows, (uint32_t)n_rows, (uint32_t)n_bits,
+            (uint32_t)stride);
+    else
+        stream_rows_transposed_kernel<<<(unsigned)qk::ceil_div(total / 16, 256), 256, 0,
+                                        c->stream>>>((const uint8_t *)c->d_packed.ptr, rows,
+                                                     (uint32_t)n_bits, (uint32_t)n_rows,
+                                                     (uint32_t)stride);
     QK_CUDA(cudaGetLastError());
     size_t pieces = n_groups * n_steps * 256;
     tile_rows_kernel<<<(unsigned)qk::ceil_div(pieces, 256), 256, 0, c->stream>>>(
@@ -2096,10 +2159,10 @@ qk_status upload_f32(qk_ctx *c, const float *host, size_t n, float **out) {
 
 extern "C" {
 
-qk_status qk_layer_create(qk_ctx *ctx, const uint8_t *ub_rows, size_t ub_len,
-                          const uint8_t *vb_t_rows, size_t vb_t_len, size_t dout, size_t din,
-                          size_t r, const float *s1, const float *s2, const float *bias,
-                          int32_t serving_dtype, qk_layer **out) {
+static qk_status layer_create(qk_ctx *ctx, bool streams, const uint8_t *ub_rows, size_t ub_len,
+                              const uint8_t *vb_t_rows, size_t vb_t_len, size_t dout, size_t din,
+                              size_t r, const float *s1, const float *s2, const float *bias,
+                              int32_t serving_dtype, qk_layer **out) {
     if (!out) return qk::fail(QK_ERR_VALUE, "qk_layer_create: out is null");
     *out = nullptr;
     if (serving_dtype != QK_F32 && serving_dtype != QK_BF16)
@@ -2108,9 +2171,18 @@ qk_status qk_layer_create(qk_ctx *ctx, const uint8_t *ub_rows, size_t ub_len,
     if (dout == 0 || din == 0 || r == 0)
         return qk::fail(QK_ERR_VALUE, "layer dimensions must be positive: dout=%zu din=%zu r=%zu",
                         dout, din, r);
-    // engine/mod.rs:343-356: both bitplanes must have the per-row layout's exact length
-    if (ub_len != dout * qk::ceil_div(r, 8) || vb_t_len != r * qk::ceil_div(din, 8))
+    if (streams) {
+        // engine/mod.rs:258-289: a container stream holds exactly its matrix's bits
+        if (ub_len != qk::ceil_div(dout * r, 8))
+            return qk::fail(QK_ERR_VALUE, "container stream holds %zu bytes; %zux%zu bits need %zu",
+                            ub_len, dout, r, qk::ceil_div(dout * r, 8));
+        if (vb_t_len != qk::ceil_div(din * r, 8))
+            return qk::fail(QK_ERR_VALUE, "container stream holds %zu bytes; %zux%zu bits need %zu",
+                            vb_t_len, din, r, qk::ceil_div(din * r, 8));
+    } else if (ub_len != dout * qk::ceil_div(r, 8) || vb_t_len != r * qk::ceil_div(din, 8)) {
+        // engine/mod.rs:343-356: both bitplanes must have the per-row layout's exact length
         return qk::fail(QK_ERR_VALUE, "bitplane length mismatch after repack");
+    }
     if ((uint64_t)dout * qk::ceil_div(r, 8) > qk::kIndexCeiling ||
         (uint64_t)r * qk::ceil_div(din, 8) > qk::kIndexCeiling)
         return qk::fail(QK_ERR_VALUE, "layer exceeds the device u32 index ceiling (%llu)",
@@ -2131,9 +2203,11 @@ qk_status qk_layer_create(qk_ctx *ctx, const uint8_t *ub_rows, size_t ub_len,
     l->din = din;
     l->r = r;
     l->serving = serving_dtype;
-    st = upload_factor(c, ub_rows, ub_len, dout, r, &l->ub, &l->ub_stride, &l->ub_tiles);
+    st = upload_factor(c, ub_rows, ub_len, dout, r, &l->ub, &l->ub_stride, &l->ub_tiles,
+                       streams ? kFormStream : kFormRows);
     if (st == QK_OK)
-        st = upload_factor(c, vb_t_rows, vb_t_len, r, din, &l->vbt, &l->vbt_stride, &l->vbt_tiles);
+        st = upload_factor(c, vb_t_rows, vb_t_len, r, din, &l->vbt, &l->vbt_stride, &l->vbt_tiles,
+                           streams ? kFormStreamTransposed : kFormRows);
     if (st == QK_OK) st = upload_f32(c, s1, dout, &l->s1);
     if (st == QK_OK) st = upload_f32(c, s2, din, &l->s2);
     if (st == QK_OK && bias) st = upload_f32(c, bias, dout, &l->bias);
@@ -2143,6 +2217,58 @@ qk_status qk_layer_create(qk_ctx *ctx, const uint8_t *ub_rows, size_t ub_len,
     }
     *out = l;
     return QK_OK;
+}
+
+qk_status qk_layer_create(qk_ctx *ctx, const uint8_t *ub_rows, size_t ub_len,
+                          const uint8_t *vb_t_rows, size_t vb_t_len, size_t dout, size_t din,
+                          size_t r, const float *s1, const float *s2, const float *bias,
+                          int32_t serving_dtype, qk_layer **out) {
+    return layer_create(ctx, false, ub_rows, ub_len, vb_t_rows, vb_t_len, dout, din, r, s1, s2, bias,
+                        serving_dtype, out);
+}
+
+qk_status qk_layer_create_from_streams(qk_ctx *ctx, const uint8_t *ub_stream, size_t ub_len,
+                                       const uint8_t *vb_stream, size_t vb_len, size_t dout,
+                                       size_t din, size_t r, const float *s1, const float *s2,
+                                       const float *bias, int32_t serving_dtype, qk_layer **out) {
+    return layer_create(ctx, true, ub_stream, ub_len, vb_stream, vb_len, dout, din, r, s1, s2, bias,
+                        serving_dtype, out);
+}
+
+qk_status qk_gpu_container_to_rows(qk_ctx *ctx, const uint8_t *stream, size_t stream_len,
+                                   size_t n_rows, size_t r, int32_t transposed, uint8_t *out,
+                                   size_t out_len) {
+    // the stream holds n_rows x r bits; the result has n_rows rows of r bits, or (transposed)
+    // r rows of n_rows bits
+    const size_t res_rows = transposed ? r : n_rows, res_bits = transposed ? n_rows : r;
+    const size_t row_words = qk::ceil_div(res_bits, 8);
+    if (stream_len != qk::ceil_div(n_rows * r, 8))
+        return qk::fail(QK_ERR_VALUE, "container stream holds %zu bytes; %zux%zu bits need %zu",
+                        stream_len, n_rows, r, qk::ceil_div(n_rows * r, 8));
+    if (out_len != res_rows * row_words)
+        return qk::fail(QK_ERR_VALUE, "output length %zu does not match %zu rows x %zu bitplanes",
+                        out_len, res_rows, row_words);
+    if (out_len == 0) return QK_OK;
+    if ((uint64_t)res_rows * row_words > qk::kIndexCeiling)
+        return qk::fail(QK_ERR_VALUE, "layer exceeds the device u32 index ceiling (%llu)",
+                        (unsigned long long)qk::kIndexCeiling);
+    qk_ctx *c;
+    qk_status st = qk::resolve_ctx(ctx, &c);
+    if (st != QK_OK) return st;
+    std::lock_guard<std::mutex> lock(c->mu);
+    QK_CUDA(cudaSetDevice(c->device));
+    uint8_t *rows = nullptr, *tiles = nullptr;
+    size_t stride = 0;
+    st = upload_factor(c, stream, stream_len, res_rows, res_bits, &rows, &stride, &tiles,
+                       transposed ? kFormStreamTransposed : kFormStream);
+    if (st == QK_OK) {
+        cudaError_t e = cudaMemcpy2D(out, row_words, rows, stride, row_words, res_rows,
+                                     cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) st = qk::fail(QK_ERR_CUDA, "cudaMemcpy2D: %s", cudaGetErrorString(e));
+    }
+    if (rows) cudaFree(rows);
+    if (tiles) cudaFree(tiles);
+    return st;
 }
 
 void qk_layer_free(qk_layer *l) {

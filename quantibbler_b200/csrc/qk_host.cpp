@@ -338,19 +338,14 @@ qk_status qk_layer_from_qpk1(qk_ctx *ctx, const uint8_t *bytes, size_t len, int3
     if (info.r > (info.dout < info.din ? info.dout : info.din))
         return qk::fail(QK_ERR_VALUE, "r=%zu exceeds min(dout, din)=%zu", info.r,
                         info.dout < info.din ? info.dout : info.din);
-    const size_t ub_words = qk::ceil_div(info.r, 8), vb_words = qk::ceil_div(info.din, 8);
-    std::vector<uint8_t> ub_rows(info.dout * ub_words), vbt_rows(info.r * vb_words);
     std::vector<float> s1(info.dout), s2(info.din), bias(info.dout);
-    if ((st = qk_container_to_rows(bytes + info.ub_offset, info.ub_len, info.dout, info.r,
-                                   ub_rows.data(), ub_rows.size())) != QK_OK)
-        return st;
-    if ((st = qk_container_to_rows_transposed(bytes + info.vb_offset, info.vb_len, info.din, info.r,
-                                              vbt_rows.data(), vbt_rows.size())) != QK_OK)
-        return st;
     if ((st = qk_qpk1_scales(bytes, len, s1.data(), s2.data(), bias.data())) != QK_OK) return st;
-    return qk_layer_create(ctx, ub_rows.data(), ub_rows.size(), vbt_rows.data(), vbt_rows.size(),
-                           info.dout, info.din, info.r, s1.data(), s2.data(),
-                           info.bias_offset ? bias.data() : nullptr, serving_dtype, out);
+    // the two container streams go to the device as they are; the rows are separated there
+    return qk_layer_create_from_streams(ctx, bytes + info.ub_offset, info.ub_len,
+                                        bytes + info.vb_offset, info.vb_len, info.dout, info.din,
+                                        info.r, s1.data(), s2.data(),
+                                        info.bias_offset ? bias.data() : nullptr, serving_dtype,
+                                        out);
 }
 
 }  // extern "C"

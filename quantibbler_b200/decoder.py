@@ -282,9 +282,7 @@ class Decoder:
                     raise ValueError("q/k norms must be present in every block or in none")
                 else:
                     self.qk_norms.append(None)
-                L = {n: PackedLayer(ctx, lw[n]["ub_rows"], lw[n]["vb_t_rows"], lw[n]["dout"],
-                                    lw[n]["din"], lw[n]["r"], lw[n]["s1"], lw[n]["s2"],
-                                    lw[n].get("bias"), serving=cfg.serving, name=n) for n in LINEARS}
+                L = {n: self._upload(ctx, lw[n], n) for n in LINEARS}
             self.layers.append(L)
 
             def rows(t, b):
@@ -409,6 +407,19 @@ class Decoder:
         self._host_positions = [0] * B
 
     # ------------------------------------------------------------------ tensor parallel
+    def _upload(self, ctx, layer: dict, name: str) -> PackedLayer:
+        """One linear onto the device: from its container streams where the dict still holds
+        them (a whole layer of a model directory; the device separates the rows), else from
+        row bitplanes (synthetic weights, tensor-parallel shards)."""
+        if "ub_packed" in layer and "ub_rows" not in layer:
+            return PackedLayer.from_container(ctx, layer["ub_packed"], layer["vb_packed"],
+                                              layer["dout"], layer["din"], layer["r"],
+                                              layer["s1"], layer["s2"], layer.get("bias"),
+                                              serving=self.cfg.serving, name=name)
+        return PackedLayer(ctx, layer["ub_rows"], layer["vb_t_rows"], layer["dout"], layer["din"],
+                           layer["r"], layer["s1"], layer["s2"], layer.get("bias"),
+                           serving=self.cfg.serving, name=name)
+
     def _setup_fused_allreduce(self, B: int, d: int) -> None:
         """Two inboxes in symmetric memory (every rank maps every peer's copy) for
         ``qk_allreduce_rmsnorm``.  If the peers cannot be mapped the decoder keeps the NCCL

@@ -99,6 +99,19 @@ class GpuContext:
             handle = int(cuda_stream) or 1
         check(_lib.lib().qk_gpu_set_stream(self._h, ctypes.c_void_p(handle)))
 
+    def container_to_rows(self, stream, n_rows: int, r: int, transposed: bool = False) -> np.ndarray:
+        """The container repack of engine/mod.rs:258-289 run by the device's kernels (the ones
+        ``PackedLayer.from_container`` uses): ``stream`` holds an ``n_rows x r`` sign matrix
+        bit by bit; the result is its rows (``n_rows x ceil(r/8)`` bytes) or, transposed, its
+        columns (``r x ceil(n_rows/8)``)."""
+        s = _f(stream, np.uint8).ravel()
+        rows, bits = (int(r), int(n_rows)) if transposed else (int(n_rows), int(r))
+        out = np.zeros((rows, (bits + 7) // 8), np.uint8)
+        check(_lib.lib().qk_gpu_container_to_rows(self._h, s.ctypes.data, s.size, int(n_rows),
+                                                  int(r), int(bool(transposed)),
+                                                  out.ctypes.data, out.size))
+        return out
+
     def set_gemv_kernel(self, which: int) -> int:
         return int(_lib.lib().qk_set_gemv_kernel(self._h, int(which)))
 
@@ -280,16 +293,34 @@ class PackedLayer:
     @classmethod
     def from_container(cls, ctx, ub_packed, vb_packed, dout, din, r, s1, s2, bias=None,
                        serving="float32", name=""):
-        """engine/mod.rs:342-381 (from_layer): container bit streams -> per-row planes."""
+        """engine/mod.rs:342-381 (from_layer) from the container's bit streams of Ub
+        (dout x r) and Vb (din x r): uploaded as they are, the rows of Ub and of Vb^T are
+        separated on the device (the repack of engine/mod.rs:258-289)."""
+        if serving not in ("float32", "bfloat16"):
+            raise KernelError(f"serving dtype must be float32 or bfloat16, got {serving!r}")
+        self = cls.__new__(cls)
+        self.ctx, self.name, self.serving = ctx, name, serving
+        self.dout, self.din, self.r = int(dout), int(din), int(r)
         ub = _f(ub_packed, np.uint8).ravel()
         vb = _f(vb_packed, np.uint8).ravel()
-        ub_rows = np.zeros(dout * ((r + 7) // 8), np.uint8)
-        vb_t_rows = np.zeros(r * ((din + 7) // 8), np.uint8)
-        check(_lib.lib().qk_container_to_rows(ub.ctypes.data, ub.size, dout, r,
-                                              ub_rows.ctypes.data, ub_rows.size))
-        check(_lib.lib().qk_container_to_rows_transposed(vb.ctypes.data, vb.size, din, r,
-                                                         vb_t_rows.ctypes.data, vb_t_rows.size))
-        return cls(ctx, ub_rows, vb_t_rows, dout, din, r, s1, s2, bias, serving, name)
+        s1 = _f(s1, np.float32).ravel()
+        s2 = _f(s2, np.float32).ravel()
+        if s1.size != self.dout or s2.size != self.din:
+            raise KernelError(f"layer {name}: scale lengths {s1.size}/{s2.size} do not match "
+                              f"dout={dout}, din={din}")
+        b = None
+        if bias is not None and np.size(bias):
+            b = _f(bias, np.float32).ravel()
+            if b.size != self.dout:  # engine/mod.rs:357-363
+                raise KernelError(
+                    f"layer {name}: bias has {b.size} entries; expected dout={dout}")
+        h = ctypes.c_void_p()
+        check(_lib.lib().qk_layer_create_from_streams(
+            ctx.handle, ub.ctypes.data, ub.size, vb.ctypes.data, vb.size, self.dout, self.din,
+            self.r, s1.ctypes.data, s2.ctypes.data, b.ctypes.data if b is not None else None,
+            QK_F32 if serving == "float32" else QK_BF16, ctypes.byref(h)))
+        self._h = h
+        return self
 
     @classmethod
     def from_qpk1(cls, ctx, data, serving="float32", name=""):

@@ -261,18 +261,32 @@ def load(model_dir: str) -> ModelDirectory:
         remainder_dtype=dtype, embedding=embedding, lm_head=lm_head, norm_weights=norm_weights)
 
 
+class _Factors(dict):
+    """One layer of a model directory as ``Decoder`` takes it: the container's two bit streams
+    (``ub_packed``, ``vb_packed``), which the device separates into rows at upload, and, made
+    on first use only (the tensor-parallel split and the CPU restatement read them), the row
+    bitplanes of Ub and of Vb^T (engine/mod.rs:342-381, PackedLayer::from_layer)."""
+
+    def __missing__(self, key):
+        if key not in ("ub_rows", "vb_t_rows"):
+            raise KeyError(key)
+        dout, din, r = self["dout"], self["din"], self["r"]
+        ub, vb = self["ub_packed"], self["vb_packed"]
+        ub_rows = np.zeros((dout, (r + 7) // 8), np.uint8)
+        vb_t_rows = np.zeros((r, (din + 7) // 8), np.uint8)
+        check(_lib.lib().qk_container_to_rows(ub.ctypes.data, ub.size, dout, r,
+                                              ub_rows.ctypes.data, ub_rows.size))
+        check(_lib.lib().qk_container_to_rows_transposed(vb.ctypes.data, vb.size, din, r,
+                                                         vb_t_rows.ctypes.data, vb_t_rows.size))
+        self["ub_rows"], self["vb_t_rows"] = ub_rows, vb_t_rows
+        return dict.__getitem__(self, key)
+
+
 def _rows(layer: dict) -> dict:
-    """engine/mod.rs:342-381 (PackedLayer::from_layer): row bitplanes of Ub and of Vb^T."""
-    dout, din, r = layer["dout"], layer["din"], layer["r"]
-    ub, vb = layer["ub_packed"], layer["vb_packed"]
-    ub_rows = np.zeros((dout, (r + 7) // 8), np.uint8)
-    vb_t_rows = np.zeros((r, (din + 7) // 8), np.uint8)
-    check(_lib.lib().qk_container_to_rows(ub.ctypes.data, ub.size, dout, r, ub_rows.ctypes.data,
-                                          ub_rows.size))
-    check(_lib.lib().qk_container_to_rows_transposed(vb.ctypes.data, vb.size, din, r,
-                                                     vb_t_rows.ctypes.data, vb_t_rows.size))
-    return dict(ub_rows=ub_rows, vb_t_rows=vb_t_rows, dout=dout, din=din, r=r, s1=layer["s1"],
-                s2=layer["s2"], bias=layer["bias"])
+    return _Factors(ub_packed=np.ascontiguousarray(layer["ub_packed"], dtype=np.uint8).ravel(),
+                    vb_packed=np.ascontiguousarray(layer["vb_packed"], dtype=np.uint8).ravel(),
+                    dout=layer["dout"], din=layer["din"], r=layer["r"], s1=layer["s1"],
+                    s2=layer["s2"], bias=layer["bias"])
 
 
 def decoder_inputs(md: ModelDirectory, **overrides):

@@ -20,10 +20,17 @@ def _range(n: int, rank: int, size: int) -> tuple[int, int]:
     return rank * step, (rank + 1) * step
 
 
+def _with_rows(layer: dict) -> dict:
+    """A plain copy that holds the row bitplanes (a model directory's layer makes them on
+    first use) and not the container streams, which describe the whole layer only."""
+    layer["ub_rows"], layer["vb_t_rows"]  # noqa: B018  (touch: see model_dir._Factors)
+    return {k: v for k, v in layer.items() if k not in ("ub_packed", "vb_packed")}
+
+
 def shard_column_parallel(layer: dict, rank: int, size: int) -> dict:
     """Rows of Ub, s1 and bias for output features [lo, hi); Vb^T and s2 whole."""
     lo, hi = _range(layer["dout"], rank, size)
-    out = dict(layer)
+    out = _with_rows(layer)
     out["ub_rows"] = np.ascontiguousarray(layer["ub_rows"][lo:hi])
     out["s1"] = np.ascontiguousarray(layer["s1"][lo:hi])
     out["bias"] = None if layer.get("bias") is None else np.ascontiguousarray(layer["bias"][lo:hi])
@@ -37,7 +44,7 @@ def shard_row_parallel(layer: dict, rank: int, size: int) -> dict:
     lo, hi = _range(layer["din"], rank, size)
     if lo % 8 or hi % 8:
         raise ValueError(f"row-parallel shard [{lo}, {hi}) must fall on byte boundaries")
-    out = dict(layer)
+    out = _with_rows(layer)
     out["vb_t_rows"] = np.ascontiguousarray(layer["vb_t_rows"][:, lo // 8:hi // 8])
     out["s2"] = np.ascontiguousarray(layer["s2"][lo:hi])
     out["din"] = hi - lo

@@ -481,3 +481,47 @@ def test_long_input_vector_in_the_few_instance_form(gpu_ctx, serving, din):
     bad[din - 3] = np.inf
     assert np.isnan(layer.apply(bad)).all()
     layer.close()
+
+
+@pytest.mark.parametrize("shape", [(5, 7), (4, 16), (9, 35), (300, 129), (257, 1000), (4096, 1024),
+                                   (1, 1), (130, 515)])
+def test_container_repack_on_the_device(gpu_ctx, shape):
+    # engine/mod.rs:258-289: rows of the matrix and rows of its transpose from the container's
+    # unpadded bit stream, byte for byte what the host functions and the restatement give
+    n_rows, r = shape
+    rng = np.random.default_rng(n_rows * 131 + r)
+    bits = rng.random((n_rows, r)) < 0.5
+    stream = np.packbits(bits.ravel(), bitorder="little")
+    assert np.array_equal(gpu_ctx.container_to_rows(stream, n_rows, r),
+                          oracle.container_to_rows(stream, n_rows, r))
+    assert np.array_equal(gpu_ctx.container_to_rows(stream, n_rows, r, transposed=True),
+                          oracle.container_to_rows_transposed(stream, n_rows, r))
+    # a wrong length is refused with the host function's text
+    with pytest.raises(KernelError, match="container stream holds"):
+        gpu_ctx.container_to_rows(np.append(stream, np.uint8(0)), n_rows, r)
+
+
+@pytest.mark.parametrize("serving", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape", [(96, 160, 72), (130, 1100, 515), (1024, 4096, 1000)])
+def test_layer_from_container_streams_equals_layer_from_rows(gpu_ctx, shape, serving):
+    # the same layer, bit for bit, whether the host or the device separates the rows
+    dout, din, r = shape
+    L = make_layer(dout, din, r, seed=dout + r, with_bias=True)
+    ub_stream = np.packbits(L["ub"].ravel(), bitorder="little")   # dout x r, no padding
+    vb_stream = np.packbits(L["vb"].ravel(), bitorder="little")   # din x r
+    a = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], dout, din, r, L["s1"], L["s2"],
+                    L["bias"], serving=serving)
+    b = PackedLayer.from_container(gpu_ctx, ub_stream, vb_stream, dout, din, r, L["s1"], L["s2"],
+                                   L["bias"], serving=serving)
+    x = np.stack([L["x"], -0.5 * L["x"][::-1]])
+    ya = np.stack([a.apply(v) for v in x])
+    yb = np.stack([b.apply(v) for v in x])
+    assert np.array_equal(ya, yb)
+    want = oracle.layer_apply(L["ub_rows"], L["vb_t_rows"], dout, din, r, L["s1"], L["s2"],
+                              L["bias"], x[0], serving=serving)
+    assert np.abs(yb[0] - want).max() <= (2e-3 if serving == "float32" else 2e-2) * np.abs(want).max()
+    with pytest.raises(KernelError, match="container stream holds"):
+        PackedLayer.from_container(gpu_ctx, ub_stream[:-1], vb_stream, dout, din, r, L["s1"],
+                                   L["s2"], L["bias"], serving=serving)
+    a.close()
+    b.close()
