@@ -443,7 +443,7 @@ class HostLayerGroup:
     duplex).  ``x_host`` is ``[n_layers, din]`` and ``y_host`` ``[n_layers, dout]`` float32
     torch CPU tensors; pinned memory makes both copies asynchronous DMA."""
 
-    def __init__(self, ctx: GpuContext, layers, n_parts: int | None = None):
+    def __init__(self, ctx: GpuContext, layers, n_parts: int | None = None, bounds=None):
         import torch
         self.torch, self.ctx, self.layers = torch, ctx, list(layers)
         first = self.layers[0]
@@ -451,10 +451,17 @@ class HostLayerGroup:
         self.x_dev = torch.zeros((n, first.din), dtype=torch.float32, device="cuda")
         self.y_dev = torch.zeros((n, first.dout), dtype=torch.float32, device="cuda")
         # sub-groups of at least ~300 layers keep every launch in its many-instance form
-        # (measured on 2368 config-0 layers: 4 parts 2200 GB/s, 8 parts 2550, 12 parts 2120)
+        # (measured on 2368 config-0 layers: 4 parts 2200 GB/s, 8 parts 2550, 12 parts 2120;
+        # uneven splits given through `bounds` - a short first or last sub-group, tapered
+        # sizes, 16 x 148 - all measured below the even 8 x 296: 2310-2585 against 2595)
         if n_parts is None:
             n_parts = max(1, min(8, n // 296))
-        bounds = [n * i // n_parts for i in range(n_parts + 1)]
+        if bounds is None:
+            bounds = [n * i // n_parts for i in range(n_parts + 1)]
+        bounds = [int(b) for b in bounds]
+        if bounds[0] != 0 or bounds[-1] != n or any(a >= b for a, b in zip(bounds, bounds[1:])):
+            raise KernelError(f"sub-group bounds must rise from 0 to {n}, got {bounds}")
+        n_parts = len(bounds) - 1
         self.parts = []
         for lo, hi in zip(bounds[:-1], bounds[1:]):
             self.parts.append(LayerGroup(ctx, self.layers[lo:hi], self.x_dev[lo:hi].data_ptr(),
