@@ -174,6 +174,43 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
     // sum is reproducible) before the epilogue.  The wait on the flags is bounded all the same.
     const uint32_t u_begin = unit_begin(blockIdx.x, g.units, gridDim.x);
     const uint32_t u_end = unit_begin(blockIdx.x + 1, g.units, gridDim.x);
+    const uint32_t total_chunks = u_end - u_begin;
+    // What depends on no other kernel is fetched before the dependency wait: the weight bits
+    // of each producer's first two chunks (a first touch of those rows: one DRAM latency that
+    // would otherwise open the main loop), the lines of its later chunks and the tensor maps
+    // into L2 / the descriptor cache, the first segment's scales and biases.
+    // The ring of stages runs on across tiles: chunk number gc (counted from the CTA's first
+    // unit) uses stage gc % 4 and belongs to group gc % 4.  Rows past the end of the factor
+    // re-read the last row: their accumulator lanes are never stored.
+    const uint32_t group = tid / kGroupThreads, row = tid % kGroupThreads;
+    auto bits_at = [&](uint32_t gc) -> const uint2 * {
+        const UnitPos at = locate(g, u_begin + gc);
+        const Problem &pr = g.p[at.problem];
+        const uint32_t n_src = min((at.tile % pr.row_tiles) * kBM + row, pr.n_rows - 1);
+        return reinterpret_cast<const uint2 *>(pr.w_rows + (size_t)n_src * pr.w_stride) + at.kc;
+    };
+    auto load_bits = [&](uint32_t gc) -> uint2 {
+        return gc < total_chunks ? *bits_at(gc) : make_uint2(0, 0);
+    };
+    uint2 q0 = make_uint2(0, 0), q1 = q0;
+    if (warp < kProducerWarps) {
+        q0 = load_bits(group);
+        q1 = load_bits(group + kGroups);
+        // (a 128-byte line of a row holds sixteen chunks)
+        for (uint32_t gc = group + 16; gc < total_chunks && gc < group + 16 * 8; gc += 16)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(bits_at(gc)));
+    } else if (warp == kMmaWarp) {
+        if (lane < g.n_problems) {
+            const CUtensorMap *m = lane == 0 ? &map0 : lane == 1 ? &map1 : lane == 2 ? &map2 : &map3;
+            asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
+        }
+    } else if (kFinal && total_chunks) {
+        const UnitPos at = locate(g, u_begin);
+        const Problem &pr = g.p[at.problem];
+        const uint32_t n = min((at.tile % pr.row_tiles) * kBM + (warp % 4) * 32 + lane, pr.n_rows - 1);
+        if (pr.out_scale) asm volatile("prefetch.global.L2 [%0];" ::"l"(pr.out_scale + n));
+        if (pr.out_bias) asm volatile("prefetch.global.L2 [%0];" ::"l"(pr.out_bias + n));
+    }
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -203,26 +240,12 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
     // waits, so that this kernel's completion implies the completion of everything before it.
     qk::pdl_wait();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t total_chunks = u_end - u_begin;
 
     if (warp < kProducerWarps) {
         // ------------------------------------------------------------ producers
-        // The ring of stages runs on across tiles: chunk number gc (counted from the CTA's
-        // first unit) uses stage gc % 4 and belongs to group gc % 4.  Rows past the end of
-        // the factor re-read the last row: their accumulator lanes are never stored.
-        const uint32_t group = tid / kGroupThreads, row = tid % kGroupThreads;
         uint8_t *a_tile = tiles + group * kStageBytes, *b_tile = a_tile + kABytes;
         uint64_t *my_full = &full[group], *my_empty = &empty[group];
         const uint32_t dst_base = smem_u32(a_tile) + row * 128, swz = (row & 7) << 4;
-        const uint2 zero2 = make_uint2(0, 0);
-        auto load_bits = [&](uint32_t gc) -> uint2 {
-            if (gc >= total_chunks) return zero2;
-            const UnitPos at = locate(g, u_begin + gc);
-            const Problem &pr = g.p[at.problem];
-            const uint32_t n_src = min((at.tile % pr.row_tiles) * kBM + row, pr.n_rows - 1);
-            return reinterpret_cast<const uint2 *>(pr.w_rows + (size_t)n_src * pr.w_stride)[at.kc];
-        };
-        uint2 q0 = load_bits(group), q1 = load_bits(group + kGroups);
         uint32_t it = 0;
         for (uint32_t gc = group; gc < total_chunks; gc += kGroups, ++it) {
             const uint2 cur = q0;
@@ -474,20 +497,26 @@ struct ScaleArgs {
 __global__ void scale_to_bf16_kernel(const float *__restrict__ x, ScaleArgs a, uint32_t n_tokens,
                                      uint32_t din, uint32_t pitch, int vec) {
     qk::pdl_launch();  // the kernel after this one may begin its prologue
-    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     const float *__restrict__ s2 = a.s2[blockIdx.y];
     uint16_t *__restrict__ z = a.z[blockIdx.y];
     const uint32_t per_row = pitch / 8;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)n_tokens * per_row) return;
+    const bool live = idx < (size_t)n_tokens * per_row;
     const uint32_t t = (uint32_t)(idx / per_row), k = (uint32_t)(idx % per_row) * 8;
+    const bool wide = vec && k + 8 <= din;
+    // (the scale is a constant of the layer: it is read before the dependency wait)
+    float4 c0 = make_float4(0.f, 0.f, 0.f, 0.f), d0 = c0;
+    if (live && wide) {
+        c0 = *reinterpret_cast<const float4 *>(s2 + k);
+        d0 = *reinterpret_cast<const float4 *>(s2 + k + 4);
+    }
+    qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
+    if (!live) return;
     const float *xr = x + (size_t)t * din;
     float v[8];
-    if (vec && k + 8 <= din) {
+    if (wide) {
         const float4 a0 = *reinterpret_cast<const float4 *>(xr + k);
         const float4 b0 = *reinterpret_cast<const float4 *>(xr + k + 4);
-        const float4 c0 = *reinterpret_cast<const float4 *>(s2 + k);
-        const float4 d0 = *reinterpret_cast<const float4 *>(s2 + k + 4);
         v[0] = c0.x * a0.x; v[1] = c0.y * a0.y; v[2] = c0.z * a0.z; v[3] = c0.w * a0.w;
         v[4] = d0.x * b0.x; v[5] = d0.y * b0.y; v[6] = d0.z * b0.z; v[7] = d0.w * b0.w;
     } else {
