@@ -36,6 +36,7 @@
 
 #include <algorithm>
 #include <cstring>
+#include <type_traits>
 
 #include "qk_common.h"
 #include "qk_umma.cuh"
@@ -358,19 +359,51 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
             if (kc0 == 0 && len < pr.k_chunks) {
                 const uint32_t hi = at.tile_begin + pr.k_chunks;
                 while (last < gridDim.x && unit_begin(last, g.units, gridDim.x) < hi) ++last;
-                for (uint32_t j = blockIdx.x + 1; j < last && !dead; ++j) {
-                    uint32_t seen = 0;
-                    for (uint32_t i = 0; i < g.wait_limit; ++i) {
-                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(g.flags + j) : "memory");
-                        if (seen) break;
-                        if ((i & 255u) == 255u && *abort_flag) break;
-                        __nanosleep(64);
-                    }
-                    // every lane made its own acquire load; the warp goes on only if all saw it
-                    dead = __all_sync(0xffffffffu, seen != 0) == 0;
+            }
+            // this CTA's own share of the tile first: once its accumulator is complete, every
+            // MMA of the CTA so far has read its operands
+            dead = !mbar_wait(&acc_full[acc], (seg >> 1) & 1, abort_flag, g.wait_limit);
+            // When this is the CTA's last segment the pipeline has drained and the stages are
+            // free: as many of the following CTAs' partials as fit there (each is contiguous,
+            // bn x 128 floats) come in by bulk copies instead of latency-bound loads, each one
+            // started the moment its flag is seen, so that the copies run while the later CTAs
+            // are still being waited for.  Any further partials are read directly.
+            const uint32_t part_bytes = kBN * kBM * 4;
+            uint32_t n_staged = 0;
+            if (last > blockIdx.x + 1 && u + len == u_end)
+                n_staged = min(last - blockIdx.x - 1, (uint32_t)(kStages * kStageBytes) / part_bytes);
+            const bool staged = n_staged > 0, issuer = warp == kEpilogueWarp0 && lane == 0;
+            for (uint32_t j = blockIdx.x + 1; j < last && !dead; ++j) {
+                uint32_t seen = 0;
+                for (uint32_t i = 0; i < g.wait_limit; ++i) {
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(g.flags + j) : "memory");
+                    if (seen) break;
+                    if ((i & 255u) == 255u && *abort_flag) break;
+                    __nanosleep(64);
+                }
+                // every lane made its own acquire load; the warp goes on only if all saw it
+                dead = __all_sync(0xffffffffu, seen != 0) == 0;
+                const uint32_t slot = j - blockIdx.x - 1;
+                if (!dead && issuer && slot < n_staged) {
+                    // (the partial was written through the generic proxy and is read by the
+                    // asynchronous one)
+                    asm volatile("fence.proxy.async.global;" ::: "memory");
+                    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(
+                                     smem_u32(staged_bar)),
+                                 "r"(part_bytes)
+                                 : "memory");
+                    asm volatile(
+                        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+                            "r"(smem_u32(tiles) + slot * part_bytes),
+                        "l"(g.partials + (size_t)j * slot_elems), "r"(part_bytes), "r"(smem_u32(staged_bar))
+                        : "memory");
                 }
             }
-            if (!dead) dead = !mbar_wait(&acc_full[acc], (seg >> 1) & 1, abort_flag, g.wait_limit);
+            // (the barrier's one pending arrival keeps its phase open until every copy that was
+            // started has been accounted for; the issuer arrives whether or not its warp gave
+            // up, and every warp waits for the copies that are in flight before it votes)
+            if (issuer && staged) mbar_arrive(staged_bar);
+            if (staged && !mbar_wait(staged_bar, 0, abort_flag, g.wait_limit)) dead = true;
             // one verdict for the four epilogue warps before any of them touches tensor memory
             // or one of the epilogue's barriers
             if (!epilogue_vote(!dead, kEpilogueWarps * 32)) {
@@ -383,77 +416,76 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
             const float scale = (kFinal && pr.out_scale && n < pr.n_rows) ? pr.out_scale[n] : 1.f;
             const float bias = (kFinal && pr.out_bias && n < pr.n_rows) ? pr.out_bias[n] : 0.f;
             float *part = g.partials + (size_t)blockIdx.x * slot_elems;
-            // When this is the CTA's last segment the pipeline has drained and the stages are
-            // free: as many of the following CTAs' partials as fit there (each is contiguous,
-            // bn x 128 floats) come in by bulk copies instead of latency-bound loads.  Any
-            // further partials are read directly.
-            const uint32_t part_bytes = kBN * kBM * 4;
-            uint32_t n_staged = 0;
-            if (last > blockIdx.x + 1 && u + len == u_end)
-                n_staged = min(last - blockIdx.x - 1, (uint32_t)(kStages * kStageBytes) / part_bytes);
-            const bool staged = n_staged > 0;
-            if (staged) {
-                if (warp == kEpilogueWarp0 && lane == 0) {
-                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
-                                     smem_u32(staged_bar)),
-                                 "r"(n_staged * part_bytes)
-                                 : "memory");
-                    for (uint32_t i = 0; i < n_staged; ++i)
-                        asm volatile(
-                            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
-                                "r"(smem_u32(tiles) + i * part_bytes),
-                            "l"(g.partials + (size_t)(blockIdx.x + 1 + i) * slot_elems), "r"(part_bytes),
-                            "r"(smem_u32(staged_bar))
-                            : "memory");
-                }
-                // (`staged` is the same in all four warps, so all of them take this vote)
-                if (!epilogue_vote(mbar_wait(staged_bar, 0, abort_flag, g.wait_limit), kEpilogueWarps * 32)) {
-                    *abort_flag = 1;
-                    dead = true;
-                    break;
-                }
-            }
             const float *staged_part = reinterpret_cast<const float *>(tiles);
-            for (uint32_t c0 = 0; c0 < kBN; c0 += 16) {
-                if (t0 + c0 >= g.tokens) break;  // warp-uniform
-                uint32_t v[16];
+            // kW token columns at a time: tensor memory -> registers, the other CTAs' shares
+            // added in CTA order, then the partial or the finished outputs stored
+            auto columns = [&](uint32_t c0, auto width) {
+                constexpr int kW = decltype(width)::value;
+                uint32_t v[kW];
                 const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + acc * kBNMax + c0;
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]),
-                      "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]),
-                      "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-                    : "r"(taddr)
-                    : "memory");
+                if constexpr (kW == 32) {
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]),
+                          "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]),
+                          "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]),
+                          "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]),
+                          "=r"(v[30]), "=r"(v[31])
+                        : "r"(taddr)
+                        : "memory");
+                } else {
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]),
+                          "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]),
+                          "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                        : "r"(taddr)
+                        : "memory");
+                }
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (kc0 != 0) {
                     // the rest of a tile another CTA began: the raw accumulator,
                     // [token column][weight row]
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
+                    for (int j = 0; j < kW; ++j)
                         part[(size_t)(c0 + j) * kBM + n_local] = __uint_as_float(v[j]);
-                    continue;
+                    return;
                 }
                 for (uint32_t i = 0; i < n_staged; ++i) {  // in CTA order
                     const float *sp = staged_part + (size_t)i * (kBN * kBM) + c0 * kBM + n_local;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
+                    for (int j = 0; j < kW; ++j)
                         v[j] = __float_as_uint(__uint_as_float(v[j]) + sp[j * kBM]);
                 }
                 for (uint32_t p = blockIdx.x + 1 + n_staged; p < last; ++p) {
                     const float *src = g.partials + (size_t)p * slot_elems + (size_t)c0 * kBM + n_local;
+                    float got[kW];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(src + j * kBM));
+                    for (int j = 0; j < kW; ++j) got[j] = __ldcg(src + j * kBM);
+#pragma unroll
+                    for (int j = 0; j < kW; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + got[j]);
                 }
                 if (n_live) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
+                    for (int j = 0; j < kW; ++j) {
                         const uint32_t tok = t0 + c0 + j;
                         if (tok >= g.tokens) break;
                         store_output<kFinal>(pr, tok, n, v[j], scale, bias);
                     }
+                }
+            };
+            for (uint32_t c0 = 0; c0 < kBN;) {
+                if (t0 + c0 >= g.tokens) break;  // warp-uniform
+                if (kBN - c0 >= 32) {
+                    columns(c0, std::integral_constant<int, 32>{});
+                    c0 += 32;
+                } else {
+                    columns(c0, std::integral_constant<int, 16>{});
+                    c0 += 16;
                 }
             }
             // the accumulator may be overwritten once every epilogue warp has read it
@@ -468,8 +500,9 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
                     for (uint32_t j = blockIdx.x + 1; j < last; ++j) g.flags[j] = 0;
             }
             if (kc0 != 0) {
-                // publish the partial: every writer fences, the four warps meet, one raises the flag
-                __threadfence();
+                // publish the partial: the four warps meet (which orders their stores before
+                // the one thread that goes on), and that thread raises the flag with a release
+                // at device scope, which is cumulative over what it has synchronised with
                 asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
                 if (warp == kEpilogueWarp0 && lane == 0)
                     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(g.flags + blockIdx.x), "r"(1u) : "memory");
