@@ -50,7 +50,9 @@ constexpr int kNormThreads = 512, kNormPer = 16;   // the stand-alone norm kerne
 constexpr int kRingStages = 3;                     // tiles in flight per warp
 constexpr int kTileBytes = 1024, kChunkBytes = kGroupTiles * kTileBytes, kGroupRows = 64;
 constexpr int kSubBlocks = 2;                      // attention groups of 128 threads per CTA
-constexpr int kSubSmemBytes = kMmaDecSmemBytes + 16;
+constexpr int kSubAttnBufs = 2;                    // staging buffers per warp of an attention group
+constexpr int kSubAttnBytes = dec_attn_smem_bytes(kSubAttnBufs);
+constexpr int kSubSmemBytes = kSubAttnBytes + 16;
 constexpr uint32_t kStepWaitLimitDefault = 4u << 20;  // polls of ~0.5 us: seconds
 
 struct StepLinear {
@@ -510,8 +512,8 @@ __device__ __noinline__ void attention_groups(const StepArgs &a, const StepSmem 
                                               uint32_t sub, uint32_t phase) {
     const SubBlock sb{threadIdx.x % 128, 1 + sub};
     uint8_t *mine = sm.attn + (size_t)sub * kSubSmemBytes;
-    const DecAttnSmem asm_ = carve_dec_attn(mine);
-    int *is_last = reinterpret_cast<int *>(mine + kMmaDecSmemBytes);
+    const DecAttnSmem asm_ = carve_dec_attn(mine, kSubAttnBufs);
+    int *is_last = reinterpret_cast<int *>(mine + kSubAttnBytes);
     const uint32_t group = a.n_heads / a.n_kv, subs = (group + a.gq - 1) / a.gq;
     const uint32_t per_seq = a.n_splits * a.n_kv * subs, total = per_seq * a.n_tok;
     for (uint32_t vb = sub * gridDim.x + blockIdx.x; vb < total; vb += kSubBlocks * gridDim.x) {
@@ -523,7 +525,7 @@ __device__ __noinline__ void attention_groups(const StepArgs &a, const StepSmem 
         if (!valid && sb.tid == 0) atomicOr(a.error, 4);  // reported like rope_cache_kernel does
         const int pos_in = min(max(pos, 0), (int)a.s_max - 1);
         const FreshKey fresh{a.k, a.v, L.cache_k, L.cache_v, a.cos_sin + (size_t)pos_in * 128, pos, seq, valid};
-        decode_attention_mma_body<true>(sb, asm_, a.q, L.cache_k, L.cache_v, a.kv_len[b], a.partial, a.n_heads,
+        decode_attention_mma_body<true, kSubAttnBufs>(sb, asm_, a.q, L.cache_k, L.cache_v, a.kv_len[b], a.partial, a.n_heads,
                                         a.n_kv, a.gq, a.s_max, a.chunk, a.n_splits, split, ky, b, fresh);
         sub_stamp(a, phase, 1, traced);
         // the last split of this (sequence, kv-head block) to finish combines them

@@ -88,19 +88,30 @@ __device__ __forceinline__ void split3(float x, uint32_t &hi, uint32_t &mid, uin
 constexpr int kMmaDecWarps = 4;
 constexpr int kMmaDecKPitch = 320, kMmaDecVPitch = 272;  // bytes per staged key row (256 + pad)
 constexpr int kMmaDecBufBytes = 16 * (kMmaDecKPitch + kMmaDecVPitch);
-// Shared memory of one group: the warps' staging buffers and the cross-warp combine arrays.
-constexpr int kMmaDecStageBytes = kMmaDecWarps * 2 * kMmaDecBufBytes;
-constexpr int kMmaDecSmemBytes = kMmaDecStageBytes + (2 * kMmaDecWarps * 8 + kMmaDecWarps * 8 * 128) * 4;
+// Shared memory of one group: every warp's private ring of staging buffers.  The cross-warp
+// combine arrays of a warp ({o[8][128], m[8], l[8]}, 4160 bytes) lie at the start of that
+// warp's own ring, which is idle by the time it writes them (its loop has ended, nothing of
+// its is in flight).  The stand-alone kernels run a ring of three buffers (two 16-key steps
+// in flight per warp: the kernel is bound by the bytes it keeps in flight, and two groups of
+// 111 KB fit an SM); the whole-step kernel, whose shared memory is shared out otherwise,
+// runs two.
+constexpr int kMmaDecBufs = 3;
+constexpr int dec_attn_smem_bytes(int bufs) { return kMmaDecWarps * bufs * kMmaDecBufBytes; }
+constexpr int kMmaDecSmemBytes = dec_attn_smem_bytes(kMmaDecBufs);
+static_assert((8 * 128 + 16) * 4 <= 2 * kMmaDecBufBytes, "a warp's combine arrays must fit its own buffers");
 struct DecAttnSmem {
-    uint8_t *stage;    // [warp][2][kMmaDecBufBytes]
-    float *m, *l, *o;  // [warp][8], [warp][8], [warp][8][128]
+    uint8_t *stage;       // [warp][bufs][kMmaDecBufBytes]
+    uint32_t warp_bytes;  // bufs * kMmaDecBufBytes
+    __device__ __forceinline__ float *o(uint32_t warp) const {  // [8][128]
+        return reinterpret_cast<float *>(stage + warp * warp_bytes);
+    }
+    __device__ __forceinline__ float *m(uint32_t warp) const { return o(warp) + 8 * 128; }  // [8]
+    __device__ __forceinline__ float *l(uint32_t warp) const { return m(warp) + 8; }        // [8]
 };
-__device__ __forceinline__ DecAttnSmem carve_dec_attn(uint8_t *base) {
+__device__ __forceinline__ DecAttnSmem carve_dec_attn(uint8_t *base, int bufs = kMmaDecBufs) {
     DecAttnSmem s;
     s.stage = base;
-    s.m = reinterpret_cast<float *>(base + kMmaDecStageBytes);
-    s.l = s.m + kMmaDecWarps * 8;
-    s.o = s.l + kMmaDecWarps * 8;
+    s.warp_bytes = (uint32_t)(bufs * kMmaDecBufBytes);
     return s;
 }
 // The position a decode step appends (whole-step kernel only): the projections' k and v rows of
@@ -118,7 +129,7 @@ struct FreshKey {
 // sequence); `sm` its shared memory; (split, ky, b) what the stand-alone kernel takes from its
 // block index.  With kRope the rotation of q (and of the new key) happens here instead of in a
 // kernel before: `fresh` describes the position being appended (see FreshKey).
-template <bool kRope>
+template <bool kRope, int kBufs = kMmaDecBufs>
 __device__ __forceinline__ void decode_attention_mma_body(
     const SubBlock sb, const DecAttnSmem sm, const float *__restrict__ q,
     const uint16_t *__restrict__ cache_k, const uint16_t *__restrict__ cache_v, int kv_len_b,
@@ -185,10 +196,11 @@ __device__ __forceinline__ void decode_attention_mma_body(
 
     const uint16_t *kb = cache_k + ((size_t)b * n_kv + kvh) * s_max * d;
     const uint16_t *vb = cache_v + ((size_t)b * n_kv + kvh) * s_max * d;
-    // Each warp streams its 16-key steps through two private shared-memory buffers with
-    // cp.async, so the next step's 8 KB of K and V are in flight while this one is multiplied.
-    // Row pitches 320 B (K) and 272 B (V) keep the 16-byte fragment reads conflict-free.
-    uint8_t *my_smem = sm.stage + warp * (2 * kMmaDecBufBytes);
+    // Each warp streams its 16-key steps through a private ring of kBufs shared-memory buffers
+    // with cp.async, so the next kBufs - 1 steps' 8 KB of K and V each are in flight while this
+    // one is multiplied.  Row pitches 320 B (K) and 272 B (V) keep the 16-byte fragment reads
+    // conflict-free.
+    uint8_t *my_smem = sm.stage + warp * sm.warp_bytes;
     auto fetch = [&](int j, int buf) {
         uint8_t *kt = my_smem + buf * kMmaDecBufBytes, *vt = kt + 16 * kMmaDecKPitch;
 #pragma unroll
@@ -229,10 +241,17 @@ __device__ __forceinline__ void decode_attention_mma_body(
         sb.sync();
     }
     int buf = 0;
-    if (j_begin + 16 * (int)warp < j_end) fetch(j_begin + 16 * (int)warp, 0);
-    for (int j = j_begin + 16 * (int)warp; j < j_end; j += 16 * kMmaDecWarps, buf ^= 1) {
-        if (j + 16 * kMmaDecWarps < j_end) {
-            fetch(j + 16 * kMmaDecWarps, buf ^ 1);
+    constexpr int kStride = 16 * kMmaDecWarps;  // keys between a warp's steps
+    const int j_first = j_begin + 16 * (int)warp;
+#pragma unroll
+    for (int ahead = 0; ahead < kBufs - 1; ++ahead)
+        if (j_first + ahead * kStride < j_end) fetch(j_first + ahead * kStride, ahead);
+    for (int j = j_first; j < j_end; j += kStride, buf = buf + 1 == kBufs ? 0 : buf + 1) {
+        // (groups still allowed in flight = the steps after this one that have been started)
+        if (j + (kBufs - 1) * kStride < j_end) {
+            fetch(j + (kBufs - 1) * kStride, (buf + kBufs - 1) % kBufs);
+            asm volatile("cp.async.wait_group %0;" ::"n"(kBufs - 1) : "memory");
+        } else if (kBufs > 2 && j + kStride < j_end) {
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -323,28 +342,28 @@ __device__ __forceinline__ void decode_attention_mma_body(
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
 
-    // ---- combine the warps of the block
-    float (*sm_m)[8] = reinterpret_cast<float (*)[8]>(sm.m), (*sm_l)[8] = reinterpret_cast<float (*)[8]>(sm.l);
-    float (*sm_o)[8][d] = reinterpret_cast<float (*)[8][d]>(sm.o);
+    // ---- combine the warps of the block (each warp's arrays lie in its own, now idle, ring)
     if (t == 0) {
-        sm_m[warp][g] = m;
-        sm_l[warp][g] = l;
+        sm.m(warp)[g] = m;
+        sm.l(warp)[g] = l;
     }
+    {
+        float *mine = sm.o(warp) + g * d;
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt)
+        for (int nt = 0; nt < 16; ++nt)
 #pragma unroll
-        for (int e = 0; e < 2; ++e)
-            sm_o[warp][g][64 * (nt / 8) + 8 * (2 * t + e) + nt % 8] = o[nt][e];
+            for (int e = 0; e < 2; ++e) mine[64 * (nt / 8) + 8 * (2 * t + e) + nt % 8] = o[nt][e];
+    }
     sb.sync();
     for (uint32_t idx = sb.tid; idx < rows * d; idx += 128) {
         const uint32_t r = idx / d, c = idx % d;
         float mm = -INFINITY;
-        for (int w = 0; w < kMmaDecWarps; ++w) mm = fmaxf(mm, sm_m[w][r]);
+        for (int w = 0; w < kMmaDecWarps; ++w) mm = fmaxf(mm, sm.m(w)[r]);
         float ll = 0.f, oo = 0.f;
         for (int w = 0; w < kMmaDecWarps; ++w) {
-            const float wt = sm_m[w][r] == -INFINITY ? 0.f : expf(sm_m[w][r] - mm);
-            ll += sm_l[w][r] * wt;
-            oo += sm_o[w][r][c] * wt;
+            const float wt = sm.m(w)[r] == -INFINITY ? 0.f : expf(sm.m(w)[r] - mm);
+            ll += sm.l(w)[r] * wt;
+            oo += sm.o(w)[r * d + c] * wt;
         }
         float *out = partial + (((size_t)b * n_heads + h0 + r) * n_splits + split) * (d + 2);
         out[2 + c] = oo;
