@@ -525,8 +525,14 @@ __device__ __noinline__ void attention_groups(const StepArgs &a, const StepSmem 
         if (!valid && sb.tid == 0) atomicOr(a.error, 4);  // reported like rope_cache_kernel does
         const int pos_in = min(max(pos, 0), (int)a.s_max - 1);
         const FreshKey fresh{a.k, a.v, L.cache_k, L.cache_v, a.cos_sin + (size_t)pos_in * 128, pos, seq, valid};
-        decode_attention_mma_body<true, kSubAttnBufs>(sb, asm_, a.q, L.cache_k, L.cache_v, a.kv_len[b], a.partial, a.n_heads,
-                                        a.n_kv, a.gq, a.s_max, a.chunk, a.n_splits, split, ky, b, fresh);
+        if (a.gq <= 4)
+            decode_attention_mma_body<true, kSubAttnBufs, true>(sb, asm_, a.q, L.cache_k, L.cache_v, a.kv_len[b],
+                                                                a.partial, a.n_heads, a.n_kv, a.gq, a.s_max, a.chunk,
+                                                                a.n_splits, split, ky, b, fresh);
+        else
+            decode_attention_mma_body<true, kSubAttnBufs, false>(sb, asm_, a.q, L.cache_k, L.cache_v, a.kv_len[b],
+                                                                 a.partial, a.n_heads, a.n_kv, a.gq, a.s_max, a.chunk,
+                                                                 a.n_splits, split, ky, b, fresh);
         sub_stamp(a, phase, 1, traced);
         // the last split of this (sequence, kv-head block) to finish combines them
         __threadfence();

@@ -519,9 +519,14 @@ decode_attention_mma_kernel(const float *__restrict__ q, const uint16_t *__restr
     qk::pdl_launch();  // the next kernel may begin its prologue
     qk::pdl_wait();    // everything before this kernel on the stream is complete and visible
     extern __shared__ __align__(16) uint8_t dec_smem[];
-    decode_attention_mma_body<false>(SubBlock{threadIdx.x, 0}, carve_dec_attn(dec_smem), q, cache_k, cache_v,
-                                     kv_len[blockIdx.z], partial, n_heads, n_kv, gq, s_max, chunk, n_splits,
-                                     blockIdx.x, blockIdx.y, blockIdx.z, FreshKey{});
+    if (gq <= 4)
+        decode_attention_mma_body<false, kMmaDecBufs, true>(
+            SubBlock{threadIdx.x, 0}, carve_dec_attn(dec_smem), q, cache_k, cache_v, kv_len[blockIdx.z], partial,
+            n_heads, n_kv, gq, s_max, chunk, n_splits, blockIdx.x, blockIdx.y, blockIdx.z, FreshKey{});
+    else
+        decode_attention_mma_body<false, kMmaDecBufs, false>(
+            SubBlock{threadIdx.x, 0}, carve_dec_attn(dec_smem), q, cache_k, cache_v, kv_len[blockIdx.z], partial,
+            n_heads, n_kv, gq, s_max, chunk, n_splits, blockIdx.x, blockIdx.y, blockIdx.z, FreshKey{});
 }
 
 
@@ -570,8 +575,14 @@ decode_attention_rope_kernel(const float *__restrict__ q, const float *__restric
     const int pos_in = min(max(pos, 0), (int)s_max - 1);
     const FreshKey fresh{k, v, cache_k, cache_v, cos_sin + (size_t)pos_in * 128, pos, seq, valid};
     const SubBlock sb{threadIdx.x, 0};
-    decode_attention_mma_body<true>(sb, carve_dec_attn(dec_smem), q, cache_k, cache_v, kv_len[b], partial, n_heads,
-                                    n_kv, gq, s_max, chunk, n_splits, split, ky, b, fresh);
+    if (gq <= 4)
+        decode_attention_mma_body<true, kMmaDecBufs, true>(sb, carve_dec_attn(dec_smem), q, cache_k, cache_v, kv_len[b],
+                                                           partial, n_heads, n_kv, gq, s_max, chunk, n_splits, split,
+                                                           ky, b, fresh);
+    else
+        decode_attention_mma_body<true, kMmaDecBufs, false>(sb, carve_dec_attn(dec_smem), q, cache_k, cache_v, kv_len[b],
+                                                            partial, n_heads, n_kv, gq, s_max, chunk, n_splits, split,
+                                                            ky, b, fresh);
     __threadfence();
     __syncthreads();
     const uint32_t group = n_heads / n_kv, subs = (group + gq - 1) / gq;

@@ -129,7 +129,13 @@ struct FreshKey {
 // sequence); `sm` its shared memory; (split, ky, b) what the stand-alone kernel takes from its
 // block index.  With kRope the rotation of q (and of the new key) happens here instead of in a
 // kernel before: `fresh` describes the position being appended (see FreshKey).
-template <bool kRope, int kBufs = kMmaDecBufs>
+// kPacked (at most four query heads per block): the legacy bf16 MMA issues at about half
+// the rate of the INT8 one on this part and the 96 MMAs of a 16-key step, not the cache
+// bytes, bound the kernel.  Only 4 of the MMA's 16 A rows were in use, so two of the three
+// terms share one MMA: rows 0-3 carry the hi terms of heads 0-3, rows 4-7 their mid terms,
+// and a second MMA carries the lo terms in rows 0-3 (64 MMAs per step).  Lane groups g and
+// g + 4 then hold the two halves of a head's sums; one shuffle per value adds them.
+template <bool kRope, int kBufs = kMmaDecBufs, bool kPacked = false>
 __device__ __forceinline__ void decode_attention_mma_body(
     const SubBlock sb, const DecAttnSmem sm, const float *__restrict__ q,
     const uint16_t *__restrict__ cache_k, const uint16_t *__restrict__ cache_v, int kv_len_b,
@@ -146,10 +152,13 @@ __device__ __forceinline__ void decode_attention_mma_body(
     const float scale = 1.0f / sqrtf((float)d);
 
     // A fragments of q: MMA m (0..7) contracts channels 32 (m/2) + 8 t + 4 (m%2) + {0,1 | 2,3}
-    uint32_t qa[3][8][2];
+    constexpr int kTerms = kPacked ? 2 : 3;
+    uint32_t qa[kTerms][8][2];
+    const uint32_t qrow = kPacked ? (g & 3u) : g;  // the query head this lane's A rows stand for
+    const bool upper = kPacked && g >= 4;           // (packed) this lane's rows carry the mid terms
     {
         // (read through L2: inside the whole-step kernel another block wrote q moments ago)
-        const float *qr = q + ((size_t)b * n_heads + h0 + min(g, rows - 1)) * d;
+        const float *qr = q + ((size_t)b * n_heads + h0 + min(qrow, rows - 1)) * d;
         float qv[4][8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -180,12 +189,18 @@ __device__ __forceinline__ void decode_attention_mma_body(
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr) {
                     uint32_t e0[3], e1[3];
-                    const float x0 = g < rows ? v[4 * half + 2 * pr] * scale : 0.f;
-                    const float x1 = g < rows ? v[4 * half + 2 * pr + 1] * scale : 0.f;
+                    const float x0 = qrow < rows ? v[4 * half + 2 * pr] * scale : 0.f;
+                    const float x1 = qrow < rows ? v[4 * half + 2 * pr + 1] * scale : 0.f;
                     split3(x0, e0[0], e0[1], e0[2]);
                     split3(x1, e1[0], e1[1], e1[2]);
+                    if (kPacked) {
+                        qa[0][2 * i + half][pr] = upper ? (e0[1] | (e1[1] << 16)) : (e0[0] | (e1[0] << 16));
+                        qa[1][2 * i + half][pr] = upper ? 0u : (e0[2] | (e1[2] << 16));
+                    } else {
 #pragma unroll
-                    for (int term = 0; term < 3; ++term) qa[term][2 * i + half][pr] = e0[term] | (e1[term] << 16);
+                        for (int term = 0; term < kTerms; ++term)
+                            qa[term][2 * i + half][pr] = e0[term] | (e1[term] << 16);
+                    }
                 }
         }
     }
@@ -270,10 +285,14 @@ __device__ __forceinline__ void decode_attention_mma_body(
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int term = 0; term < 3; ++term) {
+                for (int term = 0; term < kTerms; ++term) {
                     mma_bf16_top(s[nt], qa[term][2 * i][0], qa[term][2 * i][1], kw[i].x, kw[i].y);
                     mma_bf16_top(s[nt], qa[term][2 * i + 1][0], qa[term][2 * i + 1][1], kw[i].z, kw[i].w);
                 }
+            if (kPacked) {  // hi + lo sums (rows 0-3) and mid sums (rows 4-7) of the same head
+                s[nt][0] += __shfl_xor_sync(0xffffffffu, s[nt][0], 16);
+                s[nt][1] += __shfl_xor_sync(0xffffffffu, s[nt][1], 16);
+            }
         }
         // ---- online softmax over the 16 keys (row g holds columns 2t, 2t+1 of each tile)
         float mx = -INFINITY;
@@ -299,14 +318,19 @@ __device__ __forceinline__ void decode_attention_mma_body(
             }
         l = l * alpha + psum;
         m = m_new;
-        uint32_t pa[3][2];
+        uint32_t pa[kTerms][2];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
             uint32_t e0[3], e1[3];
             split3(p[nt][0], e0[0], e0[1], e0[2]);
             split3(p[nt][1], e1[0], e1[1], e1[2]);
+            if (kPacked) {
+                pa[0][nt] = upper ? (e0[1] | (e1[1] << 16)) : (e0[0] | (e1[0] << 16));
+                pa[1][nt] = upper ? 0u : (e0[2] | (e1[2] << 16));
+            } else {
 #pragma unroll
-            for (int term = 0; term < 3; ++term) pa[term][nt] = e0[term] | (e1[term] << 16);
+                for (int term = 0; term < kTerms; ++term) pa[term][nt] = e0[term] | (e1[term] << 16);
+            }
         }
 #pragma unroll
         for (int nt = 0; nt < 16; ++nt) {
@@ -332,7 +356,7 @@ __device__ __forceinline__ void decode_attention_mma_body(
                 const uint32_t b0 = __byte_perm(w0, w1, sel), b1 = __byte_perm(w2, w3, sel);
                 float acc[4] = {o[8 * h + jj][0], o[8 * h + jj][1], 0.f, 0.f};
 #pragma unroll
-                for (int term = 0; term < 3; ++term) mma_bf16_top(acc, pa[term][0], pa[term][1], b0, b1);
+                for (int term = 0; term < kTerms; ++term) mma_bf16_top(acc, pa[term][0], pa[term][1], b0, b1);
                 o[8 * h + jj][0] = acc[0];
                 o[8 * h + jj][1] = acc[1];
             }
@@ -341,13 +365,20 @@ __device__ __forceinline__ void decode_attention_mma_body(
     }
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (kPacked) {  // a head's output: its hi + lo share (rows 0-3) plus its mid share (rows 4-7)
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt) {
+            o[nt][0] += __shfl_xor_sync(0xffffffffu, o[nt][0], 16);
+            o[nt][1] += __shfl_xor_sync(0xffffffffu, o[nt][1], 16);
+        }
+    }
 
     // ---- combine the warps of the block (each warp's arrays lie in its own, now idle, ring)
-    if (t == 0) {
+    if (t == 0 && !upper) {
         sm.m(warp)[g] = m;
         sm.l(warp)[g] = l;
     }
-    {
+    if (!upper) {
         float *mine = sm.o(warp) + g * d;
 #pragma unroll
         for (int nt = 0; nt < 16; ++nt)
