@@ -77,6 +77,15 @@ __device__ __forceinline__ void mma_bf16_top(float (&c)[4], uint32_t a0, uint32_
         : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void mma_bf16_full(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                              uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 // x = hi + mid + lo with each term a bfloat16 (to 2^-25 of x)
 __device__ __forceinline__ void split3(float x, uint32_t &hi, uint32_t &mid, uint32_t &lo) {
     hi = float_to_bf16_bits(x);
@@ -133,8 +142,10 @@ struct FreshKey {
 // the rate of the INT8 one on this part and the 96 MMAs of a 16-key step, not the cache
 // bytes, bound the kernel.  Only 4 of the MMA's 16 A rows were in use, so two of the three
 // terms share one MMA: rows 0-3 carry the hi terms of heads 0-3, rows 4-7 their mid terms,
-// and a second MMA carries the lo terms in rows 0-3 (64 MMAs per step).  Lane groups g and
-// g + 4 then hold the two halves of a head's sums; one shuffle per value adds them.
+// and the lo terms ride in rows 8-11 of the same MMA for the scores (whose accumulator is
+// a temporary) and in rows 0-3 of a second MMA for the outputs (whose accumulators stay in
+// registers over the whole loop: two per tile, not four): 48 MMAs per step.  Lane groups g
+// and g + 4 then hold the parts of a head's sums; one shuffle per value adds them.
 template <bool kRope, int kBufs = kMmaDecBufs, bool kPacked = false>
 __device__ __forceinline__ void decode_attention_mma_body(
     const SubBlock sb, const DecAttnSmem sm, const float *__restrict__ q,
@@ -284,14 +295,23 @@ __device__ __forceinline__ void decode_attention_mma_body(
             s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
             for (int i = 0; i < 4; ++i)
+                if (kPacked) {
+                    // (qa[1], the lo terms of lanes g < 4 and zero elsewhere, as rows g + 8)
+                    mma_bf16_full(s[nt], qa[0][2 * i][0], qa[1][2 * i][0], qa[0][2 * i][1], qa[1][2 * i][1], kw[i].x,
+                                  kw[i].y);
+                    mma_bf16_full(s[nt], qa[0][2 * i + 1][0], qa[1][2 * i + 1][0], qa[0][2 * i + 1][1],
+                                  qa[1][2 * i + 1][1], kw[i].z, kw[i].w);
+                } else {
 #pragma unroll
-                for (int term = 0; term < kTerms; ++term) {
-                    mma_bf16_top(s[nt], qa[term][2 * i][0], qa[term][2 * i][1], kw[i].x, kw[i].y);
-                    mma_bf16_top(s[nt], qa[term][2 * i + 1][0], qa[term][2 * i + 1][1], kw[i].z, kw[i].w);
+                    for (int term = 0; term < kTerms; ++term) {
+                        mma_bf16_top(s[nt], qa[term][2 * i][0], qa[term][2 * i][1], kw[i].x, kw[i].y);
+                        mma_bf16_top(s[nt], qa[term][2 * i + 1][0], qa[term][2 * i + 1][1], kw[i].z, kw[i].w);
+                    }
                 }
-            if (kPacked) {  // hi + lo sums (rows 0-3) and mid sums (rows 4-7) of the same head
-                s[nt][0] += __shfl_xor_sync(0xffffffffu, s[nt][0], 16);
-                s[nt][1] += __shfl_xor_sync(0xffffffffu, s[nt][1], 16);
+            if (kPacked) {  // hi sums (rows 0-3), lo sums (rows 8-11) and mid sums (rows 4-7) of the same head
+                const float part0 = s[nt][0] + s[nt][2], part1 = s[nt][1] + s[nt][3];
+                s[nt][0] = part0 + __shfl_xor_sync(0xffffffffu, part0, 16);
+                s[nt][1] = part1 + __shfl_xor_sync(0xffffffffu, part1, 16);
             }
         }
         // ---- online softmax over the 16 keys (row g holds columns 2t, 2t+1 of each tile)
