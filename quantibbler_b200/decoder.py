@@ -236,13 +236,23 @@ class Decoder:
                         for _ in range(cfg.n_layers)]
         self.cache_v = [torch.zeros(B, self.kv_loc, cfg.max_seq, hd, dtype=kv_t, device=dev)
                         for _ in range(cfg.n_layers)]
-        # enough blocks of 128 threads to fill the SMs (about eight per SM), but chunks of at
-        # least ~128 keys
+        # Key splits: about 256 blocks of 128 threads per launch (two per SM is what stays
+        # resident) in chunks of at least ~64 keys.  Measured per step on the Llama-3-8B
+        # shape at 2048 keys, by batch (best split count: ms against the former "eight blocks
+        # per SM" rule): 4 (8: 4.18 against 4.64 at 32), 8 (4: 6.13 against 6.56 at 19), 12
+        # (4: 7.57 against 7.78 at 13), 16 (2: 5.95 against 6.25 at 10), 32 (2: 7.14 against
+        # 7.32 at 5), 64 (3: 9.75, 2: 9.81); more splits mean more partial results for the
+        # combine and more blocks that each stage a query tile for few keys.
         # (a step of one or two sequences is a chain of latencies, not a stream: sixteen splits
         # leave the last block of a head group half as many partial results to combine as
-        # thirty-two, measured 3.85 against 3.95 ms per step on the Llama-3-8B shape)
-        want = -(-8 * 148 // max(1, B * self.kv_loc))
-        most = 16 if B * self.kv_loc <= 16 else 32
+        # thirty-two, measured 3.85 against 3.95 ms per step)
+        per_split = max(1, B * self.kv_loc)
+        want = -(-256 // per_split)
+        if per_split >= 512:
+            want = 3
+        elif per_split >= 128:
+            want = max(2, want)
+        most = 16 if per_split <= 16 else 32
         self.n_splits = cfg.n_splits or max(1, min(most, want, max(1, cfg.max_seq // 64)))
         # (the one-launch form is the tensor-core attention; a context switched to the scalar
         # kernel keeps the separate launches)
