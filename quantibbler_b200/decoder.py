@@ -42,7 +42,10 @@ class DecoderConfig:
     max_seq: int = 4096
     max_batch: int = 1
     n_splits: int = 0              # key splits of the decode attention (0 = choose)
-    gemm_min_batch: int = 16       # bfloat16 serving: batches this large take the tensor-core GEMM
+    # bfloat16 serving: batches this large take the tensor-core GEMM (measured per step on the
+    # Llama-3-8B shape, GEMM against the per-token GEMV forms: batch 5 5.69 / 4.95 ms, 6 5.86 /
+    # 5.81, 7 6.03 / about 6.0, 8 5.38 / 6.14, 10 5.69 / 6.74, 12 5.73 / 7.47, 15 6.08 / 11.98)
+    gemm_min_batch: int = 8
     fused_allreduce: bool = True   # tensor parallel: the all-reduce happens inside the norm, over peer memory
     fused_allreduce_max_bytes: int = 1 << 20   # ... while a rank pushes at most this much per all-reduce
     # Batches up to this size build the digit tables of the linears' inputs where each vector is
