@@ -44,8 +44,8 @@ class DecoderConfig:
     n_splits: int = 0              # key splits of the decode attention (0 = choose)
     # bfloat16 serving: batches this large take the tensor-core GEMM (measured per step on the
     # Llama-3-8B shape, GEMM against the per-token GEMV forms: batch 5 5.69 / 4.95 ms, 6 5.86 /
-    # 5.81, 7 6.03 / about 6.0, 8 5.38 / 6.14, 10 5.69 / 6.74, 12 5.73 / 7.47, 15 6.08 / 11.98)
-    gemm_min_batch: int = 8
+    # 5.81, 7 6.03 / 6.49, 8 5.38 / 6.14, 10 5.69 / 6.74, 12 5.73 / 7.47, 15 6.08 / 11.98)
+    gemm_min_batch: int = 7
     fused_allreduce: bool = True   # tensor parallel: the all-reduce happens inside the norm, over peer memory
     fused_allreduce_max_bytes: int = 1 << 20   # ... while a rank pushes at most this much per all-reduce
     # Batches up to this size build the digit tables of the linears' inputs where each vector is
@@ -76,7 +76,11 @@ class DecoderConfig:
     # themselves (every block of the first stage forms the norm of the 4096-entry stream, which
     # costs it about a microsecond) instead of a norm launch of its own, which costs the step
     # about ten: two kernel boundaries less per block, the same bits.
-    norm_fused_max_batch: int = 4
+    # (measured per step, norm inside against a norm launch: batch 5 4.61 / 4.94 ms, batch 6
+    # 5.47 / 5.74; from batch 7 the tensor-core GEMM takes over.)  Under tensor parallelism,
+    # where these plans also carry the all-reduce, the limit is norm_fused_max_batch_tp.
+    norm_fused_max_batch: int = 6
+    norm_fused_max_batch_tp: int = 4
     prefill_min_tokens: int = 16   # generate(): prompts this long go through the trunk in one pass
     prefill_chunk: int = 2048      # ... in pieces of at most this many positions
 
@@ -336,7 +340,8 @@ class Decoder:
                 plan["up"] = LayerPlan(ctx, inst(["up"], self.h, [self.u]))
             # (under tensor parallelism the norms are also where the row-parallel outputs are summed
             # over the ranks: with the all-reduce over peer memory the plans do that themselves)
-            if (B <= cfg.norm_fused_max_batch and (tp_size == 1 or (self.fused_ar and d <= 4096))
+            if ((B <= cfg.norm_fused_max_batch if tp_size == 1
+                 else B <= cfg.norm_fused_max_batch_tp and self.fused_ar and d <= 4096)
                     and not fed and not gemm
                     and cfg.serving in ("float32", "bfloat16") and "qkv" in plan and "gu" in plan):
                 # the first norm of a block reads the stream from x and leaves it in x2, the second

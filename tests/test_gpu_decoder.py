@@ -484,21 +484,22 @@ def test_one_launch_attention_reproduces_the_three_launches(gpu_ctx, serving):
         assert torch_equal(one.cache_k[li], three.cache_k[li]) and torch_equal(one.cache_v[li], three.cache_v[li])
 
 
+@pytest.mark.parametrize("batch", [2, 6])
 @pytest.mark.parametrize("serving", ["float32", "bfloat16"])
-def test_norm_and_swiglu_inside_the_linears_reproduce_the_separate_launches(gpu_ctx, serving):
+def test_norm_and_swiglu_inside_the_linears_reproduce_the_separate_launches(gpu_ctx, serving, batch):
     """At small batches q,k,v and gate,up form the RMSNorm of the residual stream themselves
     (every block of their first stage, with the norm kernel's thread count and summation
     order; one block also writes the updated stream) and the down projection reads gate and up
     through the SwiGLU: three launches less per block.  Logits and residual stream must be the
     bits of the separate norm and SwiGLU kernels."""
-    base = dict(serving=serving, max_batch=2)
+    base = dict(serving=serving, max_batch=batch)
     weights = random_model(step_cfg(**base), STEP_RANKS, seed=79)
     apart = Decoder(gpu_ctx, step_cfg(norm_fused_max_batch=0, gated_down_max_batch=0, **base), weights)
     fused = Decoder(gpu_ctx, step_cfg(**base), weights)
     assert "qkv_normed" in fused.plans[0] and "gu_normed" in fused.plans[0] and fused.gated_down
     assert "qkv_normed" not in apart.plans[0] and not apart.gated_down
     for dec in (apart, fused):
-        dec.start([3, 77], [0, 2])
+        dec.start([3, 77, 5, 120, 9, 64][:batch], [0, 2, 1, 0, 3, 2][:batch])
     for step in range(6):
         for dec in (apart, fused):
             dec.step()

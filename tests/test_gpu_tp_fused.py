@@ -81,7 +81,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
         base = dict(n_layers=3, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16, d_ff=128,
                     vocab=128, max_seq=32, max_batch=2, kv_dtype="float32", serving=serving)
         for inside in (True, False):
-            cfg = DecoderConfig(norm_fused_max_batch=4 if inside else 0, **base)
+            cfg = DecoderConfig(norm_fused_max_batch_tp=4 if inside else 0, **base)
             dec = Decoder(ctx, cfg, random_model(cfg, RANKS, seed=12), tp_rank=rank, tp_size=world,
                           group=dist.group.WORLD)
             assert dec.fused_ar and dec.allreduce_in_plans == inside
