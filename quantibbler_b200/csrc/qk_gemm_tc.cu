@@ -522,13 +522,16 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
 
 // z_p = bf16(s2_p * x) (float32 product, one rounding), zero padded to the pitch, for each of
 // the problems of a launch (grid.y).  One thread makes eight consecutive outputs (one
-// 16-byte store).
+// 16-byte store).  With `up` given, x is the SwiGLU of the two inputs, silu(x) * up, formed
+// here with swiglu_kernel's expression instead of being written and read back as an
+// activation (engine/mod.rs:1289-1297).
 struct ScaleArgs {
     const float *s2[kMaxProblems];
     uint16_t *z[kMaxProblems];
 };
-__global__ void scale_to_bf16_kernel(const float *__restrict__ x, ScaleArgs a, uint32_t n_tokens,
-                                     uint32_t din, uint32_t pitch, int vec) {
+__device__ __forceinline__ float gated_value(float g, float u) { return g * u / (1.0f + expf(-g)); }
+__global__ void scale_to_bf16_kernel(const float *__restrict__ x, const float *__restrict__ up, ScaleArgs a,
+                                     uint32_t n_tokens, uint32_t din, uint32_t pitch, int vec) {
     qk::pdl_launch();  // the kernel after this one may begin its prologue
     const float *__restrict__ s2 = a.s2[blockIdx.y];
     uint16_t *__restrict__ z = a.z[blockIdx.y];
@@ -548,13 +551,26 @@ __global__ void scale_to_bf16_kernel(const float *__restrict__ x, ScaleArgs a, u
     const float *xr = x + (size_t)t * din;
     float v[8];
     if (wide) {
-        const float4 a0 = *reinterpret_cast<const float4 *>(xr + k);
-        const float4 b0 = *reinterpret_cast<const float4 *>(xr + k + 4);
+        float4 a0 = *reinterpret_cast<const float4 *>(xr + k);
+        float4 b0 = *reinterpret_cast<const float4 *>(xr + k + 4);
+        if (up) {
+            const float *ur = up + (size_t)t * din;
+            const float4 e0 = *reinterpret_cast<const float4 *>(ur + k);
+            const float4 f0 = *reinterpret_cast<const float4 *>(ur + k + 4);
+            a0 = make_float4(gated_value(a0.x, e0.x), gated_value(a0.y, e0.y), gated_value(a0.z, e0.z),
+                             gated_value(a0.w, e0.w));
+            b0 = make_float4(gated_value(b0.x, f0.x), gated_value(b0.y, f0.y), gated_value(b0.z, f0.z),
+                             gated_value(b0.w, f0.w));
+        }
         v[0] = c0.x * a0.x; v[1] = c0.y * a0.y; v[2] = c0.z * a0.z; v[3] = c0.w * a0.w;
         v[4] = d0.x * b0.x; v[5] = d0.y * b0.y; v[6] = d0.z * b0.z; v[7] = d0.w * b0.w;
     } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = k + i < din ? s2[k + i] * xr[k + i] : 0.f;
+        for (int i = 0; i < 8; ++i) {
+            float xv = k + i < din ? xr[k + i] : 0.f;
+            if (up && k + i < din) xv = gated_value(xv, up[(size_t)t * din + k + i]);
+            v[i] = k + i < din ? s2[k + i] * xv : 0.f;
+        }
     }
     uint32_t w[4];
 #pragma unroll
@@ -608,10 +624,8 @@ uint32_t pick_bn(size_t tokens) {
 
 }  // namespace
 
-extern "C" {
-
-qk_status qk_layers_apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers,
-                                  const float *x_dev, size_t n_tokens, float *const *y_devs) {
+static qk_status apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers, const float *x_dev,
+                               const float *up_dev, size_t n_tokens, float *const *y_devs) {
     if (n_layers == 0 || n_layers > (size_t)kMaxProblems)
         return qk::fail(QK_ERR_VALUE, "between 1 and %d layers per call, got %zu", kMaxProblems, n_layers);
     if (!layers || !y_devs) return qk::fail(QK_ERR_VALUE, "qk_layers_apply_prefill: null array");
@@ -655,11 +669,11 @@ qk_status qk_layers_apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, si
         sa.s2[i] = layers[i]->s2;
         sa.z[i] = (uint16_t *)(base + i * z_bytes);
     }
-    const int vec = ((uintptr_t)x_dev & 15) == 0 && (din & 3) == 0;
+    const int vec = ((uintptr_t)x_dev & 15) == 0 && ((uintptr_t)up_dev & 15) == 0 && (din & 3) == 0;
     const size_t total = n_tokens * (kp1 / 8);
     (void)qk::launch_pdl(c->pdl, scale_to_bf16_kernel,
                          dim3((unsigned)qk::ceil_div(total, 256), (unsigned)n_layers), dim3(256), 0, c->stream, x_dev,
-                         sa, (uint32_t)n_tokens, (uint32_t)din, (uint32_t)kp1, vec);
+                         up_dev, sa, (uint32_t)n_tokens, (uint32_t)din, (uint32_t)kp1, vec);
     QK_CUDA(cudaGetLastError());
     c->launches++;
     QK_CUDA(cudaFuncSetAttribute(factorized_gemm_tc_kernel<false>,
@@ -718,6 +732,21 @@ qk_status qk_layers_apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, si
     c->launches++;
     c->err_armed = true;
     return QK_OK;
+}
+
+extern "C" {
+
+qk_status qk_layers_apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers,
+                                  const float *x_dev, size_t n_tokens, float *const *y_devs) {
+    return apply_prefill(ctx, layers, n_layers, x_dev, nullptr, n_tokens, y_devs);
+}
+
+qk_status qk_layers_apply_prefill_gated(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers,
+                                        const float *gate_dev, const float *up_dev, size_t n_tokens,
+                                        float *const *y_devs) {
+    if (!gate_dev || !up_dev)
+        return qk::fail(QK_ERR_VALUE, "qk_layers_apply_prefill_gated: gate and up must be given");
+    return apply_prefill(ctx, layers, n_layers, gate_dev, up_dev, n_tokens, y_devs);
 }
 
 qk_status qk_layer_apply_prefill(qk_ctx *ctx, const qk_layer *layer, const float *x_dev,

@@ -21,7 +21,8 @@ import numpy as np
 
 from . import _lib, tp
 from ._lib import QK_BF16, QK_F32, KernelError, check
-from .gpu import DecodeStep, GpuContext, LayerPlan, PackedLayer, apply_prefill_many, make_feed
+from .gpu import (DecodeStep, GpuContext, LayerPlan, PackedLayer, apply_prefill_many,
+                  apply_prefill_many_gated, make_feed)
 
 LINEARS = ("q", "k", "v", "o", "gate", "up", "down")
 
@@ -567,9 +568,13 @@ class Decoder:
             if feeds:   # (the fed down plan needs no activation vector, only its digit table)
                 check(lib.qk_swiglu_feed(c, _p(self.g), _p(self.u), B, self.ff_loc, self.serving_tag,
                                          ctypes.byref(feeds["down"])))
-            elif not self.gated_down:
+            elif not self.gated_down and not self.use_gemm:
                 check(lib.qk_swiglu(c, _p(self.g), _p(self.u), B * self.ff_loc, _p(self.a)))
-            self._linears(li, ["down"], self.a, [self.delta_mlp])
+            if self.use_gemm:   # (the SwiGLU inside the GEMM's scaling kernel)
+                apply_prefill_many_gated([self.layers[li]["down"]], self.g.data_ptr(), self.u.data_ptr(), B,
+                                         [self.delta_mlp.data_ptr()])
+            else:
+                self._linears(li, ["down"], self.a, [self.delta_mlp])
             self._all_reduce(self.delta_mlp)
             pending = 1
         self._norm(pending, self.final_norm, None, xa, xb)
@@ -672,8 +677,12 @@ class Decoder:
                     check(lib.qk_rmsnorm(c, _p(pf["x"]), _p(pf["delta"]), _p(post_w), T, d, cfg.rms_eps,
                                          self.serving_tag, _p(pf["x"]), _p(pf["h"])))
                     self._prefill_linears(li, ["gate", "up"], pf["h"], [pf["g"], pf["u"]], T)
-                    check(lib.qk_swiglu(c, _p(pf["g"]), _p(pf["u"]), T * self.ff_loc, _p(pf["a"])))
-                    self._prefill_linears(li, ["down"], pf["a"], [pf["delta"]], T)
+                    if cfg.serving == "bfloat16" and T >= cfg.gemm_min_batch:
+                        apply_prefill_many_gated([self.layers[li]["down"]], pf["g"].data_ptr(), pf["u"].data_ptr(),
+                                                 T, [pf["delta"].data_ptr()])
+                    else:
+                        check(lib.qk_swiglu(c, _p(pf["g"]), _p(pf["u"]), T * self.ff_loc, _p(pf["a"])))
+                        self._prefill_linears(li, ["down"], pf["a"], [pf["delta"]], T)
                     if self.tp_size > 1:
                         torch.distributed.all_reduce(pf["delta"][:T], group=self.group)
                     pending = _p(pf["delta"])

@@ -389,6 +389,16 @@ def apply_prefill_many(layers, x_ptr: int, n_tokens: int, y_ptrs) -> None:
                                              int(n_tokens), outs))
 
 
+def apply_prefill_many_gated(layers, gate_ptr: int, up_ptr: int, n_tokens: int, y_ptrs) -> None:
+    """``apply_prefill_many`` on ``silu(gate) * up`` (the down projection behind the SwiGLU),
+    the activation formed inside the GEMM's scaling kernel.  Asynchronous."""
+    n = len(layers)
+    handles = (ctypes.c_void_p * n)(*[layer._h for layer in layers])
+    outs = (ctypes.c_void_p * n)(*[ctypes.c_void_p(p) for p in y_ptrs])
+    check(_lib.lib().qk_layers_apply_prefill_gated(layers[0].ctx.handle, handles, n, ctypes.c_void_p(gate_ptr),
+                                                   ctypes.c_void_p(up_ptr), int(n_tokens), outs))
+
+
 def apply_noalloc(layer: PackedLayer, x_ptr: int, y_ptr: int) -> None:
     """One token through ``layer`` with the library allocating nothing: for hosts that own
     all device memory themselves (for example a server whose KV cache took what was left

@@ -110,3 +110,39 @@ def test_several_layers_in_one_call(gpu_ctx):
         la = PackedLayer(gpu_ctx, a["ub_rows"], a["vb_t_rows"], 32, 64, 16, a["s1"], a["s2"], None, serving="bfloat16")
         lb = PackedLayer(gpu_ctx, b["ub_rows"], b["vb_t_rows"], 32, 128, 16, b["s1"], b["s2"], None, serving="bfloat16")
         apply_prefill_many([la, lb], 0, 4, [0, 0])
+
+
+@pytest.mark.parametrize("shape", [(96, 320, 40, 150), (200, 333, 64, 37), (256, 1024, 128, 9)])
+def test_gated_prefill_equals_swiglu_then_prefill(gpu_ctx, shape):
+    """The down projection behind the SwiGLU (engine/mod.rs:1289-1297): the activation formed
+    inside the GEMM's scaling kernel must give the bits of the SwiGLU kernel followed by the
+    plain call (the same expression, the same roundings), for widths on and off the vector
+    path."""
+    import torch
+    from quantibbler_b200 import _lib
+    from quantibbler_b200._lib import check
+    from quantibbler_b200.gpu import apply_prefill_many, apply_prefill_many_gated
+    dout, din, r, n_tokens = shape
+    L = make_layer(dout, din, r, seed=din + r, with_bias=True)
+    layer = PackedLayer(gpu_ctx, L["ub_rows"], L["vb_t_rows"], dout, din, r, L["s1"], L["s2"], L["bias"],
+                        serving="bfloat16")
+    gen = torch.Generator(device="cuda").manual_seed(din)
+    gate = torch.randn(n_tokens, din, device="cuda", generator=gen) * 2
+    up = torch.randn(n_tokens, din, device="cuda", generator=gen)
+    act = torch.zeros_like(gate)
+    apart = torch.zeros(n_tokens, dout, device="cuda")
+    fused = torch.full((n_tokens, dout), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    check(_lib.lib().qk_swiglu(gpu_ctx.handle, gate.data_ptr(), up.data_ptr(), n_tokens * din, act.data_ptr()))
+    apply_prefill_many([layer], act.data_ptr(), n_tokens, [apart.data_ptr()])
+    apply_prefill_many_gated([layer], gate.data_ptr(), up.data_ptr(), n_tokens, [fused.data_ptr()])
+    gpu_ctx.synchronize()
+    assert np.array_equal(fused.cpu().numpy(), apart.cpu().numpy())
+    # and against the restatement on one token
+    a0 = act[0].cpu().numpy()
+    want = oracle.layer_apply(L["ub_rows"], L["vb_t_rows"], dout, din, r, L["s1"], L["s2"], L["bias"], a0,
+                              serving="bfloat16")
+    assert np.abs(fused[0].cpu().numpy() - want).max() <= 2e-2 * np.abs(want).max()
+    with pytest.raises(ValueError, match="gate and up"):
+        apply_prefill_many_gated([layer], gate.data_ptr(), 0, n_tokens, [fused.data_ptr()])
+    layer.close()
