@@ -100,6 +100,7 @@ struct Problem {
     uint32_t row_tiles;    // tile t of the problem covers row tile t % row_tiles, token tile t / row_tiles
     uint32_t unit_begin;   // the problem's first unit; a tile is k_chunks consecutive units
 };
+constexpr int kMaxCtas = 192;
 struct GemmArgs {
     Problem p[kMaxProblems];
     uint32_t n_problems;
@@ -110,12 +111,10 @@ struct GemmArgs {
     float *partials;       // [CTAs][256][128] float32 accumulators of split tiles
     uint32_t *flags;       // [CTAs] flags[i] != 0: CTA i's partial is in place (its one reader clears it)
     uint32_t wait_limit;   // polls before a wait gives up
+    // CTA i works on units [cta_begin[i], cta_begin[i + 1]) (plan_ctas, on the host)
+    uint32_t cta_begin[kMaxCtas + 1];
 };
 
-// CTA i of G works on units [i * units / G, (i + 1) * units / G).
-__device__ __forceinline__ uint32_t unit_begin(uint32_t i, uint32_t units, uint32_t ctas) {
-    return (uint32_t)((uint64_t)i * units / ctas);
-}
 
 // Where unit u lies: which problem, which of its tiles, which k-chunk of the tile.
 struct UnitPos {
@@ -173,8 +172,8 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
     // rest as THEIR first segments, which they computed at the very start of the kernel, so
     // by now those partials are in place; they are added in CTA order (a fixed order, so the
     // sum is reproducible) before the epilogue.  The wait on the flags is bounded all the same.
-    const uint32_t u_begin = unit_begin(blockIdx.x, g.units, gridDim.x);
-    const uint32_t u_end = unit_begin(blockIdx.x + 1, g.units, gridDim.x);
+    const uint32_t u_begin = g.cta_begin[blockIdx.x];
+    const uint32_t u_end = g.cta_begin[blockIdx.x + 1];
     const uint32_t total_chunks = u_end - u_begin;
     // What depends on no other kernel is fetched before the dependency wait: the weight bits
     // of each producer's first two chunks (a first touch of those rows: one DRAM latency that
@@ -358,7 +357,7 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
             uint32_t last = blockIdx.x + 1;
             if (kc0 == 0 && len < pr.k_chunks) {
                 const uint32_t hi = at.tile_begin + pr.k_chunks;
-                while (last < gridDim.x && unit_begin(last, g.units, gridDim.x) < hi) ++last;
+                while (last < gridDim.x && g.cta_begin[last] < hi) ++last;
             }
             // this CTA's own share of the tile first: once its accumulator is complete, every
             // MMA of the CTA so far has read its operands
@@ -618,6 +617,43 @@ qk_status encode_activation_map(const uint16_t *base, size_t rows, size_t pitch,
 // Tokens per tile.  The MMA warp's wait-issue-commit loop takes about 530 cycles per chunk
 // whatever N is, and N = 256 is 512 cycles of tensor-core work, so a narrower tile is never
 // faster per tile; it only helps when there are fewer tokens than that.
+// Which units each CTA takes.  Many tiles (a prompt): the units are dealt out evenly, a CTA's
+// run crossing tile borders wherever it falls.  Few tiles (a decode batch: at most half as
+// many tiles as CTAs): every tile goes to a whole number of CTAs in equal parts, so that no
+// CTA has to publish the tail of one tile before it can begin the head of the next - that
+// serial step was on the critical path of the launch - and a tile's sharers finish at the same
+// time.  A tile is shared by at most seven CTAs (the six partials the head CTA can stage)
+// unless that would make a CTA's run longer than sixteen k-chunks.  Returns the grid size.
+unsigned plan_ctas(GemmArgs &g, size_t units, const size_t *tiles, size_t n_problems, unsigned sm_count) {
+    const size_t most = std::min<size_t>(sm_count, kMaxCtas);
+    const size_t ctas = std::max<size_t>(1, std::min<size_t>(most, units / 8));
+    size_t tiles_total = 0;
+    for (size_t p = 0; p < n_problems; ++p) tiles_total += tiles[p];
+    size_t n = 0;
+    bool aligned = tiles_total * 2 <= ctas;
+    if (aligned) {
+        for (size_t p = 0; p < n_problems && aligned; ++p) {
+            const size_t k = g.p[p].k_chunks;
+            size_t share = std::max<size_t>(1, std::min<size_t>(k, k * ctas / units));
+            if (share > 7 && qk::ceil_div(k, 7) <= 16) share = 7;
+            for (size_t t = 0; t < tiles[p] && aligned; ++t)
+                for (size_t j = 0; j < share; ++j) {
+                    if (n >= most) {
+                        aligned = false;
+                        break;
+                    }
+                    g.cta_begin[n++] = (uint32_t)(g.p[p].unit_begin + t * k + j * k / share);
+                }
+        }
+    }
+    if (!aligned) {
+        n = ctas;
+        for (size_t i = 0; i < n; ++i) g.cta_begin[i] = (uint32_t)((uint64_t)i * units / n);
+    }
+    g.cta_begin[n] = (uint32_t)units;
+    return (unsigned)n;
+}
+
 uint32_t pick_bn(size_t tokens) {
     return tokens >= (size_t)kBNMax ? (uint32_t)kBNMax : (uint32_t)(qk::ceil_div(tokens, 16) * 16);
 }
@@ -685,7 +721,7 @@ static qk_status apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, size_
     uint32_t *flags = (uint32_t *)c->d_err.ptr + 64;  // after the error word's 256 bytes
     GemmArgs g1{}, g2{};
     CUtensorMap maps1[kMaxProblems], maps2[kMaxProblems];
-    size_t units1 = 0, units2 = 0;
+    size_t units1 = 0, units2 = 0, tiles1[kMaxProblems] = {}, tiles2[kMaxProblems] = {};
     for (size_t i = 0; i < n_layers; ++i) {
         const qk_layer *L = layers[i];
         uint16_t *z = (uint16_t *)(base + i * z_bytes), *t = (uint16_t *)(base + t_off[i]);
@@ -696,6 +732,8 @@ static qk_status apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, size_
                           (uint32_t)L->vbt_stride, (uint32_t)kp2[i], (uint32_t)rows1, (uint32_t)units1};
         g2.p[i] = Problem{L->ub, y_devs[i], L->s1, L->bias, (uint32_t)L->dout, (uint32_t)(kp2[i] / kBK),
                           (uint32_t)L->ub_stride, (uint32_t)L->dout, (uint32_t)rows2, (uint32_t)units2};
+        tiles1[i] = rows1 * tok_tiles;
+        tiles2[i] = rows2 * tok_tiles;
         units1 += rows1 * tok_tiles * (kp1 / kBK);
         units2 += rows2 * tok_tiles * (kp2[i] / kBK);
     }
@@ -705,11 +743,9 @@ static qk_status apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, size_
     }
     if (units1 >= (1ull << 32) || units2 >= (1ull << 32))
         return qk::fail(QK_ERR_VALUE, "the work of one call must stay below 2^32 tile-chunks");
-    // every CTA gets the same number of (tile, k-chunk) units, at least eight of them
-    const auto ctas_for = [&](size_t units) {
-        return (unsigned)std::max<size_t>(1, std::min<size_t>((size_t)c->sm_count, units / 8));
-    };
-    const unsigned grid1 = ctas_for(units1), grid2 = ctas_for(units2);
+    // (tile, k-chunk) units per CTA: about eight or more
+    const unsigned grid1 = plan_ctas(g1, units1, tiles1, n_layers, (unsigned)c->sm_count);
+    const unsigned grid2 = plan_ctas(g2, units2, tiles2, n_layers, (unsigned)c->sm_count);
     const size_t slot_bytes = (size_t)kBNMax * kBM * sizeof(float);
     if ((st = c->d_t.reserve((size_t)std::max(grid1, grid2) * slot_bytes)) != QK_OK) return st;
     float *partials = (float *)c->d_t.ptr;
