@@ -52,7 +52,22 @@ def test_directory_loads_with_the_declared_inventory_and_geometry():
     assert np.array_equal(blk["q_norm"], md.norm_weights[at + 128:at + 160])
     assert np.array_equal(blk["k_norm"], md.norm_weights[at + 160:at + 192])
     assert np.array_equal(w["final_norm"], md.norm_weights[-64:])
-    assert blk["q"]["ub_rows"].shape == (128, 1) and blk["q"]["vb_t_rows"].shape == (8, 8)
+    # a layer carries the container's bit streams (what the device separates into rows at upload);
+    # the row bitplanes are made on first use and are the repack of engine/mod.rs:258-289
+    q = blk["q"]
+    assert "ub_packed" in q and "vb_packed" in q and "ub_rows" not in q and "vb_t_rows" not in q
+    assert q["ub_rows"].shape == (128, 1) and q["vb_t_rows"].shape == (8, 8)
+    assert "ub_rows" in q and "vb_t_rows" in q
+    import oracle
+    assert np.array_equal(q["ub_rows"], oracle.container_to_rows(q["ub_packed"], q["dout"], q["r"]))
+    assert np.array_equal(q["vb_t_rows"],
+                          oracle.container_to_rows_transposed(q["vb_packed"], q["din"], q["r"]))
+    with pytest.raises(KeyError):
+        q["no_such_key"]
+    # a tensor-parallel shard holds rows only: the streams describe the whole layer
+    from quantibbler_b200 import tp
+    part = tp.shard_column_parallel(blk["k"], 1, 2)
+    assert "ub_packed" not in part and part["ub_rows"].shape[0] == blk["k"]["dout"] // 2
 
 
 def test_forward_restatement_reproduces_the_reference_goldens():
