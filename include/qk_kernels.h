@@ -273,7 +273,7 @@ qk_status qk_layer_apply_prefill(qk_ctx *ctx, const qk_layer *layer, const float
  * y_devs[i] [n_tokens, layers[i]->dout].  The layers must have the same din. */
 qk_status qk_layers_apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers,
                                   const float *x_dev, size_t n_tokens, float *const *y_devs);
-/* The same with the input formed on the way in: x = silu(gate) * up (engine/mod.rs:1289-1297,
+/* The same with the input formed on the way in: x = silu(gate) * up (engine/mod.rs:931-935,
  * the SwiGLU in front of the down projection), gate_dev and up_dev float32 [n_tokens x din].
  * Same values as qk_swiglu followed by qk_layers_apply_prefill, without the activation being
  * written and read back. */

@@ -523,7 +523,7 @@ factorized_gemm_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid
 // the problems of a launch (grid.y).  One thread makes eight consecutive outputs (one
 // 16-byte store).  With `up` given, x is the SwiGLU of the two inputs, silu(x) * up, formed
 // here with swiglu_kernel's expression instead of being written and read back as an
-// activation (engine/mod.rs:1289-1297).
+// activation (engine/mod.rs:931-935).
 struct ScaleArgs {
     const float *s2[kMaxProblems];
     uint16_t *z[kMaxProblems];

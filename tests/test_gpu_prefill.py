@@ -114,7 +114,7 @@ def test_several_layers_in_one_call(gpu_ctx):
 
 @pytest.mark.parametrize("shape", [(96, 320, 40, 150), (200, 333, 64, 37), (256, 1024, 128, 9)])
 def test_gated_prefill_equals_swiglu_then_prefill(gpu_ctx, shape):
-    """The down projection behind the SwiGLU (engine/mod.rs:1289-1297): the activation formed
+    """The down projection behind the SwiGLU (engine/mod.rs:931-935): the activation formed
     inside the GEMM's scaling kernel must give the bits of the SwiGLU kernel followed by the
     plain call (the same expression, the same roundings), for widths on and off the vector
     path."""
