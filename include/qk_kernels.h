@@ -280,6 +280,14 @@ qk_status qk_layers_apply_prefill(qk_ctx *ctx, const qk_layer *const *layers, si
 qk_status qk_layers_apply_prefill_gated(qk_ctx *ctx, const qk_layer *const *layers, size_t n_layers,
                                         const float *gate_dev, const float *up_dev, size_t n_tokens,
                                         float *const *y_devs);
+/* How the prefill calls above deal their work out (host arithmetic only; no device is touched):
+ * problem p has tiles[p] output tiles of k_chunks[p] 64-wide k-chunks each, the units of
+ * work are (tile, k-chunk) pairs in problem-major, tile-major order, and CTA i of *n_ctas
+ * takes units [cta_begin[i], cta_begin[i + 1]).  With many tiles the units are dealt out
+ * evenly; with at most half as many tiles as CTAs every tile goes to a whole number of CTAs
+ * in equal parts.  cta_begin needs *n_ctas + 1 <= min(sm_count, 192) + 1 entries. */
+qk_status qk_prefill_work_split(size_t n_problems, const size_t *tiles, const size_t *k_chunks,
+                                size_t sm_count, uint32_t *cta_begin, size_t cta_begin_len, size_t *n_ctas);
 /* One token through one layer without any allocation by the library.  It has no
  * counterpart in the reference.  For callers that cannot let a library allocate device
  * memory on their behalf: a server that gave all remaining device memory to its KV cache

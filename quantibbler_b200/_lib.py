@@ -71,6 +71,7 @@ _SIGNATURES = {
     "qk_layer_apply": (c_int32, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "qk_layer_apply_prefill": (c_int32, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "qk_layers_apply_prefill": (c_int32, [c_void_p, c_void_p, c_size_t, c_void_p, c_size_t, c_void_p]),
+    "qk_prefill_work_split": (c_int32, [c_size_t, c_void_p, c_void_p, c_size_t, c_void_p, c_size_t, c_void_p]),
     "qk_layers_apply_prefill_gated": (c_int32, [c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_size_t,
                                                 c_void_p]),
     "qk_layer_apply_noalloc": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -785,6 +785,30 @@ qk_status qk_layers_apply_prefill_gated(qk_ctx *ctx, const qk_layer *const *laye
     return apply_prefill(ctx, layers, n_layers, gate_dev, up_dev, n_tokens, y_devs);
 }
 
+qk_status qk_prefill_work_split(size_t n_problems, const size_t *tiles, const size_t *k_chunks,
+                                size_t sm_count, uint32_t *cta_begin, size_t cta_begin_len, size_t *n_ctas) {
+    if (n_problems == 0 || n_problems > (size_t)kMaxProblems || !tiles || !k_chunks || !cta_begin || !n_ctas)
+        return qk::fail(QK_ERR_VALUE, "qk_prefill_work_split: between 1 and %d problems and all arrays", kMaxProblems);
+    if (sm_count == 0) return qk::fail(QK_ERR_VALUE, "qk_prefill_work_split: sm_count must be positive");
+    GemmArgs g{};
+    size_t units = 0;
+    for (size_t p = 0; p < n_problems; ++p) {
+        if (tiles[p] == 0 || k_chunks[p] == 0)
+            return qk::fail(QK_ERR_VALUE, "qk_prefill_work_split: problem %zu is empty", p);
+        g.p[p].k_chunks = (uint32_t)k_chunks[p];
+        g.p[p].unit_begin = (uint32_t)units;
+        units += tiles[p] * k_chunks[p];
+    }
+    if (units >= (1ull << 32))
+        return qk::fail(QK_ERR_VALUE, "the work of one call must stay below 2^32 tile-chunks");
+    const unsigned n = plan_ctas(g, units, tiles, n_problems, (unsigned)std::min<size_t>(sm_count, 1u << 20));
+    if (cta_begin_len < (size_t)n + 1)
+        return qk::fail(QK_ERR_VALUE, "cta_begin holds %zu entries; %u are needed", cta_begin_len, n + 1);
+    for (unsigned i = 0; i <= n; ++i) cta_begin[i] = g.cta_begin[i];
+    *n_ctas = n;
+    return QK_OK;
+}
+
 qk_status qk_layer_apply_prefill(qk_ctx *ctx, const qk_layer *layer, const float *x_dev,
                                  size_t n_tokens, float *y_dev) {
     if (!layer) return qk::fail(QK_ERR_VALUE, "qk_layer_apply_prefill: layer is null");

@@ -281,3 +281,59 @@ def test_gpu_c_program_expectations_match_the_oracle(tmp_path):
     assert float(printed["expected layer checksum"]) == want_y
     if run.returncode == 77:
         assert "no CPU fallback" in run.stdout
+
+
+def test_prefill_work_split_invariants():
+    """How the tensor-core GEMM deals (tile, k-chunk) units out to its CTAs: every unit goes to
+    exactly one CTA, the runs are contiguous and in order, the grid never exceeds the SMs, and
+    when there are few tiles every tile goes to a whole number of CTAs in equal parts (at most
+    seven unless a run would then exceed sixteen k-chunks)."""
+    import ctypes
+    lib = _lib.lib()
+
+    def split(tiles, ks, sms=148):
+        n = len(tiles)
+        t = (ctypes.c_size_t * n)(*tiles)
+        k = (ctypes.c_size_t * n)(*ks)
+        out = (ctypes.c_uint32 * 200)()
+        got = ctypes.c_size_t()
+        assert lib.qk_prefill_work_split(n, t, k, sms, out, 200, ctypes.byref(got)) == 0
+        return list(out[:got.value + 1])
+
+    rng = np.random.default_rng(11)
+    cases = [([9, 4, 4], [64, 64, 64]), ([32, 8, 8], [18, 7, 7]), ([28], [64]), ([14], [224]),
+             ([9], [64]), ([224, 224], [27, 27]), ([1], [3]), ([1], [4096]), ([72, 32, 32], [64, 64, 64])]
+    for _ in range(200):
+        n = int(rng.integers(1, 5))
+        cases.append(([int(rng.integers(1, 60)) for _ in range(n)], [int(rng.integers(1, 300)) for _ in range(n)]))
+    for tiles, ks in cases:
+        for sms in (148, 132, 16):
+            b = split(tiles, ks, sms)
+            units = sum(t * k for t, k in zip(tiles, ks))
+            n_ctas = len(b) - 1
+            assert b[0] == 0 and b[-1] == units and 1 <= n_ctas <= sms, (tiles, ks, sms)
+            assert all(lo < hi for lo, hi in zip(b, b[1:])), (tiles, ks, sms)   # no empty CTA, in order
+            # tile borders in unit space
+            borders, at = {0}, 0
+            for t, k in zip(tiles, ks):
+                for _ in range(t):
+                    at += k
+                    borders.add(at)
+            if 2 * sum(tiles) <= max(1, min(sms, units // 8)) and set(b) >= borders:
+                # the aligned form: a tile's sharers have runs that differ by at most one chunk
+                at = 0
+                for t, k in zip(tiles, ks):
+                    for _ in range(t):
+                        runs = [hi - lo for lo, hi in zip(b, b[1:]) if at <= lo < at + k]
+                        assert sum(runs) == k and max(runs) - min(runs) <= 1, (tiles, ks, sms)
+                        assert len(runs) <= 7 or -(-k // 7) > 16, (tiles, ks, sms, len(runs))
+                        at += k
+    # the decode shapes of the Llama-3-8B-like stack at 64 tokens take the aligned form
+    b = split([9, 4, 4], [64, 64, 64])
+    assert len(b) - 1 == 17 * 7 and all(hi - lo in (9, 10) for lo, hi in zip(b, b[1:]))
+    # refusals
+    t1, k1 = (ctypes.c_size_t * 1)(4), (ctypes.c_size_t * 1)(8)
+    out, got = (ctypes.c_uint32 * 2)(), ctypes.c_size_t()
+    assert lib.qk_prefill_work_split(1, t1, k1, 148, out, 2, ctypes.byref(got)) == _lib.QK_ERR_VALUE
+    assert "are needed" in _lib.last_error()
+    assert lib.qk_prefill_work_split(0, t1, k1, 148, out, 2, ctypes.byref(got)) == _lib.QK_ERR_VALUE
